@@ -1,0 +1,276 @@
+"""ctypes binding of the CPU oracle (``xn_oracle.c``).
+
+TEST INFRASTRUCTURE ONLY: the checker for the CUDA library and the timed CPU
+baseline.  The product package never imports this module.
+
+The oracle restates the reference's ``fast_attention`` path
+(src/nn/fast_attention.rs:75-204, src/nn/fast_attention_simd.rs,
+src/tensor.rs:295-376, src/models/llama/mod.rs:210-265) in C with the same x86
+intrinsics; see the header of ``xn_oracle.c`` for the parity status.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "libxn_oracle.so")
+_lib = None
+
+ISA_AUTO, ISA_SCALAR, ISA_AVX2, ISA_AVX512 = 0, 1, 2, 3
+
+_f32p = C.POINTER(C.c_float)
+_sz = C.c_size_t
+
+
+def build(force: bool = False) -> str:
+    """Compile ``libxn_oracle.so`` beside the source if it is missing or stale."""
+    src = os.path.join(_HERE, "xn_oracle.c")
+    stale = (not os.path.exists(_LIB_PATH)) or os.path.getmtime(_LIB_PATH) < os.path.getmtime(src)
+    if force or stale:
+        subprocess.run(["make", "-C", _HERE, "-B", "libxn_oracle.so"], check=True,
+                       stdout=subprocess.DEVNULL)
+    return _LIB_PATH
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        build()
+        L = C.CDLL(_LIB_PATH)
+        L.xo_set_isa.argtypes = [C.c_int]
+        L.xo_set_isa.restype = C.c_int
+        L.xo_active_isa.restype = C.c_int
+        L.xo_max_threads.restype = C.c_int
+        L.xo_batched_dot_product.argtypes = [_f32p, _f32p, _sz, _sz, _sz, _sz, _sz, _f32p]
+        L.xo_batched_dot_product.restype = None
+        L.xo_softmax_inplace.argtypes = [_f32p, _sz]
+        L.xo_softmax_inplace.restype = None
+        L.xo_weighted_sum.argtypes = [_f32p, _f32p, _f32p, _sz, _sz, _sz, _sz]
+        L.xo_weighted_sum.restype = None
+        L.xo_rope_vec.argtypes = [_f32p, _f32p, _f32p, _sz]
+        L.xo_rope_vec.restype = None
+        L.xo_tensor_rope_inplace.argtypes = [_f32p, _sz, _sz, _sz, _f32p, _f32p, _sz]
+        L.xo_tensor_rope_inplace.restype = None
+        L.xo_rope_tables.argtypes = [C.c_float, _sz, _sz, C.c_float, C.c_float, C.c_float, _sz,
+                                     _f32p, _f32p]
+        L.xo_rope_tables.restype = None
+        L.xo_transpose_seq_to_heads.argtypes = [_f32p, _f32p, _sz, _sz, _sz]
+        L.xo_transpose_seq_to_heads.restype = None
+        L.xo_transpose_heads_to_seq.argtypes = [_f32p, _f32p, _sz, _sz, _sz]
+        L.xo_transpose_heads_to_seq.restype = None
+        L.xo_cache_new.argtypes = [_sz, _sz, _sz, _sz]
+        L.xo_cache_new.restype = C.c_void_p
+        L.xo_cache_free.argtypes = [C.c_void_p]
+        L.xo_cache_free.restype = None
+        L.xo_cache_k.argtypes = [C.c_void_p, _sz]
+        L.xo_cache_k.restype = _f32p
+        L.xo_cache_v.argtypes = [C.c_void_p, _sz]
+        L.xo_cache_v.restype = _f32p
+        L.xo_cache_append.argtypes = [C.c_void_p, _sz, _sz, _sz, _f32p, _f32p]
+        L.xo_cache_append.restype = None
+        L.xo_fast_attention.argtypes = [_f32p, _f32p, _f32p, _sz, _sz, C.c_void_p, _sz, _sz, _sz,
+                                        _sz, C.c_int, _sz, _f32p, C.c_int]
+        L.xo_fast_attention.restype = C.c_int
+        L.xo_fast_attention_streams.argtypes = [
+            _sz, C.POINTER(_f32p), C.POINTER(_f32p), C.POINTER(_f32p), _sz, C.POINTER(_sz),
+            C.POINTER(_sz), C.POINTER(C.c_void_p), _sz, _sz, _sz, C.POINTER(_f32p), C.c_int]
+        L.xo_fast_attention_streams.restype = C.c_int
+        _lib = L
+    return _lib
+
+
+def _p(a: np.ndarray):
+    assert a.dtype == np.float32 and a.flags["C_CONTIGUOUS"]
+    return a.ctypes.data_as(_f32p)
+
+
+def _f32(a) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def set_isa(isa: int) -> int:
+    return lib().xo_set_isa(isa)
+
+
+def active_isa() -> int:
+    return lib().xo_active_isa()
+
+
+def max_threads() -> int:
+    return lib().xo_max_threads()
+
+
+# --- primitives (fast_attention_simd.rs) ------------------------------------------------------
+
+def batched_dot_product(q, k_buf, h_kv, max_seq_len, head_dim, t_start, t_end) -> np.ndarray:
+    q, k_buf = _f32(q), _f32(k_buf)
+    out = np.zeros(max(16, t_end - t_start), dtype=np.float32)
+    lib().xo_batched_dot_product(_p(q), _p(k_buf), h_kv, max_seq_len, head_dim, t_start, t_end,
+                                 _p(out))
+    return out[: t_end - t_start]
+
+
+def softmax_inplace(scores) -> np.ndarray:
+    s = _f32(scores).copy()
+    lib().xo_softmax_inplace(_p(s), s.size)
+    return s
+
+
+def weighted_sum(scores, v_buf, h_kv, max_seq_len, head_dim, total_kv_len) -> np.ndarray:
+    scores, v_buf = _f32(scores), _f32(v_buf)
+    out = np.zeros(head_dim, dtype=np.float32)
+    lib().xo_weighted_sum(_p(out), _p(scores), _p(v_buf), h_kv, max_seq_len, head_dim, total_kv_len)
+    return out
+
+
+def rope_tables(theta, head_dim, max_pos, scaling=None):
+    """cos, sin tables ``[max_pos, head_dim // 2]`` (mod.rs:210-265).
+
+    ``scaling`` = (factor, low_freq_factor, high_freq_factor, original_max_pos) or None.
+    """
+    half = head_dim // 2
+    cos = np.zeros((max_pos, half), dtype=np.float32)
+    sin = np.zeros((max_pos, half), dtype=np.float32)
+    f, lo, hi, orig = scaling if scaling else (0.0, 1.0, 1.0, 0)
+    lib().xo_rope_tables(theta, head_dim, max_pos, f, lo, hi, orig, _p(cos), _p(sin))
+    return cos, sin
+
+
+def tensor_rope(x, cos, sin, index_pos) -> np.ndarray:
+    """FastTensor::rope_inplace (tensor.rs:295-316); x is [1, H, S, D].  Raises on non-4-D."""
+    x = _f32(x)
+    if x.ndim != 4:
+        raise ValueError(
+            f"rope_inplace: input must be 4D shape [b_sz, num_heads, seq_len, head_dim], got {list(x.shape)}")
+    out = x.copy()
+    _, H, S, D = out.shape
+    cos, sin = _f32(cos), _f32(sin)
+    lib().xo_tensor_rope_inplace(_p(out), H * out.shape[0], S, D, _p(cos), _p(sin), index_pos)
+    return out
+
+
+def transpose_seq_to_heads(x, num_heads, head_dim) -> np.ndarray:
+    x = _f32(x)
+    b, S, hidden = x.shape
+    if hidden != num_heads * head_dim:
+        raise ValueError("transpose_seq_to_heads: hidden_size must equal num_heads * head_dim")
+    out = np.empty((b, num_heads, S, head_dim), dtype=np.float32)
+    lib().xo_transpose_seq_to_heads(_p(x), _p(out), S, num_heads, head_dim)
+    return out
+
+
+def transpose_heads_to_seq(x) -> np.ndarray:
+    x = _f32(x)
+    b, H, S, D = x.shape
+    out = np.empty((b, S, H * D), dtype=np.float32)
+    lib().xo_transpose_heads_to_seq(_p(x), _p(out), S, H, D)
+    return out
+
+
+# --- cache + attention (fast_attention.rs) ----------------------------------------------------
+
+class RingCache:
+    """CpuRingCache (fast_attention.rs:18-60) without the write-only u8 shadow."""
+
+    def __init__(self, num_layers, num_kv_heads, max_seq_len, head_dim, use_u8=False):
+        self.num_layers, self.num_kv_heads = num_layers, num_kv_heads
+        self.max_seq_len, self.head_dim = max_seq_len, head_dim
+        self._h = lib().xo_cache_new(num_layers, num_kv_heads, max_seq_len, head_dim)
+        if not self._h:
+            raise MemoryError("xo_cache_new failed")
+
+    def _view(self, fn, layer):
+        n = self.num_kv_heads * self.max_seq_len * self.head_dim
+        return np.ctypeslib.as_array(fn(self._h, layer), shape=(n,))
+
+    def k_buffer(self, layer) -> np.ndarray:
+        """The reference's pub field ``k_buffers[layer]``: index h*cap*D + t*D + d."""
+        return self._view(lib().xo_cache_k, layer)
+
+    def v_buffer(self, layer) -> np.ndarray:
+        return self._view(lib().xo_cache_v, layer)
+
+    def append(self, layer, index_pos, k, v):
+        k, v = _f32(k), _f32(v)
+        S = k.shape[-2]
+        lib().xo_cache_append(self._h, layer, index_pos, S, _p(k), _p(v))
+
+    def close(self):
+        if self._h:
+            lib().xo_cache_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def fast_attention(q, k, v, layer_idx, index_pos, cache: RingCache, num_heads, num_kv_heads,
+                   head_dim, threads: int = 0) -> np.ndarray:
+    """fast_attention (fast_attention.rs:75-204).  Raises ValueError with the reference's
+    messages for the two checked shape errors (:86-92)."""
+    q, k, v = _f32(q), _f32(k), _f32(v)
+    if q.ndim != 4:
+        raise ValueError("fast_attention: Q shape must be 4D")
+    if q.shape[0] != 1:
+        raise ValueError(
+            f"fast_attention currently only supports batch size 1, got {q.shape[0]}")
+    S = q.shape[2]
+    out = np.zeros((1, num_heads, S, head_dim), dtype=np.float32)
+    rc = lib().xo_fast_attention(_p(q), _p(k), _p(v), layer_idx, index_pos, cache._h, num_heads,
+                                 num_kv_heads, head_dim, S, 4, 1, _p(out), threads)
+    assert rc == 0
+    return out
+
+
+def fast_attention_streams(qs, ks, vs, layer_idx, index_pos, caches, num_heads, num_kv_heads,
+                           head_dim, threads: int = 0):
+    """One fast_attention call per stream, (stream, KV head) pairs spread over host threads."""
+    n = len(qs)
+    qs = [_f32(a) for a in qs]
+    ks = [_f32(a) for a in ks]
+    vs = [_f32(a) for a in vs]
+    seq = [int(a.shape[-2]) for a in qs]
+    outs = [np.zeros((1, num_heads, s, head_dim), dtype=np.float32) for s in seq]
+    PA = _f32p * n
+    rc = lib().xo_fast_attention_streams(
+        n, PA(*[_p(a) for a in qs]), PA(*[_p(a) for a in ks]), PA(*[_p(a) for a in vs]), layer_idx,
+        (_sz * n)(*[int(p) for p in index_pos]), (_sz * n)(*seq),
+        (C.c_void_p * n)(*[c._h for c in caches]), num_heads, num_kv_heads, head_dim,
+        PA(*[_p(a) for a in outs]), threads)
+    assert rc == 0
+    return outs
+
+
+# --- independent f64 arbiter -------------------------------------------------------------------
+
+def naive_attention_f64(q, k_all, v_all, index_pos, num_heads, num_kv_heads, head_dim):
+    """Textbook causal GQA attention in float64 over the first index_pos+S cached tokens.
+
+    q [Hq, S, D]; k_all, v_all [Hkv, L, D] with L = index_pos + S.  Independent of the
+    restated code; plays the role candle plays in tests/fast_attention_tests.rs:15-91.
+    """
+    q = np.asarray(q, dtype=np.float64)
+    k_all = np.asarray(k_all, dtype=np.float64)
+    v_all = np.asarray(v_all, dtype=np.float64)
+    Hq, S, D = q.shape
+    G = num_heads // num_kv_heads
+    L = index_pos + S
+    scale = np.float64(np.float32(1.0) / np.sqrt(np.float32(head_dim)))
+    out = np.zeros((Hq, S, D), dtype=np.float64)
+    mask = np.arange(L)[None, :] > (index_pos + np.arange(S))[:, None]
+    for h in range(Hq):
+        kk, vv = k_all[h // G, :L], v_all[h // G, :L]
+        s = (q[h] @ kk.T) * scale
+        s[mask] = -np.inf
+        s -= s.max(axis=1, keepdims=True)
+        p = np.exp(s)
+        p /= p.sum(axis=1, keepdims=True)
+        out[h] = p @ vv
+    return out
