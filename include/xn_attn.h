@@ -1,0 +1,216 @@
+/*
+ * xn_attn.h -- C ABI of the B200 (sm_100a) replacement for xor-net's causal
+ * grouped-query attention path: `fast_attention` and the KV cache it owns.
+ *
+ * Every entry point is extern "C", takes plain pointers, integers and
+ * plain-old-data structs, returns an xn_status, never throws and never calls
+ * back.  A language binding (Rust FFI, ctypes, cgo ...) needs nothing else.
+ *
+ * Reference interface replaced (paths inside the xor-net source tree):
+ *   src/nn/fast_attention.rs:75-85    pub fn fast_attention(q, k, v, layer_idx,
+ *                                     index_pos, cache, num_heads, num_kv_heads, head_dim)
+ *   src/nn/fast_attention.rs:18-60    pub struct CpuRingCache + CpuRingCache::new
+ *   src/models/llama/mod.rs:210-265   RoPE table construction in Cache::new
+ *   src/tensor.rs:295-316             FastTensor::rope_inplace (fused entry only)
+ *
+ * Tensor layout contract (same as the reference): row-major f32,
+ *   q   [1, num_heads,    seq_len, head_dim]
+ *   k,v [1, num_kv_heads, seq_len, head_dim]
+ *   out [1, num_heads,    seq_len, head_dim]
+ * Query head h reads KV head h / (num_heads / num_kv_heads).
+ *
+ * Cache contract: logical coordinate (layer, kv_head, t, d) with the reference's
+ * ring rule slot = t % max_seq_len.  Storage is device memory in 64-token pages
+ * taken from one pool per context; a stream (= one reference `Cache`) owns a
+ * page table shared by all layers.  The reference's public `k_buffers` view is
+ * served by xn_kv_read / xn_kv_read_range.
+ */
+#ifndef XN_ATTN_H
+#define XN_ATTN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define XN_API __attribute__((visibility("default")))
+#else
+#define XN_API
+#endif
+
+typedef struct xn_ctx xn_ctx;       /* one per GPU: page pool, kernels' workspaces, CUDA stream */
+typedef struct xn_stream xn_stream; /* one per sequence: replaces one CpuRingCache            */
+
+typedef enum xn_status {
+    XN_OK = 0,
+    XN_ERR_ARG = 1,          /* null pointer, negative size, bad flag combination               */
+    XN_ERR_SHAPE = 2,        /* head counts / head_dim outside what the kernels support          */
+    XN_ERR_HANDLE = 3,       /* context or stream handle is not live                             */
+    XN_ERR_OUT_OF_PAGES = 4, /* page pool exhausted                                              */
+    XN_ERR_CAPACITY = 5,     /* position beyond the RoPE table, or request too large             */
+    XN_ERR_CUDA = 6,         /* a CUDA runtime call failed; text in xn_last_error                */
+    XN_ERR_DEVICE_WAIT = 7,  /* a kernel gave up on a bounded wait and reported it               */
+    XN_ERR_NO_TABLES = 8,    /* fused-RoPE entry used on a context created without cos/sin       */
+    XN_ERR_NOMEM = 9,        /* host allocation failed                                           */
+    XN_ERR_NO_DEVICE = 10    /* no usable CUDA device: there is no CPU fallback                  */
+} xn_status;
+
+/* Prefill kernel choice (xn_ctx_desc.prefill_mode). */
+enum {
+    XN_PREFILL_AUTO = 0, /* tensor-core TF32 kernel where the shape allows, exact f32 otherwise */
+    XN_PREFILL_F32 = 1,  /* always the exact-f32 CUDA-core path                                 */
+    XN_PREFILL_TF32 = 2  /* TF32 kernel whenever it supports the shape                          */
+};
+
+typedef struct xn_ctx_desc {
+    int32_t device;       /* CUDA ordinal                                                        */
+    int32_t num_layers;   /* CpuRingCache::new(num_layers, ...)   fast_attention.rs:31-34        */
+    int32_t num_heads;    /* query heads                                                         */
+    int32_t num_kv_heads; /* must divide num_heads                                               */
+    int32_t head_dim;     /* 1..256                                                              */
+    int32_t page_tokens;  /* 0 or 64                                                             */
+    int64_t pool_pages;   /* pages in the pool (each holds 64 tokens of every layer); if 0,      */
+    int64_t pool_bytes;   /*   derived from pool_bytes                                           */
+    uint64_t shuffle_seed;/* 0: pages handed out in ascending order; else a seeded permutation   */
+    int32_t max_pos;      /* rows of the RoPE tables, 0 if none                                  */
+    int32_t prefill_mode; /* XN_PREFILL_*                                                        */
+    const float* rope_cos;/* host [max_pos, head_dim/2] (models/llama/mod.rs:252-265), or NULL   */
+    const float* rope_sin;
+    void* cuda_stream;    /* cudaStream_t to launch on; NULL: the context creates its own        */
+    int32_t batch_window_us; /* how long a lone xn_attention caller waits for company            */
+    int32_t reserved;
+} xn_ctx_desc;
+
+/* Request flags. */
+enum {
+    XN_REQ_DEVICE_PTRS = 1u << 0, /* q,k,v,out are device pointers; the call only enqueues work  */
+    XN_REQ_ROPE = 1u << 1,        /* q,k are pre-RoPE; rotate with the context's tables          */
+    XN_REQ_SEQ_MAJOR = 1u << 2    /* q,k,v,out are [seq_len, heads*head_dim] (the layout before  */
+                                  /* transpose_seq_to_heads, tensor.rs:332-354, and after        */
+                                  /* transpose_heads_to_seq, tensor.rs:356-376)                  */
+};
+
+typedef struct xn_req {
+    xn_stream* stream;
+    int32_t layer;     /* layer_idx  */
+    int32_t seq_len;   /* new tokens in this call (1 = decode) */
+    int64_t index_pos; /* position of the first new token      */
+    const float* q;
+    const float* k;
+    const float* v;
+    float* out;
+    uint32_t flags;
+    uint32_t reserved;
+} xn_req;
+
+typedef struct xn_stats {
+    uint64_t calls;            /* requests served                                               */
+    uint64_t batches;          /* batched submissions (one group of launches each)              */
+    uint64_t kernel_launches;  /* kernels of this library launched                              */
+    uint64_t decode_launches;  /* launches of the split-KV attention kernel                     */
+    uint64_t prefill_launches; /* launches of the tiled prefill kernels                         */
+    uint64_t h2d_bytes;
+    uint64_t d2h_bytes;
+    uint64_t pages_total;
+    uint64_t pages_in_use;
+    uint64_t streams_live;
+    uint64_t device_wait_errors;
+    uint64_t coalesced_max;    /* largest number of blocking callers merged into one batch      */
+} xn_stats;
+
+/* ---- context --------------------------------------------------------------------------------- */
+
+/* Replaces the allocation half of CpuRingCache::new (fast_attention.rs:31-60) for all streams of
+ * one GPU: reserves the page pool once instead of max_seq_len rows per request. */
+XN_API int32_t xn_ctx_create(const xn_ctx_desc* desc, xn_ctx** out_ctx);
+XN_API int32_t xn_ctx_destroy(xn_ctx* ctx);
+/* Waits for everything enqueued on the context's CUDA stream; reports bounded-wait failures. */
+XN_API int32_t xn_ctx_synchronize(xn_ctx* ctx);
+/* The cudaStream_t the context launches on (for callers that time with CUDA events). */
+XN_API void* xn_ctx_cuda_stream(xn_ctx* ctx);
+XN_API int32_t xn_stats_get(xn_ctx* ctx, xn_stats* out);
+/* Text of the most recent failure on this context (or of context creation when ctx is NULL). */
+XN_API const char* xn_last_error(xn_ctx* ctx);
+
+/* ---- streams (one per reference `Cache`, models/llama/mod.rs:202-279) ------------------------ */
+
+/* max_seq_len is the reference's ring capacity (CpuRingCache.max_seq_len): positions fold modulo
+ * it.  Pages are taken from the pool only as positions are written. */
+XN_API int32_t xn_stream_create(xn_ctx* ctx, int64_t max_seq_len, xn_stream** out_stream);
+/* Forget all cached tokens and return the pages (a fresh Cache::new in the reference). */
+XN_API int32_t xn_stream_reset(xn_ctx* ctx, xn_stream* stream);
+XN_API int32_t xn_stream_destroy(xn_ctx* ctx, xn_stream* stream);
+
+/* ---- the hot path ---------------------------------------------------------------------------- */
+
+/* Drop-in for fast_attention (fast_attention.rs:75-204): host pointers, q and k already rotated.
+ * Appends k,v at positions index_pos.. then attends every new query row to positions
+ * 0..=index_pos+t.  Blocks until `out` is written.  Calls made at the same time from different
+ * threads (one per stream, as xor-net's server slots and batch_bench do) are merged into one
+ * batched launch. */
+XN_API int32_t xn_attention(xn_ctx* ctx, xn_stream* stream, int32_t layer, int64_t index_pos,
+                            int32_t seq_len, const float* q, const float* k, const float* v,
+                            float* out);
+
+/* Same, with q and k before RoPE: fuses FastTensor::rope_inplace (tensor.rs:295-316, call site
+ * models/llama/attention.rs:88-89) into the cache-append kernel. */
+XN_API int32_t xn_attention_rope(xn_ctx* ctx, xn_stream* stream, int32_t layer, int64_t index_pos,
+                                 int32_t seq_len, const float* q, const float* k, const float* v,
+                                 float* out);
+
+/* Explicit batch: n independent requests (distinct streams) in one submission.  With
+ * XN_REQ_DEVICE_PTRS on every request the call returns after enqueueing; otherwise it blocks
+ * until the host outputs are written.  Mixing host and device requests is an error. */
+XN_API int32_t xn_attention_batch(xn_ctx* ctx, int32_t n, const xn_req* reqs);
+
+/* ---- RoPE tables ----------------------------------------------------------------------------- */
+
+/* Builds cos/sin [max_pos, head_dim/2] exactly as Cache::new does (models/llama/mod.rs:210-265):
+ * f32 powf / cosf / sinf on the host.  factor <= 0 disables the Llama-3 frequency scaling
+ * (:226-249). */
+XN_API int32_t xn_rope_tables(float theta, int32_t head_dim, int32_t max_pos, float factor,
+                              float low_freq_factor, float high_freq_factor,
+                              int32_t original_max_pos, float* cos_out, float* sin_out);
+
+/* ---- cache inspection and synthetic fill (tests, benches) ------------------------------------ */
+
+/* One cached row: the reference's k_buffers[layer][h*cap*D + (t%cap)*D ..] (fast_attention.rs:
+ * 107-108).  Either output may be NULL.  Rows never written read as zeros. */
+XN_API int32_t xn_kv_read(xn_ctx* ctx, xn_stream* stream, int32_t layer, int32_t kv_head, int64_t t,
+                          float* k_row, float* v_row);
+/* Slots [t0, t0+n) of every KV head: k_out, v_out are [num_kv_heads, n, head_dim]. */
+XN_API int32_t xn_kv_read_range(xn_ctx* ctx, xn_stream* stream, int32_t layer, int64_t t0,
+                                int64_t n, float* k_out, float* v_out);
+/* Fills slots [t0, t0+n) of one layer with N(0,1) values from a counter-based generator on the
+ * device (no host copy) so that benchmarks can build large caches. */
+XN_API int32_t xn_kv_fill_normal(xn_ctx* ctx, xn_stream* stream, int32_t layer, int64_t t0,
+                                 int64_t n, uint64_t seed);
+/* N(0,1) fill of any device buffer with the same generator. */
+XN_API int32_t xn_fill_normal(xn_ctx* ctx, float* device_ptr, int64_t n, uint64_t seed);
+/* Number of cached positions of a stream in one layer (highest written position + 1). */
+XN_API int64_t xn_stream_len(xn_ctx* ctx, xn_stream* stream, int32_t layer);
+/* Copies the stream's page table (page ids in position order) into `out`; returns the count. */
+XN_API int64_t xn_stream_pages(xn_ctx* ctx, xn_stream* stream, int32_t* out, int64_t max_out);
+
+/* ---- host-side planning, exposed for tests (no GPU needed) ----------------------------------- */
+
+/* Splits `n_units` attention units of kv_len[i] cached tokens into tiles of `tile_tokens` and
+ * deals the tiles evenly to at most `max_ctas` thread blocks, the way the split-KV kernel is
+ * launched.  Outputs (capacity `max_items` items): item_unit, item_tile_begin, item_tile_end,
+ * item_part (-1 when the unit is covered by one block and written directly), and
+ * cta_item_begin[ctas+1].  Returns the number of thread blocks, or a negative xn_status. */
+XN_API int32_t xn_plan_split(int32_t n_units, const int32_t* kv_len, int32_t tile_tokens,
+                             int32_t max_ctas, int32_t max_items, int32_t* item_unit,
+                             int32_t* item_tile_begin, int32_t* item_tile_end, int32_t* item_part,
+                             int32_t* cta_item_begin, int32_t* n_items_out, int32_t* n_parts_out);
+
+/* Library build identification: "xn_attn <version> sm_100a". */
+XN_API const char* xn_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* XN_ATTN_H */

@@ -1,0 +1,120 @@
+"""CPU-only checks: the C-ABI library loads, exports every declared symbol, refuses to compute
+without a GPU, and the split-KV planner deals tiles correctly."""
+import ctypes as C
+import os
+import re
+
+import numpy as np
+import pytest
+
+import xor_net_b200 as xn
+
+
+def header_symbols(repo_root):
+    text = open(os.path.join(repo_root, "include", "xn_attn.h")).read()
+    return sorted(set(re.findall(r"XN_API\s+[\w\s\*]+?\b(xn_\w+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol(repo_root):
+    xn.build_library()
+    lib = C.CDLL(xn.LIB_PATH)
+    names = header_symbols(repo_root)
+    assert len(names) >= 20
+    for name in names:
+        assert hasattr(lib, name), f"{name} declared in include/xn_attn.h but not exported"
+    # the ctypes table covers the same set, so a binding cannot silently lag the header
+    assert sorted(xn.SIGNATURES) == names
+
+
+def test_version_string():
+    assert xn.load().xn_version() == b"xn_attn 0.1 sm_100a"
+
+
+def test_no_cpu_fallback_without_a_device():
+    import torch
+
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    with pytest.raises(xn.XnError) as e:
+        xn.Context(1, 2, 2, 4, pool_pages=4)
+    assert e.value.code == 10 and "no CPU fallback" in str(e.value)
+
+
+def test_ctx_create_argument_errors():
+    lib = xn.load()
+    from xor_net_b200._ffi import CtxDesc
+
+    h = C.c_void_p()
+    d = CtxDesc()
+    d.num_layers, d.num_heads, d.num_kv_heads, d.head_dim, d.pool_pages = 1, 5, 2, 8, 4
+    assert lib.xn_ctx_create(C.byref(d), C.byref(h)) == 2  # heads not a multiple of kv heads
+    d.num_heads, d.head_dim = 4, 300
+    assert lib.xn_ctx_create(C.byref(d), C.byref(h)) == 2
+    assert b"head_dim" in lib.xn_last_error(None)
+    assert lib.xn_ctx_create(None, C.byref(h)) == 1
+    assert lib.xn_ctx_destroy(None) == 3
+    assert lib.xn_attention(None, None, 0, 0, 1, None, None, None, None) == 3
+
+
+def test_rope_tables_match_oracle_bitwise():
+    import oracle as xo
+
+    for theta, D, scaling in [(500000.0, 128, None), (10000.0, 100, None),
+                              (500000.0, 128, (8.0, 1.0, 4.0, 8192))]:
+        c1, s1 = xn.rope_tables(theta, D, 300, scaling)
+        c2, s2 = xo.rope_tables(theta, D, 300, scaling)
+        assert np.array_equal(c1, c2) and np.array_equal(s1, s2)
+
+
+def run_plan(kv_len, tile, max_ctas):
+    lib = xn.load()
+    kv = np.asarray(kv_len, dtype=np.int32)
+    cap = len(kv) + max_ctas + 8
+    arrs = [np.zeros(cap, np.int32) for _ in range(4)]
+    cta = np.zeros(max_ctas + 1, np.int32)
+    n_items, n_parts = C.c_int32(), C.c_int32()
+    P = lambda a: a.ctypes.data_as(C.POINTER(C.c_int32))
+    ctas = lib.xn_plan_split(len(kv), P(kv), tile, max_ctas, cap, P(arrs[0]), P(arrs[1]),
+                             P(arrs[2]), P(arrs[3]), P(cta), C.byref(n_items), C.byref(n_parts))
+    assert ctas >= 0
+    n = n_items.value
+    return ctas, [a[:n] for a in arrs], cta[:ctas + 1], n_parts.value
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_plan_split_covers_every_tile_once_and_balances(seed):
+    rng = np.random.default_rng(seed)
+    n_units = int(rng.integers(1, 400))
+    kv = rng.integers(1, 4097, n_units)
+    tile, max_ctas = 64, 148
+    ctas, (unit, tb, te, part), cta, n_parts = run_plan(kv, tile, max_ctas)
+    tiles = (kv + tile - 1) // tile
+    assert ctas == min(max_ctas, tiles.sum())
+    cover = [np.zeros(t, np.int32) for t in tiles]
+    for u, b, e in zip(unit, tb, te):
+        assert 0 <= b < e <= tiles[u]
+        cover[u][b:e] += 1
+    assert all(np.all(c == 1) for c in cover)
+    per_cta = [int(sum(te[i] - tb[i] for i in range(cta[b], cta[b + 1]))) for b in range(ctas)]
+    assert max(per_cta) - min(per_cta) <= 1
+    # units cut across blocks get consecutive partial slots; whole units are written directly
+    counts = np.bincount(unit, minlength=n_units)
+    assert n_parts == int(counts[counts > 1].sum())
+    for u in range(n_units):
+        p = part[unit == u]
+        if counts[u] == 1:
+            assert p[0] == -1
+        else:
+            assert np.array_equal(np.sort(p), np.arange(p.min(), p.min() + counts[u]))
+    used = part[part >= 0]
+    assert np.array_equal(np.sort(used), np.arange(n_parts))
+
+
+def test_plan_split_edge_cases():
+    ctas, (unit, tb, te, part), cta, n_parts = run_plan([1], 64, 148)
+    assert ctas == 1 and list(unit) == [0] and list(part) == [-1] and n_parts == 0
+    ctas, (unit, tb, te, part), cta, n_parts = run_plan([64 * 300], 64, 148)
+    assert ctas == 148 and n_parts == 148 and np.all(unit == 0)
+    ctas, items, cta, n_parts = run_plan([], 64, 148)
+    assert ctas == 0
+    assert xn.load().xn_plan_split(1, None, 64, 148, 8, None, None, None, None, None, None, None) < 0

@@ -1,0 +1,297 @@
+"""Parity of the CUDA path with the CPU oracle on identical seeded inputs, through the C ABI.
+
+Tolerance of the f32 path (gpu_util.ABS_TOL / REL_TOL): max abs <= 1e-4 and relative L2 <= 1e-5.
+Cache contents (append, fused RoPE) must be bit-identical.
+"""
+import numpy as np
+import pytest
+
+import oracle as xo
+import xor_net_b200 as xn
+from gpu_util import Pair, assert_parity, errs, rand_qkv
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ctx2b():
+    c = xn.Context(num_layers=3, num_heads=20, num_kv_heads=5, head_dim=128, pool_pages=600,
+                   shuffle_seed=11, rope=xn.rope_tables(500000.0, 128, 8192))
+    yield c
+    c.close()
+
+
+# ---- head dims and group sizes of the reference's primitive tests ------------------------------
+
+@pytest.mark.parametrize("D", [2, 4, 7, 8, 9, 15, 16, 17, 31, 32, 33, 64, 100, 128, 160, 256])
+def test_head_dims(D):
+    rng = np.random.default_rng(D)
+    for Hq, Hkv in [(4, 2), (3, 3), (8, 2)]:
+        ctx = xn.Context(2, Hq, Hkv, D, pool_pages=16)
+        p = Pair(ctx, 300)
+        q, k, v = rand_qkv(rng, Hq, Hkv, 70, D)
+        got, want = p.step(1, 0, q, k, v)                 # prefill across a page boundary
+        assert_parity(got, want, f"prefill D={D} Hq={Hq} Hkv={Hkv}")
+        for pos in (70, 71):
+            q, k, v = rand_qkv(rng, Hq, Hkv, 1, D)
+            got, want = p.step(1, pos, q, k, v)
+            assert_parity(got, want, f"decode D={D} pos={pos}")
+        p.check_cache(1)
+        ctx.close()
+
+
+@pytest.mark.parametrize("Hq,Hkv", [(1, 1), (2, 1), (3, 1), (4, 1), (5, 1), (8, 1), (12, 4), (32, 8), (20, 5)])
+def test_group_sizes(Hq, Hkv):
+    rng = np.random.default_rng(Hq * 100 + Hkv)
+    ctx = xn.Context(1, Hq, Hkv, 64, pool_pages=16)
+    p = Pair(ctx, 512)
+    q, k, v = rand_qkv(rng, Hq, Hkv, 130, 64)
+    got, want = p.step(0, 0, q, k, v)
+    assert_parity(got, want, f"G={Hq // Hkv} prefill")
+    q, k, v = rand_qkv(rng, Hq, Hkv, 1, 64)
+    got, want = p.step(0, 130, q, k, v)
+    assert_parity(got, want, f"G={Hq // Hkv} decode")
+    ctx.close()
+
+
+# ---- lengths around page (64) and tile boundaries, one token at a time ------------------------
+
+def test_decode_lengths_around_boundaries(ctx2b):
+    rng = np.random.default_rng(5)
+    for L in [1, 2, 31, 32, 33, 63, 64, 65, 127, 128, 129, 191, 192, 193, 1000]:
+        p = Pair(ctx2b, 2048)
+        if L > 1:
+            kk = rng.standard_normal((1, 5, L - 1, 128)).astype(np.float32)
+            vv = rng.standard_normal((1, 5, L - 1, 128)).astype(np.float32)
+            qq = rng.standard_normal((1, 20, L - 1, 128)).astype(np.float32)
+            p.step(0, 0, qq, kk, vv)
+        q, k, v = rand_qkv(rng, 20, 5, 1, 128)
+        got, want = p.step(0, L - 1, q, k, v)
+        assert_parity(got, want, f"L={L}")
+        p.st.destroy()
+
+
+def test_config1_decode_shape(ctx2b):
+    # BitNet-2B shape, one query token over 1024 cached tokens (first BASELINE config)
+    rng = np.random.default_rng(299792458)
+    p = Pair(ctx2b, 4096)
+    qq, kk, vv = rand_qkv(rng, 20, 5, 1023, 128)
+    p.step(2, 0, qq, kk, vv)
+    q, k, v = rand_qkv(rng, 20, 5, 1, 128)
+    got, want = p.step(2, 1023, q, k, v)
+    a, r = assert_parity(got, want, "config 1")
+    k_all, v_all = p.st.read_range(2, 0, 1024)
+    f64 = xo.naive_attention_f64(q[0], k_all, v_all, 1023, 20, 5, 128)
+    ga, gr = errs(got[0], f64)
+    ra, rr = errs(want[0], f64)
+    print(f"config1: gpu-vs-oracle abs {a:.2e} rel {r:.2e}; gpu-vs-f64 rel {gr:.2e}; oracle-vs-f64 rel {rr:.2e}")
+    assert gr <= 1e-5
+    p.st.destroy()
+
+
+# ---- reference quirks ------------------------------------------------------------------------
+
+def test_chunked_prefill_and_overwrite(ctx2b):
+    # chunked prefill (index_pos > 0 with seq_len > 1) and re-append at existing positions
+    # (speculative decoding replays positions) are legal in the reference
+    rng = np.random.default_rng(17)
+    p = Pair(ctx2b, 1024)
+    pos = 0
+    for S in (100, 57, 1, 200):
+        q, k, v = rand_qkv(rng, 20, 5, S, 128)
+        got, want = p.step(1, pos, q, k, v)
+        assert_parity(got, want, f"chunk at {pos}+{S}")
+        pos += S
+    q, k, v = rand_qkv(rng, 20, 5, 30, 128)       # overwrite positions 300..329
+    got, want = p.step(1, 300, q, k, v)
+    assert_parity(got, want, "overwrite")
+    p.check_cache(1)
+    p.st.destroy()
+
+
+def test_gap_positions_read_as_zeros(ctx2b):
+    # starting at index_pos > 0 on an empty cache: skipped positions are zero rows that still
+    # take part in the softmax (the reference never masks them)
+    rng = np.random.default_rng(23)
+    for _ in range(2):  # second round reuses pages that held other data
+        p = Pair(ctx2b, 512)
+        q, k, v = rand_qkv(rng, 20, 5, 3, 128)
+        got, want = p.step(0, 150, q, k, v)
+        assert_parity(got, want, "gap")
+        p.check_cache(0)
+        junk = rand_qkv(rng, 20, 5, 400, 128)
+        p.step(0, 0, *junk)
+        p.st.destroy()
+
+
+def test_ring_fold_matches_oracle():
+    # positions beyond the capacity fold with % capacity and overwritten slots are visited again
+    rng = np.random.default_rng(29)
+    ctx = xn.Context(1, 4, 2, 16, pool_pages=8)
+    p = Pair(ctx, 100)
+    pos = 0
+    for S in (60, 30, 25, 1, 1, 140):
+        q, k, v = rand_qkv(rng, 4, 2, S, 16)
+        got, want = p.step(0, pos, q, k, v)
+        assert_parity(got, want, f"fold at {pos}+{S}")
+        pos += S
+    p.check_cache(0)
+    ctx.close()
+
+
+# ---- fused RoPE + append: bit-exact cache, parity of the output ---------------------------------
+
+@pytest.mark.parametrize("theta,D,Hq,Hkv", [(500000.0, 128, 20, 5), (10000.0, 100, 8, 8)])
+def test_fused_rope_is_bit_exact(theta, D, Hq, Hkv):
+    rng = np.random.default_rng(31)
+    cos, sin = xn.rope_tables(theta, D, 1024)
+    ctx = xn.Context(1, Hq, Hkv, D, pool_pages=16, rope=(cos, sin))
+    st = ctx.new_stream(1024)
+    ref = xo.RingCache(1, Hkv, 1024, D)
+    pos = 0
+    for S in (90, 1, 1, 45):
+        q, k, v = rand_qkv(rng, Hq, Hkv, S, D)
+        got = ctx.attention(st, 0, pos, q, k, v, rope=True)
+        qr, kr = xo.tensor_rope(q, cos, sin, pos), xo.tensor_rope(k, cos, sin, pos)
+        want = xo.fast_attention(qr, kr, v, 0, pos, ref, Hq, Hkv, D)
+        assert_parity(got, want, f"rope S={S}")
+        pos += S
+    kd, vd = st.read_range(0, 0, 1024)
+    assert np.array_equal(kd.ravel(), ref.k_buffer(0)), "rotated keys differ in some bit"
+    assert np.array_equal(vd.ravel(), ref.v_buffer(0))
+    with pytest.raises(xn.XnError) as e:  # position beyond the table
+        ctx.attention(st, 0, 1024, *rand_qkv(rng, Hq, Hkv, 1, D), rope=True)
+    assert e.value.code == 5
+    ctx.close()
+
+
+def test_rope_entry_needs_tables():
+    ctx = xn.Context(1, 2, 2, 8, pool_pages=4)
+    st = ctx.new_stream(64)
+    rng = np.random.default_rng(1)
+    with pytest.raises(xn.XnError) as e:
+        ctx.attention(st, 0, 0, *rand_qkv(rng, 2, 2, 1, 8), rope=True)
+    assert e.value.code == 8
+    ctx.close()
+
+
+# ---- batches of independent streams (the server's shape), ragged lengths ----------------------
+
+def test_batched_ragged_decode(ctx2b):
+    # config-3 shape at reduced stream count: per-stream lengths uniform in [128, 4096] would need
+    # a larger pool; lengths here span the same page-count range more sparsely
+    rng = np.random.default_rng(37)
+    lens = [128, 129, 700, 64, 1, 2000, 333, 65, 1023, 1025, 4, 512]
+    pairs = [Pair(ctx2b, 4096) for _ in lens]
+    for p, L in zip(pairs, lens):
+        if L > 1:
+            p.step(1, 0, *rand_qkv(rng, 20, 5, L - 1, 128))
+    for step in range(2):
+        qs, ks, vs = zip(*[tuple(a for a in rand_qkv(rng, 20, 5, 1, 128)) for _ in lens])
+        pos = [L - 1 + step for L in lens]
+        outs = ctx2b.attention_batch([p.st for p in pairs], 1, pos, qs, ks, vs)
+        wants = xo.fast_attention_streams(qs, ks, vs, 1, pos, [p.ref for p in pairs], 20, 5, 128)
+        for i, (g, w) in enumerate(zip(outs, wants)):
+            assert_parity(g, w, f"stream {i} len {lens[i]} step {step}")
+    for p in pairs:
+        p.check_cache(1)
+        p.st.destroy()
+
+
+def test_batch_mixes_prefill_and_decode_and_layers(ctx2b):
+    rng = np.random.default_rng(41)
+    pairs = [Pair(ctx2b, 1024) for _ in range(4)]
+    seqs, layers, poss = [50, 1, 200, 1], [0, 1, 2, 0], [0, 0, 0, 0]
+    pairs[3].step(0, 0, *rand_qkv(rng, 20, 5, 77, 128))
+    poss[3] = 77
+    qkv = [rand_qkv(rng, 20, 5, S, 128) for S in seqs]
+    outs = ctx2b.attention_batch([p.st for p in pairs], layers, poss, [a[0] for a in qkv],
+                                 [a[1] for a in qkv], [a[2] for a in qkv])
+    for i, p in enumerate(pairs):
+        want = xo.fast_attention(*qkv[i], layers[i], poss[i], p.ref, 20, 5, 128)
+        assert_parity(outs[i], want, f"mixed request {i}")
+        p.st.destroy()
+
+
+def test_seq_major_layout(ctx2b):
+    # [S, H*D] in and out: the layouts either side of transpose_seq_to_heads / heads_to_seq
+    rng = np.random.default_rng(43)
+    p = Pair(ctx2b, 512)
+    q, k, v = rand_qkv(rng, 20, 5, 37, 128)
+    want = xo.fast_attention(q, k, v, 0, 0, p.ref, 20, 5, 128)
+    outs = ctx2b.attention_batch([p.st], 0, [0], [xo.transpose_heads_to_seq(q)],
+                                 [xo.transpose_heads_to_seq(k)], [xo.transpose_heads_to_seq(v)],
+                                 seq_major=True)
+    assert_parity(xo.transpose_seq_to_heads(outs[0], 20, 128), want, "seq-major")
+    p.st.destroy()
+
+
+def test_concurrent_blocking_callers_are_coalesced(ctx2b):
+    # one thread per stream, each blocking in xn_attention per layer, as the reference's server
+    # slots and batch_bench do; results must equal the one-by-one oracle
+    import threading
+
+    rng = np.random.default_rng(47)
+    n, steps = 8, 6
+    pairs = [Pair(ctx2b, 512) for _ in range(n)]
+    data = [[rand_qkv(rng, 20, 5, 1, 128) for _ in range(steps)] for _ in range(n)]
+    got = [[None] * steps for _ in range(n)]
+    errors = []
+    barrier = threading.Barrier(n)
+
+    def worker(i):
+        try:
+            for s in range(steps):
+                barrier.wait()
+                got[i][s] = ctx2b.attention(pairs[i].st, s % 3, s // 3, *data[i][s])
+        except Exception as e:  # pragma: no cover
+            errors.append(e)
+            barrier.abort()
+
+    ts = [threading.Thread(target=worker, args=(i,)) for i in range(n)]
+    [t.start() for t in ts]
+    [t.join() for t in ts]
+    assert not errors, errors
+    for i in range(n):
+        for s in range(steps):
+            want = xo.fast_attention(*data[i][s], s % 3, s // 3, pairs[i].ref, 20, 5, 128)
+            assert_parity(got[i][s], want, f"thread {i} step {s}")
+    assert ctx2b.stats()["coalesced_max"] >= 2
+    for p in pairs:
+        p.st.destroy()
+
+
+# ---- allocator and error behaviour -----------------------------------------------------------
+
+def test_pool_exhaustion_and_reuse():
+    ctx = xn.Context(1, 2, 2, 8, pool_pages=3)
+    rng = np.random.default_rng(53)
+    a, b = ctx.new_stream(1024), ctx.new_stream(1024)
+    ctx.attention(a, 0, 0, *rand_qkv(rng, 2, 2, 128, 8))       # 2 pages
+    with pytest.raises(xn.XnError) as e:
+        ctx.attention(b, 0, 0, *rand_qkv(rng, 2, 2, 128, 8))   # needs 2, 1 left
+    assert e.value.code == 4
+    assert ctx.stats()["pages_in_use"] == 3
+    a.reset()
+    b.reset()
+    assert ctx.stats()["pages_in_use"] == 0
+    ctx.attention(b, 0, 0, *rand_qkv(rng, 2, 2, 128, 8))
+    assert len(set(b.pages().tolist())) == 2
+    assert b.length(0) == 128
+    a.destroy()
+    with pytest.raises(xn.XnError) as e:
+        ctx.attention_batch([b, b], 0, [128, 128], *[[rand_qkv(rng, 2, 2, 1, 8)[j]] * 2 for j in range(3)])
+    assert e.value.code == 1
+    ctx.close()
+
+
+def test_shuffled_page_table_is_a_permutation():
+    ctx = xn.Context(1, 2, 2, 8, pool_pages=64, shuffle_seed=99)
+    st = ctx.new_stream(64 * 64)
+    st.fill_normal(0, 0, 64 * 64, 5)
+    pages = st.pages()
+    assert sorted(pages.tolist()) == list(range(64)) and pages.tolist() != sorted(pages.tolist())
+    k, v = st.read_range(0, 0, 64 * 64)
+    assert abs(float(k.mean())) < 0.02 and abs(float(k.std()) - 1.0) < 0.02
+    assert abs(float(v.mean())) < 0.02 and not np.array_equal(k, v)
+    ctx.close()

@@ -1,0 +1,16 @@
+"""B200 (sm_100a) implementation of xor-net's causal GQA attention path.
+
+The compute lives in ``libxn_attn.so`` (hand-written CUDA + C ABI, see ``include/xn_attn.h``);
+this package is the Python host side.  Importing it never falls back to a CPU path: calls raise
+if the library is not built or no sm_100 device is present.
+"""
+from ._build import LIB_PATH, build_library
+from .api import (Context, DeviceKvCache, FastTensor, Stream, XnError, close_default_contexts,
+                  default_context, fast_attention, rope_tables)
+from ._ffi import REQ_DEVICE_PTRS, REQ_ROPE, REQ_SEQ_MAJOR, SIGNATURES, load
+
+__all__ = [
+    "Context", "Stream", "DeviceKvCache", "FastTensor", "XnError", "fast_attention", "rope_tables",
+    "default_context", "close_default_contexts", "build_library", "load", "LIB_PATH", "SIGNATURES",
+    "REQ_DEVICE_PTRS", "REQ_ROPE", "REQ_SEQ_MAJOR",
+]

@@ -1,0 +1,336 @@
+"""Python host side over the C ABI.
+
+Two layers:
+
+* ``Context`` / ``Stream``: thin handles over ``xn_ctx`` / ``xn_stream`` with numpy (host) and
+  raw-pointer (device) calls.  Used by the benchmark and the batch tests.
+* ``FastTensor`` / ``DeviceKvCache`` / ``fast_attention``: the reference's operator interface for
+  this path with the same names, argument order and error behaviour
+  (src/nn/fast_attention.rs:18-60, :75-85; src/tensor.rs:6-40), so that tests written against the
+  reference read the same here.  ``DeviceKvCache`` stands where ``CpuRingCache`` stood.
+
+All compute happens in the CUDA library; nothing here falls back to numpy or torch.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import threading
+from typing import Optional, Sequence
+
+import numpy as np
+
+from . import _ffi
+from ._ffi import REQ_DEVICE_PTRS, REQ_ROPE, REQ_SEQ_MAJOR, CtxDesc, Req, Stats
+
+
+class XnError(RuntimeError):
+    """A non-zero xn_status; ``code`` is the status, the text comes from xn_last_error."""
+
+    def __init__(self, code: int, text: str):
+        super().__init__(f"{_ffi.STATUS_NAMES.get(code, code)}: {text}")
+        self.code = code
+        self.text = text
+
+
+def _f32(a) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _ptr(a: np.ndarray) -> int:
+    return a.ctypes.data
+
+
+def rope_tables(theta: float, head_dim: int, max_pos: int, scaling=None):
+    """cos, sin ``[max_pos, head_dim // 2]`` as Cache::new builds them (models/llama/mod.rs:210-265).
+
+    ``scaling`` = (factor, low_freq_factor, high_freq_factor, original_max_position_embeddings).
+    """
+    lib = _ffi.load()
+    half = head_dim // 2
+    cos = np.zeros((max_pos, half), dtype=np.float32)
+    sin = np.zeros((max_pos, half), dtype=np.float32)
+    f, lo, hi, orig = scaling if scaling else (0.0, 1.0, 1.0, 0)
+    rc = lib.xn_rope_tables(theta, head_dim, max_pos, f, lo, hi, orig,
+                            cos.ctypes.data_as(_ffi.c_f32p), sin.ctypes.data_as(_ffi.c_f32p))
+    if rc != 0:
+        raise XnError(rc, "xn_rope_tables: bad argument")
+    return cos, sin
+
+
+class Stream:
+    """One sequence's KV cache (one reference ``Cache``)."""
+
+    def __init__(self, ctx: "Context", handle: int, max_seq_len: int):
+        self.ctx, self.handle, self.max_seq_len = ctx, handle, max_seq_len
+
+    def reset(self):
+        self.ctx._check(self.ctx.lib.xn_stream_reset(self.ctx.handle, self.handle))
+
+    def destroy(self):
+        if self.handle and self.ctx.handle:
+            self.ctx._check(self.ctx.lib.xn_stream_destroy(self.ctx.handle, self.handle))
+        self.handle = None
+
+    def length(self, layer: int) -> int:
+        return int(self.ctx.lib.xn_stream_len(self.ctx.handle, self.handle, layer))
+
+    def pages(self) -> np.ndarray:
+        n = int(self.ctx.lib.xn_stream_pages(self.ctx.handle, self.handle, None, 0))
+        out = np.zeros(max(n, 1), dtype=np.int32)
+        self.ctx.lib.xn_stream_pages(self.ctx.handle, self.handle, out.ctypes.data_as(_ffi.c_i32p), n)
+        return out[:n]
+
+    def fill_normal(self, layer: int, t0: int, n: int, seed: int):
+        """N(0,1) fill of slots [t0, t0+n) on the device; layer -1 fills every layer."""
+        self.ctx._check(self.ctx.lib.xn_kv_fill_normal(self.ctx.handle, self.handle, layer, t0, n, seed))
+
+    def read_range(self, layer: int, t0: int, n: int):
+        """(k, v) each ``[Hkv, n, D]``: slots t0..t0+n of the logical ring."""
+        c = self.ctx
+        k = np.zeros((c.num_kv_heads, n, c.head_dim), dtype=np.float32)
+        v = np.zeros_like(k)
+        c._check(c.lib.xn_kv_read_range(c.handle, self.handle, layer, t0, n, _ptr(k), _ptr(v)))
+        return k, v
+
+    def read(self, layer: int, kv_head: int, t: int):
+        c = self.ctx
+        k = np.zeros(c.head_dim, dtype=np.float32)
+        v = np.zeros_like(k)
+        c._check(c.lib.xn_kv_read(c.handle, self.handle, layer, kv_head, t, _ptr(k), _ptr(v)))
+        return k, v
+
+
+class Context:
+    """One GPU's page pool and launch state (``xn_ctx``)."""
+
+    def __init__(self, num_layers: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                 pool_pages: int = 0, pool_bytes: int = 0, device: int = 0, shuffle_seed: int = 0,
+                 rope: Optional[tuple] = None, cuda_stream: int = 0, prefill_mode: int = 0,
+                 batch_window_us: int = 0):
+        self.lib = _ffi.load()
+        self.num_layers, self.num_heads = num_layers, num_heads
+        self.num_kv_heads, self.head_dim = num_kv_heads, head_dim
+        self.device = device
+        d = CtxDesc()
+        d.device, d.num_layers, d.num_heads = device, num_layers, num_heads
+        d.num_kv_heads, d.head_dim, d.page_tokens = num_kv_heads, head_dim, 64
+        d.pool_pages, d.pool_bytes, d.shuffle_seed = pool_pages, pool_bytes, shuffle_seed
+        d.prefill_mode, d.batch_window_us = prefill_mode, batch_window_us
+        d.cuda_stream = cuda_stream or None
+        self._rope = None
+        if rope is not None:
+            cos, sin = _f32(rope[0]), _f32(rope[1])
+            self._rope = (cos, sin)
+            d.max_pos, d.rope_cos, d.rope_sin = cos.shape[0], _ptr(cos), _ptr(sin)
+        h = C.c_void_p()
+        rc = self.lib.xn_ctx_create(C.byref(d), C.byref(h))
+        if rc != 0:
+            raise XnError(rc, (self.lib.xn_last_error(None) or b"").decode())
+        self.handle = h.value
+
+    def _check(self, rc: int):
+        if rc != 0:
+            raise XnError(rc, (self.lib.xn_last_error(self.handle) or b"").decode())
+
+    def close(self):
+        if getattr(self, "handle", None):
+            self.lib.xn_ctx_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def new_stream(self, max_seq_len: int) -> Stream:
+        h = C.c_void_p()
+        self._check(self.lib.xn_stream_create(self.handle, max_seq_len, C.byref(h)))
+        return Stream(self, h.value, max_seq_len)
+
+    def synchronize(self):
+        self._check(self.lib.xn_ctx_synchronize(self.handle))
+
+    def cuda_stream(self) -> int:
+        return int(self.lib.xn_ctx_cuda_stream(self.handle) or 0)
+
+    def stats(self) -> dict:
+        s = Stats()
+        self._check(self.lib.xn_stats_get(self.handle, C.byref(s)))
+        return {n: int(getattr(s, n)) for n, _ in Stats._fields_}
+
+    def fill_normal(self, device_ptr: int, n: int, seed: int):
+        self._check(self.lib.xn_fill_normal(self.handle, device_ptr, n, seed))
+
+    # -- blocking single-stream calls (host arrays) ------------------------------------------
+
+    def attention(self, stream: Stream, layer: int, index_pos: int, q, k, v, rope: bool = False):
+        """xn_attention / xn_attention_rope.  q [1,Hq,S,D], k,v [1,Hkv,S,D] -> out [1,Hq,S,D]."""
+        q, k, v = _f32(q), _f32(k), _f32(v)
+        S = q.shape[-2]
+        out = np.empty((1, self.num_heads, S, self.head_dim), dtype=np.float32)
+        fn = self.lib.xn_attention_rope if rope else self.lib.xn_attention
+        self._check(fn(self.handle, stream.handle, layer, index_pos, S, _ptr(q), _ptr(k), _ptr(v),
+                       _ptr(out)))
+        return out
+
+    # -- explicit batches -------------------------------------------------------------------
+
+    def make_batch(self, entries: Sequence[tuple], flags: int = 0):
+        """entries: (stream, layer, index_pos, seq_len, q_ptr, k_ptr, v_ptr, out_ptr) -> Req array."""
+        arr = (Req * len(entries))()
+        for i, (st, layer, pos, S, q, k, v, o) in enumerate(entries):
+            r = arr[i]
+            r.stream, r.layer, r.seq_len, r.index_pos = st.handle, layer, S, pos
+            r.q, r.k, r.v, r.out, r.flags = q, k, v, o, flags
+        return arr
+
+    def submit(self, reqs, n: Optional[int] = None):
+        self._check(self.lib.xn_attention_batch(self.handle, len(reqs) if n is None else n, reqs))
+
+    def attention_batch(self, streams, layer, index_pos, qs, ks, vs, rope=False, seq_major=False):
+        """Host-array batch: one request per stream; returns the list of outputs."""
+        qs = [_f32(a) for a in qs]
+        ks = [_f32(a) for a in ks]
+        vs = [_f32(a) for a in vs]
+        seq = [a.shape[-2] for a in qs]  # [1,H,S,D] and [1,S,H*D] both keep S there
+        outs = [np.empty_like(a) for a in qs]
+        layers = layer if isinstance(layer, (list, tuple)) else [layer] * len(streams)
+        flags = (REQ_ROPE if rope else 0) | (REQ_SEQ_MAJOR if seq_major else 0)
+        reqs = self.make_batch(
+            [(st, layers[i], int(index_pos[i]), int(seq[i]), _ptr(qs[i]), _ptr(ks[i]), _ptr(vs[i]),
+              _ptr(outs[i])) for i, st in enumerate(streams)], flags)
+        self.submit(reqs)
+        return outs
+
+
+# =============================================================================================
+# The reference's operator interface for this path
+# =============================================================================================
+
+class FastTensor:
+    """``FastTensor { data: Vec<f32>, shape: Vec<usize> }`` (src/tensor.rs:6-33)."""
+
+    def __init__(self, data, shape):
+        self.data = _f32(data).reshape(-1)
+        self.shape = list(int(s) for s in shape)
+        assert self.data.size == int(np.prod(self.shape)) if self.shape else True, \
+            f"FastTensor::new shape mismatch: data len is {self.data.size}"
+
+    @staticmethod
+    def new(data, shape) -> "FastTensor":
+        return FastTensor(data, shape)
+
+    @staticmethod
+    def zeros(shape) -> "FastTensor":
+        return FastTensor(np.zeros(int(np.prod(shape)), np.float32), shape)
+
+    def dims(self):
+        return self.shape
+
+    def array(self) -> np.ndarray:
+        return self.data.reshape(self.shape)
+
+
+_contexts: dict = {}
+_contexts_lock = threading.Lock()
+
+
+def default_context(num_layers, num_heads, num_kv_heads, head_dim, device: int = 0) -> Context:
+    """Process-wide context per (device, model shape), created on first use.
+
+    Pool size: ``XORNET_ATTN_POOL_PAGES`` pages if set, else ``XORNET_ATTN_POOL_MB`` (default 1024)
+    megabytes.
+    """
+    key = (device, num_layers, num_heads, num_kv_heads, head_dim)
+    with _contexts_lock:
+        ctx = _contexts.get(key)
+        if ctx is None or ctx.handle is None:
+            pages = int(os.environ.get("XORNET_ATTN_POOL_PAGES", "0"))
+            mb = int(os.environ.get("XORNET_ATTN_POOL_MB", "1024"))
+            ctx = Context(num_layers, num_heads, num_kv_heads, head_dim, pool_pages=pages,
+                          pool_bytes=0 if pages else mb << 20, device=device)
+            _contexts[key] = ctx
+        return ctx
+
+
+def close_default_contexts():
+    with _contexts_lock:
+        for ctx in _contexts.values():
+            ctx.close()
+        _contexts.clear()
+
+
+class DeviceKvCache:
+    """Stands where ``CpuRingCache`` stood (src/nn/fast_attention.rs:18-60).
+
+    Same constructor arguments.  Storage is pages of a device pool; the reference's pub fields
+    ``k_buffers`` / ``v_buffers`` are read-back views with the reference's index
+    ``h*cap*D + t*D + d``.  ``use_u8`` is accepted and ignored: the reference's u8 shadow
+    (:62-71, :117-128) is written but never read, so it cannot influence any result.
+    """
+
+    def __init__(self, num_layers, num_kv_heads, max_seq_len, head_dim, use_u8=False, device=0):
+        self.num_layers, self.num_kv_heads = num_layers, num_kv_heads
+        self.max_seq_len, self.head_dim = max_seq_len, head_dim
+        self.device = device
+        self._ctx: Optional[Context] = None
+        self._stream: Optional[Stream] = None
+
+    @staticmethod
+    def new(num_layers, num_kv_heads, max_seq_len, head_dim, use_u8=False) -> "DeviceKvCache":
+        return DeviceKvCache(num_layers, num_kv_heads, max_seq_len, head_dim, use_u8)
+
+    def _bind(self, num_heads: int):
+        if self._stream is None:
+            self._ctx = default_context(self.num_layers, num_heads, self.num_kv_heads,
+                                        self.head_dim, self.device)
+            self._stream = self._ctx.new_stream(self.max_seq_len)
+        return self._ctx, self._stream
+
+    def _buffers(self, which: int):
+        n = self.num_kv_heads * self.max_seq_len * self.head_dim
+        if self._stream is None:
+            return [np.zeros(n, np.float32) for _ in range(self.num_layers)]
+        return [self._stream.read_range(l, 0, self.max_seq_len)[which].reshape(-1)
+                for l in range(self.num_layers)]
+
+    @property
+    def k_buffers(self):
+        return self._buffers(0)
+
+    @property
+    def v_buffers(self):
+        return self._buffers(1)
+
+    def close(self):
+        if self._stream is not None:
+            self._stream.destroy()
+            self._stream = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def fast_attention(q: FastTensor, k: FastTensor, v: FastTensor, layer_idx: int, index_pos: int,
+                   cache: DeviceKvCache, num_heads: int, num_kv_heads: int,
+                   head_dim: int) -> FastTensor:
+    """``fast_attention`` (src/nn/fast_attention.rs:75-204) on the GPU.
+
+    Raises ``ValueError`` with the reference's messages for its two checked errors (:86-92);
+    anything the library rejects raises ``XnError``.
+    """
+    if len(q.shape) != 4:
+        raise ValueError("fast_attention: Q shape must be 4D")
+    b_sz, _, seq_len, _ = q.shape
+    if b_sz != 1:
+        raise ValueError(f"fast_attention currently only supports batch size 1, got {b_sz}")
+    ctx, stream = cache._bind(num_heads)
+    out = ctx.attention(stream, layer_idx, index_pos, q.data.reshape(1, num_heads, seq_len, head_dim),
+                        k.data.reshape(1, num_kv_heads, seq_len, head_dim),
+                        v.data.reshape(1, num_kv_heads, seq_len, head_dim))
+    return FastTensor(out, [b_sz, num_heads, seq_len, head_dim])

@@ -1,0 +1,1020 @@
+// C ABI, context, page allocator, batch planner and launch logic of the sm_100a attention
+// library.  Declarations and the reference interfaces they replace: include/xn_attn.h.
+#include "../../include/xn_attn.h"
+
+#include <algorithm>
+#include <chrono>
+#include <condition_variable>
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <unordered_set>
+#include <vector>
+
+#include "xn_append.cuh"
+#include "xn_common.cuh"
+#include "xn_decode.cuh"
+#include "xn_plan.hpp"
+
+using namespace xn;
+
+namespace {
+
+constexpr uint32_t kCtxMagic = 0x786e4354u;     // "xnCT"
+constexpr uint32_t kStreamMagic = 0x786e5354u;  // "xnST"
+constexpr int kPlanSlots = 4;
+constexpr long long kMaxUnits = 1ll << 22;
+
+std::mutex g_err_mu;
+std::string g_create_error;
+
+struct PlanSlot {
+    unsigned char* host = nullptr;
+    unsigned char* dev = nullptr;
+    size_t cap = 0;
+    cudaEvent_t ev = nullptr;
+    bool used = false;
+};
+
+struct Pending {
+    xn_req req;
+    int32_t status = XN_OK;
+    bool done = false;
+};
+
+}  // namespace
+
+struct xn_stream {
+    uint32_t magic = kStreamMagic;
+    xn_ctx* ctx = nullptr;
+    int64_t cap = 0;
+    std::vector<int32_t> pages;   // page id of slots [64*i, 64*i+64)
+    std::vector<int64_t> hw;      // per layer: highest written position + 1
+};
+
+struct xn_ctx {
+    uint32_t magic = kCtxMagic;
+    int device = 0, num_layers = 0, num_heads = 0, num_kv_heads = 0, head_dim = 0;
+    int group = 1, gt = 1, subs = 1;  // query heads per KV head; heads per unit; units per KV head
+    int nv = 0;                       // float4 per cached row (row length padded to 4 floats)
+    int nv_class = 0;                 // template NV of the kernel instantiation
+    bool nv_exact = false;
+    int tile_tokens = 64;
+    float scale = 1.f;
+    long long pool_pages = 0;
+    int max_pos = 0;
+    int prefill_mode = 0;
+    int batch_window_us = 0;
+    int sm_count = 0;
+    int decode_ctas = 0;
+    cudaStream_t stream = nullptr;
+    bool own_stream = false;
+    float* k_pool = nullptr;
+    float* v_pool = nullptr;
+    float* cos_d = nullptr;
+    float* sin_d = nullptr;
+    std::vector<int32_t> free_pages;  // stack: back() is handed out next
+    std::unordered_set<xn_stream*> streams;
+
+    std::mutex mu;  // serialises submissions and every mutation below
+    PlanSlot slots[kPlanSlots];
+    int next_slot = 0;
+    float* q_rot = nullptr;    size_t q_rot_cap = 0;      // floats
+    float* partials = nullptr; size_t partials_cap = 0;   // floats
+    unsigned char* io_host = nullptr; unsigned char* io_dev = nullptr; size_t io_cap = 0;
+    int* status_d = nullptr;
+    int* status_h = nullptr;  // pinned
+    xn_stats stats{};
+    std::string last_error;
+
+    // combining of concurrent blocking callers
+    std::mutex q_mu;
+    std::condition_variable q_cv;
+    std::vector<Pending*> queue;
+    bool leader_active = false;
+};
+
+namespace {
+
+int32_t fail(xn_ctx* ctx, int32_t code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    if (ctx) {
+        ctx->last_error = buf;
+    } else {
+        std::lock_guard<std::mutex> g(g_err_mu);
+        g_create_error = buf;
+    }
+    return code;
+}
+
+#define XN_CUDA(ctx, expr)                                                                    \
+    do {                                                                                      \
+        cudaError_t e__ = (expr);                                                             \
+        if (e__ != cudaSuccess)                                                               \
+            return fail(ctx, XN_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(e__));   \
+    } while (0)
+
+bool ctx_ok(const xn_ctx* c) { return c && c->magic == kCtxMagic; }
+bool stream_ok(const xn_ctx* c, const xn_stream* s) {
+    return s && s->magic == kStreamMagic && s->ctx == c;
+}
+
+size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// ---- kernel dispatch table ---------------------------------------------------------------
+
+using SplitFn = void (*)(const ReqDev*, const UnitDev*, const ItemDev*, const int*, const int*,
+                         const float*, const float*, float*, long long, int, int, int, float, int*);
+using MergeFn = void (*)(const ReqDev*, const UnitDev*, const int*, int, const float*, int, int);
+
+struct SplitKernel {
+    SplitFn fn;
+    size_t smem;
+    int threads;
+};
+
+template <int NV, int GT>
+SplitKernel make_split() {
+    return {attn_splitkv_kernel<NV, GT>, DecodeSmem<NV, GT>::kBytes, DecodeCfg<NV>::kThreads};
+}
+
+template <int NV>
+SplitKernel pick_gt(int gt) {
+    if (gt == 4) return make_split<NV, 4>();
+    if (gt == 2) return make_split<NV, 2>();
+    return make_split<NV, 1>();
+}
+
+SplitKernel pick_split(int nv_class, int gt) {
+    switch (nv_class) {
+        case 8: return pick_gt<8>(gt);
+        case 16: return pick_gt<16>(gt);
+        case 25: return pick_gt<25>(gt);
+        case 32: return pick_gt<32>(gt);
+        default: return pick_gt<64>(gt);
+    }
+}
+
+MergeFn pick_merge(int gt) {
+    if (gt == 4) return attn_merge_kernel<4>;
+    if (gt == 2) return attn_merge_kernel<2>;
+    return attn_merge_kernel<1>;
+}
+
+int nv_class_for(int nv) {
+    if (nv == 25) return 25;
+    if (nv <= 8) return 8;
+    if (nv <= 16) return 16;
+    if (nv <= 32) return 32;
+    return 64;
+}
+
+// ---- buffers -----------------------------------------------------------------------------
+
+int32_t grow_device(xn_ctx* c, float** buf, size_t* cap, size_t need_floats) {
+    if (need_floats <= *cap) return XN_OK;
+    XN_CUDA(c, cudaStreamSynchronize(c->stream));  // nothing in flight may still use the old one
+    if (*buf) XN_CUDA(c, cudaFree(*buf));
+    *buf = nullptr;
+    *cap = 0;
+    size_t want = std::max(need_floats, size_t(1) << 18);
+    want = align_up(want + want / 4, 1024);
+    XN_CUDA(c, cudaMalloc(reinterpret_cast<void**>(buf), want * sizeof(float)));
+    *cap = want;
+    return XN_OK;
+}
+
+int32_t grow_io(xn_ctx* c, size_t need_bytes) {
+    if (need_bytes <= c->io_cap) return XN_OK;
+    XN_CUDA(c, cudaStreamSynchronize(c->stream));
+    if (c->io_host) XN_CUDA(c, cudaFreeHost(c->io_host));
+    if (c->io_dev) XN_CUDA(c, cudaFree(c->io_dev));
+    c->io_host = c->io_dev = nullptr;
+    c->io_cap = 0;
+    size_t want = align_up(std::max(need_bytes + need_bytes / 4, size_t(1) << 20), 4096);
+    XN_CUDA(c, cudaMallocHost(reinterpret_cast<void**>(&c->io_host), want));
+    XN_CUDA(c, cudaMalloc(reinterpret_cast<void**>(&c->io_dev), want));
+    c->io_cap = want;
+    return XN_OK;
+}
+
+int32_t acquire_slot(xn_ctx* c, size_t need_bytes, PlanSlot** out) {
+    PlanSlot& s = c->slots[c->next_slot];
+    c->next_slot = (c->next_slot + 1) % kPlanSlots;
+    if (s.used) XN_CUDA(c, cudaEventSynchronize(s.ev));
+    s.used = false;
+    if (need_bytes > s.cap) {
+        if (s.host) XN_CUDA(c, cudaFreeHost(s.host));
+        if (s.dev) XN_CUDA(c, cudaFree(s.dev));
+        s.host = s.dev = nullptr;
+        s.cap = 0;
+        size_t want = align_up(std::max(need_bytes * 2, size_t(1) << 16), 4096);
+        XN_CUDA(c, cudaMallocHost(reinterpret_cast<void**>(&s.host), want));
+        XN_CUDA(c, cudaMalloc(reinterpret_cast<void**>(&s.dev), want));
+        s.cap = want;
+    }
+    if (!s.ev) XN_CUDA(c, cudaEventCreateWithFlags(&s.ev, cudaEventDisableTiming));
+    *out = &s;
+    return XN_OK;
+}
+
+int32_t ensure_pages(xn_ctx* c, xn_stream* s, int64_t slots_needed) {
+    const int64_t need = (slots_needed + kPageTokens - 1) / kPageTokens;
+    while (int64_t(s->pages.size()) < need) {
+        if (c->free_pages.empty())
+            return fail(c, XN_ERR_OUT_OF_PAGES, "page pool exhausted (%lld pages, all in use)",
+                        c->pool_pages);
+        s->pages.push_back(c->free_pages.back());
+        c->free_pages.pop_back();
+    }
+    return XN_OK;
+}
+
+void release_pages(xn_ctx* c, xn_stream* s) {
+    for (auto it = s->pages.rbegin(); it != s->pages.rend(); ++it) c->free_pages.push_back(*it);
+    s->pages.clear();
+    std::fill(s->hw.begin(), s->hw.end(), 0);
+}
+
+int32_t check_device_status(xn_ctx* c) {
+    if (*c->status_h != kDevOk) {
+        int code = *c->status_h;
+        *c->status_h = kDevOk;
+        c->stats.device_wait_errors += 1;
+        cudaMemsetAsync(c->status_d, 0, sizeof(int), c->stream);
+        return fail(c, XN_ERR_DEVICE_WAIT, "a kernel gave up on a bounded wait (code %d)", code);
+    }
+    return XN_OK;
+}
+
+// ---- one batched submission ----------------------------------------------------------------
+
+struct GapFill {
+    int req;
+    int64_t slot0, n;
+};
+
+// Validates one request against the context; returns XN_OK or the error (text in last_error).
+int32_t validate_req(xn_ctx* c, const xn_req& r) {
+    if (!stream_ok(c, r.stream)) return fail(c, XN_ERR_HANDLE, "stream handle is not live");
+    if (r.layer < 0 || r.layer >= c->num_layers)
+        return fail(c, XN_ERR_ARG, "layer %d outside 0..%d", r.layer, c->num_layers - 1);
+    if (r.seq_len < 0 || r.index_pos < 0) return fail(c, XN_ERR_ARG, "negative seq_len or index_pos");
+    if (r.seq_len > 0 && (!r.q || !r.k || !r.v || !r.out)) return fail(c, XN_ERR_ARG, "null tensor pointer");
+    if (r.index_pos + r.seq_len > (int64_t(1) << 30))
+        return fail(c, XN_ERR_CAPACITY, "position %lld too large", (long long)(r.index_pos + r.seq_len));
+    if (r.flags & XN_REQ_ROPE) {
+        if (!c->cos_d) return fail(c, XN_ERR_NO_TABLES, "context was created without RoPE tables");
+        if (r.index_pos + r.seq_len > c->max_pos)
+            return fail(c, XN_ERR_CAPACITY, "position %lld beyond the RoPE table (%d rows)",
+                        (long long)(r.index_pos + r.seq_len), c->max_pos);
+    }
+    return XN_OK;
+}
+
+// reqs[i] are valid, on distinct streams, all host-mode or all device-mode.
+int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
+    const int Hq = c->num_heads, Hkv = c->num_kv_heads, D = c->head_dim, nv = c->nv;
+    XN_CUDA(c, cudaSetDevice(c->device));
+
+    // -- pages, gaps, staging sizes
+    std::vector<GapFill> gaps;
+    size_t io_in = 0, io_out = 0, qrot_floats = 0, n_page_ids = 0;
+    long long n_units = 0, n_ring_rows = 0;
+    int max_rows = 0;
+    for (int i = 0; i < n; ++i) {
+        const xn_req& r = reqs[i];
+        if (r.seq_len == 0) continue;
+        xn_stream* s = r.stream;
+        const int64_t end = r.index_pos + r.seq_len;
+        int32_t rc = ensure_pages(c, s, std::min<int64_t>(end, s->cap));
+        if (rc != XN_OK) return rc;
+        int64_t& hw = s->hw[r.layer];
+        if (r.index_pos > hw && hw < s->cap)
+            gaps.push_back({i, hw, std::min<int64_t>(r.index_pos, s->cap) - hw});
+        hw = std::max(hw, end);
+        n_page_ids += s->pages.size();
+        const size_t qf = size_t(Hq) * r.seq_len * D, kvf = size_t(Hkv) * r.seq_len * D;
+        if (host_mode) {
+            io_in += align_up(qf * 4, 16) + 2 * align_up(kvf * 4, 16);
+            io_out += align_up(qf * 4, 16);
+        }
+        if (r.flags & XN_REQ_ROPE) qrot_floats += align_up(qf, 4);
+        if (end > s->cap) n_ring_rows += r.seq_len;
+        else n_units += (long long)r.seq_len * Hkv * c->subs;
+        max_rows = std::max<long long>(max_rows, (long long)r.seq_len * (Hq + 2 * Hkv));
+    }
+    if (n_units > kMaxUnits)
+        return fail(c, XN_ERR_CAPACITY, "%lld attention rows in one submission exceed the limit %lld",
+                    n_units, kMaxUnits);
+
+    int32_t rc;
+    if ((rc = grow_device(c, &c->q_rot, &c->q_rot_cap, qrot_floats)) != XN_OK) return rc;
+    if (host_mode && (rc = grow_io(c, io_in + io_out)) != XN_OK) return rc;
+
+    // -- request descriptors, page ids, units
+    std::vector<ReqDev> rd(n);
+    std::vector<int32_t> page_ids;
+    page_ids.reserve(n_page_ids);
+    std::vector<UnitDev> units;
+    units.reserve(size_t(n_units));
+    std::vector<int32_t> kv_lens;
+    kv_lens.reserve(size_t(n_units));
+    std::vector<int32_t> ring_rows;
+    size_t in_off = 0, out_off = io_in, qrot_off = 0;
+    for (int i = 0; i < n; ++i) {
+        const xn_req& r = reqs[i];
+        ReqDev& d = rd[i];
+        memset(&d, 0, sizeof d);
+        if (r.seq_len == 0) continue;
+        xn_stream* s = r.stream;
+        const int S = r.seq_len;
+        const size_t qf = size_t(Hq) * S * D, kvf = size_t(Hkv) * S * D;
+        const float *q_dev = r.q, *k_dev = r.k, *v_dev = r.v;
+        float* o_dev = r.out;
+        if (host_mode) {
+            memcpy(c->io_host + in_off, r.q, qf * 4);
+            q_dev = reinterpret_cast<const float*>(c->io_dev + in_off);
+            in_off += align_up(qf * 4, 16);
+            memcpy(c->io_host + in_off, r.k, kvf * 4);
+            k_dev = reinterpret_cast<const float*>(c->io_dev + in_off);
+            in_off += align_up(kvf * 4, 16);
+            memcpy(c->io_host + in_off, r.v, kvf * 4);
+            v_dev = reinterpret_cast<const float*>(c->io_dev + in_off);
+            in_off += align_up(kvf * 4, 16);
+            o_dev = reinterpret_cast<float*>(c->io_dev + out_off);
+            out_off += align_up(qf * 4, 16);
+        }
+        const bool seq_major = r.flags & XN_REQ_SEQ_MAJOR;
+        const long long q_hs = seq_major ? D : (long long)S * D, q_ts = seq_major ? (long long)Hq * D : D;
+        const long long kv_hs = seq_major ? D : (long long)S * D, kv_ts = seq_major ? (long long)Hkv * D : D;
+        d.q_in = q_dev; d.qi_hs = q_hs; d.qi_ts = q_ts;
+        if (r.flags & XN_REQ_ROPE) {
+            d.q = c->q_rot + qrot_off;
+            d.q_hs = (long long)S * D; d.q_ts = D;
+            qrot_off += align_up(qf, 4);
+            d.flags = 1u;
+        } else {
+            d.q = q_dev; d.q_hs = q_hs; d.q_ts = q_ts;
+        }
+        d.k = k_dev; d.v = v_dev; d.kv_hs = kv_hs; d.kv_ts = kv_ts;
+        d.out = o_dev; d.o_hs = q_hs; d.o_ts = q_ts;
+        d.page_off = int(page_ids.size());
+        d.n_pages = int(s->pages.size());
+        page_ids.insert(page_ids.end(), s->pages.begin(), s->pages.end());
+        d.layer = r.layer; d.seq_len = S; d.index_pos = int(r.index_pos);
+        d.cap = int(std::min<int64_t>(s->cap, int64_t(1) << 30));
+        if (r.index_pos + S > s->cap) {
+            for (int t = 0; t < S; ++t) { ring_rows.push_back(i); ring_rows.push_back(t); }
+        } else {
+            for (int h = 0; h < Hkv; ++h)
+                for (int sb = 0; sb < c->subs; ++sb)
+                    for (int t = 0; t < S; ++t) {
+                        UnitDev u;
+                        u.req = i; u.kv_head = h;
+                        u.head0 = h * c->group + sb * c->gt;
+                        u.nheads = std::min(c->gt, c->group - sb * c->gt);
+                        u.t_q = t; u.kv_len = int(r.index_pos) + t + 1;
+                        u.part_begin = -1; u.part_count = 1;
+                        units.push_back(u);
+                        kv_lens.push_back(u.kv_len);
+                    }
+        }
+    }
+
+    SplitPlan sp = plan_split(kv_lens.data(), int(units.size()), c->tile_tokens, c->decode_ctas);
+    std::vector<int32_t> merge_units;
+    for (size_t u = 0; u < units.size(); ++u) {
+        units[u].part_begin = sp.unit_part_begin[u];
+        units[u].part_count = sp.unit_part_count[u];
+        if (sp.unit_part_count[u] > 1) merge_units.push_back(int32_t(u));
+    }
+    if ((rc = grow_device(c, &c->partials, &c->partials_cap,
+                          size_t(sp.n_parts) * c->gt * part_stride_floats(nv))) != XN_OK)
+        return rc;
+
+    // -- pack the plan: one pinned buffer, one copy
+    size_t off = 0;
+    auto place = [&](size_t bytes) { size_t o = off; off = align_up(off + bytes, 16); return o; };
+    const size_t o_req = place(sizeof(ReqDev) * n);
+    const size_t o_unit = place(sizeof(UnitDev) * units.size());
+    const size_t o_item = place(sizeof(ItemDev) * sp.items.size());
+    const size_t o_cta = place(sizeof(int32_t) * sp.cta_item_begin.size());
+    const size_t o_page = place(sizeof(int32_t) * page_ids.size());
+    const size_t o_merge = place(sizeof(int32_t) * merge_units.size());
+    const size_t o_ring = place(sizeof(int32_t) * ring_rows.size());
+    PlanSlot* slot = nullptr;
+    if ((rc = acquire_slot(c, off, &slot)) != XN_OK) return rc;
+    memcpy(slot->host + o_req, rd.data(), sizeof(ReqDev) * n);
+    if (!units.empty()) memcpy(slot->host + o_unit, units.data(), sizeof(UnitDev) * units.size());
+    static_assert(sizeof(SplitItem) == sizeof(ItemDev), "plan item layouts must match");
+    if (!sp.items.empty()) memcpy(slot->host + o_item, sp.items.data(), sizeof(ItemDev) * sp.items.size());
+    memcpy(slot->host + o_cta, sp.cta_item_begin.data(), sizeof(int32_t) * sp.cta_item_begin.size());
+    if (!page_ids.empty()) memcpy(slot->host + o_page, page_ids.data(), sizeof(int32_t) * page_ids.size());
+    if (!merge_units.empty()) memcpy(slot->host + o_merge, merge_units.data(), sizeof(int32_t) * merge_units.size());
+    if (!ring_rows.empty()) memcpy(slot->host + o_ring, ring_rows.data(), sizeof(int32_t) * ring_rows.size());
+    XN_CUDA(c, cudaMemcpyAsync(slot->dev, slot->host, off, cudaMemcpyHostToDevice, c->stream));
+    c->stats.h2d_bytes += off;
+    const ReqDev* reqs_d = reinterpret_cast<const ReqDev*>(slot->dev + o_req);
+    const UnitDev* units_d = reinterpret_cast<const UnitDev*>(slot->dev + o_unit);
+    const ItemDev* items_d = reinterpret_cast<const ItemDev*>(slot->dev + o_item);
+    const int* cta_d = reinterpret_cast<const int*>(slot->dev + o_cta);
+    const int* pages_d = reinterpret_cast<const int*>(slot->dev + o_page);
+    const int* merge_d = reinterpret_cast<const int*>(slot->dev + o_merge);
+    const int* ring_d = reinterpret_cast<const int*>(slot->dev + o_ring);
+
+    if (host_mode && io_in) {
+        XN_CUDA(c, cudaMemcpyAsync(c->io_dev, c->io_host, io_in, cudaMemcpyHostToDevice, c->stream));
+        c->stats.h2d_bytes += io_in;
+    }
+
+    // -- launches
+    for (const GapFill& g : gaps) {
+        const long long total = g.n * Hkv * D;
+        const int blocks = int(std::min<long long>((total + 255) / 256, 4096));
+        slots_fill_kernel<<<blocks, 256, 0, c->stream>>>(
+            pages_d + rd[g.req].page_off, c->k_pool, c->v_pool, c->pool_pages, rd[g.req].layer, Hkv,
+            D, nv, g.slot0, g.n, 0, 0ull);
+        c->stats.kernel_launches += 1;
+    }
+    if (max_rows > 0) {
+        dim3 grid(unsigned(std::min<long long>((max_rows + 7) / 8, 2048)), unsigned(n));
+        rope_append_kernel<<<grid, 256, 0, c->stream>>>(reqs_d, pages_d, c->k_pool, c->v_pool,
+                                                        c->cos_d, c->sin_d, c->pool_pages, Hq, Hkv,
+                                                        D, nv);
+        c->stats.kernel_launches += 1;
+    }
+    if (sp.ctas > 0) {
+        SplitKernel k = pick_split(c->nv_class, c->gt);
+        k.fn<<<sp.ctas, k.threads, k.smem, c->stream>>>(reqs_d, units_d, items_d, cta_d, pages_d,
+                                                        c->k_pool, c->v_pool, c->partials,
+                                                        c->pool_pages, Hkv, D, nv, c->scale,
+                                                        c->status_d);
+        c->stats.kernel_launches += 1;
+        c->stats.decode_launches += 1;
+        if (!merge_units.empty()) {
+            const int warps = int(merge_units.size()) * c->gt;
+            pick_merge(c->gt)<<<(warps + 3) / 4, 128, 0, c->stream>>>(
+                reqs_d, units_d, merge_d, int(merge_units.size()), c->partials, nv, D);
+            c->stats.kernel_launches += 1;
+        }
+    }
+    if (!ring_rows.empty()) {
+        const int rows = int(ring_rows.size() / 2);
+        attn_ring_kernel<<<rows * Hq, 256, 0, c->stream>>>(reqs_d, ring_d, rows, pages_d, c->k_pool,
+                                                           c->v_pool, c->pool_pages, Hq, Hkv, D, nv,
+                                                           c->scale);
+        c->stats.kernel_launches += 1;
+    }
+    XN_CUDA(c, cudaGetLastError());
+
+    if (host_mode) {
+        if (io_out) {
+            XN_CUDA(c, cudaMemcpyAsync(c->io_host + io_in, c->io_dev + io_in, io_out,
+                                       cudaMemcpyDeviceToHost, c->stream));
+            c->stats.d2h_bytes += io_out;
+        }
+        XN_CUDA(c, cudaMemcpyAsync(c->status_h, c->status_d, sizeof(int), cudaMemcpyDeviceToHost,
+                                   c->stream));
+    }
+    XN_CUDA(c, cudaEventRecord(slot->ev, c->stream));
+    slot->used = true;
+    c->stats.batches += 1;
+    c->stats.calls += uint64_t(n);
+
+    if (host_mode) {
+        XN_CUDA(c, cudaStreamSynchronize(c->stream));
+        if ((rc = check_device_status(c)) != XN_OK) return rc;
+        size_t o = io_in;
+        for (int i = 0; i < n; ++i) {
+            if (reqs[i].seq_len == 0) continue;
+            const size_t qf = size_t(Hq) * reqs[i].seq_len * D;
+            memcpy(reqs[i].out, c->io_host + o, qf * 4);
+            o += align_up(qf * 4, 16);
+        }
+    }
+    return XN_OK;
+}
+
+// Runs a group of blocking host-pointer requests as one submission.  Requests that fail
+// validation, or that name a stream already in the group, get their own status and are left out.
+void run_group(xn_ctx* c, std::vector<Pending*>& group) {
+    std::lock_guard<std::mutex> g(c->mu);
+    std::vector<xn_req> ok;
+    std::vector<Pending*> ok_p;
+    std::unordered_set<xn_stream*> seen;
+    for (Pending* p : group) {
+        int32_t rc = validate_req(c, p->req);
+        if (rc == XN_OK && !seen.insert(p->req.stream).second)
+            rc = fail(c, XN_ERR_ARG, "two concurrent calls on one stream");
+        p->status = rc;
+        if (rc == XN_OK) {
+            ok.push_back(p->req);
+            ok_p.push_back(p);
+        }
+    }
+    if (!ok.empty()) {
+        int32_t rc = submit_locked(c, int(ok.size()), ok.data(), true);
+        for (Pending* p : ok_p) p->status = rc;
+        c->stats.coalesced_max = std::max<uint64_t>(c->stats.coalesced_max, ok.size());
+    }
+}
+
+int32_t attention_blocking(xn_ctx* c, const xn_req& req) {
+    Pending me;
+    me.req = req;
+    std::unique_lock<std::mutex> lk(c->q_mu);
+    c->queue.push_back(&me);
+    while (!me.done) {
+        if (!c->leader_active) {
+            c->leader_active = true;
+            if (c->batch_window_us > 0) {
+                const size_t target = std::max<size_t>(1, c->streams.size());
+                c->q_cv.wait_for(lk, std::chrono::microseconds(c->batch_window_us),
+                                 [&] { return c->queue.size() >= target; });
+            }
+            std::vector<Pending*> group;
+            group.swap(c->queue);
+            lk.unlock();
+            run_group(c, group);
+            lk.lock();
+            for (Pending* p : group) p->done = true;
+            c->leader_active = false;
+            c->q_cv.notify_all();
+        } else {
+            c->q_cv.notify_all();  // lets a leader that is waiting for company re-check
+            c->q_cv.wait(lk);
+        }
+    }
+    return me.status;
+}
+
+}  // namespace
+
+// ============================================================================================
+// C ABI
+// ============================================================================================
+
+extern "C" {
+
+const char* xn_version(void) { return "xn_attn 0.1 sm_100a"; }
+
+const char* xn_last_error(xn_ctx* ctx) {
+    if (ctx_ok(ctx)) return ctx->last_error.c_str();
+    std::lock_guard<std::mutex> g(g_err_mu);
+    static thread_local std::string copy;
+    copy = g_create_error;
+    return copy.c_str();
+}
+
+int32_t xn_ctx_create(const xn_ctx_desc* d, xn_ctx** out_ctx) {
+    if (!d || !out_ctx) return fail(nullptr, XN_ERR_ARG, "null descriptor or output");
+    *out_ctx = nullptr;
+    if (d->num_layers <= 0 || d->num_heads <= 0 || d->num_kv_heads <= 0)
+        return fail(nullptr, XN_ERR_SHAPE, "layer and head counts must be positive");
+    if (d->num_heads % d->num_kv_heads != 0)
+        return fail(nullptr, XN_ERR_SHAPE, "num_heads %d is not a multiple of num_kv_heads %d",
+                    d->num_heads, d->num_kv_heads);
+    if (d->head_dim < 1 || d->head_dim > 256)
+        return fail(nullptr, XN_ERR_SHAPE, "head_dim %d outside 1..256", d->head_dim);
+    if (d->page_tokens != 0 && d->page_tokens != kPageTokens)
+        return fail(nullptr, XN_ERR_ARG, "page_tokens must be 0 or %d", kPageTokens);
+    if ((d->rope_cos == nullptr) != (d->rope_sin == nullptr) || (d->rope_cos && d->max_pos <= 0))
+        return fail(nullptr, XN_ERR_ARG, "rope tables need cos, sin and max_pos together");
+
+    int n_dev = 0;
+    cudaError_t e = cudaGetDeviceCount(&n_dev);
+    if (e != cudaSuccess || n_dev <= 0)
+        return fail(nullptr, XN_ERR_NO_DEVICE,
+                    "no CUDA device (%s); this library has no CPU fallback",
+                    e != cudaSuccess ? cudaGetErrorString(e) : "count is 0");
+    if (d->device < 0 || d->device >= n_dev)
+        return fail(nullptr, XN_ERR_ARG, "device ordinal %d outside 0..%d", d->device, n_dev - 1);
+    cudaDeviceProp prop;
+    XN_CUDA(nullptr, cudaSetDevice(d->device));
+    XN_CUDA(nullptr, cudaGetDeviceProperties(&prop, d->device));
+    if (prop.major != 10)
+        return fail(nullptr, XN_ERR_NO_DEVICE, "device %d is sm_%d%d; this build targets sm_100a only",
+                    d->device, prop.major, prop.minor);
+
+    xn_ctx* c = new (std::nothrow) xn_ctx();
+    if (!c) return fail(nullptr, XN_ERR_NOMEM, "out of host memory");
+    c->device = d->device;
+    c->num_layers = d->num_layers;
+    c->num_heads = d->num_heads;
+    c->num_kv_heads = d->num_kv_heads;
+    c->head_dim = d->head_dim;
+    c->group = d->num_heads / d->num_kv_heads;
+    c->gt = (c->group >= 3) ? 4 : c->group;  // 1, 2 or 4 query heads share each K/V tile
+    c->subs = (c->group + c->gt - 1) / c->gt;
+    c->nv = (d->head_dim + 3) / 4;
+    c->nv_class = nv_class_for(c->nv);
+    c->nv_exact = c->nv_class == c->nv;
+    c->tile_tokens = (c->nv_class <= 32) ? 64 : 32;
+    c->scale = 1.0f / sqrtf(float(d->head_dim));  // fast_attention.rs:135
+    c->max_pos = d->max_pos;
+    c->prefill_mode = d->prefill_mode;
+    c->batch_window_us = d->batch_window_us;
+    c->sm_count = prop.multiProcessorCount;
+    c->decode_ctas = c->sm_count;
+    if (const char* env = getenv("XORNET_ATTN_DECODE_CTAS")) {
+        int v = atoi(env);
+        if (v > 0) c->decode_ctas = v;
+    }
+
+    const size_t page_bytes =
+        size_t(d->num_layers) * d->num_kv_heads * kPageTokens * c->nv * 16 * 2;  // K and V
+    long long pages = d->pool_pages > 0 ? d->pool_pages : (d->pool_bytes > 0 ? d->pool_bytes / (long long)page_bytes : 0);
+    if (pages <= 0 || pages > (1ll << 30)) {
+        delete c;
+        return fail(nullptr, XN_ERR_ARG, "pool_pages (or pool_bytes) must give at least one page");
+    }
+    c->pool_pages = pages;
+
+    auto bail = [&](int32_t code) {
+        std::string msg;
+        { std::lock_guard<std::mutex> g(g_err_mu); msg = g_create_error; }
+        xn_ctx_destroy(c);
+        { std::lock_guard<std::mutex> g(g_err_mu); g_create_error = msg; }
+        return code;
+    };
+#define XN_CREATE_CUDA(expr)                                                                   \
+    do {                                                                                       \
+        cudaError_t e__ = (expr);                                                              \
+        if (e__ != cudaSuccess) {                                                              \
+            fail(nullptr, XN_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(e__));       \
+            return bail(XN_ERR_CUDA);                                                          \
+        }                                                                                      \
+    } while (0)
+
+    if (d->cuda_stream) {
+        c->stream = static_cast<cudaStream_t>(d->cuda_stream);
+    } else {
+        XN_CREATE_CUDA(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
+        c->own_stream = true;
+    }
+    const size_t pool_floats = size_t(pages) * d->num_layers * d->num_kv_heads * kPageTokens * c->nv * 4;
+    XN_CREATE_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->k_pool), pool_floats * 4));
+    XN_CREATE_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->v_pool), pool_floats * 4));
+    // Row padding (head_dim rounded up to 4 floats) must hold zeros for the lifetime of the pool.
+    XN_CREATE_CUDA(cudaMemsetAsync(c->k_pool, 0, pool_floats * 4, c->stream));
+    XN_CREATE_CUDA(cudaMemsetAsync(c->v_pool, 0, pool_floats * 4, c->stream));
+    if (d->rope_cos) {
+        const size_t tb = size_t(d->max_pos) * (d->head_dim / 2) * 4;
+        XN_CREATE_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->cos_d), std::max<size_t>(tb, 16)));
+        XN_CREATE_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->sin_d), std::max<size_t>(tb, 16)));
+        XN_CREATE_CUDA(cudaMemcpyAsync(c->cos_d, d->rope_cos, tb, cudaMemcpyHostToDevice, c->stream));
+        XN_CREATE_CUDA(cudaMemcpyAsync(c->sin_d, d->rope_sin, tb, cudaMemcpyHostToDevice, c->stream));
+    }
+    XN_CREATE_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->status_d), sizeof(int)));
+    XN_CREATE_CUDA(cudaMemsetAsync(c->status_d, 0, sizeof(int), c->stream));
+    XN_CREATE_CUDA(cudaMallocHost(reinterpret_cast<void**>(&c->status_h), sizeof(int)));
+    *c->status_h = kDevOk;
+
+    {
+        SplitKernel k = pick_split(c->nv_class, c->gt);
+        XN_CREATE_CUDA(cudaFuncSetAttribute(reinterpret_cast<const void*>(k.fn),
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize, int(k.smem)));
+    }
+
+    c->free_pages.resize(size_t(pages));
+    for (long long i = 0; i < pages; ++i) c->free_pages[size_t(i)] = int32_t(pages - 1 - i);
+    if (d->shuffle_seed) {  // Fisher-Yates with the counter-based generator
+        uint64_t ctr = 0;
+        for (size_t i = c->free_pages.size(); i > 1; --i) {
+            size_t j = size_t(mix64(d->shuffle_seed * 0x9E3779B97F4A7C15ull + ctr++) % i);
+            std::swap(c->free_pages[i - 1], c->free_pages[j]);
+        }
+    }
+    c->stats.pages_total = uint64_t(pages);
+    XN_CREATE_CUDA(cudaStreamSynchronize(c->stream));
+#undef XN_CREATE_CUDA
+    *out_ctx = c;
+    return XN_OK;
+}
+
+int32_t xn_ctx_destroy(xn_ctx* c) {
+    if (!ctx_ok(c)) return XN_ERR_HANDLE;
+    cudaSetDevice(c->device);
+    if (c->stream) cudaStreamSynchronize(c->stream);
+    for (xn_stream* s : c->streams) {
+        s->magic = 0;
+        delete s;
+    }
+    c->streams.clear();
+    for (PlanSlot& s : c->slots) {
+        if (s.host) cudaFreeHost(s.host);
+        if (s.dev) cudaFree(s.dev);
+        if (s.ev) cudaEventDestroy(s.ev);
+    }
+    if (c->q_rot) cudaFree(c->q_rot);
+    if (c->partials) cudaFree(c->partials);
+    if (c->io_host) cudaFreeHost(c->io_host);
+    if (c->io_dev) cudaFree(c->io_dev);
+    if (c->status_d) cudaFree(c->status_d);
+    if (c->status_h) cudaFreeHost(c->status_h);
+    if (c->cos_d) cudaFree(c->cos_d);
+    if (c->sin_d) cudaFree(c->sin_d);
+    if (c->k_pool) cudaFree(c->k_pool);
+    if (c->v_pool) cudaFree(c->v_pool);
+    if (c->own_stream && c->stream) cudaStreamDestroy(c->stream);
+    c->magic = 0;
+    delete c;
+    return XN_OK;
+}
+
+int32_t xn_ctx_synchronize(xn_ctx* c) {
+    if (!ctx_ok(c)) return XN_ERR_HANDLE;
+    std::lock_guard<std::mutex> g(c->mu);
+    XN_CUDA(c, cudaSetDevice(c->device));
+    XN_CUDA(c, cudaMemcpyAsync(c->status_h, c->status_d, sizeof(int), cudaMemcpyDeviceToHost, c->stream));
+    XN_CUDA(c, cudaStreamSynchronize(c->stream));
+    return check_device_status(c);
+}
+
+void* xn_ctx_cuda_stream(xn_ctx* c) { return ctx_ok(c) ? static_cast<void*>(c->stream) : nullptr; }
+
+int32_t xn_stats_get(xn_ctx* c, xn_stats* out) {
+    if (!ctx_ok(c)) return XN_ERR_HANDLE;
+    if (!out) return XN_ERR_ARG;
+    std::lock_guard<std::mutex> g(c->mu);
+    c->stats.pages_in_use = c->stats.pages_total - c->free_pages.size();
+    c->stats.streams_live = c->streams.size();
+    *out = c->stats;
+    return XN_OK;
+}
+
+int32_t xn_stream_create(xn_ctx* c, int64_t max_seq_len, xn_stream** out) {
+    if (!ctx_ok(c)) return XN_ERR_HANDLE;
+    if (!out) return XN_ERR_ARG;
+    *out = nullptr;
+    std::lock_guard<std::mutex> g(c->mu);
+    if (max_seq_len <= 0) return fail(c, XN_ERR_ARG, "max_seq_len must be positive");
+    xn_stream* s = new (std::nothrow) xn_stream();
+    if (!s) return fail(c, XN_ERR_NOMEM, "out of host memory");
+    s->ctx = c;
+    s->cap = max_seq_len;
+    s->hw.assign(size_t(c->num_layers), 0);
+    {
+        std::lock_guard<std::mutex> q(c->q_mu);
+        c->streams.insert(s);
+    }
+    *out = s;
+    return XN_OK;
+}
+
+int32_t xn_stream_reset(xn_ctx* c, xn_stream* s) {
+    if (!ctx_ok(c)) return XN_ERR_HANDLE;
+    std::lock_guard<std::mutex> g(c->mu);
+    if (!stream_ok(c, s)) return fail(c, XN_ERR_HANDLE, "stream handle is not live");
+    // Pages may still be read by launches already enqueued: finish them before reuse.
+    XN_CUDA(c, cudaSetDevice(c->device));
+    XN_CUDA(c, cudaStreamSynchronize(c->stream));
+    release_pages(c, s);
+    return XN_OK;
+}
+
+int32_t xn_stream_destroy(xn_ctx* c, xn_stream* s) {
+    if (!ctx_ok(c)) return XN_ERR_HANDLE;
+    std::lock_guard<std::mutex> g(c->mu);
+    if (!stream_ok(c, s)) return fail(c, XN_ERR_HANDLE, "stream handle is not live");
+    XN_CUDA(c, cudaSetDevice(c->device));
+    XN_CUDA(c, cudaStreamSynchronize(c->stream));
+    release_pages(c, s);
+    {
+        std::lock_guard<std::mutex> q(c->q_mu);
+        c->streams.erase(s);
+    }
+    s->magic = 0;
+    delete s;
+    return XN_OK;
+}
+
+int32_t xn_attention(xn_ctx* c, xn_stream* s, int32_t layer, int64_t index_pos, int32_t seq_len,
+                     const float* q, const float* k, const float* v, float* out) {
+    if (!ctx_ok(c)) return XN_ERR_HANDLE;
+    xn_req r{s, layer, seq_len, index_pos, q, k, v, out, 0u, 0u};
+    return attention_blocking(c, r);
+}
+
+int32_t xn_attention_rope(xn_ctx* c, xn_stream* s, int32_t layer, int64_t index_pos,
+                          int32_t seq_len, const float* q, const float* k, const float* v,
+                          float* out) {
+    if (!ctx_ok(c)) return XN_ERR_HANDLE;
+    xn_req r{s, layer, seq_len, index_pos, q, k, v, out, XN_REQ_ROPE, 0u};
+    return attention_blocking(c, r);
+}
+
+int32_t xn_attention_batch(xn_ctx* c, int32_t n, const xn_req* reqs) {
+    if (!ctx_ok(c)) return XN_ERR_HANDLE;
+    std::lock_guard<std::mutex> g(c->mu);
+    if (n < 0 || (n > 0 && !reqs)) return fail(c, XN_ERR_ARG, "bad request array");
+    if (n == 0) return XN_OK;
+    const bool dev = reqs[0].flags & XN_REQ_DEVICE_PTRS;
+    std::unordered_set<xn_stream*> seen;
+    for (int i = 0; i < n; ++i) {
+        int32_t rc = validate_req(c, reqs[i]);
+        if (rc != XN_OK) return rc;
+        if (bool(reqs[i].flags & XN_REQ_DEVICE_PTRS) != dev)
+            return fail(c, XN_ERR_ARG, "host and device requests mixed in one batch");
+        if (!seen.insert(reqs[i].stream).second)
+            return fail(c, XN_ERR_ARG, "request %d repeats a stream of this batch", i);
+    }
+    return submit_locked(c, n, reqs, !dev);
+}
+
+int32_t xn_rope_tables(float theta, int32_t head_dim, int32_t max_pos, float factor,
+                       float low_freq_factor, float high_freq_factor, int32_t original_max_pos,
+                       float* cos_out, float* sin_out) {
+    if (head_dim <= 0 || max_pos < 0 || !cos_out || !sin_out) return XN_ERR_ARG;
+    const int half = head_dim / 2;
+    const int nfreq = (head_dim + 1) / 2;
+    std::vector<float> inv;
+    inv.resize(size_t(nfreq));
+    for (int j = 0; j < nfreq; ++j)  // models/llama/mod.rs:210-216
+        inv[size_t(j)] = 1.0f / powf(theta, float(2 * j) / float(head_dim));
+    if (factor > 0.0f) {  // models/llama/mod.rs:226-249
+        const float pi = 3.14159265358979323846f;
+        const float low_wl = float(original_max_pos) / low_freq_factor;
+        const float high_wl = float(original_max_pos) / high_freq_factor;
+        for (float& fr : inv) {
+            const float wl = 2.0f * pi / fr;
+            if (wl < high_wl) continue;
+            if (wl > low_wl) {
+                fr = fr / factor;
+            } else {
+                const float smooth = (float(original_max_pos) / wl - low_freq_factor) /
+                                     (high_freq_factor - low_freq_factor);
+                fr = (1.0f - smooth) * fr / factor + smooth * fr;
+            }
+        }
+    }
+    for (int pos = 0; pos < max_pos; ++pos)  // models/llama/mod.rs:252-262
+        for (int i = 0; i < half; ++i) {
+            const float a = float(pos) * inv[size_t(i)];
+            cos_out[size_t(pos) * half + i] = cosf(a);
+            sin_out[size_t(pos) * half + i] = sinf(a);
+        }
+    return XN_OK;
+}
+
+// ---- cache inspection / synthetic fill ------------------------------------------------------
+
+static int32_t upload_pages(xn_ctx* c, xn_stream* s, const int** pages_d, PlanSlot** slot_out) {
+    PlanSlot* slot = nullptr;
+    int32_t rc = acquire_slot(c, std::max<size_t>(16, s->pages.size() * 4), &slot);
+    if (rc != XN_OK) return rc;
+    memcpy(slot->host, s->pages.data(), s->pages.size() * 4);
+    XN_CUDA(c, cudaMemcpyAsync(slot->dev, slot->host, std::max<size_t>(16, s->pages.size() * 4),
+                               cudaMemcpyHostToDevice, c->stream));
+    *pages_d = reinterpret_cast<const int*>(slot->dev);
+    *slot_out = slot;
+    return XN_OK;
+}
+
+int32_t xn_kv_read_range(xn_ctx* c, xn_stream* s, int32_t layer, int64_t t0, int64_t n,
+                         float* k_out, float* v_out) {
+    if (!ctx_ok(c)) return XN_ERR_HANDLE;
+    std::lock_guard<std::mutex> g(c->mu);
+    if (!stream_ok(c, s)) return fail(c, XN_ERR_HANDLE, "stream handle is not live");
+    if (layer < 0 || layer >= c->num_layers || t0 < 0 || n < 0 || t0 + n > s->cap)
+        return fail(c, XN_ERR_ARG, "slot range outside the stream's capacity");
+    if (n == 0) return XN_OK;
+    XN_CUDA(c, cudaSetDevice(c->device));
+    const size_t elems = size_t(n) * c->num_kv_heads * c->head_dim;
+    if (k_out) memset(k_out, 0, elems * 4);
+    if (v_out) memset(v_out, 0, elems * 4);
+    // slots without a page were never written: zeros
+    // slots at or beyond the highest written position of this layer were never written either
+    const int64_t have = std::min<int64_t>(
+        {int64_t(s->pages.size()) * kPageTokens, t0 + n, std::min<int64_t>(s->hw[size_t(layer)], s->cap)});
+    if (have <= t0) return XN_OK;
+    const int64_t m = have - t0;
+    const size_t melems = size_t(m) * c->num_kv_heads * c->head_dim;
+    int32_t rc = grow_io(c, 2 * melems * 4);
+    if (rc != XN_OK) return rc;
+    const int* pages_d = nullptr;
+    PlanSlot* slot = nullptr;
+    if ((rc = upload_pages(c, s, &pages_d, &slot)) != XN_OK) return rc;
+    float* kd = reinterpret_cast<float*>(c->io_dev);
+    float* vd = kd + melems;
+    const int blocks = int(std::min<size_t>((melems + 255) / 256, 8192));
+    slots_gather_kernel<<<blocks, 256, 0, c->stream>>>(pages_d, c->k_pool, c->v_pool, c->pool_pages,
+                                                       layer, c->num_kv_heads, c->head_dim, c->nv,
+                                                       t0, m, kd, vd);
+    c->stats.kernel_launches += 1;
+    XN_CUDA(c, cudaGetLastError());
+    XN_CUDA(c, cudaMemcpyAsync(c->io_host, c->io_dev, 2 * melems * 4, cudaMemcpyDeviceToHost, c->stream));
+    XN_CUDA(c, cudaEventRecord(slot->ev, c->stream));
+    slot->used = true;
+    XN_CUDA(c, cudaStreamSynchronize(c->stream));
+    const float* kh = reinterpret_cast<const float*>(c->io_host);
+    const float* vh = kh + melems;
+    const size_t D = size_t(c->head_dim);
+    for (int h = 0; h < c->num_kv_heads; ++h) {  // [Hkv, m, D] -> [Hkv, n, D]
+        if (k_out) memcpy(k_out + size_t(h) * n * D, kh + size_t(h) * m * D, size_t(m) * D * 4);
+        if (v_out) memcpy(v_out + size_t(h) * n * D, vh + size_t(h) * m * D, size_t(m) * D * 4);
+    }
+    return XN_OK;
+}
+
+int32_t xn_kv_read(xn_ctx* c, xn_stream* s, int32_t layer, int32_t kv_head, int64_t t, float* k_row,
+                   float* v_row) {
+    if (!ctx_ok(c)) return XN_ERR_HANDLE;
+    if (!stream_ok(c, s)) return XN_ERR_HANDLE;
+    if (kv_head < 0 || kv_head >= c->num_kv_heads || t < 0) return XN_ERR_ARG;
+    const size_t D = size_t(c->head_dim);
+    std::vector<float> kb(size_t(c->num_kv_heads) * D), vb(size_t(c->num_kv_heads) * D);
+    int32_t rc = xn_kv_read_range(c, s, layer, t % s->cap, 1, kb.data(), vb.data());
+    if (rc != XN_OK) return rc;
+    if (k_row) memcpy(k_row, kb.data() + size_t(kv_head) * D, D * 4);
+    if (v_row) memcpy(v_row, vb.data() + size_t(kv_head) * D, D * 4);
+    return XN_OK;
+}
+
+int32_t xn_kv_fill_normal(xn_ctx* c, xn_stream* s, int32_t layer, int64_t t0, int64_t n,
+                          uint64_t seed) {
+    if (!ctx_ok(c)) return XN_ERR_HANDLE;
+    std::lock_guard<std::mutex> g(c->mu);
+    if (!stream_ok(c, s)) return fail(c, XN_ERR_HANDLE, "stream handle is not live");
+    if (layer < -1 || layer >= c->num_layers || t0 < 0 || n < 0 || t0 + n > s->cap)
+        return fail(c, XN_ERR_ARG, "slot range outside the stream's capacity");
+    if (n == 0) return XN_OK;
+    XN_CUDA(c, cudaSetDevice(c->device));
+    int32_t rc = ensure_pages(c, s, t0 + n);
+    if (rc != XN_OK) return rc;
+    const int* pages_d = nullptr;
+    PlanSlot* slot = nullptr;
+    if ((rc = upload_pages(c, s, &pages_d, &slot)) != XN_OK) return rc;
+    const long long total = n * c->num_kv_heads * c->head_dim;
+    const int blocks = int(std::min<long long>((total + 255) / 256, 8192));
+    const int l0 = layer < 0 ? 0 : layer, l1 = layer < 0 ? c->num_layers : layer + 1;
+    for (int l = l0; l < l1; ++l) {
+        slots_fill_kernel<<<blocks, 256, 0, c->stream>>>(pages_d, c->k_pool, c->v_pool, c->pool_pages,
+                                                         l, c->num_kv_heads, c->head_dim, c->nv, t0,
+                                                         n, 1, seed + 0x632BE59BD9B4E019ull * uint64_t(l));
+        c->stats.kernel_launches += 1;
+        s->hw[size_t(l)] = std::max<int64_t>(s->hw[size_t(l)], t0 + n);
+    }
+    XN_CUDA(c, cudaGetLastError());
+    XN_CUDA(c, cudaEventRecord(slot->ev, c->stream));
+    slot->used = true;
+    return XN_OK;
+}
+
+int32_t xn_fill_normal(xn_ctx* c, float* device_ptr, int64_t n, uint64_t seed) {
+    if (!ctx_ok(c)) return XN_ERR_HANDLE;
+    std::lock_guard<std::mutex> g(c->mu);
+    if (!device_ptr || n < 0) return fail(c, XN_ERR_ARG, "bad buffer");
+    if (n == 0) return XN_OK;
+    XN_CUDA(c, cudaSetDevice(c->device));
+    const int blocks = int(std::min<long long>((n + 255) / 256, 8192));
+    fill_normal_kernel<<<blocks, 256, 0, c->stream>>>(device_ptr, n, seed);
+    c->stats.kernel_launches += 1;
+    XN_CUDA(c, cudaGetLastError());
+    return XN_OK;
+}
+
+int64_t xn_stream_len(xn_ctx* c, xn_stream* s, int32_t layer) {
+    if (!ctx_ok(c) || !stream_ok(c, s) || layer < 0 || layer >= c->num_layers) return -1;
+    std::lock_guard<std::mutex> g(c->mu);
+    return s->hw[size_t(layer)];
+}
+
+int64_t xn_stream_pages(xn_ctx* c, xn_stream* s, int32_t* out, int64_t max_out) {
+    if (!ctx_ok(c) || !stream_ok(c, s)) return -1;
+    std::lock_guard<std::mutex> g(c->mu);
+    const int64_t n = int64_t(s->pages.size());
+    for (int64_t i = 0; i < n && i < max_out && out; ++i) out[i] = s->pages[size_t(i)];
+    return n;
+}
+
+int32_t xn_plan_split(int32_t n_units, const int32_t* kv_len, int32_t tile_tokens, int32_t max_ctas,
+                      int32_t max_items, int32_t* item_unit, int32_t* item_tile_begin,
+                      int32_t* item_tile_end, int32_t* item_part, int32_t* cta_item_begin,
+                      int32_t* n_items_out, int32_t* n_parts_out) {
+    if (n_units < 0 || (n_units > 0 && !kv_len) || tile_tokens <= 0 || max_ctas <= 0) return -XN_ERR_ARG;
+    SplitPlan p = plan_split(kv_len, n_units, tile_tokens, max_ctas);
+    if (int32_t(p.items.size()) > max_items) return -XN_ERR_CAPACITY;
+    for (size_t i = 0; i < p.items.size(); ++i) {
+        if (item_unit) item_unit[i] = p.items[i].unit;
+        if (item_tile_begin) item_tile_begin[i] = p.items[i].tile_begin;
+        if (item_tile_end) item_tile_end[i] = p.items[i].tile_end;
+        if (item_part) item_part[i] = p.items[i].part;
+    }
+    if (cta_item_begin)
+        for (size_t i = 0; i < p.cta_item_begin.size(); ++i) cta_item_begin[i] = p.cta_item_begin[i];
+    if (n_items_out) *n_items_out = int32_t(p.items.size());
+    if (n_parts_out) *n_parts_out = p.n_parts;
+    return p.ctas;
+}
+
+}  // extern "C"

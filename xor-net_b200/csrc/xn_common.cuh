@@ -1,0 +1,144 @@
+// Shared device helpers and host/device plan structures for the sm_100a attention kernels.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace xn {
+
+constexpr int kPageTokens = 64;  // tokens per KV page
+
+// Device error word values written by kernels whose bounded waits ran out.
+enum : int { kDevOk = 0, kDevWaitFull = 1, kDevWaitEmpty = 2, kDevBadIndex = 3, kDevWaitMma = 4 };
+
+// ---- plan structures (built on the host per batch, copied once to the device) ---------------
+
+// One attention request as the kernels see it.  Strides are in floats.
+struct ReqDev {
+    const float* q;    // rotated query rows (user memory, staged copy, or the rotation scratch)
+    const float* k;    // new keys   (input to the append kernel)
+    const float* v;    // new values
+    const float* q_in; // query rows as supplied (input to the append kernel when rotating)
+    float* out;
+    long long q_hs, q_ts;     // query head / token strides of `q`
+    long long qi_hs, qi_ts;   // strides of `q_in`
+    long long kv_hs, kv_ts;   // strides of k and v
+    long long o_hs, o_ts;     // output strides
+    int page_off;             // offset of this stream's page ids inside the plan's page array
+    int layer;
+    int seq_len;
+    int index_pos;
+    int cap;                  // ring capacity (positions fold modulo cap)
+    int n_pages;
+    unsigned flags;           // bit 0: rotate q and k with the context tables
+    int pad;
+};
+
+// A (request, KV head, query-head subgroup, query row) to attend over kv_len cached tokens.
+struct UnitDev {
+    int req;
+    int kv_head;
+    int head0;      // first query head of the subgroup
+    int nheads;     // query heads in the subgroup (<= template GT)
+    int t_q;        // query row within the request
+    int kv_len;     // cached tokens to attend (index_pos + t_q + 1)
+    int part_begin; // first partial slot, or -1 when the unit is written directly
+    int part_count;
+};
+
+// A contiguous tile range of one unit given to one thread block.
+struct ItemDev {
+    int unit;
+    int tile_begin;
+    int tile_end;
+    int part;  // partial slot or -1 (direct)
+};
+
+// ---- PTX wrappers: mbarrier + bulk async copy (TMA engine, no tensor map, no multicast) ------
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_fence_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+                 "r"(bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Waits for the given phase parity at most ~2 s.  Returns false when it gave up; the caller
+// records an error code and leaves its loop, so a lost copy can never hang the GPU.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    unsigned long long t0 = 0;
+    for (uint32_t spins = 1;; ++spins) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spins & 0x3ffu) == 0) {
+            unsigned long long now = global_timer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > 2000000000ull) return false;
+        }
+    }
+}
+
+// 1-D bulk copy global -> shared, completion counted in bytes on an mbarrier.  Both addresses
+// must be 16-byte aligned and bytes a multiple of 16.
+__device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gmem_src, uint32_t bytes,
+                                         uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
+}
+
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+// ---- counter-based N(0,1) generator ---------------------------------------------------------
+
+__host__ __device__ __forceinline__ uint64_t mix64(uint64_t z) {
+    z += 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+
+__device__ __forceinline__ float normal_from(uint64_t seed, uint64_t idx) {
+    uint64_t r = mix64(seed * 0xD1342543DE82EF95ull + idx);
+    uint32_t a = static_cast<uint32_t>(r), b = static_cast<uint32_t>(r >> 32);
+    float u1 = (static_cast<float>(a >> 8) + 1.0f) * (1.0f / 16777217.0f);  // (0,1)
+    float u2 = static_cast<float>(b >> 8) * (1.0f / 16777216.0f);           // [0,1)
+    return sqrtf(-2.0f * logf(u1)) * cospif(2.0f * u2);
+}
+
+}  // namespace xn
