@@ -1,0 +1,430 @@
+#!/usr/bin/env python
+"""Benchmark of the attention path: batched multi-stream decode over the paged KV cache.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c3|c1|c5] [--impl reference]
+
+Workload (default ``c3``, BitNet-2B shape): 64 independent streams per GPU, one new token each,
+20 query heads, 5 KV heads, head_dim 128, per-stream cached lengths drawn uniformly from
+[128, 4096] with a fixed seed, f32 KV in 64-token pages handed out in a shuffled order, 30
+layers each with its own N(0,1) cache contents.  One *step* = one decode step of every stream
+through all layers = one batched submission per layer.  Data is synthetic: generated on the
+device by the library's counter-based generator (the cache) and seeded N(0,1) inputs.
+
+Printed JSON (one line, rank 0):
+  value    algorithmic HBM GB/s of the whole job, inputs resident in HBM (device pointers);
+           algorithmic bytes per layer = sum over streams of
+           2*Hkv*L*D*4 (K and V read once) + 4*Hkv*D*4 (new K,V read + append) + 2*Hq*D*4 (q, out)
+  e2e      the same metric through the blocking C-ABI call with HOST buffers: every layer call
+           copies q,k,v host->device and the output device->host inside the timed region
+  roofline the split-KV attention kernel alone: CUDA events around each of its launches
+  cpu_baseline / --impl reference: the CPU oracle (a C port of the reference's AVX-512 path,
+           all host threads) on a bounded sample of the same workload
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+BASE_SEED = 299792458  # the reference's habitual seed (examples/batch_bench.rs:189)
+
+WORKLOADS = {
+    # name: (streams per GPU, Hq, Hkv, D, layers, L_lo, L_hi, description)
+    "c3": (64, 20, 5, 128, 30, 128, 4096,
+           "batched decode, BitNet-2B shape: 64 streams/GPU x 30 layers, KV len U[128,4096]"),
+    "c1": (1, 20, 5, 128, 1, 1024, 1024,
+           "single-stream decode, BitNet-2B shape: 1 stream, 1 layer, KV len 1024"),
+    "c5": (32, 32, 8, 128, 32, 2048, 8192,
+           "long-context batched decode, LLaMA-3-8B shape: 32 streams/GPU x 32 layers, KV len U[2048,8192]"),
+}
+
+
+def algorithmic_bytes_per_layer(lens, Hq, Hkv, D):
+    return int(sum(2 * Hkv * int(L) * D * 4 + 4 * Hkv * D * 4 + 2 * Hq * D * 4 for L in lens))
+
+
+def stream_lengths(n, lo, hi, seed):
+    rng = np.random.default_rng(seed)
+    return rng.integers(lo, hi + 1, n).astype(np.int64)
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.proc = None
+        self.lines = []
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-i", str(gpu_index), "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.time(), line.strip()))
+
+    def stop(self, t0, t1):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()  # the exact process started above
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ts, line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            inside = t0 - 0.05 <= ts <= t1 + 0.15
+            try:
+                if inside:
+                    sm.append(float(parts[0]))
+                smax.append(float(parts[1]))
+            except ValueError:
+                continue
+            if inside:
+                for nm, val in zip(names, parts[3:7]):
+                    if val.lower().startswith("active"):
+                        reasons.add(nm)
+        if not sm:  # region shorter than the sampling period: use every sample taken
+            for ts, line in self.lines:
+                try:
+                    sm.append(float(line.split(",")[0]))
+                except ValueError:
+                    pass
+        return {"sm_mhz": float(np.median(sm)) if sm else None,
+                "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# =================================================================================================
+# CPU baseline (the oracle: C port of the reference's path), bounded sample
+# =================================================================================================
+
+def cpu_sample(lens, Hq, Hkv, D, kv_by_stream, q, k, v, layer, budget_s=12.0, max_reps=50):
+    """Times the oracle on the given streams of one layer with every host thread.
+
+    kv_by_stream[i] = (K, V) each [Hkv, L_i - 1, D] already cached; q/k/v per stream are the new
+    token's tensors.  Returns (GB/s, seconds per pass, outputs of the last pass, threads).
+    """
+    import oracle as xo
+
+    n = len(lens)
+    threads = xo.max_threads()
+    cap = int(max(lens))
+    caches = []
+    for i in range(n):
+        c = xo.RingCache(layer + 1, Hkv, cap, D)
+        if lens[i] > 1:
+            c.append(layer, 0, kv_by_stream[i][0], kv_by_stream[i][1])
+        caches.append(c)
+    pos = [int(L) - 1 for L in lens]
+    nbytes = algorithmic_bytes_per_layer(lens, Hq, Hkv, D)
+    xo.fast_attention_streams(q, k, v, layer, pos, caches, Hq, Hkv, D, threads)  # warm-up
+    t_total, reps, outs = 0.0, 0, None
+    while reps < max_reps and (reps < 3 or t_total < budget_s):
+        t0 = time.perf_counter()
+        outs = xo.fast_attention_streams(q, k, v, layer, pos, caches, Hq, Hkv, D, threads)
+        t_total += time.perf_counter() - t0
+        reps += 1
+    per_pass = t_total / reps
+    return nbytes / per_pass / 1e9, per_pass, outs, threads, reps
+
+
+def run_reference_arm(args):
+    """--impl reference: the reference's CPU algorithm (oracle port; the reference itself is
+    Rust and no Rust toolchain exists here) on the host cores, bounded sample per step."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    import oracle as xo
+
+    n_streams, Hq, Hkv, D, layers, lo, hi, desc = WORKLOADS[args.workload]
+    lens_all = stream_lengths(n_streams, lo, hi, BASE_SEED + 3000)
+    sample = min(args.cpu_streams, n_streams)
+    lens = lens_all[:sample]
+    rng = np.random.default_rng(BASE_SEED + 3000 + 1)
+    threads = xo.max_threads()
+    cap = int(max(lens))
+    caches, qs, ks, vs = [], [], [], []
+    for L in lens:
+        c = xo.RingCache(1, Hkv, cap, D)
+        if L > 1:
+            c.append(0, 0, rng.standard_normal((Hkv, int(L) - 1, D)).astype(np.float32),
+                     rng.standard_normal((Hkv, int(L) - 1, D)).astype(np.float32))
+        caches.append(c)
+        qs.append(rng.standard_normal((1, Hq, 1, D)).astype(np.float32))
+        ks.append(rng.standard_normal((1, Hkv, 1, D)).astype(np.float32))
+        vs.append(rng.standard_normal((1, Hkv, 1, D)).astype(np.float32))
+    pos = [int(L) - 1 for L in lens]
+    nbytes = algorithmic_bytes_per_layer(lens, Hq, Hkv, D)
+    for _ in range(args.warmup):
+        xo.fast_attention_streams(qs, ks, vs, 0, pos, caches, Hq, Hkv, D, threads)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        xo.fast_attention_streams(qs, ks, vs, 0, pos, caches, Hq, Hkv, D, threads)
+    dt = time.perf_counter() - t0
+    gbs = nbytes * args.steps / dt / 1e9
+    sample_txt = (f"{sample} of {n_streams} streams x 1 of {layers} layers per step "
+                  f"({nbytes / 1e6:.1f} MB algorithmic), isa level {xo.active_isa()}")
+    line = {
+        "impl": "reference", "metric": "decode_attn_hbm_gbs", "value": gbs, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{args.workload}: {desc}", "sample": sample_txt},
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port",
+                         "sample": sample_txt},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "tokens_per_s": sample * args.steps / dt,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+# =================================================================================================
+# GPU arm
+# =================================================================================================
+
+def run_gpu_arm(args):
+    import torch
+    import torch.distributed as dist
+
+    import xor_net_b200 as xn
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the attention library has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    n_streams, Hq, Hkv, D, layers, lo, hi, desc = WORKLOADS[args.workload]
+    # every rank owns its own streams (weak scaling: per-GPU work is fixed); no data-path collective
+    lens = stream_lengths(n_streams, lo, hi, BASE_SEED + 3000 + 7919 * rank)
+    pages_needed = int(sum((int(L) + 63) // 64 for L in lens))
+    tstream = torch.cuda.current_stream()
+    ctx = xn.Context(num_layers=layers, num_heads=Hq, num_kv_heads=Hkv, head_dim=D,
+                     pool_pages=pages_needed + 8, device=local_rank,
+                     shuffle_seed=BASE_SEED + rank, cuda_stream=tstream.cuda_stream)
+    streams = [ctx.new_stream(int(hi)) for _ in range(n_streams)]
+    for i, st in enumerate(streams):
+        if lens[i] > 1:
+            st.fill_normal(-1, 0, int(lens[i]) - 1, BASE_SEED + 3000 + 1000003 * rank + i)
+    ctx.synchronize()
+
+    # per-layer inputs, resident on the device and mirrored in pinned host memory
+    q_elems, kv_elems = n_streams * Hq * D, n_streams * Hkv * D
+    gen = torch.Generator(device="cpu").manual_seed(BASE_SEED + 3000 + rank)
+    q_h = torch.randn(layers, n_streams, Hq, D, generator=gen).pin_memory()
+    k_h = torch.randn(layers, n_streams, Hkv, D, generator=gen).pin_memory()
+    v_h = torch.randn(layers, n_streams, Hkv, D, generator=gen).pin_memory()
+    o_h = torch.empty(layers, n_streams, Hq, D).pin_memory()
+    q_d, k_d, v_d = q_h.cuda(non_blocking=True), k_h.cuda(non_blocking=True), v_h.cuda(non_blocking=True)
+    o_d = torch.zeros(layers, n_streams, Hq, D, device="cuda")
+    torch.cuda.synchronize()
+
+    def batches(q, k, v, o, flags):
+        out = []
+        for l in range(layers):
+            out.append(ctx.make_batch(
+                [(streams[i], l, int(lens[i]) - 1, 1, q[l, i].data_ptr(), k[l, i].data_ptr(),
+                  v[l, i].data_ptr(), o[l, i].data_ptr()) for i in range(n_streams)], flags))
+        return out
+
+    dev_batches = batches(q_d, k_d, v_d, o_d, xn.REQ_DEVICE_PTRS)
+    host_batches = batches(q_h, k_h, v_h, o_h, 0)
+
+    def step_device():
+        for b in dev_batches:
+            ctx.submit(b)
+
+    def step_host():
+        for b in host_batches:
+            ctx.submit(b)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    bytes_per_layer = algorithmic_bytes_per_layer(lens, Hq, Hkv, D)
+    bytes_per_step = bytes_per_layer * layers
+
+    # ---- device-resident timing (value) + live kernel timing (roofline) -------------------------
+    for _ in range(max(args.warmup, 3)):
+        step_device()
+    barrier()
+    s0 = ctx.stats()
+    ctx.profile_enable(True)
+    ctx.profile_read()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    wall0 = time.time()
+    ev0.record(tstream)
+    for _ in range(args.steps):
+        step_device()
+    ev1.record(tstream)
+    barrier()
+    wall1 = time.time()
+    ms = ev0.elapsed_time(ev1)
+    kern_ms, kern_n = ctx.profile_read()
+    ctx.profile_enable(False)
+    s1 = ctx.stats()
+    clocks = sampler.stop(wall0, wall1) if sampler else None
+    ctx.synchronize()
+
+    # ---- end to end through the blocking C-ABI call with host buffers ----------------------------
+    for _ in range(max(1, min(args.warmup, 3))):
+        step_host()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    e0.record(tstream)
+    for _ in range(args.steps):
+        step_host()
+    e1.record(tstream)
+    barrier()
+    e2e_wall_ms = (time.perf_counter() - t0) * 1e3
+    e2e_ms = max(e0.elapsed_time(e1), 0.0)
+    # the host-side staging is part of the call: the wall clock is the honest end-to-end time
+    e2e_ms = max(e2e_ms, e2e_wall_ms)
+
+    if world > 1:
+        t = torch.tensor([ms, e2e_ms, kern_ms / max(kern_n, 1)], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms, kern_avg_ms = (float(x) for x in t.tolist())
+        tot = torch.tensor([bytes_per_step], device="cuda", dtype=torch.float64)
+        dist.all_reduce(tot, op=dist.ReduceOp.SUM)
+        total_bytes_per_step = float(tot.item())
+    else:
+        kern_avg_ms = kern_ms / max(kern_n, 1)
+        total_bytes_per_step = float(bytes_per_step)
+
+    # outputs of both paths agree (same kernels, same inputs)
+    same = bool(torch.equal(o_d.cpu(), o_h)) if args.steps > 0 else None
+
+    line = None
+    if rank == 0:
+        peak, peak_kind = load_peaks()
+        achieved = bytes_per_layer / (kern_avg_ms * 1e-3) / 1e9 if kern_avg_ms > 0 else 0.0
+        value = total_bytes_per_step * args.steps / (ms * 1e-3) / 1e9
+        e2e_value = total_bytes_per_step * args.steps / (e2e_ms * 1e-3) / 1e9
+        launches = s1["kernel_launches"] - s0["kernel_launches"]
+        line = {
+            "metric": "decode_attn_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": f"{args.workload}: {desc}", "streams_per_gpu": n_streams,
+                       "layers": layers, "num_heads": Hq, "num_kv_heads": Hkv, "head_dim": D,
+                       "kv_tokens_per_gpu": int(lens.sum()), "page_tokens": 64,
+                       "parallelism": f"streams sharded over {world} GPU(s), no collective",
+                       "l2": "inputs larger than L2: %.1f GB of KV per GPU read per step" %
+                             (bytes_per_step / 1e9)},
+            "tokens_per_s": n_streams * world * args.steps / (ms * 1e-3),
+            "e2e": {"value": e2e_value, "unit": "GB/s",
+                    "h2d_bytes_per_step": layers * (q_elems + 2 * kv_elems) * 4,
+                    "d2h_bytes_per_step": layers * q_elems * 4,
+                    "ms_per_step": e2e_ms / args.steps,
+                    "tokens_per_s": n_streams * world * args.steps / (e2e_ms * 1e-3),
+                    "api": "xn_attention_batch with host pointers, one blocking call per layer"},
+            "gpu_launches": int(launches),
+            "roofline": {"bound": "hbm", "kernel": "attn_splitkv_kernel<32,4>",
+                         "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak if peak else None, "peak_source": peak_kind,
+                         "traffic": None, "avg_launch_ms": kern_avg_ms,
+                         "launches_timed": int(kern_n),
+                         "algorithmic_bytes_per_launch": bytes_per_layer},
+            "clocks": clocks,
+            "host_and_device_paths_agree": same,
+        }
+
+    # ---- CPU baseline on a bounded sample (rank 0, N=1 only) -------------------------------------
+    if rank == 0 and world == 1 and not args.no_cpu:
+        sample = min(args.cpu_streams, n_streams)
+        layer = layers // 2
+        kv = []
+        for i in range(sample):
+            kk, vv = streams[i].read_range(layer, 0, int(lens[i]) - 1) if lens[i] > 1 else (
+                np.zeros((Hkv, 0, D), np.float32), np.zeros((Hkv, 0, D), np.float32))
+            kv.append((kk, vv))
+        qs = [q_h[layer, i].numpy().reshape(1, Hq, 1, D) for i in range(sample)]
+        ks = [k_h[layer, i].numpy().reshape(1, Hkv, 1, D) for i in range(sample)]
+        vs = [v_h[layer, i].numpy().reshape(1, Hkv, 1, D) for i in range(sample)]
+        gbs, per_pass, outs, threads, reps = cpu_sample(lens[:sample], Hq, Hkv, D, kv, qs, ks, vs,
+                                                        layer, budget_s=args.cpu_seconds)
+        got = o_h[layer, :sample].numpy()
+        want = np.stack([o.reshape(Hq, D) for o in outs])
+        max_abs = float(np.max(np.abs(got - want)))
+        rel = float(np.linalg.norm(got - want) / np.linalg.norm(want))
+        line["cpu_baseline"] = {
+            "value": gbs, "unit": "GB/s", "cores": threads, "kind": "port",
+            "sample": f"{sample} of {n_streams} streams x 1 of {layers} layers (layer {layer}), "
+                      f"{reps} passes of {per_pass * 1e3:.1f} ms, host nproc {os.cpu_count()}",
+            "tokens_per_s": sample / per_pass}
+        line["parity_vs_cpu_sample"] = {"max_abs": max_abs, "rel_l2": rel,
+                                        "tolerance": "max_abs<=1e-4, rel_l2<=1e-5"}
+    elif rank == 0:
+        line["cpu_baseline"] = None
+
+    if rank == 0:
+        print(json.dumps(line))
+    ctx.close()
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--cpu-streams", type=int, default=16, help="streams in the CPU sample")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0, help="time budget of the CPU sample")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference_arm(args)
+    return run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

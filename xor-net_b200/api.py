@@ -163,6 +163,15 @@ class Context:
     def fill_normal(self, device_ptr: int, n: int, seed: int):
         self._check(self.lib.xn_fill_normal(self.handle, device_ptr, n, seed))
 
+    def profile_enable(self, on: bool = True):
+        self._check(self.lib.xn_profile_enable(self.handle, 1 if on else 0))
+
+    def profile_read(self):
+        """(milliseconds, launches) of the split-KV kernel since the last read."""
+        ms, n = C.c_double(), C.c_uint64()
+        self._check(self.lib.xn_profile_read(self.handle, C.byref(ms), C.byref(n)))
+        return ms.value, int(n.value)
+
     # -- blocking single-stream calls (host arrays) ------------------------------------------
 
     def attention(self, stream: Stream, layer: int, index_pos: int, q, k, v, rope: bool = False):

@@ -91,6 +91,11 @@ struct xn_ctx {
     xn_stats stats{};
     std::string last_error;
 
+    // optional device timing of the split-KV kernel
+    bool profile = false;
+    std::vector<cudaEvent_t> prof_events;  // pairs (start, stop), reused
+    size_t prof_used = 0;
+
     // combining of concurrent blocking callers
     std::mutex q_mu;
     std::condition_variable q_cv;
@@ -454,10 +459,24 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
     }
     if (sp.ctas > 0) {
         SplitKernel k = pick_split(c->nv_class, c->gt);
+        if (c->profile) {
+            if (c->prof_used + 2 > c->prof_events.size()) {
+                cudaEvent_t a, b;
+                XN_CUDA(c, cudaEventCreate(&a));
+                XN_CUDA(c, cudaEventCreate(&b));
+                c->prof_events.push_back(a);
+                c->prof_events.push_back(b);
+            }
+            XN_CUDA(c, cudaEventRecord(c->prof_events[c->prof_used], c->stream));
+        }
         k.fn<<<sp.ctas, k.threads, k.smem, c->stream>>>(reqs_d, units_d, items_d, cta_d, pages_d,
                                                         c->k_pool, c->v_pool, c->partials,
                                                         c->pool_pages, Hkv, D, nv, c->scale,
                                                         c->status_d);
+        if (c->profile) {
+            XN_CUDA(c, cudaEventRecord(c->prof_events[c->prof_used + 1], c->stream));
+            c->prof_used += 2;
+        }
         c->stats.kernel_launches += 1;
         c->stats.decode_launches += 1;
         if (!merge_units.empty()) {
@@ -715,6 +734,7 @@ int32_t xn_ctx_destroy(xn_ctx* c) {
         if (s.dev) cudaFree(s.dev);
         if (s.ev) cudaEventDestroy(s.ev);
     }
+    for (cudaEvent_t e : c->prof_events) cudaEventDestroy(e);
     if (c->q_rot) cudaFree(c->q_rot);
     if (c->partials) cudaFree(c->partials);
     if (c->io_host) cudaFreeHost(c->io_host);
@@ -749,6 +769,30 @@ int32_t xn_stats_get(xn_ctx* c, xn_stats* out) {
     c->stats.pages_in_use = c->stats.pages_total - c->free_pages.size();
     c->stats.streams_live = c->streams.size();
     *out = c->stats;
+    return XN_OK;
+}
+
+int32_t xn_profile_enable(xn_ctx* c, int32_t on) {
+    if (!ctx_ok(c)) return XN_ERR_HANDLE;
+    std::lock_guard<std::mutex> g(c->mu);
+    c->profile = on != 0;
+    return XN_OK;
+}
+
+int32_t xn_profile_read(xn_ctx* c, double* splitkv_ms, uint64_t* splitkv_launches) {
+    if (!ctx_ok(c)) return XN_ERR_HANDLE;
+    std::lock_guard<std::mutex> g(c->mu);
+    XN_CUDA(c, cudaSetDevice(c->device));
+    XN_CUDA(c, cudaStreamSynchronize(c->stream));
+    double total = 0.0;
+    for (size_t i = 0; i + 1 < c->prof_used; i += 2) {
+        float ms = 0.f;
+        XN_CUDA(c, cudaEventElapsedTime(&ms, c->prof_events[i], c->prof_events[i + 1]));
+        total += ms;
+    }
+    if (splitkv_ms) *splitkv_ms = total;
+    if (splitkv_launches) *splitkv_launches = c->prof_used / 2;
+    c->prof_used = 0;
     return XN_OK;
 }
 
