@@ -233,6 +233,12 @@ def run_gpu_arm(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     n_streams, Hq, Hkv, D, layers, lo, hi, desc = WORKLOADS[args.workload]
+    if args.layers:   # reduced-size run for profiler captures; named in config.workload
+        layers = args.layers
+        desc += f" [reduced to {layers} layers]"
+    if args.streams:
+        n_streams = args.streams
+        desc += f" [reduced to {n_streams} streams]"
     # every rank owns its own streams (weak scaling: per-GPU work is fixed); no data-path collective
     lens = stream_lengths(n_streams, lo, hi, BASE_SEED + 3000 + 7919 * rank)
     pages_needed = int(sum((int(L) + 63) // 64 for L in lens))
@@ -309,13 +315,14 @@ def run_gpu_arm(args):
     ctx.synchronize()
 
     # ---- end to end through the blocking C-ABI call with host buffers ----------------------------
-    for _ in range(max(1, min(args.warmup, 3))):
+    e2e_steps = 0 if args.no_e2e else args.steps
+    for _ in range(0 if args.no_e2e else max(1, min(args.warmup, 3))):
         step_host()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0 = time.perf_counter()
     e0.record(tstream)
-    for _ in range(args.steps):
+    for _ in range(e2e_steps):
         step_host()
     e1.record(tstream)
     barrier()
@@ -336,14 +343,14 @@ def run_gpu_arm(args):
         total_bytes_per_step = float(bytes_per_step)
 
     # outputs of both paths agree (same kernels, same inputs)
-    same = bool(torch.equal(o_d.cpu(), o_h)) if args.steps > 0 else None
+    same = bool(torch.equal(o_d.cpu(), o_h)) if e2e_steps > 0 else None
 
     line = None
     if rank == 0:
         peak, peak_kind = load_peaks()
         achieved = bytes_per_layer / (kern_avg_ms * 1e-3) / 1e9 if kern_avg_ms > 0 else 0.0
         value = total_bytes_per_step * args.steps / (ms * 1e-3) / 1e9
-        e2e_value = total_bytes_per_step * args.steps / (e2e_ms * 1e-3) / 1e9
+        e2e_value = total_bytes_per_step * e2e_steps / (e2e_ms * 1e-3) / 1e9
         launches = s1["kernel_launches"] - s0["kernel_launches"]
         line = {
             "metric": "decode_attn_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world,
@@ -360,8 +367,8 @@ def run_gpu_arm(args):
             "e2e": {"value": e2e_value, "unit": "GB/s",
                     "h2d_bytes_per_step": layers * (q_elems + 2 * kv_elems) * 4,
                     "d2h_bytes_per_step": layers * q_elems * 4,
-                    "ms_per_step": e2e_ms / args.steps,
-                    "tokens_per_s": n_streams * world * args.steps / (e2e_ms * 1e-3),
+                    "ms_per_step": e2e_ms / max(e2e_steps, 1),
+                    "tokens_per_s": n_streams * world * e2e_steps / (e2e_ms * 1e-3),
                     "api": "xn_attention_batch with host pointers, one blocking call per layer"},
             "gpu_launches": int(launches),
             "roofline": {"bound": "hbm", "kernel": "attn_splitkv_kernel<32,4>",
@@ -375,7 +382,7 @@ def run_gpu_arm(args):
         }
 
     # ---- CPU baseline on a bounded sample (rank 0, N=1 only) -------------------------------------
-    if rank == 0 and world == 1 and not args.no_cpu:
+    if rank == 0 and world == 1 and not args.no_cpu and e2e_steps > 0:
         sample = min(args.cpu_streams, n_streams)
         layer = layers // 2
         kv = []
@@ -420,6 +427,9 @@ def main():
     ap.add_argument("--cpu-streams", type=int, default=16, help="streams in the CPU sample")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="time budget of the CPU sample")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg")
+    ap.add_argument("--layers", type=int, default=0, help="override the layer count (profiling)")
+    ap.add_argument("--streams", type=int, default=0, help="override streams per GPU (profiling)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)
