@@ -173,6 +173,37 @@ XN_API int32_t xn_attention_rope(xn_ctx* ctx, xn_stream* stream, int32_t layer, 
  * until the host outputs are written.  Mixing host and device requests is an error. */
 XN_API int32_t xn_attention_batch(xn_ctx* ctx, int32_t n, const xn_req* reqs);
 
+/* No counterpart in the reference: decode attention for callers that must not allocate.
+ *
+ * Some users of this library run where cudaMalloc is off limits -- a serving loop that has handed
+ * all device memory to its own arena, a latency-critical thread where an allocation's implicit
+ * device synchronisation is unacceptable, a plugin host that forbids it.  This one entry point
+ * computes single-token attention (one query row per head over kv_len cached positions, q.k *
+ * 1/sqrt(head_dim), softmax, weighted V sum; query head h reads KV head h / (num_heads /
+ * num_kv_heads)) without allocating anything: it calls no cudaMalloc, cudaFree or other
+ * allocating routine, and creates no context.  The split-KV partial results go to a fixed scratch
+ * array inside the library image (about 1.0 MiB of every GPU that loads the library, held until
+ * the process exits).
+ *
+ * All pointers are device memory owned by the caller on the current device:
+ *   q [num_heads, head_dim], out [num_heads, head_dim],
+ *   k_cache, v_cache [num_kv_heads, capacity, head_dim] (the reference's ring layout,
+ *   fast_attention.rs:107-108) with positions 0..kv_len-1 already written, the new token included.
+ * Work is enqueued on cuda_stream (NULL = the default stream); the call does not wait for it.
+ *
+ * Limits, rejected with XN_ERR_CAPACITY and a message in xn_last_error(NULL): head_dim <= 256 and
+ * num_heads <= 1024 (the scratch holds 1024 partial records of 260 floats).
+ *
+ * The first call on each device looks up the scratch array's device address; make that first
+ * call before starting any stream capture.  Every call on a device shares the one scratch array:
+ * two calls whose kernels overlap on the GPU (different streams, or different threads on
+ * different streams) race on it -- keep calls on one stream or order them yourself.  Nothing in
+ * the scratch has to start at zero; each call rewrites every record it later reads. */
+XN_API int32_t xn_decode_attention_static(const float* q, const float* k_cache, const float* v_cache,
+                                          float* out, int32_t num_heads, int32_t num_kv_heads,
+                                          int32_t head_dim, int64_t kv_len, int64_t capacity,
+                                          void* cuda_stream);
+
 /* ---- RoPE tables ----------------------------------------------------------------------------- */
 
 /* Builds cos/sin [max_pos, head_dim/2] exactly as Cache::new does (models/llama/mod.rs:210-265):

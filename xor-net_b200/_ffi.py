@@ -62,6 +62,9 @@ SIGNATURES = {
     "xn_attention_rope": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int32,
                                       C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "xn_attention_batch": (C.c_int32, [C.c_void_p, C.c_int32, C.POINTER(Req)]),
+    "xn_decode_attention_static": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                               C.c_int32, C.c_int32, C.c_int32, C.c_int64,
+                                               C.c_int64, C.c_void_p]),
     "xn_rope_tables": (C.c_int32, [C.c_float, C.c_int32, C.c_int32, C.c_float, C.c_float,
                                    C.c_float, C.c_int32, c_f32p, c_f32p]),
     "xn_kv_read": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int64,

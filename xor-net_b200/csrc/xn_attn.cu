@@ -19,6 +19,7 @@
 #include "xn_common.cuh"
 #include "xn_decode.cuh"
 #include "xn_plan.hpp"
+#include "xn_static_decode.cuh"
 
 using namespace xn;
 
@@ -1062,3 +1063,67 @@ int32_t xn_plan_split(int32_t n_units, const int32_t* kv_len, int32_t tile_token
 }
 
 }  // extern "C"
+
+// ============================================================================================
+// Allocation-free decode entry point
+// ============================================================================================
+
+// Scratch of xn_decode_attention_static: partial (max, sum, accumulator) records of the split-KV
+// pass.  It is part of the library image, so every GPU that loads the library holds these
+// kStaticScratchFloats * 4 bytes (about 1.0 MiB) until the process exits.  In host code this name
+// is only a handle for cudaGetSymbolAddress, never a device address.
+static __device__ __align__(256) float g_static_scratch[xn::kStaticScratchFloats];
+
+namespace {
+constexpr int kStaticMaxDevices = 64;
+std::mutex g_static_mu;
+float* g_static_scratch_addr[kStaticMaxDevices] = {nullptr};  // per device, resolved once
+}  // namespace
+
+extern "C" int32_t xn_decode_attention_static(const float* q, const float* k_cache,
+                                              const float* v_cache, float* out, int32_t num_heads,
+                                              int32_t num_kv_heads, int32_t head_dim,
+                                              int64_t kv_len, int64_t capacity, void* cuda_stream) {
+    if (!q || !k_cache || !v_cache || !out) return fail(nullptr, XN_ERR_ARG, "null tensor pointer");
+    if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads != 0)
+        return fail(nullptr, XN_ERR_SHAPE, "num_heads %d must be a positive multiple of num_kv_heads %d",
+                    num_heads, num_kv_heads);
+    if (head_dim < 1 || head_dim > kStaticMaxDim)
+        return fail(nullptr, XN_ERR_CAPACITY,
+                    "head_dim %d is beyond the static scratch limit of %d", head_dim, kStaticMaxDim);
+    if (num_heads > kStaticMaxRecords)
+        return fail(nullptr, XN_ERR_CAPACITY,
+                    "num_heads %d is beyond the static scratch limit of %d partial records",
+                    num_heads, kStaticMaxRecords);
+    if (kv_len < 1 || capacity < kv_len || kv_len > (int64_t(1) << 40))
+        return fail(nullptr, XN_ERR_ARG, "need 1 <= kv_len <= capacity");
+
+    int dev = -1;
+    XN_CUDA(nullptr, cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kStaticMaxDevices)
+        return fail(nullptr, XN_ERR_ARG, "device ordinal %d outside 0..%d", dev, kStaticMaxDevices - 1);
+    float* scratch = nullptr;
+    {
+        // First call on this device: resolve the device address of the static array, with this
+        // device current.  Later calls reuse it.
+        std::lock_guard<std::mutex> g(g_static_mu);
+        if (!g_static_scratch_addr[dev]) {
+            void* p = nullptr;
+            XN_CUDA(nullptr, cudaGetSymbolAddress(&p, g_static_scratch));
+            g_static_scratch_addr[dev] = static_cast<float*>(p);
+        }
+        scratch = g_static_scratch_addr[dev];
+    }
+
+    // as many splits as the record budget allows, at least 256 tokens each, at most ~4 waves
+    int64_t splits = std::min<int64_t>(kStaticMaxRecords / num_heads, (kv_len + 255) / 256);
+    splits = std::max<int64_t>(1, std::min<int64_t>(splits, std::max<int64_t>(1, 592 / num_heads)));
+    cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+    const float scale = 1.0f / sqrtf(float(head_dim));
+    static_split_kernel<<<dim3(unsigned(splits), unsigned(num_heads)), 128, 0, st>>>(
+        q, k_cache, v_cache, scratch, num_heads, num_kv_heads, head_dim, kv_len, capacity,
+        int(splits), scale);
+    static_merge_kernel<<<unsigned(num_heads), 256, 0, st>>>(scratch, out, head_dim, int(splits));
+    XN_CUDA(nullptr, cudaGetLastError());
+    return XN_OK;
+}
