@@ -11,12 +11,14 @@ import xor_net_b200 as xn
 from gpu_util import Pair, assert_parity, errs, rand_qkv
 
 pytestmark = pytest.mark.gpu
+F32 = 1  # XN_PREFILL_F32
 
 
 @pytest.fixture(scope="module")
 def ctx2b():
+    # exact-f32 prefill: this module checks the f32 tolerances (the TF32 kernel has its own tests)
     c = xn.Context(num_layers=3, num_heads=20, num_kv_heads=5, head_dim=128, pool_pages=600,
-                   shuffle_seed=11, rope=xn.rope_tables(500000.0, 128, 8192))
+                   shuffle_seed=11, rope=xn.rope_tables(500000.0, 128, 8192), prefill_mode=F32)
     yield c
     c.close()
 
@@ -27,7 +29,7 @@ def ctx2b():
 def test_head_dims(D):
     rng = np.random.default_rng(D)
     for Hq, Hkv in [(4, 2), (3, 3), (8, 2)]:
-        ctx = xn.Context(2, Hq, Hkv, D, pool_pages=16)
+        ctx = xn.Context(2, Hq, Hkv, D, pool_pages=16, prefill_mode=F32)
         p = Pair(ctx, 300)
         q, k, v = rand_qkv(rng, Hq, Hkv, 70, D)
         got, want = p.step(1, 0, q, k, v)                 # prefill across a page boundary
@@ -43,7 +45,7 @@ def test_head_dims(D):
 @pytest.mark.parametrize("Hq,Hkv", [(1, 1), (2, 1), (3, 1), (4, 1), (5, 1), (8, 1), (12, 4), (32, 8), (20, 5)])
 def test_group_sizes(Hq, Hkv):
     rng = np.random.default_rng(Hq * 100 + Hkv)
-    ctx = xn.Context(1, Hq, Hkv, 64, pool_pages=16)
+    ctx = xn.Context(1, Hq, Hkv, 64, pool_pages=16, prefill_mode=F32)
     p = Pair(ctx, 512)
     q, k, v = rand_qkv(rng, Hq, Hkv, 130, 64)
     got, want = p.step(0, 0, q, k, v)
@@ -127,7 +129,7 @@ def test_gap_positions_read_as_zeros(ctx2b):
 def test_ring_fold_matches_oracle():
     # positions beyond the capacity fold with % capacity and overwritten slots are visited again
     rng = np.random.default_rng(29)
-    ctx = xn.Context(1, 4, 2, 16, pool_pages=8)
+    ctx = xn.Context(1, 4, 2, 16, pool_pages=8, prefill_mode=F32)
     p = Pair(ctx, 100)
     pos = 0
     for S in (60, 30, 25, 1, 1, 140):
@@ -145,7 +147,7 @@ def test_ring_fold_matches_oracle():
 def test_fused_rope_is_bit_exact(theta, D, Hq, Hkv):
     rng = np.random.default_rng(31)
     cos, sin = xn.rope_tables(theta, D, 1024)
-    ctx = xn.Context(1, Hq, Hkv, D, pool_pages=16, rope=(cos, sin))
+    ctx = xn.Context(1, Hq, Hkv, D, pool_pages=16, rope=(cos, sin), prefill_mode=F32)
     st = ctx.new_stream(1024)
     ref = xo.RingCache(1, Hkv, 1024, D)
     pos = 0

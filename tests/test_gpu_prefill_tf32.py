@@ -1,0 +1,113 @@
+"""The tensor-core (tcgen05, TF32) causal prefill kernel against the CPU oracle, through the C ABI.
+
+Tolerance of the TF32 path: relative L2 error <= 5e-3 per output tensor (inputs are truncated to
+TF32 by the tensor cores; accumulation is f32).  The cache written by a TF32 prefill is still
+exact, so a decode step that follows meets the f32 tolerances.
+"""
+import numpy as np
+import pytest
+
+import oracle as xo
+import xor_net_b200 as xn
+from gpu_util import Pair, assert_parity, errs, rand_qkv
+
+pytestmark = pytest.mark.gpu
+TF32 = 2         # XN_PREFILL_TF32: use the tensor-core kernel for every multi-row call
+TF32_REL = 5e-3  # north-star bound for the TF32 prefill path
+
+
+def check_tf32(got, want, what):
+    a, r = errs(got, want)
+    assert np.all(np.isfinite(got)), f"{what}: non-finite output"
+    assert r <= TF32_REL, f"{what}: rel {r:.3e} > {TF32_REL}"
+    return a, r
+
+
+@pytest.mark.parametrize("S", [2, 64, 127, 128, 129, 200, 257, 1000])
+def test_prefill_lengths_2b_shape(S):
+    rng = np.random.default_rng(S)
+    ctx = xn.Context(1, 20, 5, 128, pool_pages=40, shuffle_seed=3, prefill_mode=TF32)
+    p = Pair(ctx, 2048)
+    got, want = p.step(0, 0, *rand_qkv(rng, 20, 5, S, 128))
+    a, r = check_tf32(got, want, f"S={S}")
+    print(f"S={S}: max abs {a:.2e} rel {r:.2e}")
+    assert ctx.stats()["prefill_launches"] == 1
+    p.check_cache(0)                        # appended K/V are exact
+    q, k, v = rand_qkv(rng, 20, 5, 1, 128)  # decode over the prefilled cache: f32 tolerances
+    got, want = p.step(0, S, q, k, v)
+    assert_parity(got, want, f"decode after TF32 prefill S={S}")
+    ctx.close()
+
+
+def test_chunked_prefill_with_offset():
+    # index_pos > 0 with many rows: the causal diagonal moves by index_pos
+    rng = np.random.default_rng(77)
+    ctx = xn.Context(2, 20, 5, 128, pool_pages=40, prefill_mode=TF32)
+    p = Pair(ctx, 2048)
+    pos = 0
+    for S in (300, 512, 70, 129):
+        got, want = p.step(1, pos, *rand_qkv(rng, 20, 5, S, 128))
+        check_tf32(got, want, f"chunk at {pos}+{S}")
+        pos += S
+    p.check_cache(1)
+    ctx.close()
+
+
+@pytest.mark.parametrize("Hq,Hkv,D", [(32, 32, 100), (8, 2, 64), (4, 4, 32), (6, 2, 96), (3, 1, 16)])
+def test_head_dims_and_groups(Hq, Hkv, D):
+    rng = np.random.default_rng(D)
+    ctx = xn.Context(1, Hq, Hkv, D, pool_pages=24, prefill_mode=TF32)
+    p = Pair(ctx, 1024)
+    got, want = p.step(0, 0, *rand_qkv(rng, Hq, Hkv, 333, D))
+    check_tf32(got, want, f"D={D}")
+    got, want = p.step(0, 333, *rand_qkv(rng, Hq, Hkv, 150, D))
+    check_tf32(got, want, f"D={D} second chunk")
+    ctx.close()
+
+
+def test_fused_rope_prefill_config2_shape():
+    # BASELINE config 2: 2048 tokens, 20/5 heads, head_dim 128, fused RoPE (theta 500000) and
+    # append into 64-token pages, causal; output 2048 x 20 x 128
+    rng = np.random.default_rng(299792458 + 2000)
+    cos, sin = xn.rope_tables(500000.0, 128, 4096)
+    ctx = xn.Context(1, 20, 5, 128, pool_pages=40, shuffle_seed=5, rope=(cos, sin))  # AUTO mode
+    st = ctx.new_stream(4096)
+    ref = xo.RingCache(1, 5, 4096, 128)
+    q, k, v = rand_qkv(rng, 20, 5, 2048, 128)
+    got = ctx.attention(st, 0, 0, q, k, v, rope=True)
+    assert ctx.stats()["prefill_launches"] == 1
+    want = xo.fast_attention(xo.tensor_rope(q, cos, sin, 0), xo.tensor_rope(k, cos, sin, 0), v, 0, 0,
+                             ref, 20, 5, 128)
+    a, r = check_tf32(got, want, "config 2")
+    print(f"config2 TF32 prefill: max abs {a:.2e} rel {r:.2e}")
+    kd, vd = st.read_range(0, 0, 2048)
+    assert np.array_equal(kd.ravel(), ref.k_buffer(0)[: 5 * 4096 * 128].reshape(5, 4096, 128)[:, :2048].ravel())
+    ctx.close()
+
+
+def test_seq_major_prefill():
+    rng = np.random.default_rng(5)
+    ctx = xn.Context(1, 20, 5, 128, pool_pages=16, prefill_mode=TF32)
+    p = Pair(ctx, 512)
+    q, k, v = rand_qkv(rng, 20, 5, 300, 128)
+    want = xo.fast_attention(q, k, v, 0, 0, p.ref, 20, 5, 128)
+    outs = ctx.attention_batch([p.st], 0, [0], [xo.transpose_heads_to_seq(q)],
+                               [xo.transpose_heads_to_seq(k)], [xo.transpose_heads_to_seq(v)],
+                               seq_major=True)
+    check_tf32(xo.transpose_seq_to_heads(outs[0], 20, 128), want, "seq-major TF32")
+    ctx.close()
+
+
+def test_large_scores_trigger_the_lazy_rescale():
+    # scores that keep growing along the sequence force accumulator rescales (max jumps > 2^8)
+    rng = np.random.default_rng(9)
+    Hq, Hkv, D, S = 4, 2, 64, 400
+    ctx = xn.Context(1, Hq, Hkv, D, pool_pages=16, prefill_mode=TF32)
+    p = Pair(ctx, 512)
+    q, k, v = rand_qkv(rng, Hq, Hkv, S, D)
+    ramp = np.linspace(0.2, 6.0, S, dtype=np.float32)[None, None, :, None]
+    k = (np.abs(k) * ramp).astype(np.float32)
+    q = (np.abs(q) * 2.0).astype(np.float32)
+    got, want = p.step(0, 0, q, k, v)
+    check_tf32(got, want, "rescale")
+    ctx.close()

@@ -45,7 +45,7 @@ def test_static_entry_matches_regular_entry_twice(Hq, Hkv, D, L0):
 
     lib = xn.load()
     rng = np.random.default_rng(1000 + D)
-    ctx = xn.Context(1, Hq, Hkv, D, pool_pages=40)
+    ctx = xn.Context(1, Hq, Hkv, D, pool_pages=40, prefill_mode=1)
     st = ctx.new_stream(2048)
     ctx.attention(st, 0, 0, *rand_qkv(rng, Hq, Hkv, L0, D))  # fill the cache
     grown = []

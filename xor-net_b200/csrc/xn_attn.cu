@@ -19,6 +19,7 @@
 #include "xn_common.cuh"
 #include "xn_decode.cuh"
 #include "xn_plan.hpp"
+#include "xn_prefill_tf32.cuh"
 #include "xn_static_decode.cuh"
 
 using namespace xn;
@@ -91,6 +92,11 @@ struct xn_ctx {
     int* status_h = nullptr;  // pinned
     xn_stats stats{};
     std::string last_error;
+
+    // tensor-core prefill (tcgen05 TF32): tensor maps over the K and V pools
+    bool tf32_ok = false;
+    int tf32_min_rows = 128;
+    CUtensorMap k_map, v_map;
 
     // optional device timing of the split-KV kernel
     bool profile = false;
@@ -181,6 +187,37 @@ int nv_class_for(int nv) {
     if (nv <= 16) return 16;
     if (nv <= 32) return 32;
     return 64;
+}
+
+// ---- TMA tensor maps (driver entry point resolved at run time; libcuda is not linked) -------
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+// f32 tensor of `rank` dims (dims[0] innermost, contiguous), byte strides for dims 1..rank-1,
+// box of box[] elements, 128-byte swizzle, zero fill outside the tensor.
+bool make_map_f32(CUtensorMap* map, const void* base, int rank, const cuuint64_t* dims,
+                  const cuuint64_t* strides_bytes, const cuuint32_t* box) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, cuuint32_t(rank), const_cast<void*>(base), dims,
+              strides_bytes, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 // ---- buffers -----------------------------------------------------------------------------
@@ -286,6 +323,14 @@ int32_t validate_req(xn_ctx* c, const xn_req& r) {
     return XN_OK;
 }
 
+// Whether a request goes to the tcgen05 prefill kernel (shape and mode only; pointer alignment is
+// re-checked at launch where the device pointers are known).
+bool use_tf32(const xn_ctx* c, const xn_req& r) {
+    if (!c->tf32_ok || c->prefill_mode == XN_PREFILL_F32) return false;
+    if (r.index_pos + r.seq_len > r.stream->cap) return false;
+    return r.seq_len >= (c->prefill_mode == XN_PREFILL_TF32 ? 2 : c->tf32_min_rows);
+}
+
 // reqs[i] are valid, on distinct streams, all host-mode or all device-mode.
 int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
     const int Hq = c->num_heads, Hkv = c->num_kv_heads, D = c->head_dim, nv = c->nv;
@@ -315,6 +360,7 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         }
         if (r.flags & XN_REQ_ROPE) qrot_floats += align_up(qf, 4);
         if (end > s->cap) n_ring_rows += r.seq_len;
+        else if (use_tf32(c, r)) { /* served by the tensor-core prefill kernel */ }
         else n_units += (long long)r.seq_len * Hkv * c->subs;
         max_rows = std::max<long long>(max_rows, (long long)r.seq_len * (Hq + 2 * Hkv));
     }
@@ -335,6 +381,7 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
     std::vector<int32_t> kv_lens;
     kv_lens.reserve(size_t(n_units));
     std::vector<int32_t> ring_rows;
+    std::vector<int> tf32_reqs;
     size_t in_off = 0, out_off = io_in, qrot_off = 0;
     for (int i = 0; i < n; ++i) {
         const xn_req& r = reqs[i];
@@ -380,6 +427,8 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         d.cap = int(std::min<int64_t>(s->cap, int64_t(1) << 30));
         if (r.index_pos + S > s->cap) {
             for (int t = 0; t < S; ++t) { ring_rows.push_back(i); ring_rows.push_back(t); }
+        } else if (use_tf32(c, r)) {
+            tf32_reqs.push_back(i);
         } else {
             for (int h = 0; h < Hkv; ++h)
                 for (int sb = 0; sb < c->subs; ++sb)
@@ -486,6 +535,36 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
                 reqs_d, units_d, merge_d, int(merge_units.size()), c->partials, nv, D);
             c->stats.kernel_launches += 1;
         }
+    }
+    for (int i : tf32_reqs) {
+        const ReqDev& d = rd[i];
+        if ((reinterpret_cast<uintptr_t>(d.q) & 15) || (reinterpret_cast<uintptr_t>(d.out) & 15))
+            return fail(c, XN_ERR_ARG, "tensor-core prefill needs 16-byte aligned q and out");
+        CUtensorMap q_map;
+        const cuuint64_t qdims[3] = {cuuint64_t(D), cuuint64_t(d.seq_len), cuuint64_t(Hq)};
+        const cuuint64_t qstr[2] = {cuuint64_t(d.q_ts) * 4, cuuint64_t(d.q_hs) * 4};
+        const cuuint32_t qbox[3] = {32, cuuint32_t(pf::kBM), 1};
+        if (!make_map_f32(&q_map, d.q, 3, qdims, qstr, qbox))
+            return fail(c, XN_ERR_CUDA, "cuTensorMapEncodeTiled failed for the query tensor");
+        PrefillArgs pa;
+        pa.pages = pages_d + d.page_off;
+        pa.out = d.out;
+        pa.o_hs = d.o_hs;
+        pa.o_ts = d.o_ts;
+        pa.kv_row_base_mul = (long long)Hkv * kPageTokens;
+        pa.layer_page_base = (long long)d.layer * c->pool_pages;
+        pa.num_kv_heads = Hkv;
+        pa.group = c->group;
+        pa.seq_len = d.seq_len;
+        pa.index_pos = d.index_pos;
+        pa.head_dim = D;
+        pa.scale_log2 = c->scale * 1.4426950408889634f;
+        pa.status = c->status_d;
+        dim3 grid(unsigned((d.seq_len + pf::kBM - 1) / pf::kBM), unsigned(Hq));
+        prefill_tf32_kernel<<<grid, pf::kThreads, pf::kSmemBytes, c->stream>>>(q_map, c->k_map,
+                                                                              c->v_map, pa);
+        c->stats.kernel_launches += 1;
+        c->stats.prefill_launches += 1;
     }
     if (!ring_rows.empty()) {
         const int rows = int(ring_rows.size() / 2);
@@ -703,6 +782,30 @@ int32_t xn_ctx_create(const xn_ctx_desc* d, xn_ctx** out_ctx) {
         SplitKernel k = pick_split(c->nv_class, c->gt);
         XN_CREATE_CUDA(cudaFuncSetAttribute(reinterpret_cast<const void*>(k.fn),
                                             cudaFuncAttributeMaxDynamicSharedMemorySize, int(k.smem)));
+    }
+
+    // tensor-core prefill: possible when rows are exactly head_dim floats and TMA can address them
+    {
+        const unsigned long long rows = (unsigned long long)pages * d->num_layers * d->num_kv_heads * kPageTokens;
+        if (d->head_dim % 4 == 0 && d->head_dim >= 16 && d->head_dim <= 128 && rows < (1ull << 31)) {
+            const cuuint64_t dims[2] = {cuuint64_t(d->head_dim), cuuint64_t(rows)};
+            const cuuint64_t str[1] = {cuuint64_t(d->head_dim) * 4};
+            const cuuint32_t box[2] = {32, cuuint32_t(pf::kBN)};
+            c->tf32_ok = make_map_f32(&c->k_map, c->k_pool, 2, dims, str, box) &&
+                         make_map_f32(&c->v_map, c->v_pool, 2, dims, str, box);
+            if (c->tf32_ok)
+                XN_CREATE_CUDA(cudaFuncSetAttribute(reinterpret_cast<const void*>(prefill_tf32_kernel),
+                                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                    pf::kSmemBytes));
+        }
+        if (const char* env = getenv("XORNET_ATTN_TF32_MIN_ROWS")) {
+            int v = atoi(env);
+            if (v > 0) c->tf32_min_rows = v;
+        }
+        if (d->prefill_mode == XN_PREFILL_TF32 && !c->tf32_ok) {
+            fail(nullptr, XN_ERR_SHAPE, "head_dim %d cannot use the TF32 prefill kernel", d->head_dim);
+            return bail(XN_ERR_SHAPE);
+        }
     }
 
     c->free_pages.resize(size_t(pages));

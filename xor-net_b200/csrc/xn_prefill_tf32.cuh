@@ -1,0 +1,428 @@
+// Causal prefill attention on the 5th-generation tensor cores (tcgen05, TF32 inputs, f32
+// accumulators in tensor memory), sm_100a only.
+//
+// Replaces, for long prompts, the per-row loop of the reference (src/nn/fast_attention.rs:
+// 157-198): S = Q K^T and O = P V become tcgen05.mma.kind::tf32 instructions; the causal loop
+// bound `limit = index_pos + t_q` (:162) becomes "key tiles above the diagonal are never issued,
+// the diagonal tile is masked element-wise".
+//
+// One thread block = one (query head, 128-row query tile).  Key/value tiles are the cache's
+// 64-token pages.  Roles (192 threads):
+//   warp 0      TMA producer: tensor-map loads of the Q tile (once) and of K / V pages into
+//               128-byte-swizzled shared memory, two stages each, mbarrier byte counting;
+//   warp 1      MMA issuer (one lane): S_j = Q K_j^T into one of two 64-column TMEM buffers,
+//               then O += P_j V_j with P read from TMEM (it overwrites S_j in place) and V taken
+//               MN-major straight from its [token][dim] page; tcgen05.commit signals mbarriers;
+//   warps 2..5  softmax: thread r owns query row r: tcgen05.ld of its S row, scale, causal mask,
+//               running max / sum, exp2, P written back with tcgen05.st.  The accumulator is
+//               rescaled lazily: only when a row's maximum grows by more than 2^8.
+// Every wait is bounded; on expiry the kernel records a status code, drains and returns.
+#pragma once
+#include <cuda.h>
+
+#include "xn_common.cuh"
+
+namespace xn {
+
+struct PrefillArgs {
+    const int* pages;     // page ids of the stream (device)
+    float* out;           // output base
+    long long o_hs, o_ts; // output head / token strides in floats
+    long long kv_row_base_mul;  // rows per page slot block: num_kv_heads * 64
+    long long layer_page_base;  // layer * pool_pages
+    int num_kv_heads;
+    int group;            // query heads per KV head
+    int seq_len;          // S
+    int index_pos;        // P
+    int head_dim;         // D (multiple of 4, 16..128)
+    float scale_log2;     // (1/sqrt(D)) * log2(e)
+    int* status;
+};
+
+namespace pf {
+
+constexpr int kBM = 128;          // query rows per block
+constexpr int kBN = 64;           // keys per tile (= page)
+constexpr int kKB = 4;            // 32-float (128-byte) column blocks per row, at most
+constexpr int kQSub = kBM * 128;  // bytes of one Q column block  [128 rows x 128 B]
+constexpr int kKVSub = kBN * 128; // bytes of one K/V column block [64 rows x 128 B]
+constexpr int kQBytes = kKB * kQSub;     // 64 KB
+constexpr int kKVBytes = kKB * kKVSub;   // 32 KB
+constexpr int kStages = 2;
+constexpr int kSmemData = kQBytes + 2 * kStages * kKVBytes;  // 192 KB
+constexpr int kSmemBytes = kSmemData + 1024 /* alignment slack */ + 256 /* barriers */;
+constexpr int kThreads = 192;
+constexpr int kTmemCols = 256;    // S0 [0,64) S1 [64,128) O [128,256)
+constexpr float kRescaleThreshold = 8.0f;  // log2 units
+
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int x, int y, int z,
+                                            uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(smem_u32(dst)),
+        "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y,
+                                            uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%2, %3}], [%4];" ::"r"(smem_u32(dst)),
+        "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+
+// Shared-memory matrix descriptor for tcgen05.mma, 128-byte swizzle.
+//   bits [0,14) start address >> 4, [16,30) leading byte offset >> 4, [32,46) stride byte
+//   offset >> 4, [46,48) descriptor version (1 on sm_100), [61,64) layout (2 = 128-byte swizzle).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= uint64_t((saddr >> 4) & 0x3fff);
+    d |= uint64_t((lbo_bytes >> 4) & 0x3fff) << 16;
+    d |= uint64_t((sbo_bytes >> 4) & 0x3fff) << 32;
+    d |= uint64_t(1) << 46;
+    d |= uint64_t(2) << 61;
+    return d;
+}
+
+// Instruction descriptor, kind::tf32, f32 accumulate: [4,6) D format 1 = f32, [7,10) A format
+// 2 = tf32, [10,13) B format 2 = tf32, bit 15 A major, bit 16 B major (1 = MN-major),
+// [17,23) N >> 3, [24,29) M >> 4.
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n, int b_mn_major) {
+    return (1u << 4) | (2u << 7) | (2u << 10) | (uint32_t(b_mn_major) << 16) |
+           (uint32_t(n >> 3) << 17) | (uint32_t(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                       uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+                                       uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void mma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                     smem_u32(bar))
+                 : "memory");
+}
+
+__device__ __forceinline__ void fence_before_sync() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void fence_after_sync() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, "
+        "%12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, "
+        "%30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+          "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, "
+        "%12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, "
+        "%30, %31, %32};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]),
+        "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
+        "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__device__ __forceinline__ uint32_t to_tf32_rna(float x) {
+    uint32_t y;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(y) : "f"(x));
+    return y;
+}
+
+}  // namespace pf
+
+__global__ void __launch_bounds__(pf::kThreads, 1)
+prefill_tf32_kernel(const __grid_constant__ CUtensorMap q_map,
+                    const __grid_constant__ CUtensorMap k_map,
+                    const __grid_constant__ CUtensorMap v_map, const PrefillArgs a) {
+    using namespace pf;
+    extern __shared__ unsigned char smem_dyn[];
+    // 128-byte swizzled tiles want 1024-byte alignment
+    unsigned char* smem = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
+    unsigned char* q_s = smem;
+    unsigned char* k_s = smem + kQBytes;
+    unsigned char* v_s = k_s + kStages * kKVBytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kSmemData);
+    uint64_t* q_full = bars + 0;
+    uint64_t* k_full = bars + 1;    // [2]
+    uint64_t* k_empty = bars + 3;   // [2]
+    uint64_t* v_full = bars + 5;    // [2]
+    uint64_t* v_empty = bars + 7;   // [2]
+    uint64_t* s_full = bars + 9;    // [2]
+    uint64_t* p_full = bars + 11;   // [2]
+    uint64_t* pv_done = bars + 13;  // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 17);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n_qtiles = (a.seq_len + kBM - 1) / kBM;
+    const int qt = n_qtiles - 1 - blockIdx.x;  // longest rows first
+    const int h = blockIdx.y;
+    const int h_kv = h / a.group;
+    const int t0 = qt * kBM;
+    const int last_row = min(t0 + kBM, a.seq_len) - 1;
+    const int n_tiles = (a.index_pos + last_row) / kBN + 1;
+    const int D = a.head_dim;
+    const int n_kb = (D + 31) / 32;        // column blocks actually loaded
+    const int k_steps = (D + 7) / 8;       // K=8 MMA steps over head_dim
+    const int n_pv = (D + 15) / 16 * 16;   // N of the PV MMA
+
+    if (tid == 0) {
+        mbar_init(q_full, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&k_full[s], 1);
+            mbar_init(&k_empty[s], 1);
+            mbar_init(&v_full[s], 1);
+            mbar_init(&v_empty[s], 1);
+            mbar_init(&s_full[s], 1);
+            mbar_init(&p_full[s], 128);
+            mbar_init(&pv_done[s], 1);
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         smem_u32(tmem_slot)),
+                     "r"(uint32_t(kTmemCols))
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_o = tmem_base + 128;
+
+    if (warp == 0) {
+        // =============================== TMA producer ===============================
+        if (lane == 0) {
+            mbar_arrive_expect_tx(q_full, uint32_t(n_kb) * kQSub);
+            for (int kb = 0; kb < n_kb; ++kb)
+                tma_load_3d(q_s + kb * kQSub, &q_map, kb * 32, t0, h, q_full);
+            for (int j = 0; j < n_tiles; ++j) {
+                const int s = j & 1;
+                const uint32_t ph = uint32_t((j >> 1) & 1);
+                const int page = a.pages[j];
+                const long long row = ((a.layer_page_base + page) * a.num_kv_heads + h_kv) * kBN;
+                if (j >= kStages && !mbar_wait_bounded(&k_empty[s], ph ^ 1)) {
+                    atomicExch(a.status, kDevWaitEmpty); *abort_flag = 1; break;
+                }
+                mbar_arrive_expect_tx(&k_full[s], uint32_t(n_kb) * kKVSub);
+                for (int kb = 0; kb < n_kb; ++kb)
+                    tma_load_2d(k_s + s * kKVBytes + kb * kKVSub, &k_map, kb * 32, int(row), &k_full[s]);
+                if (j >= kStages && !mbar_wait_bounded(&v_empty[s], ph ^ 1)) {
+                    atomicExch(a.status, kDevWaitEmpty); *abort_flag = 1; break;
+                }
+                mbar_arrive_expect_tx(&v_full[s], uint32_t(n_kb) * kKVSub);
+                for (int kb = 0; kb < n_kb; ++kb)
+                    tma_load_2d(v_s + s * kKVBytes + kb * kKVSub, &v_map, kb * 32, int(row), &v_full[s]);
+                if (*abort_flag) break;
+            }
+        }
+    } else if (warp == 1) {
+        // =============================== MMA issuer ===============================
+        if (lane == 0) {
+            const uint32_t idesc_qk = make_idesc(kBM, kBN, 0);
+            const uint32_t idesc_pv = make_idesc(kBM, n_pv, 1);
+            const uint32_t q_addr = smem_u32(q_s), k_addr = smem_u32(k_s), v_addr = smem_u32(v_s);
+            bool ok = mbar_wait_bounded(q_full, 0);
+            if (!ok) { atomicExch(a.status, kDevWaitFull); *abort_flag = 1; }
+            // issues O += P_j V_j
+            auto issue_pv = [&](int j) -> bool {
+                const int s = j & 1;
+                const uint32_t ph = uint32_t((j >> 1) & 1);
+                if (!mbar_wait_bounded(&p_full[s], ph) || !mbar_wait_bounded(&v_full[s], ph)) return false;
+                fence_after_sync();
+                for (int ks = 0; ks < kBN / 8; ++ks) {
+                    // V is [token][dim]: MN-major B; 8 tokens = 1024 B inside each column block,
+                    // column blocks kKVSub apart (leading offset), 8-token groups 1024 B apart
+                    const uint64_t bd = smem_desc(v_addr + s * kKVBytes + ks * 1024, kKVSub, 1024);
+                    mma_ts(tmem_o, tmem_base + s * kBN + ks * 8, bd, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+                }
+                mma_commit(&v_empty[s]);
+                mma_commit(&pv_done[s]);
+                return true;
+            };
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                const int s = j & 1;
+                const uint32_t ph = uint32_t((j >> 1) & 1);
+                if (!mbar_wait_bounded(&k_full[s], ph)) { ok = false; break; }
+                fence_after_sync();
+                for (int ks = 0; ks < k_steps; ++ks) {
+                    const int kb = ks >> 2, kin = ks & 3;  // column block, 32-byte step inside it
+                    const uint64_t ad = smem_desc(q_addr + kb * kQSub + kin * 32, 0, 1024);
+                    const uint64_t bd = smem_desc(k_addr + s * kKVBytes + kb * kKVSub + kin * 32, 0, 1024);
+                    mma_ss(tmem_base + s * kBN, ad, bd, idesc_qk, ks > 0 ? 1u : 0u);
+                }
+                mma_commit(&k_empty[s]);
+                mma_commit(&s_full[s]);
+                if (j > 0 && !issue_pv(j - 1)) { ok = false; break; }
+                if (*abort_flag) { ok = false; break; }
+            }
+            if (ok && !issue_pv(n_tiles - 1)) ok = false;
+            if (!ok) { atomicExch(a.status, kDevWaitMma); *abort_flag = 1; }
+        }
+    } else {
+        // =============================== softmax + epilogue ===============================
+        const int quarter = warp & 3;            // TMEM lane quarter this warp may touch
+        const int r = quarter * 32 + lane;       // query row inside the tile
+        const uint32_t lane_base = uint32_t(quarter * 32) << 16;
+        const int pq = a.index_pos + t0 + r;     // absolute position of this query row
+        float m_ref = -INFINITY, l_sum = 0.f;
+        bool dead = false;
+        for (int j = 0; j < n_tiles; ++j) {
+            const int s = j & 1;
+            const uint32_t ph = uint32_t((j >> 1) & 1);
+            if (!dead && !__all_sync(0xffffffffu, mbar_wait_bounded(&s_full[s], ph))) {
+                atomicExch(a.status, kDevWaitFull); *abort_flag = 1; dead = true;
+            }
+            if (*abort_flag) dead = true;
+            dead = __any_sync(0xffffffffu, dead);
+            if (dead) break;
+            fence_after_sync();
+            uint32_t x0[32], x1[32];
+            const uint32_t s_addr = tmem_base + lane_base + s * kBN;
+            tmem_ld32(s_addr, x0);
+            tmem_ld32(s_addr + 32, x1);
+            tmem_wait_ld();
+            const bool diag = j * kBN + kBN - 1 > a.index_pos + t0;  // some row masks some key here
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 32; ++c) {
+                float v0 = __uint_as_float(x0[c]) * a.scale_log2;
+                float v1 = __uint_as_float(x1[c]) * a.scale_log2;
+                if (diag) {
+                    if (j * kBN + c > pq) v0 = -INFINITY;
+                    if (j * kBN + 32 + c > pq) v1 = -INFINITY;
+                }
+                x0[c] = __float_as_uint(v0);
+                x1[c] = __float_as_uint(v1);
+                mx = fmaxf(mx, fmaxf(v0, v1));
+            }
+            // lazy rescale: keep the old reference maximum unless this tile exceeds it by 2^8
+            float alpha = 1.f;
+            bool need = false;
+            if (j == 0) {
+                m_ref = mx;  // key 0 is visible to every row, so mx is finite
+            } else if (mx > m_ref + kRescaleThreshold) {
+                alpha = ex2(m_ref - mx);
+                m_ref = mx;
+                need = true;
+            }
+            if (__any_sync(0xffffffffu, need)) {
+                // the accumulator must be quiet: wait for O += P_{j-1} V_{j-1}
+                const int sp = (j - 1) & 1;
+                const uint32_t php = uint32_t(((j - 1) >> 1) & 1);
+                if (!__all_sync(0xffffffffu, mbar_wait_bounded(&pv_done[sp], php))) {
+                    atomicExch(a.status, kDevWaitMma); *abort_flag = 1; break;
+                }
+                fence_after_sync();
+                l_sum *= alpha;
+                for (int c0 = 0; c0 < n_pv; c0 += 32) {
+                    uint32_t o[32];
+                    tmem_ld32(tmem_o + lane_base + c0, o);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
+                    tmem_st32(tmem_o + lane_base + c0, o);
+                }
+                tmem_wait_st();
+            }
+            float psum = 0.f;
+#pragma unroll
+            for (int c = 0; c < 32; ++c) {
+                const float p0 = ex2(__uint_as_float(x0[c]) - m_ref);
+                const float p1 = ex2(__uint_as_float(x1[c]) - m_ref);
+                psum += p0 + p1;
+                x0[c] = to_tf32_rna(p0);
+                x1[c] = to_tf32_rna(p1);
+            }
+            l_sum += psum;
+            tmem_st32(s_addr, x0);
+            tmem_st32(s_addr + 32, x1);
+            tmem_wait_st();
+            fence_before_sync();
+            mbar_arrive(&p_full[s]);
+        }
+        // ---- epilogue: O / l -> global
+        const bool aborted = __any_sync(0xffffffffu, *abort_flag != 0);  // warp-uniform
+        if (!dead && !aborted) {
+            const int jl = n_tiles - 1;
+            if (__all_sync(0xffffffffu, mbar_wait_bounded(&pv_done[jl & 1], uint32_t((jl >> 1) & 1)))) {
+                fence_after_sync();
+                const float inv = 1.0f / l_sum;
+                const int t = t0 + r;
+                float* orow = a.out + size_t(h) * a.o_hs + size_t(t) * a.o_ts;
+                for (int c0 = 0; c0 < n_pv; c0 += 32) {
+                    uint32_t o[32];
+                    tmem_ld32(tmem_o + lane_base + c0, o);
+                    tmem_wait_ld();
+                    if (t < a.seq_len) {
+#pragma unroll
+                        for (int c = 0; c < 32; c += 4) {
+                            if (c0 + c + 3 < D) {
+                                float4 v4 = make_float4(__uint_as_float(o[c]) * inv, __uint_as_float(o[c + 1]) * inv,
+                                                        __uint_as_float(o[c + 2]) * inv, __uint_as_float(o[c + 3]) * inv);
+                                *reinterpret_cast<float4*>(orow + c0 + c) = v4;
+                            }
+                        }
+                    }
+                }
+            } else {
+                atomicExch(a.status, kDevWaitMma);
+                *abort_flag = 1;
+            }
+        }
+    }
+
+    fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        fence_after_sync();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                     "r"(uint32_t(kTmemCols))
+                     : "memory");
+    }
+}
+
+}  // namespace xn
