@@ -209,14 +209,15 @@ EncodeTiledFn encode_tiled_fn() {
 }
 
 // f32 tensor of `rank` dims (dims[0] innermost, contiguous), byte strides for dims 1..rank-1,
-// box of box[] elements, 128-byte swizzle, zero fill outside the tensor.
+// box of box[] elements, the given 128-byte swizzle flavour, zero fill outside the tensor.
 bool make_map_f32(CUtensorMap* map, const void* base, int rank, const cuuint64_t* dims,
-                  const cuuint64_t* strides_bytes, const cuuint32_t* box) {
+                  const cuuint64_t* strides_bytes, const cuuint32_t* box,
+                  CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return false;
     cuuint32_t estr[5] = {1, 1, 1, 1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, cuuint32_t(rank), const_cast<void*>(base), dims,
-              strides_bytes, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+              strides_bytes, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -560,6 +561,8 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         pa.head_dim = D;
         pa.scale_log2 = c->scale * 1.4426950408889634f;
         pa.status = c->status_d;
+        pa.dbg = nullptr;
+        pa.variant = 0;
         dim3 grid(unsigned((d.seq_len + pf::kBM - 1) / pf::kBM), unsigned(Hq));
         prefill_tf32_kernel<<<grid, pf::kThreads, pf::kSmemBytes, c->stream>>>(q_map, c->k_map,
                                                                               c->v_map, pa);
@@ -792,7 +795,9 @@ int32_t xn_ctx_create(const xn_ctx_desc* d, xn_ctx** out_ctx) {
             const cuuint64_t str[1] = {cuuint64_t(d->head_dim) * 4};
             const cuuint32_t box[2] = {32, cuuint32_t(pf::kBN)};
             c->tf32_ok = make_map_f32(&c->k_map, c->k_pool, 2, dims, str, box) &&
-                         make_map_f32(&c->v_map, c->v_pool, 2, dims, str, box);
+                         // V is consumed MN-major: 32-byte-chunk swizzle
+                         make_map_f32(&c->v_map, c->v_pool, 2, dims, str, box,
+                                      CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
             if (c->tf32_ok)
                 XN_CREATE_CUDA(cudaFuncSetAttribute(reinterpret_cast<const void*>(prefill_tf32_kernel),
                                                     cudaFuncAttributeMaxDynamicSharedMemorySize,

@@ -37,6 +37,10 @@ struct PrefillArgs {
     int head_dim;         // D (multiple of 4, 16..128)
     float scale_log2;     // (1/sqrt(D)) * log2(e)
     int* status;
+    int variant;          // diagnostics only: 0 = normal, see the probe for the others
+    float* dbg;           // diagnostics only (nullptr in normal use): block (0,0) dumps its first
+                          // raw score tile [128x64], first P tile [128x64], final raw O [128x128],
+                          // and the row sums [128]
 };
 
 namespace pf {
@@ -73,16 +77,21 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
         : "memory");
 }
 
-// Shared-memory matrix descriptor for tcgen05.mma, 128-byte swizzle.
+// Shared-memory matrix descriptor for tcgen05.mma.
 //   bits [0,14) start address >> 4, [16,30) leading byte offset >> 4, [32,46) stride byte
-//   offset >> 4, [46,48) descriptor version (1 on sm_100), [61,64) layout (2 = 128-byte swizzle).
-__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+//   offset >> 4, [46,48) descriptor version (1 on sm_100), [61,64) layout:
+//   2 = 128-byte swizzle of 16-byte chunks (K-major operands, TMA SWIZZLE_128B);
+//   1 = 128-byte swizzle of 32-byte chunks, the only layout the tensor cores accept for an
+//       MN-major TF32 operand (TMA SWIZZLE_128B_ATOM_32B; the pattern repeats every 4 rows).
+constexpr uint32_t kLayoutSw128 = 2, kLayoutSw128Base32 = 1;
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                              uint32_t layout = kLayoutSw128) {
     uint64_t d = 0;
     d |= uint64_t((saddr >> 4) & 0x3fff);
     d |= uint64_t((lbo_bytes >> 4) & 0x3fff) << 16;
     d |= uint64_t((sbo_bytes >> 4) & 0x3fff) << 32;
     d |= uint64_t(1) << 46;
-    d |= uint64_t(2) << 61;
+    d |= uint64_t(layout) << 61;
     return d;
 }
 
@@ -273,10 +282,24 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap q_map,
                 const uint32_t ph = uint32_t((j >> 1) & 1);
                 if (!mbar_wait_bounded(&p_full[s], ph) || !mbar_wait_bounded(&v_full[s], ph)) return false;
                 fence_after_sync();
+                if (a.variant == 1) {  // TMEM A with a K-major B (first 64 dims of the V page as K)
+                    const uint32_t idk = make_idesc(kBM, 64, 0);
+                    for (int ks = 0; ks < 8; ++ks) {
+                        const uint64_t bd = smem_desc(v_addr + s * kKVBytes + (ks >> 2) * kKVSub + (ks & 3) * 32, 0, 1024);
+                        mma_ts(tmem_o, tmem_base + s * kBN + ks * 8, bd, idk, (j > 0 || ks > 0) ? 1u : 0u);
+                    }
+                } else if (a.variant == 2) {  // shared-memory A (Q) with the MN-major V
+                    for (int ks = 0; ks < 8; ++ks) {
+                        const uint64_t ad = smem_desc(q_addr + (ks >> 2) * kQSub + (ks & 3) * 32, 0, 1024);
+                        const uint64_t bd = smem_desc(v_addr + s * kKVBytes + ks * 1024, kKVSub, 512, kLayoutSw128Base32);
+                        mma_ss(tmem_o, ad, bd, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+                    }
+                } else
                 for (int ks = 0; ks < kBN / 8; ++ks) {
-                    // V is [token][dim]: MN-major B; 8 tokens = 1024 B inside each column block,
-                    // column blocks kKVSub apart (leading offset), 8-token groups 1024 B apart
-                    const uint64_t bd = smem_desc(v_addr + s * kKVBytes + ks * 1024, kKVSub, 1024);
+                    // V is [token][dim]: MN-major B.  8 tokens = 1024 B inside each column block,
+                    // column blocks kKVSub apart (leading offset), 4-token swizzle groups 512 B
+                    // apart (stride offset)
+                    const uint64_t bd = smem_desc(v_addr + s * kKVBytes + ks * 1024, kKVSub, 512, kLayoutSw128Base32);
                     mma_ts(tmem_o, tmem_base + s * kBN + ks * 8, bd, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
                 }
                 mma_commit(&v_empty[s]);
@@ -325,6 +348,13 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap q_map,
             tmem_ld32(s_addr, x0);
             tmem_ld32(s_addr + 32, x1);
             tmem_wait_ld();
+            if (a.dbg && j == 0 && blockIdx.x == gridDim.x - 1 && blockIdx.y == 0) {
+#pragma unroll
+                for (int c = 0; c < 32; ++c) {
+                    a.dbg[r * 64 + c] = __uint_as_float(x0[c]);
+                    a.dbg[r * 64 + 32 + c] = __uint_as_float(x1[c]);
+                }
+            }
             const bool diag = j * kBN + kBN - 1 > a.index_pos + t0;  // some row masks some key here
             float mx = -INFINITY;
 #pragma unroll
@@ -378,6 +408,13 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap q_map,
                 x1[c] = to_tf32_rna(p1);
             }
             l_sum += psum;
+            if (a.dbg && j == 0 && blockIdx.x == gridDim.x - 1 && blockIdx.y == 0) {
+#pragma unroll
+                for (int c = 0; c < 32; ++c) {
+                    a.dbg[8192 + r * 64 + c] = __uint_as_float(x0[c]);
+                    a.dbg[8192 + r * 64 + 32 + c] = __uint_as_float(x1[c]);
+                }
+            }
             tmem_st32(s_addr, x0);
             tmem_st32(s_addr + 32, x1);
             tmem_wait_st();
@@ -397,6 +434,11 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap q_map,
                     uint32_t o[32];
                     tmem_ld32(tmem_o + lane_base + c0, o);
                     tmem_wait_ld();
+                    if (a.dbg && blockIdx.x == gridDim.x - 1 && blockIdx.y == 0) {
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) a.dbg[16384 + r * 128 + c0 + c] = __uint_as_float(o[c]);
+                        a.dbg[16384 + 16384 + r] = l_sum;
+                    }
                     if (t < a.seq_len) {
 #pragma unroll
                         for (int c = 0; c < 32; c += 4) {
