@@ -39,6 +39,7 @@ if ROOT not in sys.path:
 BASE_SEED = 299792458  # the reference's habitual seed (examples/batch_bench.rs:189)
 
 WORKLOADS = {
+    "c2": (1, 20, 5, 128, 1, 2048, 2048, "causal GQA prefill, BitNet-2B shape, 2048 tokens"),
     # name: (streams per GPU, Hq, Hkv, D, layers, L_lo, L_hi, description)
     "c3": (64, 20, 5, 128, 30, 128, 4096,
            "batched decode, BitNet-2B shape: 64 streams/GPU x 30 layers, KV len U[128,4096]"),
@@ -207,6 +208,124 @@ def run_reference_arm(args):
                          "sample": sample_txt},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "tokens_per_s": sample * args.steps / dt,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+# =================================================================================================
+# Prefill (tensor-core TF32 kernel)
+# =================================================================================================
+
+def prefill_flops(Hq, D, S, P=0):
+    """Algorithmic flops of causal attention: QK^T and PV over unmasked pairs only."""
+    return 4 * Hq * D * (S * P + S * (S + 1) // 2)
+
+
+def load_tf32_peak():
+    """TF32 dense peak taken as half of the measured bf16 cuBLAS burst figure (the two kinds
+    differ by exactly 2x in tensor-core rate); no TF32 GEMM was measured on this pool."""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["bf16_tflops"]) / 2.0, "measured bf16 burst / 2"
+    return 1590.0 / 2.0, "fallback bf16 / 2"
+
+
+def measure_prefill(xn, torch, tstream, device, S, Hq, Hkv, D, theta, steps, warmup, e2e=True):
+    """One causal prefill of S tokens (fused RoPE + append + attention) per step, one layer."""
+    cos, sin = xn.rope_tables(theta, D, S)
+    ctx = xn.Context(num_layers=1, num_heads=Hq, num_kv_heads=Hkv, head_dim=D,
+                     pool_pages=(S + 63) // 64 + 2, device=device, shuffle_seed=BASE_SEED + 2000,
+                     rope=(cos, sin), cuda_stream=tstream.cuda_stream)
+    st = ctx.new_stream(S)
+    gen = torch.Generator(device="cpu").manual_seed(BASE_SEED + 2000)
+    q_h = torch.randn(Hq, S, D, generator=gen).pin_memory()
+    k_h = torch.randn(Hkv, S, D, generator=gen).pin_memory()
+    v_h = torch.randn(Hkv, S, D, generator=gen).pin_memory()
+    o_h = torch.empty(Hq, S, D).pin_memory()
+    q_d, k_d, v_d = q_h.cuda(), k_h.cuda(), v_h.cuda()
+    o_d = torch.empty(Hq, S, D, device="cuda")
+    dev = ctx.make_batch([(st, 0, 0, S, q_d.data_ptr(), k_d.data_ptr(), v_d.data_ptr(), o_d.data_ptr())],
+                         xn.REQ_DEVICE_PTRS | xn.REQ_ROPE)
+    host = ctx.make_batch([(st, 0, 0, S, q_h.data_ptr(), k_h.data_ptr(), v_h.data_ptr(), o_h.data_ptr())],
+                          xn.REQ_ROPE)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")  # > L2 (126 MB)
+    for _ in range(max(warmup, 3)):
+        ctx.submit(dev)
+    torch.cuda.synchronize()
+    ctx.profile_enable(True)
+    ctx.profile_read()
+    total_ms = 0.0
+    for _ in range(steps):
+        flush.zero_()  # L2 flush between timed iterations
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(tstream)
+        ctx.submit(dev)
+        e1.record(tstream)
+        torch.cuda.synchronize()
+        total_ms += e0.elapsed_time(e1)
+    kern_ms, kern_n = ctx.profile_read("prefill")
+    ctx.profile_enable(False)
+    flops = prefill_flops(Hq, D, S)
+    res = {"seq_len": S, "flops": flops, "ms": total_ms / steps,
+           "tflops": flops / (total_ms / steps * 1e-3) / 1e12,
+           "kernel_ms": kern_ms / max(kern_n, 1),
+           "kernel_tflops": flops / (kern_ms / max(kern_n, 1) * 1e-3) / 1e12 if kern_n else None,
+           "launches_per_step": 2}
+    if e2e:
+        ctx.submit(host)
+        t0 = time.perf_counter()
+        n = max(1, min(steps, 5))
+        for _ in range(n):
+            ctx.submit(host)
+        dt = (time.perf_counter() - t0) / n
+        res["e2e_ms"] = dt * 1e3
+        res["e2e_tflops"] = flops / dt / 1e12
+        res["e2e_h2d_bytes"] = (Hq + 2 * Hkv) * S * D * 4
+        res["e2e_d2h_bytes"] = Hq * S * D * 4
+    ctx.close()
+    return res
+
+
+def run_prefill_arm(args):
+    """--workload c2: BASELINE config 2 (causal GQA prefill, BitNet-2B shape, 2048 tokens)."""
+    import torch
+
+    import xor_net_b200 as xn
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local_rank)
+    tstream = torch.cuda.current_stream()
+    S = args.seq or 2048
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    wall0 = time.time()
+    r = measure_prefill(xn, torch, tstream, local_rank, S, 20, 5, 128, 500000.0, args.steps, args.warmup)
+    wall1 = time.time()
+    clocks = sampler.stop(wall0, wall1) if sampler else None
+    if rank != 0:
+        return 0
+    peak, peak_kind = load_tf32_peak()
+    line = {
+        "metric": "prefill_attn_tflops", "value": r["tflops"] * world, "unit": "TFLOP/s",
+        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": r["ms"],
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "tf32",
+        "data": "synthetic",
+        "config": {"workload": f"c2: causal GQA prefill, BitNet-2B shape, {S} tokens, 20/5 heads, "
+                               "head_dim 128, fused RoPE theta 5e5 + append into 64-token pages",
+                   "l2": "256 MB buffer written between timed iterations (L2 flush)",
+                   "parallelism": f"{world} independent replica(s)"},
+        "e2e": {"value": r.get("e2e_tflops"), "unit": "TFLOP/s",
+                "h2d_bytes_per_step": r.get("e2e_h2d_bytes"), "d2h_bytes_per_step": r.get("e2e_d2h_bytes"),
+                "ms_per_step": r.get("e2e_ms")},
+        "gpu_launches": 2 * args.steps,
+        "roofline": {"bound": "tensor", "kernel": "prefill_tf32_kernel", "achieved": r["kernel_tflops"],
+                     "peak": peak, "unit": "TFLOP/s", "frac": r["kernel_tflops"] / peak,
+                     "peak_source": peak_kind, "traffic": None, "avg_launch_ms": r["kernel_ms"],
+                     "algorithmic_flops_per_launch": r["flops"]},
+        "clocks": clocks, "cpu_baseline": None,
     }
     print(json.dumps(line))
     return 0
@@ -409,9 +528,21 @@ def run_gpu_arm(args):
     elif rank == 0:
         line["cpu_baseline"] = None
 
+    ctx.close()
+    if rank == 0 and not args.no_prefill:
+        # the other half of the metric: causal prefill TFLOP/s on the tensor-core kernel
+        peak, peak_kind = load_tf32_peak()
+        pre = {}
+        for S in (2048, 8192):
+            r = measure_prefill(xn, torch, tstream, local_rank, S, 20, 5, 128, 500000.0,
+                                steps=5, warmup=3, e2e=(S == 2048))
+            r["frac_of_tf32_peak"] = r["kernel_tflops"] / peak
+            pre[f"S{S}"] = r
+        line["prefill"] = {"kernel": "prefill_tf32_kernel (tcgen05 TF32, TMEM accumulators)",
+                           "shape": "1 sequence, 20/5 heads, head_dim 128, fused RoPE + append",
+                           "tf32_peak_tflops": peak, "peak_source": peak_kind, **pre}
     if rank == 0:
         print(json.dumps(line))
-    ctx.close()
     if world > 1:
         dist.destroy_process_group()
     return 0
@@ -428,11 +559,15 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="time budget of the CPU sample")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the prefill summary")
+    ap.add_argument("--seq", type=int, default=0, help="prefill length for --workload c2")
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (profiling)")
     ap.add_argument("--streams", type=int, default=0, help="override streams per GPU (profiling)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)
+    if args.workload == "c2":
+        return run_prefill_arm(args)
     return run_gpu_arm(args)
 
 

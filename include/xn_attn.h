@@ -135,12 +135,14 @@ XN_API int32_t xn_stats_get(xn_ctx* ctx, xn_stats* out);
 /* Text of the most recent failure on this context (or of context creation when ctx is NULL). */
 XN_API const char* xn_last_error(xn_ctx* ctx);
 
-/* Device-side timing of the split-KV attention kernel: when enabled, every launch of that kernel
- * is bracketed by CUDA events on the context's stream.  xn_profile_read waits for the stream,
- * adds up the elapsed times recorded since the last read and returns them (milliseconds) with
- * the number of launches they cover. */
+/* Device-side timing of the two attention kernels: when enabled, every launch of the split-KV
+ * kernel and of the tensor-core prefill kernel is bracketed by CUDA events on the context's
+ * stream.  xn_profile_read waits for the stream, adds up the elapsed times recorded since the
+ * last read and returns them (milliseconds) with the number of launches they cover; any output
+ * pointer may be NULL. */
 XN_API int32_t xn_profile_enable(xn_ctx* ctx, int32_t on);
-XN_API int32_t xn_profile_read(xn_ctx* ctx, double* splitkv_ms, uint64_t* splitkv_launches);
+XN_API int32_t xn_profile_read(xn_ctx* ctx, double* splitkv_ms, uint64_t* splitkv_launches,
+                               double* prefill_ms, uint64_t* prefill_launches);
 
 /* ---- streams (one per reference `Cache`, models/llama/mod.rs:202-279) ------------------------ */
 

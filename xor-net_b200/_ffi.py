@@ -53,7 +53,8 @@ SIGNATURES = {
     "xn_stats_get": (C.c_int32, [C.c_void_p, C.POINTER(Stats)]),
     "xn_last_error": (C.c_char_p, [C.c_void_p]),
     "xn_profile_enable": (C.c_int32, [C.c_void_p, C.c_int32]),
-    "xn_profile_read": (C.c_int32, [C.c_void_p, C.POINTER(C.c_double), C.POINTER(C.c_uint64)]),
+    "xn_profile_read": (C.c_int32, [C.c_void_p, C.POINTER(C.c_double), C.POINTER(C.c_uint64),
+                                    C.POINTER(C.c_double), C.POINTER(C.c_uint64)]),
     "xn_stream_create": (C.c_int32, [C.c_void_p, C.c_int64, C.POINTER(C.c_void_p)]),
     "xn_stream_reset": (C.c_int32, [C.c_void_p, C.c_void_p]),
     "xn_stream_destroy": (C.c_int32, [C.c_void_p, C.c_void_p]),

@@ -166,11 +166,15 @@ class Context:
     def profile_enable(self, on: bool = True):
         self._check(self.lib.xn_profile_enable(self.handle, 1 if on else 0))
 
-    def profile_read(self):
-        """(milliseconds, launches) of the split-KV kernel since the last read."""
-        ms, n = C.c_double(), C.c_uint64()
-        self._check(self.lib.xn_profile_read(self.handle, C.byref(ms), C.byref(n)))
-        return ms.value, int(n.value)
+    def profile_read(self, which: str = "splitkv"):
+        """(milliseconds, launches) of the split-KV kernel (or "prefill") since the last read;
+        "both" returns the two pairs."""
+        ms, n, pms, pn = C.c_double(), C.c_uint64(), C.c_double(), C.c_uint64()
+        self._check(self.lib.xn_profile_read(self.handle, C.byref(ms), C.byref(n), C.byref(pms),
+                                             C.byref(pn)))
+        if which == "both":
+            return (ms.value, int(n.value)), (pms.value, int(pn.value))
+        return (pms.value, int(pn.value)) if which == "prefill" else (ms.value, int(n.value))
 
     # -- blocking single-stream calls (host arrays) ------------------------------------------
 

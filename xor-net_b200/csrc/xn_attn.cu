@@ -101,6 +101,7 @@ struct xn_ctx {
     // optional device timing of the split-KV kernel
     bool profile = false;
     std::vector<cudaEvent_t> prof_events;  // pairs (start, stop), reused
+    std::vector<int> prof_kind;            // per pair: 0 split-KV, 1 prefill
     size_t prof_used = 0;
 
     // combining of concurrent blocking callers
@@ -296,6 +297,26 @@ int32_t check_device_status(xn_ctx* c) {
         cudaMemsetAsync(c->status_d, 0, sizeof(int), c->stream);
         return fail(c, XN_ERR_DEVICE_WAIT, "a kernel gave up on a bounded wait (code %d)", code);
     }
+    return XN_OK;
+}
+
+int32_t profile_begin(xn_ctx* c, int kind) {
+    if (c->prof_used + 2 > c->prof_events.size()) {
+        cudaEvent_t a, b;
+        XN_CUDA(c, cudaEventCreate(&a));
+        XN_CUDA(c, cudaEventCreate(&b));
+        c->prof_events.push_back(a);
+        c->prof_events.push_back(b);
+        c->prof_kind.push_back(kind);
+    }
+    c->prof_kind[c->prof_used / 2] = kind;
+    XN_CUDA(c, cudaEventRecord(c->prof_events[c->prof_used], c->stream));
+    return XN_OK;
+}
+
+int32_t profile_end(xn_ctx* c) {
+    XN_CUDA(c, cudaEventRecord(c->prof_events[c->prof_used + 1], c->stream));
+    c->prof_used += 2;
     return XN_OK;
 }
 
@@ -510,24 +531,12 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
     }
     if (sp.ctas > 0) {
         SplitKernel k = pick_split(c->nv_class, c->gt);
-        if (c->profile) {
-            if (c->prof_used + 2 > c->prof_events.size()) {
-                cudaEvent_t a, b;
-                XN_CUDA(c, cudaEventCreate(&a));
-                XN_CUDA(c, cudaEventCreate(&b));
-                c->prof_events.push_back(a);
-                c->prof_events.push_back(b);
-            }
-            XN_CUDA(c, cudaEventRecord(c->prof_events[c->prof_used], c->stream));
-        }
+        if (c->profile && (rc = profile_begin(c, 0)) != XN_OK) return rc;
         k.fn<<<sp.ctas, k.threads, k.smem, c->stream>>>(reqs_d, units_d, items_d, cta_d, pages_d,
                                                         c->k_pool, c->v_pool, c->partials,
                                                         c->pool_pages, Hkv, D, nv, c->scale,
                                                         c->status_d);
-        if (c->profile) {
-            XN_CUDA(c, cudaEventRecord(c->prof_events[c->prof_used + 1], c->stream));
-            c->prof_used += 2;
-        }
+        if (c->profile && (rc = profile_end(c)) != XN_OK) return rc;
         c->stats.kernel_launches += 1;
         c->stats.decode_launches += 1;
         if (!merge_units.empty()) {
@@ -564,8 +573,10 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         pa.dbg = nullptr;
         pa.variant = 0;
         dim3 grid(unsigned((d.seq_len + pf::kBM - 1) / pf::kBM), unsigned(Hq));
+        if (c->profile && (rc = profile_begin(c, 1)) != XN_OK) return rc;
         prefill_tf32_kernel<<<grid, pf::kThreads, pf::kSmemBytes, c->stream>>>(q_map, c->k_map,
                                                                               c->v_map, pa);
+        if (c->profile && (rc = profile_end(c)) != XN_OK) return rc;
         c->stats.kernel_launches += 1;
         c->stats.prefill_launches += 1;
     }
@@ -888,19 +899,25 @@ int32_t xn_profile_enable(xn_ctx* c, int32_t on) {
     return XN_OK;
 }
 
-int32_t xn_profile_read(xn_ctx* c, double* splitkv_ms, uint64_t* splitkv_launches) {
+int32_t xn_profile_read(xn_ctx* c, double* splitkv_ms, uint64_t* splitkv_launches,
+                        double* prefill_ms, uint64_t* prefill_launches) {
     if (!ctx_ok(c)) return XN_ERR_HANDLE;
     std::lock_guard<std::mutex> g(c->mu);
     XN_CUDA(c, cudaSetDevice(c->device));
     XN_CUDA(c, cudaStreamSynchronize(c->stream));
-    double total = 0.0;
+    double total[2] = {0.0, 0.0};
+    uint64_t count[2] = {0, 0};
     for (size_t i = 0; i + 1 < c->prof_used; i += 2) {
         float ms = 0.f;
         XN_CUDA(c, cudaEventElapsedTime(&ms, c->prof_events[i], c->prof_events[i + 1]));
-        total += ms;
+        const int kind = c->prof_kind[i / 2] ? 1 : 0;
+        total[kind] += ms;
+        count[kind] += 1;
     }
-    if (splitkv_ms) *splitkv_ms = total;
-    if (splitkv_launches) *splitkv_launches = c->prof_used / 2;
+    if (splitkv_ms) *splitkv_ms = total[0];
+    if (splitkv_launches) *splitkv_launches = count[0];
+    if (prefill_ms) *prefill_ms = total[1];
+    if (prefill_launches) *prefill_launches = count[1];
     c->prof_used = 0;
     return XN_OK;
 }
