@@ -298,7 +298,8 @@ def run_prefill_arm(args):
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     torch.cuda.set_device(local_rank)
-    tstream = torch.cuda.current_stream()
+    tstream = torch.cuda.Stream(device=local_rank)
+    torch.cuda.set_stream(tstream)
     S = args.seq or 2048
     sampler = ClockSampler(local_rank) if rank == 0 else None
     wall0 = time.time()
@@ -361,7 +362,10 @@ def run_gpu_arm(args):
     # every rank owns its own streams (weak scaling: per-GPU work is fixed); no data-path collective
     lens = stream_lengths(n_streams, lo, hi, BASE_SEED + 3000 + 7919 * rank)
     pages_needed = int(sum((int(L) + 63) // 64 for L in lens))
-    tstream = torch.cuda.current_stream()
+    # a real (non-default) stream shared by torch and the library, so that CUDA events recorded
+    # here bracket the library's launches
+    tstream = torch.cuda.Stream(device=local_rank)
+    torch.cuda.set_stream(tstream)
     ctx = xn.Context(num_layers=layers, num_heads=Hq, num_kv_heads=Hkv, head_dim=D,
                      pool_pages=pages_needed + 8, device=local_rank,
                      shuffle_seed=BASE_SEED + rank, cuda_stream=tstream.cuda_stream)
