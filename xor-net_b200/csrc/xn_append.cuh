@@ -12,7 +12,8 @@ __device__ __forceinline__ size_t slot_offset(const int* pages, long long pool_p
            size_t(slot % kPageTokens) * dp;
 }
 
-// One warp per (new token, row), rows = [q heads (only when rotating)] + [k heads] + [v heads].
+// One half-warp per (new token, row), rows = [q heads (only when rotating)] + [k heads] +
+// [v heads].
 //   * K rows: the append loop of src/nn/fast_attention.rs:104-116 (slot = position % capacity),
 //     preceded, when the request asks for it, by the rotation of src/nn/fast_attention_simd.rs:
 //     380-387 with table row index_pos + t (src/tensor.rs:302-309).  The rotation is written
@@ -22,6 +23,54 @@ __device__ __forceinline__ size_t slot_offset(const int* pages, long long pool_p
 //   * Q rows: rotated into a dense [Hq, S, D] scratch read by the attention kernels.
 // When one call carries more new tokens than the ring holds, only the last writer of a slot
 // stores (the reference's sequential loop leaves exactly that value).
+// Rows move as float4 when head_dim is a multiple of 8 and both pointers are 16-byte aligned,
+// element by element otherwise.
+__device__ __forceinline__ void rotate4(float4& lo, float4& hi, const float4& c, const float4& s) {
+    const float4 a = lo, b = hi;
+    lo.x = __fsub_rn(__fmul_rn(a.x, c.x), __fmul_rn(b.x, s.x));
+    lo.y = __fsub_rn(__fmul_rn(a.y, c.y), __fmul_rn(b.y, s.y));
+    lo.z = __fsub_rn(__fmul_rn(a.z, c.z), __fmul_rn(b.z, s.z));
+    lo.w = __fsub_rn(__fmul_rn(a.w, c.w), __fmul_rn(b.w, s.w));
+    hi.x = __fadd_rn(__fmul_rn(a.x, s.x), __fmul_rn(b.x, c.x));
+    hi.y = __fadd_rn(__fmul_rn(a.y, s.y), __fmul_rn(b.y, c.y));
+    hi.z = __fadd_rn(__fmul_rn(a.z, s.z), __fmul_rn(b.z, c.z));
+    hi.w = __fadd_rn(__fmul_rn(a.w, s.w), __fmul_rn(b.w, c.w));
+}
+
+__device__ __forceinline__ void row_rotate(const float* __restrict__ src, float* __restrict__ dst,
+                                           const float* __restrict__ c, const float* __restrict__ s,
+                                           int head_dim, int hl, bool vec) {
+    const int half = head_dim / 2;
+    if (vec) {
+        for (int i = hl * 4; i < half; i += 64) {
+            float4 lo = *reinterpret_cast<const float4*>(src + i);
+            float4 hi = *reinterpret_cast<const float4*>(src + i + half);
+            const float4 cv = *reinterpret_cast<const float4*>(c + i);
+            const float4 sv = *reinterpret_cast<const float4*>(s + i);
+            rotate4(lo, hi, cv, sv);
+            *reinterpret_cast<float4*>(dst + i) = lo;
+            *reinterpret_cast<float4*>(dst + i + half) = hi;
+        }
+    } else {
+        for (int i = hl; i < half; i += 16) {
+            const float x1 = src[i], x2 = src[i + half], cv = c[i], sv = s[i];
+            dst[i] = __fsub_rn(__fmul_rn(x1, cv), __fmul_rn(x2, sv));
+            dst[i + half] = __fadd_rn(__fmul_rn(x1, sv), __fmul_rn(x2, cv));
+        }
+        if ((head_dim & 1) && hl == 0) dst[head_dim - 1] = src[head_dim - 1];
+    }
+}
+
+__device__ __forceinline__ void row_copy(const float* __restrict__ src, float* __restrict__ dst,
+                                         int head_dim, int hl, bool vec) {
+    if (vec) {
+        for (int i = hl * 4; i < head_dim; i += 64)
+            *reinterpret_cast<float4*>(dst + i) = *reinterpret_cast<const float4*>(src + i);
+    } else {
+        for (int i = hl; i < head_dim; i += 16) dst[i] = src[i];
+    }
+}
+
 __global__ void __launch_bounds__(256)
 rope_append_kernel(const ReqDev* __restrict__ reqs, const int* __restrict__ page_ids,
                    float* __restrict__ k_pool, float* __restrict__ v_pool,
@@ -31,51 +80,45 @@ rope_append_kernel(const ReqDev* __restrict__ reqs, const int* __restrict__ page
     const bool rope = r.flags & 1u;
     const int rows_per_tok = (rope ? num_heads : 0) + 2 * num_kv_heads;
     const long long n_rows = (long long)r.seq_len * rows_per_tok;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int hl = threadIdx.x & 15;         // lane inside the half-warp
+    const int hw = threadIdx.x >> 4;         // half-warp inside the block (16 per block)
     const int half = head_dim / 2;
     const int dp = nv * 4;
     const int* pages = page_ids + r.page_off;
-    for (long long row = (long long)blockIdx.x * 8 + warp; row < n_rows;
-         row += (long long)gridDim.x * 8) {
+    const bool dim_vec = (head_dim % 8) == 0;
+    for (long long row = (long long)blockIdx.x * 16 + hw; row < n_rows;
+         row += (long long)gridDim.x * 16) {
         const int t = int(row / rows_per_tok);
         int rr = int(row % rows_per_tok);
         const int pos = r.index_pos + t;
         const float* c = cos_t + size_t(pos) * half;
         const float* s = sin_t + size_t(pos) * half;
+        const float* src;
+        float* dst;
+        bool rotate = false;
         if (rope && rr < num_heads) {
             // query row -> rotation scratch (ReqDev::q points at it)
-            const float* src = r.q_in + size_t(rr) * r.qi_hs + size_t(t) * r.qi_ts;
-            float* dst = const_cast<float*>(r.q) + size_t(rr) * r.q_hs + size_t(t) * r.q_ts;
-            for (int i = lane; i < half; i += 32) {
-                const float x1 = src[i], x2 = src[i + half], cv = c[i], sv = s[i];
-                dst[i] = __fsub_rn(__fmul_rn(x1, cv), __fmul_rn(x2, sv));
-                dst[i + half] = __fadd_rn(__fmul_rn(x1, sv), __fmul_rn(x2, cv));
-            }
-            if ((head_dim & 1) && lane == 0) dst[head_dim - 1] = src[head_dim - 1];
-            continue;
-        }
-        if (rope) rr -= num_heads;
-        if ((long long)t + r.cap < (long long)r.seq_len) continue;  // overwritten later in this call
-        const int slot = pos % r.cap;
-        if (rr < num_kv_heads) {
-            const float* src = r.k + size_t(rr) * r.kv_hs + size_t(t) * r.kv_ts;
-            float* dst = k_pool + slot_offset(pages, pool_pages, r.layer, num_kv_heads, rr, slot, dp);
-            if (rope) {
-                for (int i = lane; i < half; i += 32) {
-                    const float x1 = src[i], x2 = src[i + half], cv = c[i], sv = s[i];
-                    dst[i] = __fsub_rn(__fmul_rn(x1, cv), __fmul_rn(x2, sv));
-                    dst[i + half] = __fadd_rn(__fmul_rn(x1, sv), __fmul_rn(x2, cv));
-                }
-                if ((head_dim & 1) && lane == 0) dst[head_dim - 1] = src[head_dim - 1];
-            } else {
-                for (int i = lane; i < head_dim; i += 32) dst[i] = src[i];
-            }
+            src = r.q_in + size_t(rr) * r.qi_hs + size_t(t) * r.qi_ts;
+            dst = const_cast<float*>(r.q) + size_t(rr) * r.q_hs + size_t(t) * r.q_ts;
+            rotate = true;
         } else {
-            rr -= num_kv_heads;
-            const float* src = r.v + size_t(rr) * r.kv_hs + size_t(t) * r.kv_ts;
-            float* dst = v_pool + slot_offset(pages, pool_pages, r.layer, num_kv_heads, rr, slot, dp);
-            for (int i = lane; i < head_dim; i += 32) dst[i] = src[i];
+            if (rope) rr -= num_heads;
+            if ((long long)t + r.cap < (long long)r.seq_len) continue;  // overwritten later in this call
+            const int slot = pos % r.cap;
+            if (rr < num_kv_heads) {
+                src = r.k + size_t(rr) * r.kv_hs + size_t(t) * r.kv_ts;
+                dst = k_pool + slot_offset(pages, pool_pages, r.layer, num_kv_heads, rr, slot, dp);
+                rotate = rope;
+            } else {
+                rr -= num_kv_heads;
+                src = r.v + size_t(rr) * r.kv_hs + size_t(t) * r.kv_ts;
+                dst = v_pool + slot_offset(pages, pool_pages, r.layer, num_kv_heads, rr, slot, dp);
+            }
         }
+        const bool vec = dim_vec &&
+                         (((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0);
+        if (rotate) row_rotate(src, dst, c, s, head_dim, hl, vec);
+        else row_copy(src, dst, head_dim, hl, vec);
     }
 }
 

@@ -523,7 +523,7 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         c->stats.kernel_launches += 1;
     }
     if (max_rows > 0) {
-        dim3 grid(unsigned(std::min<long long>((max_rows + 7) / 8, 2048)), unsigned(n));
+        dim3 grid(unsigned(std::min<long long>((max_rows + 15) / 16, 4096)), unsigned(n));
         rope_append_kernel<<<grid, 256, 0, c->stream>>>(reqs_d, pages_d, c->k_pool, c->v_pool,
                                                         c->cos_d, c->sin_d, c->pool_pages, Hq, Hkv,
                                                         D, nv);

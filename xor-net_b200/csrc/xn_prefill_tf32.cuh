@@ -9,10 +9,11 @@
 // One thread block = one (query head, 128-row query tile).  Key/value tiles are the cache's
 // 64-token pages.  Roles (192 threads):
 //   warp 0      TMA producer: tensor-map loads of the Q tile (once) and of K / V pages into
-//               128-byte-swizzled shared memory, two stages each, mbarrier byte counting;
-//   warp 1      MMA issuer (one lane): S_j = Q K_j^T into one of two 64-column TMEM buffers,
-//               then O += P_j V_j with P read from TMEM (it overwrites S_j in place) and V taken
-//               MN-major straight from its [token][dim] page; tcgen05.commit signals mbarriers;
+//               128-byte-swizzled shared memory (3 K stages, 2 V stages), mbarrier byte counting;
+//   warp 1      MMA issuer (one lane): S_j = Q K_j^T into one of four 64-column TMEM buffers,
+//               issued two tiles ahead of O += P_j V_j, which reads P from TMEM (it overwrites
+//               S_j in place) and V MN-major straight from its [token][dim] page;
+//               tcgen05.commit signals the mbarriers;
 //   warps 2..5  softmax: thread r owns query row r: tcgen05.ld of its S row, scale, causal mask,
 //               running max / sum, exp2, P written back with tcgen05.st.  The accumulator is
 //               rescaled lazily: only when a row's maximum grows by more than 2^8.
@@ -52,11 +53,15 @@ constexpr int kQSub = kBM * 128;  // bytes of one Q column block  [128 rows x 12
 constexpr int kKVSub = kBN * 128; // bytes of one K/V column block [64 rows x 128 B]
 constexpr int kQBytes = kKB * kQSub;     // 64 KB
 constexpr int kKVBytes = kKB * kKVSub;   // 32 KB
-constexpr int kStages = 2;
-constexpr int kSmemData = kQBytes + 2 * kStages * kKVBytes;  // 192 KB
+constexpr int kKStages = 3;       // K pages in flight
+constexpr int kVStages = 2;       // V pages in flight
+constexpr int kSBufs = 4;         // score / probability buffers in tensor memory
+constexpr int kLookahead = 2;     // S_j is issued this many tiles before O += P V of tile j
+constexpr int kSmemData = kQBytes + (kKStages + kVStages) * kKVBytes;  // 224 KB
 constexpr int kSmemBytes = kSmemData + 1024 /* alignment slack */ + 256 /* barriers */;
 constexpr int kThreads = 192;
-constexpr int kTmemCols = 256;    // S0 [0,64) S1 [64,128) O [128,256)
+constexpr int kTmemCols = 512;    // S buffers [0,256), O [256,384)
+constexpr int kTmemO = kSBufs * kBN;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int x, int y, int z,
@@ -189,18 +194,19 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap q_map,
         (reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
     unsigned char* q_s = smem;
     unsigned char* k_s = smem + kQBytes;
-    unsigned char* v_s = k_s + kStages * kKVBytes;
+    unsigned char* v_s = k_s + kKStages * kKVBytes;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kSmemData);
     uint64_t* q_full = bars + 0;
-    uint64_t* k_full = bars + 1;    // [2]
-    uint64_t* k_empty = bars + 3;   // [2]
-    uint64_t* v_full = bars + 5;    // [2]
-    uint64_t* v_empty = bars + 7;   // [2]
-    uint64_t* s_full = bars + 9;    // [2]
-    uint64_t* p_full = bars + 11;   // [2]
-    uint64_t* pv_done = bars + 13;  // [2]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 17);
+    uint64_t* k_full = bars + 1;                 // [kKStages]
+    uint64_t* k_empty = k_full + kKStages;       // [kKStages]
+    uint64_t* v_full = k_empty + kKStages;       // [kVStages]
+    uint64_t* v_empty = v_full + kVStages;       // [kVStages]
+    uint64_t* s_full = v_empty + kVStages;       // [kSBufs]
+    uint64_t* p_full = s_full + kSBufs;          // [kSBufs]
+    uint64_t* pv_done = p_full + kSBufs;         // [kSBufs]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + kSBufs);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);
+    static_assert((1 + 2 * kKStages + 2 * kVStages + 3 * kSBufs) * 8 + 16 <= 256, "barrier area");
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n_qtiles = (a.seq_len + kBM - 1) / kBM;
@@ -217,11 +223,15 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap q_map,
 
     if (tid == 0) {
         mbar_init(q_full, 1);
-        for (int s = 0; s < 2; ++s) {
+        for (int s = 0; s < kKStages; ++s) {
             mbar_init(&k_full[s], 1);
             mbar_init(&k_empty[s], 1);
+        }
+        for (int s = 0; s < kVStages; ++s) {
             mbar_init(&v_full[s], 1);
             mbar_init(&v_empty[s], 1);
+        }
+        for (int s = 0; s < kSBufs; ++s) {
             mbar_init(&s_full[s], 1);
             mbar_init(&p_full[s], 128);
             mbar_init(&pv_done[s], 1);
@@ -240,7 +250,7 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap q_map,
     __syncthreads();
     fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_o = tmem_base + 128;
+    const uint32_t tmem_o = tmem_base + kTmemO;
 
     if (warp == 0) {
         // =============================== TMA producer ===============================
@@ -249,22 +259,21 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap q_map,
             for (int kb = 0; kb < n_kb; ++kb)
                 tma_load_3d(q_s + kb * kQSub, &q_map, kb * 32, t0, h, q_full);
             for (int j = 0; j < n_tiles; ++j) {
-                const int s = j & 1;
-                const uint32_t ph = uint32_t((j >> 1) & 1);
+                const int ks_ = j % kKStages, vs_ = j % kVStages;
                 const int page = a.pages[j];
                 const long long row = ((a.layer_page_base + page) * a.num_kv_heads + h_kv) * kBN;
-                if (j >= kStages && !mbar_wait_bounded(&k_empty[s], ph ^ 1)) {
+                if (j >= kKStages && !mbar_wait_bounded(&k_empty[ks_], uint32_t((j / kKStages - 1) & 1))) {
                     atomicExch(a.status, kDevWaitEmpty); *abort_flag = 1; break;
                 }
-                mbar_arrive_expect_tx(&k_full[s], uint32_t(n_kb) * kKVSub);
+                mbar_arrive_expect_tx(&k_full[ks_], uint32_t(n_kb) * kKVSub);
                 for (int kb = 0; kb < n_kb; ++kb)
-                    tma_load_2d(k_s + s * kKVBytes + kb * kKVSub, &k_map, kb * 32, int(row), &k_full[s]);
-                if (j >= kStages && !mbar_wait_bounded(&v_empty[s], ph ^ 1)) {
+                    tma_load_2d(k_s + ks_ * kKVBytes + kb * kKVSub, &k_map, kb * 32, int(row), &k_full[ks_]);
+                if (j >= kVStages && !mbar_wait_bounded(&v_empty[vs_], uint32_t((j / kVStages - 1) & 1))) {
                     atomicExch(a.status, kDevWaitEmpty); *abort_flag = 1; break;
                 }
-                mbar_arrive_expect_tx(&v_full[s], uint32_t(n_kb) * kKVSub);
+                mbar_arrive_expect_tx(&v_full[vs_], uint32_t(n_kb) * kKVSub);
                 for (int kb = 0; kb < n_kb; ++kb)
-                    tma_load_2d(v_s + s * kKVBytes + kb * kKVSub, &v_map, kb * 32, int(row), &v_full[s]);
+                    tma_load_2d(v_s + vs_ * kKVBytes + kb * kKVSub, &v_map, kb * 32, int(row), &v_full[vs_]);
                 if (*abort_flag) break;
             }
         }
@@ -278,15 +287,16 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap q_map,
             if (!ok) { atomicExch(a.status, kDevWaitFull); *abort_flag = 1; }
             // issues O += P_j V_j
             auto issue_pv = [&](int j) -> bool {
-                const int s = j & 1;
-                const uint32_t ph = uint32_t((j >> 1) & 1);
-                if (!mbar_wait_bounded(&p_full[s], ph) || !mbar_wait_bounded(&v_full[s], ph)) return false;
+                const int sb = j % kSBufs, s = j % kVStages;
+                if (!mbar_wait_bounded(&p_full[sb], uint32_t((j / kSBufs) & 1)) ||
+                    !mbar_wait_bounded(&v_full[s], uint32_t((j / kVStages) & 1)))
+                    return false;
                 fence_after_sync();
                 if (a.variant == 1) {  // TMEM A with a K-major B (first 64 dims of the V page as K)
                     const uint32_t idk = make_idesc(kBM, 64, 0);
                     for (int ks = 0; ks < 8; ++ks) {
                         const uint64_t bd = smem_desc(v_addr + s * kKVBytes + (ks >> 2) * kKVSub + (ks & 3) * 32, 0, 1024);
-                        mma_ts(tmem_o, tmem_base + s * kBN + ks * 8, bd, idk, (j > 0 || ks > 0) ? 1u : 0u);
+                        mma_ts(tmem_o, tmem_base + sb * kBN + ks * 8, bd, idk, (j > 0 || ks > 0) ? 1u : 0u);
                     }
                 } else if (a.variant == 2) {  // shared-memory A (Q) with the MN-major V
                     for (int ks = 0; ks < 8; ++ks) {
@@ -300,29 +310,29 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap q_map,
                     // column blocks kKVSub apart (leading offset), 4-token swizzle groups 512 B
                     // apart (stride offset)
                     const uint64_t bd = smem_desc(v_addr + s * kKVBytes + ks * 1024, kKVSub, 512, kLayoutSw128Base32);
-                    mma_ts(tmem_o, tmem_base + s * kBN + ks * 8, bd, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+                    mma_ts(tmem_o, tmem_base + sb * kBN + ks * 8, bd, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
                 }
                 mma_commit(&v_empty[s]);
-                mma_commit(&pv_done[s]);
+                mma_commit(&pv_done[sb]);
                 return true;
             };
             for (int j = 0; j < n_tiles && ok; ++j) {
-                const int s = j & 1;
-                const uint32_t ph = uint32_t((j >> 1) & 1);
-                if (!mbar_wait_bounded(&k_full[s], ph)) { ok = false; break; }
+                const int s = j % kKStages, sb = j % kSBufs;
+                if (!mbar_wait_bounded(&k_full[s], uint32_t((j / kKStages) & 1))) { ok = false; break; }
                 fence_after_sync();
                 for (int ks = 0; ks < k_steps; ++ks) {
                     const int kb = ks >> 2, kin = ks & 3;  // column block, 32-byte step inside it
                     const uint64_t ad = smem_desc(q_addr + kb * kQSub + kin * 32, 0, 1024);
                     const uint64_t bd = smem_desc(k_addr + s * kKVBytes + kb * kKVSub + kin * 32, 0, 1024);
-                    mma_ss(tmem_base + s * kBN, ad, bd, idesc_qk, ks > 0 ? 1u : 0u);
+                    mma_ss(tmem_base + sb * kBN, ad, bd, idesc_qk, ks > 0 ? 1u : 0u);
                 }
                 mma_commit(&k_empty[s]);
-                mma_commit(&s_full[s]);
-                if (j > 0 && !issue_pv(j - 1)) { ok = false; break; }
+                mma_commit(&s_full[sb]);
+                if (j >= kLookahead && !issue_pv(j - kLookahead)) { ok = false; break; }
                 if (*abort_flag) { ok = false; break; }
             }
-            if (ok && !issue_pv(n_tiles - 1)) ok = false;
+            for (int j = max(0, n_tiles - kLookahead); j < n_tiles && ok; ++j)
+                if (!issue_pv(j)) ok = false;
             if (!ok) { atomicExch(a.status, kDevWaitMma); *abort_flag = 1; }
         }
     } else {
@@ -334,8 +344,8 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap q_map,
         float m_ref = -INFINITY, l_sum = 0.f;
         bool dead = false;
         for (int j = 0; j < n_tiles; ++j) {
-            const int s = j & 1;
-            const uint32_t ph = uint32_t((j >> 1) & 1);
+            const int s = j % kSBufs;
+            const uint32_t ph = uint32_t((j / kSBufs) & 1);
             if (!dead && !__all_sync(0xffffffffu, mbar_wait_bounded(&s_full[s], ph))) {
                 atomicExch(a.status, kDevWaitFull); *abort_flag = 1; dead = true;
             }
@@ -356,19 +366,20 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap q_map,
                 }
             }
             const bool diag = j * kBN + kBN - 1 > a.index_pos + t0;  // some row masks some key here
+            // raw scores stay unscaled: max commutes with the positive scale, and the scale is
+            // folded into the exponent's fused multiply-add below
             float mx = -INFINITY;
+            if (diag) {
 #pragma unroll
-            for (int c = 0; c < 32; ++c) {
-                float v0 = __uint_as_float(x0[c]) * a.scale_log2;
-                float v1 = __uint_as_float(x1[c]) * a.scale_log2;
-                if (diag) {
-                    if (j * kBN + c > pq) v0 = -INFINITY;
-                    if (j * kBN + 32 + c > pq) v1 = -INFINITY;
+                for (int c = 0; c < 32; ++c) {
+                    if (j * kBN + c > pq) x0[c] = 0xff800000u;       // -inf
+                    if (j * kBN + 32 + c > pq) x1[c] = 0xff800000u;
                 }
-                x0[c] = __float_as_uint(v0);
-                x1[c] = __float_as_uint(v1);
-                mx = fmaxf(mx, fmaxf(v0, v1));
             }
+#pragma unroll
+            for (int c = 0; c < 32; ++c)
+                mx = fmaxf(mx, fmaxf(__uint_as_float(x0[c]), __uint_as_float(x1[c])));
+            mx *= a.scale_log2;
             // lazy rescale: keep the old reference maximum unless this tile exceeds it by 2^8
             float alpha = 1.f;
             bool need = false;
@@ -381,8 +392,8 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap q_map,
             }
             if (__any_sync(0xffffffffu, need)) {
                 // the accumulator must be quiet: wait for O += P_{j-1} V_{j-1}
-                const int sp = (j - 1) & 1;
-                const uint32_t php = uint32_t(((j - 1) >> 1) & 1);
+                const int sp = (j - 1) % kSBufs;
+                const uint32_t php = uint32_t(((j - 1) / kSBufs) & 1);
                 if (!__all_sync(0xffffffffu, mbar_wait_bounded(&pv_done[sp], php))) {
                     atomicExch(a.status, kDevWaitMma); *abort_flag = 1; break;
                 }
@@ -398,16 +409,19 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap q_map,
                 }
                 tmem_wait_st();
             }
-            float psum = 0.f;
+            float psum0 = 0.f, psum1 = 0.f;
+            const float neg_m = -m_ref;
 #pragma unroll
             for (int c = 0; c < 32; ++c) {
-                const float p0 = ex2(__uint_as_float(x0[c]) - m_ref);
-                const float p1 = ex2(__uint_as_float(x1[c]) - m_ref);
-                psum += p0 + p1;
-                x0[c] = to_tf32_rna(p0);
-                x1[c] = to_tf32_rna(p1);
+                const float p0 = ex2(fmaf(__uint_as_float(x0[c]), a.scale_log2, neg_m));
+                const float p1 = ex2(fmaf(__uint_as_float(x1[c]), a.scale_log2, neg_m));
+                psum0 += p0;
+                psum1 += p1;
+                // round to TF32 (the tensor core drops the low 13 mantissa bits): add half an ulp
+                x0[c] = __float_as_uint(p0) + 0x1000u;
+                x1[c] = __float_as_uint(p1) + 0x1000u;
             }
-            l_sum += psum;
+            l_sum += psum0 + psum1;
             if (a.dbg && j == 0 && blockIdx.x == gridDim.x - 1 && blockIdx.y == 0) {
 #pragma unroll
                 for (int c = 0; c < 32; ++c) {
@@ -425,7 +439,7 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap q_map,
         const bool aborted = __any_sync(0xffffffffu, *abort_flag != 0);  // warp-uniform
         if (!dead && !aborted) {
             const int jl = n_tiles - 1;
-            if (__all_sync(0xffffffffu, mbar_wait_bounded(&pv_done[jl & 1], uint32_t((jl >> 1) & 1)))) {
+            if (__all_sync(0xffffffffu, mbar_wait_bounded(&pv_done[jl % kSBufs], uint32_t((jl / kSBufs) & 1)))) {
                 fence_after_sync();
                 const float inv = 1.0f / l_sum;
                 const int t = t0 + r;
