@@ -454,16 +454,9 @@ def run_gpu_arm(args):
     # the host-side staging is part of the call: the wall clock is the honest end-to-end time
     e2e_ms = max(e2e_ms, e2e_wall_ms)
 
-    if world > 1:
-        t = torch.tensor([ms, e2e_ms, kern_ms / max(kern_n, 1)], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, e2e_ms, kern_avg_ms = (float(x) for x in t.tolist())
-        tot = torch.tensor([bytes_per_step], device="cuda", dtype=torch.float64)
-        dist.all_reduce(tot, op=dist.ReduceOp.SUM)
-        total_bytes_per_step = float(tot.item())
-    else:
-        kern_avg_ms = kern_ms / max(kern_n, 1)
-        total_bytes_per_step = float(bytes_per_step)
+    # job-wide figures: slowest rank's time, all ranks' bytes (no-op in a single process)
+    (ms, e2e_ms, kern_avg_ms), (total_bytes_per_step,) = xn.sharding.aggregate(
+        [ms, e2e_ms, kern_ms / max(kern_n, 1)], [float(bytes_per_step)], device="cuda")
 
     # outputs of both paths agree (same kernels, same inputs)
     same = bool(torch.equal(o_d.cpu(), o_h)) if e2e_steps > 0 else None

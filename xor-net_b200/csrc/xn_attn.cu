@@ -550,18 +550,14 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         const ReqDev& d = rd[i];
         if ((reinterpret_cast<uintptr_t>(d.q) & 15) || (reinterpret_cast<uintptr_t>(d.out) & 15))
             return fail(c, XN_ERR_ARG, "tensor-core prefill needs 16-byte aligned q and out");
-        CUtensorMap q_map;
-        const cuuint64_t qdims[3] = {cuuint64_t(D), cuuint64_t(d.seq_len), cuuint64_t(Hq)};
-        const cuuint64_t qstr[2] = {cuuint64_t(d.q_ts) * 4, cuuint64_t(d.q_hs) * 4};
-        const cuuint32_t qbox[3] = {32, cuuint32_t(pf::kBM), 1};
-        if (!make_map_f32(&q_map, d.q, 3, qdims, qstr, qbox))
-            return fail(c, XN_ERR_CUDA, "cuTensorMapEncodeTiled failed for the query tensor");
         PrefillArgs pa;
+        pa.q = d.q;
+        pa.q_hs = d.q_hs;
+        pa.q_ts = d.q_ts;
         pa.pages = pages_d + d.page_off;
         pa.out = d.out;
         pa.o_hs = d.o_hs;
         pa.o_ts = d.o_ts;
-        pa.kv_row_base_mul = (long long)Hkv * kPageTokens;
         pa.layer_page_base = (long long)d.layer * c->pool_pages;
         pa.num_kv_heads = Hkv;
         pa.group = c->group;
@@ -570,12 +566,9 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         pa.head_dim = D;
         pa.scale_log2 = c->scale * 1.4426950408889634f;
         pa.status = c->status_d;
-        pa.dbg = nullptr;
-        pa.variant = 0;
         dim3 grid(unsigned((d.seq_len + pf::kBM - 1) / pf::kBM), unsigned(Hq));
         if (c->profile && (rc = profile_begin(c, 1)) != XN_OK) return rc;
-        prefill_tf32_kernel<<<grid, pf::kThreads, pf::kSmemBytes, c->stream>>>(q_map, c->k_map,
-                                                                              c->v_map, pa);
+        prefill_tf32_kernel<<<grid, pf::kThreads, pf::kSmemBytes, c->stream>>>(c->k_map, c->v_map, pa);
         if (c->profile && (rc = profile_end(c)) != XN_OK) return rc;
         c->stats.kernel_launches += 1;
         c->stats.prefill_launches += 1;

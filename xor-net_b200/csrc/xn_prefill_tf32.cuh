@@ -7,16 +7,21 @@
 // the diagonal tile is masked element-wise".
 //
 // One thread block = one (query head, 128-row query tile).  Key/value tiles are the cache's
-// 64-token pages.  Roles (192 threads):
-//   warp 0      TMA producer: tensor-map loads of the Q tile (once) and of K / V pages into
-//               128-byte-swizzled shared memory (3 K stages, 2 V stages), mbarrier byte counting;
-//   warp 1      MMA issuer (one lane): S_j = Q K_j^T into one of four 64-column TMEM buffers,
-//               issued two tiles ahead of O += P_j V_j, which reads P from TMEM (it overwrites
-//               S_j in place) and V MN-major straight from its [token][dim] page;
-//               tcgen05.commit signals the mbarriers;
-//   warps 2..5  softmax: thread r owns query row r: tcgen05.ld of its S row, scale, causal mask,
-//               running max / sum, exp2, P written back with tcgen05.st.  The accumulator is
-//               rescaled lazily: only when a row's maximum grows by more than 2^8.
+// 64-token pages.  Tensor memory (512 columns): Q [0,128) | four S/P buffers [128,384) |
+// O [384,512).  Roles (192 threads):
+//   warp 0      TMA producer: tensor-map loads of K pages (4 stages, 128-byte swizzle) and V
+//               pages (3 stages, 128-byte swizzle of 32-byte chunks) with mbarrier byte counts;
+//               K runs two tiles ahead of V, the order in which the MMA warp consumes them;
+//   warp 1      MMA issuer (one lane): S_j = Q K_j^T with Q read from tensor memory, issued two
+//               tiles ahead of O += P_j V_j, which reads P from tensor memory (P overwrites S_j
+//               in place) and V MN-major straight from its [token][dim] page; tcgen05.commit
+//               signals the mbarriers;
+//   warps 2..5  thread r owns query row r.  Prologue: the row of Q goes global -> registers ->
+//               tensor memory (rounded to TF32).  Per tile: tcgen05.ld of the S row (the next
+//               tile's load is issued before this tile's arithmetic), causal mask, running
+//               max / sum, exp2 with the softmax scale folded into one FMA, P written back with
+//               tcgen05.st and published one tile later.  The accumulator is rescaled lazily:
+//               only when a row's maximum grows by more than 2^8.  Epilogue: O / l to global.
 // Every wait is bounded; on expiry the kernel records a status code, drains and returns.
 #pragma once
 #include <cuda.h>
@@ -26,10 +31,11 @@
 namespace xn {
 
 struct PrefillArgs {
+    const float* q;       // rotated queries (device)
+    long long q_hs, q_ts; // query head / token strides in floats
     const int* pages;     // page ids of the stream (device)
     float* out;           // output base
     long long o_hs, o_ts; // output head / token strides in floats
-    long long kv_row_base_mul;  // rows per page slot block: num_kv_heads * 64
     long long layer_page_base;  // layer * pool_pages
     int num_kv_heads;
     int group;            // query heads per KV head
@@ -38,10 +44,9 @@ struct PrefillArgs {
     int head_dim;         // D (multiple of 4, 16..128)
     float scale_log2;     // (1/sqrt(D)) * log2(e)
     int* status;
-    int variant;          // diagnostics only: 0 = normal, see the probe for the others
-    float* dbg;           // diagnostics only (nullptr in normal use): block (0,0) dumps its first
-                          // raw score tile [128x64], first P tile [128x64], final raw O [128x128],
-                          // and the row sums [128]
+#ifdef XN_PF_TIMING
+    long long* timing;    // instrumentation build only: cycle counters of one softmax thread
+#endif
 };
 
 namespace pf {
@@ -49,29 +54,20 @@ namespace pf {
 constexpr int kBM = 128;          // query rows per block
 constexpr int kBN = 64;           // keys per tile (= page)
 constexpr int kKB = 4;            // 32-float (128-byte) column blocks per row, at most
-constexpr int kQSub = kBM * 128;  // bytes of one Q column block  [128 rows x 128 B]
 constexpr int kKVSub = kBN * 128; // bytes of one K/V column block [64 rows x 128 B]
-constexpr int kQBytes = kKB * kQSub;     // 64 KB
 constexpr int kKVBytes = kKB * kKVSub;   // 32 KB
-constexpr int kKStages = 3;       // K pages in flight
-constexpr int kVStages = 2;       // V pages in flight
+constexpr int kKStages = 4;       // K pages in flight
+constexpr int kVStages = 3;       // V pages in flight
 constexpr int kSBufs = 4;         // score / probability buffers in tensor memory
 constexpr int kLookahead = 2;     // S_j is issued this many tiles before O += P V of tile j
-constexpr int kSmemData = kQBytes + (kKStages + kVStages) * kKVBytes;  // 224 KB
+constexpr int kSmemData = (kKStages + kVStages) * kKVBytes;  // 224 KB
 constexpr int kSmemBytes = kSmemData + 1024 /* alignment slack */ + 256 /* barriers */;
 constexpr int kThreads = 192;
-constexpr int kTmemCols = 512;    // S buffers [0,256), O [256,384)
-constexpr int kTmemO = kSBufs * kBN;
+constexpr int kTmemCols = 512;
+constexpr int kTmemQ = 0;         // 128 columns
+constexpr int kTmemS = 128;       // kSBufs x 64 columns
+constexpr int kTmemO = 384;       // 128 columns
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
-
-__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int x, int y, int z,
-                                            uint64_t* bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
-        " [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(smem_u32(dst)),
-        "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
-        : "memory");
-}
 
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y,
                                             uint64_t* bar) {
@@ -90,7 +86,7 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
 //       MN-major TF32 operand (TMA SWIZZLE_128B_ATOM_32B; the pattern repeats every 4 rows).
 constexpr uint32_t kLayoutSw128 = 2, kLayoutSw128Base32 = 1;
 __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes,
-                                              uint32_t layout = kLayoutSw128) {
+                                              uint32_t layout) {
     uint64_t d = 0;
     d |= uint64_t((saddr >> 4) & 0x3fff);
     d |= uint64_t((lbo_bytes >> 4) & 0x3fff) << 16;
@@ -108,15 +104,7 @@ __host__ __device__ constexpr uint32_t make_idesc(int m, int n, int b_mn_major) 
            (uint32_t(n >> 3) << 17) | (uint32_t(m >> 4) << 24);
 }
 
-__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                       uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-
+// D[tmem] (+)= A[tmem] * B[smem]
 __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
                                        uint32_t idesc, uint32_t accumulate) {
     asm volatile(
@@ -167,6 +155,23 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
 }
 
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// Same wait, written so that the compiler sees the 64 registers of an earlier, still in-flight
+// pair of loads as produced here: nothing may read or copy them before this point.
+__device__ __forceinline__ void tmem_wait_ld_into(uint32_t (&x)[32], uint32_t (&y)[32]) {
+    asm volatile(
+        "tcgen05.wait::ld.sync.aligned;"
+        : "+r"(x[0]), "+r"(x[1]), "+r"(x[2]), "+r"(x[3]), "+r"(x[4]), "+r"(x[5]), "+r"(x[6]), "+r"(x[7]),
+          "+r"(x[8]), "+r"(x[9]), "+r"(x[10]), "+r"(x[11]), "+r"(x[12]), "+r"(x[13]), "+r"(x[14]),
+          "+r"(x[15]), "+r"(x[16]), "+r"(x[17]), "+r"(x[18]), "+r"(x[19]), "+r"(x[20]), "+r"(x[21]),
+          "+r"(x[22]), "+r"(x[23]), "+r"(x[24]), "+r"(x[25]), "+r"(x[26]), "+r"(x[27]), "+r"(x[28]),
+          "+r"(x[29]), "+r"(x[30]), "+r"(x[31]), "+r"(y[0]), "+r"(y[1]), "+r"(y[2]), "+r"(y[3]),
+          "+r"(y[4]), "+r"(y[5]), "+r"(y[6]), "+r"(y[7]), "+r"(y[8]), "+r"(y[9]), "+r"(y[10]),
+          "+r"(y[11]), "+r"(y[12]), "+r"(y[13]), "+r"(y[14]), "+r"(y[15]), "+r"(y[16]), "+r"(y[17]),
+          "+r"(y[18]), "+r"(y[19]), "+r"(y[20]), "+r"(y[21]), "+r"(y[22]), "+r"(y[23]), "+r"(y[24]),
+          "+r"(y[25]), "+r"(y[26]), "+r"(y[27]), "+r"(y[28]), "+r"(y[29]), "+r"(y[30]), "+r"(y[31])
+        :
+        : "memory");
+}
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 __device__ __forceinline__ float ex2(float x) {
@@ -175,28 +180,30 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
-__device__ __forceinline__ uint32_t to_tf32_rna(float x) {
-    uint32_t y;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(y) : "f"(x));
-    return y;
-}
+// Round an f32 to the nearest TF32 (ties away from zero): the tensor core drops the low 13
+// mantissa bits, so adding half an ulp of the kept part to the bit pattern rounds the magnitude.
+__device__ __forceinline__ uint32_t round_tf32(uint32_t bits) { return bits + 0x1000u; }
+
+// State one softmax thread carries across tiles.
+struct RowState {
+    float m_ref;   // reference maximum (scaled, log2 domain) the stored probabilities use
+    float l_sum;   // running sum of probabilities
+};
 
 }  // namespace pf
 
 __global__ void __launch_bounds__(pf::kThreads, 1)
-prefill_tf32_kernel(const __grid_constant__ CUtensorMap q_map,
-                    const __grid_constant__ CUtensorMap k_map,
+prefill_tf32_kernel(const __grid_constant__ CUtensorMap k_map,
                     const __grid_constant__ CUtensorMap v_map, const PrefillArgs a) {
     using namespace pf;
     extern __shared__ unsigned char smem_dyn[];
     // 128-byte swizzled tiles want 1024-byte alignment
     unsigned char* smem = reinterpret_cast<unsigned char*>(
         (reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
-    unsigned char* q_s = smem;
-    unsigned char* k_s = smem + kQBytes;
+    unsigned char* k_s = smem;
     unsigned char* v_s = k_s + kKStages * kKVBytes;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kSmemData);
-    uint64_t* q_full = bars + 0;
+    uint64_t* q_ready = bars + 0;
     uint64_t* k_full = bars + 1;                 // [kKStages]
     uint64_t* k_empty = k_full + kKStages;       // [kKStages]
     uint64_t* v_full = k_empty + kKStages;       // [kVStages]
@@ -222,7 +229,7 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap q_map,
     const int n_pv = (D + 15) / 16 * 16;   // N of the PV MMA
 
     if (tid == 0) {
-        mbar_init(q_full, 1);
+        mbar_init(q_ready, 128);
         for (int s = 0; s < kKStages; ++s) {
             mbar_init(&k_full[s], 1);
             mbar_init(&k_empty[s], 1);
@@ -250,30 +257,35 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap q_map,
     __syncthreads();
     fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_q = tmem_base + kTmemQ;
+    const uint32_t tmem_s = tmem_base + kTmemS;
     const uint32_t tmem_o = tmem_base + kTmemO;
 
     if (warp == 0) {
         // =============================== TMA producer ===============================
         if (lane == 0) {
-            mbar_arrive_expect_tx(q_full, uint32_t(n_kb) * kQSub);
-            for (int kb = 0; kb < n_kb; ++kb)
-                tma_load_3d(q_s + kb * kQSub, &q_map, kb * 32, t0, h, q_full);
-            for (int j = 0; j < n_tiles; ++j) {
-                const int ks_ = j % kKStages, vs_ = j % kVStages;
-                const int page = a.pages[j];
-                const long long row = ((a.layer_page_base + page) * a.num_kv_heads + h_kv) * kBN;
-                if (j >= kKStages && !mbar_wait_bounded(&k_empty[ks_], uint32_t((j / kKStages - 1) & 1))) {
-                    atomicExch(a.status, kDevWaitEmpty); *abort_flag = 1; break;
+            for (int t = 0; t < n_tiles + kLookahead; ++t) {
+                if (t < n_tiles) {
+                    const int st = t % kKStages;
+                    const long long row = ((a.layer_page_base + a.pages[t]) * a.num_kv_heads + h_kv) * kBN;
+                    if (t >= kKStages && !mbar_wait_bounded(&k_empty[st], uint32_t((t / kKStages - 1) & 1))) {
+                        atomicExch(a.status, kDevWaitEmpty); *abort_flag = 1; break;
+                    }
+                    mbar_arrive_expect_tx(&k_full[st], uint32_t(n_kb) * kKVSub);
+                    for (int kb = 0; kb < n_kb; ++kb)
+                        tma_load_2d(k_s + st * kKVBytes + kb * kKVSub, &k_map, kb * 32, int(row), &k_full[st]);
                 }
-                mbar_arrive_expect_tx(&k_full[ks_], uint32_t(n_kb) * kKVSub);
-                for (int kb = 0; kb < n_kb; ++kb)
-                    tma_load_2d(k_s + ks_ * kKVBytes + kb * kKVSub, &k_map, kb * 32, int(row), &k_full[ks_]);
-                if (j >= kVStages && !mbar_wait_bounded(&v_empty[vs_], uint32_t((j / kVStages - 1) & 1))) {
-                    atomicExch(a.status, kDevWaitEmpty); *abort_flag = 1; break;
+                const int jv = t - kLookahead;
+                if (jv >= 0) {
+                    const int st = jv % kVStages;
+                    const long long row = ((a.layer_page_base + a.pages[jv]) * a.num_kv_heads + h_kv) * kBN;
+                    if (jv >= kVStages && !mbar_wait_bounded(&v_empty[st], uint32_t((jv / kVStages - 1) & 1))) {
+                        atomicExch(a.status, kDevWaitEmpty); *abort_flag = 1; break;
+                    }
+                    mbar_arrive_expect_tx(&v_full[st], uint32_t(n_kb) * kKVSub);
+                    for (int kb = 0; kb < n_kb; ++kb)
+                        tma_load_2d(v_s + st * kKVBytes + kb * kKVSub, &v_map, kb * 32, int(row), &v_full[st]);
                 }
-                mbar_arrive_expect_tx(&v_full[vs_], uint32_t(n_kb) * kKVSub);
-                for (int kb = 0; kb < n_kb; ++kb)
-                    tma_load_2d(v_s + vs_ * kKVBytes + kb * kKVSub, &v_map, kb * 32, int(row), &v_full[vs_]);
                 if (*abort_flag) break;
             }
         }
@@ -282,9 +294,10 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap q_map,
         if (lane == 0) {
             const uint32_t idesc_qk = make_idesc(kBM, kBN, 0);
             const uint32_t idesc_pv = make_idesc(kBM, n_pv, 1);
-            const uint32_t q_addr = smem_u32(q_s), k_addr = smem_u32(k_s), v_addr = smem_u32(v_s);
-            bool ok = mbar_wait_bounded(q_full, 0);
+            const uint32_t k_addr = smem_u32(k_s), v_addr = smem_u32(v_s);
+            bool ok = mbar_wait_bounded(q_ready, 0);
             if (!ok) { atomicExch(a.status, kDevWaitFull); *abort_flag = 1; }
+            fence_after_sync();
             // issues O += P_j V_j
             auto issue_pv = [&](int j) -> bool {
                 const int sb = j % kSBufs, s = j % kVStages;
@@ -292,25 +305,13 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap q_map,
                     !mbar_wait_bounded(&v_full[s], uint32_t((j / kVStages) & 1)))
                     return false;
                 fence_after_sync();
-                if (a.variant == 1) {  // TMEM A with a K-major B (first 64 dims of the V page as K)
-                    const uint32_t idk = make_idesc(kBM, 64, 0);
-                    for (int ks = 0; ks < 8; ++ks) {
-                        const uint64_t bd = smem_desc(v_addr + s * kKVBytes + (ks >> 2) * kKVSub + (ks & 3) * 32, 0, 1024);
-                        mma_ts(tmem_o, tmem_base + sb * kBN + ks * 8, bd, idk, (j > 0 || ks > 0) ? 1u : 0u);
-                    }
-                } else if (a.variant == 2) {  // shared-memory A (Q) with the MN-major V
-                    for (int ks = 0; ks < 8; ++ks) {
-                        const uint64_t ad = smem_desc(q_addr + (ks >> 2) * kQSub + (ks & 3) * 32, 0, 1024);
-                        const uint64_t bd = smem_desc(v_addr + s * kKVBytes + ks * 1024, kKVSub, 512, kLayoutSw128Base32);
-                        mma_ss(tmem_o, ad, bd, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
-                    }
-                } else
                 for (int ks = 0; ks < kBN / 8; ++ks) {
                     // V is [token][dim]: MN-major B.  8 tokens = 1024 B inside each column block,
                     // column blocks kKVSub apart (leading offset), 4-token swizzle groups 512 B
                     // apart (stride offset)
-                    const uint64_t bd = smem_desc(v_addr + s * kKVBytes + ks * 1024, kKVSub, 512, kLayoutSw128Base32);
-                    mma_ts(tmem_o, tmem_base + sb * kBN + ks * 8, bd, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+                    const uint64_t bd = smem_desc(v_addr + s * kKVBytes + ks * 1024, kKVSub, 512,
+                                                  kLayoutSw128Base32);
+                    mma_ts(tmem_o, tmem_s + sb * kBN + ks * 8, bd, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
                 }
                 mma_commit(&v_empty[s]);
                 mma_commit(&pv_done[sb]);
@@ -322,9 +323,9 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap q_map,
                 fence_after_sync();
                 for (int ks = 0; ks < k_steps; ++ks) {
                     const int kb = ks >> 2, kin = ks & 3;  // column block, 32-byte step inside it
-                    const uint64_t ad = smem_desc(q_addr + kb * kQSub + kin * 32, 0, 1024);
-                    const uint64_t bd = smem_desc(k_addr + s * kKVBytes + kb * kKVSub + kin * 32, 0, 1024);
-                    mma_ss(tmem_base + sb * kBN, ad, bd, idesc_qk, ks > 0 ? 1u : 0u);
+                    const uint64_t bd = smem_desc(k_addr + s * kKVBytes + kb * kKVSub + kin * 32, 0, 1024,
+                                                  kLayoutSw128);
+                    mma_ts(tmem_s + sb * kBN, tmem_q + ks * 8, bd, idesc_qk, ks > 0 ? 1u : 0u);
                 }
                 mma_commit(&k_empty[s]);
                 mma_commit(&s_full[sb]);
@@ -337,68 +338,102 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap q_map,
         }
     } else {
         // =============================== softmax + epilogue ===============================
+        constexpr unsigned kFull = 0xffffffffu;
         const int quarter = warp & 3;            // TMEM lane quarter this warp may touch
         const int r = quarter * 32 + lane;       // query row inside the tile
         const uint32_t lane_base = uint32_t(quarter * 32) << 16;
-        const int pq = a.index_pos + t0 + r;     // absolute position of this query row
-        float m_ref = -INFINITY, l_sum = 0.f;
-        bool dead = false;
-        for (int j = 0; j < n_tiles; ++j) {
-            const int s = j % kSBufs;
-            const uint32_t ph = uint32_t((j / kSBufs) & 1);
-            if (!dead && !__all_sync(0xffffffffu, mbar_wait_bounded(&s_full[s], ph))) {
-                atomicExch(a.status, kDevWaitFull); *abort_flag = 1; dead = true;
+        const int t = t0 + r;                    // query row inside the request
+        const int pq = a.index_pos + t;          // its absolute position
+
+        // ---- prologue: this thread's row of Q -> tensor memory (rounded to TF32) ----
+        {
+            const float* qrow = a.q + size_t(h) * a.q_hs + size_t(t) * a.q_ts;
+            const bool valid = t < a.seq_len;
+            for (int c0 = 0; c0 < k_steps * 8; c0 += 32) {
+                uint32_t qv[32];
+#pragma unroll
+                for (int c = 0; c < 32; c += 4) {
+                    float4 v4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (valid && c0 + c < D) v4 = *reinterpret_cast<const float4*>(qrow + c0 + c);
+                    qv[c] = round_tf32(__float_as_uint(v4.x));
+                    qv[c + 1] = round_tf32(__float_as_uint(v4.y));
+                    qv[c + 2] = round_tf32(__float_as_uint(v4.z));
+                    qv[c + 3] = round_tf32(__float_as_uint(v4.w));
+                }
+                tmem_st32(tmem_q + lane_base + c0, qv);
             }
-            if (*abort_flag) dead = true;
-            dead = __any_sync(0xffffffffu, dead);
-            if (dead) break;
+            tmem_wait_st();
+            fence_before_sync();
+            mbar_arrive(q_ready);
+        }
+
+        RowState st{-INFINITY, 0.f};
+        bool dead = false;
+        int pending = -1;  // tile whose P is stored but not yet published
+#ifdef XN_PF_TIMING
+        long long tm_pub = 0;
+#endif
+
+        // waits for S_j and starts loading this thread's row of it
+        auto fetch = [&](int j, uint32_t (&x0)[32], uint32_t (&x1)[32]) -> bool {
+            const int sb = j % kSBufs;
+            if (!__all_sync(kFull, mbar_wait_bounded(&s_full[sb], uint32_t((j / kSBufs) & 1)))) return false;
             fence_after_sync();
-            uint32_t x0[32], x1[32];
-            const uint32_t s_addr = tmem_base + lane_base + s * kBN;
+            const uint32_t s_addr = tmem_s + lane_base + sb * kBN;
             tmem_ld32(s_addr, x0);
             tmem_ld32(s_addr + 32, x1);
-            tmem_wait_ld();
-            if (a.dbg && j == 0 && blockIdx.x == gridDim.x - 1 && blockIdx.y == 0) {
-#pragma unroll
-                for (int c = 0; c < 32; ++c) {
-                    a.dbg[r * 64 + c] = __uint_as_float(x0[c]);
-                    a.dbg[r * 64 + 32 + c] = __uint_as_float(x1[c]);
-                }
+            return true;
+        };
+        // makes the P of tile `pending` visible to the MMA warp
+        auto publish = [&]() {
+            if (pending >= 0) {
+#ifdef XN_PF_TIMING
+                long long t_p = clock64();
+#endif
+                tmem_wait_st();
+                fence_before_sync();
+                mbar_arrive(&p_full[pending % kSBufs]);
+                pending = -1;
+#ifdef XN_PF_TIMING
+                tm_pub += clock64() - t_p;
+#endif
             }
+        };
+        // mask, max, (rare) accumulator rescale, probabilities; stores P_j
+        auto process = [&](int j, uint32_t (&x0)[32], uint32_t (&x1)[32]) -> bool {
             const bool diag = j * kBN + kBN - 1 > a.index_pos + t0;  // some row masks some key here
-            // raw scores stay unscaled: max commutes with the positive scale, and the scale is
-            // folded into the exponent's fused multiply-add below
-            float mx = -INFINITY;
             if (diag) {
 #pragma unroll
                 for (int c = 0; c < 32; ++c) {
-                    if (j * kBN + c > pq) x0[c] = 0xff800000u;       // -inf
+                    if (j * kBN + c > pq) x0[c] = 0xff800000u;  // -inf
                     if (j * kBN + 32 + c > pq) x1[c] = 0xff800000u;
                 }
             }
+            // raw scores stay unscaled: max commutes with the positive scale, and the scale is
+            // folded into the exponent's fused multiply-add below
+            float mx = -INFINITY;
 #pragma unroll
             for (int c = 0; c < 32; ++c)
                 mx = fmaxf(mx, fmaxf(__uint_as_float(x0[c]), __uint_as_float(x1[c])));
             mx *= a.scale_log2;
-            // lazy rescale: keep the old reference maximum unless this tile exceeds it by 2^8
             float alpha = 1.f;
             bool need = false;
             if (j == 0) {
-                m_ref = mx;  // key 0 is visible to every row, so mx is finite
-            } else if (mx > m_ref + kRescaleThreshold) {
-                alpha = ex2(m_ref - mx);
-                m_ref = mx;
+                st.m_ref = mx;  // key 0 is visible to every row, so mx is finite
+            } else if (mx > st.m_ref + kRescaleThreshold) {
+                alpha = ex2(st.m_ref - mx);
+                st.m_ref = mx;
                 need = true;
             }
-            if (__any_sync(0xffffffffu, need)) {
-                // the accumulator must be quiet: wait for O += P_{j-1} V_{j-1}
+            if (__any_sync(kFull, need)) {
+                // the accumulator must be quiet: publish what is pending, then wait for
+                // O += P_{j-1} V_{j-1}
+                publish();
                 const int sp = (j - 1) % kSBufs;
-                const uint32_t php = uint32_t(((j - 1) / kSBufs) & 1);
-                if (!__all_sync(0xffffffffu, mbar_wait_bounded(&pv_done[sp], php))) {
-                    atomicExch(a.status, kDevWaitMma); *abort_flag = 1; break;
-                }
+                if (!__all_sync(kFull, mbar_wait_bounded(&pv_done[sp], uint32_t(((j - 1) / kSBufs) & 1))))
+                    return false;
                 fence_after_sync();
-                l_sum *= alpha;
+                st.l_sum *= alpha;
                 for (int c0 = 0; c0 < n_pv; c0 += 32) {
                     uint32_t o[32];
                     tmem_ld32(tmem_o + lane_base + c0, o);
@@ -410,49 +445,71 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap q_map,
                 tmem_wait_st();
             }
             float psum0 = 0.f, psum1 = 0.f;
-            const float neg_m = -m_ref;
+            const float neg_m = -st.m_ref;
 #pragma unroll
             for (int c = 0; c < 32; ++c) {
                 const float p0 = ex2(fmaf(__uint_as_float(x0[c]), a.scale_log2, neg_m));
                 const float p1 = ex2(fmaf(__uint_as_float(x1[c]), a.scale_log2, neg_m));
                 psum0 += p0;
                 psum1 += p1;
-                // round to TF32 (the tensor core drops the low 13 mantissa bits): add half an ulp
-                x0[c] = __float_as_uint(p0) + 0x1000u;
-                x1[c] = __float_as_uint(p1) + 0x1000u;
+                x0[c] = round_tf32(__float_as_uint(p0));
+                x1[c] = round_tf32(__float_as_uint(p1));
             }
-            l_sum += psum0 + psum1;
-            if (a.dbg && j == 0 && blockIdx.x == gridDim.x - 1 && blockIdx.y == 0) {
-#pragma unroll
-                for (int c = 0; c < 32; ++c) {
-                    a.dbg[8192 + r * 64 + c] = __uint_as_float(x0[c]);
-                    a.dbg[8192 + r * 64 + 32 + c] = __uint_as_float(x1[c]);
-                }
-            }
+            st.l_sum += psum0 + psum1;
+            publish();  // the previous tile's P: its stores have long completed
+            const uint32_t s_addr = tmem_s + lane_base + (j % kSBufs) * kBN;
             tmem_st32(s_addr, x0);
             tmem_st32(s_addr + 32, x1);
-            tmem_wait_st();
-            fence_before_sync();
-            mbar_arrive(&p_full[s]);
+            pending = j;
+            return true;
+        };
+
+#ifdef XN_PF_TIMING
+        long long tm_wait_s = 0, tm_wait_ld = 0, tm_proc = 0, tm_total = clock64();
+#define PF_T0 long long t_0 = clock64();
+#define PF_ACC(var) var += clock64() - t_0;
+#else
+#define PF_T0
+#define PF_ACC(var)
+#endif
+        uint32_t a0[32], a1[32], b0[32], b1[32];
+        if (!fetch(0, a0, a1)) dead = true;
+        for (int j = 0; j < n_tiles && !dead; j += 2) {
+            // tile j lives in (a0,a1); tile j+1 is fetched into (b0,b1) while j is processed
+            { PF_T0 tmem_wait_ld_into(a0, a1); PF_ACC(tm_wait_ld) }
+            { PF_T0 if (j + 1 < n_tiles && !fetch(j + 1, b0, b1)) { dead = true; break; } PF_ACC(tm_wait_s) }
+            { PF_T0 if (!process(j, a0, a1)) { dead = true; break; } PF_ACC(tm_proc) }
+            if (j + 1 >= n_tiles) break;
+            { PF_T0 tmem_wait_ld_into(b0, b1); PF_ACC(tm_wait_ld) }
+            { PF_T0 if (j + 2 < n_tiles && !fetch(j + 2, a0, a1)) { dead = true; break; } PF_ACC(tm_wait_s) }
+            { PF_T0 if (!process(j + 1, b0, b1)) { dead = true; break; } PF_ACC(tm_proc) }
+            if (__any_sync(kFull, *abort_flag != 0)) { dead = true; break; }
         }
+        if (dead) {
+            atomicExch(a.status, kDevWaitFull);
+            *abort_flag = 1;
+        } else {
+            publish();
+        }
+#ifdef XN_PF_TIMING
+        if (a.timing && blockIdx.x == 0 && blockIdx.y == 0 && tid == 64) {
+            a.timing[0] = n_tiles; a.timing[1] = clock64() - tm_total; a.timing[2] = tm_wait_s;
+            a.timing[3] = tm_wait_ld; a.timing[4] = tm_proc; a.timing[5] = tm_pub;
+        }
+#endif
+
         // ---- epilogue: O / l -> global
-        const bool aborted = __any_sync(0xffffffffu, *abort_flag != 0);  // warp-uniform
+        const bool aborted = __any_sync(kFull, *abort_flag != 0);  // warp-uniform
         if (!dead && !aborted) {
             const int jl = n_tiles - 1;
-            if (__all_sync(0xffffffffu, mbar_wait_bounded(&pv_done[jl % kSBufs], uint32_t((jl / kSBufs) & 1)))) {
+            if (__all_sync(kFull, mbar_wait_bounded(&pv_done[jl % kSBufs], uint32_t((jl / kSBufs) & 1)))) {
                 fence_after_sync();
-                const float inv = 1.0f / l_sum;
-                const int t = t0 + r;
+                const float inv = 1.0f / st.l_sum;
                 float* orow = a.out + size_t(h) * a.o_hs + size_t(t) * a.o_ts;
                 for (int c0 = 0; c0 < n_pv; c0 += 32) {
                     uint32_t o[32];
                     tmem_ld32(tmem_o + lane_base + c0, o);
                     tmem_wait_ld();
-                    if (a.dbg && blockIdx.x == gridDim.x - 1 && blockIdx.y == 0) {
-#pragma unroll
-                        for (int c = 0; c < 32; ++c) a.dbg[16384 + r * 128 + c0 + c] = __uint_as_float(o[c]);
-                        a.dbg[16384 + 16384 + r] = l_sum;
-                    }
                     if (t < a.seq_len) {
 #pragma unroll
                         for (int c = 0; c < 32; c += 4) {
