@@ -38,7 +38,8 @@ struct PlanSlot {
     unsigned char* host = nullptr;
     unsigned char* dev = nullptr;
     size_t cap = 0;
-    cudaEvent_t ev = nullptr;
+    cudaEvent_t ev = nullptr;     // recorded after the last launch that reads the slot
+    cudaEvent_t up_ev = nullptr;  // recorded after the plan upload on the copy stream
     bool used = false;
 };
 
@@ -72,9 +73,13 @@ struct xn_ctx {
     int prefill_mode = 0;
     int batch_window_us = 0;
     int sm_count = 0;
-    int decode_ctas = 0;
+    int decode_ctas = 0;     // thread blocks of the split-KV launch (one per SM)
+    int decode_chunks = 0;   // chunks the tile list is cut into (several per block)
+    int* sync_d = nullptr;   // chunk counter, done counter, per-unit arrival counters
+    size_t sync_cap = 0;     // ints
     cudaStream_t stream = nullptr;
     bool own_stream = false;
+    cudaStream_t copy_stream = nullptr;  // plan uploads run here, off the launch stream's critical path
     float* k_pool = nullptr;
     float* v_pool = nullptr;
     float* cos_d = nullptr;
@@ -144,9 +149,9 @@ size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 // ---- kernel dispatch table ---------------------------------------------------------------
 
-using SplitFn = void (*)(const ReqDev*, const UnitDev*, const ItemDev*, const int*, const int*,
-                         const float*, const float*, float*, long long, int, int, int, float, int*);
-using MergeFn = void (*)(const ReqDev*, const UnitDev*, const int*, int, const float*, int, int);
+using SplitFn = void (*)(const ReqDev*, const UnitDev*, const ItemDev*, const int*, int, const int*,
+                         const float*, const float*, float*, int*, long long, int, int, int, float,
+                         int*);
 
 struct SplitKernel {
     SplitFn fn;
@@ -174,12 +179,6 @@ SplitKernel pick_split(int nv_class, int gt) {
         case 32: return pick_gt<32>(gt);
         default: return pick_gt<64>(gt);
     }
-}
-
-MergeFn pick_merge(int gt) {
-    if (gt == 4) return attn_merge_kernel<4>;
-    if (gt == 2) return attn_merge_kernel<2>;
-    return attn_merge_kernel<1>;
 }
 
 int nv_class_for(int nv) {
@@ -267,6 +266,7 @@ int32_t acquire_slot(xn_ctx* c, size_t need_bytes, PlanSlot** out) {
         s.cap = want;
     }
     if (!s.ev) XN_CUDA(c, cudaEventCreateWithFlags(&s.ev, cudaEventDisableTiming));
+    if (!s.up_ev) XN_CUDA(c, cudaEventCreateWithFlags(&s.up_ev, cudaEventDisableTiming));
     *out = &s;
     return XN_OK;
 }
@@ -295,6 +295,8 @@ int32_t check_device_status(xn_ctx* c) {
         *c->status_h = kDevOk;
         c->stats.device_wait_errors += 1;
         cudaMemsetAsync(c->status_d, 0, sizeof(int), c->stream);
+        // a kernel that gave up may have left its arrival counters half-way
+        cudaMemsetAsync(c->sync_d, 0, c->sync_cap * sizeof(int), c->stream);
         return fail(c, XN_ERR_DEVICE_WAIT, "a kernel gave up on a bounded wait (code %d)", code);
     }
     return XN_OK;
@@ -460,20 +462,22 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
                         u.head0 = h * c->group + sb * c->gt;
                         u.nheads = std::min(c->gt, c->group - sb * c->gt);
                         u.t_q = t; u.kv_len = int(r.index_pos) + t + 1;
-                        u.part_begin = -1; u.part_count = 1;
+                        u.part_begin = -1; u.part_count = 1; u.merge_slot = -1; u.pad = 0;
                         units.push_back(u);
                         kv_lens.push_back(u.kv_len);
                     }
         }
     }
 
-    SplitPlan sp = plan_split(kv_lens.data(), int(units.size()), c->tile_tokens, c->decode_ctas);
-    std::vector<int32_t> merge_units;
+    SplitPlan sp = plan_split(kv_lens.data(), int(units.size()), c->tile_tokens, c->decode_chunks);
+    int n_cut = 0;
     for (size_t u = 0; u < units.size(); ++u) {
         units[u].part_begin = sp.unit_part_begin[u];
         units[u].part_count = sp.unit_part_count[u];
-        if (sp.unit_part_count[u] > 1) merge_units.push_back(int32_t(u));
+        units[u].merge_slot = sp.unit_part_count[u] > 1 ? n_cut++ : -1;
     }
+    if (size_t(n_cut) + 2 > c->sync_cap)
+        return fail(c, XN_ERR_CAPACITY, "internal: %d cut units exceed the arrival counters", n_cut);
     if ((rc = grow_device(c, &c->partials, &c->partials_cap,
                           size_t(sp.n_parts) * c->gt * part_stride_floats(nv))) != XN_OK)
         return rc;
@@ -486,7 +490,6 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
     const size_t o_item = place(sizeof(ItemDev) * sp.items.size());
     const size_t o_cta = place(sizeof(int32_t) * sp.cta_item_begin.size());
     const size_t o_page = place(sizeof(int32_t) * page_ids.size());
-    const size_t o_merge = place(sizeof(int32_t) * merge_units.size());
     const size_t o_ring = place(sizeof(int32_t) * ring_rows.size());
     PlanSlot* slot = nullptr;
     if ((rc = acquire_slot(c, off, &slot)) != XN_OK) return rc;
@@ -496,16 +499,18 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
     if (!sp.items.empty()) memcpy(slot->host + o_item, sp.items.data(), sizeof(ItemDev) * sp.items.size());
     memcpy(slot->host + o_cta, sp.cta_item_begin.data(), sizeof(int32_t) * sp.cta_item_begin.size());
     if (!page_ids.empty()) memcpy(slot->host + o_page, page_ids.data(), sizeof(int32_t) * page_ids.size());
-    if (!merge_units.empty()) memcpy(slot->host + o_merge, merge_units.data(), sizeof(int32_t) * merge_units.size());
     if (!ring_rows.empty()) memcpy(slot->host + o_ring, ring_rows.data(), sizeof(int32_t) * ring_rows.size());
-    XN_CUDA(c, cudaMemcpyAsync(slot->dev, slot->host, off, cudaMemcpyHostToDevice, c->stream));
+    // The plan does not depend on anything in flight: upload it on the copy stream so that it
+    // overlaps the previous submission's kernels, and make the launch stream wait for it.
+    XN_CUDA(c, cudaMemcpyAsync(slot->dev, slot->host, off, cudaMemcpyHostToDevice, c->copy_stream));
+    XN_CUDA(c, cudaEventRecord(slot->up_ev, c->copy_stream));
+    XN_CUDA(c, cudaStreamWaitEvent(c->stream, slot->up_ev, 0));
     c->stats.h2d_bytes += off;
     const ReqDev* reqs_d = reinterpret_cast<const ReqDev*>(slot->dev + o_req);
     const UnitDev* units_d = reinterpret_cast<const UnitDev*>(slot->dev + o_unit);
     const ItemDev* items_d = reinterpret_cast<const ItemDev*>(slot->dev + o_item);
     const int* cta_d = reinterpret_cast<const int*>(slot->dev + o_cta);
     const int* pages_d = reinterpret_cast<const int*>(slot->dev + o_page);
-    const int* merge_d = reinterpret_cast<const int*>(slot->dev + o_merge);
     const int* ring_d = reinterpret_cast<const int*>(slot->dev + o_ring);
 
     if (host_mode && io_in) {
@@ -532,19 +537,13 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
     if (sp.ctas > 0) {
         SplitKernel k = pick_split(c->nv_class, c->gt);
         if (c->profile && (rc = profile_begin(c, 0)) != XN_OK) return rc;
-        k.fn<<<sp.ctas, k.threads, k.smem, c->stream>>>(reqs_d, units_d, items_d, cta_d, pages_d,
-                                                        c->k_pool, c->v_pool, c->partials,
-                                                        c->pool_pages, Hkv, D, nv, c->scale,
-                                                        c->status_d);
+        // sp.ctas chunks, taken dynamically by at most one block per SM
+        k.fn<<<std::min(sp.ctas, c->decode_ctas), k.threads, k.smem, c->stream>>>(
+            reqs_d, units_d, items_d, cta_d, sp.ctas, pages_d, c->k_pool, c->v_pool, c->partials,
+            c->sync_d, c->pool_pages, Hkv, D, nv, c->scale, c->status_d);
         if (c->profile && (rc = profile_end(c)) != XN_OK) return rc;
         c->stats.kernel_launches += 1;
         c->stats.decode_launches += 1;
-        if (!merge_units.empty()) {
-            const int warps = int(merge_units.size()) * c->gt;
-            pick_merge(c->gt)<<<(warps + 3) / 4, 128, 0, c->stream>>>(
-                reqs_d, units_d, merge_d, int(merge_units.size()), c->partials, nv, D);
-            c->stats.kernel_launches += 1;
-        }
     }
     for (int i : tf32_reqs) {
         const ReqDev& d = rd[i];
@@ -735,6 +734,12 @@ int32_t xn_ctx_create(const xn_ctx_desc* d, xn_ctx** out_ctx) {
         int v = atoi(env);
         if (v > 0) c->decode_ctas = v;
     }
+    int chunks_per_cta = 4;
+    if (const char* env = getenv("XORNET_ATTN_DECODE_CHUNKS_PER_CTA")) {
+        int v = atoi(env);
+        if (v > 0) chunks_per_cta = v;
+    }
+    c->decode_chunks = c->decode_ctas * chunks_per_cta;
 
     const size_t page_bytes =
         size_t(d->num_layers) * d->num_kv_heads * kPageTokens * c->nv * 16 * 2;  // K and V
@@ -767,6 +772,7 @@ int32_t xn_ctx_create(const xn_ctx_desc* d, xn_ctx** out_ctx) {
         XN_CREATE_CUDA(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
         c->own_stream = true;
     }
+    XN_CREATE_CUDA(cudaStreamCreateWithFlags(&c->copy_stream, cudaStreamNonBlocking));
     const size_t pool_floats = size_t(pages) * d->num_layers * d->num_kv_heads * kPageTokens * c->nv * 4;
     XN_CREATE_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->k_pool), pool_floats * 4));
     XN_CREATE_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->v_pool), pool_floats * 4));
@@ -780,6 +786,9 @@ int32_t xn_ctx_create(const xn_ctx_desc* d, xn_ctx** out_ctx) {
         XN_CREATE_CUDA(cudaMemcpyAsync(c->cos_d, d->rope_cos, tb, cudaMemcpyHostToDevice, c->stream));
         XN_CREATE_CUDA(cudaMemcpyAsync(c->sin_d, d->rope_sin, tb, cudaMemcpyHostToDevice, c->stream));
     }
+    c->sync_cap = size_t(c->decode_chunks) + 8;  // a unit is cut at most once per chunk boundary
+    XN_CREATE_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->sync_d), c->sync_cap * sizeof(int)));
+    XN_CREATE_CUDA(cudaMemsetAsync(c->sync_d, 0, c->sync_cap * sizeof(int), c->stream));
     XN_CREATE_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->status_d), sizeof(int)));
     XN_CREATE_CUDA(cudaMemsetAsync(c->status_d, 0, sizeof(int), c->stream));
     XN_CREATE_CUDA(cudaMallocHost(reinterpret_cast<void**>(&c->status_h), sizeof(int)));
@@ -846,18 +855,21 @@ int32_t xn_ctx_destroy(xn_ctx* c) {
         if (s.host) cudaFreeHost(s.host);
         if (s.dev) cudaFree(s.dev);
         if (s.ev) cudaEventDestroy(s.ev);
+        if (s.up_ev) cudaEventDestroy(s.up_ev);
     }
     for (cudaEvent_t e : c->prof_events) cudaEventDestroy(e);
     if (c->q_rot) cudaFree(c->q_rot);
     if (c->partials) cudaFree(c->partials);
     if (c->io_host) cudaFreeHost(c->io_host);
     if (c->io_dev) cudaFree(c->io_dev);
+    if (c->sync_d) cudaFree(c->sync_d);
     if (c->status_d) cudaFree(c->status_d);
     if (c->status_h) cudaFreeHost(c->status_h);
     if (c->cos_d) cudaFree(c->cos_d);
     if (c->sin_d) cudaFree(c->sin_d);
     if (c->k_pool) cudaFree(c->k_pool);
     if (c->v_pool) cudaFree(c->v_pool);
+    if (c->copy_stream) cudaStreamDestroy(c->copy_stream);
     if (c->own_stream && c->stream) cudaStreamDestroy(c->stream);
     c->magic = 0;
     delete c;

@@ -43,6 +43,8 @@ struct UnitDev {
     int kv_len;     // cached tokens to attend (index_pos + t_q + 1)
     int part_begin; // first partial slot, or -1 when the unit is written directly
     int part_count;
+    int merge_slot; // arrival counter of a cut unit
+    int pad;
 };
 
 // A contiguous tile range of one unit given to one thread block.

@@ -10,9 +10,10 @@
 //   * work unit  = (request, KV head, <=GT query heads, query row), kv_len cached tokens;
 //   * tile       = TPS consecutive tokens of one unit: a K block and a V block, each a
 //                  contiguous run inside one 64-token page;
-//   * the host deals the flattened tile list evenly to the thread blocks (one per SM), so
-//     ragged lengths cost nothing; a unit cut across blocks yields partials that
-//     `attn_merge_kernel` combines with the usual log-sum-exp weights;
+//   * the host cuts the flattened tile list into equal chunks, several per SM; thread blocks
+//     (one per SM) take chunks dynamically, so neither ragged lengths nor uneven per-SM memory
+//     throughput leave an SM idle; a unit cut across chunks yields partial records, combined
+//     with the usual log-sum-exp weights by the block that delivers the last one;
 //   * inside a block one producer lane streams tiles into a ring of shared-memory stages with
 //     1-D bulk async copies (TMA engine, mbarrier byte counting, no tensor map, no multicast);
 //     WARPS consumer warps each own a fixed subset of a tile's tokens and keep an independent
@@ -36,17 +37,6 @@ struct DecodeCfg {
     static constexpr int kStages = 3;
     static constexpr int kStageFloats = 2 * kTPS * NV * 4;  // K block then V block
     static_assert(kIters >= 1, "tile too small for the warp layout");
-};
-
-template <int NV, int GT>
-struct DecodeSmem {
-    using Cfg = DecodeCfg<NV>;
-    static constexpr size_t kStageBytes = size_t(Cfg::kStageFloats) * 4;
-    static constexpr size_t kRedFloats = size_t(Cfg::kWarps) * GT * NV * 4;
-    static constexpr size_t kScratchFloats = size_t(Cfg::kWarps) * (Cfg::kKPW + 1) * 4;  // GT<=4
-    static constexpr size_t kBytes = Cfg::kStages * kStageBytes + kRedFloats * 4 +
-                                     kScratchFloats * 4 + Cfg::kWarps * 4 * 2 * 4 /* m,l */ +
-                                     2 * Cfg::kStages * 8 /* barriers */ + 16 /* flags */;
 };
 
 // Sum GT per-lane partial dots over the LPK lanes that share a key.  On return every lane holds
@@ -91,14 +81,61 @@ __device__ __forceinline__ int owned_head(int sub) {
 // Partial record of one (item, head): [m, l, 0, 0, acc[Dp]] floats.
 __host__ __device__ __forceinline__ size_t part_stride_floats(int nv) { return size_t(nv) * 4 + 4; }
 
+// What the producer tells the consumers about the tile in a stage.
+struct StageHdr {
+    const float* q;   // row of the unit's first query head (global)
+    float* out;       // output row of the unit's first query head
+    long long q_hs;   // query head stride (floats)
+    long long o_hs;   // output head stride (floats)
+    int flags;        // kHdr* bits
+    int ntok;         // valid tokens in this tile
+    int nheads;       // query heads of the unit (<= GT)
+    int part;         // partial slot of the item, or -1: the block writes the output itself
+    int part_begin;   // first partial slot of the unit
+    int part_count;   // items the unit was cut into
+    int merge_slot;   // arrival counter of the unit (cut units only)
+    int pad;
+};
+enum : int { kHdrFirst = 1, kHdrLast = 2, kHdrQStaged = 4, kHdrEnd = 8 };
+
+// Words of the per-context synchronisation array used by the kernel.
+enum : int { kSyncChunk = 0, kSyncDone = 1, kSyncMerge0 = 2 };
+
+template <int NV, int GT>
+struct DecodeSmem {
+    using Cfg = DecodeCfg<NV>;
+    static constexpr bool kStageQ = NV <= 32;  // query rows travel with the first tile of an item
+    static constexpr size_t kQFloats = kStageQ ? size_t(GT) * NV * 4 : 0;
+    static constexpr size_t kStageBytes = (size_t(Cfg::kStageFloats) + kQFloats) * 4;
+    static constexpr size_t kRedFloats = size_t(Cfg::kWarps) * GT * NV * 4;
+    static constexpr size_t kScratchFloats = size_t(Cfg::kWarps) * (Cfg::kKPW + 1) * 4;  // GT<=4
+    static constexpr size_t kBytes = Cfg::kStages * kStageBytes + kRedFloats * 4 +
+                                     kScratchFloats * 4 + Cfg::kWarps * 4 * 2 * 4 /* m,l */ +
+                                     Cfg::kStages * sizeof(StageHdr) + 2 * Cfg::kStages * 8 /* barriers */ +
+                                     32 /* flags */;
+};
+
+// Launch: one block per SM (at most `n_chunks` blocks).  The host cut the flattened tile list of
+// the batch into `n_chunks` chunks (several per block); a block takes chunk blockIdx.x first and
+// then whatever `sync[kSyncChunk]` hands out next, so a block that runs on a slower path to
+// memory simply takes fewer chunks.
+//
+//   producer warp  all 32 lanes resolve the descriptors of up to 32 items of a chunk at once
+//                  (item -> unit -> request, page ids), lane 0 then writes a StageHdr and issues
+//                  the bulk copies tile by tile: no dependent global load sits between two tiles;
+//   consumer warps follow the headers: load q (from the stage when it was staged) at the first
+//                  tile of an item, accumulate, merge their states at its last tile and write
+//                  either the output row (unit in one piece) or a partial record.  The block
+//                  that writes a unit's last missing partial combines all of them (arrival
+//                  counter in `sync`), so no second kernel is needed.
 template <int NV, int GT>
 __global__ void __launch_bounds__(DecodeCfg<NV>::kThreads, 1)
 attn_splitkv_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restrict__ units,
-                    const ItemDev* __restrict__ items, const int* __restrict__ cta_item_begin,
-                    const int* __restrict__ page_ids, const float* __restrict__ k_pool,
-                    const float* __restrict__ v_pool, float* __restrict__ partials,
-                    long long pool_pages, int num_kv_heads, int head_dim, int nv, float scale,
-                    int* __restrict__ status) {
+                    const ItemDev* __restrict__ items, const int* __restrict__ chunk_item_begin,
+                    int n_chunks, const int* __restrict__ page_ids,
+                    const float* __restrict__ k_pool, const float* __restrict__ v_pool,
+                    float* __restrict__ partials, int* __restrict__ sync, long long pool_pages,
+                    int num_kv_heads, int head_dim, int nv, float scale, int* __restrict__ status) {
     using Cfg = DecodeCfg<NV>;
     using Sm = DecodeSmem<NV, GT>;
     constexpr int W = Cfg::kWarps, LPK = Cfg::kLPK, KPI = Cfg::kKPI, TPS = Cfg::kTPS;
@@ -107,19 +144,20 @@ attn_splitkv_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restrict__
     constexpr unsigned kFull = 0xffffffffu;
 
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    float* stage_base = reinterpret_cast<float*>(smem_raw);
     float* red = reinterpret_cast<float*>(smem_raw + ST * Sm::kStageBytes);
     float* scratch = red + Sm::kRedFloats;
     float* sm_m = scratch + Sm::kScratchFloats;  // [W][4]
     float* sm_l = sm_m + W * 4;                  // [W][4]
-    uint64_t* full_bar = reinterpret_cast<uint64_t*>(sm_l + W * 4);
+    StageHdr* hdr = reinterpret_cast<StageHdr*>(sm_l + W * 4);
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(hdr + ST);
     uint64_t* empty_bar = full_bar + ST;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(empty_bar + ST);
+    volatile int* last_flag = abort_flag + 1;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int item_lo = cta_item_begin[blockIdx.x], item_hi = cta_item_begin[blockIdx.x + 1];
     const int dp = nv * 4;  // padded row length in floats
     const size_t page_floats = size_t(kPageTokens) * dp;
+    auto stage_ptr = [&](int s) { return reinterpret_cast<float*>(smem_raw + size_t(s) * Sm::kStageBytes); };
 
     if (tid == 0) {
         for (int s = 0; s < ST; ++s) {
@@ -127,54 +165,142 @@ attn_splitkv_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restrict__
             mbar_init(&empty_bar[s], W);
         }
         *abort_flag = 0;
+        *last_flag = 0;
         mbar_fence_init();
     }
     __syncthreads();
 
     if (warp == 0) {
-        // ---------------- producer: one lane feeds the stage ring ----------------
-        if (lane == 0) {
-            int fill = 0;
-            bool ok = true;
-            for (int it = item_lo; it < item_hi && ok; ++it) {
-                const ItemDev item = items[it];
-                const UnitDev u = units[item.unit];
-                const ReqDev& r = reqs[u.req];
-                const int* pages = page_ids + r.page_off;
-                const size_t layer_base = size_t(r.layer) * size_t(pool_pages);
-                for (int tile = item.tile_begin; tile < item.tile_end; ++tile, ++fill) {
-                    const int s = fill % ST;
-                    if (fill >= ST) {
-                        if (!mbar_wait_bounded(&empty_bar[s], ((fill / ST) - 1) & 1)) {
-                            atomicExch(status, kDevWaitEmpty);
-                            *abort_flag = 1;
-                            ok = false;
-                            break;
+        // =============================== producer ===============================
+        int fill = 0;
+        bool ok = true;
+        int chunk = blockIdx.x;
+        while (ok && chunk < n_chunks) {
+            const int it_lo = chunk_item_begin[chunk], it_hi = chunk_item_begin[chunk + 1];
+            for (int base = it_lo; base < it_hi && ok; base += 32) {
+                // ---- every lane resolves one item of this batch of 32 ----
+                const int my_it = base + lane;
+                ItemDev item = {0, 0, 0, -1};
+                UnitDev u = {};
+                const float* q_ptr = nullptr;
+                float* o_ptr = nullptr;
+                long long q_hs = 0, o_hs = 0;
+                const int* pages = page_ids;
+                size_t layer_base = 0;
+                if (my_it < it_hi) {
+                    item = items[my_it];
+                    u = units[item.unit];
+                    const ReqDev& r = reqs[u.req];
+                    q_ptr = r.q + size_t(u.head0) * r.q_hs + size_t(u.t_q) * r.q_ts;
+                    o_ptr = r.out + size_t(u.head0) * r.o_hs + size_t(u.t_q) * r.o_ts;
+                    q_hs = r.q_hs;
+                    o_hs = r.o_hs;
+                    pages = page_ids + r.page_off;
+                    layer_base = size_t(r.layer) * size_t(pool_pages);
+                }
+                const int n_here = min(32, it_hi - base);
+                for (int k = 0; k < n_here && ok; ++k) {
+                    __syncwarp();
+                    const int tile_begin = __shfl_sync(kFull, item.tile_begin, k);
+                    const int tile_end = __shfl_sync(kFull, item.tile_end, k);
+                    const int kv_len = __shfl_sync(kFull, u.kv_len, k);
+                    const int kv_head = __shfl_sync(kFull, u.kv_head, k);
+                    const unsigned long long pages_k =
+                        __shfl_sync(kFull, reinterpret_cast<unsigned long long>(pages), k);
+                    const unsigned long long lbase_k = __shfl_sync(kFull, (unsigned long long)layer_base, k);
+                    StageHdr h;
+                    h.q = reinterpret_cast<const float*>(__shfl_sync(kFull, reinterpret_cast<unsigned long long>(q_ptr), k));
+                    h.out = reinterpret_cast<float*>(__shfl_sync(kFull, reinterpret_cast<unsigned long long>(o_ptr), k));
+                    h.q_hs = __shfl_sync(kFull, q_hs, k);
+                    h.o_hs = __shfl_sync(kFull, o_hs, k);
+                    h.nheads = __shfl_sync(kFull, u.nheads, k);
+                    h.part = __shfl_sync(kFull, item.part, k);
+                    h.part_begin = __shfl_sync(kFull, u.part_begin, k);
+                    h.part_count = __shfl_sync(kFull, u.part_count, k);
+                    h.merge_slot = __shfl_sync(kFull, u.merge_slot, k);
+                    h.pad = 0;
+                    const bool stage_q = Sm::kStageQ && (head_dim % 4 == 0) &&
+                                         ((reinterpret_cast<uintptr_t>(h.q) | uintptr_t(h.q_hs * 4)) & 15) == 0;
+                    const int* pages_ptr = reinterpret_cast<const int*>(pages_k);
+                    for (int tb = tile_begin; tb < tile_end && ok; tb += 32) {
+                        // page ids of the next 32 tiles, one per lane
+                        const int my_tile = tb + lane;
+                        int my_page = 0;
+                        if (my_tile < tile_end) my_page = pages_ptr[(my_tile * TPS) / kPageTokens];
+                        const int n_t = min(32, tile_end - tb);
+                        for (int tt = 0; tt < n_t; ++tt, ++fill) {
+                            __syncwarp();
+                            const int page = __shfl_sync(kFull, my_page, tt);
+                            if (lane == 0) {
+                                const int tile = tb + tt;
+                                const int s = fill % ST;
+                                if (fill >= ST && !mbar_wait_bounded(&empty_bar[s], ((fill / ST) - 1) & 1)) {
+                                    atomicExch(status, kDevWaitEmpty);
+                                    *abort_flag = 1;
+                                    ok = false;
+                                } else {
+                                    const int tok0 = tile * TPS;
+                                    const int ntok = min(TPS, kv_len - tok0);
+                                    const size_t src = ((size_t(lbase_k) + size_t(page)) * num_kv_heads + kv_head) *
+                                                           page_floats +
+                                                       size_t(tok0 % kPageTokens) * dp;
+                                    const uint32_t bytes = uint32_t(ntok) * dp * 4;
+                                    const bool first = tile == tile_begin;
+                                    h.flags = (first ? kHdrFirst : 0) | (tile == tile_end - 1 ? kHdrLast : 0) |
+                                              (first && stage_q ? kHdrQStaged : 0);
+                                    h.ntok = ntok;
+                                    hdr[s] = h;
+                                    float* dst = stage_ptr(s);
+                                    const uint32_t q_bytes = (first && stage_q) ? uint32_t(h.nheads) * dp * 4 : 0u;
+                                    mbar_arrive_expect_tx(&full_bar[s], 2 * bytes + q_bytes);
+                                    bulk_g2s(dst, k_pool + src, bytes, &full_bar[s]);
+                                    bulk_g2s(dst + TPS * NV * 4, v_pool + src, bytes, &full_bar[s]);
+                                    if (q_bytes)
+                                        for (int hh = 0; hh < h.nheads; ++hh)
+                                            bulk_g2s(dst + Cfg::kStageFloats + hh * dp, h.q + size_t(hh) * h.q_hs,
+                                                     uint32_t(dp) * 4, &full_bar[s]);
+                                }
+                            }
+                            ok = __shfl_sync(kFull, ok ? 1 : 0, 0) != 0;
+                            if (!ok) break;
                         }
                     }
-                    const int tok0 = tile * TPS;
-                    const int ntok = min(TPS, u.kv_len - tok0);
-                    const int page = pages[tok0 / kPageTokens];
-                    const size_t src = ((layer_base + size_t(page)) * num_kv_heads + u.kv_head) *
-                                           page_floats +
-                                       size_t(tok0 % kPageTokens) * dp;
-                    const uint32_t bytes = uint32_t(ntok) * dp * 4;
-                    float* dst = stage_base + size_t(s) * Cfg::kStageFloats;
-                    mbar_arrive_expect_tx(&full_bar[s], 2 * bytes);
-                    bulk_g2s(dst, k_pool + src, bytes, &full_bar[s]);
-                    bulk_g2s(dst + TPS * NV * 4, v_pool + src, bytes, &full_bar[s]);
                 }
             }
-            if (!ok) {
+            // next chunk: dynamic
+            int next = 0;
+            if (lane == 0) next = atomicAdd(&sync[kSyncChunk], 1) + int(gridDim.x);
+            chunk = __shfl_sync(kFull, next, 0);
+        }
+        if (lane == 0) {
+            if (ok) {
+                // end-of-work marker
+                const int s = fill % ST;
+                if (fill >= ST && !mbar_wait_bounded(&empty_bar[s], ((fill / ST) - 1) & 1)) {
+                    atomicExch(status, kDevWaitEmpty);
+                    *abort_flag = 1;
+                } else {
+                    StageHdr h = {};
+                    h.flags = kHdrEnd;
+                    hdr[s] = h;
+                    mbar_arrive(&full_bar[s]);
+                }
+            } else {
                 // Do not retire the block with copies still landing in its shared memory.
                 for (int f = max(0, fill - ST); f < fill; ++f)
                     mbar_wait_bounded(&full_bar[f % ST], (f / ST) & 1);
+            }
+            // the last block to finish re-arms the chunk counter for the next launch
+            __threadfence();
+            if (atomicAdd(&sync[kSyncDone], 1) == int(gridDim.x) - 1) {
+                sync[kSyncChunk] = 0;
+                sync[kSyncDone] = 0;
             }
         }
         return;
     }
 
-    // ---------------- consumers ----------------
+    // =============================== consumers ===============================
     const int cw = warp - 1;
     const int sub = lane % LPK, grp = lane / LPK;
     const int hown = owned_head<GT>(sub);
@@ -182,155 +308,151 @@ attn_splitkv_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restrict__
     float* my_scr = scratch + cw * (KPW + 1) * 4;
     const int ctid = tid - 32;  // 0 .. W*32-1
 
-    int fill = 0;
-    bool dead = false;  // set when a wait gave up: keep the barrier protocol, skip the math
+    float4 qreg[GT][SQ];
+    float4 acc[GT][SV];
+    float m_run = -INFINITY, l_run = 0.f;
 
-    for (int it = item_lo; it < item_hi; ++it) {
-        const ItemDev item = items[it];
-        const UnitDev u = units[item.unit];
-        const ReqDev& r = reqs[u.req];
+    for (int fill = 0;; ++fill) {
+        const int s = fill % ST;
+        if (!__all_sync(kFull, mbar_wait_bounded(&full_bar[s], (fill / ST) & 1))) {
+            atomicExch(status, kDevWaitFull);
+            *abort_flag = 1;
+            break;  // the producer notices the flag or runs into its own bounded wait
+        }
+        // (the abort flag is deliberately not polled here: every consumer warp must leave at the
+        // same tile, or the block-wide barriers of the merge below would lose a participant)
+        const StageHdr h = hdr[s];
+        if (h.flags & kHdrEnd) break;
+        const float4* Ks = reinterpret_cast<const float4*>(stage_ptr(s));
+        const float4* Vs = Ks + TPS * NV;
 
-        // query rows of the unit's heads, the float4 slots this lane multiplies
-        float4 qreg[GT][SQ];
+        if (h.flags & kHdrFirst) {
+            // query rows of the unit's heads, the float4 slots this lane multiplies
 #pragma unroll
-        for (int h = 0; h < GT; ++h) {
-            const float* qrow = r.q + size_t(u.head0 + h) * r.q_hs + size_t(u.t_q) * r.q_ts;
+            for (int hh = 0; hh < GT; ++hh) {
 #pragma unroll
-            for (int j = 0; j < SQ; ++j) {
-                const int idx = j * LPK + sub;
-                float4 val = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (h < u.nheads && idx < nv) {
-                    const int d = idx * 4;
-                    if (d + 3 < head_dim && ((reinterpret_cast<uintptr_t>(qrow + d) & 15) == 0)) {
-                        val = *reinterpret_cast<const float4*>(qrow + d);
-                    } else {
-                        if (d + 0 < head_dim) val.x = qrow[d + 0];
-                        if (d + 1 < head_dim) val.y = qrow[d + 1];
-                        if (d + 2 < head_dim) val.z = qrow[d + 2];
-                        if (d + 3 < head_dim) val.w = qrow[d + 3];
+                for (int j = 0; j < SQ; ++j) {
+                    const int idx = j * LPK + sub;
+                    float4 val = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (hh < h.nheads && idx < nv) {
+                        if (h.flags & kHdrQStaged) {
+                            val = reinterpret_cast<const float4*>(stage_ptr(s) + Cfg::kStageFloats)[hh * nv + idx];
+                        } else {
+                            const float* qrow = h.q + size_t(hh) * h.q_hs;
+                            const int d = idx * 4;
+                            if (d + 0 < head_dim) val.x = qrow[d + 0];
+                            if (d + 1 < head_dim) val.y = qrow[d + 1];
+                            if (d + 2 < head_dim) val.z = qrow[d + 2];
+                            if (d + 3 < head_dim) val.w = qrow[d + 3];
+                        }
                     }
+                    qreg[hh][j] = val;
                 }
-                qreg[h][j] = val;
             }
+            m_run = -INFINITY;
+            l_run = 0.f;
+#pragma unroll
+            for (int hh = 0; hh < GT; ++hh)
+#pragma unroll
+                for (int sv = 0; sv < SV; ++sv) acc[hh][sv] = make_float4(0.f, 0.f, 0.f, 0.f);
         }
 
-        float m_run = -INFINITY, l_run = 0.f;
-        float4 acc[GT][SV];
+        {
+            const int ntok = h.ntok;
+            // ---- scores for this warp's keys ----
+            float sc[ITERS];
+            float bm = -INFINITY;
 #pragma unroll
-        for (int h = 0; h < GT; ++h)
+            for (int i = 0; i < ITERS; ++i) {
+                const int key = i * (W * KPI) + cw * KPI + grp;
+                const float4* krow = Ks + size_t(key) * nv;
+                float part[GT];
 #pragma unroll
-            for (int s = 0; s < SV; ++s) acc[h][s] = make_float4(0.f, 0.f, 0.f, 0.f);
-
-        for (int tile = item.tile_begin; tile < item.tile_end; ++tile, ++fill) {
-            const int s = fill % ST;
-            if (!dead) {
-                if (!mbar_wait_bounded(&full_bar[s], (fill / ST) & 1)) {
-                    atomicExch(status, kDevWaitFull);
-                    *abort_flag = 1;
-                    dead = true;
-                }
-            }
-            if (!dead && *abort_flag) dead = true;
-            if (!dead) {
-                const int ntok = min(TPS, u.kv_len - tile * TPS);
-                const float4* Ks =
-                    reinterpret_cast<const float4*>(stage_base + size_t(s) * Cfg::kStageFloats);
-                const float4* Vs = Ks + TPS * NV;
-
-                // ---- scores for this warp's keys ----
-                float sc[ITERS];
-                float bm = -INFINITY;
+                for (int hh = 0; hh < GT; ++hh) part[hh] = 0.f;
 #pragma unroll
-                for (int i = 0; i < ITERS; ++i) {
-                    const int key = i * (W * KPI) + cw * KPI + grp;
-                    const float4* krow = Ks + size_t(key) * nv;
-                    float part[GT];
+                for (int j = 0; j < SQ; ++j) {
+                    const int idx = j * LPK + sub;
+                    if (idx < nv) {
+                        const float4 kv = krow[idx];
 #pragma unroll
-                    for (int h = 0; h < GT; ++h) part[h] = 0.f;
-#pragma unroll
-                    for (int j = 0; j < SQ; ++j) {
-                        const int idx = j * LPK + sub;
-                        if (NV % LPK == 0 && nv == NV ? true : idx < nv) {
-                            const float4 kv = krow[idx];
-#pragma unroll
-                            for (int h = 0; h < GT; ++h) {
-                                part[h] = fmaf(qreg[h][j].x, kv.x, part[h]);
-                                part[h] = fmaf(qreg[h][j].y, kv.y, part[h]);
-                                part[h] = fmaf(qreg[h][j].z, kv.z, part[h]);
-                                part[h] = fmaf(qreg[h][j].w, kv.w, part[h]);
-                            }
-                        }
-                    }
-                    float dot = group_reduce<GT, LPK>(part, sub);
-                    // invalid keys hold stale shared memory: discard whatever came out
-                    sc[i] = (key < ntok) ? dot * scale : -INFINITY;
-                    bm = fmaxf(bm, sc[i]);
-                }
-#pragma unroll
-                for (int o = LPK; o < 32; o <<= 1) bm = fmaxf(bm, __shfl_xor_sync(kFull, bm, o));
-
-                const float m_new = fmaxf(m_run, bm);
-                const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
-                const float alpha = expf(m_run - m_safe);  // exp(-inf) = 0 on the first tile
-                float psum = 0.f;
-#pragma unroll
-                for (int i = 0; i < ITERS; ++i) {
-                    const float p = (sc[i] == -INFINITY) ? 0.f : expf(sc[i] - m_safe);
-                    psum += p;
-                    if (canon) my_scr[(i * KPI + grp) * GT + hown] = p;
-                }
-                l_run = l_run * alpha + psum;
-                if (canon && grp == 0) my_scr[KPW * 4 + hown] = alpha;
-                const bool moved = __any_sync(kFull, m_new > m_run);
-                m_run = m_new;
-                __syncwarp();
-
-                if (moved) {
-                    float al[GT];
-#pragma unroll
-                    for (int h = 0; h < GT; ++h) al[h] = my_scr[KPW * 4 + h];
-#pragma unroll
-                    for (int h = 0; h < GT; ++h)
-#pragma unroll
-                        for (int sv = 0; sv < SV; ++sv) {
-                            acc[h][sv].x *= al[h];
-                            acc[h][sv].y *= al[h];
-                            acc[h][sv].z *= al[h];
-                            acc[h][sv].w *= al[h];
-                        }
-                }
-
-                // ---- weighted V rows of the same keys ----
-#pragma unroll
-                for (int kk = 0; kk < KPW; ++kk) {
-                    const int key = (kk / KPI) * (W * KPI) + cw * KPI + (kk % KPI);
-                    if (key < ntok) {
-                        float pv[GT];
-#pragma unroll
-                        for (int h = 0; h < GT; ++h) pv[h] = my_scr[kk * GT + h];
-                        const float4* vrow = Vs + size_t(key) * nv;
-#pragma unroll
-                        for (int sv = 0; sv < SV; ++sv) {
-                            const int idx = lane + 32 * sv;
-                            if (idx < nv) {
-                                const float4 vv = vrow[idx];
-#pragma unroll
-                                for (int h = 0; h < GT; ++h) {
-                                    acc[h][sv].x = fmaf(pv[h], vv.x, acc[h][sv].x);
-                                    acc[h][sv].y = fmaf(pv[h], vv.y, acc[h][sv].y);
-                                    acc[h][sv].z = fmaf(pv[h], vv.z, acc[h][sv].z);
-                                    acc[h][sv].w = fmaf(pv[h], vv.w, acc[h][sv].w);
-                                }
-                            }
+                        for (int hh = 0; hh < GT; ++hh) {
+                            part[hh] = fmaf(qreg[hh][j].x, kv.x, part[hh]);
+                            part[hh] = fmaf(qreg[hh][j].y, kv.y, part[hh]);
+                            part[hh] = fmaf(qreg[hh][j].z, kv.z, part[hh]);
+                            part[hh] = fmaf(qreg[hh][j].w, kv.w, part[hh]);
                         }
                     }
                 }
+                float dot = group_reduce<GT, LPK>(part, sub);
+                // invalid keys hold stale shared memory: discard whatever came out
+                sc[i] = (key < ntok) ? dot * scale : -INFINITY;
+                bm = fmaxf(bm, sc[i]);
             }
+#pragma unroll
+            for (int o = LPK; o < 32; o <<= 1) bm = fmaxf(bm, __shfl_xor_sync(kFull, bm, o));
+
+            const float m_new = fmaxf(m_run, bm);
+            const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
+            const float alpha = expf(m_run - m_safe);  // exp(-inf) = 0 on the first tile
+            float psum = 0.f;
+#pragma unroll
+            for (int i = 0; i < ITERS; ++i) {
+                const float p = (sc[i] == -INFINITY) ? 0.f : expf(sc[i] - m_safe);
+                psum += p;
+                if (canon) my_scr[(i * KPI + grp) * GT + hown] = p;
+            }
+            l_run = l_run * alpha + psum;
+            if (canon && grp == 0) my_scr[KPW * 4 + hown] = alpha;
+            const bool moved = __any_sync(kFull, m_new > m_run);
+            m_run = m_new;
             __syncwarp();
-            if (lane == 0) mbar_arrive(&empty_bar[s]);
-        }
 
-        // ---- merge the W warp states of this item ----
+            if (moved) {
+                float al[GT];
+#pragma unroll
+                for (int hh = 0; hh < GT; ++hh) al[hh] = my_scr[KPW * 4 + hh];
+#pragma unroll
+                for (int hh = 0; hh < GT; ++hh)
+#pragma unroll
+                    for (int sv = 0; sv < SV; ++sv) {
+                        acc[hh][sv].x *= al[hh];
+                        acc[hh][sv].y *= al[hh];
+                        acc[hh][sv].z *= al[hh];
+                        acc[hh][sv].w *= al[hh];
+                    }
+            }
+
+            // ---- weighted V rows of the same keys ----
+#pragma unroll
+            for (int kk = 0; kk < KPW; ++kk) {
+                const int key = (kk / KPI) * (W * KPI) + cw * KPI + (kk % KPI);
+                if (key < ntok) {
+                    float pv[GT];
+#pragma unroll
+                    for (int hh = 0; hh < GT; ++hh) pv[hh] = my_scr[kk * GT + hh];
+                    const float4* vrow = Vs + size_t(key) * nv;
+#pragma unroll
+                    for (int sv = 0; sv < SV; ++sv) {
+                        const int idx = lane + 32 * sv;
+                        if (idx < nv) {
+                            const float4 vv = vrow[idx];
+#pragma unroll
+                            for (int hh = 0; hh < GT; ++hh) {
+                                acc[hh][sv].x = fmaf(pv[hh], vv.x, acc[hh][sv].x);
+                                acc[hh][sv].y = fmaf(pv[hh], vv.y, acc[hh][sv].y);
+                                acc[hh][sv].z = fmaf(pv[hh], vv.z, acc[hh][sv].z);
+                                acc[hh][sv].w = fmaf(pv[hh], vv.w, acc[hh][sv].w);
+                            }
+                        }
+                    }
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty_bar[s]);
+        if (!(h.flags & kHdrLast)) continue;
+
+        // ---- last tile of the item: merge the W warp states ----
         float l_tot = l_run;
 #pragma unroll
         for (int o = LPK; o < 32; o <<= 1) l_tot += __shfl_xor_sync(kFull, l_tot, o);
@@ -341,107 +463,104 @@ attn_splitkv_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restrict__
         named_bar_sync(1, W * 32);
         float f[GT];
 #pragma unroll
-        for (int h = 0; h < GT; ++h) {
+        for (int hh = 0; hh < GT; ++hh) {
             float M = -INFINITY;
 #pragma unroll
-            for (int w = 0; w < W; ++w) M = fmaxf(M, sm_m[w * 4 + h]);
-            const float mw = sm_m[cw * 4 + h];
-            f[h] = (mw == -INFINITY) ? 0.f : expf(mw - M);
+            for (int w = 0; w < W; ++w) M = fmaxf(M, sm_m[w * 4 + hh]);
+            const float mw = sm_m[cw * 4 + hh];
+            f[hh] = (mw == -INFINITY) ? 0.f : expf(mw - M);
         }
 #pragma unroll
-        for (int h = 0; h < GT; ++h)
+        for (int hh = 0; hh < GT; ++hh)
 #pragma unroll
             for (int sv = 0; sv < SV; ++sv) {
                 const int idx = lane + 32 * sv;
                 if (idx < nv) {
-                    float4 a = acc[h][sv];
-                    a.x *= f[h]; a.y *= f[h]; a.z *= f[h]; a.w *= f[h];
-                    reinterpret_cast<float4*>(red)[(size_t(cw) * GT + h) * nv + idx] = a;
+                    float4 a = acc[hh][sv];
+                    a.x *= f[hh]; a.y *= f[hh]; a.z *= f[hh]; a.w *= f[hh];
+                    reinterpret_cast<float4*>(red)[(size_t(cw) * GT + hh) * nv + idx] = a;
                 }
             }
         named_bar_sync(1, W * 32);
-        if (!dead) {
-            for (int e = ctid; e < GT * nv; e += W * 32) {
-                const int h = e / nv, idx = e % nv;
-                if (h >= u.nheads) continue;
-                float M = -INFINITY;
+        for (int e = ctid; e < GT * nv; e += W * 32) {
+            const int hh = e / nv, idx = e % nv;
+            if (hh >= h.nheads) continue;
+            float M = -INFINITY;
 #pragma unroll
-                for (int w = 0; w < W; ++w) M = fmaxf(M, sm_m[w * 4 + h]);
-                float L = 0.f;
-                float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int w = 0; w < W; ++w) M = fmaxf(M, sm_m[w * 4 + hh]);
+            float L = 0.f;
+            float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-                for (int w = 0; w < W; ++w) {
-                    const float mw = sm_m[w * 4 + h];
-                    const float fw = (mw == -INFINITY) ? 0.f : expf(mw - M);
-                    L += sm_l[w * 4 + h] * fw;
-                    const float4 a = reinterpret_cast<const float4*>(red)[(size_t(w) * GT + h) * nv + idx];
-                    sum.x += a.x; sum.y += a.y; sum.z += a.z; sum.w += a.w;
-                }
-                if (item.part < 0) {
-                    float* orow = r.out + size_t(u.head0 + h) * r.o_hs + size_t(u.t_q) * r.o_ts;
-                    const float inv = 1.0f / L;
-                    const int d = idx * 4;
-                    if (d + 3 < head_dim && ((reinterpret_cast<uintptr_t>(orow + d) & 15) == 0)) {
-                        *reinterpret_cast<float4*>(orow + d) =
-                            make_float4(sum.x * inv, sum.y * inv, sum.z * inv, sum.w * inv);
-                    } else {
-                        if (d + 0 < head_dim) orow[d + 0] = sum.x * inv;
-                        if (d + 1 < head_dim) orow[d + 1] = sum.y * inv;
-                        if (d + 2 < head_dim) orow[d + 2] = sum.z * inv;
-                        if (d + 3 < head_dim) orow[d + 3] = sum.w * inv;
-                    }
+            for (int w = 0; w < W; ++w) {
+                const float mw = sm_m[w * 4 + hh];
+                const float fw = (mw == -INFINITY) ? 0.f : expf(mw - M);
+                L += sm_l[w * 4 + hh] * fw;
+                const float4 a = reinterpret_cast<const float4*>(red)[(size_t(w) * GT + hh) * nv + idx];
+                sum.x += a.x; sum.y += a.y; sum.z += a.z; sum.w += a.w;
+            }
+            if (h.part < 0) {
+                float* orow = h.out + size_t(hh) * h.o_hs;
+                const float inv = 1.0f / L;
+                const int d = idx * 4;
+                if (d + 3 < head_dim && ((reinterpret_cast<uintptr_t>(orow + d) & 15) == 0)) {
+                    *reinterpret_cast<float4*>(orow + d) =
+                        make_float4(sum.x * inv, sum.y * inv, sum.z * inv, sum.w * inv);
                 } else {
-                    float* rec = partials + (size_t(item.part) * GT + h) * part_stride_floats(nv);
-                    if (idx == 0) *reinterpret_cast<float4*>(rec) = make_float4(M, L, 0.f, 0.f);
-                    reinterpret_cast<float4*>(rec + 4)[idx] = sum;
+                    if (d + 0 < head_dim) orow[d + 0] = sum.x * inv;
+                    if (d + 1 < head_dim) orow[d + 1] = sum.y * inv;
+                    if (d + 2 < head_dim) orow[d + 2] = sum.z * inv;
+                    if (d + 3 < head_dim) orow[d + 3] = sum.w * inv;
                 }
+            } else {
+                float* rec = partials + (size_t(h.part) * GT + hh) * part_stride_floats(nv);
+                if (idx == 0) *reinterpret_cast<float4*>(rec) = make_float4(M, L, 0.f, 0.f);
+                reinterpret_cast<float4*>(rec + 4)[idx] = sum;
             }
         }
-    }
-}
+        if (h.part < 0) continue;
 
-// Combines the partials of every unit that was cut across thread blocks.  One warp per
-// (unit, head): out = sum_i exp(m_i - M) acc_i / sum_i exp(m_i - M) l_i.
-template <int GT>
-__global__ void attn_merge_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restrict__ units,
-                                  const int* __restrict__ merge_units, int n_merge,
-                                  const float* __restrict__ partials, int nv, int head_dim) {
-    const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    const int lane = threadIdx.x & 31;
-    if (gw >= n_merge * GT) return;
-    const UnitDev u = units[merge_units[gw / GT]];
-    const int h = gw % GT;
-    if (h >= u.nheads) return;
-    const ReqDev& r = reqs[u.req];
-    const size_t ps = part_stride_floats(nv);
-    float M = -INFINITY;
-    for (int i = 0; i < u.part_count; ++i)
-        M = fmaxf(M, partials[(size_t(u.part_begin + i) * GT + h) * ps]);
-    float L = 0.f;
-    for (int i = 0; i < u.part_count; ++i) {
-        const float* rec = partials + (size_t(u.part_begin + i) * GT + h) * ps;
-        const float mi = rec[0];
-        L += (mi == -INFINITY) ? 0.f : rec[1] * expf(mi - M);
-    }
-    const float inv = 1.0f / L;
-    float* orow = r.out + size_t(u.head0 + h) * r.o_hs + size_t(u.t_q) * r.o_ts;
-    for (int idx = lane; idx < nv; idx += 32) {
-        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int i = 0; i < u.part_count; ++i) {
-            const float* rec = partials + (size_t(u.part_begin + i) * GT + h) * ps;
-            const float mi = rec[0];
-            const float w = (mi == -INFINITY) ? 0.f : expf(mi - M);
-            const float4 a = reinterpret_cast<const float4*>(rec + 4)[idx];
-            sum.x = fmaf(w, a.x, sum.x);
-            sum.y = fmaf(w, a.y, sum.y);
-            sum.z = fmaf(w, a.z, sum.z);
-            sum.w = fmaf(w, a.w, sum.w);
+        // ---- the unit was cut: whoever delivers its last partial combines them all ----
+        __threadfence();
+        named_bar_sync(1, W * 32);
+        if (ctid == 0) {
+            const int old = atomicAdd(&sync[kSyncMerge0 + h.merge_slot], 1);
+            const int last = old == h.part_count - 1;
+            if (last) sync[kSyncMerge0 + h.merge_slot] = 0;  // re-armed for the next launch
+            *last_flag = last;
         }
-        const int d = idx * 4;
-        if (d + 0 < head_dim) orow[d + 0] = sum.x * inv;
-        if (d + 1 < head_dim) orow[d + 1] = sum.y * inv;
-        if (d + 2 < head_dim) orow[d + 2] = sum.z * inv;
-        if (d + 3 < head_dim) orow[d + 3] = sum.w * inv;
+        named_bar_sync(1, W * 32);
+        if (*last_flag) {
+            __threadfence();
+            const size_t ps = part_stride_floats(nv);
+            for (int e = ctid; e < GT * nv; e += W * 32) {
+                const int hh = e / nv, idx = e % nv;
+                if (hh >= h.nheads) continue;
+                float M = -INFINITY;
+                for (int i = 0; i < h.part_count; ++i)
+                    M = fmaxf(M, __ldcg(partials + (size_t(h.part_begin + i) * GT + hh) * ps));
+                float L = 0.f;
+                float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int i = 0; i < h.part_count; ++i) {
+                    const float* rec = partials + (size_t(h.part_begin + i) * GT + hh) * ps;
+                    const float mi = __ldcg(rec);
+                    const float wgt = (mi == -INFINITY) ? 0.f : expf(mi - M);
+                    L += __ldcg(rec + 1) * wgt;
+                    const float4 a = __ldcg(reinterpret_cast<const float4*>(rec + 4) + idx);
+                    sum.x = fmaf(wgt, a.x, sum.x);
+                    sum.y = fmaf(wgt, a.y, sum.y);
+                    sum.z = fmaf(wgt, a.z, sum.z);
+                    sum.w = fmaf(wgt, a.w, sum.w);
+                }
+                const float inv = 1.0f / L;
+                float* orow = h.out + size_t(hh) * h.o_hs;
+                const int d = idx * 4;
+                if (d + 0 < head_dim) orow[d + 0] = sum.x * inv;
+                if (d + 1 < head_dim) orow[d + 1] = sum.y * inv;
+                if (d + 2 < head_dim) orow[d + 2] = sum.z * inv;
+                if (d + 3 < head_dim) orow[d + 3] = sum.w * inv;
+            }
+        }
+        named_bar_sync(1, W * 32);  // last_flag and red are reused by the next item
     }
 }
 
