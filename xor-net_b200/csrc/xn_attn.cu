@@ -502,9 +502,14 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
     if (!ring_rows.empty()) memcpy(slot->host + o_ring, ring_rows.data(), sizeof(int32_t) * ring_rows.size());
     // The plan does not depend on anything in flight: upload it on the copy stream so that it
     // overlaps the previous submission's kernels, and make the launch stream wait for it.
-    XN_CUDA(c, cudaMemcpyAsync(slot->dev, slot->host, off, cudaMemcpyHostToDevice, c->copy_stream));
-    XN_CUDA(c, cudaEventRecord(slot->up_ev, c->copy_stream));
-    XN_CUDA(c, cudaStreamWaitEvent(c->stream, slot->up_ev, 0));
+    // (A blocking host-pointer call has nothing in flight to overlap with: plain in-stream copy.)
+    if (host_mode) {
+        XN_CUDA(c, cudaMemcpyAsync(slot->dev, slot->host, off, cudaMemcpyHostToDevice, c->stream));
+    } else {
+        XN_CUDA(c, cudaMemcpyAsync(slot->dev, slot->host, off, cudaMemcpyHostToDevice, c->copy_stream));
+        XN_CUDA(c, cudaEventRecord(slot->up_ev, c->copy_stream));
+        XN_CUDA(c, cudaStreamWaitEvent(c->stream, slot->up_ev, 0));
+    }
     c->stats.h2d_bytes += off;
     const ReqDev* reqs_d = reinterpret_cast<const ReqDev*>(slot->dev + o_req);
     const UnitDev* units_d = reinterpret_cast<const UnitDev*>(slot->dev + o_unit);

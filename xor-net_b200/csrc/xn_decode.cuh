@@ -520,17 +520,19 @@ attn_splitkv_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restrict__
         if (h.part < 0) continue;
 
         // ---- the unit was cut: whoever delivers its last partial combines them all ----
-        __threadfence();
+        // (block barrier, then one thread fences and counts: the fence is cumulative over the
+        // writes the barrier ordered before it, so the other threads need none of their own)
         named_bar_sync(1, W * 32);
         if (ctid == 0) {
+            __threadfence();
             const int old = atomicAdd(&sync[kSyncMerge0 + h.merge_slot], 1);
             const int last = old == h.part_count - 1;
             if (last) sync[kSyncMerge0 + h.merge_slot] = 0;  // re-armed for the next launch
+            __threadfence();
             *last_flag = last;
         }
         named_bar_sync(1, W * 32);
         if (*last_flag) {
-            __threadfence();
             const size_t ps = part_stride_floats(nv);
             for (int e = ctid; e < GT * nv; e += W * 32) {
                 const int hh = e / nv, idx = e % nv;

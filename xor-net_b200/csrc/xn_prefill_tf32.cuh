@@ -291,49 +291,75 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap k_map,
         }
     } else if (warp == 1) {
         // =============================== MMA issuer ===============================
+        // One lane issues every tcgen05.mma of the block, so its instruction stream is kept
+        // short: descriptors are a constant plus a small offset, ring positions and mbarrier
+        // parities are carried as counters, and the head_dim = 128 loops are fully unrolled.
         if (lane == 0) {
             const uint32_t idesc_qk = make_idesc(kBM, kBN, 0);
             const uint32_t idesc_pv = make_idesc(kBM, n_pv, 1);
-            const uint32_t k_addr = smem_u32(k_s), v_addr = smem_u32(v_s);
+            // descriptor of stage 0; a stage is kKVBytes further, offsets are in 16-byte units
+            const uint64_t kdesc0 = smem_desc(smem_u32(k_s), 0, 1024, kLayoutSw128);
+            const uint64_t vdesc0 = smem_desc(smem_u32(v_s), kKVSub, 512, kLayoutSw128Base32);
+            constexpr uint64_t kStageStep = uint64_t(kKVBytes) >> 4;
+            constexpr uint64_t kBlockStep = uint64_t(kKVSub) >> 4;  // next 32-float column block
             bool ok = mbar_wait_bounded(q_ready, 0);
             if (!ok) { atomicExch(a.status, kDevWaitFull); *abort_flag = 1; }
             fence_after_sync();
-            // issues O += P_j V_j
-            auto issue_pv = [&](int j) -> bool {
-                const int sb = j % kSBufs, s = j % kVStages;
-                if (!mbar_wait_bounded(&p_full[sb], uint32_t((j / kSBufs) & 1)) ||
-                    !mbar_wait_bounded(&v_full[s], uint32_t((j / kVStages) & 1)))
-                    return false;
+
+            int k_st = 0, k_ph = 0;     // K ring position / parity of the next S = Q K^T
+            int s_qk = 0;               // score buffer of the next S = Q K^T
+            int v_st = 0, v_ph = 0;     // V ring position / parity of the next O += P V
+            int s_pv = 0, p_ph = 0;     // score buffer / parity of the next O += P V
+            int pv_issued = 0;
+
+            auto issue_qk = [&]() -> bool {
+                if (!mbar_wait_bounded(&k_full[k_st], uint32_t(k_ph))) return false;
                 fence_after_sync();
-                for (int ks = 0; ks < kBN / 8; ++ks) {
-                    // V is [token][dim]: MN-major B.  8 tokens = 1024 B inside each column block,
-                    // column blocks kKVSub apart (leading offset), 4-token swizzle groups 512 B
-                    // apart (stride offset)
-                    const uint64_t bd = smem_desc(v_addr + s * kKVBytes + ks * 1024, kKVSub, 512,
-                                                  kLayoutSw128Base32);
-                    mma_ts(tmem_o, tmem_s + sb * kBN + ks * 8, bd, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+                const uint64_t kd = kdesc0 + uint64_t(k_st) * kStageStep;
+                const uint32_t d_addr = tmem_s + s_qk * kBN;
+                if (k_steps == 16) {
+#pragma unroll
+                    for (int ks = 0; ks < 16; ++ks)
+                        mma_ts(d_addr, tmem_q + ks * 8, kd + (ks >> 2) * kBlockStep + (ks & 3) * 2, idesc_qk,
+                               ks > 0 ? 1u : 0u);
+                } else {
+                    for (int ks = 0; ks < k_steps; ++ks)
+                        mma_ts(d_addr, tmem_q + ks * 8, kd + (ks >> 2) * kBlockStep + (ks & 3) * 2, idesc_qk,
+                               ks > 0 ? 1u : 0u);
                 }
-                mma_commit(&v_empty[s]);
-                mma_commit(&pv_done[sb]);
+                mma_commit(&k_empty[k_st]);
+                mma_commit(&s_full[s_qk]);
+                if (++k_st == kKStages) { k_st = 0; k_ph ^= 1; }
+                s_qk = (s_qk + 1) & (kSBufs - 1);
                 return true;
             };
-            for (int j = 0; j < n_tiles && ok; ++j) {
-                const int s = j % kKStages, sb = j % kSBufs;
-                if (!mbar_wait_bounded(&k_full[s], uint32_t((j / kKStages) & 1))) { ok = false; break; }
+            // O += P_j V_j.  V is [token][dim]: MN-major B; 8 tokens = 1024 B inside each column
+            // block, column blocks kKVSub apart (leading offset), 4-token swizzle groups 512 B apart
+            auto issue_pv = [&]() -> bool {
+                if (!mbar_wait_bounded(&p_full[s_pv], uint32_t(p_ph)) ||
+                    !mbar_wait_bounded(&v_full[v_st], uint32_t(v_ph)))
+                    return false;
                 fence_after_sync();
-                for (int ks = 0; ks < k_steps; ++ks) {
-                    const int kb = ks >> 2, kin = ks & 3;  // column block, 32-byte step inside it
-                    const uint64_t bd = smem_desc(k_addr + s * kKVBytes + kb * kKVSub + kin * 32, 0, 1024,
-                                                  kLayoutSw128);
-                    mma_ts(tmem_s + sb * kBN, tmem_q + ks * 8, bd, idesc_qk, ks > 0 ? 1u : 0u);
-                }
-                mma_commit(&k_empty[s]);
-                mma_commit(&s_full[sb]);
-                if (j >= kLookahead && !issue_pv(j - kLookahead)) { ok = false; break; }
-                if (*abort_flag) { ok = false; break; }
+                const uint64_t vd = vdesc0 + uint64_t(v_st) * kStageStep;
+                const uint32_t p_addr = tmem_s + s_pv * kBN;
+                const uint32_t first = pv_issued > 0 ? 1u : 0u;
+#pragma unroll
+                for (int ks = 0; ks < kBN / 8; ++ks)
+                    mma_ts(tmem_o, p_addr + ks * 8, vd + ks * 64, idesc_pv, ks > 0 ? 1u : first);
+                mma_commit(&v_empty[v_st]);
+                mma_commit(&pv_done[s_pv]);
+                if (++v_st == kVStages) { v_st = 0; v_ph ^= 1; }
+                if (++s_pv == kSBufs) { s_pv = 0; p_ph ^= 1; }
+                ++pv_issued;
+                return true;
+            };
+            static_assert((kSBufs & (kSBufs - 1)) == 0, "score buffers: power of two");
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                if (!issue_qk()) { ok = false; break; }
+                if (j >= kLookahead && !issue_pv()) { ok = false; break; }
             }
-            for (int j = max(0, n_tiles - kLookahead); j < n_tiles && ok; ++j)
-                if (!issue_pv(j)) ok = false;
+            while (ok && pv_issued < n_tiles)
+                if (!issue_pv()) ok = false;
             if (!ok) { atomicExch(a.status, kDevWaitMma); *abort_flag = 1; }
         }
     } else {
