@@ -89,7 +89,7 @@ def load() -> C.CDLL:
     """Loads the in-tree CUDA library; raises if it is missing (there is no fallback)."""
     global _lib
     if _lib is None:
-        path = _build.LIB_PATH
+        path = os.environ.get("XORNET_ATTN_LIB") or _build.LIB_PATH  # override: a tuning build
         if not os.path.exists(path):
             raise RuntimeError(
                 f"{path} is missing: build it with __graft_entry__.build() "

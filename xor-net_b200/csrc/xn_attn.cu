@@ -157,11 +157,13 @@ struct SplitKernel {
     SplitFn fn;
     size_t smem;
     int threads;
+    int tile_tokens;
 };
 
 template <int NV, int GT>
 SplitKernel make_split() {
-    return {attn_splitkv_kernel<NV, GT>, DecodeSmem<NV, GT>::kBytes, DecodeCfg<NV>::kThreads};
+    return {attn_splitkv_kernel<NV, GT>, DecodeSmem<NV, GT>::kBytes, DecodeCfg<NV>::kThreads,
+            DecodeCfg<NV>::kTPS};
 }
 
 template <int NV>
@@ -728,7 +730,7 @@ int32_t xn_ctx_create(const xn_ctx_desc* d, xn_ctx** out_ctx) {
     c->nv = (d->head_dim + 3) / 4;
     c->nv_class = nv_class_for(c->nv);
     c->nv_exact = c->nv_class == c->nv;
-    c->tile_tokens = (c->nv_class <= 32) ? 64 : 32;
+    c->tile_tokens = pick_split(c->nv_class, c->gt).tile_tokens;
     c->scale = 1.0f / sqrtf(float(d->head_dim));  // fast_attention.rs:135
     c->max_pos = d->max_pos;
     c->prefill_mode = d->prefill_mode;
@@ -739,7 +741,7 @@ int32_t xn_ctx_create(const xn_ctx_desc* d, xn_ctx** out_ctx) {
         int v = atoi(env);
         if (v > 0) c->decode_ctas = v;
     }
-    int chunks_per_cta = 4;
+    int chunks_per_cta = 1;  // more chunks = dynamic balancing, at the cost of more cut units
     if (const char* env = getenv("XORNET_ATTN_DECODE_CHUNKS_PER_CTA")) {
         int v = atoi(env);
         if (v > 0) chunks_per_cta = v;
@@ -811,7 +813,7 @@ int32_t xn_ctx_create(const xn_ctx_desc* d, xn_ctx** out_ctx) {
         if (d->head_dim % 4 == 0 && d->head_dim >= 16 && d->head_dim <= 128 && rows < (1ull << 31)) {
             const cuuint64_t dims[2] = {cuuint64_t(d->head_dim), cuuint64_t(rows)};
             const cuuint64_t str[1] = {cuuint64_t(d->head_dim) * 4};
-            const cuuint32_t box[2] = {32, cuuint32_t(pf::kBN)};
+            const cuuint32_t box[2] = {32, cuuint32_t(pf::kPage)};
             c->tf32_ok = make_map_f32(&c->k_map, c->k_pool, 2, dims, str, box) &&
                          // V is consumed MN-major: 32-byte-chunk swizzle
                          make_map_f32(&c->v_map, c->v_pool, 2, dims, str, box,

@@ -23,18 +23,26 @@
 
 namespace xn {
 
+// Tokens per stage and ring depth for head dims up to 128 (build-time knobs for tuning).
+#ifndef XN_DECODE_TPS
+#define XN_DECODE_TPS 64
+#endif
+#ifndef XN_DECODE_STAGES
+#define XN_DECODE_STAGES 3
+#endif
+
 template <int NV>
 struct DecodeCfg {
     static constexpr int kWarps = 8;                      // consumer warps
     static constexpr int kThreads = (kWarps + 1) * 32;    // + 1 producer warp
     static constexpr int kLPK = (NV <= 32) ? 8 : 16;      // lanes sharing one key in q.k
     static constexpr int kKPI = 32 / kLPK;                // keys per warp iteration
-    static constexpr int kTPS = (NV <= 32) ? 64 : 32;     // tokens per stage
+    static constexpr int kTPS = (NV <= 32) ? XN_DECODE_TPS : 32;  // tokens per stage
     static constexpr int kKPW = kTPS / kWarps;            // keys per warp per stage
     static constexpr int kIters = kKPW / kKPI;
     static constexpr int kSlotsQ = (NV + kLPK - 1) / kLPK;  // float4 of q per lane per head
     static constexpr int kSlotsV = (NV + 31) / 32;          // float4 of output per lane per head
-    static constexpr int kStages = 3;
+    static constexpr int kStages = (NV <= 32) ? XN_DECODE_STAGES : 3;
     static constexpr int kStageFloats = 2 * kTPS * NV * 4;  // K block then V block
     static_assert(kIters >= 1, "tile too small for the warp layout");
 };

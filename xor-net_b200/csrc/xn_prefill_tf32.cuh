@@ -6,22 +6,23 @@
 // bound `limit = index_pos + t_q` (:162) becomes "key tiles above the diagonal are never issued,
 // the diagonal tile is masked element-wise".
 //
-// One thread block = one (query head, 128-row query tile).  Key/value tiles are the cache's
-// 64-token pages.  Tensor memory (512 columns): Q [0,128) | four S/P buffers [128,384) |
-// O [384,512).  Roles (192 threads):
-//   warp 0      TMA producer: tensor-map loads of K pages (4 stages, 128-byte swizzle) and V
-//               pages (3 stages, 128-byte swizzle of 32-byte chunks) with mbarrier byte counts;
-//               K runs two tiles ahead of V, the order in which the MMA warp consumes them;
-//   warp 1      MMA issuer (one lane): S_j = Q K_j^T with Q read from tensor memory, issued two
-//               tiles ahead of O += P_j V_j, which reads P from tensor memory (P overwrites S_j
+// One thread block = one (query head, 128-row query tile).  A score tile spans 128 keys = two of
+// the cache's 64-token pages (a tcgen05.mma of this kind costs the same for N = 64 and N = 128).
+// Tensor memory (512 columns): Q [0,128) | two S/P buffers [128,384) | O [384,512).
+// Roles (320 threads):
+//   warp 0      TMA producer: tensor-map loads of K tiles (2 stages of 2 pages, 128-byte swizzle)
+//               and V pages (3 stages, 128-byte swizzle of 32-byte chunks), mbarrier byte counts;
+//   warp 1      MMA issuer (one lane): S_j = Q K_j^T with Q read from tensor memory, issued one
+//               tile ahead of O += P_j V_j, which reads P from tensor memory (P overwrites S_j
 //               in place) and V MN-major straight from its [token][dim] page; tcgen05.commit
 //               signals the mbarriers;
-//   warps 2..5  thread r owns query row r.  Prologue: the row of Q goes global -> registers ->
-//               tensor memory (rounded to TF32).  Per tile: tcgen05.ld of the S row (the next
-//               tile's load is issued before this tile's arithmetic), causal mask, running
-//               max / sum, exp2 with the softmax scale folded into one FMA, P written back with
-//               tcgen05.st and published one tile later.  The accumulator is rescaled lazily:
-//               only when a row's maximum grows by more than 2^8.  Epilogue: O / l to global.
+//   warps 2..9  two softmax warpgroups; thread r of each owns query row r, warpgroup 0 the first
+//               page of every score tile, warpgroup 1 the second.  Prologue: Q goes global ->
+//               registers -> tensor memory (rounded to TF32).  Per tile: tcgen05.ld of the S
+//               row, causal mask, row maximum exchanged between the two warpgroups through
+//               shared memory, exp2 with the softmax scale folded into one FMA, P written back
+//               with tcgen05.st.  The accumulator is rescaled lazily: only when a row's maximum
+//               grows by more than 2^8.  Epilogue: O / l to global.
 // Every wait is bounded; on expiry the kernel records a status code, drains and returns.
 #pragma once
 #include <cuda.h>
@@ -52,20 +53,22 @@ struct PrefillArgs {
 namespace pf {
 
 constexpr int kBM = 128;          // query rows per block
-constexpr int kBN = 64;           // keys per tile (= page)
+constexpr int kPage = 64;         // tokens per cache page
+constexpr int kBN = 128;          // keys per score tile (= 2 pages): N of the S = Q K^T MMA
 constexpr int kKB = 4;            // 32-float (128-byte) column blocks per row, at most
-constexpr int kKVSub = kBN * 128; // bytes of one K/V column block [64 rows x 128 B]
-constexpr int kKVBytes = kKB * kKVSub;   // 32 KB
-constexpr int kKStages = 4;       // K pages in flight
+constexpr int kKSub = kBN * 128;  // bytes of one K column block   [128 rows x 128 B]
+constexpr int kVSub = kPage * 128;// bytes of one V column block   [64 rows x 128 B]
+constexpr int kKBytes = kKB * kKSub;     // 64 KB per K tile
+constexpr int kVBytes = kKB * kVSub;     // 32 KB per V page
+constexpr int kKStages = 2;       // K tiles in flight
 constexpr int kVStages = 3;       // V pages in flight
-constexpr int kSBufs = 4;         // score / probability buffers in tensor memory
-constexpr int kLookahead = 2;     // S_j is issued this many tiles before O += P V of tile j
-constexpr int kSmemData = (kKStages + kVStages) * kKVBytes;  // 224 KB
-constexpr int kSmemBytes = kSmemData + 1024 /* alignment slack */ + 256 /* barriers */;
-constexpr int kThreads = 192;
+constexpr int kSBufs = 2;         // score / probability buffers in tensor memory
+constexpr int kSmemData = kKStages * kKBytes + kVStages * kVBytes;  // 224 KB
+constexpr int kSmemBytes = kSmemData + 1024 /* alignment slack */ + 2048 /* barriers, exchange */;
+constexpr int kThreads = 320;     // TMA warp, MMA warp, two softmax warpgroups
 constexpr int kTmemCols = 512;
 constexpr int kTmemQ = 0;         // 128 columns
-constexpr int kTmemS = 128;       // kSBufs x 64 columns
+constexpr int kTmemS = 128;       // kSBufs x 128 columns
 constexpr int kTmemO = 384;       // 128 columns
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
@@ -155,23 +158,6 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
 }
 
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-// Same wait, written so that the compiler sees the 64 registers of an earlier, still in-flight
-// pair of loads as produced here: nothing may read or copy them before this point.
-__device__ __forceinline__ void tmem_wait_ld_into(uint32_t (&x)[32], uint32_t (&y)[32]) {
-    asm volatile(
-        "tcgen05.wait::ld.sync.aligned;"
-        : "+r"(x[0]), "+r"(x[1]), "+r"(x[2]), "+r"(x[3]), "+r"(x[4]), "+r"(x[5]), "+r"(x[6]), "+r"(x[7]),
-          "+r"(x[8]), "+r"(x[9]), "+r"(x[10]), "+r"(x[11]), "+r"(x[12]), "+r"(x[13]), "+r"(x[14]),
-          "+r"(x[15]), "+r"(x[16]), "+r"(x[17]), "+r"(x[18]), "+r"(x[19]), "+r"(x[20]), "+r"(x[21]),
-          "+r"(x[22]), "+r"(x[23]), "+r"(x[24]), "+r"(x[25]), "+r"(x[26]), "+r"(x[27]), "+r"(x[28]),
-          "+r"(x[29]), "+r"(x[30]), "+r"(x[31]), "+r"(y[0]), "+r"(y[1]), "+r"(y[2]), "+r"(y[3]),
-          "+r"(y[4]), "+r"(y[5]), "+r"(y[6]), "+r"(y[7]), "+r"(y[8]), "+r"(y[9]), "+r"(y[10]),
-          "+r"(y[11]), "+r"(y[12]), "+r"(y[13]), "+r"(y[14]), "+r"(y[15]), "+r"(y[16]), "+r"(y[17]),
-          "+r"(y[18]), "+r"(y[19]), "+r"(y[20]), "+r"(y[21]), "+r"(y[22]), "+r"(y[23]), "+r"(y[24]),
-          "+r"(y[25]), "+r"(y[26]), "+r"(y[27]), "+r"(y[28]), "+r"(y[29]), "+r"(y[30]), "+r"(y[31])
-        :
-        : "memory");
-}
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 __device__ __forceinline__ float ex2(float x) {
@@ -184,12 +170,6 @@ __device__ __forceinline__ float ex2(float x) {
 // mantissa bits, so adding half an ulp of the kept part to the bit pattern rounds the magnitude.
 __device__ __forceinline__ uint32_t round_tf32(uint32_t bits) { return bits + 0x1000u; }
 
-// State one softmax thread carries across tiles.
-struct RowState {
-    float m_ref;   // reference maximum (scaled, log2 domain) the stored probabilities use
-    float l_sum;   // running sum of probabilities
-};
-
 }  // namespace pf
 
 __global__ void __launch_bounds__(pf::kThreads, 1)
@@ -201,7 +181,7 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap k_map,
     unsigned char* smem = reinterpret_cast<unsigned char*>(
         (reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
     unsigned char* k_s = smem;
-    unsigned char* v_s = k_s + kKStages * kKVBytes;
+    unsigned char* v_s = k_s + kKStages * kKBytes;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kSmemData);
     uint64_t* q_ready = bars + 0;
     uint64_t* k_full = bars + 1;                 // [kKStages]
@@ -213,6 +193,8 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap k_map,
     uint64_t* pv_done = p_full + kSBufs;         // [kSBufs]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + kSBufs);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);
+    volatile int* sm_dead = abort_flag + 1;  // written and read by the softmax warps only
+    float* xchg = reinterpret_cast<float*>(bars + 32);  // [2 warpgroups][128 rows]
     static_assert((1 + 2 * kKStages + 2 * kVStages + 3 * kSBufs) * 8 + 16 <= 256, "barrier area");
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -222,14 +204,15 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap k_map,
     const int h_kv = h / a.group;
     const int t0 = qt * kBM;
     const int last_row = min(t0 + kBM, a.seq_len) - 1;
-    const int n_tiles = (a.index_pos + last_row) / kBN + 1;
+    const int n_pages = (a.index_pos + last_row) / kPage + 1;  // cache pages this block reads
+    const int n_tiles = (n_pages + 1) / 2;                     // 128-key score tiles
     const int D = a.head_dim;
     const int n_kb = (D + 31) / 32;        // column blocks actually loaded
     const int k_steps = (D + 7) / 8;       // K=8 MMA steps over head_dim
     const int n_pv = (D + 15) / 16 * 16;   // N of the PV MMA
 
     if (tid == 0) {
-        mbar_init(q_ready, 128);
+        mbar_init(q_ready, 256);
         for (int s = 0; s < kKStages; ++s) {
             mbar_init(&k_full[s], 1);
             mbar_init(&k_empty[s], 1);
@@ -240,10 +223,11 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap k_map,
         }
         for (int s = 0; s < kSBufs; ++s) {
             mbar_init(&s_full[s], 1);
-            mbar_init(&p_full[s], 128);
+            mbar_init(&p_full[s], 256);
             mbar_init(&pv_done[s], 1);
         }
         *abort_flag = 0;
+        *sm_dead = 0;
         mbar_fence_init();
     }
     if (warp == 1) {
@@ -263,119 +247,135 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap k_map,
 
     if (warp == 0) {
         // =============================== TMA producer ===============================
+        // Order of issue = order of consumption by the MMA warp: K tile j+1 is wanted before the
+        // V pages of tile j.
         if (lane == 0) {
-            for (int t = 0; t < n_tiles + kLookahead; ++t) {
-                if (t < n_tiles) {
-                    const int st = t % kKStages;
-                    const long long row = ((a.layer_page_base + a.pages[t]) * a.num_kv_heads + h_kv) * kBN;
-                    if (t >= kKStages && !mbar_wait_bounded(&k_empty[st], uint32_t((t / kKStages - 1) & 1))) {
-                        atomicExch(a.status, kDevWaitEmpty); *abort_flag = 1; break;
-                    }
-                    mbar_arrive_expect_tx(&k_full[st], uint32_t(n_kb) * kKVSub);
+            auto page_row = [&](int pg) -> int {
+                return int(((a.layer_page_base + a.pages[pg]) * a.num_kv_heads + h_kv) * kPage);
+            };
+            auto load_k_tile = [&](int j) -> bool {
+                const int st = j % kKStages;
+                if (j >= kKStages && !mbar_wait_bounded(&k_empty[st], uint32_t((j / kKStages - 1) & 1))) return false;
+                const int np = min(2, n_pages - 2 * j);
+                mbar_arrive_expect_tx(&k_full[st], uint32_t(np * n_kb) * kVSub);
+                for (int p = 0; p < np; ++p) {
+                    const int row = page_row(2 * j + p);
                     for (int kb = 0; kb < n_kb; ++kb)
-                        tma_load_2d(k_s + st * kKVBytes + kb * kKVSub, &k_map, kb * 32, int(row), &k_full[st]);
+                        tma_load_2d(k_s + st * kKBytes + kb * kKSub + p * kVSub, &k_map, kb * 32, row, &k_full[st]);
                 }
-                const int jv = t - kLookahead;
-                if (jv >= 0) {
-                    const int st = jv % kVStages;
-                    const long long row = ((a.layer_page_base + a.pages[jv]) * a.num_kv_heads + h_kv) * kBN;
-                    if (jv >= kVStages && !mbar_wait_bounded(&v_empty[st], uint32_t((jv / kVStages - 1) & 1))) {
-                        atomicExch(a.status, kDevWaitEmpty); *abort_flag = 1; break;
-                    }
-                    mbar_arrive_expect_tx(&v_full[st], uint32_t(n_kb) * kKVSub);
-                    for (int kb = 0; kb < n_kb; ++kb)
-                        tma_load_2d(v_s + st * kKVBytes + kb * kKVSub, &v_map, kb * 32, int(row), &v_full[st]);
-                }
+                return true;
+            };
+            auto load_v_page = [&](int pg) -> bool {
+                const int st = pg % kVStages;
+                if (pg >= kVStages && !mbar_wait_bounded(&v_empty[st], uint32_t((pg / kVStages - 1) & 1))) return false;
+                const int row = page_row(pg);
+                mbar_arrive_expect_tx(&v_full[st], uint32_t(n_kb) * kVSub);
+                for (int kb = 0; kb < n_kb; ++kb)
+                    tma_load_2d(v_s + st * kVBytes + kb * kVSub, &v_map, kb * 32, row, &v_full[st]);
+                return true;
+            };
+            bool ok = load_k_tile(0);
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                if (j + 1 < n_tiles) ok = load_k_tile(j + 1);
+                for (int p = 2 * j; p < min(2 * j + 2, n_pages) && ok; ++p) ok = load_v_page(p);
                 if (*abort_flag) break;
             }
+            if (!ok) { atomicExch(a.status, kDevWaitEmpty); *abort_flag = 1; }
         }
     } else if (warp == 1) {
         // =============================== MMA issuer ===============================
         // One lane issues every tcgen05.mma of the block, so its instruction stream is kept
         // short: descriptors are a constant plus a small offset, ring positions and mbarrier
         // parities are carried as counters, and the head_dim = 128 loops are fully unrolled.
+        // A tcgen05.mma of this kind costs about the same for N = 64 and N = 128, which is why
+        // the score tile spans two pages.
         if (lane == 0) {
             const uint32_t idesc_qk = make_idesc(kBM, kBN, 0);
             const uint32_t idesc_pv = make_idesc(kBM, n_pv, 1);
-            // descriptor of stage 0; a stage is kKVBytes further, offsets are in 16-byte units
+            // descriptors of stage 0; offsets are in 16-byte units
             const uint64_t kdesc0 = smem_desc(smem_u32(k_s), 0, 1024, kLayoutSw128);
-            const uint64_t vdesc0 = smem_desc(smem_u32(v_s), kKVSub, 512, kLayoutSw128Base32);
-            constexpr uint64_t kStageStep = uint64_t(kKVBytes) >> 4;
-            constexpr uint64_t kBlockStep = uint64_t(kKVSub) >> 4;  // next 32-float column block
+            const uint64_t vdesc0 = smem_desc(smem_u32(v_s), kVSub, 512, kLayoutSw128Base32);
+            constexpr uint64_t kKStageStep = uint64_t(kKBytes) >> 4;
+            constexpr uint64_t kVStageStep = uint64_t(kVBytes) >> 4;
+            constexpr uint64_t kKBlockStep = uint64_t(kKSub) >> 4;  // next 32-float column block
             bool ok = mbar_wait_bounded(q_ready, 0);
             if (!ok) { atomicExch(a.status, kDevWaitFull); *abort_flag = 1; }
             fence_after_sync();
 
             int k_st = 0, k_ph = 0;     // K ring position / parity of the next S = Q K^T
-            int s_qk = 0;               // score buffer of the next S = Q K^T
-            int v_st = 0, v_ph = 0;     // V ring position / parity of the next O += P V
-            int s_pv = 0, p_ph = 0;     // score buffer / parity of the next O += P V
-            int pv_issued = 0;
+            int v_st = 0, v_ph = 0;     // V ring position / parity of the next page of O += P V
+            int pv_issued = 0;          // tiles whose O += P V has been issued
 
-            auto issue_qk = [&]() -> bool {
+            auto issue_qk = [&](int j) -> bool {
                 if (!mbar_wait_bounded(&k_full[k_st], uint32_t(k_ph))) return false;
                 fence_after_sync();
-                const uint64_t kd = kdesc0 + uint64_t(k_st) * kStageStep;
-                const uint32_t d_addr = tmem_s + s_qk * kBN;
+                const uint64_t kd = kdesc0 + uint64_t(k_st) * kKStageStep;
+                const uint32_t d_addr = tmem_s + (j & 1) * kBN;
                 if (k_steps == 16) {
 #pragma unroll
                     for (int ks = 0; ks < 16; ++ks)
-                        mma_ts(d_addr, tmem_q + ks * 8, kd + (ks >> 2) * kBlockStep + (ks & 3) * 2, idesc_qk,
+                        mma_ts(d_addr, tmem_q + ks * 8, kd + (ks >> 2) * kKBlockStep + (ks & 3) * 2, idesc_qk,
                                ks > 0 ? 1u : 0u);
                 } else {
                     for (int ks = 0; ks < k_steps; ++ks)
-                        mma_ts(d_addr, tmem_q + ks * 8, kd + (ks >> 2) * kBlockStep + (ks & 3) * 2, idesc_qk,
+                        mma_ts(d_addr, tmem_q + ks * 8, kd + (ks >> 2) * kKBlockStep + (ks & 3) * 2, idesc_qk,
                                ks > 0 ? 1u : 0u);
                 }
                 mma_commit(&k_empty[k_st]);
-                mma_commit(&s_full[s_qk]);
+                mma_commit(&s_full[j & 1]);
                 if (++k_st == kKStages) { k_st = 0; k_ph ^= 1; }
-                s_qk = (s_qk + 1) & (kSBufs - 1);
                 return true;
             };
-            // O += P_j V_j.  V is [token][dim]: MN-major B; 8 tokens = 1024 B inside each column
-            // block, column blocks kKVSub apart (leading offset), 4-token swizzle groups 512 B apart
-            auto issue_pv = [&]() -> bool {
-                if (!mbar_wait_bounded(&p_full[s_pv], uint32_t(p_ph)) ||
-                    !mbar_wait_bounded(&v_full[v_st], uint32_t(v_ph)))
-                    return false;
-                fence_after_sync();
-                const uint64_t vd = vdesc0 + uint64_t(v_st) * kStageStep;
-                const uint32_t p_addr = tmem_s + s_pv * kBN;
-                const uint32_t first = pv_issued > 0 ? 1u : 0u;
+            // O += P_j V_j, one page (64 keys, 8 MMAs) at a time.  V is [token][dim]: MN-major B;
+            // 8 tokens = 1024 B inside each column block, column blocks kVSub apart (leading
+            // offset), 4-token swizzle groups 512 B apart (stride offset).
+            auto issue_pv = [&](int j) -> bool {
+                if (!mbar_wait_bounded(&p_full[j & 1], uint32_t((j >> 1) & 1))) return false;
+                const int np = min(2, n_pages - 2 * j);
+                for (int p = 0; p < np; ++p) {
+                    if (!mbar_wait_bounded(&v_full[v_st], uint32_t(v_ph))) return false;
+                    fence_after_sync();
+                    const uint64_t vd = vdesc0 + uint64_t(v_st) * kVStageStep;
+                    const uint32_t p_addr = tmem_s + (j & 1) * kBN + p * kPage;
+                    const uint32_t first = (j > 0 || p > 0) ? 1u : 0u;
 #pragma unroll
-                for (int ks = 0; ks < kBN / 8; ++ks)
-                    mma_ts(tmem_o, p_addr + ks * 8, vd + ks * 64, idesc_pv, ks > 0 ? 1u : first);
-                mma_commit(&v_empty[v_st]);
-                mma_commit(&pv_done[s_pv]);
-                if (++v_st == kVStages) { v_st = 0; v_ph ^= 1; }
-                if (++s_pv == kSBufs) { s_pv = 0; p_ph ^= 1; }
+                    for (int ks = 0; ks < kPage / 8; ++ks)
+                        mma_ts(tmem_o, p_addr + ks * 8, vd + ks * 64, idesc_pv, ks > 0 ? 1u : first);
+                    mma_commit(&v_empty[v_st]);
+                    if (++v_st == kVStages) { v_st = 0; v_ph ^= 1; }
+                }
+                mma_commit(&pv_done[j & 1]);
                 ++pv_issued;
                 return true;
             };
-            static_assert((kSBufs & (kSBufs - 1)) == 0, "score buffers: power of two");
             for (int j = 0; j < n_tiles && ok; ++j) {
-                if (!issue_qk()) { ok = false; break; }
-                if (j >= kLookahead && !issue_pv()) { ok = false; break; }
+                if (!issue_qk(j)) { ok = false; break; }
+                if (j >= 1 && !issue_pv(j - 1)) { ok = false; break; }
             }
-            while (ok && pv_issued < n_tiles)
-                if (!issue_pv()) ok = false;
+            if (ok && !issue_pv(n_tiles - 1)) ok = false;
             if (!ok) { atomicExch(a.status, kDevWaitMma); *abort_flag = 1; }
         }
     } else {
         // =============================== softmax + epilogue ===============================
+        // Two warpgroups; both own all 128 rows (thread r of each = query row r).  Warpgroup 0
+        // handles the first page (columns 0..63) of every score tile, warpgroup 1 the second;
+        // they exchange their row maxima through shared memory so that both scale with the same
+        // reference, and each keeps its own partial row sum.
         constexpr unsigned kFull = 0xffffffffu;
+        const int wg = (warp - 2) >> 2;          // 0 or 1
         const int quarter = warp & 3;            // TMEM lane quarter this warp may touch
         const int r = quarter * 32 + lane;       // query row inside the tile
         const uint32_t lane_base = uint32_t(quarter * 32) << 16;
         const int t = t0 + r;                    // query row inside the request
         const int pq = a.index_pos + t;          // its absolute position
+        const int col0 = wg * kPage;             // this warpgroup's columns of a score tile
+        auto wg_barrier = [&]() { named_bar_sync(1, 256); };
 
-        // ---- prologue: this thread's row of Q -> tensor memory (rounded to TF32) ----
+        // ---- prologue: Q -> tensor memory (rounded to TF32); each warpgroup half of the columns
         {
             const float* qrow = a.q + size_t(h) * a.q_hs + size_t(t) * a.q_ts;
             const bool valid = t < a.seq_len;
-            for (int c0 = 0; c0 < k_steps * 8; c0 += 32) {
+            for (int c0 = col0; c0 < min(col0 + kPage, k_steps * 8); c0 += 32) {
                 uint32_t qv[32];
 #pragma unroll
                 for (int c = 0; c < 32; c += 4) {
@@ -393,74 +393,60 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap k_map,
             mbar_arrive(q_ready);
         }
 
-        RowState st{-INFINITY, 0.f};
+        float m_ref = -INFINITY, l_sum = 0.f;
         bool dead = false;
-        int pending = -1;  // tile whose P is stored but not yet published
-#ifdef XN_PF_TIMING
-        long long tm_pub = 0;
-#endif
-
-        // waits for S_j and starts loading this thread's row of it
-        auto fetch = [&](int j, uint32_t (&x0)[32], uint32_t (&x1)[32]) -> bool {
-            const int sb = j % kSBufs;
-            if (!__all_sync(kFull, mbar_wait_bounded(&s_full[sb], uint32_t((j / kSBufs) & 1)))) return false;
+        for (int j = 0; j < n_tiles; ++j) {
+            const int sb = j & 1;
+            if (!__all_sync(kFull, mbar_wait_bounded(&s_full[sb], uint32_t((j >> 1) & 1)))) dead = true;
+            // all eight warps must take the same exit: agree through a flag only they write
+            if (lane == 0 && dead) { *sm_dead = 1; *abort_flag = 1; }
             fence_after_sync();
-            const uint32_t s_addr = tmem_s + lane_base + sb * kBN;
-            tmem_ld32(s_addr, x0);
-            tmem_ld32(s_addr + 32, x1);
-            return true;
-        };
-        // makes the P of tile `pending` visible to the MMA warp
-        auto publish = [&]() {
-            if (pending >= 0) {
-#ifdef XN_PF_TIMING
-                long long t_p = clock64();
-#endif
-                tmem_wait_st();
-                fence_before_sync();
-                mbar_arrive(&p_full[pending % kSBufs]);
-                pending = -1;
-#ifdef XN_PF_TIMING
-                tm_pub += clock64() - t_p;
-#endif
-            }
-        };
-        // mask, max, (rare) accumulator rescale, probabilities; stores P_j
-        auto process = [&](int j, uint32_t (&x0)[32], uint32_t (&x1)[32]) -> bool {
-            const bool diag = j * kBN + kBN - 1 > a.index_pos + t0;  // some row masks some key here
-            if (diag) {
-#pragma unroll
-                for (int c = 0; c < 32; ++c) {
-                    if (j * kBN + c > pq) x0[c] = 0xff800000u;  // -inf
-                    if (j * kBN + 32 + c > pq) x1[c] = 0xff800000u;
-                }
-            }
-            // raw scores stay unscaled: max commutes with the positive scale, and the scale is
-            // folded into the exponent's fused multiply-add below
+            uint32_t x0[32], x1[32];
+            const uint32_t s_addr = tmem_s + lane_base + sb * kBN + col0;
+            const int key0 = j * kBN + col0;                  // first key of this warpgroup's page
+            const bool have_page = 2 * j + wg < n_pages;      // the tile's second page may not exist
             float mx = -INFINITY;
+            if (!dead && have_page) {
+                tmem_ld32(s_addr, x0);
+                tmem_ld32(s_addr + 32, x1);
+                tmem_wait_ld();
+                if (key0 + kPage - 1 > a.index_pos + t0) {    // some row masks some key here
 #pragma unroll
-            for (int c = 0; c < 32; ++c)
-                mx = fmaxf(mx, fmaxf(__uint_as_float(x0[c]), __uint_as_float(x1[c])));
-            mx *= a.scale_log2;
+                    for (int c = 0; c < 32; ++c) {
+                        if (key0 + c > pq) x0[c] = 0xff800000u;  // -inf
+                        if (key0 + 32 + c > pq) x1[c] = 0xff800000u;
+                    }
+                }
+                // raw scores stay unscaled: max commutes with the positive scale, and the scale
+                // is folded into the exponent's fused multiply-add below
+#pragma unroll
+                for (int c = 0; c < 32; ++c)
+                    mx = fmaxf(mx, fmaxf(__uint_as_float(x0[c]), __uint_as_float(x1[c])));
+                mx *= a.scale_log2;
+            }
+            xchg[wg * 128 + r] = mx;
+            wg_barrier();
+            dead = __any_sync(kFull, *sm_dead != 0);
+            if (dead) break;  // taken by all eight warps: the flag was set before the barrier
+            mx = fmaxf(mx, xchg[(wg ^ 1) * 128 + r]);
             float alpha = 1.f;
             bool need = false;
             if (j == 0) {
-                st.m_ref = mx;  // key 0 is visible to every row, so mx is finite
-            } else if (mx > st.m_ref + kRescaleThreshold) {
-                alpha = ex2(st.m_ref - mx);
-                st.m_ref = mx;
+                m_ref = mx;  // key 0 is visible to every row, so mx is finite
+            } else if (mx > m_ref + kRescaleThreshold) {
+                alpha = ex2(m_ref - mx);
+                m_ref = mx;
                 need = true;
             }
             if (__any_sync(kFull, need)) {
-                // the accumulator must be quiet: publish what is pending, then wait for
-                // O += P_{j-1} V_{j-1}
-                publish();
-                const int sp = (j - 1) % kSBufs;
-                if (!__all_sync(kFull, mbar_wait_bounded(&pv_done[sp], uint32_t(((j - 1) / kSBufs) & 1))))
-                    return false;
+                // the accumulator must be quiet: wait for O += P_{j-1} V_{j-1}; each warpgroup
+                // rescales its half of the columns
+                if (!__all_sync(kFull, mbar_wait_bounded(&pv_done[(j - 1) & 1], uint32_t(((j - 1) >> 1) & 1)))) {
+                    // cannot bail out alone (the other warpgroup may not rescale): record and go on
+                    atomicExch(a.status, kDevWaitMma);
+                }
                 fence_after_sync();
-                st.l_sum *= alpha;
-                for (int c0 = 0; c0 < n_pv; c0 += 32) {
+                for (int c0 = col0; c0 < min(col0 + kPage, n_pv); c0 += 32) {
                     uint32_t o[32];
                     tmem_ld32(tmem_o + lane_base + c0, o);
                     tmem_wait_ld();
@@ -470,69 +456,41 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap k_map,
                 }
                 tmem_wait_st();
             }
-            float psum0 = 0.f, psum1 = 0.f;
-            const float neg_m = -st.m_ref;
+            l_sum *= alpha;
+            if (have_page) {
+                float psum0 = 0.f, psum1 = 0.f;
+                const float neg_m = -m_ref;
 #pragma unroll
-            for (int c = 0; c < 32; ++c) {
-                const float p0 = ex2(fmaf(__uint_as_float(x0[c]), a.scale_log2, neg_m));
-                const float p1 = ex2(fmaf(__uint_as_float(x1[c]), a.scale_log2, neg_m));
-                psum0 += p0;
-                psum1 += p1;
-                x0[c] = round_tf32(__float_as_uint(p0));
-                x1[c] = round_tf32(__float_as_uint(p1));
+                for (int c = 0; c < 32; ++c) {
+                    const float p0 = ex2(fmaf(__uint_as_float(x0[c]), a.scale_log2, neg_m));
+                    const float p1 = ex2(fmaf(__uint_as_float(x1[c]), a.scale_log2, neg_m));
+                    psum0 += p0;
+                    psum1 += p1;
+                    x0[c] = round_tf32(__float_as_uint(p0));
+                    x1[c] = round_tf32(__float_as_uint(p1));
+                }
+                l_sum += psum0 + psum1;
+                tmem_st32(s_addr, x0);
+                tmem_st32(s_addr + 32, x1);
+                tmem_wait_st();
             }
-            st.l_sum += psum0 + psum1;
-            publish();  // the previous tile's P: its stores have long completed
-            const uint32_t s_addr = tmem_s + lane_base + (j % kSBufs) * kBN;
-            tmem_st32(s_addr, x0);
-            tmem_st32(s_addr + 32, x1);
-            pending = j;
-            return true;
-        };
+            fence_before_sync();
+            mbar_arrive(&p_full[sb]);
+            wg_barrier();  // the exchange area is rewritten by the next tile
+        }
+        if (dead && lane == 0) atomicExch(a.status, kDevWaitFull);
 
-#ifdef XN_PF_TIMING
-        long long tm_wait_s = 0, tm_wait_ld = 0, tm_proc = 0, tm_total = clock64();
-#define PF_T0 long long t_0 = clock64();
-#define PF_ACC(var) var += clock64() - t_0;
-#else
-#define PF_T0
-#define PF_ACC(var)
-#endif
-        uint32_t a0[32], a1[32], b0[32], b1[32];
-        if (!fetch(0, a0, a1)) dead = true;
-        for (int j = 0; j < n_tiles && !dead; j += 2) {
-            // tile j lives in (a0,a1); tile j+1 is fetched into (b0,b1) while j is processed
-            { PF_T0 tmem_wait_ld_into(a0, a1); PF_ACC(tm_wait_ld) }
-            { PF_T0 if (j + 1 < n_tiles && !fetch(j + 1, b0, b1)) { dead = true; break; } PF_ACC(tm_wait_s) }
-            { PF_T0 if (!process(j, a0, a1)) { dead = true; break; } PF_ACC(tm_proc) }
-            if (j + 1 >= n_tiles) break;
-            { PF_T0 tmem_wait_ld_into(b0, b1); PF_ACC(tm_wait_ld) }
-            { PF_T0 if (j + 2 < n_tiles && !fetch(j + 2, a0, a1)) { dead = true; break; } PF_ACC(tm_wait_s) }
-            { PF_T0 if (!process(j + 1, b0, b1)) { dead = true; break; } PF_ACC(tm_proc) }
-            if (__any_sync(kFull, *abort_flag != 0)) { dead = true; break; }
-        }
-        if (dead) {
-            atomicExch(a.status, kDevWaitFull);
-            *abort_flag = 1;
-        } else {
-            publish();
-        }
-#ifdef XN_PF_TIMING
-        if (a.timing && blockIdx.x == 0 && blockIdx.y == 0 && tid == 64) {
-            a.timing[0] = n_tiles; a.timing[1] = clock64() - tm_total; a.timing[2] = tm_wait_s;
-            a.timing[3] = tm_wait_ld; a.timing[4] = tm_proc; a.timing[5] = tm_pub;
-        }
-#endif
-
-        // ---- epilogue: O / l -> global
-        const bool aborted = __any_sync(kFull, *abort_flag != 0);  // warp-uniform
-        if (!dead && !aborted) {
+        // ---- epilogue: O / l -> global; each warpgroup its half of the columns
+        if (!dead) {
+            xchg[wg * 128 + r] = l_sum;
+            wg_barrier();
+            const float l_tot = l_sum + xchg[(wg ^ 1) * 128 + r];
             const int jl = n_tiles - 1;
-            if (__all_sync(kFull, mbar_wait_bounded(&pv_done[jl % kSBufs], uint32_t((jl / kSBufs) & 1)))) {
+            if (__all_sync(kFull, mbar_wait_bounded(&pv_done[jl & 1], uint32_t((jl >> 1) & 1)))) {
                 fence_after_sync();
-                const float inv = 1.0f / st.l_sum;
+                const float inv = 1.0f / l_tot;
                 float* orow = a.out + size_t(h) * a.o_hs + size_t(t) * a.o_ts;
-                for (int c0 = 0; c0 < n_pv; c0 += 32) {
+                for (int c0 = col0; c0 < min(col0 + kPage, n_pv); c0 += 32) {
                     uint32_t o[32];
                     tmem_ld32(tmem_o + lane_base + c0, o);
                     tmem_wait_ld();
