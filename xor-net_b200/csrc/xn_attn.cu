@@ -160,26 +160,27 @@ struct SplitKernel {
     int tile_tokens;
 };
 
-template <int NV, int GT>
+template <int NV, int GT, bool EXACT>
 SplitKernel make_split() {
-    return {attn_splitkv_kernel<NV, GT>, DecodeSmem<NV, GT>::kBytes, DecodeCfg<NV>::kThreads,
+    return {attn_splitkv_kernel<NV, GT, EXACT>, DecodeSmem<NV, GT>::kBytes, DecodeCfg<NV>::kThreads,
             DecodeCfg<NV>::kTPS};
 }
 
-template <int NV>
+template <int NV, bool EXACT>
 SplitKernel pick_gt(int gt) {
-    if (gt == 4) return make_split<NV, 4>();
-    if (gt == 2) return make_split<NV, 2>();
-    return make_split<NV, 1>();
+    if (gt == 4) return make_split<NV, 4, EXACT>();
+    if (gt == 2) return make_split<NV, 2, EXACT>();
+    return make_split<NV, 1, EXACT>();
 }
 
-SplitKernel pick_split(int nv_class, int gt) {
+// Exact instantiations exist for the row lengths of head_dim 64, 100, 128 and 256.
+SplitKernel pick_split(int nv_class, int gt, bool exact) {
     switch (nv_class) {
-        case 8: return pick_gt<8>(gt);
-        case 16: return pick_gt<16>(gt);
-        case 25: return pick_gt<25>(gt);
-        case 32: return pick_gt<32>(gt);
-        default: return pick_gt<64>(gt);
+        case 8: return pick_gt<8, false>(gt);
+        case 16: return exact ? pick_gt<16, true>(gt) : pick_gt<16, false>(gt);
+        case 25: return pick_gt<25, true>(gt);
+        case 32: return exact ? pick_gt<32, true>(gt) : pick_gt<32, false>(gt);
+        default: return exact ? pick_gt<64, true>(gt) : pick_gt<64, false>(gt);
     }
 }
 
@@ -542,7 +543,7 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         c->stats.kernel_launches += 1;
     }
     if (sp.ctas > 0) {
-        SplitKernel k = pick_split(c->nv_class, c->gt);
+        SplitKernel k = pick_split(c->nv_class, c->gt, c->nv_exact);
         if (c->profile && (rc = profile_begin(c, 0)) != XN_OK) return rc;
         // sp.ctas chunks, taken dynamically by at most one block per SM
         k.fn<<<std::min(sp.ctas, c->decode_ctas), k.threads, k.smem, c->stream>>>(
@@ -730,7 +731,7 @@ int32_t xn_ctx_create(const xn_ctx_desc* d, xn_ctx** out_ctx) {
     c->nv = (d->head_dim + 3) / 4;
     c->nv_class = nv_class_for(c->nv);
     c->nv_exact = c->nv_class == c->nv;
-    c->tile_tokens = pick_split(c->nv_class, c->gt).tile_tokens;
+    c->tile_tokens = pick_split(c->nv_class, c->gt, c->nv_exact).tile_tokens;
     c->scale = 1.0f / sqrtf(float(d->head_dim));  // fast_attention.rs:135
     c->max_pos = d->max_pos;
     c->prefill_mode = d->prefill_mode;
@@ -802,7 +803,7 @@ int32_t xn_ctx_create(const xn_ctx_desc* d, xn_ctx** out_ctx) {
     *c->status_h = kDevOk;
 
     {
-        SplitKernel k = pick_split(c->nv_class, c->gt);
+        SplitKernel k = pick_split(c->nv_class, c->gt, c->nv_exact);
         XN_CREATE_CUDA(cudaFuncSetAttribute(reinterpret_cast<const void*>(k.fn),
                                             cudaFuncAttributeMaxDynamicSharedMemorySize, int(k.smem)));
     }

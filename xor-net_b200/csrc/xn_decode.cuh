@@ -19,6 +19,8 @@
 //     WARPS consumer warps each own a fixed subset of a tile's tokens and keep an independent
 //     online-softmax state (running max, sum, accumulator) merged once per unit.
 #pragma once
+#include <cstdio>
+
 #include "xn_common.cuh"
 
 namespace xn {
@@ -136,14 +138,18 @@ struct DecodeSmem {
 //                  either the output row (unit in one piece) or a partial record.  The block
 //                  that writes a unit's last missing partial combines all of them (arrival
 //                  counter in `sync`), so no second kernel is needed.
-template <int NV, int GT>
+// EXACT: rows are exactly NV float4 long (nv_arg == NV), which turns every bound check on the
+// row length into a compile-time constant.
+template <int NV, int GT, bool EXACT>
 __global__ void __launch_bounds__(DecodeCfg<NV>::kThreads, 1)
 attn_splitkv_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restrict__ units,
                     const ItemDev* __restrict__ items, const int* __restrict__ chunk_item_begin,
                     int n_chunks, const int* __restrict__ page_ids,
                     const float* __restrict__ k_pool, const float* __restrict__ v_pool,
                     float* __restrict__ partials, int* __restrict__ sync, long long pool_pages,
-                    int num_kv_heads, int head_dim, int nv, float scale, int* __restrict__ status) {
+                    int num_kv_heads, int head_dim, int nv_arg, float scale,
+                    int* __restrict__ status) {
+    const int nv = EXACT ? NV : nv_arg;
     using Cfg = DecodeCfg<NV>;
     using Sm = DecodeSmem<NV, GT>;
     constexpr int W = Cfg::kWarps, LPK = Cfg::kLPK, KPI = Cfg::kKPI, TPS = Cfg::kTPS;
@@ -319,10 +325,22 @@ attn_splitkv_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restrict__
     float4 qreg[GT][SQ];
     float4 acc[GT][SV];
     float m_run = -INFINITY, l_run = 0.f;
+#ifdef XN_DECODE_TIMING
+    long long tm_wait = 0, tm_qk = 0, tm_sm = 0, tm_pv = 0, tm_merge = 0, tm_start = clock64(), tm_t = 0;
+    int tm_tiles = 0, tm_items = 0;
+#define DT_BEGIN tm_t = clock64();
+#define DT_END(v) v += clock64() - tm_t;
+#else
+#define DT_BEGIN
+#define DT_END(v)
+#endif
 
     for (int fill = 0;; ++fill) {
         const int s = fill % ST;
-        if (!__all_sync(kFull, mbar_wait_bounded(&full_bar[s], (fill / ST) & 1))) {
+        DT_BEGIN
+        const bool got = __all_sync(kFull, mbar_wait_bounded(&full_bar[s], (fill / ST) & 1));
+        DT_END(tm_wait)
+        if (!got) {
             atomicExch(status, kDevWaitFull);
             *abort_flag = 1;
             break;  // the producer notices the flag or runs into its own bounded wait
@@ -331,6 +349,9 @@ attn_splitkv_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restrict__
         // same tile, or the block-wide barriers of the merge below would lose a participant)
         const StageHdr h = hdr[s];
         if (h.flags & kHdrEnd) break;
+#ifdef XN_DECODE_TIMING
+        ++tm_tiles;
+#endif
         const float4* Ks = reinterpret_cast<const float4*>(stage_ptr(s));
         const float4* Vs = Ks + TPS * NV;
 
@@ -367,6 +388,7 @@ attn_splitkv_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restrict__
 
         {
             const int ntok = h.ntok;
+            DT_BEGIN
             // ---- scores for this warp's keys ----
             float sc[ITERS];
             float bm = -INFINITY;
@@ -398,6 +420,8 @@ attn_splitkv_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restrict__
             }
 #pragma unroll
             for (int o = LPK; o < 32; o <<= 1) bm = fmaxf(bm, __shfl_xor_sync(kFull, bm, o));
+            DT_END(tm_qk)
+            DT_BEGIN
 
             const float m_new = fmaxf(m_run, bm);
             const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
@@ -430,35 +454,43 @@ attn_splitkv_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restrict__
                     }
             }
 
+            DT_END(tm_sm)
+            DT_BEGIN
             // ---- weighted V rows of the same keys ----
+            // No branch per key: a key beyond the tile's end has p = 0 and is pointed at the
+            // tile's first row (always valid data of this unit), never at stale shared memory.
 #pragma unroll
             for (int kk = 0; kk < KPW; ++kk) {
                 const int key = (kk / KPI) * (W * KPI) + cw * KPI + (kk % KPI);
-                if (key < ntok) {
-                    float pv[GT];
+                const int key_c = key < ntok ? key : 0;
+                float pv[GT];
 #pragma unroll
-                    for (int hh = 0; hh < GT; ++hh) pv[hh] = my_scr[kk * GT + hh];
-                    const float4* vrow = Vs + size_t(key) * nv;
+                for (int hh = 0; hh < GT; ++hh) pv[hh] = my_scr[kk * GT + hh];
+                const float4* vrow = Vs + size_t(key_c) * nv;
 #pragma unroll
-                    for (int sv = 0; sv < SV; ++sv) {
-                        const int idx = lane + 32 * sv;
-                        if (idx < nv) {
-                            const float4 vv = vrow[idx];
+                for (int sv = 0; sv < SV; ++sv) {
+                    const int idx = lane + 32 * sv;
+                    if (idx < nv) {
+                        const float4 vv = vrow[idx];
 #pragma unroll
-                            for (int hh = 0; hh < GT; ++hh) {
-                                acc[hh][sv].x = fmaf(pv[hh], vv.x, acc[hh][sv].x);
-                                acc[hh][sv].y = fmaf(pv[hh], vv.y, acc[hh][sv].y);
-                                acc[hh][sv].z = fmaf(pv[hh], vv.z, acc[hh][sv].z);
-                                acc[hh][sv].w = fmaf(pv[hh], vv.w, acc[hh][sv].w);
-                            }
+                        for (int hh = 0; hh < GT; ++hh) {
+                            acc[hh][sv].x = fmaf(pv[hh], vv.x, acc[hh][sv].x);
+                            acc[hh][sv].y = fmaf(pv[hh], vv.y, acc[hh][sv].y);
+                            acc[hh][sv].z = fmaf(pv[hh], vv.z, acc[hh][sv].z);
+                            acc[hh][sv].w = fmaf(pv[hh], vv.w, acc[hh][sv].w);
                         }
                     }
                 }
             }
         }
         __syncwarp();
+        DT_END(tm_pv)
         if (lane == 0) mbar_arrive(&empty_bar[s]);
         if (!(h.flags & kHdrLast)) continue;
+        DT_BEGIN
+#ifdef XN_DECODE_TIMING
+        ++tm_items;
+#endif
 
         // ---- last tile of the item: merge the W warp states ----
         float l_tot = l_run;
@@ -525,7 +557,7 @@ attn_splitkv_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restrict__
                 reinterpret_cast<float4*>(rec + 4)[idx] = sum;
             }
         }
-        if (h.part < 0) continue;
+        if (h.part < 0) { DT_END(tm_merge) continue; }
 
         // ---- the unit was cut: whoever delivers its last partial combines them all ----
         // (block barrier, then one thread fences and counts: the fence is cumulative over the
@@ -571,7 +603,14 @@ attn_splitkv_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restrict__
             }
         }
         named_bar_sync(1, W * 32);  // last_flag and red are reused by the next item
+        DT_END(tm_merge)
     }
+#ifdef XN_DECODE_TIMING
+    if ((blockIdx.x == 0 || blockIdx.x == 77) && tid == 32 && tm_tiles > 8)
+        printf("block %d: %d tiles %d items, total %lld clk (%lld/tile): wait %lld qk %lld softmax %lld pv %lld per tile; merge %lld per item\n",
+               blockIdx.x, tm_tiles, tm_items, clock64() - tm_start, (clock64() - tm_start) / tm_tiles, tm_wait / tm_tiles,
+               tm_qk / tm_tiles, tm_sm / tm_tiles, tm_pv / tm_tiles, tm_items ? tm_merge / tm_items : 0);
+#endif
 }
 
 // Generic attention for requests whose positions fold around the ring (index_pos + seq_len >
