@@ -395,7 +395,9 @@ def run_gpu_arm(args):
         return out
 
     dev_batches = batches(q_d, k_d, v_d, o_d, xn.REQ_DEVICE_PTRS)
-    host_batches = batches(q_h, k_h, v_h, o_h, 0)
+    # host buffers are page-locked: the kernels move them over PCIe themselves
+    host_batches = batches(q_h, k_h, v_h, o_h, xn.REQ_HOST_PINNED)
+    staged_batches = batches(q_h, k_h, v_h, o_h, 0)  # same buffers treated as pageable
 
     def step_device():
         for b in dev_batches:
@@ -403,6 +405,10 @@ def run_gpu_arm(args):
 
     def step_host():
         for b in host_batches:
+            ctx.submit(b)
+
+    def step_staged():
+        for b in staged_batches:
             ctx.submit(b)
 
     def barrier():
@@ -451,8 +457,18 @@ def run_gpu_arm(args):
     barrier()
     e2e_wall_ms = (time.perf_counter() - t0) * 1e3
     e2e_ms = max(e0.elapsed_time(e1), 0.0)
-    # the host-side staging is part of the call: the wall clock is the honest end-to-end time
+    # the host side of the call is part of it: the wall clock is the honest end-to-end time
     e2e_ms = max(e2e_ms, e2e_wall_ms)
+    # the same through the library's own staging copies (what a caller with pageable memory gets)
+    staged_ms = 0.0
+    if e2e_steps:
+        step_staged()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            step_staged()
+        barrier()
+        staged_ms = (time.perf_counter() - t0) * 1e3
 
     # job-wide figures: slowest rank's time, all ranks' bytes (no-op in a single process)
     (ms, e2e_ms, kern_avg_ms), (total_bytes_per_step,) = xn.sharding.aggregate(
@@ -485,7 +501,10 @@ def run_gpu_arm(args):
                     "d2h_bytes_per_step": layers * q_elems * 4,
                     "ms_per_step": e2e_ms / max(e2e_steps, 1),
                     "tokens_per_s": n_streams * world * e2e_steps / (e2e_ms * 1e-3),
-                    "api": "xn_attention_batch with host pointers, one blocking call per layer"},
+                    "api": "xn_attention_batch, page-locked host pointers (XN_REQ_HOST_PINNED), one "
+                           "blocking call per layer",
+                    "staged_ms_per_step": staged_ms / max(e2e_steps, 1),
+                    "staged_value": (bytes_per_step * e2e_steps / (staged_ms * 1e-3) / 1e9) if staged_ms else None},
             "gpu_launches": int(launches),
             "roofline": {"bound": "hbm", "kernel": "attn_splitkv_kernel<32,4>",
                          "achieved": achieved, "peak": peak, "unit": "GB/s",

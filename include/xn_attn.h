@@ -88,9 +88,15 @@ typedef struct xn_ctx_desc {
 enum {
     XN_REQ_DEVICE_PTRS = 1u << 0, /* q,k,v,out are device pointers; the call only enqueues work  */
     XN_REQ_ROPE = 1u << 1,        /* q,k are pre-RoPE; rotate with the context's tables          */
-    XN_REQ_SEQ_MAJOR = 1u << 2    /* q,k,v,out are [seq_len, heads*head_dim] (the layout before  */
+    XN_REQ_SEQ_MAJOR = 1u << 2,   /* q,k,v,out are [seq_len, heads*head_dim] (the layout before  */
                                   /* transpose_seq_to_heads, tensor.rs:332-354, and after        */
                                   /* transpose_heads_to_seq, tensor.rs:356-376)                  */
+    XN_REQ_HOST_PINNED = 1u << 3  /* host pointers are page-locked, device-mapped memory         */
+                                  /* (cudaHostAlloc / cudaHostRegister): the kernels read the    */
+                                  /* inputs and write the output over PCIe themselves and the    */
+                                  /* library's staging copies are skipped.  The call still       */
+                                  /* blocks until the output is complete.  All requests of a     */
+                                  /* batch must agree on this flag.                              */
 };
 
 typedef struct xn_req {

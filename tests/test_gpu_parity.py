@@ -297,3 +297,45 @@ def test_shuffled_page_table_is_a_permutation():
     assert abs(float(k.mean())) < 0.02 and abs(float(k.std()) - 1.0) < 0.02
     assert abs(float(v.mean())) < 0.02 and not np.array_equal(k, v)
     ctx.close()
+
+
+def test_pinned_host_buffers_skip_the_staging_copies(ctx2b):
+    # XN_REQ_HOST_PINNED: the kernels read q,k,v from and write out to page-locked host memory
+    # themselves; results must equal the staged host path bit for bit, for decode and prefill
+    import torch
+
+    rng = np.random.default_rng(59)
+    lens = [300, 64, 1500, 1]
+    pairs = [Pair(ctx2b, 2048) for _ in lens]
+    for p, L in zip(pairs, lens):
+        if L > 1:
+            p.step(2, 0, *rand_qkv(rng, 20, 5, L - 1, 128))
+    n = len(lens)
+    q = torch.from_numpy(rng.standard_normal((n, 20, 128)).astype(np.float32)).pin_memory()
+    k = torch.from_numpy(rng.standard_normal((n, 5, 128)).astype(np.float32)).pin_memory()
+    v = torch.from_numpy(rng.standard_normal((n, 5, 128)).astype(np.float32)).pin_memory()
+    out = torch.zeros(n, 20, 128).pin_memory()
+    before = ctx2b.stats()
+    reqs = ctx2b.make_batch([(pairs[i].st, 2, lens[i] - 1, 1, q[i].data_ptr(), k[i].data_ptr(),
+                              v[i].data_ptr(), out[i].data_ptr()) for i in range(n)], xn.REQ_HOST_PINNED)
+    ctx2b.submit(reqs)
+    after = ctx2b.stats()
+    assert after["h2d_bytes"] - before["h2d_bytes"] >= n * 30 * 128 * 4   # counted as moved by the kernels
+    for i, p in enumerate(pairs):
+        want = xo.fast_attention(q[i].numpy().reshape(1, 20, 1, 128), k[i].numpy().reshape(1, 5, 1, 128),
+                                 v[i].numpy().reshape(1, 5, 1, 128), 2, lens[i] - 1, p.ref, 20, 5, 128)
+        assert_parity(out[i].numpy().reshape(1, 20, 1, 128), want, f"pinned stream {i}")
+    # same call again through the staged path at the same positions: identical bits
+    staged = ctx2b.attention_batch([p.st for p in pairs], 2, [L - 1 for L in lens],
+                                   [q[i].numpy().reshape(1, 20, 1, 128) for i in range(n)],
+                                   [k[i].numpy().reshape(1, 5, 1, 128) for i in range(n)],
+                                   [v[i].numpy().reshape(1, 5, 1, 128) for i in range(n)])
+    for i in range(n):
+        assert np.array_equal(staged[i].reshape(20, 128), out[i].numpy())
+    # mixing pinned and staged requests in one batch is rejected
+    reqs[1].flags = 0
+    with pytest.raises(xn.XnError) as e:
+        ctx2b.submit(reqs)
+    assert e.value.code == 1
+    for p in pairs:
+        p.st.destroy()

@@ -8,10 +8,10 @@ from ._build import LIB_PATH, build_library
 from .api import (Context, DeviceKvCache, FastTensor, Stream, XnError, close_default_contexts,
                   default_context, fast_attention, rope_tables)
 from . import sharding
-from ._ffi import REQ_DEVICE_PTRS, REQ_ROPE, REQ_SEQ_MAJOR, SIGNATURES, load
+from ._ffi import REQ_DEVICE_PTRS, REQ_HOST_PINNED, REQ_ROPE, REQ_SEQ_MAJOR, SIGNATURES, load
 
 __all__ = [
     "Context", "Stream", "DeviceKvCache", "FastTensor", "XnError", "fast_attention", "rope_tables",
     "default_context", "close_default_contexts", "build_library", "load", "LIB_PATH", "SIGNATURES",
-    "REQ_DEVICE_PTRS", "REQ_ROPE", "REQ_SEQ_MAJOR", "sharding",
+    "REQ_DEVICE_PTRS", "REQ_ROPE", "REQ_SEQ_MAJOR", "REQ_HOST_PINNED", "sharding",
 ]

@@ -36,7 +36,7 @@ class Stats(C.Structure):
         "coalesced_max")]
 
 
-REQ_DEVICE_PTRS, REQ_ROPE, REQ_SEQ_MAJOR = 1, 2, 4
+REQ_DEVICE_PTRS, REQ_ROPE, REQ_SEQ_MAJOR, REQ_HOST_PINNED = 1, 2, 4, 8
 
 STATUS_NAMES = {
     0: "XN_OK", 1: "XN_ERR_ARG", 2: "XN_ERR_SHAPE", 3: "XN_ERR_HANDLE", 4: "XN_ERR_OUT_OF_PAGES",

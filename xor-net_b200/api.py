@@ -21,7 +21,7 @@ from typing import Optional, Sequence
 import numpy as np
 
 from . import _ffi
-from ._ffi import REQ_DEVICE_PTRS, REQ_ROPE, REQ_SEQ_MAJOR, CtxDesc, Req, Stats
+from ._ffi import REQ_DEVICE_PTRS, REQ_HOST_PINNED, REQ_ROPE, REQ_SEQ_MAJOR, CtxDesc, Req, Stats
 
 
 class XnError(RuntimeError):

@@ -20,7 +20,8 @@ __device__ __forceinline__ size_t slot_offset(const int* pages, long long pool_p
 //     with explicitly unfused multiplies and add/sub so that the stored bits equal the
 //     reference's.
 //   * V rows: plain copy.
-//   * Q rows: rotated into a dense [Hq, S, D] scratch read by the attention kernels.
+//   * Q rows: rotated into a dense [Hq, S, D] scratch read by the attention kernels (also used,
+//     without rotation, to bring queries that live in mapped host memory next to the kernels).
 // When one call carries more new tokens than the ring holds, only the last writer of a slot
 // stores (the reference's sequential loop leaves exactly that value).
 // Rows move as float4 when head_dim is a multiple of 8 and both pointers are 16-byte aligned,
@@ -78,7 +79,8 @@ rope_append_kernel(const ReqDev* __restrict__ reqs, const int* __restrict__ page
                    long long pool_pages, int num_heads, int num_kv_heads, int head_dim, int nv) {
     const ReqDev& r = reqs[blockIdx.y];
     const bool rope = r.flags & 1u;
-    const int rows_per_tok = (rope ? num_heads : 0) + 2 * num_kv_heads;
+    const bool q_rows = r.flags & 3u;  // q is rotated, or just moved next to the kernels
+    const int rows_per_tok = (q_rows ? num_heads : 0) + 2 * num_kv_heads;
     const long long n_rows = (long long)r.seq_len * rows_per_tok;
     const int hl = threadIdx.x & 15;         // lane inside the half-warp
     const int hw = threadIdx.x >> 4;         // half-warp inside the block (16 per block)
@@ -96,13 +98,13 @@ rope_append_kernel(const ReqDev* __restrict__ reqs, const int* __restrict__ page
         const float* src;
         float* dst;
         bool rotate = false;
-        if (rope && rr < num_heads) {
-            // query row -> rotation scratch (ReqDev::q points at it)
+        if (q_rows && rr < num_heads) {
+            // query row -> scratch (ReqDev::q points at it), rotated when the request asks for it
             src = r.q_in + size_t(rr) * r.qi_hs + size_t(t) * r.qi_ts;
             dst = const_cast<float*>(r.q) + size_t(rr) * r.q_hs + size_t(t) * r.q_ts;
-            rotate = true;
+            rotate = rope;
         } else {
-            if (rope) rr -= num_heads;
+            if (q_rows) rr -= num_heads;
             if ((long long)t + r.cap < (long long)r.seq_len) continue;  // overwritten later in this call
             const int slot = pos % r.cap;
             if (rr < num_kv_heads) {

@@ -363,6 +363,8 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
     const int Hq = c->num_heads, Hkv = c->num_kv_heads, D = c->head_dim, nv = c->nv;
     XN_CUDA(c, cudaSetDevice(c->device));
 
+    // host memory that is page-locked and device-mapped is read and written by the kernels directly
+    const bool pinned = host_mode && (reqs[0].flags & XN_REQ_HOST_PINNED);
     // -- pages, gaps, staging sizes
     std::vector<GapFill> gaps;
     size_t io_in = 0, io_out = 0, qrot_floats = 0, n_page_ids = 0;
@@ -381,15 +383,19 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         hw = std::max(hw, end);
         n_page_ids += s->pages.size();
         const size_t qf = size_t(Hq) * r.seq_len * D, kvf = size_t(Hkv) * r.seq_len * D;
-        if (host_mode) {
+        if (host_mode && !pinned) {
             io_in += align_up(qf * 4, 16) + 2 * align_up(kvf * 4, 16);
             io_out += align_up(qf * 4, 16);
         }
-        if (r.flags & XN_REQ_ROPE) qrot_floats += align_up(qf, 4);
+        if ((r.flags & XN_REQ_ROPE) || pinned) qrot_floats += align_up(qf, 4);
         if (end > s->cap) n_ring_rows += r.seq_len;
         else if (use_tf32(c, r)) { /* served by the tensor-core prefill kernel */ }
         else n_units += (long long)r.seq_len * Hkv * c->subs;
         max_rows = std::max<long long>(max_rows, (long long)r.seq_len * (Hq + 2 * Hkv));
+        if (pinned) {  // bytes the kernels move over PCIe themselves
+            c->stats.h2d_bytes += (qf + 2 * kvf) * 4;
+            c->stats.d2h_bytes += qf * 4;
+        }
     }
     if (n_units > kMaxUnits)
         return fail(c, XN_ERR_CAPACITY, "%lld attention rows in one submission exceed the limit %lld",
@@ -420,7 +426,7 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         const size_t qf = size_t(Hq) * S * D, kvf = size_t(Hkv) * S * D;
         const float *q_dev = r.q, *k_dev = r.k, *v_dev = r.v;
         float* o_dev = r.out;
-        if (host_mode) {
+        if (host_mode && !pinned) {
             memcpy(c->io_host + in_off, r.q, qf * 4);
             q_dev = reinterpret_cast<const float*>(c->io_dev + in_off);
             in_off += align_up(qf * 4, 16);
@@ -437,11 +443,11 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         const long long q_hs = seq_major ? D : (long long)S * D, q_ts = seq_major ? (long long)Hq * D : D;
         const long long kv_hs = seq_major ? D : (long long)S * D, kv_ts = seq_major ? (long long)Hkv * D : D;
         d.q_in = q_dev; d.qi_hs = q_hs; d.qi_ts = q_ts;
-        if (r.flags & XN_REQ_ROPE) {
+        if ((r.flags & XN_REQ_ROPE) || pinned) {
             d.q = c->q_rot + qrot_off;
             d.q_hs = (long long)S * D; d.q_ts = D;
             qrot_off += align_up(qf, 4);
-            d.flags = 1u;
+            d.flags = (r.flags & XN_REQ_ROPE) ? 1u : 2u;
         } else {
             d.q = q_dev; d.q_hs = q_hs; d.q_ts = q_ts;
         }
@@ -521,7 +527,7 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
     const int* pages_d = reinterpret_cast<const int*>(slot->dev + o_page);
     const int* ring_d = reinterpret_cast<const int*>(slot->dev + o_ring);
 
-    if (host_mode && io_in) {
+    if (host_mode && !pinned && io_in) {
         XN_CUDA(c, cudaMemcpyAsync(c->io_dev, c->io_host, io_in, cudaMemcpyHostToDevice, c->stream));
         c->stats.h2d_bytes += io_in;
     }
@@ -606,6 +612,7 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
     if (host_mode) {
         XN_CUDA(c, cudaStreamSynchronize(c->stream));
         if ((rc = check_device_status(c)) != XN_OK) return rc;
+        if (pinned) return XN_OK;  // the kernels wrote the outputs in place
         size_t o = io_in;
         for (int i = 0; i < n; ++i) {
             if (reqs[i].seq_len == 0) continue;
@@ -1008,6 +1015,9 @@ int32_t xn_attention_batch(xn_ctx* c, int32_t n, const xn_req* reqs) {
         if (rc != XN_OK) return rc;
         if (bool(reqs[i].flags & XN_REQ_DEVICE_PTRS) != dev)
             return fail(c, XN_ERR_ARG, "host and device requests mixed in one batch");
+        if ((reqs[i].flags & XN_REQ_HOST_PINNED) != (reqs[0].flags & XN_REQ_HOST_PINNED) ||
+            (dev && (reqs[i].flags & XN_REQ_HOST_PINNED)))
+            return fail(c, XN_ERR_ARG, "XN_REQ_HOST_PINNED must be set on all host requests of a batch or on none");
         if (!seen.insert(reqs[i].stream).second)
             return fail(c, XN_ERR_ARG, "request %d repeats a stream of this batch", i);
     }

@@ -29,7 +29,8 @@ struct ReqDev {
     int index_pos;
     int cap;                  // ring capacity (positions fold modulo cap)
     int n_pages;
-    unsigned flags;           // bit 0: rotate q and k with the context tables
+    unsigned flags;           // bit 0: rotate q and k with the context tables; bit 1: copy q
+                              // (unrotated) into the scratch `q` points at
     int pad;
 };
 
