@@ -53,7 +53,7 @@ def test_partition_and_aggregation_across_gloo_ranks(world):
     assert streams == list(range(256))                       # every stream on exactly one rank
     for r, (mine, heads) in enumerate(gathered):
         assert all(s % world == r for s in mine)             # round-robin rule
-        assert all((h // 4) % world == r for h in heads)     # query heads follow their KV head
+        assert heads == list(range(r * 32 // world, (r + 1) * 32 // world))  # contiguous head blocks
     heads = sorted(h for _, hs in gathered for h in hs)
     assert heads == list(range(32))
     assert times == [10.0 + world - 1, 5.0]                  # max over ranks
@@ -67,7 +67,9 @@ def test_sharding_helpers_single_process():
     assert sharding.streams_of_rank(10, 4, 1) == [1, 5, 9]
     assert sharding.rank_of_stream(9, 4) == 1
     assert sharding.kv_heads_of_rank(8, 8, 3) == [3]
-    assert sharding.query_heads_of_rank(20, 5, 2, 1) == [4, 5, 6, 7, 12, 13, 14, 15]
+    assert sharding.query_heads_of_rank(32, 8, 2, 1) == list(range(16, 32))
+    with pytest.raises(ValueError):
+        sharding.kv_heads_of_rank(5, 2, 0)
     assert sharding.aggregate([1.0], [2.0]) == ([1.0], [2.0])
     with pytest.raises(ValueError):
         sharding.streams_of_rank(4, 2, 2)

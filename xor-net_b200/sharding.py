@@ -2,7 +2,7 @@
 
 Decode shards by stream: stream ``i`` lives on GPU ``i mod world`` for its whole life (its pages
 are in that GPU's pool), so a decode step needs no exchange between GPUs.  A long prefill can be
-split by KV-head group: GPU ``g`` owns KV heads ``g, g+world, ...`` and their query heads; only the
+split by KV-head group: GPU ``g`` owns a contiguous block of KV heads and their query heads; only the
 per-head outputs are gathered at the end.  The only collectives here are the ones a benchmark
 needs to agree on a result (maximum time over ranks, total work), and they run on whatever
 ``torch.distributed`` backend the caller initialised (NCCL on GPUs, gloo in CPU tests).
@@ -24,10 +24,14 @@ def rank_of_stream(stream_id: int, world: int) -> int:
 
 
 def kv_heads_of_rank(num_kv_heads: int, world: int, rank: int) -> List[int]:
-    """KV heads (and with them the query-head groups) a rank computes in a head-split prefill."""
+    """KV heads (and with them the query-head groups) a rank computes in a head-split prefill:
+    contiguous blocks, so that the gathered per-rank outputs are already in head order."""
     if world <= 0 or not (0 <= rank < world):
         raise ValueError("need 0 <= rank < world")
-    return list(range(rank, num_kv_heads, world))
+    if num_kv_heads % world != 0:
+        raise ValueError("the number of KV heads must be a multiple of the number of GPUs")
+    per = num_kv_heads // world
+    return list(range(rank * per, (rank + 1) * per))
 
 
 def query_heads_of_rank(num_heads: int, num_kv_heads: int, world: int, rank: int) -> List[int]:
