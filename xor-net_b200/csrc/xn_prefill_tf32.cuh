@@ -489,20 +489,30 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap k_map,
             if (__all_sync(kFull, mbar_wait_bounded(&pv_done[jl & 1], uint32_t((jl >> 1) & 1)))) {
                 fence_after_sync();
                 const float inv = 1.0f / l_tot;
-                float* orow = a.out + size_t(h) * a.o_hs + size_t(t) * a.o_ts;
+                // Stage the tile in shared memory (the K stages are idle by now) so that the
+                // global stores are whole 512-byte rows per warp instead of 16 bytes per thread:
+                // matters most when `out` is a peer GPU's memory.  16-byte chunk c of row r sits
+                // at chunk position c ^ (r & 31): conflict-free both ways.
+                float4* tile = reinterpret_cast<float4*>(k_s);  // [128 rows][32 chunks]
                 for (int c0 = col0; c0 < min(col0 + kPage, n_pv); c0 += 32) {
                     uint32_t o[32];
                     tmem_ld32(tmem_o + lane_base + c0, o);
                     tmem_wait_ld();
-                    if (t < a.seq_len) {
 #pragma unroll
-                        for (int c = 0; c < 32; c += 4) {
-                            if (c0 + c + 3 < D) {
-                                float4 v4 = make_float4(__uint_as_float(o[c]) * inv, __uint_as_float(o[c + 1]) * inv,
-                                                        __uint_as_float(o[c + 2]) * inv, __uint_as_float(o[c + 3]) * inv);
-                                *reinterpret_cast<float4*>(orow + c0 + c) = v4;
-                            }
-                        }
+                    for (int c = 0; c < 32; c += 4) {
+                        const int chunk = (c0 + c) >> 2;
+                        tile[r * 32 + (chunk ^ (r & 31))] =
+                            make_float4(__uint_as_float(o[c]) * inv, __uint_as_float(o[c + 1]) * inv,
+                                        __uint_as_float(o[c + 2]) * inv, __uint_as_float(o[c + 3]) * inv);
+                    }
+                }
+                wg_barrier();
+                const int w8 = warp - 2;  // 0..7: 16 rows each
+                for (int rr = w8 * 16; rr < w8 * 16 + 16; ++rr) {
+                    const int tt = t0 + rr;
+                    if (tt < a.seq_len && lane * 4 + 3 < D) {
+                        float* orow = a.out + size_t(h) * a.o_hs + size_t(tt) * a.o_ts;
+                        *reinterpret_cast<float4*>(orow + lane * 4) = tile[rr * 32 + (lane ^ (rr & 31))];
                     }
                 }
             } else {
