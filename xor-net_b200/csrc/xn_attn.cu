@@ -579,7 +579,7 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         pa.head_dim = D;
         pa.scale_log2 = c->scale * 1.4426950408889634f;
         pa.status = c->status_d;
-        dim3 grid(unsigned((d.seq_len + pf::kBM - 1) / pf::kBM), unsigned(Hq));
+        dim3 grid(unsigned((d.seq_len + pf::kBM - 1) / pf::kBM) * unsigned(Hq));
         if (c->profile && (rc = profile_begin(c, 1)) != XN_OK) return rc;
         prefill_tf32_kernel<<<grid, pf::kThreads, pf::kSmemBytes, c->stream>>>(c->k_map, c->v_map, pa);
         if (c->profile && (rc = profile_end(c)) != XN_OK) return rc;

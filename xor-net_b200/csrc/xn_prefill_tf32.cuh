@@ -198,9 +198,13 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap k_map,
     static_assert((1 + 2 * kKStages + 2 * kVStages + 3 * kSBufs) * 8 + 16 <= 256, "barrier area");
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // 1-D grid, longest query tiles first across ALL heads (blocks are handed to SMs in index
+    // order, so the causal triangle is packed heaviest-first); neighbouring blocks are the heads
+    // of one KV group on the same rows, which keeps their shared K/V pages hot in L2.
     const int n_qtiles = (a.seq_len + kBM - 1) / kBM;
-    const int qt = n_qtiles - 1 - blockIdx.x;  // longest rows first
-    const int h = blockIdx.y;
+    const int n_heads = a.num_kv_heads * a.group;
+    const int qt = n_qtiles - 1 - int(blockIdx.x) / n_heads;
+    const int h = int(blockIdx.x) % n_heads;
     const int h_kv = h / a.group;
     const int t0 = qt * kBM;
     const int last_row = min(t0 + kBM, a.seq_len) - 1;
