@@ -250,7 +250,7 @@ def measure_prefill(xn, torch, tstream, device, S, Hq, Hkv, D, theta, steps, war
     dev = ctx.make_batch([(st, 0, 0, S, q_d.data_ptr(), k_d.data_ptr(), v_d.data_ptr(), o_d.data_ptr())],
                          xn.REQ_DEVICE_PTRS | xn.REQ_ROPE)
     host = ctx.make_batch([(st, 0, 0, S, q_h.data_ptr(), k_h.data_ptr(), v_h.data_ptr(), o_h.data_ptr())],
-                          xn.REQ_ROPE)
+                          xn.REQ_ROPE | xn.REQ_HOST_PINNED)  # page-locked host buffers
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")  # > L2 (126 MB)
     for _ in range(max(warmup, 3)):
         ctx.submit(dev)
@@ -633,6 +633,13 @@ def run_gpu_arm(args):
         value = total_bytes_per_step * args.steps / (ms * 1e-3) / 1e9
         e2e_value = total_bytes_per_step * e2e_steps / (e2e_ms * 1e-3) / 1e9
         launches = s1["kernel_launches"] - s0["kernel_launches"]
+        # DRAM bytes per launch of the split-KV kernel from the ncu capture of this same workload
+        # (profiles/attn_splitkv_c3_2layers.md: dram__bytes_read.sum + dram__bytes_write.sum);
+        # only valid for the unmodified c3 workload, whose per-launch work is fixed by its seed
+        traffic, traffic_src = None, None
+        if args.workload == "c3" and not args.streams and world == 1:
+            traffic = 708.70e6 + 6.33e6
+            traffic_src = "ncu capture, profiles/attn_splitkv_c3_2layers.md"
         line = {
             "metric": "decode_attn_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
@@ -658,7 +665,7 @@ def run_gpu_arm(args):
             "roofline": {"bound": "hbm", "kernel": "attn_splitkv_kernel<32,4>",
                          "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak if peak else None, "peak_source": peak_kind,
-                         "traffic": None, "avg_launch_ms": kern_avg_ms,
+                         "traffic": traffic, "traffic_source": traffic_src, "avg_launch_ms": kern_avg_ms,
                          "launches_timed": int(kern_n),
                          "algorithmic_bytes_per_launch": bytes_per_layer},
             "clocks": clocks,

@@ -32,10 +32,14 @@ namespace xn {
 #ifndef XN_DECODE_STAGES
 #define XN_DECODE_STAGES 3
 #endif
+#ifndef XN_DECODE_WARPS
+#define XN_DECODE_WARPS 8
+#endif
 
 template <int NV>
 struct DecodeCfg {
-    static constexpr int kWarps = 8;                      // consumer warps
+    static constexpr int kWarps = (NV <= 32) ? XN_DECODE_WARPS : 8;  // consumer warps
+    static constexpr int kRedWarps = 8;                   // warp states merged per round
     static constexpr int kThreads = (kWarps + 1) * 32;    // + 1 producer warp
     static constexpr int kLPK = (NV <= 32) ? 8 : 16;      // lanes sharing one key in q.k
     static constexpr int kKPI = 32 / kLPK;                // keys per warp iteration
@@ -117,7 +121,7 @@ struct DecodeSmem {
     static constexpr bool kStageQ = NV <= 32;  // query rows travel with the first tile of an item
     static constexpr size_t kQFloats = kStageQ ? size_t(GT) * NV * 4 : 0;
     static constexpr size_t kStageBytes = (size_t(Cfg::kStageFloats) + kQFloats) * 4;
-    static constexpr size_t kRedFloats = size_t(Cfg::kWarps) * GT * NV * 4;
+    static constexpr size_t kRedFloats = size_t(Cfg::kRedWarps) * GT * NV * 4;
     static constexpr size_t kScratchFloats = size_t(Cfg::kWarps) * (Cfg::kKPW + 1) * 4;  // GT<=4
     static constexpr size_t kBytes = Cfg::kStages * kStageBytes + kRedFloats * 4 +
                                      kScratchFloats * 4 + Cfg::kWarps * 4 * 2 * 4 /* m,l */ +
@@ -510,51 +514,74 @@ attn_splitkv_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restrict__
             const float mw = sm_m[cw * 4 + hh];
             f[hh] = (mw == -INFINITY) ? 0.f : expf(mw - M);
         }
+        // The W warp states go through the reduction buffer RW warps at a time; thread e of the
+        // first GT*nv consumer threads owns output element e and adds up each round.
+        constexpr int RW = Cfg::kRedWarps;
+        float4 esum[(GT * NV + W * 32 - 1) / (W * 32)];
 #pragma unroll
-        for (int hh = 0; hh < GT; ++hh)
+        for (int i = 0; i < int(sizeof(esum) / sizeof(esum[0])); ++i) esum[i] = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-            for (int sv = 0; sv < SV; ++sv) {
-                const int idx = lane + 32 * sv;
-                if (idx < nv) {
-                    float4 a = acc[hh][sv];
-                    a.x *= f[hh]; a.y *= f[hh]; a.z *= f[hh]; a.w *= f[hh];
-                    reinterpret_cast<float4*>(red)[(size_t(cw) * GT + hh) * nv + idx] = a;
+        for (int round = 0; round < W / RW; ++round) {
+            if (cw / RW == round) {
+#pragma unroll
+                for (int hh = 0; hh < GT; ++hh)
+#pragma unroll
+                    for (int sv = 0; sv < SV; ++sv) {
+                        const int idx = lane + 32 * sv;
+                        if (idx < nv) {
+                            float4 a = acc[hh][sv];
+                            a.x *= f[hh]; a.y *= f[hh]; a.z *= f[hh]; a.w *= f[hh];
+                            reinterpret_cast<float4*>(red)[(size_t(cw % RW) * GT + hh) * nv + idx] = a;
+                        }
+                    }
+            }
+            named_bar_sync(1, W * 32);
+            int slot = 0;
+            for (int e = ctid; e < GT * nv; e += W * 32, ++slot) {
+                const int hh = e / nv, idx = e % nv;
+                float4 sum = esum[slot];
+#pragma unroll
+                for (int w = 0; w < RW; ++w) {
+                    const float4 a = reinterpret_cast<const float4*>(red)[(size_t(w) * GT + hh) * nv + idx];
+                    sum.x += a.x; sum.y += a.y; sum.z += a.z; sum.w += a.w;
                 }
+                esum[slot] = sum;
             }
-        named_bar_sync(1, W * 32);
-        for (int e = ctid; e < GT * nv; e += W * 32) {
-            const int hh = e / nv, idx = e % nv;
-            if (hh >= h.nheads) continue;
-            float M = -INFINITY;
+            if (round + 1 < W / RW) named_bar_sync(1, W * 32);
+        }
+        {
+            int slot = 0;
+            for (int e = ctid; e < GT * nv; e += W * 32, ++slot) {
+                const int hh = e / nv, idx = e % nv;
+                if (hh >= h.nheads) continue;
+                float M = -INFINITY;
 #pragma unroll
-            for (int w = 0; w < W; ++w) M = fmaxf(M, sm_m[w * 4 + hh]);
-            float L = 0.f;
-            float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int w = 0; w < W; ++w) M = fmaxf(M, sm_m[w * 4 + hh]);
+                float L = 0.f;
 #pragma unroll
-            for (int w = 0; w < W; ++w) {
-                const float mw = sm_m[w * 4 + hh];
-                const float fw = (mw == -INFINITY) ? 0.f : expf(mw - M);
-                L += sm_l[w * 4 + hh] * fw;
-                const float4 a = reinterpret_cast<const float4*>(red)[(size_t(w) * GT + hh) * nv + idx];
-                sum.x += a.x; sum.y += a.y; sum.z += a.z; sum.w += a.w;
-            }
-            if (h.part < 0) {
-                float* orow = h.out + size_t(hh) * h.o_hs;
-                const float inv = 1.0f / L;
-                const int d = idx * 4;
-                if (d + 3 < head_dim && ((reinterpret_cast<uintptr_t>(orow + d) & 15) == 0)) {
-                    *reinterpret_cast<float4*>(orow + d) =
-                        make_float4(sum.x * inv, sum.y * inv, sum.z * inv, sum.w * inv);
+                for (int w = 0; w < W; ++w) {
+                    const float mw = sm_m[w * 4 + hh];
+                    L += sm_l[w * 4 + hh] * ((mw == -INFINITY) ? 0.f : expf(mw - M));
+                }
+                const float4 sum = esum[slot];
+                if (h.part < 0) {
+                    float* orow = h.out + size_t(hh) * h.o_hs;
+                    const float inv = 1.0f / L;
+                    const int d = idx * 4;
+                    if (d + 3 < head_dim && ((reinterpret_cast<uintptr_t>(orow + d) & 15) == 0)) {
+                        *reinterpret_cast<float4*>(orow + d) =
+                            make_float4(sum.x * inv, sum.y * inv, sum.z * inv, sum.w * inv);
+                    } else {
+                        if (d + 0 < head_dim) orow[d + 0] = sum.x * inv;
+                        if (d + 1 < head_dim) orow[d + 1] = sum.y * inv;
+                        if (d + 2 < head_dim) orow[d + 2] = sum.z * inv;
+                        if (d + 3 < head_dim) orow[d + 3] = sum.w * inv;
+                    }
                 } else {
-                    if (d + 0 < head_dim) orow[d + 0] = sum.x * inv;
-                    if (d + 1 < head_dim) orow[d + 1] = sum.y * inv;
-                    if (d + 2 < head_dim) orow[d + 2] = sum.z * inv;
-                    if (d + 3 < head_dim) orow[d + 3] = sum.w * inv;
+                    float* rec = partials + (size_t(h.part) * GT + hh) * part_stride_floats(nv);
+                    if (idx == 0) *reinterpret_cast<float4*>(rec) = make_float4(M, L, 0.f, 0.f);
+                    reinterpret_cast<float4*>(rec + 4)[idx] = sum;
                 }
-            } else {
-                float* rec = partials + (size_t(h.part) * GT + hh) * part_stride_floats(nv);
-                if (idx == 0) *reinterpret_cast<float4*>(rec) = make_float4(M, L, 0.f, 0.f);
-                reinterpret_cast<float4*>(rec + 4)[idx] = sum;
             }
         }
         if (h.part < 0) { DT_END(tm_merge) continue; }
