@@ -290,7 +290,7 @@ def measure_prefill(xn, torch, tstream, device, S, Hq, Hkv, D, theta, steps, war
 
 
 def run_prefill_arm(args):
-    """--workload c2: BASELINE config 2 (causal GQA prefill, BitNet-2B shape, 2048 tokens)."""
+    """--workload c2: causal GQA prefill, BitNet-2B shape, 2048 tokens (--seq overrides the length)."""
     import torch
 
     import xor_net_b200 as xn
@@ -633,13 +633,13 @@ def run_gpu_arm(args):
         value = total_bytes_per_step * args.steps / (ms * 1e-3) / 1e9
         e2e_value = total_bytes_per_step * e2e_steps / (e2e_ms * 1e-3) / 1e9
         launches = s1["kernel_launches"] - s0["kernel_launches"]
-        # DRAM bytes per launch of the split-KV kernel from the ncu capture of this same workload
-        # (profiles/attn_splitkv_c3_2layers.md: dram__bytes_read.sum + dram__bytes_write.sum);
+        # DRAM bytes per launch of the split-KV kernel from an ncu capture of this same workload
+        # (dram__bytes_read.sum + dram__bytes_write.sum; the summary is kept under profiles/);
         # only valid for the unmodified c3 workload, whose per-launch work is fixed by its seed
         traffic, traffic_src = None, None
         if args.workload == "c3" and not args.streams and world == 1:
             traffic = 708.70e6 + 6.33e6
-            traffic_src = "ncu capture, profiles/attn_splitkv_c3_2layers.md"
+            traffic_src = "ncu capture of this workload (2 of 30 layers), summary under profiles/"
         line = {
             "metric": "decode_attn_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,

@@ -1,4 +1,4 @@
-"""BASELINE configs 4 and 5 as parity cases (the configs that are not benchmark lines), through the
+"""The BitNet-3B and long-context LLaMA-3-8B workload shapes as parity cases (they are not benchmark lines), through the
 C ABI, against the CPU oracle on identical bytes."""
 import numpy as np
 import pytest

@@ -74,7 +74,7 @@ def test_decode_lengths_around_boundaries(ctx2b):
 
 
 def test_config1_decode_shape(ctx2b):
-    # BitNet-2B shape, one query token over 1024 cached tokens (first BASELINE config)
+    # BitNet-2B shape, one query token over 1024 cached tokens (the single-stream decode workload)
     rng = np.random.default_rng(299792458)
     p = Pair(ctx2b, 4096)
     qq, kk, vv = rand_qkv(rng, 20, 5, 1023, 128)

@@ -66,7 +66,7 @@ def test_head_dims_and_groups(Hq, Hkv, D):
 
 
 def test_fused_rope_prefill_config2_shape():
-    # BASELINE config 2: 2048 tokens, 20/5 heads, head_dim 128, fused RoPE (theta 500000) and
+    # the 2048-token prefill workload: 2048 tokens, 20/5 heads, head_dim 128, fused RoPE (theta 500000) and
     # append into 64-token pages, causal; output 2048 x 20 x 128
     rng = np.random.default_rng(299792458 + 2000)
     cos, sin = xn.rope_tables(500000.0, 128, 4096)
