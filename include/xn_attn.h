@@ -253,6 +253,11 @@ XN_API int32_t xn_plan_split(int32_t n_units, const int32_t* kv_len, int32_t til
                              int32_t* item_tile_begin, int32_t* item_tile_end, int32_t* item_part,
                              int32_t* cta_item_begin, int32_t* n_items_out, int32_t* n_parts_out);
 
+/* Diagnostic for the error path of the kernels' bounded waits: launches a one-thread kernel
+ * that waits, for at most timeout_ms (1..1000), on a barrier nothing will complete, then
+ * synchronises.  Returns XN_ERR_DEVICE_WAIT (the expected outcome); the context stays usable. */
+XN_API int32_t xn_debug_expire_wait(xn_ctx* ctx, int32_t timeout_ms);
+
 /* Library build identification: "xn_attn <version> sm_100a". */
 XN_API const char* xn_version(void);
 

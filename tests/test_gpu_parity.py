@@ -339,3 +339,20 @@ def test_pinned_host_buffers_skip_the_staging_copies(ctx2b):
     assert e.value.code == 1
     for p in pairs:
         p.st.destroy()
+
+
+def test_expired_device_wait_is_reported_and_the_context_survives():
+    # a kernel-side bounded wait that runs out: the kernel records a status and returns, the host
+    # reports XN_ERR_DEVICE_WAIT, and the next call works (nothing is trapped, hung or faulted)
+    ctx = xn.Context(1, 4, 2, 16, pool_pages=4, prefill_mode=F32)
+    rc = ctx.lib.xn_debug_expire_wait(ctx.handle, 20)
+    assert rc == 7
+    assert b"bounded wait" in ctx.lib.xn_last_error(ctx.handle)
+    assert ctx.stats()["device_wait_errors"] == 1
+    assert ctx.lib.xn_debug_expire_wait(ctx.handle, 0) == 1        # argument check
+    rng = np.random.default_rng(61)
+    p = Pair(ctx, 128)
+    got, want = p.step(0, 0, *rand_qkv(rng, 4, 2, 40, 16))
+    assert_parity(got, want, "after an expired wait")
+    ctx.synchronize()                                              # status word was cleared
+    ctx.close()

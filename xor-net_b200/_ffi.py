@@ -79,6 +79,7 @@ SIGNATURES = {
     "xn_stream_pages": (C.c_int64, [C.c_void_p, C.c_void_p, c_i32p, C.c_int64]),
     "xn_plan_split": (C.c_int32, [C.c_int32, c_i32p, C.c_int32, C.c_int32, C.c_int32, c_i32p,
                                   c_i32p, c_i32p, c_i32p, c_i32p, c_i32p, c_i32p]),
+    "xn_debug_expire_wait": (C.c_int32, [C.c_void_p, C.c_int32]),
     "xn_version": (C.c_char_p, []),
 }
 

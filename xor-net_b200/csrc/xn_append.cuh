@@ -174,6 +174,18 @@ slots_gather_kernel(const int* __restrict__ pages, const float* __restrict__ k_p
     }
 }
 
+// Diagnostic: one thread waits on an mbarrier that nothing will ever complete, with a short limit,
+// and reports the expiry the way the attention kernels do.  Exercises the host's handling of a
+// bounded wait that ran out without disturbing the GPU.
+__global__ void wait_probe_kernel(int* __restrict__ status, unsigned long long limit_ns) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        mbar_fence_init();
+        if (!mbar_wait_bounded(&bar, 0, limit_ns)) atomicExch(status, kDevWaitFull);
+    }
+}
+
 __global__ void __launch_bounds__(256)
 fill_normal_kernel(float* __restrict__ dst, long long n, unsigned long long seed) {
     for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < n;

@@ -1190,6 +1190,19 @@ int64_t xn_stream_pages(xn_ctx* c, xn_stream* s, int32_t* out, int64_t max_out) 
     return n;
 }
 
+int32_t xn_debug_expire_wait(xn_ctx* c, int32_t timeout_ms) {
+    if (!ctx_ok(c)) return XN_ERR_HANDLE;
+    std::lock_guard<std::mutex> g(c->mu);
+    if (timeout_ms < 1 || timeout_ms > 1000) return fail(c, XN_ERR_ARG, "timeout_ms outside 1..1000");
+    XN_CUDA(c, cudaSetDevice(c->device));
+    wait_probe_kernel<<<1, 32, 0, c->stream>>>(c->status_d, (unsigned long long)timeout_ms * 1000000ull);
+    c->stats.kernel_launches += 1;
+    XN_CUDA(c, cudaGetLastError());
+    XN_CUDA(c, cudaMemcpyAsync(c->status_h, c->status_d, sizeof(int), cudaMemcpyDeviceToHost, c->stream));
+    XN_CUDA(c, cudaStreamSynchronize(c->stream));
+    return check_device_status(c);
+}
+
 int32_t xn_plan_split(int32_t n_units, const int32_t* kv_len, int32_t tile_tokens, int32_t max_ctas,
                       int32_t max_items, int32_t* item_unit, int32_t* item_tile_begin,
                       int32_t* item_tile_end, int32_t* item_part, int32_t* cta_item_begin,

@@ -98,9 +98,11 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
     return t;
 }
 
-// Waits for the given phase parity at most ~2 s.  Returns false when it gave up; the caller
-// records an error code and leaves its loop, so a lost copy can never hang the GPU.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+// Waits for the given phase parity at most `limit_ns` (default ~2 s).  Returns false when it
+// gave up; the caller records an error code and leaves its loop, so a lost copy can never hang
+// the GPU.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity,
+                                                  unsigned long long limit_ns = 2000000000ull) {
     if (mbar_try_wait(bar, parity)) return true;
     unsigned long long t0 = 0;
     for (uint32_t spins = 1;; ++spins) {
@@ -108,7 +110,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
         if ((spins & 0x3ffu) == 0) {
             unsigned long long now = global_timer_ns();
             if (t0 == 0) t0 = now;
-            else if (now - t0 > 2000000000ull) return false;
+            else if (now - t0 > limit_ns) return false;
         }
     }
 }
