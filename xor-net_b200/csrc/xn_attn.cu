@@ -75,6 +75,8 @@ struct xn_ctx {
     int sm_count = 0;
     int decode_ctas = 0;     // thread blocks of the split-KV launch (one per SM)
     int decode_chunks = 0;   // chunks the tile list is cut into (several per block)
+    bool fuse_append = true; // decode batches: the attention kernel appends the new token itself
+    bool fuse_pinned = true; // ... also when q,k,v live in page-locked host memory
     int* sync_d = nullptr;   // chunk counter, done counter, per-unit arrival counters
     size_t sync_cap = 0;     // ints
     cudaStream_t stream = nullptr;
@@ -151,7 +153,7 @@ size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 using SplitFn = void (*)(const ReqDev*, const UnitDev*, const ItemDev*, const int*, int, const int*,
                          const float*, const float*, float*, int*, long long, int, int, int, float,
-                         int*);
+                         const float*, const float*, int*);
 
 struct SplitKernel {
     SplitFn fn;
@@ -397,6 +399,25 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
             c->stats.d2h_bytes += qf * 4;
         }
     }
+    // Pure decode batches (one new token per request) let the attention kernel append, and rotate,
+    // the new token itself: no separate append launch.  Needs rows the bulk copies can take
+    // (head_dim % 4 == 0, 16-byte aligned pointers) and, for RoPE, the pair layout of head_dim
+    // 64 / 128.
+    bool fused = c->fuse_append && n_ring_rows == 0 && D % 4 == 0 && c->nv_class <= 32;
+    for (int i = 0; i < n && fused; ++i) {
+        const xn_req& r = reqs[i];
+        if (r.seq_len != 1) { fused = false; break; }
+        if ((r.flags & XN_REQ_ROPE) && !(c->nv_exact && (c->nv == 16 || c->nv == 32))) fused = false;
+        if (pinned && !c->fuse_pinned) fused = false;
+        if (!host_mode || pinned)
+            if ((reinterpret_cast<uintptr_t>(r.q) | reinterpret_cast<uintptr_t>(r.k) |
+                 reinterpret_cast<uintptr_t>(r.v)) & 15)
+                fused = false;
+    }
+    if (fused) {
+        qrot_floats = 0;
+        max_rows = 0;
+    }
     if (n_units > kMaxUnits)
         return fail(c, XN_ERR_CAPACITY, "%lld attention rows in one submission exceed the limit %lld",
                     n_units, kMaxUnits);
@@ -443,7 +464,10 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         const long long q_hs = seq_major ? D : (long long)S * D, q_ts = seq_major ? (long long)Hq * D : D;
         const long long kv_hs = seq_major ? D : (long long)S * D, kv_ts = seq_major ? (long long)Hkv * D : D;
         d.q_in = q_dev; d.qi_hs = q_hs; d.qi_ts = q_ts;
-        if ((r.flags & XN_REQ_ROPE) || pinned) {
+        if (fused) {
+            d.q = q_dev; d.q_hs = q_hs; d.q_ts = q_ts;
+            d.flags = 8u | ((r.flags & XN_REQ_ROPE) ? 1u : 0u);
+        } else if ((r.flags & XN_REQ_ROPE) || pinned) {
             d.q = c->q_rot + qrot_off;
             d.q_hs = (long long)S * D; d.q_ts = D;
             qrot_off += align_up(qf, 4);
@@ -471,7 +495,8 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
                         u.head0 = h * c->group + sb * c->gt;
                         u.nheads = std::min(c->gt, c->group - sb * c->gt);
                         u.t_q = t; u.kv_len = int(r.index_pos) + t + 1;
-                        u.part_begin = -1; u.part_count = 1; u.merge_slot = -1; u.pad = 0;
+                        u.part_begin = -1; u.part_count = 1; u.merge_slot = -1;
+                        u.store_new = sb == 0 ? 1 : 0;
                         units.push_back(u);
                         kv_lens.push_back(u.kv_len);
                     }
@@ -554,7 +579,7 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         // sp.ctas chunks, taken dynamically by at most one block per SM
         k.fn<<<std::min(sp.ctas, c->decode_ctas), k.threads, k.smem, c->stream>>>(
             reqs_d, units_d, items_d, cta_d, sp.ctas, pages_d, c->k_pool, c->v_pool, c->partials,
-            c->sync_d, c->pool_pages, Hkv, D, nv, c->scale, c->status_d);
+            c->sync_d, c->pool_pages, Hkv, D, nv, c->scale, c->cos_d, c->sin_d, c->status_d);
         if (c->profile && (rc = profile_end(c)) != XN_OK) return rc;
         c->stats.kernel_launches += 1;
         c->stats.decode_launches += 1;
@@ -755,6 +780,8 @@ int32_t xn_ctx_create(const xn_ctx_desc* d, xn_ctx** out_ctx) {
         if (v > 0) chunks_per_cta = v;
     }
     c->decode_chunks = c->decode_ctas * chunks_per_cta;
+    if (const char* env = getenv("XORNET_ATTN_FUSE_APPEND")) c->fuse_append = atoi(env) != 0;
+    if (const char* env = getenv("XORNET_ATTN_FUSE_PINNED")) c->fuse_pinned = atoi(env) != 0;
 
     const size_t page_bytes =
         size_t(d->num_layers) * d->num_kv_heads * kPageTokens * c->nv * 16 * 2;  // K and V

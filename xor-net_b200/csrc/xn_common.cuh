@@ -30,7 +30,8 @@ struct ReqDev {
     int cap;                  // ring capacity (positions fold modulo cap)
     int n_pages;
     unsigned flags;           // bit 0: rotate q and k with the context tables; bit 1: copy q
-                              // (unrotated) into the scratch `q` points at
+                              // (unrotated) into the scratch `q` points at; bit 3: one new
+                              // token, appended (and rotated) by the attention kernel itself
     int pad;
 };
 
@@ -45,7 +46,7 @@ struct UnitDev {
     int part_begin; // first partial slot, or -1 when the unit is written directly
     int part_count;
     int merge_slot; // arrival counter of a cut unit
-    int pad;
+    int store_new;  // fused append: this unit writes the new token's K/V rows into the cache
 };
 
 // A contiguous tile range of one unit given to one thread block.

@@ -108,9 +108,11 @@ struct StageHdr {
     int part_begin;   // first partial slot of the unit
     int part_count;   // items the unit was cut into
     int merge_slot;   // arrival counter of the unit (cut units only)
-    int pad;
+    int new_key;      // row of this tile that holds the request's new token (fused append), or -1
+    float* k_dst;     // cache rows the new token's K / V must be written to (nullptr: another
+    float* v_dst;     //   unit of the same KV head does it)
 };
-enum : int { kHdrFirst = 1, kHdrLast = 2, kHdrQStaged = 4, kHdrEnd = 8 };
+enum : int { kHdrFirst = 1, kHdrLast = 2, kHdrQStaged = 4, kHdrEnd = 8, kHdrRope = 16 };
 
 // Words of the per-context synchronisation array used by the kernel.
 enum : int { kSyncChunk = 0, kSyncDone = 1, kSyncMerge0 = 2 };
@@ -119,7 +121,8 @@ template <int NV, int GT>
 struct DecodeSmem {
     using Cfg = DecodeCfg<NV>;
     static constexpr bool kStageQ = NV <= 32;  // query rows travel with the first tile of an item
-    static constexpr size_t kQFloats = kStageQ ? size_t(GT) * NV * 4 : 0;
+    // extra area of a stage: GT query rows, then one cos row and one sin row (fused RoPE)
+    static constexpr size_t kQFloats = kStageQ ? size_t(GT + 1) * NV * 4 : 0;
     static constexpr size_t kStageBytes = (size_t(Cfg::kStageFloats) + kQFloats) * 4;
     static constexpr size_t kRedFloats = size_t(Cfg::kRedWarps) * GT * NV * 4;
     static constexpr size_t kScratchFloats = size_t(Cfg::kWarps) * (Cfg::kKPW + 1) * 4;  // GT<=4
@@ -137,6 +140,11 @@ struct DecodeSmem {
 //   producer warp  all 32 lanes resolve the descriptors of up to 32 items of a chunk at once
 //                  (item -> unit -> request, page ids), lane 0 then writes a StageHdr and issues
 //                  the bulk copies tile by tile: no dependent global load sits between two tiles;
+//                  When the request carries one new token and asks for it (ReqDev flag 8), the
+//                  tile that ends the unit takes its last row from the request's k / v instead of
+//                  the cache, and the consumer warp that owns that row rotates it (RoPE, if asked),
+//                  and stores it into the cache: the append of src/nn/fast_attention.rs:104-116
+//                  without a separate kernel;
 //   consumer warps follow the headers: load q (from the stage when it was staged) at the first
 //                  tile of an item, accumulate, merge their states at its last tile and write
 //                  either the output row (unit in one piece) or a partial record.  The block
@@ -152,6 +160,7 @@ attn_splitkv_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restrict__
                     const float* __restrict__ k_pool, const float* __restrict__ v_pool,
                     float* __restrict__ partials, int* __restrict__ sync, long long pool_pages,
                     int num_kv_heads, int head_dim, int nv_arg, float scale,
+                    const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                     int* __restrict__ status) {
     const int nv = EXACT ? NV : nv_arg;
     using Cfg = DecodeCfg<NV>;
@@ -205,6 +214,10 @@ attn_splitkv_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restrict__
                 long long q_hs = 0, o_hs = 0;
                 const int* pages = page_ids;
                 size_t layer_base = 0;
+                const float* k_new = nullptr;  // fused append: the new token's rows of this KV head
+                const float* v_new = nullptr;
+                int fused = 0;                 // bit 0 fused append, bit 1 rotate, bit 2 this unit stores
+                int pos = 0;
                 if (my_it < it_hi) {
                     item = items[my_it];
                     u = units[item.unit];
@@ -215,6 +228,12 @@ attn_splitkv_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restrict__
                     o_hs = r.o_hs;
                     pages = page_ids + r.page_off;
                     layer_base = size_t(r.layer) * size_t(pool_pages);
+                    if (r.flags & 8u) {
+                        k_new = r.k + size_t(u.kv_head) * r.kv_hs;
+                        v_new = r.v + size_t(u.kv_head) * r.kv_hs;
+                        fused = 1 | ((r.flags & 1u) ? 2 : 0) | (u.store_new ? 4 : 0);
+                        pos = r.index_pos;
+                    }
                 }
                 const int n_here = min(32, it_hi - base);
                 for (int k = 0; k < n_here && ok; ++k) {
@@ -236,7 +255,15 @@ attn_splitkv_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restrict__
                     h.part_begin = __shfl_sync(kFull, u.part_begin, k);
                     h.part_count = __shfl_sync(kFull, u.part_count, k);
                     h.merge_slot = __shfl_sync(kFull, u.merge_slot, k);
-                    h.pad = 0;
+                    h.new_key = -1;
+                    h.k_dst = nullptr;
+                    h.v_dst = nullptr;
+                    const int fused_k = __shfl_sync(kFull, fused, k);
+                    const int pos_k = __shfl_sync(kFull, pos, k);
+                    const float* k_new_k = reinterpret_cast<const float*>(
+                        __shfl_sync(kFull, reinterpret_cast<unsigned long long>(k_new), k));
+                    const float* v_new_k = reinterpret_cast<const float*>(
+                        __shfl_sync(kFull, reinterpret_cast<unsigned long long>(v_new), k));
                     const bool stage_q = Sm::kStageQ && (head_dim % 4 == 0) &&
                                          ((reinterpret_cast<uintptr_t>(h.q) | uintptr_t(h.q_hs * 4)) & 15) == 0;
                     const int* pages_ptr = reinterpret_cast<const int*>(pages_k);
@@ -262,21 +289,43 @@ attn_splitkv_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restrict__
                                     const size_t src = ((size_t(lbase_k) + size_t(page)) * num_kv_heads + kv_head) *
                                                            page_floats +
                                                        size_t(tok0 % kPageTokens) * dp;
-                                    const uint32_t bytes = uint32_t(ntok) * dp * 4;
                                     const bool first = tile == tile_begin;
+                                    // fused append: the tile that ends the unit takes its last
+                                    // row from the request instead of the cache
+                                    const bool has_new = (fused_k & 1) && tok0 + ntok == kv_len;
+                                    const int n_cache = has_new ? ntok - 1 : ntok;
+                                    const uint32_t bytes = uint32_t(n_cache) * dp * 4;
+                                    const uint32_t row_bytes = uint32_t(dp) * 4;
+                                    const bool rope_here = (fused_k & 2) && (first || has_new);
                                     h.flags = (first ? kHdrFirst : 0) | (tile == tile_end - 1 ? kHdrLast : 0) |
-                                              (first && stage_q ? kHdrQStaged : 0);
+                                              (first && stage_q ? kHdrQStaged : 0) | ((fused_k & 2) ? kHdrRope : 0);
                                     h.ntok = ntok;
+                                    h.new_key = has_new ? ntok - 1 : -1;
+                                    h.k_dst = (has_new && (fused_k & 4)) ? const_cast<float*>(k_pool) + src + size_t(ntok - 1) * dp : nullptr;
+                                    h.v_dst = (has_new && (fused_k & 4)) ? const_cast<float*>(v_pool) + src + size_t(ntok - 1) * dp : nullptr;
                                     hdr[s] = h;
                                     float* dst = stage_ptr(s);
-                                    const uint32_t q_bytes = (first && stage_q) ? uint32_t(h.nheads) * dp * 4 : 0u;
-                                    mbar_arrive_expect_tx(&full_bar[s], 2 * bytes + q_bytes);
-                                    bulk_g2s(dst, k_pool + src, bytes, &full_bar[s]);
-                                    bulk_g2s(dst + TPS * NV * 4, v_pool + src, bytes, &full_bar[s]);
+                                    const uint32_t q_bytes = (first && stage_q) ? uint32_t(h.nheads) * row_bytes : 0u;
+                                    mbar_arrive_expect_tx(&full_bar[s], 2 * bytes + q_bytes + (has_new ? 2 * row_bytes : 0u) +
+                                                                            (rope_here ? row_bytes : 0u));
+                                    if (bytes) {
+                                        bulk_g2s(dst, k_pool + src, bytes, &full_bar[s]);
+                                        bulk_g2s(dst + TPS * NV * 4, v_pool + src, bytes, &full_bar[s]);
+                                    }
+                                    if (has_new) {
+                                        bulk_g2s(dst + size_t(n_cache) * dp, k_new_k, row_bytes, &full_bar[s]);
+                                        bulk_g2s(dst + TPS * NV * 4 + size_t(n_cache) * dp, v_new_k, row_bytes, &full_bar[s]);
+                                    }
                                     if (q_bytes)
                                         for (int hh = 0; hh < h.nheads; ++hh)
                                             bulk_g2s(dst + Cfg::kStageFloats + hh * dp, h.q + size_t(hh) * h.q_hs,
-                                                     uint32_t(dp) * 4, &full_bar[s]);
+                                                     row_bytes, &full_bar[s]);
+                                    if (rope_here) {  // cos row then sin row of the token's position
+                                        const int half = head_dim / 2;
+                                        float* cs = dst + Cfg::kStageFloats + GT * NV * 4;
+                                        bulk_g2s(cs, cos_t + size_t(pos_k) * half, row_bytes / 2, &full_bar[s]);
+                                        bulk_g2s(cs + half, sin_t + size_t(pos_k) * half, row_bytes / 2, &full_bar[s]);
+                                    }
                                 }
                             }
                             ok = __shfl_sync(kFull, ok ? 1 : 0, 0) != 0;
@@ -382,12 +431,75 @@ attn_splitkv_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restrict__
                     qreg[hh][j] = val;
                 }
             }
+            if (h.flags & kHdrRope) {
+                // rotate-half RoPE of the staged q rows (src/nn/fast_attention_simd.rs:380-387):
+                // dims (i, i + D/2) sit in slots (j, j + SQ/2) of the same lane; unfused
+                // multiplies so that the values equal the reference's
+                const float4* cs4 = reinterpret_cast<const float4*>(stage_ptr(s) + Cfg::kStageFloats + GT * NV * 4);
+                const float4* sn4 = cs4 + nv / 2;
+#pragma unroll
+                for (int j = 0; j < SQ / 2; ++j) {
+                    const int idx = j * LPK + sub;
+                    const float4 c = cs4[idx], sn = sn4[idx];
+#pragma unroll
+                    for (int hh = 0; hh < GT; ++hh) {
+                        const float4 a = qreg[hh][j], b = qreg[hh][j + SQ / 2];
+                        qreg[hh][j] = make_float4(__fsub_rn(__fmul_rn(a.x, c.x), __fmul_rn(b.x, sn.x)),
+                                                  __fsub_rn(__fmul_rn(a.y, c.y), __fmul_rn(b.y, sn.y)),
+                                                  __fsub_rn(__fmul_rn(a.z, c.z), __fmul_rn(b.z, sn.z)),
+                                                  __fsub_rn(__fmul_rn(a.w, c.w), __fmul_rn(b.w, sn.w)));
+                        qreg[hh][j + SQ / 2] = make_float4(__fadd_rn(__fmul_rn(a.x, sn.x), __fmul_rn(b.x, c.x)),
+                                                           __fadd_rn(__fmul_rn(a.y, sn.y), __fmul_rn(b.y, c.y)),
+                                                           __fadd_rn(__fmul_rn(a.z, sn.z), __fmul_rn(b.z, c.z)),
+                                                           __fadd_rn(__fmul_rn(a.w, sn.w), __fmul_rn(b.w, c.w)));
+                    }
+                }
+            }
             m_run = -INFINITY;
             l_run = 0.f;
 #pragma unroll
             for (int hh = 0; hh < GT; ++hh)
 #pragma unroll
                 for (int sv = 0; sv < SV; ++sv) acc[hh][sv] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+
+        if (h.new_key >= 0 && ((h.new_key / KPI) % W) == cw) {
+            // This warp owns the new token's row: rotate K in place if asked (lanes l and
+            // l ^ nv/2 hold the two halves of a pair), then store K and V into the cache.
+            float4* k4 = reinterpret_cast<float4*>(stage_ptr(s)) + size_t(h.new_key) * nv;
+            const float4* v4 = reinterpret_cast<const float4*>(stage_ptr(s)) + TPS * NV + size_t(h.new_key) * nv;
+            if (lane < nv) {  // nv is 16 or 32 on this path
+                float4 kv = k4[lane];
+                if (h.flags & kHdrRope) {
+                    const int half4 = nv / 2;
+                    const float4* cs4 = reinterpret_cast<const float4*>(stage_ptr(s) + Cfg::kStageFloats + GT * NV * 4);
+                    const float4* sn4 = cs4 + half4;
+                    float4 other;
+                    other.x = __shfl_xor_sync(nv == 32 ? kFull : 0x0000ffffu, kv.x, half4);
+                    other.y = __shfl_xor_sync(nv == 32 ? kFull : 0x0000ffffu, kv.y, half4);
+                    other.z = __shfl_xor_sync(nv == 32 ? kFull : 0x0000ffffu, kv.z, half4);
+                    other.w = __shfl_xor_sync(nv == 32 ? kFull : 0x0000ffffu, kv.w, half4);
+                    const bool lo = lane < half4;
+                    const float4 c = cs4[lo ? lane : lane - half4], sn = sn4[lo ? lane : lane - half4];
+                    if (lo) {  // x1*cos - x2*sin
+                        kv = make_float4(__fsub_rn(__fmul_rn(kv.x, c.x), __fmul_rn(other.x, sn.x)),
+                                         __fsub_rn(__fmul_rn(kv.y, c.y), __fmul_rn(other.y, sn.y)),
+                                         __fsub_rn(__fmul_rn(kv.z, c.z), __fmul_rn(other.z, sn.z)),
+                                         __fsub_rn(__fmul_rn(kv.w, c.w), __fmul_rn(other.w, sn.w)));
+                    } else {   // x1*sin + x2*cos
+                        kv = make_float4(__fadd_rn(__fmul_rn(other.x, sn.x), __fmul_rn(kv.x, c.x)),
+                                         __fadd_rn(__fmul_rn(other.y, sn.y), __fmul_rn(kv.y, c.y)),
+                                         __fadd_rn(__fmul_rn(other.z, sn.z), __fmul_rn(kv.z, c.z)),
+                                         __fadd_rn(__fmul_rn(other.w, sn.w), __fmul_rn(kv.w, c.w)));
+                    }
+                    k4[lane] = kv;
+                }
+                if (h.k_dst) {
+                    reinterpret_cast<float4*>(h.k_dst)[lane] = kv;
+                    reinterpret_cast<float4*>(h.v_dst)[lane] = v4[lane];
+                }
+            }
+            __syncwarp();
         }
 
         {
