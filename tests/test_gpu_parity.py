@@ -228,14 +228,17 @@ def test_seq_major_layout(ctx2b):
     p.st.destroy()
 
 
-def test_concurrent_blocking_callers_are_coalesced(ctx2b):
+def test_concurrent_blocking_callers_are_coalesced():
     # one thread per stream, each blocking in xn_attention per layer, as the reference's server
-    # slots and batch_bench do; results must equal the one-by-one oracle
+    # slots and batch_bench do; results must equal the one-by-one oracle.  The context waits up to
+    # 50 ms for all of its live streams to show up, which makes the merge deterministic here.
     import threading
 
     rng = np.random.default_rng(47)
     n, steps = 8, 6
-    pairs = [Pair(ctx2b, 512) for _ in range(n)]
+    ctx = xn.Context(num_layers=3, num_heads=20, num_kv_heads=5, head_dim=128, pool_pages=32,
+                     prefill_mode=F32, batch_window_us=50000)
+    pairs = [Pair(ctx, 512) for _ in range(n)]
     data = [[rand_qkv(rng, 20, 5, 1, 128) for _ in range(steps)] for _ in range(n)]
     got = [[None] * steps for _ in range(n)]
     errors = []
@@ -245,7 +248,7 @@ def test_concurrent_blocking_callers_are_coalesced(ctx2b):
         try:
             for s in range(steps):
                 barrier.wait()
-                got[i][s] = ctx2b.attention(pairs[i].st, s % 3, s // 3, *data[i][s])
+                got[i][s] = ctx.attention(pairs[i].st, s % 3, s // 3, *data[i][s])
         except Exception as e:  # pragma: no cover
             errors.append(e)
             barrier.abort()
@@ -258,9 +261,27 @@ def test_concurrent_blocking_callers_are_coalesced(ctx2b):
         for s in range(steps):
             want = xo.fast_attention(*data[i][s], s % 3, s // 3, pairs[i].ref, 20, 5, 128)
             assert_parity(got[i][s], want, f"thread {i} step {s}")
-    assert ctx2b.stats()["coalesced_max"] >= 2
-    for p in pairs:
-        p.st.destroy()
+    stats = ctx.stats()
+    assert stats["coalesced_max"] == n, stats
+    assert stats["batches"] == steps, stats   # one merged submission per step
+    ctx.close()
+
+
+def test_lone_blocking_caller_is_not_delayed():
+    # without a batching window a single caller is served at once; with one, it waits at most
+    # that long for company that never comes
+    import time
+
+    rng = np.random.default_rng(48)
+    ctx = xn.Context(num_layers=1, num_heads=4, num_kv_heads=2, head_dim=16, pool_pages=8,
+                     prefill_mode=F32, batch_window_us=30000)
+    a, b = ctx.new_stream(64), ctx.new_stream(64)   # two live streams, only one calls
+    ctx.attention(a, 0, 0, *rand_qkv(rng, 4, 2, 1, 16))
+    t0 = time.perf_counter()
+    ctx.attention(a, 0, 1, *rand_qkv(rng, 4, 2, 1, 16))
+    dt = time.perf_counter() - t0
+    assert 0.02 < dt < 0.5, dt
+    ctx.close()
 
 
 # ---- allocator and error behaviour -----------------------------------------------------------

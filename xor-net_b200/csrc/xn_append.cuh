@@ -182,7 +182,7 @@ __global__ void wait_probe_kernel(int* __restrict__ status, unsigned long long l
     if (threadIdx.x == 0) {
         mbar_init(&bar, 1);
         mbar_fence_init();
-        if (!mbar_wait_bounded(&bar, 0, limit_ns)) atomicExch(status, kDevWaitFull);
+        if (!mbar_wait_bounded(&bar, 0, limit_ns)) report_status(status, kDevWaitFull);
     }
 }
 

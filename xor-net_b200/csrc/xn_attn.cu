@@ -95,8 +95,10 @@ struct xn_ctx {
     float* q_rot = nullptr;    size_t q_rot_cap = 0;      // floats
     float* partials = nullptr; size_t partials_cap = 0;   // floats
     unsigned char* io_host = nullptr; unsigned char* io_dev = nullptr; size_t io_cap = 0;
-    int* status_d = nullptr;
-    int* status_h = nullptr;  // pinned
+    // Error word of the kernels' bounded waits: page-locked host memory that the kernels write
+    // directly (they only ever write it when a wait ran out), so reading it needs no copy.
+    int* status_d = nullptr;  // device-side address of the same word
+    int* status_h = nullptr;
     xn_stats stats{};
     std::string last_error;
 
@@ -299,7 +301,6 @@ int32_t check_device_status(xn_ctx* c) {
         int code = *c->status_h;
         *c->status_h = kDevOk;
         c->stats.device_wait_errors += 1;
-        cudaMemsetAsync(c->status_d, 0, sizeof(int), c->stream);
         // a kernel that gave up may have left its arrival counters half-way
         cudaMemsetAsync(c->sync_d, 0, c->sync_cap * sizeof(int), c->stream);
         return fail(c, XN_ERR_DEVICE_WAIT, "a kernel gave up on a bounded wait (code %d)", code);
@@ -626,8 +627,6 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
                                        cudaMemcpyDeviceToHost, c->stream));
             c->stats.d2h_bytes += io_out;
         }
-        XN_CUDA(c, cudaMemcpyAsync(c->status_h, c->status_d, sizeof(int), cudaMemcpyDeviceToHost,
-                                   c->stream));
     }
     XN_CUDA(c, cudaEventRecord(slot->ev, c->stream));
     slot->used = true;
@@ -831,10 +830,9 @@ int32_t xn_ctx_create(const xn_ctx_desc* d, xn_ctx** out_ctx) {
     c->sync_cap = size_t(c->decode_chunks) + 8;  // a unit is cut at most once per chunk boundary
     XN_CREATE_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->sync_d), c->sync_cap * sizeof(int)));
     XN_CREATE_CUDA(cudaMemsetAsync(c->sync_d, 0, c->sync_cap * sizeof(int), c->stream));
-    XN_CREATE_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->status_d), sizeof(int)));
-    XN_CREATE_CUDA(cudaMemsetAsync(c->status_d, 0, sizeof(int), c->stream));
-    XN_CREATE_CUDA(cudaMallocHost(reinterpret_cast<void**>(&c->status_h), sizeof(int)));
+    XN_CREATE_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&c->status_h), sizeof(int), cudaHostAllocMapped));
     *c->status_h = kDevOk;
+    XN_CREATE_CUDA(cudaHostGetDevicePointer(reinterpret_cast<void**>(&c->status_d), c->status_h, 0));
 
     {
         SplitKernel k = pick_split(c->nv_class, c->gt, c->nv_exact);
@@ -905,7 +903,6 @@ int32_t xn_ctx_destroy(xn_ctx* c) {
     if (c->io_host) cudaFreeHost(c->io_host);
     if (c->io_dev) cudaFree(c->io_dev);
     if (c->sync_d) cudaFree(c->sync_d);
-    if (c->status_d) cudaFree(c->status_d);
     if (c->status_h) cudaFreeHost(c->status_h);
     if (c->cos_d) cudaFree(c->cos_d);
     if (c->sin_d) cudaFree(c->sin_d);
@@ -922,7 +919,6 @@ int32_t xn_ctx_synchronize(xn_ctx* c) {
     if (!ctx_ok(c)) return XN_ERR_HANDLE;
     std::lock_guard<std::mutex> g(c->mu);
     XN_CUDA(c, cudaSetDevice(c->device));
-    XN_CUDA(c, cudaMemcpyAsync(c->status_h, c->status_d, sizeof(int), cudaMemcpyDeviceToHost, c->stream));
     XN_CUDA(c, cudaStreamSynchronize(c->stream));
     return check_device_status(c);
 }
@@ -1225,7 +1221,6 @@ int32_t xn_debug_expire_wait(xn_ctx* c, int32_t timeout_ms) {
     wait_probe_kernel<<<1, 32, 0, c->stream>>>(c->status_d, (unsigned long long)timeout_ms * 1000000ull);
     c->stats.kernel_launches += 1;
     XN_CUDA(c, cudaGetLastError());
-    XN_CUDA(c, cudaMemcpyAsync(c->status_h, c->status_d, sizeof(int), cudaMemcpyDeviceToHost, c->stream));
     XN_CUDA(c, cudaStreamSynchronize(c->stream));
     return check_device_status(c);
 }

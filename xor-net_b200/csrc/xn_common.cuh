@@ -10,6 +10,13 @@ constexpr int kPageTokens = 64;  // tokens per KV page
 // Device error word values written by kernels whose bounded waits ran out.
 enum : int { kDevOk = 0, kDevWaitFull = 1, kDevWaitEmpty = 2, kDevBadIndex = 3, kDevWaitMma = 4 };
 
+// The status word lives in page-locked host memory mapped into the device: a plain store, made
+// visible to the host, is all a kernel needs when one of its bounded waits ran out.
+__device__ __forceinline__ void report_status(int* status, int code) {
+    *reinterpret_cast<volatile int*>(status) = code;
+    __threadfence_system();
+}
+
 // ---- plan structures (built on the host per batch, copied once to the device) ---------------
 
 // One attention request as the kernels see it.  Strides are in floats.

@@ -280,7 +280,7 @@ attn_splitkv_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restrict__
                                 const int tile = tb + tt;
                                 const int s = fill % ST;
                                 if (fill >= ST && !mbar_wait_bounded(&empty_bar[s], ((fill / ST) - 1) & 1)) {
-                                    atomicExch(status, kDevWaitEmpty);
+                                    report_status(status, kDevWaitEmpty);
                                     *abort_flag = 1;
                                     ok = false;
                                 } else {
@@ -344,7 +344,7 @@ attn_splitkv_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restrict__
                 // end-of-work marker
                 const int s = fill % ST;
                 if (fill >= ST && !mbar_wait_bounded(&empty_bar[s], ((fill / ST) - 1) & 1)) {
-                    atomicExch(status, kDevWaitEmpty);
+                    report_status(status, kDevWaitEmpty);
                     *abort_flag = 1;
                 } else {
                     StageHdr h = {};
@@ -394,7 +394,7 @@ attn_splitkv_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restrict__
         const bool got = __all_sync(kFull, mbar_wait_bounded(&full_bar[s], (fill / ST) & 1));
         DT_END(tm_wait)
         if (!got) {
-            atomicExch(status, kDevWaitFull);
+            report_status(status, kDevWaitFull);
             *abort_flag = 1;
             break;  // the producer notices the flag or runs into its own bounded wait
         }

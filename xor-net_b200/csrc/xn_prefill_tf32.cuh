@@ -284,7 +284,7 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap k_map,
                 for (int p = 2 * j; p < min(2 * j + 2, n_pages) && ok; ++p) ok = load_v_page(p);
                 if (*abort_flag) break;
             }
-            if (!ok) { atomicExch(a.status, kDevWaitEmpty); *abort_flag = 1; }
+            if (!ok) { report_status(a.status, kDevWaitEmpty); *abort_flag = 1; }
         }
     } else if (warp == 1) {
         // =============================== MMA issuer ===============================
@@ -303,7 +303,7 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap k_map,
             constexpr uint64_t kVStageStep = uint64_t(kVBytes) >> 4;
             constexpr uint64_t kKBlockStep = uint64_t(kKSub) >> 4;  // next 32-float column block
             bool ok = mbar_wait_bounded(q_ready, 0);
-            if (!ok) { atomicExch(a.status, kDevWaitFull); *abort_flag = 1; }
+            if (!ok) { report_status(a.status, kDevWaitFull); *abort_flag = 1; }
             fence_after_sync();
 
             int k_st = 0, k_ph = 0;     // K ring position / parity of the next S = Q K^T
@@ -357,7 +357,7 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap k_map,
                 if (j >= 1 && !issue_pv(j - 1)) { ok = false; break; }
             }
             if (ok && !issue_pv(n_tiles - 1)) ok = false;
-            if (!ok) { atomicExch(a.status, kDevWaitMma); *abort_flag = 1; }
+            if (!ok) { report_status(a.status, kDevWaitMma); *abort_flag = 1; }
         }
     } else {
         // =============================== softmax + epilogue ===============================
@@ -447,7 +447,7 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap k_map,
                 // rescales its half of the columns
                 if (!__all_sync(kFull, mbar_wait_bounded(&pv_done[(j - 1) & 1], uint32_t(((j - 1) >> 1) & 1)))) {
                     // cannot bail out alone (the other warpgroup may not rescale): record and go on
-                    atomicExch(a.status, kDevWaitMma);
+                    report_status(a.status, kDevWaitMma);
                 }
                 fence_after_sync();
                 for (int c0 = col0; c0 < min(col0 + kPage, n_pv); c0 += 32) {
@@ -482,7 +482,7 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap k_map,
             mbar_arrive(&p_full[sb]);
             wg_barrier();  // the exchange area is rewritten by the next tile
         }
-        if (dead && lane == 0) atomicExch(a.status, kDevWaitFull);
+        if (dead && lane == 0) report_status(a.status, kDevWaitFull);
 
         // ---- epilogue: O / l -> global; each warpgroup its half of the columns
         if (!dead) {
@@ -520,7 +520,7 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap k_map,
                     }
                 }
             } else {
-                atomicExch(a.status, kDevWaitMma);
+                report_status(a.status, kDevWaitMma);
                 *abort_flag = 1;
             }
         }
