@@ -85,6 +85,21 @@ __device__ __forceinline__ float group_reduce(const float (&s)[GT], int sub) {
     return keep;
 }
 
+// acc += p * v on four lanes with two packed f32x2 FMAs (sm_100 issues two fused
+// multiply-adds per instruction this way; each component is the same correctly rounded fma).
+__device__ __forceinline__ void fma4_scalar(float4& acc, float p, const float4& v) {
+    const float2 pp = make_float2(p, p);
+    const float2 lo = __ffma2_rn(pp, make_float2(v.x, v.y), make_float2(acc.x, acc.y));
+    const float2 hi = __ffma2_rn(pp, make_float2(v.z, v.w), make_float2(acc.z, acc.w));
+    acc = make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+
+// two running partial dots (even / odd components) of q . k, again with packed FMAs
+__device__ __forceinline__ void dot4_acc(float2& part, const float4& q, const float4& k) {
+    part = __ffma2_rn(make_float2(q.x, q.y), make_float2(k.x, k.y), part);
+    part = __ffma2_rn(make_float2(q.z, q.w), make_float2(k.z, k.w), part);
+}
+
 template <int GT>
 __device__ __forceinline__ int owned_head(int sub) {
     if constexpr (GT == 4) return ((sub & 1) << 1) | ((sub >> 1) & 1);
@@ -512,23 +527,21 @@ attn_splitkv_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restrict__
             for (int i = 0; i < ITERS; ++i) {
                 const int key = i * (W * KPI) + cw * KPI + grp;
                 const float4* krow = Ks + size_t(key) * nv;
-                float part[GT];
+                float2 part2[GT];
 #pragma unroll
-                for (int hh = 0; hh < GT; ++hh) part[hh] = 0.f;
+                for (int hh = 0; hh < GT; ++hh) part2[hh] = make_float2(0.f, 0.f);
 #pragma unroll
                 for (int j = 0; j < SQ; ++j) {
                     const int idx = j * LPK + sub;
                     if (idx < nv) {
                         const float4 kv = krow[idx];
 #pragma unroll
-                        for (int hh = 0; hh < GT; ++hh) {
-                            part[hh] = fmaf(qreg[hh][j].x, kv.x, part[hh]);
-                            part[hh] = fmaf(qreg[hh][j].y, kv.y, part[hh]);
-                            part[hh] = fmaf(qreg[hh][j].z, kv.z, part[hh]);
-                            part[hh] = fmaf(qreg[hh][j].w, kv.w, part[hh]);
-                        }
+                        for (int hh = 0; hh < GT; ++hh) dot4_acc(part2[hh], qreg[hh][j], kv);
                     }
                 }
+                float part[GT];
+#pragma unroll
+                for (int hh = 0; hh < GT; ++hh) part[hh] = part2[hh].x + part2[hh].y;
                 float dot = group_reduce<GT, LPK>(part, sub);
                 // invalid keys hold stale shared memory: discard whatever came out
                 sc[i] = (key < ntok) ? dot * scale : -INFINITY;
@@ -589,12 +602,7 @@ attn_splitkv_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restrict__
                     if (idx < nv) {
                         const float4 vv = vrow[idx];
 #pragma unroll
-                        for (int hh = 0; hh < GT; ++hh) {
-                            acc[hh][sv].x = fmaf(pv[hh], vv.x, acc[hh][sv].x);
-                            acc[hh][sv].y = fmaf(pv[hh], vv.y, acc[hh][sv].y);
-                            acc[hh][sv].z = fmaf(pv[hh], vv.z, acc[hh][sv].z);
-                            acc[hh][sv].w = fmaf(pv[hh], vv.w, acc[hh][sv].w);
-                        }
+                        for (int hh = 0; hh < GT; ++hh) fma4_scalar(acc[hh][sv], pv[hh], vv);
                     }
                 }
             }
