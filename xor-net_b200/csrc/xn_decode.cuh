@@ -714,8 +714,10 @@ attn_splitkv_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restrict__
             __threadfence();
             const int old = atomicAdd(&sync[kSyncMerge0 + h.merge_slot], 1);
             const int last = old == h.part_count - 1;
-            if (last) sync[kSyncMerge0 + h.merge_slot] = 0;  // re-armed for the next launch
-            __threadfence();
+            if (last) {
+                sync[kSyncMerge0 + h.merge_slot] = 0;  // re-armed for the next launch
+                __threadfence();                       // the other partials are read after this
+            }
             *last_flag = last;
         }
         named_bar_sync(1, W * 32);
@@ -749,7 +751,8 @@ attn_splitkv_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restrict__
                 if (d + 3 < head_dim) orow[d + 3] = sum.w * inv;
             }
         }
-        named_bar_sync(1, W * 32);  // last_flag and red are reused by the next item
+        // (no barrier here: `red` and `last_flag` are next written behind the next item's barriers,
+        // which no thread passes before every thread has left this point)
         DT_END(tm_merge)
     }
 #ifdef XN_DECODE_TIMING
