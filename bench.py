@@ -638,7 +638,7 @@ def run_gpu_arm(args):
         # only valid for the unmodified c3 workload, whose per-launch work is fixed by its seed
         traffic, traffic_src = None, None
         if args.workload == "c3" and not args.streams and world == 1:
-            traffic = 708.70e6 + 6.33e6
+            traffic = 708.71e6 + 5.04e6
             traffic_src = "ncu capture of this workload (2 of 30 layers), summary under profiles/"
         line = {
             "metric": "decode_attn_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world,
