@@ -294,7 +294,7 @@ def test_pool_exhaustion_and_reuse():
     with pytest.raises(xn.XnError) as e:
         ctx.attention(b, 0, 0, *rand_qkv(rng, 2, 2, 128, 8))   # needs 2, 1 left
     assert e.value.code == 4
-    assert ctx.stats()["pages_in_use"] == 3
+    assert ctx.stats()["pages_in_use"] == 2 and b.length(0) == 0   # the refused call took nothing
     a.reset()
     b.reset()
     assert ctx.stats()["pages_in_use"] == 0
@@ -305,6 +305,23 @@ def test_pool_exhaustion_and_reuse():
     with pytest.raises(xn.XnError) as e:
         ctx.attention_batch([b, b], 0, [128, 128], *[[rand_qkv(rng, 2, 2, 1, 8)[j]] * 2 for j in range(3)])
     assert e.value.code == 1
+    ctx.close()
+
+
+def test_batch_that_does_not_fit_the_pool_touches_no_stream():
+    # the page check covers the whole batch before any stream is given pages or its length moves
+    ctx = xn.Context(1, 2, 2, 8, pool_pages=3)
+    rng = np.random.default_rng(54)
+    a, b = ctx.new_stream(1024), ctx.new_stream(1024)
+    qs, ks, vs = zip(*[rand_qkv(rng, 2, 2, 128, 8) for _ in range(2)])
+    with pytest.raises(xn.XnError) as e:
+        ctx.attention_batch([a, b], 0, [0, 0], qs, ks, vs)     # 2 + 2 pages, 3 in the pool
+    assert e.value.code == 4
+    assert ctx.stats()["pages_in_use"] == 0
+    assert a.length(0) == 0 and b.length(0) == 0 and len(a.pages()) == 0
+    p = Pair(ctx, 64)
+    got, want = p.step(0, 0, *rand_qkv(rng, 2, 2, 3, 8))       # the context is still good
+    assert_parity(got, want, "after a refused batch")
     ctx.close()
 
 

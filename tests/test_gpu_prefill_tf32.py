@@ -111,3 +111,30 @@ def test_large_scores_trigger_the_lazy_rescale():
     got, want = p.step(0, 0, q, k, v)
     check_tf32(got, want, "rescale")
     ctx.close()
+
+
+def test_unaligned_device_tensors_fall_back_to_the_exact_path():
+    # the tensor-core kernel moves whole 16-byte pieces of q and out; tensors that start off that
+    # grid are served by the exact-f32 path instead of being refused
+    import torch
+
+    rng = np.random.default_rng(5)
+    ctx = xn.Context(1, 4, 2, 64, pool_pages=8, prefill_mode=TF32)
+    p = Pair(ctx, 256)
+    S = 130
+    q, k, v = rand_qkv(rng, 4, 2, S, 64)
+    dev = torch.device("cuda:0")
+    qd = torch.zeros(q.size + 1, device=dev)
+    od = torch.zeros(q.size + 1, device=dev)
+    qd[1:] = torch.from_numpy(q.ravel()).to(dev)
+    kd, vd = torch.from_numpy(k).to(dev), torch.from_numpy(v).to(dev)
+    torch.cuda.synchronize()
+    assert (qd.data_ptr() + 4) % 16 != 0
+    reqs = ctx.make_batch([(p.st, 0, 0, S, qd.data_ptr() + 4, kd.data_ptr(), vd.data_ptr(),
+                            od.data_ptr() + 4)], xn.REQ_DEVICE_PTRS)
+    ctx.submit(reqs)
+    ctx.synchronize()
+    assert ctx.stats()["prefill_launches"] == 0
+    want = xo.fast_attention(q, k, v, 0, 0, p.ref, 4, 2, 64)
+    assert_parity(od[1:].cpu().numpy().reshape(q.shape), want, "unaligned device tensors")
+    ctx.close()

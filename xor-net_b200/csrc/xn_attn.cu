@@ -353,11 +353,19 @@ int32_t validate_req(xn_ctx* c, const xn_req& r) {
     return XN_OK;
 }
 
-// Whether a request goes to the tcgen05 prefill kernel (shape and mode only; pointer alignment is
-// re-checked at launch where the device pointers are known).
-bool use_tf32(const xn_ctx* c, const xn_req& r) {
+// Whether a request goes to the tcgen05 prefill kernel: mode, shape, and 16-byte aligned rows
+// where the kernel touches the caller's memory itself (`direct`: device or page-locked host
+// pointers; pageable host tensors pass through the library's own aligned staging).  Anything
+// else is served by the exact-f32 path.
+bool use_tf32(const xn_ctx* c, const xn_req& r, bool direct) {
     if (!c->tf32_ok || c->prefill_mode == XN_PREFILL_F32) return false;
     if (r.index_pos + r.seq_len > r.stream->cap) return false;
+    if (direct) {
+        uintptr_t bits = reinterpret_cast<uintptr_t>(r.out);
+        const bool q_scratch = (r.flags & (XN_REQ_ROPE | XN_REQ_HOST_PINNED)) != 0;  // q read from the rotation scratch
+        if (!q_scratch) bits |= reinterpret_cast<uintptr_t>(r.q);
+        if (bits & 15) return false;
+    }
     return r.seq_len >= (c->prefill_mode == XN_PREFILL_TF32 ? 2 : c->tf32_min_rows);
 }
 
@@ -368,6 +376,22 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
 
     // host memory that is page-locked and device-mapped is read and written by the kernels directly
     const bool pinned = host_mode && (reqs[0].flags & XN_REQ_HOST_PINNED);
+    const bool direct = !host_mode || pinned;
+    // -- the whole batch must fit the page pool before any stream is touched
+    {
+        long long new_pages = 0;
+        for (int i = 0; i < n; ++i) {
+            const xn_req& r = reqs[i];
+            if (r.seq_len == 0) continue;
+            const int64_t slots = std::min<int64_t>(r.index_pos + r.seq_len, r.stream->cap);
+            const int64_t need = (slots + kPageTokens - 1) / kPageTokens;
+            new_pages += std::max<int64_t>(0, need - int64_t(r.stream->pages.size()));
+        }
+        if (new_pages > (long long)c->free_pages.size())
+            return fail(c, XN_ERR_OUT_OF_PAGES,
+                        "page pool exhausted: the batch needs %lld more pages, %zu of %lld are free",
+                        new_pages, c->free_pages.size(), c->pool_pages);
+    }
     // -- pages, gaps, staging sizes
     std::vector<GapFill> gaps;
     size_t io_in = 0, io_out = 0, qrot_floats = 0, n_page_ids = 0;
@@ -392,7 +416,7 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         }
         if ((r.flags & XN_REQ_ROPE) || pinned) qrot_floats += align_up(qf, 4);
         if (end > s->cap) n_ring_rows += r.seq_len;
-        else if (use_tf32(c, r)) { /* served by the tensor-core prefill kernel */ }
+        else if (use_tf32(c, r, direct)) { /* served by the tensor-core prefill kernel */ }
         else n_units += (long long)r.seq_len * Hkv * c->subs;
         max_rows = std::max<long long>(max_rows, (long long)r.seq_len * (Hq + 2 * Hkv));
         if (pinned) {  // bytes the kernels move over PCIe themselves
@@ -485,7 +509,7 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         d.cap = int(std::min<int64_t>(s->cap, int64_t(1) << 30));
         if (r.index_pos + S > s->cap) {
             for (int t = 0; t < S; ++t) { ring_rows.push_back(i); ring_rows.push_back(t); }
-        } else if (use_tf32(c, r)) {
+        } else if (use_tf32(c, r, direct)) {
             tf32_reqs.push_back(i);
         } else {
             for (int h = 0; h < Hkv; ++h)
@@ -587,8 +611,6 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
     }
     for (int i : tf32_reqs) {
         const ReqDev& d = rd[i];
-        if ((reinterpret_cast<uintptr_t>(d.q) & 15) || (reinterpret_cast<uintptr_t>(d.out) & 15))
-            return fail(c, XN_ERR_ARG, "tensor-core prefill needs 16-byte aligned q and out");
         PrefillArgs pa;
         pa.q = d.q;
         pa.q_hs = d.q_hs;
