@@ -23,13 +23,18 @@ _lib = None
 ISA_AUTO, ISA_SCALAR, ISA_AVX2, ISA_AVX512 = 0, 1, 2, 3
 
 _f32p = C.POINTER(C.c_float)
+_i8p = C.POINTER(C.c_int8)
+_u8p = C.POINTER(C.c_uint8)
 _sz = C.c_size_t
+
+PACK4, PACK5 = 4, 5
 
 
 def build(force: bool = False) -> str:
     """Compile ``libxn_oracle.so`` beside the source if it is missing or stale."""
-    src = os.path.join(_HERE, "xn_oracle.c")
-    stale = (not os.path.exists(_LIB_PATH)) or os.path.getmtime(_LIB_PATH) < os.path.getmtime(src)
+    srcs = [os.path.join(_HERE, f) for f in ("xn_oracle.c", "xn_oracle_outproj.c", "Makefile")]
+    stale = (not os.path.exists(_LIB_PATH)) or \
+        os.path.getmtime(_LIB_PATH) < max(os.path.getmtime(f) for f in srcs)
     if force or stale:
         subprocess.run(["make", "-C", _HERE, "-B", "libxn_oracle.so"], check=True,
                        stdout=subprocess.DEVNULL)
@@ -79,6 +84,32 @@ def lib() -> C.CDLL:
             _sz, C.POINTER(_f32p), C.POINTER(_f32p), C.POINTER(_f32p), _sz, C.POINTER(_sz),
             C.POINTER(_sz), C.POINTER(C.c_void_p), _sz, _sz, _sz, C.POINTER(_f32p), C.c_int]
         L.xo_fast_attention_streams.restype = C.c_int
+        # attention output block (xn_oracle_outproj.c)
+        L.xo_rms_norm.argtypes = [_f32p, _f32p, C.c_float, _sz]
+        L.xo_rms_norm.restype = None
+        L.xo_tensor_rmsnorm.argtypes = [_f32p, _f32p, _f32p, C.c_float, _sz, _sz]
+        L.xo_tensor_rmsnorm.restype = None
+        L.xo_quantize_f32_to_i8.argtypes = [_f32p, _sz, _i8p]
+        L.xo_quantize_f32_to_i8.restype = C.c_float
+        L.xo_packed_row_bytes.argtypes = [_sz, C.c_int]
+        L.xo_packed_row_bytes.restype = _sz
+        for name in ("xo_pack4", "xo_pack5"):
+            getattr(L, name).argtypes = [_f32p, _sz, C.c_float, _u8p]
+            getattr(L, name).restype = None
+        for name in ("xo_unpack4", "xo_unpack5"):
+            getattr(L, name).argtypes = [_u8p, _sz, _f32p]
+            getattr(L, name).restype = None
+        for name in ("xo_ternary_dot_pack4", "xo_ternary_dot_pack5"):
+            getattr(L, name).argtypes = [_i8p, _u8p, _sz]
+            getattr(L, name).restype = C.c_int32
+        L.xo_ternary_linear_pack.argtypes = [_sz, _sz, _f32p, C.c_int, C.c_float, _u8p, _f32p]
+        L.xo_ternary_linear_pack.restype = None
+        L.xo_ternary_linear_forward.argtypes = [_f32p, _sz, _sz, _sz, C.c_int, _u8p, _f32p, _f32p,
+                                                C.c_int]
+        L.xo_ternary_linear_forward.restype = None
+        L.xo_attention_out_block.argtypes = [_f32p, _sz, _sz, _sz, _f32p, C.c_float, _sz, C.c_int,
+                                             _u8p, _f32p, _f32p, C.c_int]
+        L.xo_attention_out_block.restype = None
         _lib = L
     return _lib
 
@@ -246,6 +277,99 @@ def fast_attention_streams(qs, ks, vs, layer_idx, index_pos, caches, num_heads, 
         PA(*[_p(a) for a in outs]), threads)
     assert rc == 0
     return outs
+
+
+# --- attention output block: sub-norm + ternary o_proj (attention.rs:103-108) --------------------
+
+def rms_norm(x, weight, eps) -> np.ndarray:
+    """rms_norm (fast_attention_simd.rs:502-521) on one row; returns the normalised copy."""
+    x, weight = _f32(x).copy(), _f32(weight)
+    lib().xo_rms_norm(_p(x), _p(weight), eps, x.size)
+    return x
+
+
+def tensor_rmsnorm(x, weight, eps) -> np.ndarray:
+    """FastTensor::rmsnorm (tensor.rs:242-265): every row of the last dimension."""
+    x, weight = _f32(x), _f32(weight)
+    if weight.size != x.shape[-1]:
+        raise ValueError(f"FastTensor::rmsnorm weight size mismatch: expected {x.shape[-1]}, got {weight.size}")
+    out = np.empty_like(x)
+    lib().xo_tensor_rmsnorm(_p(x), _p(out), _p(weight), eps, x.size // x.shape[-1], x.shape[-1])
+    return out
+
+
+def quantize_f32_to_i8(acts):
+    """quantize_f32_to_i8 (bit1_58/quantization.rs:95-187) -> (i8 array, inv_scale)."""
+    acts = _f32(acts).ravel()
+    q = np.zeros(acts.size, dtype=np.int8)
+    inv = lib().xo_quantize_f32_to_i8(_p(acts), acts.size, q.ctypes.data_as(_i8p))
+    return q, float(np.float32(inv))
+
+
+def pack_ternary(weights, w_scale, pack_type=PACK4) -> np.ndarray:
+    w = _f32(weights).ravel()
+    out = np.zeros(lib().xo_packed_row_bytes(w.size, pack_type), dtype=np.uint8)
+    (lib().xo_pack5 if pack_type == PACK5 else lib().xo_pack4)(_p(w), w.size, w_scale,
+                                                               out.ctypes.data_as(_u8p))
+    return out
+
+
+def unpack_ternary(packed, n, pack_type=PACK4) -> np.ndarray:
+    packed = np.ascontiguousarray(packed, dtype=np.uint8)
+    out = np.zeros(n, dtype=np.float32)
+    (lib().xo_unpack5 if pack_type == PACK5 else lib().xo_unpack4)(packed.ctypes.data_as(_u8p), n,
+                                                                   _p(out))
+    return out
+
+
+def ternary_dot(acts_i8, packed, n, pack_type=PACK4) -> int:
+    a = np.ascontiguousarray(acts_i8, dtype=np.int8)
+    packed = np.ascontiguousarray(packed, dtype=np.uint8)
+    fn = lib().xo_ternary_dot_pack5 if pack_type == PACK5 else lib().xo_ternary_dot_pack4
+    return int(fn(a.ctypes.data_as(_i8p), packed.ctypes.data_as(_u8p), n))
+
+
+class TernaryLinear:
+    """TernaryLinear with the dense packed representation (bit1_58/layers.rs:34-149, 262-313)."""
+
+    def __init__(self, in_dim, out_dim, weights_f32, pack_type=PACK4, provided_scale=None):
+        w = _f32(weights_f32).ravel()
+        if w.size != in_dim * out_dim:
+            raise ValueError("Weight length must match in_dim * out_dim")
+        self.in_dim, self.out_dim, self.pack_type = in_dim, out_dim, pack_type
+        self.row_bytes = int(lib().xo_packed_row_bytes(in_dim, pack_type))
+        self.packed = np.zeros(out_dim * self.row_bytes, dtype=np.uint8)
+        self.w_scales = np.zeros(out_dim, dtype=np.float32)
+        lib().xo_ternary_linear_pack(in_dim, out_dim, _p(w), pack_type,
+                                     float("nan") if provided_scale is None else provided_scale,
+                                     self.packed.ctypes.data_as(_u8p), _p(self.w_scales))
+
+    def forward(self, x, threads: int = 0) -> np.ndarray:
+        x = _f32(x)
+        if x.ndim == 0:
+            raise ValueError("Input must have at least 1 dimension")
+        if x.shape[-1] != self.in_dim:
+            raise ValueError(f"Input dimension mismatch: expected {self.in_dim}, got {x.shape[-1]}")
+        rows = x.size // self.in_dim
+        out = np.empty(x.shape[:-1] + (self.out_dim,), dtype=np.float32)
+        lib().xo_ternary_linear_forward(_p(x), rows, self.in_dim, self.out_dim, self.pack_type,
+                                        self.packed.ctypes.data_as(_u8p), _p(self.w_scales), _p(out),
+                                        threads)
+        return out
+
+
+def attention_out_block(y, norm_weight, eps, o_proj: TernaryLinear, threads: int = 0) -> np.ndarray:
+    """y [1,Hq,S,D] -> heads_to_seq -> optional sub-norm -> o_proj -> [1,S,out_dim]
+    (models/llama/attention.rs:103-108)."""
+    y = _f32(y)
+    _, H, S, D = y.shape
+    out = np.empty((1, S, o_proj.out_dim), dtype=np.float32)
+    nw = _f32(norm_weight) if norm_weight is not None else None
+    lib().xo_attention_out_block(_p(y), H, S, D, _p(nw) if nw is not None else None, eps,
+                                 o_proj.out_dim, o_proj.pack_type,
+                                 o_proj.packed.ctypes.data_as(_u8p), _p(o_proj.w_scales), _p(out),
+                                 threads)
+    return out
 
 
 # --- independent f64 arbiter -------------------------------------------------------------------

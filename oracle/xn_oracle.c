@@ -65,6 +65,14 @@ XO_API int xo_active_isa(void) {
     return XO_ISA_SCALAR;
 }
 
+/* Whether the i8 activation quantiser takes its AVX-512 body: the reference tests avx512f alone
+ * there (src/bit1_58/quantization.rs:148-165).  Used by xn_oracle_outproj.c. */
+int xo_quant_uses_avx512(void) {
+    if (g_isa_force == XO_ISA_SCALAR || g_isa_force == XO_ISA_AVX2) return 0;
+    if (g_isa_force == XO_ISA_AVX512) return 1;
+    return cpu_has_avx512f();
+}
+
 /* ------------------------------------------------------------------------- */
 /* batched_dot_product  (src/nn/fast_attention_simd.rs:527-664)               */
 /* ------------------------------------------------------------------------- */
