@@ -91,12 +91,16 @@ enum {
     XN_REQ_SEQ_MAJOR = 1u << 2,   /* q,k,v,out are [seq_len, heads*head_dim] (the layout before  */
                                   /* transpose_seq_to_heads, tensor.rs:332-354, and after        */
                                   /* transpose_heads_to_seq, tensor.rs:356-376)                  */
-    XN_REQ_HOST_PINNED = 1u << 3  /* host pointers are page-locked, device-mapped memory         */
+    XN_REQ_HOST_PINNED = 1u << 3, /* host pointers are page-locked, device-mapped memory         */
                                   /* (cudaHostAlloc / cudaHostRegister): the kernels read the    */
                                   /* inputs and write the output over PCIe themselves and the    */
                                   /* library's staging copies are skipped.  The call still       */
                                   /* blocks until the output is complete.  All requests of a     */
                                   /* batch must agree on this flag.                              */
+    XN_REQ_OUT_PROJ = 1u << 4     /* `out` receives [seq_len, out_dim]: the attention output run */
+                                  /* through the layer's output block (xn_out_proj_set) on the   */
+                                  /* device, i.e. what models/llama/attention.rs:103-108 does    */
+                                  /* after fast_attention returns                                */
 };
 
 typedef struct xn_req {
@@ -125,6 +129,7 @@ typedef struct xn_stats {
     uint64_t streams_live;
     uint64_t device_wait_errors;
     uint64_t coalesced_max;    /* largest number of blocking callers merged into one batch      */
+    uint64_t out_proj_rows;    /* token rows run through the attention output block             */
 } xn_stats;
 
 /* ---- context --------------------------------------------------------------------------------- */
@@ -240,6 +245,51 @@ XN_API int32_t xn_fill_normal(xn_ctx* ctx, float* device_ptr, int64_t n, uint64_
 XN_API int64_t xn_stream_len(xn_ctx* ctx, xn_stream* stream, int32_t layer);
 /* Copies the stream's page table (page ids in position order) into `out`; returns the count. */
 XN_API int64_t xn_stream_pages(xn_ctx* ctx, xn_stream* stream, int32_t* out, int64_t max_out);
+
+/* ---- attention output block: sub-norm + ternary o_proj ---------------------------------------- */
+
+/* Packing of ternary weights, TernaryPackType (src/bit1_58/quantization.rs:1-5). */
+enum {
+    XN_PACK4 = 4, /* four 2-bit codes per byte  (pack_1_58bit_4pack, quantization.rs:7-27)        */
+    XN_PACK5 = 5  /* five base-3 digits per byte (pack_1_58bit_5pack, quantization.rs:49-72)      */
+};
+
+/* The tensors CausalSelfAttention holds for the tail of its forward pass
+ * (src/models/llama/attention.rs:38-40, loaded at :147-163): the o_proj TernaryLinear in its
+ * dense representation (src/bit1_58/layers.rs:34-41: packed rows + per-row scales) and the optional
+ * inner_attn_ln / attn_sub_norm FastRmsNorm (src/nn/fast_rmsnorm.rs:5-17).  The sparse
+ * representation (TernaryRep::Sparse) is not taken. */
+typedef struct xn_out_proj_desc {
+    int32_t layer;
+    int32_t in_dim;           /* must equal num_heads * head_dim                                  */
+    int32_t out_dim;
+    int32_t pack_type;        /* XN_PACK4 or XN_PACK5                                             */
+    const uint8_t* packed;    /* host: out_dim rows of ceil(in_dim/4) or ceil(in_dim/5) bytes     */
+    const float* w_scales;    /* host: [out_dim]                                                  */
+    const float* norm_weight; /* host: [in_dim], or NULL when the model has no sub-norm           */
+    float norm_eps;
+    uint32_t reserved;
+} xn_out_proj_desc;
+
+/* Uploads (or replaces) the output block of one layer.  Requests of that layer may then carry
+ * XN_REQ_OUT_PROJ. */
+XN_API int32_t xn_out_proj_set(xn_ctx* ctx, const xn_out_proj_desc* desc);
+
+/* The output block on its own: y is [rows, in_dim] (the sequence-major attention output), out is
+ * [rows, out_dim] = o_proj(sub_norm(y)): FastRmsNorm::forward (src/nn/fast_rmsnorm.rs:15-17,
+ * src/tensor.rs:242-265) then TernaryLinear::forward (src/bit1_58/layers.rs:262-313).  flags: 0 for
+ * host pointers (blocks), XN_REQ_DEVICE_PTRS for device pointers (enqueues).  Given the same y the
+ * result equals the reference's AVX-512 build bit for bit (integer dot products; the float steps
+ * keep its order of operations). */
+XN_API int32_t xn_out_proj(xn_ctx* ctx, int32_t layer, int32_t rows, const float* y, float* out,
+                           uint32_t flags);
+
+/* TernaryLinear::new with the dense representation (src/bit1_58/layers.rs:91-149), on the host:
+ * ternarises and packs `weights` [out_dim, in_dim].  provided_scale: NaN for None.  packed must
+ * hold out_dim * ceil(in_dim / pack) bytes, w_scales out_dim floats.  No GPU needed. */
+XN_API int32_t xn_ternary_pack(int32_t in_dim, int32_t out_dim, const float* weights,
+                               int32_t pack_type, float provided_scale, uint8_t* packed,
+                               float* w_scales);
 
 /* ---- host-side planning, exposed for tests (no GPU needed) ----------------------------------- */
 

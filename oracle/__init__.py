@@ -84,6 +84,8 @@ def lib() -> C.CDLL:
             _sz, C.POINTER(_f32p), C.POINTER(_f32p), C.POINTER(_f32p), _sz, C.POINTER(_sz),
             C.POINTER(_sz), C.POINTER(C.c_void_p), _sz, _sz, _sz, C.POINTER(_f32p), C.c_int]
         L.xo_fast_attention_streams.restype = C.c_int
+        L.xo_set_quant_body.argtypes = [C.c_int]
+        L.xo_set_quant_body.restype = C.c_int
         # attention output block (xn_oracle_outproj.c)
         L.xo_rms_norm.argtypes = [_f32p, _f32p, C.c_float, _sz]
         L.xo_rms_norm.restype = None
@@ -296,6 +298,11 @@ def tensor_rmsnorm(x, weight, eps) -> np.ndarray:
     out = np.empty_like(x)
     lib().xo_tensor_rmsnorm(_p(x), _p(out), _p(weight), eps, x.size // x.shape[-1], x.shape[-1])
     return out
+
+
+def set_quant_body(body: int) -> int:
+    """-1: the quantiser follows the ISA level; 0: scalar body; 1: AVX-512 body (any CPU)."""
+    return lib().xo_set_quant_body(body)
 
 
 def quantize_f32_to_i8(acts):

@@ -67,7 +67,18 @@ XO_API int xo_active_isa(void) {
 
 /* Whether the i8 activation quantiser takes its AVX-512 body: the reference tests avx512f alone
  * there (src/bit1_58/quantization.rs:148-165).  Used by xn_oracle_outproj.c. */
+static int g_quant_body = -1; /* -1: follow the ISA level; 0 scalar body; 1 AVX-512 body */
+
+/* Selects the quantiser body regardless of the CPU (both are restated in portable C), so that the
+ * rounding of either build of the reference can be checked anywhere. */
+XO_API int xo_set_quant_body(int body) {
+    if (body < -1 || body > 1) return -1;
+    g_quant_body = body;
+    return 0;
+}
+
 int xo_quant_uses_avx512(void) {
+    if (g_quant_body >= 0) return g_quant_body;
     if (g_isa_force == XO_ISA_SCALAR || g_isa_force == XO_ISA_AVX2) return 0;
     if (g_isa_force == XO_ISA_AVX512) return 1;
     return cpu_has_avx512f();

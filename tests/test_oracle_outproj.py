@@ -110,17 +110,20 @@ def test_quantize_rounding_follows_the_selected_body():
     acts[1] = 0.5       # tie inside the first whole chunk
     acts[2] = 2.5
     acts[17] = 0.5      # tie inside the tail
-    old = xo.active_isa()
     try:
-        assert xo.set_isa(xo.ISA_SCALAR) == 0
+        assert xo.set_quant_body(0) == 0
         q, _ = xo.quantize_f32_to_i8(acts)
         assert (q[1], q[2], q[17]) == (1, 3, 1)
-        if xo.set_isa(xo.ISA_AVX512) == 0:
-            q, _ = xo.quantize_f32_to_i8(acts)
-            assert (q[1], q[2], q[17]) == (0, 2, 1)
+        assert xo.set_quant_body(1) == 0
+        q, _ = xo.quantize_f32_to_i8(acts)
+        assert (q[1], q[2], q[17]) == (0, 2, 1)
+        xo.set_quant_body(-1)
+        assert xo.set_isa(xo.ISA_SCALAR) == 0          # the ISA level selects the body too
+        q, _ = xo.quantize_f32_to_i8(acts)
+        assert (q[1], q[2], q[17]) == (1, 3, 1)
     finally:
+        xo.set_quant_body(-1)
         xo.set_isa(xo.ISA_AUTO)
-    assert xo.active_isa() == old
 
 
 # ---- tests/tensor_rmsnorm_tests.rs, tests/tensor_ops_tests.rs -----------------------------------

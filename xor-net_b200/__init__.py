@@ -5,13 +5,15 @@ this package is the Python host side.  Importing it never falls back to a CPU pa
 if the library is not built or no sm_100 device is present.
 """
 from ._build import LIB_PATH, build_library
-from .api import (Context, DeviceKvCache, FastTensor, Stream, XnError, close_default_contexts,
-                  default_context, fast_attention, rope_tables)
+from .api import (Context, DeviceKvCache, FastTensor, Stream, TernaryLinear, XnError,
+                  close_default_contexts, default_context, fast_attention, rope_tables)
 from . import sharding
-from ._ffi import REQ_DEVICE_PTRS, REQ_HOST_PINNED, REQ_ROPE, REQ_SEQ_MAJOR, SIGNATURES, load
+from ._ffi import (PACK4, PACK5, REQ_DEVICE_PTRS, REQ_HOST_PINNED, REQ_OUT_PROJ, REQ_ROPE,
+                   REQ_SEQ_MAJOR, SIGNATURES, load)
 
 __all__ = [
     "Context", "Stream", "DeviceKvCache", "FastTensor", "XnError", "fast_attention", "rope_tables",
     "default_context", "close_default_contexts", "build_library", "load", "LIB_PATH", "SIGNATURES",
-    "REQ_DEVICE_PTRS", "REQ_ROPE", "REQ_SEQ_MAJOR", "REQ_HOST_PINNED", "sharding",
+    "REQ_DEVICE_PTRS", "REQ_ROPE", "REQ_SEQ_MAJOR", "REQ_HOST_PINNED", "REQ_OUT_PROJ", "PACK4",
+    "PACK5", "TernaryLinear", "sharding",
 ]

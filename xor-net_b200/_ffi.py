@@ -33,10 +33,17 @@ class Stats(C.Structure):
     _fields_ = [(n, C.c_uint64) for n in (
         "calls", "batches", "kernel_launches", "decode_launches", "prefill_launches", "h2d_bytes",
         "d2h_bytes", "pages_total", "pages_in_use", "streams_live", "device_wait_errors",
-        "coalesced_max")]
+        "coalesced_max", "out_proj_rows")]
 
 
-REQ_DEVICE_PTRS, REQ_ROPE, REQ_SEQ_MAJOR, REQ_HOST_PINNED = 1, 2, 4, 8
+class OutProjDesc(C.Structure):
+    _fields_ = [("layer", C.c_int32), ("in_dim", C.c_int32), ("out_dim", C.c_int32),
+                ("pack_type", C.c_int32), ("packed", C.c_void_p), ("w_scales", C.c_void_p),
+                ("norm_weight", C.c_void_p), ("norm_eps", C.c_float), ("reserved", C.c_uint32)]
+
+
+REQ_DEVICE_PTRS, REQ_ROPE, REQ_SEQ_MAJOR, REQ_HOST_PINNED, REQ_OUT_PROJ = 1, 2, 4, 8, 16
+PACK4, PACK5 = 4, 5
 
 STATUS_NAMES = {
     0: "XN_OK", 1: "XN_ERR_ARG", 2: "XN_ERR_SHAPE", 3: "XN_ERR_HANDLE", 4: "XN_ERR_OUT_OF_PAGES",
@@ -80,6 +87,10 @@ SIGNATURES = {
     "xn_plan_split": (C.c_int32, [C.c_int32, c_i32p, C.c_int32, C.c_int32, C.c_int32, c_i32p,
                                   c_i32p, c_i32p, c_i32p, c_i32p, c_i32p, c_i32p]),
     "xn_debug_expire_wait": (C.c_int32, [C.c_void_p, C.c_int32]),
+    "xn_out_proj_set": (C.c_int32, [C.c_void_p, C.POINTER(OutProjDesc)]),
+    "xn_out_proj": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_uint32]),
+    "xn_ternary_pack": (C.c_int32, [C.c_int32, C.c_int32, C.c_void_p, C.c_int32, C.c_float,
+                                    C.c_void_p, C.c_void_p]),
     "xn_version": (C.c_char_p, []),
 }
 

@@ -21,7 +21,8 @@ from typing import Optional, Sequence
 import numpy as np
 
 from . import _ffi
-from ._ffi import REQ_DEVICE_PTRS, REQ_HOST_PINNED, REQ_ROPE, REQ_SEQ_MAJOR, CtxDesc, Req, Stats
+from ._ffi import (PACK4, PACK5, REQ_DEVICE_PTRS, REQ_HOST_PINNED, REQ_OUT_PROJ, REQ_ROPE, REQ_SEQ_MAJOR,
+                   CtxDesc, OutProjDesc, Req, Stats)
 
 
 class XnError(RuntimeError):
@@ -176,6 +177,27 @@ class Context:
             return (ms.value, int(n.value)), (pms.value, int(pn.value))
         return (pms.value, int(pn.value)) if which == "prefill" else (ms.value, int(n.value))
 
+    # -- attention output block (sub-norm + ternary o_proj) ------------------------------------
+
+    def set_out_proj(self, layer: int, linear: "TernaryLinear", norm_weight=None, eps: float = 1e-5):
+        """xn_out_proj_set: the o_proj weights (and optional sub-norm) of one layer."""
+        d = OutProjDesc()
+        d.layer, d.in_dim, d.out_dim, d.pack_type = layer, linear.in_dim, linear.out_dim, linear.pack_type
+        d.packed, d.w_scales = linear.packed.ctypes.data, _ptr(linear.w_scales)
+        nw = _f32(norm_weight) if norm_weight is not None else None
+        d.norm_weight, d.norm_eps = (_ptr(nw) if nw is not None else None), eps
+        self._check(self.lib.xn_out_proj_set(self.handle, C.byref(d)))
+        self._out_dims = getattr(self, "_out_dims", {})
+        self._out_dims[layer] = linear.out_dim
+
+    def out_proj(self, layer: int, y) -> np.ndarray:
+        """xn_out_proj on host arrays: y [..., in_dim] -> [..., out_dim]."""
+        y = _f32(y)
+        out = np.empty(y.shape[:-1] + (self._out_dims[layer],), dtype=np.float32)
+        rows = y.size // y.shape[-1] if y.size else 0
+        self._check(self.lib.xn_out_proj(self.handle, layer, rows, _ptr(y), _ptr(out), 0))
+        return out
+
     # -- blocking single-stream calls (host arrays) ------------------------------------------
 
     def attention(self, stream: Stream, layer: int, index_pos: int, q, k, v, rope: bool = False):
@@ -202,15 +224,22 @@ class Context:
     def submit(self, reqs, n: Optional[int] = None):
         self._check(self.lib.xn_attention_batch(self.handle, len(reqs) if n is None else n, reqs))
 
-    def attention_batch(self, streams, layer, index_pos, qs, ks, vs, rope=False, seq_major=False):
-        """Host-array batch: one request per stream; returns the list of outputs."""
+    def attention_batch(self, streams, layer, index_pos, qs, ks, vs, rope=False, seq_major=False,
+                        out_proj=False):
+        """Host-array batch: one request per stream; returns the list of outputs
+        ([1,S,out_dim] each with ``out_proj``: the layer's output block applied on the device)."""
         qs = [_f32(a) for a in qs]
         ks = [_f32(a) for a in ks]
         vs = [_f32(a) for a in vs]
         seq = [a.shape[-2] for a in qs]  # [1,H,S,D] and [1,S,H*D] both keep S there
-        outs = [np.empty_like(a) for a in qs]
         layers = layer if isinstance(layer, (list, tuple)) else [layer] * len(streams)
-        flags = (REQ_ROPE if rope else 0) | (REQ_SEQ_MAJOR if seq_major else 0)
+        if out_proj:
+            outs = [np.empty((1, seq[i], self._out_dims[layers[i]]), dtype=np.float32)
+                    for i in range(len(qs))]
+        else:
+            outs = [np.empty_like(a) for a in qs]
+        flags = (REQ_ROPE if rope else 0) | (REQ_SEQ_MAJOR if seq_major else 0) | \
+            (REQ_OUT_PROJ if out_proj else 0)
         reqs = self.make_batch(
             [(st, layers[i], int(index_pos[i]), int(seq[i]), _ptr(qs[i]), _ptr(ks[i]), _ptr(vs[i]),
               _ptr(outs[i])) for i, st in enumerate(streams)], flags)
@@ -221,6 +250,31 @@ class Context:
 # =============================================================================================
 # The reference's operator interface for this path
 # =============================================================================================
+
+class TernaryLinear:
+    """Host mirror of ``TernaryLinear`` with the dense packed representation
+    (src/bit1_58/layers.rs:34-149): ternarises and packs f32 weights exactly like
+    ``TernaryLinear::new``; the forward pass runs on the device through a Context
+    (``Context.set_out_proj`` / ``Context.out_proj`` / ``REQ_OUT_PROJ``)."""
+
+    def __init__(self, in_dim: int, out_dim: int, weights_f32, pack_type: int = PACK4,
+                 provided_scale: Optional[float] = None):
+        w = _f32(weights_f32).ravel()
+        if w.size != in_dim * out_dim:
+            raise ValueError("Weight length must match in_dim * out_dim")
+        if pack_type not in (PACK4, PACK5):
+            raise ValueError("pack_type must be PACK4 or PACK5")
+        self.in_dim, self.out_dim, self.pack_type = in_dim, out_dim, pack_type
+        self.row_bytes = (in_dim + 4) // 5 if pack_type == PACK5 else (in_dim + 3) // 4
+        self.packed = np.zeros(max(1, out_dim * self.row_bytes), dtype=np.uint8)
+        self.w_scales = np.zeros(max(1, out_dim), dtype=np.float32)
+        rc = _ffi.load().xn_ternary_pack(in_dim, out_dim, _ptr(w), pack_type,
+                                         float("nan") if provided_scale is None else provided_scale,
+                                         self.packed.ctypes.data, _ptr(self.w_scales))
+        if rc != 0:
+            raise XnError(rc, "xn_ternary_pack")
+        self.w_scales = self.w_scales[:out_dim]
+
 
 class FastTensor:
     """``FastTensor { data: Vec<f32>, shape: Vec<usize> }`` (src/tensor.rs:6-33)."""

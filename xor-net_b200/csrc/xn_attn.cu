@@ -18,9 +18,11 @@
 #include "xn_append.cuh"
 #include "xn_common.cuh"
 #include "xn_decode.cuh"
+#include "xn_outproj.cuh"
 #include "xn_plan.hpp"
 #include "xn_prefill_tf32.cuh"
 #include "xn_static_decode.cuh"
+#include "xn_ternary.hpp"
 
 using namespace xn;
 
@@ -41,6 +43,24 @@ struct PlanSlot {
     cudaEvent_t ev = nullptr;     // recorded after the last launch that reads the slot
     cudaEvent_t up_ev = nullptr;  // recorded after the plan upload on the copy stream
     bool used = false;
+};
+
+// Output block of one layer on the device (xn_out_proj_set).
+struct OutProj {
+    bool set = false;
+    int in_dim = 0, out_dim = 0;
+    int q_stride = 0;  // bytes per quantised activation row (in_dim rounded up to 64)
+    int w_stride = 0;  // bytes per 2-bit weight row (q_stride / 4)
+    uint8_t* w2 = nullptr;
+    float* w_scales = nullptr;
+    float* norm_w = nullptr;  // nullptr: no sub-norm
+    float eps = 0.f;
+};
+
+// A run of consecutive token rows that go through the same layer's output block.
+struct OutRun {
+    int layer;
+    int row_begin, row_count;
 };
 
 struct Pending {
@@ -94,6 +114,10 @@ struct xn_ctx {
     int next_slot = 0;
     float* q_rot = nullptr;    size_t q_rot_cap = 0;      // floats
     float* partials = nullptr; size_t partials_cap = 0;   // floats
+    // attention output block (sub-norm + ternary o_proj)
+    std::vector<OutProj> out_proj;                         // per layer
+    float* attn_seq = nullptr; size_t attn_seq_cap = 0;    // floats: sequence-major attention rows
+    float* q8 = nullptr; size_t q8_cap = 0;                // floats: i8 activation rows + inverse scales
     unsigned char* io_host = nullptr; unsigned char* io_dev = nullptr; size_t io_cap = 0;
     // Error word of the kernels' bounded waits: page-locked host memory that the kernels write
     // directly (they only ever write it when a wait ran out), so reading it needs no copy.
@@ -328,6 +352,34 @@ int32_t profile_end(xn_ctx* c) {
     return XN_OK;
 }
 
+// ---- attention output block ----------------------------------------------------------------
+
+size_t q8_floats(const xn_ctx* c, size_t rows) {
+    const size_t q_stride = align_up(size_t(c->num_heads) * c->head_dim, 64);
+    return align_up(rows * q_stride / 4, 4) + rows + 4;
+}
+
+// Sub-norm, quantiser and ternary projection of `n_rows` token rows; rows_d[i] names the source
+// row (in_dim floats) and the destination row (out_dim floats) of row i.  `row0` is the index of
+// the first row inside the context's quantised-activation buffer, which holds `rows_total` rows.
+int32_t launch_out_block(xn_ctx* c, int layer, const OutRowDev* rows_d, int n_rows, size_t row0,
+                         size_t rows_total) {
+    const OutProj& op = c->out_proj[size_t(layer)];
+    int8_t* q = reinterpret_cast<int8_t*>(c->q8) + row0 * size_t(op.q_stride);
+    float* inv = c->q8 + align_up(rows_total * size_t(op.q_stride) / 4, 4) + row0;
+    subnorm_quant_kernel<<<unsigned(n_rows), 256, size_t(op.in_dim) * 4, c->stream>>>(
+        rows_d, op.norm_w, op.eps, op.in_dim, q, op.q_stride, inv);
+    const int R = std::max(1, std::min(kOutMaxRowsPerCta, (op.out_dim + c->sm_count - 1) / c->sm_count));
+    dim3 grid(unsigned((op.out_dim + R - 1) / R), unsigned((n_rows + kOutRowsTile - 1) / kOutRowsTile));
+    ternary_gemm_kernel<<<grid, 256, kOutGemmSmem, c->stream>>>(q, op.q_stride, inv, op.w2, op.w_stride,
+                                                                op.w_scales, rows_d, n_rows,
+                                                                op.out_dim, R);
+    c->stats.kernel_launches += 2;
+    c->stats.out_proj_rows += uint64_t(n_rows);
+    XN_CUDA(c, cudaGetLastError());
+    return XN_OK;
+}
+
 // ---- one batched submission ----------------------------------------------------------------
 
 struct GapFill {
@@ -350,6 +402,8 @@ int32_t validate_req(xn_ctx* c, const xn_req& r) {
             return fail(c, XN_ERR_CAPACITY, "position %lld beyond the RoPE table (%d rows)",
                         (long long)(r.index_pos + r.seq_len), c->max_pos);
     }
+    if ((r.flags & XN_REQ_OUT_PROJ) && !c->out_proj[size_t(r.layer)].set)
+        return fail(c, XN_ERR_ARG, "XN_REQ_OUT_PROJ: layer %d has no output block (xn_out_proj_set)", r.layer);
     return XN_OK;
 }
 
@@ -361,7 +415,8 @@ bool use_tf32(const xn_ctx* c, const xn_req& r, bool direct) {
     if (!c->tf32_ok || c->prefill_mode == XN_PREFILL_F32) return false;
     if (r.index_pos + r.seq_len > r.stream->cap) return false;
     if (direct) {
-        uintptr_t bits = reinterpret_cast<uintptr_t>(r.out);
+        // with XN_REQ_OUT_PROJ the kernel writes into the library's own (aligned) row buffer
+        uintptr_t bits = (r.flags & XN_REQ_OUT_PROJ) ? 0 : reinterpret_cast<uintptr_t>(r.out);
         const bool q_scratch = (r.flags & (XN_REQ_ROPE | XN_REQ_HOST_PINNED)) != 0;  // q read from the rotation scratch
         if (!q_scratch) bits |= reinterpret_cast<uintptr_t>(r.q);
         if (bits & 15) return false;
@@ -394,7 +449,7 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
     }
     // -- pages, gaps, staging sizes
     std::vector<GapFill> gaps;
-    size_t io_in = 0, io_out = 0, qrot_floats = 0, n_page_ids = 0;
+    size_t io_in = 0, io_out = 0, qrot_floats = 0, n_page_ids = 0, out_rows = 0;
     long long n_units = 0, n_ring_rows = 0;
     int max_rows = 0;
     for (int i = 0; i < n; ++i) {
@@ -410,9 +465,12 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         hw = std::max(hw, end);
         n_page_ids += s->pages.size();
         const size_t qf = size_t(Hq) * r.seq_len * D, kvf = size_t(Hkv) * r.seq_len * D;
+        const bool proj = r.flags & XN_REQ_OUT_PROJ;
+        const size_t of = proj ? size_t(r.seq_len) * c->out_proj[size_t(r.layer)].out_dim : qf;  // floats returned
+        if (proj) out_rows += size_t(r.seq_len);
         if (host_mode && !pinned) {
             io_in += align_up(qf * 4, 16) + 2 * align_up(kvf * 4, 16);
-            io_out += align_up(qf * 4, 16);
+            io_out += align_up(of * 4, 16);
         }
         if ((r.flags & XN_REQ_ROPE) || pinned) qrot_floats += align_up(qf, 4);
         if (end > s->cap) n_ring_rows += r.seq_len;
@@ -421,7 +479,7 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         max_rows = std::max<long long>(max_rows, (long long)r.seq_len * (Hq + 2 * Hkv));
         if (pinned) {  // bytes the kernels move over PCIe themselves
             c->stats.h2d_bytes += (qf + 2 * kvf) * 4;
-            c->stats.d2h_bytes += qf * 4;
+            c->stats.d2h_bytes += of * 4;
         }
     }
     // Pure decode batches (one new token per request) let the attention kernel append, and rotate,
@@ -449,6 +507,10 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
 
     int32_t rc;
     if ((rc = grow_device(c, &c->q_rot, &c->q_rot_cap, qrot_floats)) != XN_OK) return rc;
+    if (out_rows) {
+        if ((rc = grow_device(c, &c->attn_seq, &c->attn_seq_cap, out_rows * size_t(Hq) * D)) != XN_OK) return rc;
+        if ((rc = grow_device(c, &c->q8, &c->q8_cap, q8_floats(c, out_rows))) != XN_OK) return rc;
+    }
     if (host_mode && (rc = grow_io(c, io_in + io_out)) != XN_OK) return rc;
 
     // -- request descriptors, page ids, units
@@ -461,6 +523,9 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
     kv_lens.reserve(size_t(n_units));
     std::vector<int32_t> ring_rows;
     std::vector<int> tf32_reqs;
+    std::vector<OutRowDev> out_row_tab;
+    out_row_tab.reserve(out_rows);
+    std::vector<OutRun> out_runs;
     size_t in_off = 0, out_off = io_in, qrot_off = 0;
     for (int i = 0; i < n; ++i) {
         const xn_req& r = reqs[i];
@@ -483,7 +548,8 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
             v_dev = reinterpret_cast<const float*>(c->io_dev + in_off);
             in_off += align_up(kvf * 4, 16);
             o_dev = reinterpret_cast<float*>(c->io_dev + out_off);
-            out_off += align_up(qf * 4, 16);
+            out_off += align_up(((r.flags & XN_REQ_OUT_PROJ)
+                                     ? size_t(S) * c->out_proj[size_t(r.layer)].out_dim : qf) * 4, 16);
         }
         const bool seq_major = r.flags & XN_REQ_SEQ_MAJOR;
         const long long q_hs = seq_major ? D : (long long)S * D, q_ts = seq_major ? (long long)Hq * D : D;
@@ -502,6 +568,17 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         }
         d.k = k_dev; d.v = v_dev; d.kv_hs = kv_hs; d.kv_ts = kv_ts;
         d.out = o_dev; d.o_hs = q_hs; d.o_ts = q_ts;
+        if (r.flags & XN_REQ_OUT_PROJ) {
+            // the attention kernels write sequence-major rows into the block's input buffer
+            const OutProj& op = c->out_proj[size_t(r.layer)];
+            const size_t row0 = out_row_tab.size();
+            float* rows = c->attn_seq + row0 * size_t(op.in_dim);
+            d.out = rows; d.o_hs = D; d.o_ts = op.in_dim;
+            for (int t = 0; t < S; ++t)
+                out_row_tab.push_back({rows + size_t(t) * op.in_dim, o_dev + size_t(t) * op.out_dim});
+            if (!out_runs.empty() && out_runs.back().layer == r.layer) out_runs.back().row_count += S;
+            else out_runs.push_back({r.layer, int(row0), S});
+        }
         d.page_off = int(page_ids.size());
         d.n_pages = int(s->pages.size());
         page_ids.insert(page_ids.end(), s->pages.begin(), s->pages.end());
@@ -550,6 +627,7 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
     const size_t o_cta = place(sizeof(int32_t) * sp.cta_item_begin.size());
     const size_t o_page = place(sizeof(int32_t) * page_ids.size());
     const size_t o_ring = place(sizeof(int32_t) * ring_rows.size());
+    const size_t o_rows = place(sizeof(OutRowDev) * out_row_tab.size());
     PlanSlot* slot = nullptr;
     if ((rc = acquire_slot(c, off, &slot)) != XN_OK) return rc;
     memcpy(slot->host + o_req, rd.data(), sizeof(ReqDev) * n);
@@ -559,6 +637,8 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
     memcpy(slot->host + o_cta, sp.cta_item_begin.data(), sizeof(int32_t) * sp.cta_item_begin.size());
     if (!page_ids.empty()) memcpy(slot->host + o_page, page_ids.data(), sizeof(int32_t) * page_ids.size());
     if (!ring_rows.empty()) memcpy(slot->host + o_ring, ring_rows.data(), sizeof(int32_t) * ring_rows.size());
+    if (!out_row_tab.empty())
+        memcpy(slot->host + o_rows, out_row_tab.data(), sizeof(OutRowDev) * out_row_tab.size());
     // The plan does not depend on anything in flight: upload it on the copy stream so that it
     // overlaps the previous submission's kernels, and make the launch stream wait for it.
     // (A blocking host-pointer call has nothing in flight to overlap with: plain in-stream copy.)
@@ -642,6 +722,12 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         c->stats.kernel_launches += 1;
     }
     XN_CUDA(c, cudaGetLastError());
+    for (const OutRun& run : out_runs) {
+        const OutRowDev* rows_d = reinterpret_cast<const OutRowDev*>(slot->dev + o_rows) + run.row_begin;
+        if ((rc = launch_out_block(c, run.layer, rows_d, run.row_count, size_t(run.row_begin),
+                                   out_row_tab.size())) != XN_OK)
+            return rc;
+    }
 
     if (host_mode) {
         if (io_out) {
@@ -662,9 +748,11 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         size_t o = io_in;
         for (int i = 0; i < n; ++i) {
             if (reqs[i].seq_len == 0) continue;
-            const size_t qf = size_t(Hq) * reqs[i].seq_len * D;
-            memcpy(reqs[i].out, c->io_host + o, qf * 4);
-            o += align_up(qf * 4, 16);
+            const size_t of = (reqs[i].flags & XN_REQ_OUT_PROJ)
+                                  ? size_t(reqs[i].seq_len) * c->out_proj[size_t(reqs[i].layer)].out_dim
+                                  : size_t(Hq) * reqs[i].seq_len * D;
+            memcpy(reqs[i].out, c->io_host + o, of * 4);
+            o += align_up(of * 4, 16);
         }
     }
     return XN_OK;
@@ -790,6 +878,7 @@ int32_t xn_ctx_create(const xn_ctx_desc* d, xn_ctx** out_ctx) {
     c->prefill_mode = d->prefill_mode;
     c->batch_window_us = d->batch_window_us;
     c->sm_count = prop.multiProcessorCount;
+    c->out_proj.resize(size_t(d->num_layers));
     c->decode_ctas = c->sm_count;
     if (const char* env = getenv("XORNET_ATTN_DECODE_CTAS")) {
         int v = atoi(env);
@@ -920,6 +1009,13 @@ int32_t xn_ctx_destroy(xn_ctx* c) {
         if (s.up_ev) cudaEventDestroy(s.up_ev);
     }
     for (cudaEvent_t e : c->prof_events) cudaEventDestroy(e);
+    for (OutProj& op : c->out_proj) {
+        if (op.w2) cudaFree(op.w2);
+        if (op.w_scales) cudaFree(op.w_scales);
+        if (op.norm_w) cudaFree(op.norm_w);
+    }
+    if (c->attn_seq) cudaFree(c->attn_seq);
+    if (c->q8) cudaFree(c->q8);
     if (c->q_rot) cudaFree(c->q_rot);
     if (c->partials) cudaFree(c->partials);
     if (c->io_host) cudaFreeHost(c->io_host);
@@ -1233,6 +1329,117 @@ int64_t xn_stream_pages(xn_ctx* c, xn_stream* s, int32_t* out, int64_t max_out) 
     const int64_t n = int64_t(s->pages.size());
     for (int64_t i = 0; i < n && i < max_out && out; ++i) out[i] = s->pages[size_t(i)];
     return n;
+}
+
+// ---- attention output block ------------------------------------------------------------------
+
+int32_t xn_ternary_pack(int32_t in_dim, int32_t out_dim, const float* weights, int32_t pack_type,
+                        float provided_scale, uint8_t* packed, float* w_scales) {
+    if (in_dim < 0 || out_dim < 0 || !weights || !packed || !w_scales) return XN_ERR_ARG;
+    if (pack_type != XN_PACK4 && pack_type != XN_PACK5) return XN_ERR_ARG;
+    ternary_linear_pack(size_t(in_dim), size_t(out_dim), weights, pack_type, !std::isnan(provided_scale),
+                        provided_scale, packed, w_scales);
+    return XN_OK;
+}
+
+int32_t xn_out_proj_set(xn_ctx* c, const xn_out_proj_desc* d) {
+    if (!ctx_ok(c)) return XN_ERR_HANDLE;
+    std::lock_guard<std::mutex> g(c->mu);
+    if (!d || !d->packed || !d->w_scales) return fail(c, XN_ERR_ARG, "null descriptor or weight pointer");
+    if (d->layer < 0 || d->layer >= c->num_layers)
+        return fail(c, XN_ERR_ARG, "layer %d outside 0..%d", d->layer, c->num_layers - 1);
+    if (d->in_dim != c->num_heads * c->head_dim)
+        return fail(c, XN_ERR_SHAPE, "Input dimension mismatch: expected %d, got %d",
+                    c->num_heads * c->head_dim, d->in_dim);
+    if (d->out_dim <= 0 || d->out_dim > (1 << 20)) return fail(c, XN_ERR_SHAPE, "out_dim %d outside 1..2^20", d->out_dim);
+    if (d->pack_type != XN_PACK4 && d->pack_type != XN_PACK5)
+        return fail(c, XN_ERR_ARG, "pack_type must be XN_PACK4 or XN_PACK5");
+    if (size_t(d->in_dim) * 4 > 200 * 1024) return fail(c, XN_ERR_CAPACITY, "in_dim %d is beyond one block's shared memory", d->in_dim);
+    XN_CUDA(c, cudaSetDevice(c->device));
+    XN_CUDA(c, cudaStreamSynchronize(c->stream));  // launches in flight may still read the old block
+
+    OutProj op;
+    op.in_dim = d->in_dim;
+    op.out_dim = d->out_dim;
+    op.q_stride = int(align_up(size_t(d->in_dim), 64));
+    op.w_stride = op.q_stride / 4;
+    op.eps = d->norm_eps;
+    const size_t bpr = packed_row_bytes(size_t(d->in_dim), d->pack_type);
+    std::vector<uint8_t> w2(size_t(d->out_dim) * op.w_stride);
+    for (int o = 0; o < d->out_dim; ++o)
+        recode_row_2bit(d->packed + size_t(o) * bpr, size_t(d->in_dim), d->pack_type,
+                        w2.data() + size_t(o) * op.w_stride, size_t(op.w_stride));
+    auto upload = [&](void** dst, const void* src, size_t bytes) -> cudaError_t {
+        cudaError_t e = cudaMalloc(dst, bytes);
+        if (e != cudaSuccess) return e;
+        return cudaMemcpy(*dst, src, bytes, cudaMemcpyHostToDevice);
+    };
+    cudaError_t e = upload(reinterpret_cast<void**>(&op.w2), w2.data(), w2.size());
+    if (e == cudaSuccess) e = upload(reinterpret_cast<void**>(&op.w_scales), d->w_scales, size_t(d->out_dim) * 4);
+    if (e == cudaSuccess && d->norm_weight)
+        e = upload(reinterpret_cast<void**>(&op.norm_w), d->norm_weight, size_t(d->in_dim) * 4);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(reinterpret_cast<const void*>(ternary_gemm_kernel),
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, kOutGemmSmem);
+    if (e == cudaSuccess && size_t(d->in_dim) * 4 > 48 * 1024)
+        e = cudaFuncSetAttribute(reinterpret_cast<const void*>(subnorm_quant_kernel),
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, d->in_dim * 4);
+    if (e != cudaSuccess) {
+        if (op.w2) cudaFree(op.w2);
+        if (op.w_scales) cudaFree(op.w_scales);
+        if (op.norm_w) cudaFree(op.norm_w);
+        return fail(c, XN_ERR_CUDA, "uploading the output block failed: %s", cudaGetErrorString(e));
+    }
+    OutProj& old = c->out_proj[size_t(d->layer)];
+    if (old.w2) cudaFree(old.w2);
+    if (old.w_scales) cudaFree(old.w_scales);
+    if (old.norm_w) cudaFree(old.norm_w);
+    op.set = true;
+    old = op;
+    return XN_OK;
+}
+
+int32_t xn_out_proj(xn_ctx* c, int32_t layer, int32_t rows, const float* y, float* out, uint32_t flags) {
+    if (!ctx_ok(c)) return XN_ERR_HANDLE;
+    std::lock_guard<std::mutex> g(c->mu);
+    if (layer < 0 || layer >= c->num_layers || !c->out_proj[size_t(layer)].set)
+        return fail(c, XN_ERR_ARG, "layer %d has no output block (xn_out_proj_set)", layer);
+    if (rows < 0 || (rows > 0 && (!y || !out))) return fail(c, XN_ERR_ARG, "bad rows or null tensor pointer");
+    if (flags & ~uint32_t(XN_REQ_DEVICE_PTRS)) return fail(c, XN_ERR_ARG, "only XN_REQ_DEVICE_PTRS is accepted here");
+    if (rows == 0) return XN_OK;
+    XN_CUDA(c, cudaSetDevice(c->device));
+    const OutProj& op = c->out_proj[size_t(layer)];
+    const bool dev = flags & XN_REQ_DEVICE_PTRS;
+    const size_t in_b = size_t(rows) * op.in_dim * 4, out_b = size_t(rows) * op.out_dim * 4;
+    int32_t rc;
+    if ((rc = grow_device(c, &c->q8, &c->q8_cap, q8_floats(c, size_t(rows)))) != XN_OK) return rc;
+    const float* src = y;
+    float* dst = out;
+    if (!dev) {
+        if ((rc = grow_io(c, align_up(in_b, 16) + out_b)) != XN_OK) return rc;
+        memcpy(c->io_host, y, in_b);
+        XN_CUDA(c, cudaMemcpyAsync(c->io_dev, c->io_host, in_b, cudaMemcpyHostToDevice, c->stream));
+        c->stats.h2d_bytes += in_b;
+        src = reinterpret_cast<const float*>(c->io_dev);
+        dst = reinterpret_cast<float*>(c->io_dev + align_up(in_b, 16));
+    }
+    PlanSlot* slot = nullptr;
+    if ((rc = acquire_slot(c, sizeof(OutRowDev) * size_t(rows), &slot)) != XN_OK) return rc;
+    OutRowDev* tab = reinterpret_cast<OutRowDev*>(slot->host);
+    for (int t = 0; t < rows; ++t) tab[t] = {src + size_t(t) * op.in_dim, dst + size_t(t) * op.out_dim};
+    XN_CUDA(c, cudaMemcpyAsync(slot->dev, slot->host, sizeof(OutRowDev) * size_t(rows),
+                               cudaMemcpyHostToDevice, c->stream));
+    rc = launch_out_block(c, layer, reinterpret_cast<const OutRowDev*>(slot->dev), rows, 0, size_t(rows));
+    XN_CUDA(c, cudaEventRecord(slot->ev, c->stream));
+    slot->used = true;
+    if (rc != XN_OK) return rc;
+    if (!dev) {
+        XN_CUDA(c, cudaMemcpyAsync(c->io_host + align_up(in_b, 16), dst, out_b, cudaMemcpyDeviceToHost, c->stream));
+        XN_CUDA(c, cudaStreamSynchronize(c->stream));
+        c->stats.d2h_bytes += out_b;
+        memcpy(out, c->io_host + align_up(in_b, 16), out_b);
+    }
+    return XN_OK;
 }
 
 int32_t xn_debug_expire_wait(xn_ctx* c, int32_t timeout_ms) {

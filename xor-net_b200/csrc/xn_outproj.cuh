@@ -1,0 +1,199 @@
+// The attention output block on the device: heads->sequence layout (done by the attention kernels'
+// output strides), the optional sub-norm (RMSNorm), the i8 activation quantiser and the ternary
+// output projection (src/models/llama/attention.rs:103-108 of the reference).
+//
+// Everything after the RMS sum is integer work or single rounded multiplies, so given the same
+// attention output the projected rows equal the reference's bit for bit:
+//   * rms_norm (src/nn/fast_attention_simd.rs:453-521): squares rounded to f32 and added to ONE
+//     accumulator in index order (all three ISA bodies do that), rms = sqrt(sum/n + eps),
+//     (x * (1/rms)) * weight;
+//   * quantize_f32_to_i8, AVX-512 body (src/bit1_58/quantization.rs:97-143): scale = 127/max|x|,
+//     whole 16-element chunks round to nearest EVEN after clamping, the tail rounds half away from
+//     zero; inverse scale max|x|/127 (both 1 for an all-zero row);
+//   * TernaryLinear::forward (src/bit1_58/layers.rs:262-313): (i32 dot as f32 * inv_scale) * w_scale.
+#pragma once
+#include "xn_common.cuh"
+
+namespace xn {
+
+// One token row of the block: where the attention output row lives (in_dim floats) and where the
+// projected row goes (out_dim floats).
+struct OutRowDev {
+    const float* src;
+    float* dst;
+};
+
+constexpr int kOutRowsTile = 64;    // token rows per GEMM block
+constexpr int kOutKChunk = 1280;    // activation bytes per row staged at a time (multiple of 128)
+constexpr int kOutMaxRowsPerCta = 32;
+constexpr int kOutActStride = kOutKChunk + 16;  // conflict-free 16-byte reads by 8 consecutive lanes
+constexpr int kOutGemmSmem = kOutRowsTile * kOutActStride + kOutMaxRowsPerCta * kOutKChunk;
+
+// ---- sub-norm + quantiser: one block per token row ---------------------------------------------
+//
+// The sum of squares is a 1-thread dependent chain on purpose (see the header: the reference's
+// order is the only one that reproduces its bits); the other threads stage the row, then
+// normalise, reduce max|x| (order-free) and quantise.  Dynamic shared memory: in_dim floats.
+__global__ void __launch_bounds__(256)
+subnorm_quant_kernel(const OutRowDev* __restrict__ rows, const float* __restrict__ norm_w, float eps,
+                     int in_dim, int8_t* __restrict__ q_out, int q_stride,
+                     float* __restrict__ inv_scale_out) {
+    extern __shared__ float row_s[];
+    __shared__ float red_s[8];
+    __shared__ float bc_s;
+    const int r = blockIdx.x;
+    const float* src = rows[r].src;
+    const int tid = threadIdx.x;
+    const bool vec = (in_dim % 4 == 0) && ((reinterpret_cast<uintptr_t>(src) & 15) == 0);
+    if (vec) {
+        for (int i = tid * 4; i < in_dim; i += blockDim.x * 4)
+            *reinterpret_cast<float4*>(row_s + i) = *reinterpret_cast<const float4*>(src + i);
+    } else {
+        for (int i = tid; i < in_dim; i += blockDim.x) row_s[i] = src[i];
+    }
+    __syncthreads();
+    if (norm_w != nullptr) {
+        if (tid == 0) {
+            float sum_sq = 0.f;
+            int i = 0;
+            for (; i + 8 <= in_dim; i += 8) {
+                const float4 a = *reinterpret_cast<const float4*>(row_s + i);
+                const float4 b = *reinterpret_cast<const float4*>(row_s + i + 4);
+                sum_sq = __fadd_rn(sum_sq, __fmul_rn(a.x, a.x));
+                sum_sq = __fadd_rn(sum_sq, __fmul_rn(a.y, a.y));
+                sum_sq = __fadd_rn(sum_sq, __fmul_rn(a.z, a.z));
+                sum_sq = __fadd_rn(sum_sq, __fmul_rn(a.w, a.w));
+                sum_sq = __fadd_rn(sum_sq, __fmul_rn(b.x, b.x));
+                sum_sq = __fadd_rn(sum_sq, __fmul_rn(b.y, b.y));
+                sum_sq = __fadd_rn(sum_sq, __fmul_rn(b.z, b.z));
+                sum_sq = __fadd_rn(sum_sq, __fmul_rn(b.w, b.w));
+            }
+            for (; i < in_dim; ++i) sum_sq = __fadd_rn(sum_sq, __fmul_rn(row_s[i], row_s[i]));
+            const float rms = __fsqrt_rn(__fadd_rn(__fdiv_rn(sum_sq, float(in_dim)), eps));
+            bc_s = __fdiv_rn(1.0f, rms);
+        }
+        __syncthreads();
+        const float inv_rms = bc_s;
+        for (int i = tid; i < in_dim; i += blockDim.x)
+            row_s[i] = __fmul_rn(__fmul_rn(row_s[i], inv_rms), norm_w[i]);
+        __syncthreads();
+    }
+    float m = 0.f;
+    for (int i = tid; i < in_dim; i += blockDim.x) m = fmaxf(m, fabsf(row_s[i]));
+    for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if ((tid & 31) == 0) red_s[tid >> 5] = m;
+    __syncthreads();
+    m = red_s[0];
+    for (int w = 1; w < int(blockDim.x >> 5); ++w) m = fmaxf(m, red_s[w]);
+    const float scale = m > 0.f ? __fdiv_rn(127.0f, m) : 1.0f;
+    if (tid == 0) inv_scale_out[r] = m > 0.f ? __fdiv_rn(m, 127.0f) : 1.0f;
+    const int simd_end = (in_dim / 16) * 16;
+    int8_t* q = q_out + size_t(r) * q_stride;
+    for (int i = tid; i < q_stride; i += blockDim.x) {
+        int v = 0;
+        if (i < in_dim) {
+            const float s = __fmul_rn(row_s[i], scale);
+            if (i < simd_end) v = __float2int_rn(fmaxf(-127.0f, fminf(127.0f, s)));
+            else v = int(fmaxf(-127.0f, fminf(127.0f, roundf(s))));
+        }
+        q[i] = int8_t(v);
+    }
+}
+
+// ---- ternary projection: i8 activations x 2-bit weights -> f32 rows ---------------------------
+//
+// Device weight format: 2 bits per weight, weight i of a row in bits 2(i%4).. of byte i/4 with the
+// reference's pack4 codes (0 -> -1, 1 -> 0, 2 -> +1, 3 -> 0; bit1_58/quantization.rs:7-47); rows
+// padded with code 1 to a multiple of 64 weights.  pack5 weights are re-coded on the host.
+//
+// Block = 64 token rows x `rows_per_cta` output rows.  The activations of the tile and the decoded
+// weights are staged in shared memory one 1280-column chunk at a time; lane l of each warp owns
+// tokens l and l+32, warp w the output rows w, w+8, ...; every 16 columns cost two 16-byte
+// activation reads plus, per output row, one broadcast 16-byte weight read and eight dp4a.
+
+__device__ __forceinline__ uint32_t decode4(uint32_t byte_codes) {
+    // four 2-bit codes (one byte) -> four i8 in one word
+    const uint32_t x = (byte_codes | (byte_codes << 6) | (byte_codes << 12) | (byte_codes << 18)) & 0x03030303u;
+    const uint32_t nz = (x & 0x01010101u) ^ 0x01010101u;      // 1 where the code is even (weight != 0)
+    const uint32_t pos = (x >> 1) & nz;                       // 1 where the weight is +1
+    const uint32_t neg = nz ^ pos;                            // 1 where the weight is -1
+    return pos | ((neg << 8) - neg);                          // -1 = 0xff per byte
+}
+
+__global__ void __launch_bounds__(256)
+ternary_gemm_kernel(const int8_t* __restrict__ q, int q_stride, const float* __restrict__ inv_scale,
+                    const uint8_t* __restrict__ w2, int w_stride, const float* __restrict__ w_scales,
+                    const OutRowDev* __restrict__ rows, int n_rows, int out_dim, int rows_per_cta) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    int8_t* act_s = reinterpret_cast<int8_t*>(smem_raw);
+    int8_t* w_s = act_s + kOutRowsTile * kOutActStride;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int o0 = blockIdx.x * rows_per_cta;
+    const int R = min(rows_per_cta, out_dim - o0);
+    const int t0 = blockIdx.y * kOutRowsTile;
+    int acc[2][4];
+#pragma unroll
+    for (int a = 0; a < 2; ++a)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[a][j] = 0;
+
+    for (int k0 = 0; k0 < q_stride; k0 += kOutKChunk) {
+        const int kc = min(kOutKChunk, q_stride - k0);  // multiple of 16
+        const int kv = kc / 16;
+        for (int e = tid; e < kOutRowsTile * kv; e += blockDim.x) {
+            const int t = e / kv, c = e % kv;
+            int4 v = make_int4(0, 0, 0, 0);
+            if (t0 + t < n_rows)
+                v = *reinterpret_cast<const int4*>(q + size_t(t0 + t) * q_stride + k0 + c * 16);
+            *reinterpret_cast<int4*>(act_s + t * kOutActStride + c * 16) = v;
+        }
+        for (int e = tid; e < R * kv; e += blockDim.x) {
+            const int rr = e / kv, c = e % kv;
+            const uint32_t codes = *reinterpret_cast<const uint32_t*>(
+                w2 + size_t(o0 + rr) * w_stride + (k0 + c * 16) / 4);
+            int4 v;
+            v.x = int(decode4(codes & 0xffu));
+            v.y = int(decode4((codes >> 8) & 0xffu));
+            v.z = int(decode4((codes >> 16) & 0xffu));
+            v.w = int(decode4(codes >> 24));
+            *reinterpret_cast<int4*>(w_s + rr * kOutKChunk + c * 16) = v;
+        }
+        __syncthreads();
+        const int8_t* a0p = act_s + lane * kOutActStride;
+        const int8_t* a1p = act_s + (lane + 32) * kOutActStride;
+        for (int c = 0; c < kv; ++c) {
+            const int4 a0 = *reinterpret_cast<const int4*>(a0p + c * 16);
+            const int4 a1 = *reinterpret_cast<const int4*>(a1p + c * 16);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int rr = warp + 8 * j;
+                if (rr < R) {
+                    const int4 w = *reinterpret_cast<const int4*>(w_s + rr * kOutKChunk + c * 16);
+                    acc[0][j] = __dp4a(a0.x, w.x, acc[0][j]);
+                    acc[0][j] = __dp4a(a0.y, w.y, acc[0][j]);
+                    acc[0][j] = __dp4a(a0.z, w.z, acc[0][j]);
+                    acc[0][j] = __dp4a(a0.w, w.w, acc[0][j]);
+                    acc[1][j] = __dp4a(a1.x, w.x, acc[1][j]);
+                    acc[1][j] = __dp4a(a1.y, w.y, acc[1][j]);
+                    acc[1][j] = __dp4a(a1.z, w.z, acc[1][j]);
+                    acc[1][j] = __dp4a(a1.w, w.w, acc[1][j]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int a = 0; a < 2; ++a) {
+        const int t = t0 + lane + 32 * a;
+        if (t >= n_rows) continue;
+        const float is = inv_scale[t];
+        float* dst = rows[t].dst;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int rr = warp + 8 * j;
+            if (rr < R) dst[o0 + rr] = __fmul_rn(__fmul_rn(float(acc[a][j]), is), w_scales[o0 + rr]);
+        }
+    }
+}
+
+}  // namespace xn
