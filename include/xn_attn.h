@@ -152,6 +152,10 @@ XN_API const char* xn_last_error(xn_ctx* ctx);
  * last read and returns them (milliseconds) with the number of launches they cover; any output
  * pointer may be NULL. */
 XN_API int32_t xn_profile_enable(xn_ctx* ctx, int32_t on);
+/* The same for every timed kind: ms and launches are arrays of XN_PROFILE_KINDS entries
+ * (0 split-KV attention, 1 tensor-core prefill, 2 output block = sub-norm + projection pair). */
+#define XN_PROFILE_KINDS 3
+XN_API int32_t xn_profile_read_all(xn_ctx* ctx, double* ms, uint64_t* launches);
 XN_API int32_t xn_profile_read(xn_ctx* ctx, double* splitkv_ms, uint64_t* splitkv_launches,
                                double* prefill_ms, uint64_t* prefill_launches);
 

@@ -62,6 +62,25 @@ def test_block_alone_is_bit_exact(Hq, D, out_dim, pack, norm, rows):
     ctx.close()
 
 
+@pytest.mark.parametrize("rows", [1, 64, 65, 128, 129, 300, 700])
+def test_tensor_core_and_cuda_core_projections_agree(rows, monkeypatch):
+    # the tcgen05 (kind::i8) kernel and the dp4a kernel compute the same integers; token tiles of
+    # 64 / 128 / 256 rows, ragged last tile, output rows that do not fill the last 128-row block
+    rng = np.random.default_rng(rows)
+    Hq, D, out_dim = 6, 64, 200
+    dev, ref, nw = make_block(rng, Hq, D, out_dim, xn.PACK4)
+    y = rng.standard_normal((rows, Hq * D)).astype(np.float32)
+    outs = []
+    for tc in ("1", "0"):
+        monkeypatch.setenv("XORNET_ATTN_OUTPROJ_TC", tc)
+        ctx = xn.Context(1, Hq, 1, D, pool_pages=1)
+        ctx.set_out_proj(0, dev, nw, 1e-5)
+        outs.append(ctx.out_proj(0, y))
+        ctx.close()
+    assert np.array_equal(outs[0], outs[1])
+    assert np.array_equal(outs[0], ref_block(ref, nw, 1e-5, y))
+
+
 def test_rounding_ties_follow_the_avx512_body():
     # rows whose scale is exactly 1 (max |x| = 127) with values on .5: whole chunks round to even,
     # the tail rounds half away from zero; an all-zero row has scale 1 and gives zeros

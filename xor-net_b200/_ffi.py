@@ -87,6 +87,7 @@ SIGNATURES = {
     "xn_plan_split": (C.c_int32, [C.c_int32, c_i32p, C.c_int32, C.c_int32, C.c_int32, c_i32p,
                                   c_i32p, c_i32p, c_i32p, c_i32p, c_i32p, c_i32p]),
     "xn_debug_expire_wait": (C.c_int32, [C.c_void_p, C.c_int32]),
+    "xn_profile_read_all": (C.c_int32, [C.c_void_p, C.POINTER(C.c_double), C.POINTER(C.c_uint64)]),
     "xn_out_proj_set": (C.c_int32, [C.c_void_p, C.POINTER(OutProjDesc)]),
     "xn_out_proj": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_uint32]),
     "xn_ternary_pack": (C.c_int32, [C.c_int32, C.c_int32, C.c_void_p, C.c_int32, C.c_float,

@@ -177,6 +177,12 @@ class Context:
             return (ms.value, int(n.value)), (pms.value, int(pn.value))
         return (pms.value, int(pn.value)) if which == "prefill" else (ms.value, int(n.value))
 
+    def profile_read_all(self):
+        """[(milliseconds, launches)] per timed kind: split-KV, tensor-core prefill, output block."""
+        ms, n = (C.c_double * 3)(), (C.c_uint64 * 3)()
+        self._check(self.lib.xn_profile_read_all(self.handle, ms, n))
+        return [(ms[i], int(n[i])) for i in range(3)]
+
     # -- attention output block (sub-norm + ternary o_proj) ------------------------------------
 
     def set_out_proj(self, layer: int, linear: "TernaryLinear", norm_weight=None, eps: float = 1e-5):

@@ -19,6 +19,7 @@
 #include "xn_common.cuh"
 #include "xn_decode.cuh"
 #include "xn_outproj.cuh"
+#include "xn_outproj_tc.cuh"
 #include "xn_plan.hpp"
 #include "xn_prefill_tf32.cuh"
 #include "xn_static_decode.cuh"
@@ -49,7 +50,7 @@ struct PlanSlot {
 struct OutProj {
     bool set = false;
     int in_dim = 0, out_dim = 0;
-    int q_stride = 0;  // bytes per quantised activation row (in_dim rounded up to 64)
+    int q_stride = 0;  // bytes per quantised activation row (in_dim rounded up to 128)
     int w_stride = 0;  // bytes per 2-bit weight row (q_stride / 4)
     uint8_t* w2 = nullptr;
     float* w_scales = nullptr;
@@ -60,7 +61,8 @@ struct OutProj {
 // A run of consecutive token rows that go through the same layer's output block.
 struct OutRun {
     int layer;
-    int row_begin, row_count;
+    int row_begin, row_count;  // rows of the submission's row table
+    size_t q_row0;             // first row in the quantised-activation buffer (multiple of 256)
 };
 
 struct Pending {
@@ -97,6 +99,7 @@ struct xn_ctx {
     int decode_chunks = 0;   // chunks the tile list is cut into (several per block)
     bool fuse_append = true; // decode batches: the attention kernel appends the new token itself
     bool fuse_pinned = true; // ... also when q,k,v live in page-locked host memory
+    bool out_tc = true;      // output projection on the tensor cores (else the dp4a kernel)
     int* sync_d = nullptr;   // chunk counter, done counter, per-unit arrival counters
     size_t sync_cap = 0;     // ints
     cudaStream_t stream = nullptr;
@@ -134,7 +137,7 @@ struct xn_ctx {
     // optional device timing of the split-KV kernel
     bool profile = false;
     std::vector<cudaEvent_t> prof_events;  // pairs (start, stop), reused
-    std::vector<int> prof_kind;            // per pair: 0 split-KV, 1 prefill
+    std::vector<int> prof_kind;            // per pair: 0 split-KV, 1 prefill, 2 output block
     size_t prof_used = 0;
 
     // combining of concurrent blocking callers
@@ -241,15 +244,21 @@ EncodeTiledFn encode_tiled_fn() {
 
 // f32 tensor of `rank` dims (dims[0] innermost, contiguous), byte strides for dims 1..rank-1,
 // box of box[] elements, the given 128-byte swizzle flavour, zero fill outside the tensor.
-bool make_map_f32(CUtensorMap* map, const void* base, int rank, const cuuint64_t* dims,
-                  const cuuint64_t* strides_bytes, const cuuint32_t* box,
-                  CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
+bool make_map(CUtensorMap* map, CUtensorMapDataType type, const void* base, int rank,
+              const cuuint64_t* dims, const cuuint64_t* strides_bytes, const cuuint32_t* box,
+              CUtensorMapSwizzle swizzle) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return false;
     cuuint32_t estr[5] = {1, 1, 1, 1, 1};
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, cuuint32_t(rank), const_cast<void*>(base), dims,
-              strides_bytes, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
-              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    return fn(map, type, cuuint32_t(rank), const_cast<void*>(base), dims, strides_bytes, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool make_map_f32(CUtensorMap* map, const void* base, int rank, const cuuint64_t* dims,
+                  const cuuint64_t* strides_bytes, const cuuint32_t* box,
+                  CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
+    return make_map(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, base, rank, dims, strides_bytes, box, swizzle);
 }
 
 // ---- buffers -----------------------------------------------------------------------------
@@ -354,26 +363,40 @@ int32_t profile_end(xn_ctx* c) {
 
 // ---- attention output block ----------------------------------------------------------------
 
-size_t q8_floats(const xn_ctx* c, size_t rows) {
-    const size_t q_stride = align_up(size_t(c->num_heads) * c->head_dim, 64);
-    return align_up(rows * q_stride / 4, 4) + rows + 4;
+// Floats of the quantised-activation buffer for `rows_pad` rows (a multiple of 256): the tiled i8
+// rows, then one inverse scale per row.
+size_t q8_floats(const xn_ctx* c, size_t rows_pad) {
+    const size_t q_stride = align_up(size_t(c->num_heads) * c->head_dim, 128);
+    return rows_pad * q_stride / 4 + rows_pad + 4;
 }
 
 // Sub-norm, quantiser and ternary projection of `n_rows` token rows; rows_d[i] names the source
-// row (in_dim floats) and the destination row (out_dim floats) of row i.  `row0` is the index of
-// the first row inside the context's quantised-activation buffer, which holds `rows_total` rows.
-int32_t launch_out_block(xn_ctx* c, int layer, const OutRowDev* rows_d, int n_rows, size_t row0,
-                         size_t rows_total) {
+// row (in_dim floats) and the destination row (out_dim floats) of row i.  The rows occupy rows
+// [q_row0, q_row0 + n_rows) of the context's quantised-activation buffer, which holds q_rows_pad
+// rows (both multiples of 256).
+int32_t launch_out_block(xn_ctx* c, int layer, const OutRowDev* rows_d, int n_rows, size_t q_row0,
+                         size_t q_rows_pad) {
     const OutProj& op = c->out_proj[size_t(layer)];
-    int8_t* q = reinterpret_cast<int8_t*>(c->q8) + row0 * size_t(op.q_stride);
-    float* inv = c->q8 + align_up(rows_total * size_t(op.q_stride) / 4, 4) + row0;
-    subnorm_quant_kernel<<<unsigned(n_rows), 256, size_t(op.in_dim) * 4, c->stream>>>(
-        rows_d, op.norm_w, op.eps, op.in_dim, q, op.q_stride, inv);
-    const int R = std::max(1, std::min(kOutMaxRowsPerCta, (op.out_dim + c->sm_count - 1) / c->sm_count));
-    dim3 grid(unsigned((op.out_dim + R - 1) / R), unsigned((n_rows + kOutRowsTile - 1) / kOutRowsTile));
-    ternary_gemm_kernel<<<grid, 256, kOutGemmSmem, c->stream>>>(q, op.q_stride, inv, op.w2, op.w_stride,
-                                                                op.w_scales, rows_d, n_rows,
-                                                                op.out_dim, R);
+    int8_t* q = reinterpret_cast<int8_t*>(c->q8);
+    float* inv = c->q8 + q_rows_pad * size_t(op.q_stride) / 4;
+    subnorm_quant_kernel<<<unsigned(n_rows), 256, align_up(size_t(op.in_dim), 4) * 12, c->stream>>>(
+        rows_d, op.norm_w, op.eps, op.in_dim, q, op.q_stride, (long long)q_row0, (long long)q_rows_pad, inv);
+    if (c->out_tc && op.q_stride / tg::kBK <= tg::max_nkb()) {
+        // tensor cores: 128 token rows x 32 output rows per block, the block's weights resident
+        TernaryGemmArgs ga;
+        ga.q = q; ga.w2 = op.w2; ga.q_rows_pad = (long long)q_rows_pad; ga.q_row0 = (long long)q_row0;
+        ga.w_scales = op.w_scales; ga.inv_scale = inv; ga.rows = rows_d;
+        ga.n_rows = n_rows; ga.out_dim = op.out_dim; ga.k_bytes = op.q_stride;
+        ga.status = c->status_d;
+        dim3 grid(unsigned((op.out_dim + tg::kTN - 1) / tg::kTN), unsigned((n_rows + tg::kTM - 1) / tg::kTM));
+        ternary_gemm_tc_kernel<<<grid, tg::kThreads, tg::smem_bytes(op.q_stride / tg::kBK), c->stream>>>(ga);
+    } else {
+        const int R = std::max(1, std::min(kOutMaxRowsPerCta, (op.out_dim + c->sm_count - 1) / c->sm_count));
+        dim3 grid(unsigned((op.out_dim + R - 1) / R), unsigned((n_rows + kOutRowsTile - 1) / kOutRowsTile));
+        ternary_gemm_kernel<<<grid, 256, kOutGemmSmem, c->stream>>>(
+            q, op.q_stride, (long long)q_row0, (long long)q_rows_pad, inv, op.w2, op.w_scales, rows_d,
+            n_rows, op.out_dim, R);
+    }
     c->stats.kernel_launches += 2;
     c->stats.out_proj_rows += uint64_t(n_rows);
     XN_CUDA(c, cudaGetLastError());
@@ -509,7 +532,6 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
     if ((rc = grow_device(c, &c->q_rot, &c->q_rot_cap, qrot_floats)) != XN_OK) return rc;
     if (out_rows) {
         if ((rc = grow_device(c, &c->attn_seq, &c->attn_seq_cap, out_rows * size_t(Hq) * D)) != XN_OK) return rc;
-        if ((rc = grow_device(c, &c->q8, &c->q8_cap, q8_floats(c, out_rows))) != XN_OK) return rc;
     }
     if (host_mode && (rc = grow_io(c, io_in + io_out)) != XN_OK) return rc;
 
@@ -577,7 +599,7 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
             for (int t = 0; t < S; ++t)
                 out_row_tab.push_back({rows + size_t(t) * op.in_dim, o_dev + size_t(t) * op.out_dim});
             if (!out_runs.empty() && out_runs.back().layer == r.layer) out_runs.back().row_count += S;
-            else out_runs.push_back({r.layer, int(row0), S});
+            else out_runs.push_back({r.layer, int(row0), S, 0});
         }
         d.page_off = int(page_ids.size());
         d.n_pages = int(s->pages.size());
@@ -722,11 +744,18 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         c->stats.kernel_launches += 1;
     }
     XN_CUDA(c, cudaGetLastError());
+    size_t q_rows_pad = 0;   // every run starts on a 256-row boundary of the activation buffer
+    for (OutRun& run : out_runs) {
+        run.q_row0 = q_rows_pad;
+        q_rows_pad += align_up(size_t(run.row_count), 256);
+    }
+    if (q_rows_pad && (rc = grow_device(c, &c->q8, &c->q8_cap, q8_floats(c, q_rows_pad))) != XN_OK) return rc;
     for (const OutRun& run : out_runs) {
         const OutRowDev* rows_d = reinterpret_cast<const OutRowDev*>(slot->dev + o_rows) + run.row_begin;
-        if ((rc = launch_out_block(c, run.layer, rows_d, run.row_count, size_t(run.row_begin),
-                                   out_row_tab.size())) != XN_OK)
+        if (c->profile && (rc = profile_begin(c, 2)) != XN_OK) return rc;
+        if ((rc = launch_out_block(c, run.layer, rows_d, run.row_count, run.q_row0, q_rows_pad)) != XN_OK)
             return rc;
+        if (c->profile && (rc = profile_end(c)) != XN_OK) return rc;
     }
 
     if (host_mode) {
@@ -892,6 +921,8 @@ int32_t xn_ctx_create(const xn_ctx_desc* d, xn_ctx** out_ctx) {
     c->decode_chunks = c->decode_ctas * chunks_per_cta;
     if (const char* env = getenv("XORNET_ATTN_FUSE_APPEND")) c->fuse_append = atoi(env) != 0;
     if (const char* env = getenv("XORNET_ATTN_FUSE_PINNED")) c->fuse_pinned = atoi(env) != 0;
+    if (const char* env = getenv("XORNET_ATTN_OUTPROJ_TC")) c->out_tc = atoi(env) != 0;
+
 
     const size_t page_bytes =
         size_t(d->num_layers) * d->num_kv_heads * kPageTokens * c->nv * 16 * 2;  // K and V
@@ -1060,26 +1091,38 @@ int32_t xn_profile_enable(xn_ctx* c, int32_t on) {
     return XN_OK;
 }
 
-int32_t xn_profile_read(xn_ctx* c, double* splitkv_ms, uint64_t* splitkv_launches,
-                        double* prefill_ms, uint64_t* prefill_launches) {
+int32_t xn_profile_read_all(xn_ctx* c, double* ms, uint64_t* launches) {
     if (!ctx_ok(c)) return XN_ERR_HANDLE;
     std::lock_guard<std::mutex> g(c->mu);
     XN_CUDA(c, cudaSetDevice(c->device));
     XN_CUDA(c, cudaStreamSynchronize(c->stream));
-    double total[2] = {0.0, 0.0};
-    uint64_t count[2] = {0, 0};
+    double total[XN_PROFILE_KINDS] = {0.0, 0.0, 0.0};
+    uint64_t count[XN_PROFILE_KINDS] = {0, 0, 0};
     for (size_t i = 0; i + 1 < c->prof_used; i += 2) {
-        float ms = 0.f;
-        XN_CUDA(c, cudaEventElapsedTime(&ms, c->prof_events[i], c->prof_events[i + 1]));
-        const int kind = c->prof_kind[i / 2] ? 1 : 0;
-        total[kind] += ms;
+        float t = 0.f;
+        XN_CUDA(c, cudaEventElapsedTime(&t, c->prof_events[i], c->prof_events[i + 1]));
+        const int kind = std::min(std::max(c->prof_kind[i / 2], 0), XN_PROFILE_KINDS - 1);
+        total[kind] += t;
         count[kind] += 1;
     }
-    if (splitkv_ms) *splitkv_ms = total[0];
-    if (splitkv_launches) *splitkv_launches = count[0];
-    if (prefill_ms) *prefill_ms = total[1];
-    if (prefill_launches) *prefill_launches = count[1];
+    for (int k = 0; k < XN_PROFILE_KINDS; ++k) {
+        if (ms) ms[k] = total[k];
+        if (launches) launches[k] = count[k];
+    }
     c->prof_used = 0;
+    return XN_OK;
+}
+
+int32_t xn_profile_read(xn_ctx* c, double* splitkv_ms, uint64_t* splitkv_launches,
+                        double* prefill_ms, uint64_t* prefill_launches) {
+    double ms[XN_PROFILE_KINDS];
+    uint64_t n[XN_PROFILE_KINDS];
+    const int32_t rc = xn_profile_read_all(c, ms, n);
+    if (rc != XN_OK) return rc;
+    if (splitkv_ms) *splitkv_ms = ms[0];
+    if (splitkv_launches) *splitkv_launches = n[0];
+    if (prefill_ms) *prefill_ms = ms[1];
+    if (prefill_launches) *prefill_launches = n[1];
     return XN_OK;
 }
 
@@ -1354,21 +1397,28 @@ int32_t xn_out_proj_set(xn_ctx* c, const xn_out_proj_desc* d) {
     if (d->out_dim <= 0 || d->out_dim > (1 << 20)) return fail(c, XN_ERR_SHAPE, "out_dim %d outside 1..2^20", d->out_dim);
     if (d->pack_type != XN_PACK4 && d->pack_type != XN_PACK5)
         return fail(c, XN_ERR_ARG, "pack_type must be XN_PACK4 or XN_PACK5");
-    if (size_t(d->in_dim) * 4 > 200 * 1024) return fail(c, XN_ERR_CAPACITY, "in_dim %d is beyond one block's shared memory", d->in_dim);
+    if (size_t(d->in_dim) * 12 > 200 * 1024) return fail(c, XN_ERR_CAPACITY, "in_dim %d is beyond one block's shared memory", d->in_dim);
     XN_CUDA(c, cudaSetDevice(c->device));
     XN_CUDA(c, cudaStreamSynchronize(c->stream));  // launches in flight may still read the old block
 
     OutProj op;
     op.in_dim = d->in_dim;
     op.out_dim = d->out_dim;
-    op.q_stride = int(align_up(size_t(d->in_dim), 64));
+    op.q_stride = int(align_up(size_t(d->in_dim), 128));
     op.w_stride = op.q_stride / 4;
     op.eps = d->norm_eps;
     const size_t bpr = packed_row_bytes(size_t(d->in_dim), d->pack_type);
-    std::vector<uint8_t> w2(size_t(d->out_dim) * op.w_stride);
-    for (int o = 0; o < d->out_dim; ++o)
-        recode_row_2bit(d->packed + size_t(o) * bpr, size_t(d->in_dim), d->pack_type,
-                        w2.data() + size_t(o) * op.w_stride, size_t(op.w_stride));
+    // device layout: [row / 32][K / 128][32 rows][32 bytes] (code_offset); rows past out_dim and
+    // columns past in_dim hold code 1 = weight 0
+    const int nkb = op.q_stride / 128;
+    std::vector<uint8_t> w2(size_t((d->out_dim + 31) / 32) * nkb * 1024, uint8_t(0x55));
+    std::vector<uint8_t> row_codes(size_t(op.w_stride));
+    for (int o = 0; o < d->out_dim; ++o) {
+        recode_row_2bit(d->packed + size_t(o) * bpr, size_t(d->in_dim), d->pack_type, row_codes.data(),
+                        row_codes.size());
+        for (int kb = 0; kb < nkb; ++kb)
+            memcpy(w2.data() + code_offset(o, kb * 128, nkb), row_codes.data() + size_t(kb) * 32, 32);
+    }
     auto upload = [&](void** dst, const void* src, size_t bytes) -> cudaError_t {
         cudaError_t e = cudaMalloc(dst, bytes);
         if (e != cudaSuccess) return e;
@@ -1381,9 +1431,15 @@ int32_t xn_out_proj_set(xn_ctx* c, const xn_out_proj_desc* d) {
     if (e == cudaSuccess)
         e = cudaFuncSetAttribute(reinterpret_cast<const void*>(ternary_gemm_kernel),
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, kOutGemmSmem);
-    if (e == cudaSuccess && size_t(d->in_dim) * 4 > 48 * 1024)
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(reinterpret_cast<const void*>(ternary_gemm_tc_kernel),
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 std::max(tg::smem_bytes(24), tg::smem_bytes(tg::max_nkb())));
+
+    if (e == cudaSuccess && align_up(size_t(d->in_dim), 4) * 12 > 40 * 1024)  // static shared memory counts too
         e = cudaFuncSetAttribute(reinterpret_cast<const void*>(subnorm_quant_kernel),
-                                 cudaFuncAttributeMaxDynamicSharedMemorySize, d->in_dim * 4);
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 int(align_up(size_t(d->in_dim), 4) * 12));
     if (e != cudaSuccess) {
         if (op.w2) cudaFree(op.w2);
         if (op.w_scales) cudaFree(op.w_scales);
@@ -1412,7 +1468,8 @@ int32_t xn_out_proj(xn_ctx* c, int32_t layer, int32_t rows, const float* y, floa
     const bool dev = flags & XN_REQ_DEVICE_PTRS;
     const size_t in_b = size_t(rows) * op.in_dim * 4, out_b = size_t(rows) * op.out_dim * 4;
     int32_t rc;
-    if ((rc = grow_device(c, &c->q8, &c->q8_cap, q8_floats(c, size_t(rows)))) != XN_OK) return rc;
+    const size_t q_rows_pad = align_up(size_t(rows), 256);
+    if ((rc = grow_device(c, &c->q8, &c->q8_cap, q8_floats(c, q_rows_pad))) != XN_OK) return rc;
     const float* src = y;
     float* dst = out;
     if (!dev) {
@@ -1429,7 +1486,7 @@ int32_t xn_out_proj(xn_ctx* c, int32_t layer, int32_t rows, const float* y, floa
     for (int t = 0; t < rows; ++t) tab[t] = {src + size_t(t) * op.in_dim, dst + size_t(t) * op.out_dim};
     XN_CUDA(c, cudaMemcpyAsync(slot->dev, slot->host, sizeof(OutRowDev) * size_t(rows),
                                cudaMemcpyHostToDevice, c->stream));
-    rc = launch_out_block(c, layer, reinterpret_cast<const OutRowDev*>(slot->dev), rows, 0, size_t(rows));
+    rc = launch_out_block(c, layer, reinterpret_cast<const OutRowDev*>(slot->dev), rows, 0, q_rows_pad);
     XN_CUDA(c, cudaEventRecord(slot->ev, c->stream));
     slot->used = true;
     if (rc != XN_OK) return rc;

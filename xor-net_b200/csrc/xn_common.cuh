@@ -106,6 +106,22 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
     return t;
 }
 
+// try_wait with a suspend-time hint: the thread may sleep in hardware, for up to about `hint_ns`,
+// until the phase completes.  A polling loop without the hint re-issues the instruction back to
+// back, and a handful of polling warps then crowd the copy producer's and the MMA issuer's own
+// barrier and copy instructions out of the SM's memory-instruction queue.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return ok != 0;
+}
+
 // Waits for the given phase parity at most `limit_ns` (default ~2 s).  Returns false when it
 // gave up; the caller records an error code and leaves its loop, so a lost copy can never hang
 // the GPU.
@@ -114,8 +130,36 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     if (mbar_try_wait(bar, parity)) return true;
     unsigned long long t0 = 0;
     for (uint32_t spins = 1;; ++spins) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((spins & 0x3ffu) == 0) {
+        if (mbar_try_wait_hint(bar, parity, 20000u)) return true;
+        if ((spins & 0x3fu) == 0) {
+            unsigned long long now = global_timer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > limit_ns) return false;
+        }
+    }
+}
+
+// Non-blocking test of the phase, and a bounded wait built on it: the thread keeps polling, so it
+// notices the completion within a few cycles (try_wait may park the thread and wake it late),
+// at the price of occupying the shared-memory pipe.  For waits on a kernel's critical hand-offs.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+__device__ __forceinline__ bool mbar_spin_bounded(uint64_t* bar, uint32_t parity,
+                                                  unsigned long long limit_ns = 2000000000ull) {
+    unsigned long long t0 = 0;
+    for (uint32_t spins = 1;; ++spins) {
+        if (mbar_test_wait(bar, parity)) return true;
+        if ((spins & 0xfffu) == 0) {
             unsigned long long now = global_timer_ns();
             if (t0 == 0) t0 = now;
             else if (now - t0 > limit_ns) return false;

@@ -23,6 +23,23 @@ struct OutRowDev {
     float* dst;
 };
 
+// Global layout of the quantised activations: [K / 128][row][128 bytes], and inside a row the
+// eight 16-byte chunks permuted by (row & 7).  A tile of rows (starting at a multiple of 8) of one
+// 128-column block is then contiguous AND already in the 128-byte-swizzled K-major layout the
+// tensor cores read from shared memory.  rows_pad = rows of the buffer (a multiple of 256).
+__host__ __device__ __forceinline__ size_t act_offset(long long row, int k, long long rows_pad) {
+    return (size_t(k >> 7) * size_t(rows_pad) + size_t(row)) * 128 +
+           size_t((((k >> 4) & 7) ^ int(row & 7)) << 4) + size_t(k & 15);
+}
+
+// Global layout of the 2-bit weight codes: [row / 32][K / 128][32 rows][32 bytes]: everything one
+// thread block of the tensor-core kernel needs (32 output rows, all of K) is one contiguous piece.
+// nkb = K / 128.
+__host__ __device__ __forceinline__ size_t code_offset(int row, int k, int nkb) {
+    return ((size_t(row >> 5) * size_t(nkb) + size_t(k >> 7)) * 32 + size_t(row & 31)) * 32 +
+           size_t((k & 127) >> 2);
+}
+
 constexpr int kOutRowsTile = 64;    // token rows per GEMM block
 constexpr int kOutKChunk = 1280;    // activation bytes per row staged at a time (multiple of 128)
 constexpr int kOutMaxRowsPerCta = 32;
@@ -33,49 +50,72 @@ constexpr int kOutGemmSmem = kOutRowsTile * kOutActStride + kOutMaxRowsPerCta * 
 //
 // The sum of squares is a 1-thread dependent chain on purpose (see the header: the reference's
 // order is the only one that reproduces its bits); the other threads stage the row, then
-// normalise, reduce max|x| (order-free) and quantise.  Dynamic shared memory: in_dim floats.
+// normalise, reduce max|x| (order-free) and quantise.  Dynamic shared memory: the row, its
+// squares and the norm weights, 3 * round_up(in_dim, 4) floats.
 __global__ void __launch_bounds__(256)
 subnorm_quant_kernel(const OutRowDev* __restrict__ rows, const float* __restrict__ norm_w, float eps,
-                     int in_dim, int8_t* __restrict__ q_out, int q_stride,
-                     float* __restrict__ inv_scale_out) {
+                     int in_dim, int8_t* __restrict__ q_out, int q_stride, long long q_row0,
+                     long long q_rows_pad, float* __restrict__ inv_scale_out) {
     extern __shared__ float row_s[];
     __shared__ float red_s[8];
     __shared__ float bc_s;
     const int r = blockIdx.x;
     const float* src = rows[r].src;
     const int tid = threadIdx.x;
+    const int pad = (in_dim + 3) & ~3;
+    float* sq_s = row_s + pad;       // squares of the row
+    float* nw_s = sq_s + pad;        // sub-norm weights, fetched while the row is
     const bool vec = (in_dim % 4 == 0) && ((reinterpret_cast<uintptr_t>(src) & 15) == 0);
     if (vec) {
-        for (int i = tid * 4; i < in_dim; i += blockDim.x * 4)
-            *reinterpret_cast<float4*>(row_s + i) = *reinterpret_cast<const float4*>(src + i);
+        for (int i = tid * 4; i < in_dim; i += blockDim.x * 4) {
+            const float4 x = *reinterpret_cast<const float4*>(src + i);
+            *reinterpret_cast<float4*>(row_s + i) = x;
+            // squares in parallel (each a single rounded multiply); the adds come later, in order
+            *reinterpret_cast<float4*>(sq_s + i) = make_float4(__fmul_rn(x.x, x.x), __fmul_rn(x.y, x.y),
+                                                                __fmul_rn(x.z, x.z), __fmul_rn(x.w, x.w));
+            if (norm_w != nullptr)
+                *reinterpret_cast<float4*>(nw_s + i) = *reinterpret_cast<const float4*>(norm_w + i);
+        }
     } else {
-        for (int i = tid; i < in_dim; i += blockDim.x) row_s[i] = src[i];
+        for (int i = tid; i < in_dim; i += blockDim.x) {
+            const float x = src[i];
+            row_s[i] = x;
+            sq_s[i] = __fmul_rn(x, x);
+            if (norm_w != nullptr) nw_s[i] = norm_w[i];
+        }
     }
     __syncthreads();
     if (norm_w != nullptr) {
-        if (tid == 0) {
+        if (tid < 32) {
+            // the whole first warp runs the chain (same value in every lane: no divergence);
+            // 16 elements per trip, the next 16 loaded before the adds of the current ones, which
+            // keeps the chain at the 4-cycle latency of a dependent add
             float sum_sq = 0.f;
-            int i = 0;
-            for (; i + 8 <= in_dim; i += 8) {
-                const float4 a = *reinterpret_cast<const float4*>(row_s + i);
-                const float4 b = *reinterpret_cast<const float4*>(row_s + i + 4);
-                sum_sq = __fadd_rn(sum_sq, __fmul_rn(a.x, a.x));
-                sum_sq = __fadd_rn(sum_sq, __fmul_rn(a.y, a.y));
-                sum_sq = __fadd_rn(sum_sq, __fmul_rn(a.z, a.z));
-                sum_sq = __fadd_rn(sum_sq, __fmul_rn(a.w, a.w));
-                sum_sq = __fadd_rn(sum_sq, __fmul_rn(b.x, b.x));
-                sum_sq = __fadd_rn(sum_sq, __fmul_rn(b.y, b.y));
-                sum_sq = __fadd_rn(sum_sq, __fmul_rn(b.z, b.z));
-                sum_sq = __fadd_rn(sum_sq, __fmul_rn(b.w, b.w));
+            const int n16 = in_dim >> 4;
+            const float4* p = reinterpret_cast<const float4*>(sq_s);
+            float4 b0 = make_float4(0.f, 0.f, 0.f, 0.f), b1 = b0, b2 = b0, b3 = b0;
+            if (n16 > 0) { b0 = p[0]; b1 = p[1]; b2 = p[2]; b3 = p[3]; }
+            for (int i = 0; i < n16; ++i) {
+                const int nx = (i + 1 < n16 ? i + 1 : i) * 4;
+                const float4 c0 = p[nx], c1 = p[nx + 1], c2 = p[nx + 2], c3 = p[nx + 3];
+                sum_sq = __fadd_rn(sum_sq, b0.x); sum_sq = __fadd_rn(sum_sq, b0.y);
+                sum_sq = __fadd_rn(sum_sq, b0.z); sum_sq = __fadd_rn(sum_sq, b0.w);
+                sum_sq = __fadd_rn(sum_sq, b1.x); sum_sq = __fadd_rn(sum_sq, b1.y);
+                sum_sq = __fadd_rn(sum_sq, b1.z); sum_sq = __fadd_rn(sum_sq, b1.w);
+                sum_sq = __fadd_rn(sum_sq, b2.x); sum_sq = __fadd_rn(sum_sq, b2.y);
+                sum_sq = __fadd_rn(sum_sq, b2.z); sum_sq = __fadd_rn(sum_sq, b2.w);
+                sum_sq = __fadd_rn(sum_sq, b3.x); sum_sq = __fadd_rn(sum_sq, b3.y);
+                sum_sq = __fadd_rn(sum_sq, b3.z); sum_sq = __fadd_rn(sum_sq, b3.w);
+                b0 = c0; b1 = c1; b2 = c2; b3 = c3;
             }
-            for (; i < in_dim; ++i) sum_sq = __fadd_rn(sum_sq, __fmul_rn(row_s[i], row_s[i]));
+            for (int i = n16 << 4; i < in_dim; ++i) sum_sq = __fadd_rn(sum_sq, sq_s[i]);
             const float rms = __fsqrt_rn(__fadd_rn(__fdiv_rn(sum_sq, float(in_dim)), eps));
-            bc_s = __fdiv_rn(1.0f, rms);
+            if (tid == 0) bc_s = __fdiv_rn(1.0f, rms);
         }
         __syncthreads();
         const float inv_rms = bc_s;
         for (int i = tid; i < in_dim; i += blockDim.x)
-            row_s[i] = __fmul_rn(__fmul_rn(row_s[i], inv_rms), norm_w[i]);
+            row_s[i] = __fmul_rn(__fmul_rn(row_s[i], inv_rms), nw_s[i]);
         __syncthreads();
     }
     float m = 0.f;
@@ -86,9 +126,8 @@ subnorm_quant_kernel(const OutRowDev* __restrict__ rows, const float* __restrict
     m = red_s[0];
     for (int w = 1; w < int(blockDim.x >> 5); ++w) m = fmaxf(m, red_s[w]);
     const float scale = m > 0.f ? __fdiv_rn(127.0f, m) : 1.0f;
-    if (tid == 0) inv_scale_out[r] = m > 0.f ? __fdiv_rn(m, 127.0f) : 1.0f;
+    if (tid == 0) inv_scale_out[q_row0 + r] = m > 0.f ? __fdiv_rn(m, 127.0f) : 1.0f;
     const int simd_end = (in_dim / 16) * 16;
-    int8_t* q = q_out + size_t(r) * q_stride;
     for (int i = tid; i < q_stride; i += blockDim.x) {
         int v = 0;
         if (i < in_dim) {
@@ -96,7 +135,7 @@ subnorm_quant_kernel(const OutRowDev* __restrict__ rows, const float* __restrict
             if (i < simd_end) v = __float2int_rn(fmaxf(-127.0f, fminf(127.0f, s)));
             else v = int(fmaxf(-127.0f, fminf(127.0f, roundf(s))));
         }
-        q[i] = int8_t(v);
+        q_out[act_offset(q_row0 + r, i, q_rows_pad)] = int8_t(v);
     }
 }
 
@@ -104,7 +143,7 @@ subnorm_quant_kernel(const OutRowDev* __restrict__ rows, const float* __restrict
 //
 // Device weight format: 2 bits per weight, weight i of a row in bits 2(i%4).. of byte i/4 with the
 // reference's pack4 codes (0 -> -1, 1 -> 0, 2 -> +1, 3 -> 0; bit1_58/quantization.rs:7-47); rows
-// padded with code 1 to a multiple of 64 weights.  pack5 weights are re-coded on the host.
+// padded with code 1 (and code 3 re-coded as 1) to a multiple of 128 weights.  pack5 weights are re-coded on the host.
 //
 // Block = 64 token rows x `rows_per_cta` output rows.  The activations of the tile and the decoded
 // weights are staged in shared memory one 1280-column chunk at a time; lane l of each warp owns
@@ -121,9 +160,10 @@ __device__ __forceinline__ uint32_t decode4(uint32_t byte_codes) {
 }
 
 __global__ void __launch_bounds__(256)
-ternary_gemm_kernel(const int8_t* __restrict__ q, int q_stride, const float* __restrict__ inv_scale,
-                    const uint8_t* __restrict__ w2, int w_stride, const float* __restrict__ w_scales,
-                    const OutRowDev* __restrict__ rows, int n_rows, int out_dim, int rows_per_cta) {
+ternary_gemm_kernel(const int8_t* __restrict__ q, int q_stride, long long q_row0, long long q_rows_pad,
+                    const float* __restrict__ inv_scale, const uint8_t* __restrict__ w2,
+                    const float* __restrict__ w_scales, const OutRowDev* __restrict__ rows, int n_rows,
+                    int out_dim, int rows_per_cta) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     int8_t* act_s = reinterpret_cast<int8_t*>(smem_raw);
     int8_t* w_s = act_s + kOutRowsTile * kOutActStride;
@@ -144,13 +184,13 @@ ternary_gemm_kernel(const int8_t* __restrict__ q, int q_stride, const float* __r
             const int t = e / kv, c = e % kv;
             int4 v = make_int4(0, 0, 0, 0);
             if (t0 + t < n_rows)
-                v = *reinterpret_cast<const int4*>(q + size_t(t0 + t) * q_stride + k0 + c * 16);
+                v = *reinterpret_cast<const int4*>(q + act_offset(q_row0 + t0 + t, k0 + c * 16, q_rows_pad));
             *reinterpret_cast<int4*>(act_s + t * kOutActStride + c * 16) = v;
         }
         for (int e = tid; e < R * kv; e += blockDim.x) {
             const int rr = e / kv, c = e % kv;
             const uint32_t codes = *reinterpret_cast<const uint32_t*>(
-                w2 + size_t(o0 + rr) * w_stride + (k0 + c * 16) / 4);
+                w2 + code_offset(o0 + rr, k0 + c * 16, q_stride >> 7));
             int4 v;
             v.x = int(decode4(codes & 0xffu));
             v.y = int(decode4((codes >> 8) & 0xffu));
@@ -186,7 +226,7 @@ ternary_gemm_kernel(const int8_t* __restrict__ q, int q_stride, const float* __r
     for (int a = 0; a < 2; ++a) {
         const int t = t0 + lane + 32 * a;
         if (t >= n_rows) continue;
-        const float is = inv_scale[t];
+        const float is = inv_scale[q_row0 + t];
         float* dst = rows[t].dst;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {

@@ -1,0 +1,340 @@
+// Ternary output projection on the 5th-generation tensor cores: i8 activations x 2-bit ternary
+// weights -> i32 accumulators in tensor memory (tcgen05.mma.kind::i8), sm_100a only.
+//
+//   out[t][o] = (i32 dot(q[t], W[o]) as f32 * inv_scale[t]) * w_scale[o]
+// is TernaryLinear::forward of the reference (src/bit1_58/layers.rs:262-313).  The dot products
+// are integers, so the tensor-core result equals the CUDA-core kernel's and the reference's.
+//
+// One thread block = 128 token rows (the MMA's M: activations are operand A) x 32 output rows
+// (N: weights are operand B), all of K.  80 blocks for the 2B model's 2560 outputs, whatever the
+// number of tokens up to 128.  What shapes the kernel is latency, not throughput: one barrier
+// hand-off costs ~100-200 cycles and a 128-column step only holds ~200 cycles of tensor work, so
+//   * the block's whole weight slab [32 rows x K] is decoded ONCE into shared memory (80 KB for
+//     K = 2560), in coarse pieces of 512 columns, instead of being re-staged every step;
+//   * the activations stream through a ring of 256-column stages that are contiguous in global
+//     memory AND already laid out the way the tensor core reads them (act_offset), so a stage is
+//     two plain bulk copies; tiled tensor-map loads of the same tiles were several times slower
+//     (one request per row);
+//   * ring positions and phases are counted, never divided out, and every control warp runs its
+//     loop converged with one lane issuing.
+// Roles (352 threads):
+//   warp 0      copy producer: activation stages (bulk async copies, no tensor map, no multicast);
+//   warp 1      MMA issuer (one lane): eight tcgen05.mma (K = 32 each) per stage, both operands
+//               from shared memory; tcgen05.commit frees the stage and finally signals the
+//               epilogue; owns the tensor-memory allocation (32 columns);
+//   warp 2      copy producer: the block's 2-bit codes, one bulk copy per 512 columns;
+//   warps 3..10 weight decoders: 64 weights (16 bytes of codes) per thread and item, five
+//               integer instructions per four weights, stored in the K-major 128-byte-swizzled
+//               operand layout.  Afterwards the same warps are the epilogue: thread = token row,
+//               tcgen05.ld of 16 output columns, two rounded multiplies, 64 contiguous bytes out.
+// Every wait is bounded; on expiry the kernel records a status code, drains and returns.
+#pragma once
+#include "xn_outproj.cuh"
+#include "xn_prefill_tf32.cuh"
+
+namespace xn {
+
+namespace tg {
+constexpr int kTM = 128;                 // token rows per block (MMA M)
+constexpr int kTN = 32;                  // output rows per block (MMA N)
+constexpr int kBK = 128;                 // K bytes (= i8 elements) per K-block
+constexpr int kStepKb = 2;               // K-blocks per activation stage
+constexpr int kActBlock = kTM * kBK;     // 16 KB: one K-block of one token tile
+constexpr int kActStage = kStepKb * kActBlock;
+constexpr int kMaxActStages = 3;
+constexpr int kWBlock = kTN * kBK;       // 4 KB of decoded weights per K-block
+constexpr int kCBlock = kTN * kBK / 4;   // 1 KB of codes per K-block
+constexpr int kPieceKb = 4;              // K-blocks per decode piece (one code copy, one barrier)
+constexpr int kMaxPieces = 8;            // K <= 4096
+constexpr int kThreads = 352;
+constexpr int kDecoderWarps = 8;
+
+// three activation stages while the weight slab leaves room for them (K <= 3072), else two
+__host__ __device__ constexpr int act_stages(int nkb) { return nkb <= 24 ? 3 : 2; }
+__host__ __device__ constexpr int smem_bytes(int nkb) {
+    return act_stages(nkb) * kActStage + nkb * (kWBlock + kCBlock) + 1024 /* alignment slack */ +
+           512 /* barriers */;
+}
+__host__ __device__ constexpr int max_nkb() { return kMaxPieces * kPieceKb; }
+
+// Instruction descriptor, kind::i8: [4,6) D format 2 = s32, [7,10) A format 1 = s8, [10,13) B
+// format 1 = s8, bits 15/16 A/B major 0 = K-major, [17,23) N >> 3, [24,29) M >> 4.
+__host__ __device__ constexpr uint32_t make_idesc_i8(int m, int n) {
+    return (2u << 4) | (1u << 7) | (1u << 10) | (uint32_t(n >> 3) << 17) | (uint32_t(m >> 4) << 24);
+}
+
+// D[tmem] (+)= A[smem] * B[smem]
+__device__ __forceinline__ void mma_ss_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                          uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// Four canonical 2-bit codes (0 -> -1, 1 -> 0, 2 -> +1; code 3 never occurs in the device
+// format) in one byte -> four i8 in one word: spread the fields to the byte lanes, then
+// code - 1 per byte without inter-byte borrows.
+__device__ __forceinline__ uint32_t decode4_canon(uint32_t b) {
+    const uint32_t t = b * 0x1001u;                       // b | b << 12 (disjoint fields)
+    const uint32_t x = (t | (t << 6)) & 0x03030303u;      // code i in byte i
+    return (x + 0x7F7F7F7Fu) ^ 0x80808080u;
+}
+
+// One lane polls (bounded) for the phase; every lane of the (converged) warp gets the outcome.
+__device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, int lane) {
+    int ok = 1;
+    if (lane == 0) ok = mbar_spin_bounded(bar, parity) ? 1 : 0;
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+
+__device__ __forceinline__ void fence_generic_to_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, "
+        "%12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+}  // namespace tg
+
+struct TernaryGemmArgs {
+    const int8_t* q;         // activations, tiled: act_offset()
+    const uint8_t* w2;       // weight codes, tiled: code_offset()
+    long long q_rows_pad;    // rows of the activation buffer (multiple of 256)
+    long long q_row0;        // first activation row of this launch (multiple of 256)
+    const float* w_scales;   // [out_dim]
+    const float* inv_scale;  // [q_rows_pad], indexed like the activation rows
+    const OutRowDev* rows;   // destination rows of this launch
+    int n_rows;              // token rows of this launch
+    int out_dim;
+    int k_bytes;             // i8 elements per activation row, multiple of 128
+    int* status;
+};
+
+__global__ void __launch_bounds__(tg::kThreads, 1)
+ternary_gemm_tc_kernel(const TernaryGemmArgs a) {
+    using namespace tg;
+    extern __shared__ unsigned char smem_dyn[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
+    const int nkb = a.k_bytes / kBK;
+    const int n_pieces = (nkb + kPieceKb - 1) / kPieceKb;
+    const int n_steps = (nkb + kStepKb - 1) / kStepKb;
+    const int kActStages = act_stages(nkb);
+    unsigned char* act_s = smem;                                  // [kActStages][kStepKb][128 rows x 128 B]
+    unsigned char* w_s = act_s + kActStages * kActStage;          // [nkb][32 rows x 128 B], decoded
+    unsigned char* c_s = w_s + nkb * kWBlock;                     // [nkb][32 rows x 32 B], codes
+    uint64_t* bars = reinterpret_cast<uint64_t*>(c_s + nkb * kCBlock);
+    uint64_t* act_full = bars;                       // [kActStages] stage landed (copy bytes)
+    uint64_t* act_empty = act_full + kMaxActStages;  // [kActStages] the MMAs that read it are done
+    uint64_t* c_full = act_empty + kMaxActStages;    // [kMaxPieces] codes of the piece landed
+    uint64_t* w_full = c_full + kMaxPieces;          // [kMaxPieces] piece decoded (one arrival per decoder warp)
+    uint64_t* acc_full = w_full + kMaxPieces;        // all MMAs done
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);
+    static_assert((2 * kMaxActStages + 2 * kMaxPieces + 1) * 8 + 16 <= 512, "barrier area");
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int o0 = blockIdx.x * kTN;
+    const int t0 = blockIdx.y * kTM;
+
+    if (tid == 0) {
+        for (int s = 0; s < kActStages; ++s) {
+            mbar_init(&act_full[s], 1);
+            mbar_init(&act_empty[s], 1);
+        }
+        for (int p = 0; p < n_pieces; ++p) {
+            mbar_init(&c_full[p], 1);
+            mbar_init(&w_full[p], kDecoderWarps);
+        }
+        mbar_init(acc_full, 1);
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         smem_u32(tmem_slot)),
+                     "r"(uint32_t(kTN))
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    pf::fence_before_sync();
+    __syncthreads();
+    pf::fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 2) {
+        // ======================= copy producer: the block's weight codes =======================
+        if (lane == 0) {
+            const uint8_t* src = a.w2 + size_t(blockIdx.x) * nkb * kCBlock;
+            for (int p = 0; p < n_pieces; ++p) {
+                const int kbs = min(kPieceKb, nkb - p * kPieceKb);
+                mbar_arrive_expect_tx(&c_full[p], uint32_t(kbs * kCBlock));
+                bulk_g2s(c_s + p * kPieceKb * kCBlock, src + size_t(p) * kPieceKb * kCBlock,
+                         uint32_t(kbs * kCBlock), &c_full[p]);
+            }
+        }
+    } else if (warp == 0) {
+        // ======================= copy producer: activation stages =======================
+        const int8_t* src = a.q + size_t(a.q_row0 + t0) * kBK;
+        const size_t kb_step = size_t(a.q_rows_pad) * kBK;   // one K-block further in global memory
+        int st = 0;
+        uint32_t wrap_par = 1;   // parity of the `empty` phase that frees the stage being refilled
+        for (int s = 0; s < n_steps; ++s) {
+            if (s >= kActStages) {
+                wrap_par ^= (st == 0) ? 1u : 0u;
+                if (!warp_wait(&act_empty[st], wrap_par, lane)) {
+                    if (lane == 0) {
+                        report_status(a.status, kDevWaitEmpty);
+                        *abort_flag = 1;
+                    }
+                    break;
+                }
+            }
+            if (lane == 0) {
+                const int kbs = min(kStepKb, nkb - s * kStepKb);
+                mbar_arrive_expect_tx(&act_full[st], uint32_t(kbs * kActBlock));
+                for (int j = 0; j < kbs; ++j)
+                    bulk_g2s(act_s + st * kActStage + j * kActBlock, src + size_t(j) * kb_step,
+                             uint32_t(kActBlock), &act_full[st]);
+            }
+            src += size_t(kStepKb) * kb_step;
+            if (++st == kActStages) st = 0;
+            __syncwarp();
+        }
+    } else if (warp == 1) {
+        // =============================== MMA issuer ===============================
+        const uint32_t idesc = make_idesc_i8(kTM, kTN);
+        bool ok = true;
+        int st = 0;
+        uint32_t par = 0;
+        int pieces_seen = 0;
+        for (int s = 0; s < n_steps; ++s) {
+            const int kb0 = s * kStepKb;
+            const int kbs = min(kStepKb, nkb - kb0);
+            const int need_piece = (kb0 + kbs - 1) / kPieceKb;   // compile-time divisor
+            while (ok && pieces_seen <= need_piece) ok = warp_wait(&w_full[pieces_seen++], 0, lane);
+            ok = ok && warp_wait(&act_full[st], par, lane);
+            if (!ok || *abort_flag) { ok = false; break; }
+            if (lane == 0) {
+                pf::fence_after_sync();
+                for (int j = 0; j < kbs; ++j) {
+                    const uint64_t adesc = pf::smem_desc(smem_u32(act_s + st * kActStage + j * kActBlock), 0,
+                                                         1024, pf::kLayoutSw128);
+                    const uint64_t bdesc = pf::smem_desc(smem_u32(w_s + (kb0 + j) * kWBlock), 0, 1024,
+                                                         pf::kLayoutSw128);
+#pragma unroll
+                    for (int k4 = 0; k4 < kBK / 32; ++k4)   // 32 bytes of K per instruction: +2 in the address field
+                        mma_ss_i8(tmem_base, adesc + uint64_t(k4 * 2), bdesc + uint64_t(k4 * 2), idesc,
+                                  uint32_t((s | j | k4) != 0));
+                }
+                pf::mma_commit(&act_empty[st]);
+            }
+            if (++st == kActStages) { st = 0; par ^= 1u; }
+            __syncwarp();
+        }
+        if (lane == 0) {
+            if (ok) {
+                pf::mma_commit(acc_full);
+            } else {
+                report_status(a.status, kDevWaitFull);
+                *abort_flag = 1;
+            }
+        }
+    } else {
+        // =============================== weight decoders ===============================
+        // item = (K-block, row, half): 16 bytes of codes -> 64 i8.  64 items per K-block, so one
+        // pass of the 256 decoder threads covers one piece of 4 K-blocks.
+        const int dtid = tid - 96;            // 0..255
+        const int kb_in = dtid >> 6;          // K-block inside the piece
+        const int r = (dtid >> 1) & 31, h = dtid & 1;
+        const bool valid = o0 + r < a.out_dim;   // rows past the matrix decode to weight 0
+        const int w_off = (r >> 3) * 1024 + (r & 7) * 128;
+        bool ok = true;
+        for (int p = 0; p < n_pieces; ++p) {
+            ok = warp_wait(&c_full[p], 0, lane);
+            if (!ok || *abort_flag) break;
+            const int kb = p * kPieceKb + kb_in;
+            if (kb < nkb) {
+                uint4 cur = *reinterpret_cast<const uint4*>(c_s + kb * kCBlock + r * 32 + h * 16);
+                if (!valid) cur = make_uint4(0x55555555u, 0x55555555u, 0x55555555u, 0x55555555u);
+                const uint32_t w[4] = {cur.x, cur.y, cur.z, cur.w};
+                unsigned char* dst = w_s + kb * kWBlock + w_off;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    uint4 v;
+                    v.x = decode4_canon(w[j] & 0xffu);
+                    v.y = decode4_canon((w[j] >> 8) & 0xffu);
+                    v.z = decode4_canon((w[j] >> 16) & 0xffu);
+                    v.w = decode4_canon(w[j] >> 24);
+                    *reinterpret_cast<uint4*>(dst + (((h * 4 + j) ^ (r & 7)) << 4)) = v;
+                }
+            }
+            fence_generic_to_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&w_full[p]);
+        }
+        if (!ok && lane == 0) {
+            report_status(a.status, kDevWaitFull);
+            *abort_flag = 1;
+        }
+
+        // =============================== epilogue ===============================
+        // thread = token row (tensor-memory lane); the two warps of a lane quarter split the 32
+        // output columns
+        const bool acc_ok = warp_wait(acc_full, 0, lane) && !*abort_flag;
+        pf::fence_after_sync();
+        if (acc_ok) {
+            const int quarter = warp & 3;
+            const int half = (warp - 3) >> 2;
+            const int t = t0 + quarter * 32 + lane;
+            const int oc = o0 + half * 16;
+            uint32_t acc[16];
+            tmem_ld16(tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(half * 16), acc);
+            const bool t_valid = t < a.n_rows;
+            float* dst = t_valid ? a.rows[t].dst + oc : nullptr;
+            const float is = t_valid ? a.inv_scale[a.q_row0 + t] : 0.f;
+            pf::tmem_wait_ld();
+            if (t_valid) {
+                if (oc + 16 <= a.out_dim && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+                    for (int i = 0; i < 16; i += 4) {
+                        const float4 ws = *reinterpret_cast<const float4*>(a.w_scales + oc + i);
+                        float4 v;
+                        v.x = __fmul_rn(__fmul_rn(float(int(acc[i + 0])), is), ws.x);
+                        v.y = __fmul_rn(__fmul_rn(float(int(acc[i + 1])), is), ws.y);
+                        v.z = __fmul_rn(__fmul_rn(float(int(acc[i + 2])), is), ws.z);
+                        v.w = __fmul_rn(__fmul_rn(float(int(acc[i + 3])), is), ws.w);
+                        *reinterpret_cast<float4*>(dst + i) = v;
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i)
+                        if (oc + i < a.out_dim)
+                            dst[i] = __fmul_rn(__fmul_rn(float(int(acc[i])), is), a.w_scales[oc + i]);
+                }
+            }
+        } else if (lane == 0 && !*abort_flag) {
+            report_status(a.status, kDevWaitMma);
+        }
+    }
+
+    pf::fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        pf::fence_after_sync();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                     "r"(uint32_t(kTN))
+                     : "memory");
+    }
+}
+
+}  // namespace xn

@@ -58,8 +58,8 @@ inline void ternary_linear_pack(size_t in_dim, size_t out_dim, const float* weig
 }
 
 // One packed row -> the device format: 2-bit pack4 codes, `stride` bytes per row, positions
-// past in_dim hold code 1 (weight 0).  Codes 3 of a pack4 row (which decode to 0,
-// quantization.rs:36-40) and base-3 digits of a pack5 row are kept / translated one to one.
+// past in_dim hold code 1 (weight 0).  Code 3 of a pack4 row decodes to 0 in the reference
+// (quantization.rs:36-40) and becomes code 1 here; base-3 digits of a pack5 row map one to one.
 inline void recode_row_2bit(const uint8_t* src, size_t in_dim, int pack, uint8_t* dst, size_t stride) {
     for (size_t b = 0; b < stride; ++b) dst[b] = 0x55u;
     for (size_t i = 0; i < in_dim; ++i) {
@@ -70,6 +70,7 @@ inline void recode_row_2bit(const uint8_t* src, size_t in_dim, int pack, uint8_t
             code = cur % 3;
         } else {
             code = (src[i / 4] >> ((i % 4) * 2)) & 3u;
+            if (code == 3u) code = 1u;  // both decode to weight 0; the kernels rely on codes 0..2
         }
         uint8_t& byte = dst[i / 4];
         byte = uint8_t((byte & ~(3u << ((i % 4) * 2))) | (code << ((i % 4) * 2)));
