@@ -100,8 +100,36 @@ static void shape_errors() {  // fast_attention.rs:86-92
     CHECK(threw, "batch message");
 }
 
+// tests/bit1_58_tests.rs:68-92 (test_ternary_linear_layer): pack4 and pack5 give the same output,
+// and the literals of that test, which belong to the global weight scale 5/8 it was written with.
+static void ternary_linear_layer() {
+    using namespace xor_net;
+    AttnContext ctx(0, 1, 1, 1, 4, 1);
+    const std::vector<float> w = {1, 0, -1, 1, 0, -1, 1, 0};
+    const FastTensor x({0.5f, 1.0f, -0.5f, 2.0f}, {1, 4});
+    set_out_proj(ctx, 0, TernaryLinear::create(4, 2, w, TernaryPackType::Pack4, 0.625f), nullptr);
+    const FastTensor o4 = out_proj_forward(ctx, 0, x, 2);
+    set_out_proj(ctx, 0, TernaryLinear::create(4, 2, w, TernaryPackType::Pack5, 0.625f), nullptr);
+    const FastTensor o5 = out_proj_forward(ctx, 0, x, 2);
+    CHECK(o4.data == o5.data, "pack4 == pack5");
+    CHECK(std::fabs(o4.data[0] - 1.879921f) < 1e-4f, "o_proj[0]");
+    CHECK(std::fabs(o4.data[1] + 0.944882f) < 1e-4f, "o_proj[1]");
+    // tests/tensor_rmsnorm_tests.rs:20-31 through the block: identity weights, unit norm weight
+    AttnContext ctx2(0, 1, 1, 1, 2, 1);
+    FastRmsNorm norm;
+    norm.eps = 1e-6f;
+    norm.weight = {1.0f, 1.0f};
+    set_out_proj(ctx2, 0, TernaryLinear::create(2, 2, {1, 0, 0, 1}, TernaryPackType::Pack4, NAN), &norm);
+    const FastTensor n = out_proj_forward(ctx2, 0, FastTensor({3.0f, 4.0f}, {1, 2}), 2);
+    // normalised row (3,4)/sqrt(12.5) quantised to i8 with scale 127/max and dequantised again
+    const float rms = std::sqrt(12.5f), mx = 4.0f / rms;
+    CHECK(std::fabs(n.data[1] - mx) < 1e-5f, "sub-norm max element");
+    CHECK(std::fabs(n.data[0] - std::round(3.0f / rms * (127.0f / mx)) * (mx / 127.0f)) < 1e-5f, "sub-norm other element");
+}
+
 int main() {
     try {
+        ternary_linear_layer();
         attention_single_token_is_identity();
         attention_causal_mask_second_token_no_future();
         attention_output_finite();

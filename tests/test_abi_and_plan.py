@@ -118,3 +118,22 @@ def test_plan_split_edge_cases():
     ctas, items, cta, n_parts = run_plan([], 64, 148)
     assert ctas == 0
     assert xn.load().xn_plan_split(1, None, 64, 148, 8, None, None, None, None, None, None, None) < 0
+
+
+def test_ternary_pack_matches_the_oracle_packer():
+    # xn_ternary_pack is host-only (TernaryLinear::new, dense representation): no GPU needed
+    import oracle as xo
+    from xor_net_b200.api import TernaryLinear
+
+    rng = np.random.default_rng(3)
+    for pack in (xo.PACK4, xo.PACK5):
+        for in_dim, out_dim in ((1, 1), (7, 3), (64, 5), (33, 2), (2560, 3)):
+            w = rng.standard_normal((out_dim, in_dim)).astype(np.float32)
+            tern = rng.integers(-1, 2, (out_dim, in_dim)).astype(np.float32)
+            for weights, scale in ((w, None), (w, 0.7), (tern, None), (tern, 0.25)):
+                a = xo.TernaryLinear(in_dim, out_dim, weights, pack, scale)
+                b = TernaryLinear(in_dim, out_dim, weights, pack, scale)
+                assert np.array_equal(a.packed, b.packed[:a.packed.size]), (pack, in_dim, out_dim, scale)
+                assert np.array_equal(a.w_scales, b.w_scales)
+    with pytest.raises(ValueError):
+        TernaryLinear(4, 2, np.zeros(7, np.float32))

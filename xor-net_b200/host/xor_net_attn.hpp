@@ -18,6 +18,8 @@
 #include <tuple>
 #include <vector>
 
+#include <cstdint>
+
 #include "xn_attn.h"
 
 namespace xor_net {
@@ -140,6 +142,71 @@ inline FastTensor fast_attention(const FastTensor& q, const FastTensor& k, const
                           k.data.data(), v.data.data(), out.data.data());
     if (rc != XN_OK)
         throw std::runtime_error("xn_attention failed (" + std::to_string(rc) + "): " + xn_last_error(ctx));
+    return out;
+}
+
+// ---- attention output block (src/models/llama/attention.rs:103-108) ---------------------------
+
+enum class TernaryPackType { Pack4 = XN_PACK4, Pack5 = XN_PACK5 };
+
+// TernaryLinear with the dense packed representation (src/bit1_58/layers.rs:34-149): `create`
+// ternarises and packs exactly like TernaryLinear::new; the forward pass runs on the device.
+struct TernaryLinear {
+    size_t in_dim = 0, out_dim = 0;
+    TernaryPackType pack_type = TernaryPackType::Pack4;
+    std::vector<uint8_t> packed;
+    std::vector<float> w_scales;
+
+    // provided_scale: NaN stands for None
+    static TernaryLinear create(size_t in_dim, size_t out_dim, const std::vector<float>& weights_f32,
+                                TernaryPackType pack_type, float provided_scale) {
+        if (weights_f32.size() != in_dim * out_dim)
+            throw std::runtime_error("Weight length must match in_dim * out_dim");
+        TernaryLinear l;
+        l.in_dim = in_dim;
+        l.out_dim = out_dim;
+        l.pack_type = pack_type;
+        const size_t per = pack_type == TernaryPackType::Pack5 ? 5 : 4;
+        l.packed.assign(out_dim * ((in_dim + per - 1) / per), 0);
+        l.w_scales.assign(out_dim, 0.0f);
+        if (xn_ternary_pack(int(in_dim), int(out_dim), weights_f32.data(), int(pack_type), provided_scale,
+                            l.packed.data(), l.w_scales.data()) != XN_OK)
+            throw std::runtime_error("xn_ternary_pack failed");
+        return l;
+    }
+};
+
+struct FastRmsNorm {  // src/nn/fast_rmsnorm.rs:5-17
+    float eps = 1e-5f;
+    std::vector<float> weight;
+};
+
+// Uploads a layer's o_proj (and optional sub-norm) to the context.
+inline void set_out_proj(AttnContext& ctx, size_t layer, const TernaryLinear& o_proj,
+                         const FastRmsNorm* sub_norm) {
+    xn_out_proj_desc d{};
+    d.layer = int(layer);
+    d.in_dim = int(o_proj.in_dim);
+    d.out_dim = int(o_proj.out_dim);
+    d.pack_type = int(o_proj.pack_type);
+    d.packed = o_proj.packed.data();
+    d.w_scales = o_proj.w_scales.data();
+    d.norm_weight = sub_norm ? sub_norm->weight.data() : nullptr;
+    d.norm_eps = sub_norm ? sub_norm->eps : 0.0f;
+    if (xn_out_proj_set(ctx.get(), &d) != XN_OK)
+        throw std::runtime_error(std::string("xn_out_proj_set: ") + xn_last_error(ctx.get()));
+}
+
+// y [.., in_dim] -> o_proj(sub_norm(y)) [.., out_dim]: FastRmsNorm::forward + TernaryLinear::forward.
+inline FastTensor out_proj_forward(AttnContext& ctx, size_t layer, const FastTensor& y, size_t out_dim) {
+    if (y.shape.empty()) throw std::runtime_error("Input must have at least 1 dimension");
+    const size_t in_dim = y.shape.back();
+    const size_t rows = in_dim ? y.data.size() / in_dim : 0;
+    std::vector<size_t> shape = y.shape;
+    shape.back() = out_dim;
+    FastTensor out = FastTensor::zeros(shape);
+    if (xn_out_proj(ctx.get(), int(layer), int(rows), y.data.data(), out.data.data(), 0) != XN_OK)
+        throw std::runtime_error(std::string("xn_out_proj: ") + xn_last_error(ctx.get()));
     return out;
 }
 
