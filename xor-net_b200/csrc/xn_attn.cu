@@ -100,6 +100,7 @@ struct xn_ctx {
     bool fuse_append = true; // decode batches: the attention kernel appends the new token itself
     bool fuse_pinned = true; // ... also when q,k,v live in page-locked host memory
     bool out_tc = true;      // output projection on the tensor cores (else the dp4a kernel)
+    bool out_pdl = true;     // ... launched as a programmatic dependent of the quantiser kernel
     int* sync_d = nullptr;   // chunk counter, done counter, per-unit arrival counters
     size_t sync_cap = 0;     // ints
     cudaStream_t stream = nullptr;
@@ -379,8 +380,23 @@ int32_t launch_out_block(xn_ctx* c, int layer, const OutRowDev* rows_d, int n_ro
     const OutProj& op = c->out_proj[size_t(layer)];
     int8_t* q = reinterpret_cast<int8_t*>(c->q8);
     float* inv = c->q8 + q_rows_pad * size_t(op.q_stride) / 4;
-    subnorm_quant_kernel<<<unsigned(n_rows), 256, align_up(size_t(op.in_dim), 4) * 12, c->stream>>>(
-        rows_d, op.norm_w, op.eps, op.in_dim, q, op.q_stride, (long long)q_row0, (long long)q_rows_pad, inv);
+    {
+        // a programmatic dependent of whatever kernel precedes it in the stream (the attention
+        // kernel when the block runs behind one): its launch overlaps that kernel's tail
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(unsigned(n_rows));
+        cfg.blockDim = dim3(256);
+        cfg.dynamicSmemBytes = align_up(size_t(op.in_dim), 4) * 12;
+        cfg.stream = c->stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = c->out_pdl ? 1 : 0;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        XN_CUDA(c, cudaLaunchKernelEx(&cfg, subnorm_quant_kernel, rows_d, (const float*)op.norm_w, op.eps,
+                                      op.in_dim, q, op.q_stride, (long long)q_row0, (long long)q_rows_pad,
+                                      inv));
+    }
     if (c->out_tc && op.q_stride / tg::kBK <= tg::max_nkb()) {
         // tensor cores: 128 token rows x 32 output rows per block, the block's weights resident
         TernaryGemmArgs ga;
@@ -389,7 +405,19 @@ int32_t launch_out_block(xn_ctx* c, int layer, const OutRowDev* rows_d, int n_ro
         ga.n_rows = n_rows; ga.out_dim = op.out_dim; ga.k_bytes = op.q_stride;
         ga.status = c->status_d;
         dim3 grid(unsigned((op.out_dim + tg::kTN - 1) / tg::kTN), unsigned((n_rows + tg::kTM - 1) / tg::kTM));
-        ternary_gemm_tc_kernel<<<grid, tg::kThreads, tg::smem_bytes(op.q_stride / tg::kBK), c->stream>>>(ga);
+        // programmatic dependent launch: the blocks may start while the quantiser kernel still
+        // runs (it releases them at its start) and decode their weights in the meantime
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(tg::kThreads);
+        cfg.dynamicSmemBytes = size_t(tg::smem_bytes(op.q_stride / tg::kBK));
+        cfg.stream = c->stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = c->out_pdl ? 1 : 0;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        XN_CUDA(c, cudaLaunchKernelEx(&cfg, ternary_gemm_tc_kernel, ga));
     } else {
         const int R = std::max(1, std::min(kOutMaxRowsPerCta, (op.out_dim + c->sm_count - 1) / c->sm_count));
         dim3 grid(unsigned((op.out_dim + R - 1) / R), unsigned((n_rows + kOutRowsTile - 1) / kOutRowsTile));
@@ -922,6 +950,7 @@ int32_t xn_ctx_create(const xn_ctx_desc* d, xn_ctx** out_ctx) {
     if (const char* env = getenv("XORNET_ATTN_FUSE_APPEND")) c->fuse_append = atoi(env) != 0;
     if (const char* env = getenv("XORNET_ATTN_FUSE_PINNED")) c->fuse_pinned = atoi(env) != 0;
     if (const char* env = getenv("XORNET_ATTN_OUTPROJ_TC")) c->out_tc = atoi(env) != 0;
+    if (const char* env = getenv("XORNET_ATTN_OUTPROJ_PDL")) c->out_pdl = atoi(env) != 0;
 
 
     const size_t page_bytes =

@@ -181,6 +181,16 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
+// ---- programmatic dependent launch ------------------------------------------------------------
+// A kernel launched with the programmatic-stream-serialization attribute may start while its
+// predecessor in the stream still runs, once every block of the predecessor has called
+// pdl_launch_dependents() (or exited); it must call pdl_wait() before it touches anything the
+// predecessor writes (the wait returns when the predecessor has completed and flushed).
+__device__ __forceinline__ void pdl_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ---- counter-based N(0,1) generator ---------------------------------------------------------
 
 __host__ __device__ __forceinline__ uint64_t mix64(uint64_t z) {

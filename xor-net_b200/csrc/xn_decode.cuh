@@ -185,6 +185,9 @@ attn_splitkv_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restrict__
     constexpr int SQ = Cfg::kSlotsQ, SV = Cfg::kSlotsV;
     constexpr unsigned kFull = 0xffffffffu;
 
+    // a kernel launched behind this one as a programmatic dependent (the output block's quantiser)
+    // may be set up now; it waits for this kernel's completion before it reads the rows
+    pdl_launch_dependents();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     float* red = reinterpret_cast<float*>(smem_raw + ST * Sm::kStageBytes);
     float* scratch = red + Sm::kRedFloats;

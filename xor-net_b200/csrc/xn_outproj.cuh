@@ -59,6 +59,10 @@ subnorm_quant_kernel(const OutRowDev* __restrict__ rows, const float* __restrict
     extern __shared__ float row_s[];
     __shared__ float red_s[8];
     __shared__ float bc_s;
+    // the projection kernel behind this one may start now: its prologue (fetching and decoding its
+    // weights) does not depend on anything written here, and it waits before it reads the rows
+    pdl_launch_dependents();
+    pdl_wait();   // this kernel itself may have been set up while the attention kernel still ran
     const int r = blockIdx.x;
     const float* src = rows[r].src;
     const int tid = threadIdx.x;
@@ -118,8 +122,22 @@ subnorm_quant_kernel(const OutRowDev* __restrict__ rows, const float* __restrict
             row_s[i] = __fmul_rn(__fmul_rn(row_s[i], inv_rms), nw_s[i]);
         __syncthreads();
     }
+    // each thread owns whole 16-element chunks from here on: the unit of the quantiser's rounding
+    // rule and of the swizzled global layout
+    const int n_chunks = q_stride >> 4;
     float m = 0.f;
-    for (int i = tid; i < in_dim; i += blockDim.x) m = fmaxf(m, fabsf(row_s[i]));
+    for (int c = tid; c < n_chunks; c += blockDim.x) {
+        const int i0 = c << 4;
+        if (i0 + 16 <= in_dim) {
+#pragma unroll
+            for (int j = 0; j < 16; j += 4) {
+                const float4 v = *reinterpret_cast<const float4*>(row_s + i0 + j);
+                m = fmaxf(m, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+            }
+        } else {
+            for (int i = i0; i < in_dim; ++i) m = fmaxf(m, fabsf(row_s[i]));
+        }
+    }
     for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
     if ((tid & 31) == 0) red_s[tid >> 5] = m;
     __syncthreads();
@@ -128,14 +146,22 @@ subnorm_quant_kernel(const OutRowDev* __restrict__ rows, const float* __restrict
     const float scale = m > 0.f ? __fdiv_rn(127.0f, m) : 1.0f;
     if (tid == 0) inv_scale_out[q_row0 + r] = m > 0.f ? __fdiv_rn(m, 127.0f) : 1.0f;
     const int simd_end = (in_dim / 16) * 16;
-    for (int i = tid; i < q_stride; i += blockDim.x) {
-        int v = 0;
-        if (i < in_dim) {
-            const float s = __fmul_rn(row_s[i], scale);
-            if (i < simd_end) v = __float2int_rn(fmaxf(-127.0f, fminf(127.0f, s)));
-            else v = int(fmaxf(-127.0f, fminf(127.0f, roundf(s))));
+    for (int c = tid; c < n_chunks; c += blockDim.x) {
+        const int i0 = c << 4;
+        uint32_t packed[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int i = i0 + j;
+            int v = 0;
+            if (i < in_dim) {
+                const float s = __fmul_rn(row_s[i], scale);
+                if (i < simd_end) v = __float2int_rn(fmaxf(-127.0f, fminf(127.0f, s)));
+                else v = int(fmaxf(-127.0f, fminf(127.0f, roundf(s))));
+            }
+            packed[j >> 2] |= uint32_t(v & 0xff) << ((j & 3) * 8);
         }
-        q_out[act_offset(q_row0 + r, i, q_rows_pad)] = int8_t(v);
+        *reinterpret_cast<uint4*>(q_out + act_offset(q_row0 + r, i0, q_rows_pad)) =
+            make_uint4(packed[0], packed[1], packed[2], packed[3]);
     }
 }
 

@@ -10,23 +10,27 @@
 // number of tokens up to 128.  What shapes the kernel is latency, not throughput: one barrier
 // hand-off costs ~100-200 cycles and a 128-column step only holds ~200 cycles of tensor work, so
 //   * the block's whole weight slab [32 rows x K] is decoded ONCE into shared memory (80 KB for
-//     K = 2560), in coarse pieces of 512 columns, instead of being re-staged every step;
-//   * the activations stream through a ring of 256-column stages that are contiguous in global
-//     memory AND already laid out the way the tensor core reads them (act_offset), so a stage is
-//     two plain bulk copies; tiled tensor-map loads of the same tiles were several times slower
-//     (one request per row);
-//   * ring positions and phases are counted, never divided out, and every control warp runs its
-//     loop converged with one lane issuing.
-// Roles (352 threads):
+//     K = 2560), in pieces of 512 columns, instead of being re-staged every step; the codes of
+//     all pieces are fetched into registers up front;
+//   * the activations stream through two 512-column stages that are contiguous in global memory
+//     AND already laid out the way the tensor core reads them (act_offset), so a stage is four
+//     plain bulk copies; tiled tensor-map loads of the same tiles were several times slower (one
+//     request per row);
+//   * one stage = one piece = 16 MMAs: five hand-offs for K = 2560; ring positions and phases
+//     are counted, never divided out; the control warps run their loops converged with one lane
+//     issuing, operand descriptors are built before the loop;
+//   * the kernel is launched as a programmatic dependent of the quantiser kernel: its blocks start
+//     while that kernel runs, fetch and decode their weights, and only then wait for the rows.
+// Roles (320 threads):
 //   warp 0      copy producer: activation stages (bulk async copies, no tensor map, no multicast);
-//   warp 1      MMA issuer (one lane): eight tcgen05.mma (K = 32 each) per stage, both operands
+//   warp 1      MMA issuer (one lane): sixteen tcgen05.mma (K = 32 each) per stage, both operands
 //               from shared memory; tcgen05.commit frees the stage and finally signals the
 //               epilogue; owns the tensor-memory allocation (32 columns);
-//   warp 2      copy producer: the block's 2-bit codes, one bulk copy per 512 columns;
-//   warps 3..10 weight decoders: 64 weights (16 bytes of codes) per thread and item, five
+//   warps 2..9  weight decoders: 64 weights (16 bytes of codes) per thread and piece, five
 //               integer instructions per four weights, stored in the K-major 128-byte-swizzled
-//               operand layout.  Afterwards the same warps are the epilogue: thread = token row,
-//               tcgen05.ld of 16 output columns, two rounded multiplies, 64 contiguous bytes out.
+//               operand layout.  Afterwards the same warps are the epilogue: tcgen05.ld, a pass
+//               through shared memory, then whole 128-byte row segments out with the two rounded
+//               multiplies applied.
 // Every wait is bounded; on expiry the kernel records a status code, drains and returns.
 #pragma once
 #include "xn_outproj.cuh"
@@ -38,24 +42,22 @@ namespace tg {
 constexpr int kTM = 128;                 // token rows per block (MMA M)
 constexpr int kTN = 32;                  // output rows per block (MMA N)
 constexpr int kBK = 128;                 // K bytes (= i8 elements) per K-block
-constexpr int kStepKb = 2;               // K-blocks per activation stage
+constexpr int kPieceKb = 4;              // K-blocks per piece = per activation stage
 constexpr int kActBlock = kTM * kBK;     // 16 KB: one K-block of one token tile
-constexpr int kActStage = kStepKb * kActBlock;
-constexpr int kMaxActStages = 3;
+constexpr int kActStage = kPieceKb * kActBlock;   // 64 KB
+constexpr int kActStages = 2;
 constexpr int kWBlock = kTN * kBK;       // 4 KB of decoded weights per K-block
 constexpr int kCBlock = kTN * kBK / 4;   // 1 KB of codes per K-block
-constexpr int kPieceKb = 4;              // K-blocks per decode piece (one code copy, one barrier)
-constexpr int kMaxPieces = 8;            // K <= 4096
-constexpr int kThreads = 352;
+constexpr int kMaxPieces = 6;            // K <= 3072: 128 KB of stages + 96 KB of weights
+constexpr int kThreads = 320;
 constexpr int kDecoderWarps = 8;
+constexpr int kOutStride = kTN + 1;      // floats per staged output row (conflict-free both ways)
 
-// three activation stages while the weight slab leaves room for them (K <= 3072), else two
-__host__ __device__ constexpr int act_stages(int nkb) { return nkb <= 24 ? 3 : 2; }
 __host__ __device__ constexpr int smem_bytes(int nkb) {
-    return act_stages(nkb) * kActStage + nkb * (kWBlock + kCBlock) + 1024 /* alignment slack */ +
-           512 /* barriers */;
+    return kActStages * kActStage + nkb * kWBlock + 1024 /* alignment slack */ + 512 /* barriers */;
 }
 __host__ __device__ constexpr int max_nkb() { return kMaxPieces * kPieceKb; }
+static_assert(kTM * kOutStride * 4 <= kActStage, "the output tile is staged in a retired activation stage");
 
 // Instruction descriptor, kind::i8: [4,6) D format 2 = s32, [7,10) A format 1 = s8, [10,13) B
 // format 1 = s8, bits 15/16 A/B major 0 = K-major, [17,23) N >> 3, [24,29) M >> 4.
@@ -105,6 +107,14 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 }
 }  // namespace tg
 
+#ifdef XN_TG_TIMING
+// tuning build: cycle stamps of block 0, stored as they happen, printed by the block at its end
+__device__ long long g_tg_dbg[256];
+#define TGD(idx) do { if (blockIdx.x == 0 && blockIdx.y == 0) g_tg_dbg[idx] = clock64() - tg_t0; } while (0)
+#else
+#define TGD(idx)
+#endif
+
 struct TernaryGemmArgs {
     const int8_t* q;         // activations, tiled: act_offset()
     const uint8_t* w2;       // weight codes, tiled: code_offset()
@@ -127,34 +137,46 @@ ternary_gemm_tc_kernel(const TernaryGemmArgs a) {
         (reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
     const int nkb = a.k_bytes / kBK;
     const int n_pieces = (nkb + kPieceKb - 1) / kPieceKb;
-    const int n_steps = (nkb + kStepKb - 1) / kStepKb;
-    const int kActStages = act_stages(nkb);
-    unsigned char* act_s = smem;                                  // [kActStages][kStepKb][128 rows x 128 B]
+    unsigned char* act_s = smem;                                  // [kActStages][kPieceKb][128 rows x 128 B]
     unsigned char* w_s = act_s + kActStages * kActStage;          // [nkb][32 rows x 128 B], decoded
-    unsigned char* c_s = w_s + nkb * kWBlock;                     // [nkb][32 rows x 32 B], codes
-    uint64_t* bars = reinterpret_cast<uint64_t*>(c_s + nkb * kCBlock);
-    uint64_t* act_full = bars;                       // [kActStages] stage landed (copy bytes)
-    uint64_t* act_empty = act_full + kMaxActStages;  // [kActStages] the MMAs that read it are done
-    uint64_t* c_full = act_empty + kMaxActStages;    // [kMaxPieces] codes of the piece landed
-    uint64_t* w_full = c_full + kMaxPieces;          // [kMaxPieces] piece decoded (one arrival per decoder warp)
-    uint64_t* acc_full = w_full + kMaxPieces;        // all MMAs done
+    uint64_t* bars = reinterpret_cast<uint64_t*>(w_s + nkb * kWBlock);
+    // one barrier per piece, used once: the activation copies' bytes AND the eight decoder warps'
+    // arrivals complete it, so the MMA issuer pays one barrier wait per piece
+    uint64_t* piece_full = bars;                     // [kMaxPieces]
+    uint64_t* act_empty = piece_full + kMaxPieces;   // [kActStages] the MMAs that read the stage are done
+    uint64_t* acc_full = act_empty + kActStages;     // all MMAs done
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);
-    static_assert((2 * kMaxActStages + 2 * kMaxPieces + 1) * 8 + 16 <= 512, "barrier area");
+    static_assert((kActStages + kMaxPieces + 1) * 8 + 16 <= 512, "barrier area");
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#ifdef XN_TG_TIMING
+    const long long tg_t0 = clock64();
+#endif
     const int o0 = blockIdx.x * kTN;
     const int t0 = blockIdx.y * kTM;
 
+    // decoders: this thread's codes of every piece, requested before anything else happens
+    // item = (K-block, row, half): 16 bytes of codes -> 64 i8; 64 items per K-block, so one pass of
+    // the 256 decoder threads covers one piece of 4 K-blocks
+    const int dtid = tid - 64;                   // 0..255 for decoder threads
+    const int kb_in = (dtid >> 6) & 3;           // K-block inside the piece
+    const int r = (dtid >> 1) & 31, h = dtid & 1;
+    uint4 codes[kMaxPieces];
+    if (warp >= 2) {
+        const bool valid = o0 + r < a.out_dim;   // rows past the matrix decode to weight 0
+        const uint8_t* src = a.w2 + (size_t(blockIdx.x) * nkb + kb_in) * kCBlock + r * 32 + h * 16;
+#pragma unroll
+        for (int p = 0; p < kMaxPieces; ++p) {
+            codes[p] = make_uint4(0x55555555u, 0x55555555u, 0x55555555u, 0x55555555u);
+            if (valid && p * kPieceKb + kb_in < nkb)
+                codes[p] = __ldg(reinterpret_cast<const uint4*>(src + size_t(p) * kPieceKb * kCBlock));
+        }
+    }
+
     if (tid == 0) {
-        for (int s = 0; s < kActStages; ++s) {
-            mbar_init(&act_full[s], 1);
-            mbar_init(&act_empty[s], 1);
-        }
-        for (int p = 0; p < n_pieces; ++p) {
-            mbar_init(&c_full[p], 1);
-            mbar_init(&w_full[p], kDecoderWarps);
-        }
+        for (int s = 0; s < kActStages; ++s) mbar_init(&act_empty[s], 1);
+        for (int p = 0; p < n_pieces; ++p) mbar_init(&piece_full[p], 1 + kDecoderWarps);
         mbar_init(acc_full, 1);
         *abort_flag = 0;
         mbar_fence_init();
@@ -170,26 +192,17 @@ ternary_gemm_tc_kernel(const TernaryGemmArgs a) {
     __syncthreads();
     pf::fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    if (tid == 0) TGD(0);
 
-    if (warp == 2) {
-        // ======================= copy producer: the block's weight codes =======================
-        if (lane == 0) {
-            const uint8_t* src = a.w2 + size_t(blockIdx.x) * nkb * kCBlock;
-            for (int p = 0; p < n_pieces; ++p) {
-                const int kbs = min(kPieceKb, nkb - p * kPieceKb);
-                mbar_arrive_expect_tx(&c_full[p], uint32_t(kbs * kCBlock));
-                bulk_g2s(c_s + p * kPieceKb * kCBlock, src + size_t(p) * kPieceKb * kCBlock,
-                         uint32_t(kbs * kCBlock), &c_full[p]);
-            }
-        }
-    } else if (warp == 0) {
+    if (warp == 0) {
         // ======================= copy producer: activation stages =======================
+        pdl_wait();   // the activation rows are written by the kernel launched before this one
         const int8_t* src = a.q + size_t(a.q_row0 + t0) * kBK;
         const size_t kb_step = size_t(a.q_rows_pad) * kBK;   // one K-block further in global memory
         int st = 0;
         uint32_t wrap_par = 1;   // parity of the `empty` phase that frees the stage being refilled
-        for (int s = 0; s < n_steps; ++s) {
-            if (s >= kActStages) {
+        for (int p = 0; p < n_pieces; ++p) {
+            if (p >= kActStages) {
                 wrap_par ^= (st == 0) ? 1u : 0u;
                 if (!warp_wait(&act_empty[st], wrap_par, lane)) {
                     if (lane == 0) {
@@ -200,45 +213,55 @@ ternary_gemm_tc_kernel(const TernaryGemmArgs a) {
                 }
             }
             if (lane == 0) {
-                const int kbs = min(kStepKb, nkb - s * kStepKb);
-                mbar_arrive_expect_tx(&act_full[st], uint32_t(kbs * kActBlock));
+                const int kbs = min(kPieceKb, nkb - p * kPieceKb);
+                mbar_arrive_expect_tx(&piece_full[p], uint32_t(kbs * kActBlock));
                 for (int j = 0; j < kbs; ++j)
                     bulk_g2s(act_s + st * kActStage + j * kActBlock, src + size_t(j) * kb_step,
-                             uint32_t(kActBlock), &act_full[st]);
+                             uint32_t(kActBlock), &piece_full[p]);
             }
-            src += size_t(kStepKb) * kb_step;
-            if (++st == kActStages) st = 0;
+            src += size_t(kPieceKb) * kb_step;
+            st ^= 1;
             __syncwarp();
         }
     } else if (warp == 1) {
         // =============================== MMA issuer ===============================
         const uint32_t idesc = make_idesc_i8(kTM, kTN);
+        // descriptor address fields advance by bytes >> 4
+        const uint64_t adesc0 = pf::smem_desc(smem_u32(act_s), 0, 1024, pf::kLayoutSw128);
+        uint64_t bdesc = pf::smem_desc(smem_u32(w_s), 0, 1024, pf::kLayoutSw128);
         bool ok = true;
         int st = 0;
-        uint32_t par = 0;
-        int pieces_seen = 0;
-        for (int s = 0; s < n_steps; ++s) {
-            const int kb0 = s * kStepKb;
-            const int kbs = min(kStepKb, nkb - kb0);
-            const int need_piece = (kb0 + kbs - 1) / kPieceKb;   // compile-time divisor
-            while (ok && pieces_seen <= need_piece) ok = warp_wait(&w_full[pieces_seen++], 0, lane);
-            ok = ok && warp_wait(&act_full[st], par, lane);
+        for (int p = 0; p < n_pieces; ++p) {
+            if (lane == 0) TGD(96 + p);
+            ok = warp_wait(&piece_full[p], 0, lane);
             if (!ok || *abort_flag) { ok = false; break; }
             if (lane == 0) {
+                TGD(48 + p);
                 pf::fence_after_sync();
-                for (int j = 0; j < kbs; ++j) {
-                    const uint64_t adesc = pf::smem_desc(smem_u32(act_s + st * kActStage + j * kActBlock), 0,
-                                                         1024, pf::kLayoutSw128);
-                    const uint64_t bdesc = pf::smem_desc(smem_u32(w_s + (kb0 + j) * kWBlock), 0, 1024,
-                                                         pf::kLayoutSw128);
+                const int kbs = min(kPieceKb, nkb - p * kPieceKb);
+                const uint64_t adesc = adesc0 + uint64_t(st * (kActStage >> 4));
+                // 32 bytes of K per instruction: +2 in the descriptor's address field
+                if (kbs == kPieceKb) {
 #pragma unroll
-                    for (int k4 = 0; k4 < kBK / 32; ++k4)   // 32 bytes of K per instruction: +2 in the address field
-                        mma_ss_i8(tmem_base, adesc + uint64_t(k4 * 2), bdesc + uint64_t(k4 * 2), idesc,
-                                  uint32_t((s | j | k4) != 0));
+                    for (int j = 0; j < kPieceKb; ++j)
+#pragma unroll
+                        for (int k4 = 0; k4 < kBK / 32; ++k4)
+                            mma_ss_i8(tmem_base, adesc + uint64_t(j * (kActBlock >> 4) + k4 * 2),
+                                      bdesc + uint64_t(j * (kWBlock >> 4) + k4 * 2), idesc,
+                                      uint32_t((p | j | k4) != 0));
+                } else {
+                    for (int j = 0; j < kbs; ++j)
+#pragma unroll
+                        for (int k4 = 0; k4 < kBK / 32; ++k4)
+                            mma_ss_i8(tmem_base, adesc + uint64_t(j * (kActBlock >> 4) + k4 * 2),
+                                      bdesc + uint64_t(j * (kWBlock >> 4) + k4 * 2), idesc,
+                                      uint32_t((p | j | k4) != 0));
                 }
+                bdesc += uint64_t(kPieceKb * (kWBlock >> 4));
                 pf::mma_commit(&act_empty[st]);
+                TGD(64 + p);
             }
-            if (++st == kActStages) { st = 0; par ^= 1u; }
+            st ^= 1;
             __syncwarp();
         }
         if (lane == 0) {
@@ -251,84 +274,84 @@ ternary_gemm_tc_kernel(const TernaryGemmArgs a) {
         }
     } else {
         // =============================== weight decoders ===============================
-        // item = (K-block, row, half): 16 bytes of codes -> 64 i8.  64 items per K-block, so one
-        // pass of the 256 decoder threads covers one piece of 4 K-blocks.
-        const int dtid = tid - 96;            // 0..255
-        const int kb_in = dtid >> 6;          // K-block inside the piece
-        const int r = (dtid >> 1) & 31, h = dtid & 1;
-        const bool valid = o0 + r < a.out_dim;   // rows past the matrix decode to weight 0
         const int w_off = (r >> 3) * 1024 + (r & 7) * 128;
-        bool ok = true;
-        for (int p = 0; p < n_pieces; ++p) {
-            ok = warp_wait(&c_full[p], 0, lane);
-            if (!ok || *abort_flag) break;
-            const int kb = p * kPieceKb + kb_in;
-            if (kb < nkb) {
-                uint4 cur = *reinterpret_cast<const uint4*>(c_s + kb * kCBlock + r * 32 + h * 16);
-                if (!valid) cur = make_uint4(0x55555555u, 0x55555555u, 0x55555555u, 0x55555555u);
-                const uint32_t w[4] = {cur.x, cur.y, cur.z, cur.w};
-                unsigned char* dst = w_s + kb * kWBlock + w_off;
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    uint4 v;
-                    v.x = decode4_canon(w[j] & 0xffu);
-                    v.y = decode4_canon((w[j] >> 8) & 0xffu);
-                    v.z = decode4_canon((w[j] >> 16) & 0xffu);
-                    v.w = decode4_canon(w[j] >> 24);
-                    *reinterpret_cast<uint4*>(dst + (((h * 4 + j) ^ (r & 7)) << 4)) = v;
+        for (int p = 0; p < kMaxPieces; ++p) {
+            if (p < n_pieces) {
+                const int kb = p * kPieceKb + kb_in;
+                if (kb < nkb) {
+                    const uint32_t w[4] = {codes[p].x, codes[p].y, codes[p].z, codes[p].w};
+                    unsigned char* dst = w_s + kb * kWBlock + w_off;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        uint4 v;
+                        v.x = decode4_canon(w[j] & 0xffu);
+                        v.y = decode4_canon((w[j] >> 8) & 0xffu);
+                        v.z = decode4_canon((w[j] >> 16) & 0xffu);
+                        v.w = decode4_canon(w[j] >> 24);
+                        *reinterpret_cast<uint4*>(dst + (((h * 4 + j) ^ (r & 7)) << 4)) = v;
+                    }
                 }
+                fence_generic_to_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&piece_full[p]);
+                if (lane == 0 && warp == 2) TGD(32 + p);
             }
-            fence_generic_to_async_smem();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&w_full[p]);
-        }
-        if (!ok && lane == 0) {
-            report_status(a.status, kDevWaitFull);
-            *abort_flag = 1;
         }
 
         // =============================== epilogue ===============================
-        // thread = token row (tensor-memory lane); the two warps of a lane quarter split the 32
-        // output columns
+        // tensor memory -> registers (thread = token row; the two warps of a lane quarter split
+        // the 32 output columns) -> shared memory -> whole 128-byte row segments out
+        // (what the store pass needs from global memory is fetched before waiting for the MMAs)
+        pdl_wait();   // the inverse scales come from the kernel launched before this one
+        const int o = o0 + lane;
+        const bool o_valid = o < a.out_dim;
+        const float ws = o_valid ? a.w_scales[o] : 0.f;
+        const int tw = (warp - 2) * 16;    // this warp's 16 token rows of the tile in the store pass
+        const int t_mine = t0 + tw + (lane & 15);
+        float* dst_mine = t_mine < a.n_rows ? a.rows[t_mine].dst : nullptr;
+        const float is_mine = t_mine < a.n_rows ? a.inv_scale[a.q_row0 + t_mine] : 0.f;
         const bool acc_ok = warp_wait(acc_full, 0, lane) && !*abort_flag;
         pf::fence_after_sync();
+        if (lane == 0 && warp == 2) TGD(1);
+        float* out_s = reinterpret_cast<float*>(act_s);   // every stage has been consumed by now
         if (acc_ok) {
             const int quarter = warp & 3;
-            const int half = (warp - 3) >> 2;
-            const int t = t0 + quarter * 32 + lane;
-            const int oc = o0 + half * 16;
+            const int half = (warp - 2) >> 2;
             uint32_t acc[16];
             tmem_ld16(tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(half * 16), acc);
-            const bool t_valid = t < a.n_rows;
-            float* dst = t_valid ? a.rows[t].dst + oc : nullptr;
-            const float is = t_valid ? a.inv_scale[a.q_row0 + t] : 0.f;
             pf::tmem_wait_ld();
-            if (t_valid) {
-                if (oc + 16 <= a.out_dim && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+            float* row = out_s + (quarter * 32 + lane) * kOutStride + half * 16;
 #pragma unroll
-                    for (int i = 0; i < 16; i += 4) {
-                        const float4 ws = *reinterpret_cast<const float4*>(a.w_scales + oc + i);
-                        float4 v;
-                        v.x = __fmul_rn(__fmul_rn(float(int(acc[i + 0])), is), ws.x);
-                        v.y = __fmul_rn(__fmul_rn(float(int(acc[i + 1])), is), ws.y);
-                        v.z = __fmul_rn(__fmul_rn(float(int(acc[i + 2])), is), ws.z);
-                        v.w = __fmul_rn(__fmul_rn(float(int(acc[i + 3])), is), ws.w);
-                        *reinterpret_cast<float4*>(dst + i) = v;
-                    }
-                } else {
+            for (int i = 0; i < 16; ++i) row[i] = float(int(acc[i]));
+        }
+        named_bar_sync(1, kDecoderWarps * 32);
+        if (acc_ok) {
 #pragma unroll
-                    for (int i = 0; i < 16; ++i)
-                        if (oc + i < a.out_dim)
-                            dst[i] = __fmul_rn(__fmul_rn(float(int(acc[i])), is), a.w_scales[oc + i]);
-                }
+            for (int i = 0; i < 16; ++i) {
+                float* dst = reinterpret_cast<float*>(
+                    __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(dst_mine), i));
+                const float is = __shfl_sync(0xffffffffu, is_mine, i);
+                const float v = out_s[(tw + i) * kOutStride + lane];
+                if (dst != nullptr && o_valid) dst[o] = __fmul_rn(__fmul_rn(v, is), ws);
             }
         } else if (lane == 0 && !*abort_flag) {
             report_status(a.status, kDevWaitMma);
         }
     }
 
+    if (lane == 0 && warp == 2) TGD(2);
     pf::fence_before_sync();
     __syncthreads();
+#ifdef XN_TG_TIMING
+    if (tid == 0 && blockIdx.x == 0 && blockIdx.y == 0) {
+        __threadfence();
+        printf("tg setup %lld, acc ready %lld, epilogue done %lld\n", g_tg_dbg[0], g_tg_dbg[1], g_tg_dbg[2]);
+        for (int p = 0; p < n_pieces; ++p)
+            printf("tg piece %d: decoded %6lld  mma: waiting %6lld  operands seen %6lld  committed %6lld\n", p,
+                   g_tg_dbg[32 + p], g_tg_dbg[96 + p], g_tg_dbg[48 + p], g_tg_dbg[64 + p]);
+    }
+#endif
     if (warp == 1) {
         pf::fence_after_sync();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),

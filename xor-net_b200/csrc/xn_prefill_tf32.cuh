@@ -197,6 +197,7 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap k_map,
     float* xchg = reinterpret_cast<float*>(bars + 32);  // [2 warpgroups][128 rows]
     static_assert((1 + 2 * kKStages + 2 * kVStages + 3 * kSBufs) * 8 + 16 <= 256, "barrier area");
 
+    pdl_launch_dependents();   // see attn_splitkv_kernel
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // 1-D grid, longest query tiles first across ALL heads (blocks are handed to SMs in index
     // order, so the causal triangle is packed heaviest-first); neighbouring blocks are the heads
