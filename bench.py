@@ -47,6 +47,10 @@ WORKLOADS = {
     "c3o": (64, 20, 5, 128, 30, 128, 4096,
             "batched decode + output block (sub-norm, ternary o_proj 2560x2560) on the device, "
             "BitNet-2B shape: 64 streams/GPU x 30 layers, KV len U[128,4096]"),
+    "c3b": (64, 20, 5, 128, 30, 128, 4096,
+            "batched decode, whole attention block on the device (ternary q/k/v projections, RoPE, "
+            "attention, sub-norm, ternary o_proj; hidden 2560), BitNet-2B shape: 64 streams/GPU x 30 "
+            "layers, KV len U[128,4096]"),
     "c1": (1, 20, 5, 128, 1, 1024, 1024,
            "single-stream decode, BitNet-2B shape: 1 stream, 1 layer, KV len 1024"),
     "c5": (32, 32, 8, 128, 32, 2048, 8192,
@@ -518,9 +522,11 @@ def run_gpu_arm(args):
     # here bracket the library's launches
     tstream = torch.cuda.Stream(device=local_rank)
     torch.cuda.set_stream(tstream)
+    whole_block = args.workload.endswith("b")   # x in, y out: projections on the device too
+    rope = xn.rope_tables(500000.0, D, int(hi) + 1) if whole_block else None
     ctx = xn.Context(num_layers=layers, num_heads=Hq, num_kv_heads=Hkv, head_dim=D,
                      pool_pages=pages_needed + 8, device=local_rank,
-                     shuffle_seed=BASE_SEED + rank, cuda_stream=tstream.cuda_stream)
+                     shuffle_seed=BASE_SEED + rank, cuda_stream=tstream.cuda_stream, rope=rope)
     streams = [ctx.new_stream(int(hi)) for _ in range(n_streams)]
     for i, st in enumerate(streams):
         if lens[i] > 1:
@@ -540,7 +546,7 @@ def run_gpu_arm(args):
 
     # the "o" workloads run the layer's output block behind the attention, on the device: out is
     # then [streams, hidden] per layer (hidden = Hq*D, as in the 2B model's square o_proj)
-    out_block = args.workload.endswith("o")
+    out_block = args.workload.endswith("o") or whole_block
     extra_flags = 0
     if out_block:
         rng = np.random.default_rng(BASE_SEED + 4000 + rank)
@@ -551,13 +557,30 @@ def run_gpu_arm(args):
         for l in range(layers):   # same synthetic weights on every layer; each layer has its own copy
             ctx.set_out_proj(l, lin, norm_w, 1e-5)
         extra_flags = xn.REQ_OUT_PROJ
+    if whole_block:
+        # q/k/v projections with a global weight scale that keeps the projected rows O(1)
+        qkv_lin = [xn.TernaryLinear(hidden, rows, rng.integers(-1, 2, (rows, hidden)).astype(np.float32),
+                                    xn.PACK4, provided_scale=float(hidden) ** -0.5)
+                   for rows in (Hq * D, Hkv * D, Hkv * D)]
+        for l in range(layers):
+            ctx.set_qkv_proj(l, *qkv_lin)
+        extra_flags |= xn.REQ_QKV_PROJ
+        # x replaces q (one hidden-state row per stream and layer); k and v are not passed
+        x_h = torch.randn(layers, n_streams, hidden, generator=gen).pin_memory()
+        x_d = x_h.cuda(non_blocking=True)
+        torch.cuda.synchronize()
 
     def batches(q, k, v, o, flags):
         out = []
         for l in range(layers):
-            out.append(ctx.make_batch(
-                [(streams[i], l, int(lens[i]) - 1, 1, q[l, i].data_ptr(), k[l, i].data_ptr(),
-                  v[l, i].data_ptr(), o[l, i].data_ptr()) for i in range(n_streams)], flags))
+            if whole_block:
+                x = x_d if (flags & xn.REQ_DEVICE_PTRS) else x_h
+                entries = [(streams[i], l, int(lens[i]) - 1, 1, x[l, i].data_ptr(), None, None,
+                            o[l, i].data_ptr()) for i in range(n_streams)]
+            else:
+                entries = [(streams[i], l, int(lens[i]) - 1, 1, q[l, i].data_ptr(), k[l, i].data_ptr(),
+                            v[l, i].data_ptr(), o[l, i].data_ptr()) for i in range(n_streams)]
+            out.append(ctx.make_batch(entries, flags))
         return out
 
     dev_batches = batches(q_d, k_d, v_d, o_d, xn.REQ_DEVICE_PTRS | extra_flags)
@@ -603,7 +626,7 @@ def run_gpu_arm(args):
     barrier()
     wall1 = time.time()
     ms = ev0.elapsed_time(ev1)
-    (kern_ms, kern_n), _, (ob_ms, ob_n) = ctx.profile_read_all()
+    (kern_ms, kern_n), _, (ob_ms, ob_n), (qb_ms, qb_n) = ctx.profile_read_all()
     ctx.profile_enable(False)
     s1 = ctx.stats()
     clocks = sampler.stop(wall0, wall1) if sampler else None
@@ -670,7 +693,7 @@ def run_gpu_arm(args):
                              (bytes_per_step / 1e9)},
             "tokens_per_s": n_streams * world * args.steps / (ms * 1e-3),
             "e2e": {"value": e2e_value, "unit": "GB/s",
-                    "h2d_bytes_per_step": layers * (q_elems + 2 * kv_elems) * 4,
+                    "h2d_bytes_per_step": layers * (n_streams * Hq * D if whole_block else q_elems + 2 * kv_elems) * 4,
                     "d2h_bytes_per_step": layers * q_elems * 4,
                     "ms_per_step": e2e_ms / max(e2e_steps, 1),
                     "tokens_per_s": n_streams * world * e2e_steps / (e2e_ms * 1e-3),
@@ -688,6 +711,11 @@ def run_gpu_arm(args):
             "clocks": clocks,
             "host_and_device_paths_agree": same,
         }
+        if whole_block:
+            line["qkv_block"] = {
+                "kernels": "subnorm_quant_kernel (quantiser only) + ternary_gemm_tc_kernel, one pair per layer",
+                "avg_pair_ms": qb_ms / max(qb_n, 1), "pairs_timed": int(qb_n),
+                "rows_per_pair": n_streams, "in_dim": Hq * D, "out_dim": (Hq + 2 * Hkv) * D}
         if out_block:
             line["out_block"] = {
                 "kernels": "subnorm_quant_kernel + ternary_gemm_kernel (dp4a), one pair per layer",
@@ -696,7 +724,7 @@ def run_gpu_arm(args):
                 "weight_bytes_per_layer": Hq * D * (Hq * D // 4)}
 
     # ---- CPU baseline on a bounded sample (rank 0, N=1 only) -------------------------------------
-    if rank == 0 and world == 1 and not args.no_cpu and e2e_steps > 0:
+    if rank == 0 and world == 1 and not args.no_cpu and e2e_steps > 0 and not whole_block:
         sample = min(args.cpu_streams, n_streams)
         layer = layers // 2
         kv = []
@@ -729,6 +757,30 @@ def run_gpu_arm(args):
         line["parity_vs_cpu_sample"] = {"max_abs": max_abs, "rel_l2": rel, "tolerance": tol}
     elif rank == 0:
         line["cpu_baseline"] = None
+    if rank == 0 and world == 1 and whole_block and e2e_steps > 0 and not args.no_cpu:
+        # the checker runs the whole block on a few streams (not timed): oracle chain vs device chain
+        import oracle as xo
+        xo.set_quant_body(1)
+        layer, hidden = layers // 2, Hq * D
+        mk = lambda l_, rows: xo.TernaryLinear(hidden, rows, xo.unpack_ternary(l_.packed, rows * hidden), xo.PACK4,
+                                               provided_scale=float(l_.w_scales[0]))
+        ref_q, ref_k, ref_v = (mk(l_, rows) for l_, rows in zip(qkv_lin, (Hq * D, Hkv * D, Hkv * D)))
+        ref_o = mk(lin, hidden)
+        worst = 0.0
+        for i in range(min(4, n_streams)):
+            L = int(lens[i])
+            cache = xo.RingCache(1, Hkv, L, D)
+            if L > 1:
+                kk, vv = streams[i].read_range(layer, 0, L - 1)
+                cache.append(0, 0, kk, vv)
+            y_ref, _ = xo.causal_self_attention_forward(
+                x_h[layer, i].numpy().reshape(1, 1, hidden), L - 1, 0, cache, rope[0], rope[1], ref_q, ref_k, ref_v,
+                Hq, Hkv, D, norm_w, 1e-5, ref_o)
+            got = o_h[layer, i].numpy().reshape(1, 1, hidden)
+            worst = max(worst, float(np.linalg.norm(got - y_ref) / np.linalg.norm(y_ref)))
+        line["parity_vs_cpu_sample"] = {"rel_l2": worst, "streams": min(4, n_streams), "layer": layer,
+                                        "tolerance": "rel_l2<=1e-3 (whole block; an activation may quantise one "
+                                                     "step apart where the attention rows differ in the last bits)"}
 
     ctx.close()
     if rank == 0 and not args.no_prefill:

@@ -97,10 +97,15 @@ enum {
                                   /* library's staging copies are skipped.  The call still       */
                                   /* blocks until the output is complete.  All requests of a     */
                                   /* batch must agree on this flag.                              */
-    XN_REQ_OUT_PROJ = 1u << 4     /* `out` receives [seq_len, out_dim]: the attention output run */
+    XN_REQ_OUT_PROJ = 1u << 4,    /* `out` receives [seq_len, out_dim]: the attention output run */
                                   /* through the layer's output block (xn_out_proj_set) on the   */
                                   /* device, i.e. what models/llama/attention.rs:103-108 does    */
                                   /* after fast_attention returns                                */
+    XN_REQ_QKV_PROJ = 1u << 5     /* `q` points at the hidden states x [seq_len, hidden] that    */
+                                  /* CausalSelfAttention::forward receives; k and v are ignored. */
+                                  /* The layer's q/k/v projections (xn_qkv_proj_set), the heads  */
+                                  /* layout and the rotation run on the device                   */
+                                  /* (models/llama/attention.rs:52-89); needs RoPE tables        */
 };
 
 typedef struct xn_req {
@@ -153,8 +158,9 @@ XN_API const char* xn_last_error(xn_ctx* ctx);
  * pointer may be NULL. */
 XN_API int32_t xn_profile_enable(xn_ctx* ctx, int32_t on);
 /* The same for every timed kind: ms and launches are arrays of XN_PROFILE_KINDS entries
- * (0 split-KV attention, 1 tensor-core prefill, 2 output block = sub-norm + projection pair). */
-#define XN_PROFILE_KINDS 3
+ * (0 split-KV attention, 1 tensor-core prefill, 2 output block = sub-norm + projection pair,
+ * 3 q/k/v block = quantiser + projection pair). */
+#define XN_PROFILE_KINDS 4
 XN_API int32_t xn_profile_read_all(xn_ctx* ctx, double* ms, uint64_t* launches);
 XN_API int32_t xn_profile_read(xn_ctx* ctx, double* splitkv_ms, uint64_t* splitkv_launches,
                                double* prefill_ms, uint64_t* prefill_launches);
@@ -274,6 +280,29 @@ typedef struct xn_out_proj_desc {
     float norm_eps;
     uint32_t reserved;
 } xn_out_proj_desc;
+
+/* The q_proj / k_proj / v_proj TernaryLinears of one layer (src/models/llama/attention.rs:34-36),
+ * dense representation, all with in_dim = hidden size; out dims are num_heads * head_dim for q and
+ * num_kv_heads * head_dim for k and v. */
+typedef struct xn_qkv_proj_desc {
+    int32_t layer;
+    int32_t in_dim;
+    int32_t pack_type;        /* XN_PACK4 or XN_PACK5, the same for the three                     */
+    int32_t reserved;
+    const uint8_t* q_packed;
+    const float* q_scales;
+    const uint8_t* k_packed;
+    const float* k_scales;
+    const uint8_t* v_packed;
+    const float* v_scales;
+} xn_qkv_proj_desc;
+
+/* Uploads (or replaces) the q/k/v projections of one layer.  Requests of that layer may then
+ * carry XN_REQ_QKV_PROJ: the rows of x are quantised to i8 once (quantize_f32_to_i8,
+ * src/bit1_58/quantization.rs:95-187, AVX-512 body) and projected by all three
+ * (TernaryLinear::forward / fused_forward_qkv, src/bit1_58/layers.rs:262-424); given the same x
+ * the projected q, k, v equal the reference's bit for bit, and so do the cached K and V. */
+XN_API int32_t xn_qkv_proj_set(xn_ctx* ctx, const xn_qkv_proj_desc* desc);
 
 /* Uploads (or replaces) the output block of one layer.  Requests of that layer may then carry
  * XN_REQ_OUT_PROJ. */

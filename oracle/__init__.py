@@ -379,6 +379,25 @@ def attention_out_block(y, norm_weight, eps, o_proj: TernaryLinear, threads: int
     return out
 
 
+def causal_self_attention_forward(x, index_pos, layer_idx, cache: "RingCache", cos, sin,
+                                  q_proj: TernaryLinear, k_proj: TernaryLinear, v_proj: TernaryLinear,
+                                  num_heads, num_kv_heads, head_dim, sub_norm_weight, eps,
+                                  o_proj: TernaryLinear, threads: int = 0):
+    """CausalSelfAttention::forward (models/llama/attention.rs:40-108) for ternary projections:
+    x [1,S,hidden] -> q/k/v projections (each quantises the rows of x the same way, as the fused
+    single-token path of bit1_58/layers.rs:347-424 does once) -> heads layout -> RoPE ->
+    fast_attention -> heads_to_seq -> optional sub-norm -> o_proj.  Returns (y [1,S,out], attention
+    output [1,Hq,S,D])."""
+    x = _f32(x)
+    q = transpose_seq_to_heads(q_proj.forward(x, threads), num_heads, head_dim)
+    k = transpose_seq_to_heads(k_proj.forward(x, threads), num_kv_heads, head_dim)
+    v = transpose_seq_to_heads(v_proj.forward(x, threads), num_kv_heads, head_dim)
+    q = tensor_rope(q, cos, sin, index_pos)
+    k = tensor_rope(k, cos, sin, index_pos)
+    attn = fast_attention(q, k, v, layer_idx, index_pos, cache, num_heads, num_kv_heads, head_dim, threads)
+    return attention_out_block(attn, sub_norm_weight, eps, o_proj, threads), attn
+
+
 # --- independent f64 arbiter -------------------------------------------------------------------
 
 def naive_attention_f64(q, k_all, v_all, index_pos, num_heads, num_kv_heads, head_dim):

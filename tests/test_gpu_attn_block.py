@@ -1,0 +1,166 @@
+"""The whole attention block on the device -- q/k/v projections, heads layout, RoPE, append,
+attention, sub-norm, o_proj -- against the CPU oracle's CausalSelfAttention::forward
+(models/llama/attention.rs:40-108), through the C ABI.
+
+Bars: the projections are integer work, so what they write is BIT-EXACT: the cached K and V rows
+(k_proj / v_proj of x, K rotated) equal the oracle's cache bit for bit, and a single-token call at
+position 0 (one key: the softmax weight is exactly 1) returns v_proj(x) exactly.  The attention
+output keeps the f32 tolerances (max abs <= 1e-4, rel L2 <= 1e-5; <= 5e-3 rel for the TF32 prefill
+kernel); behind o_proj the chain is checked bit-exactly against the oracle block applied to the
+device's own attention output and with rel L2 <= 1e-3 against the all-oracle chain.
+"""
+import numpy as np
+import pytest
+
+import oracle as xo
+import xor_net_b200 as xn
+from gpu_util import assert_parity, errs
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(autouse=True)
+def avx512_quantiser():
+    xo.set_quant_body(1)
+    yield
+    xo.set_quant_body(-1)
+
+
+class Block:
+    """One layer's weights on the device and in the oracle, plus a paired stream / ring cache."""
+
+    def __init__(self, rng, Hq, Hkv, D, hidden, out_dim, pack, layers=2, layer=1, prefill_mode=1,
+                 theta=10000.0, max_pos=2048, cap=1024, pool_pages=40):
+        self.Hq, self.Hkv, self.D, self.hidden, self.layer = Hq, Hkv, D, hidden, layer
+        self.cos, self.sin = xn.rope_tables(theta, D, max_pos)
+        self.ctx = xn.Context(layers, Hq, Hkv, D, pool_pages=pool_pages, rope=(self.cos, self.sin),
+                              prefill_mode=prefill_mode, shuffle_seed=7)
+        mk = lambda o, i: rng.standard_normal((o, i)).astype(np.float32)
+        ws = {"q": mk(Hq * D, hidden), "k": mk(Hkv * D, hidden), "v": mk(Hkv * D, hidden),
+              "o": mk(out_dim, Hq * D)}
+        # q, k, v get a global weight scale that keeps the projected rows O(1) (about hidden**-0.5), so
+        # that the softmax is not saturated and the f32 attention tolerances keep their meaning;
+        # o_proj uses the per-row abs-mean scale
+        scale = {n: (float(hidden) ** -0.5 if n != "o" else None) for n in ws}
+        self.dev = {n: xn.TernaryLinear(w.shape[1], w.shape[0], w, pack, scale[n]) for n, w in ws.items()}
+        self.ref = {n: xo.TernaryLinear(w.shape[1], w.shape[0], w, pack, scale[n]) for n, w in ws.items()}
+        self.nw = (1.0 + 0.2 * rng.standard_normal(Hq * D)).astype(np.float32)
+        self.eps = 1e-5
+        self.ctx.set_qkv_proj(layer, self.dev["q"], self.dev["k"], self.dev["v"])
+        self.ctx.set_out_proj(layer, self.dev["o"], self.nw, self.eps)
+        self.cap = cap
+
+    def pair(self):
+        return self.ctx.new_stream(self.cap), xo.RingCache(self.ctx.num_layers, self.Hkv, self.cap, self.D)
+
+    def oracle(self, x, pos, cache):
+        return xo.causal_self_attention_forward(x, pos, self.layer, cache, self.cos, self.sin, self.ref["q"],
+                                                self.ref["k"], self.ref["v"], self.Hq, self.Hkv, self.D,
+                                                self.nw, self.eps, self.ref["o"])
+
+    def check_cache(self, st, cache):
+        k, v = st.read_range(self.layer, 0, self.cap)
+        assert np.array_equal(k.ravel(), cache.k_buffer(self.layer)), "cached K differs"
+        assert np.array_equal(v.ravel(), cache.v_buffer(self.layer)), "cached V differs"
+
+
+@pytest.mark.parametrize("pack", [xn.PACK4, xn.PACK5])
+def test_block_prefill_then_batched_decode(pack):
+    rng = np.random.default_rng(100 + pack)
+    b = Block(rng, 20, 5, 128, 2560, 2560, pack)
+    lens = [1, 70, 300]
+    pairs = [b.pair() for _ in lens]
+    worst = 0.0
+    for (st, cache), L in zip(pairs, lens):
+        x = rng.standard_normal((1, L, b.hidden)).astype(np.float32)
+        attn_dev = b.ctx.attention_batch([st], b.layer, [0], [x], qkv_proj=True)[0]               # [1,L,Hq*D]
+        y_dev = b.ctx.attention_batch([st], b.layer, [0], [x], qkv_proj=True, out_proj=True)[0]   # same position again
+        y_ref, attn_ref = b.oracle(x, 0, cache)
+        b.check_cache(st, cache)                                   # k_proj, v_proj, RoPE: bit-exact
+        assert_parity(attn_dev, xo.transpose_heads_to_seq(attn_ref), f"attention, prefill L={L}")
+        if L == 1:
+            assert np.array_equal(attn_dev, xo.transpose_heads_to_seq(attn_ref))   # = v_proj(x), exactly
+            assert np.array_equal(y_dev, y_ref)
+        # o_proj block: exact on the device's own attention rows, close to the all-oracle chain
+        heads = xo.transpose_seq_to_heads(attn_dev, b.Hq, b.D)
+        assert np.array_equal(y_dev, xo.attention_out_block(heads, b.nw, b.eps, b.ref["o"])), f"block L={L}"
+        worst = max(worst, errs(y_dev, y_ref)[1])
+    # one decode step for every stream in one batch (the attention kernel appends and rotates itself)
+    xs = [rng.standard_normal((1, 1, b.hidden)).astype(np.float32) for _ in lens]
+    sts = [p[0] for p in pairs]
+    attn_dev = b.ctx.attention_batch(sts, b.layer, lens, xs, qkv_proj=True)
+    y_dev = b.ctx.attention_batch(sts, b.layer, lens, xs, qkv_proj=True, out_proj=True)
+    assert b.ctx.stats()["decode_launches"] >= 2
+    for i, (st, cache) in enumerate(pairs):
+        y_ref, attn_ref = b.oracle(xs[i], lens[i], cache)
+        b.check_cache(st, cache)
+        assert_parity(attn_dev[i], xo.transpose_heads_to_seq(attn_ref), f"attention, decode {i}")
+        heads = xo.transpose_seq_to_heads(attn_dev[i], b.Hq, b.D)
+        assert np.array_equal(y_dev[i], xo.attention_out_block(heads, b.nw, b.eps, b.ref["o"]))
+        worst = max(worst, errs(y_dev[i], y_ref)[1])
+    print(f"device block vs all-oracle block: worst rel {worst:.2e}")
+    assert worst <= 1e-3
+    b.ctx.close()
+
+
+def test_block_with_tensor_core_prefill_and_other_shape():
+    # TF32 prefill kernel behind the projections; hidden size different from heads * head_dim
+    rng = np.random.default_rng(7)
+    b = Block(rng, 8, 2, 64, 384, 96, xn.PACK4, prefill_mode=2, cap=512, pool_pages=16)
+    st, cache = b.pair()
+    S = 200
+    x = rng.standard_normal((1, S, b.hidden)).astype(np.float32)
+    attn_dev = b.ctx.attention_batch([st], b.layer, [0], [x], qkv_proj=True)[0]
+    assert b.ctx.stats()["prefill_launches"] == 1
+    _, attn_ref = b.oracle(x, 0, cache)
+    b.check_cache(st, cache)                                       # the cache is exact even when the math is TF32
+    assert errs(attn_dev, xo.transpose_heads_to_seq(attn_ref))[1] <= 5e-3
+    x1 = rng.standard_normal((1, 1, b.hidden)).astype(np.float32)  # a decode step behind it: exact-f32 path
+    attn_dev = b.ctx.attention_batch([st], b.layer, [S], [x1], qkv_proj=True)[0]
+    _, attn_ref = b.oracle(x1, S, cache)
+    b.check_cache(st, cache)
+    assert_parity(attn_dev, xo.transpose_heads_to_seq(attn_ref), "decode step after the prefill")
+    b.ctx.close()
+
+
+def test_block_with_pinned_host_tensors():
+    import torch
+
+    rng = np.random.default_rng(8)
+    b = Block(rng, 20, 5, 128, 2560, 2560, xn.PACK4)
+    lens = [33, 1, 64]
+    pairs = [b.pair() for _ in lens]
+    for (st, cache), L in zip(pairs, lens):
+        x = rng.standard_normal((1, L, b.hidden)).astype(np.float32)
+        b.ctx.attention_batch([st], b.layer, [0], [x], qkv_proj=True)
+        b.oracle(x, 0, cache)
+    n = len(lens)
+    x = torch.from_numpy(rng.standard_normal((n, b.hidden)).astype(np.float32)).pin_memory()
+    y = torch.zeros(n, 2560).pin_memory()
+    reqs = b.ctx.make_batch([(pairs[i][0], b.layer, lens[i], 1, x[i].data_ptr(), None, None, y[i].data_ptr())
+                             for i in range(n)], xn.REQ_HOST_PINNED | xn.REQ_QKV_PROJ | xn.REQ_OUT_PROJ)
+    b.ctx.submit(reqs)
+    for i, (st, cache) in enumerate(pairs):
+        y_ref, _ = b.oracle(x[i].numpy().reshape(1, 1, b.hidden), lens[i], cache)
+        b.check_cache(st, cache)
+        assert errs(y[i].numpy().reshape(1, 1, 2560), y_ref)[1] <= 1e-3
+    b.ctx.close()
+
+
+def test_errors():
+    rng = np.random.default_rng(9)
+    ctx = xn.Context(1, 2, 1, 16, pool_pages=2)                   # no RoPE tables
+    lin = lambda o, i: xn.TernaryLinear(i, o, rng.standard_normal((o, i)).astype(np.float32))
+    st = ctx.new_stream(64)
+    x = rng.standard_normal((1, 1, 24)).astype(np.float32)
+    with pytest.raises(xn.XnError) as e:                           # projections not set
+        ctx.attention_batch([st], 0, [0], [x], qkv_proj=True)
+    assert e.value.code == 1
+    ctx.set_qkv_proj(0, lin(32, 24), lin(16, 24), lin(16, 24))
+    with pytest.raises(xn.XnError) as e:                           # the rotation needs tables
+        ctx.attention_batch([st], 0, [0], [x], qkv_proj=True)
+    assert e.value.code == 8
+    with pytest.raises(ValueError):
+        ctx.set_qkv_proj(0, lin(32, 24), lin(16, 20), lin(16, 24))
+    assert st.length(0) == 0
+    ctx.close()

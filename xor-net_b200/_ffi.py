@@ -36,13 +36,20 @@ class Stats(C.Structure):
         "coalesced_max", "out_proj_rows")]
 
 
+class QkvProjDesc(C.Structure):
+    _fields_ = [("layer", C.c_int32), ("in_dim", C.c_int32), ("pack_type", C.c_int32),
+                ("reserved", C.c_int32), ("q_packed", C.c_void_p), ("q_scales", C.c_void_p),
+                ("k_packed", C.c_void_p), ("k_scales", C.c_void_p), ("v_packed", C.c_void_p),
+                ("v_scales", C.c_void_p)]
+
+
 class OutProjDesc(C.Structure):
     _fields_ = [("layer", C.c_int32), ("in_dim", C.c_int32), ("out_dim", C.c_int32),
                 ("pack_type", C.c_int32), ("packed", C.c_void_p), ("w_scales", C.c_void_p),
                 ("norm_weight", C.c_void_p), ("norm_eps", C.c_float), ("reserved", C.c_uint32)]
 
 
-REQ_DEVICE_PTRS, REQ_ROPE, REQ_SEQ_MAJOR, REQ_HOST_PINNED, REQ_OUT_PROJ = 1, 2, 4, 8, 16
+REQ_DEVICE_PTRS, REQ_ROPE, REQ_SEQ_MAJOR, REQ_HOST_PINNED, REQ_OUT_PROJ, REQ_QKV_PROJ = 1, 2, 4, 8, 16, 32
 PACK4, PACK5 = 4, 5
 
 STATUS_NAMES = {
@@ -88,6 +95,7 @@ SIGNATURES = {
                                   c_i32p, c_i32p, c_i32p, c_i32p, c_i32p, c_i32p]),
     "xn_debug_expire_wait": (C.c_int32, [C.c_void_p, C.c_int32]),
     "xn_profile_read_all": (C.c_int32, [C.c_void_p, C.POINTER(C.c_double), C.POINTER(C.c_uint64)]),
+    "xn_qkv_proj_set": (C.c_int32, [C.c_void_p, C.POINTER(QkvProjDesc)]),
     "xn_out_proj_set": (C.c_int32, [C.c_void_p, C.POINTER(OutProjDesc)]),
     "xn_out_proj": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_uint32]),
     "xn_ternary_pack": (C.c_int32, [C.c_int32, C.c_int32, C.c_void_p, C.c_int32, C.c_float,

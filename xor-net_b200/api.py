@@ -21,8 +21,8 @@ from typing import Optional, Sequence
 import numpy as np
 
 from . import _ffi
-from ._ffi import (PACK4, PACK5, REQ_DEVICE_PTRS, REQ_HOST_PINNED, REQ_OUT_PROJ, REQ_ROPE, REQ_SEQ_MAJOR,
-                   CtxDesc, OutProjDesc, Req, Stats)
+from ._ffi import (PACK4, PACK5, REQ_DEVICE_PTRS, REQ_HOST_PINNED, REQ_OUT_PROJ, REQ_QKV_PROJ, REQ_ROPE,
+                   REQ_SEQ_MAJOR, CtxDesc, OutProjDesc, QkvProjDesc, Req, Stats)
 
 
 class XnError(RuntimeError):
@@ -178,10 +178,11 @@ class Context:
         return (pms.value, int(pn.value)) if which == "prefill" else (ms.value, int(n.value))
 
     def profile_read_all(self):
-        """[(milliseconds, launches)] per timed kind: split-KV, tensor-core prefill, output block."""
-        ms, n = (C.c_double * 3)(), (C.c_uint64 * 3)()
+        """[(milliseconds, launches)] per timed kind: split-KV, tensor-core prefill, output block,
+        q/k/v block."""
+        ms, n = (C.c_double * 4)(), (C.c_uint64 * 4)()
         self._check(self.lib.xn_profile_read_all(self.handle, ms, n))
-        return [(ms[i], int(n[i])) for i in range(3)]
+        return [(ms[i], int(n[i])) for i in range(4)]
 
     # -- attention output block (sub-norm + ternary o_proj) ------------------------------------
 
@@ -195,6 +196,19 @@ class Context:
         self._check(self.lib.xn_out_proj_set(self.handle, C.byref(d)))
         self._out_dims = getattr(self, "_out_dims", {})
         self._out_dims[layer] = linear.out_dim
+
+    def set_qkv_proj(self, layer: int, q_proj: "TernaryLinear", k_proj: "TernaryLinear",
+                     v_proj: "TernaryLinear"):
+        """xn_qkv_proj_set: the three input projections of one layer (same in_dim and packing)."""
+        if not (q_proj.in_dim == k_proj.in_dim == v_proj.in_dim and
+                q_proj.pack_type == k_proj.pack_type == v_proj.pack_type):
+            raise ValueError("q, k, v projections must share in_dim and pack_type")
+        d = QkvProjDesc()
+        d.layer, d.in_dim, d.pack_type = layer, q_proj.in_dim, q_proj.pack_type
+        d.q_packed, d.q_scales = q_proj.packed.ctypes.data, _ptr(q_proj.w_scales)
+        d.k_packed, d.k_scales = k_proj.packed.ctypes.data, _ptr(k_proj.w_scales)
+        d.v_packed, d.v_scales = v_proj.packed.ctypes.data, _ptr(v_proj.w_scales)
+        self._check(self.lib.xn_qkv_proj_set(self.handle, C.byref(d)))
 
     def out_proj(self, layer: int, y) -> np.ndarray:
         """xn_out_proj on host arrays: y [..., in_dim] -> [..., out_dim]."""
@@ -230,24 +244,31 @@ class Context:
     def submit(self, reqs, n: Optional[int] = None):
         self._check(self.lib.xn_attention_batch(self.handle, len(reqs) if n is None else n, reqs))
 
-    def attention_batch(self, streams, layer, index_pos, qs, ks, vs, rope=False, seq_major=False,
-                        out_proj=False):
+    def attention_batch(self, streams, layer, index_pos, qs, ks=None, vs=None, rope=False,
+                        seq_major=False, out_proj=False, qkv_proj=False):
         """Host-array batch: one request per stream; returns the list of outputs
-        ([1,S,out_dim] each with ``out_proj``: the layer's output block applied on the device)."""
+        ([1,S,out_dim] each with ``out_proj``: the layer's output block applied on the device).
+        With ``qkv_proj`` the entries of ``qs`` are the hidden states x [1,S,hidden] and the layer's
+        q/k/v projections, the heads layout and the rotation run on the device; the attention output
+        then comes back sequence-major, [1,S,Hq*D]."""
         qs = [_f32(a) for a in qs]
-        ks = [_f32(a) for a in ks]
-        vs = [_f32(a) for a in vs]
+        ks = [_f32(a) for a in ks] if not qkv_proj else [None] * len(qs)
+        vs = [_f32(a) for a in vs] if not qkv_proj else [None] * len(qs)
         seq = [a.shape[-2] for a in qs]  # [1,H,S,D] and [1,S,H*D] both keep S there
         layers = layer if isinstance(layer, (list, tuple)) else [layer] * len(streams)
         if out_proj:
             outs = [np.empty((1, seq[i], self._out_dims[layers[i]]), dtype=np.float32)
                     for i in range(len(qs))]
+        elif qkv_proj:
+            outs = [np.empty((1, seq[i], self.num_heads * self.head_dim), dtype=np.float32)
+                    for i in range(len(qs))]
         else:
             outs = [np.empty_like(a) for a in qs]
         flags = (REQ_ROPE if rope else 0) | (REQ_SEQ_MAJOR if seq_major else 0) | \
-            (REQ_OUT_PROJ if out_proj else 0)
+            (REQ_OUT_PROJ if out_proj else 0) | (REQ_QKV_PROJ if qkv_proj else 0)
         reqs = self.make_batch(
-            [(st, layers[i], int(index_pos[i]), int(seq[i]), _ptr(qs[i]), _ptr(ks[i]), _ptr(vs[i]),
+            [(st, layers[i], int(index_pos[i]), int(seq[i]), _ptr(qs[i]),
+              _ptr(ks[i]) if ks[i] is not None else None, _ptr(vs[i]) if vs[i] is not None else None,
               _ptr(outs[i])) for i, st in enumerate(streams)], flags)
         self.submit(reqs)
         return outs

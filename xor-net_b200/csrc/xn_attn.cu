@@ -120,6 +120,8 @@ struct xn_ctx {
     float* partials = nullptr; size_t partials_cap = 0;   // floats
     // attention output block (sub-norm + ternary o_proj)
     std::vector<OutProj> out_proj;                         // per layer
+    std::vector<OutProj> qkv_proj;                         // per layer: q, k, v rows stacked, no norm
+    float* qkv_seq = nullptr; size_t qkv_seq_cap = 0;      // floats: projected [row][q | k | v]
     float* attn_seq = nullptr; size_t attn_seq_cap = 0;    // floats: sequence-major attention rows
     float* q8 = nullptr; size_t q8_cap = 0;                // floats: i8 activation rows + inverse scales
     unsigned char* io_host = nullptr; unsigned char* io_dev = nullptr; size_t io_cap = 0;
@@ -138,7 +140,7 @@ struct xn_ctx {
     // optional device timing of the split-KV kernel
     bool profile = false;
     std::vector<cudaEvent_t> prof_events;  // pairs (start, stop), reused
-    std::vector<int> prof_kind;            // per pair: 0 split-KV, 1 prefill, 2 output block
+    std::vector<int> prof_kind;            // per pair: 0 split-KV, 1 prefill, 2 output block, 3 q/k/v block
     size_t prof_used = 0;
 
     // combining of concurrent blocking callers
@@ -366,18 +368,14 @@ int32_t profile_end(xn_ctx* c) {
 
 // Floats of the quantised-activation buffer for `rows_pad` rows (a multiple of 256): the tiled i8
 // rows, then one inverse scale per row.
-size_t q8_floats(const xn_ctx* c, size_t rows_pad) {
-    const size_t q_stride = align_up(size_t(c->num_heads) * c->head_dim, 128);
-    return rows_pad * q_stride / 4 + rows_pad + 4;
-}
+size_t q8_floats(size_t q_stride, size_t rows_pad) { return rows_pad * q_stride / 4 + rows_pad + 4; }
 
 // Sub-norm, quantiser and ternary projection of `n_rows` token rows; rows_d[i] names the source
 // row (in_dim floats) and the destination row (out_dim floats) of row i.  The rows occupy rows
 // [q_row0, q_row0 + n_rows) of the context's quantised-activation buffer, which holds q_rows_pad
 // rows (both multiples of 256).
-int32_t launch_out_block(xn_ctx* c, int layer, const OutRowDev* rows_d, int n_rows, size_t q_row0,
+int32_t launch_out_block(xn_ctx* c, const OutProj& op, const OutRowDev* rows_d, int n_rows, size_t q_row0,
                          size_t q_rows_pad) {
-    const OutProj& op = c->out_proj[size_t(layer)];
     int8_t* q = reinterpret_cast<int8_t*>(c->q8);
     float* inv = c->q8 + q_rows_pad * size_t(op.q_stride) / 4;
     {
@@ -444,10 +442,14 @@ int32_t validate_req(xn_ctx* c, const xn_req& r) {
     if (r.layer < 0 || r.layer >= c->num_layers)
         return fail(c, XN_ERR_ARG, "layer %d outside 0..%d", r.layer, c->num_layers - 1);
     if (r.seq_len < 0 || r.index_pos < 0) return fail(c, XN_ERR_ARG, "negative seq_len or index_pos");
-    if (r.seq_len > 0 && (!r.q || !r.k || !r.v || !r.out)) return fail(c, XN_ERR_ARG, "null tensor pointer");
+    const bool qkv = r.flags & XN_REQ_QKV_PROJ;   // k and v are produced by the library then
+    if (r.seq_len > 0 && (!r.q || !r.out || (!qkv && (!r.k || !r.v))))
+        return fail(c, XN_ERR_ARG, "null tensor pointer");
     if (r.index_pos + r.seq_len > (int64_t(1) << 30))
         return fail(c, XN_ERR_CAPACITY, "position %lld too large", (long long)(r.index_pos + r.seq_len));
-    if (r.flags & XN_REQ_ROPE) {
+    if (qkv && !c->qkv_proj[size_t(r.layer)].set)
+        return fail(c, XN_ERR_ARG, "XN_REQ_QKV_PROJ: layer %d has no q/k/v projections (xn_qkv_proj_set)", r.layer);
+    if ((r.flags & XN_REQ_ROPE) || qkv) {
         if (!c->cos_d) return fail(c, XN_ERR_NO_TABLES, "context was created without RoPE tables");
         if (r.index_pos + r.seq_len > c->max_pos)
             return fail(c, XN_ERR_CAPACITY, "position %lld beyond the RoPE table (%d rows)",
@@ -468,7 +470,7 @@ bool use_tf32(const xn_ctx* c, const xn_req& r, bool direct) {
     if (direct) {
         // with XN_REQ_OUT_PROJ the kernel writes into the library's own (aligned) row buffer
         uintptr_t bits = (r.flags & XN_REQ_OUT_PROJ) ? 0 : reinterpret_cast<uintptr_t>(r.out);
-        const bool q_scratch = (r.flags & (XN_REQ_ROPE | XN_REQ_HOST_PINNED)) != 0;  // q read from the rotation scratch
+        const bool q_scratch = (r.flags & (XN_REQ_ROPE | XN_REQ_HOST_PINNED | XN_REQ_QKV_PROJ)) != 0;  // q read from the rotation scratch
         if (!q_scratch) bits |= reinterpret_cast<uintptr_t>(r.q);
         if (bits & 15) return false;
     }
@@ -500,7 +502,8 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
     }
     // -- pages, gaps, staging sizes
     std::vector<GapFill> gaps;
-    size_t io_in = 0, io_out = 0, qrot_floats = 0, n_page_ids = 0, out_rows = 0;
+    size_t io_in = 0, io_out = 0, qrot_floats = 0, n_page_ids = 0, out_rows = 0, qkv_rows = 0;
+    const size_t qkv_width = size_t(Hq + 2 * Hkv) * D;   // floats of one projected row [q | k | v]
     long long n_units = 0, n_ring_rows = 0;
     int max_rows = 0;
     for (int i = 0; i < n; ++i) {
@@ -519,17 +522,20 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         const bool proj = r.flags & XN_REQ_OUT_PROJ;
         const size_t of = proj ? size_t(r.seq_len) * c->out_proj[size_t(r.layer)].out_dim : qf;  // floats returned
         if (proj) out_rows += size_t(r.seq_len);
+        const bool qkv = r.flags & XN_REQ_QKV_PROJ;
+        const size_t xf = qkv ? size_t(r.seq_len) * c->qkv_proj[size_t(r.layer)].in_dim : 0;  // floats of x
+        if (qkv) qkv_rows += size_t(r.seq_len);
         if (host_mode && !pinned) {
-            io_in += align_up(qf * 4, 16) + 2 * align_up(kvf * 4, 16);
+            io_in += qkv ? align_up(xf * 4, 16) : align_up(qf * 4, 16) + 2 * align_up(kvf * 4, 16);
             io_out += align_up(of * 4, 16);
         }
-        if ((r.flags & XN_REQ_ROPE) || pinned) qrot_floats += align_up(qf, 4);
+        if ((r.flags & XN_REQ_ROPE) || pinned || qkv) qrot_floats += align_up(qf, 4);
         if (end > s->cap) n_ring_rows += r.seq_len;
         else if (use_tf32(c, r, direct)) { /* served by the tensor-core prefill kernel */ }
         else n_units += (long long)r.seq_len * Hkv * c->subs;
         max_rows = std::max<long long>(max_rows, (long long)r.seq_len * (Hq + 2 * Hkv));
         if (pinned) {  // bytes the kernels move over PCIe themselves
-            c->stats.h2d_bytes += (qf + 2 * kvf) * 4;
+            c->stats.h2d_bytes += (qkv ? xf : qf + 2 * kvf) * 4;
             c->stats.d2h_bytes += of * 4;
         }
     }
@@ -541,9 +547,10 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
     for (int i = 0; i < n && fused; ++i) {
         const xn_req& r = reqs[i];
         if (r.seq_len != 1) { fused = false; break; }
-        if ((r.flags & XN_REQ_ROPE) && !(c->nv_exact && (c->nv == 16 || c->nv == 32))) fused = false;
+        const bool qkv = r.flags & XN_REQ_QKV_PROJ;   // q, k, v then live in the library's aligned rows
+        if (((r.flags & XN_REQ_ROPE) || qkv) && !(c->nv_exact && (c->nv == 16 || c->nv == 32))) fused = false;
         if (pinned && !c->fuse_pinned) fused = false;
-        if (!host_mode || pinned)
+        if ((!host_mode || pinned) && !qkv)
             if ((reinterpret_cast<uintptr_t>(r.q) | reinterpret_cast<uintptr_t>(r.k) |
                  reinterpret_cast<uintptr_t>(r.v)) & 15)
                 fused = false;
@@ -561,6 +568,7 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
     if (out_rows) {
         if ((rc = grow_device(c, &c->attn_seq, &c->attn_seq_cap, out_rows * size_t(Hq) * D)) != XN_OK) return rc;
     }
+    if (qkv_rows && (rc = grow_device(c, &c->qkv_seq, &c->qkv_seq_cap, qkv_rows * qkv_width)) != XN_OK) return rc;
     if (host_mode && (rc = grow_io(c, io_in + io_out)) != XN_OK) return rc;
 
     // -- request descriptors, page ids, units
@@ -576,6 +584,9 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
     std::vector<OutRowDev> out_row_tab;
     out_row_tab.reserve(out_rows);
     std::vector<OutRun> out_runs;
+    std::vector<OutRowDev> qkv_row_tab;
+    qkv_row_tab.reserve(qkv_rows);
+    std::vector<OutRun> qkv_runs;
     size_t in_off = 0, out_off = io_in, qrot_off = 0;
     for (int i = 0; i < n; ++i) {
         const xn_req& r = reqs[i];
@@ -587,37 +598,62 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         const size_t qf = size_t(Hq) * S * D, kvf = size_t(Hkv) * S * D;
         const float *q_dev = r.q, *k_dev = r.k, *v_dev = r.v;
         float* o_dev = r.out;
+        const bool qkv = r.flags & XN_REQ_QKV_PROJ;
         if (host_mode && !pinned) {
-            memcpy(c->io_host + in_off, r.q, qf * 4);
-            q_dev = reinterpret_cast<const float*>(c->io_dev + in_off);
-            in_off += align_up(qf * 4, 16);
-            memcpy(c->io_host + in_off, r.k, kvf * 4);
-            k_dev = reinterpret_cast<const float*>(c->io_dev + in_off);
-            in_off += align_up(kvf * 4, 16);
-            memcpy(c->io_host + in_off, r.v, kvf * 4);
-            v_dev = reinterpret_cast<const float*>(c->io_dev + in_off);
-            in_off += align_up(kvf * 4, 16);
+            if (qkv) {
+                const size_t xf = size_t(S) * c->qkv_proj[size_t(r.layer)].in_dim;
+                memcpy(c->io_host + in_off, r.q, xf * 4);
+                q_dev = reinterpret_cast<const float*>(c->io_dev + in_off);   // x, for now
+                in_off += align_up(xf * 4, 16);
+            } else {
+                memcpy(c->io_host + in_off, r.q, qf * 4);
+                q_dev = reinterpret_cast<const float*>(c->io_dev + in_off);
+                in_off += align_up(qf * 4, 16);
+                memcpy(c->io_host + in_off, r.k, kvf * 4);
+                k_dev = reinterpret_cast<const float*>(c->io_dev + in_off);
+                in_off += align_up(kvf * 4, 16);
+                memcpy(c->io_host + in_off, r.v, kvf * 4);
+                v_dev = reinterpret_cast<const float*>(c->io_dev + in_off);
+                in_off += align_up(kvf * 4, 16);
+            }
             o_dev = reinterpret_cast<float*>(c->io_dev + out_off);
             out_off += align_up(((r.flags & XN_REQ_OUT_PROJ)
                                      ? size_t(S) * c->out_proj[size_t(r.layer)].out_dim : qf) * 4, 16);
         }
-        const bool seq_major = r.flags & XN_REQ_SEQ_MAJOR;
-        const long long q_hs = seq_major ? D : (long long)S * D, q_ts = seq_major ? (long long)Hq * D : D;
-        const long long kv_hs = seq_major ? D : (long long)S * D, kv_ts = seq_major ? (long long)Hkv * D : D;
+        const bool seq_major = (r.flags & XN_REQ_SEQ_MAJOR) || qkv;
+        const bool rope = (r.flags & XN_REQ_ROPE) || qkv;
+        long long q_hs = seq_major ? D : (long long)S * D, q_ts = seq_major ? (long long)Hq * D : D;
+        long long kv_hs = seq_major ? D : (long long)S * D, kv_ts = seq_major ? (long long)Hkv * D : D;
+        const long long o_hs = q_hs, o_ts = q_ts;
+        if (qkv) {
+            // x rows -> projected rows [q | k | v] in the library's buffer; the attention kernels read
+            // q, k, v out of those rows through their strides
+            const OutProj& op = c->qkv_proj[size_t(r.layer)];
+            const size_t row0 = qkv_row_tab.size();
+            float* rows = c->qkv_seq + row0 * qkv_width;
+            for (int t = 0; t < S; ++t)
+                qkv_row_tab.push_back({q_dev + size_t(t) * op.in_dim, rows + size_t(t) * qkv_width});
+            if (!qkv_runs.empty() && qkv_runs.back().layer == r.layer) qkv_runs.back().row_count += S;
+            else qkv_runs.push_back({r.layer, int(row0), S, 0});
+            q_dev = rows;
+            k_dev = rows + size_t(Hq) * D;
+            v_dev = k_dev + size_t(Hkv) * D;
+            q_ts = kv_ts = (long long)qkv_width;
+        }
         d.q_in = q_dev; d.qi_hs = q_hs; d.qi_ts = q_ts;
         if (fused) {
             d.q = q_dev; d.q_hs = q_hs; d.q_ts = q_ts;
-            d.flags = 8u | ((r.flags & XN_REQ_ROPE) ? 1u : 0u);
-        } else if ((r.flags & XN_REQ_ROPE) || pinned) {
+            d.flags = 8u | (rope ? 1u : 0u);
+        } else if (rope || pinned) {
             d.q = c->q_rot + qrot_off;
             d.q_hs = (long long)S * D; d.q_ts = D;
             qrot_off += align_up(qf, 4);
-            d.flags = (r.flags & XN_REQ_ROPE) ? 1u : 2u;
+            d.flags = rope ? 1u : 2u;
         } else {
             d.q = q_dev; d.q_hs = q_hs; d.q_ts = q_ts;
         }
         d.k = k_dev; d.v = v_dev; d.kv_hs = kv_hs; d.kv_ts = kv_ts;
-        d.out = o_dev; d.o_hs = q_hs; d.o_ts = q_ts;
+        d.out = o_dev; d.o_hs = o_hs; d.o_ts = o_ts;
         if (r.flags & XN_REQ_OUT_PROJ) {
             // the attention kernels write sequence-major rows into the block's input buffer
             const OutProj& op = c->out_proj[size_t(r.layer)];
@@ -678,6 +714,7 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
     const size_t o_page = place(sizeof(int32_t) * page_ids.size());
     const size_t o_ring = place(sizeof(int32_t) * ring_rows.size());
     const size_t o_rows = place(sizeof(OutRowDev) * out_row_tab.size());
+    const size_t o_qkv = place(sizeof(OutRowDev) * qkv_row_tab.size());
     PlanSlot* slot = nullptr;
     if ((rc = acquire_slot(c, off, &slot)) != XN_OK) return rc;
     memcpy(slot->host + o_req, rd.data(), sizeof(ReqDev) * n);
@@ -689,6 +726,8 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
     if (!ring_rows.empty()) memcpy(slot->host + o_ring, ring_rows.data(), sizeof(int32_t) * ring_rows.size());
     if (!out_row_tab.empty())
         memcpy(slot->host + o_rows, out_row_tab.data(), sizeof(OutRowDev) * out_row_tab.size());
+    if (!qkv_row_tab.empty())
+        memcpy(slot->host + o_qkv, qkv_row_tab.data(), sizeof(OutRowDev) * qkv_row_tab.size());
     // The plan does not depend on anything in flight: upload it on the copy stream so that it
     // overlaps the previous submission's kernels, and make the launch stream wait for it.
     // (A blocking host-pointer call has nothing in flight to overlap with: plain in-stream copy.)
@@ -712,7 +751,35 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         c->stats.h2d_bytes += io_in;
     }
 
+    // -- the two projection blocks share one quantised-activation buffer (they run one after the
+    //    other); every run of rows starts on a 256-row boundary of it
+    size_t qkv_rows_pad = 0, q_rows_pad = 0;
+    for (OutRun& run : qkv_runs) {
+        run.q_row0 = qkv_rows_pad;
+        qkv_rows_pad += align_up(size_t(run.row_count), 256);
+    }
+    for (OutRun& run : out_runs) {
+        run.q_row0 = q_rows_pad;
+        q_rows_pad += align_up(size_t(run.row_count), 256);
+    }
+    {
+        size_t need = 0;
+        for (const OutRun& run : qkv_runs)
+            need = std::max(need, q8_floats(size_t(c->qkv_proj[size_t(run.layer)].q_stride), qkv_rows_pad));
+        for (const OutRun& run : out_runs)
+            need = std::max(need, q8_floats(size_t(c->out_proj[size_t(run.layer)].q_stride), q_rows_pad));
+        if (need && (rc = grow_device(c, &c->q8, &c->q8_cap, need)) != XN_OK) return rc;
+    }
+
     // -- launches
+    for (const OutRun& run : qkv_runs) {   // x -> [q | k | v] rows, before anything reads them
+        const OutRowDev* rows_d = reinterpret_cast<const OutRowDev*>(slot->dev + o_qkv) + run.row_begin;
+        if (c->profile && (rc = profile_begin(c, 3)) != XN_OK) return rc;
+        if ((rc = launch_out_block(c, c->qkv_proj[size_t(run.layer)], rows_d, run.row_count, run.q_row0,
+                                   qkv_rows_pad)) != XN_OK)
+            return rc;
+        if (c->profile && (rc = profile_end(c)) != XN_OK) return rc;
+    }
     for (const GapFill& g : gaps) {
         const long long total = g.n * Hkv * D;
         const int blocks = int(std::min<long long>((total + 255) / 256, 4096));
@@ -772,16 +839,11 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         c->stats.kernel_launches += 1;
     }
     XN_CUDA(c, cudaGetLastError());
-    size_t q_rows_pad = 0;   // every run starts on a 256-row boundary of the activation buffer
-    for (OutRun& run : out_runs) {
-        run.q_row0 = q_rows_pad;
-        q_rows_pad += align_up(size_t(run.row_count), 256);
-    }
-    if (q_rows_pad && (rc = grow_device(c, &c->q8, &c->q8_cap, q8_floats(c, q_rows_pad))) != XN_OK) return rc;
     for (const OutRun& run : out_runs) {
         const OutRowDev* rows_d = reinterpret_cast<const OutRowDev*>(slot->dev + o_rows) + run.row_begin;
         if (c->profile && (rc = profile_begin(c, 2)) != XN_OK) return rc;
-        if ((rc = launch_out_block(c, run.layer, rows_d, run.row_count, run.q_row0, q_rows_pad)) != XN_OK)
+        if ((rc = launch_out_block(c, c->out_proj[size_t(run.layer)], rows_d, run.row_count, run.q_row0,
+                                   q_rows_pad)) != XN_OK)
             return rc;
         if (c->profile && (rc = profile_end(c)) != XN_OK) return rc;
     }
@@ -936,6 +998,7 @@ int32_t xn_ctx_create(const xn_ctx_desc* d, xn_ctx** out_ctx) {
     c->batch_window_us = d->batch_window_us;
     c->sm_count = prop.multiProcessorCount;
     c->out_proj.resize(size_t(d->num_layers));
+    c->qkv_proj.resize(size_t(d->num_layers));
     c->decode_ctas = c->sm_count;
     if (const char* env = getenv("XORNET_ATTN_DECODE_CTAS")) {
         int v = atoi(env);
@@ -1069,11 +1132,13 @@ int32_t xn_ctx_destroy(xn_ctx* c) {
         if (s.up_ev) cudaEventDestroy(s.up_ev);
     }
     for (cudaEvent_t e : c->prof_events) cudaEventDestroy(e);
-    for (OutProj& op : c->out_proj) {
-        if (op.w2) cudaFree(op.w2);
-        if (op.w_scales) cudaFree(op.w_scales);
-        if (op.norm_w) cudaFree(op.norm_w);
-    }
+    for (std::vector<OutProj>* v : {&c->out_proj, &c->qkv_proj})
+        for (OutProj& op : *v) {
+            if (op.w2) cudaFree(op.w2);
+            if (op.w_scales) cudaFree(op.w_scales);
+            if (op.norm_w) cudaFree(op.norm_w);
+        }
+    if (c->qkv_seq) cudaFree(c->qkv_seq);
     if (c->attn_seq) cudaFree(c->attn_seq);
     if (c->q8) cudaFree(c->q8);
     if (c->q_rot) cudaFree(c->q_rot);
@@ -1125,8 +1190,8 @@ int32_t xn_profile_read_all(xn_ctx* c, double* ms, uint64_t* launches) {
     std::lock_guard<std::mutex> g(c->mu);
     XN_CUDA(c, cudaSetDevice(c->device));
     XN_CUDA(c, cudaStreamSynchronize(c->stream));
-    double total[XN_PROFILE_KINDS] = {0.0, 0.0, 0.0};
-    uint64_t count[XN_PROFILE_KINDS] = {0, 0, 0};
+    double total[XN_PROFILE_KINDS] = {};
+    uint64_t count[XN_PROFILE_KINDS] = {};
     for (size_t i = 0; i + 1 < c->prof_used; i += 2) {
         float t = 0.f;
         XN_CUDA(c, cudaEventElapsedTime(&t, c->prof_events[i], c->prof_events[i + 1]));
@@ -1414,6 +1479,87 @@ int32_t xn_ternary_pack(int32_t in_dim, int32_t out_dim, const float* weights, i
     return XN_OK;
 }
 
+namespace {
+struct LinearPart {
+    const uint8_t* packed;
+    const float* scales;
+    int rows;
+};
+
+// Builds the device form of a ternary linear layer whose rows are the concatenation of `parts`
+// (all with the same in_dim and packing) and stores it in *slot, replacing what was there.
+int32_t install_linear(xn_ctx* c, OutProj* slot, int in_dim, int pack_type, const LinearPart* parts,
+                       int n_parts, const float* norm_weight, float norm_eps) {
+    if (pack_type != XN_PACK4 && pack_type != XN_PACK5)
+        return fail(c, XN_ERR_ARG, "pack_type must be XN_PACK4 or XN_PACK5");
+    if (in_dim <= 0 || size_t(in_dim) * 12 > 200 * 1024)
+        return fail(c, XN_ERR_CAPACITY, "in_dim %d outside what one block's shared memory holds", in_dim);
+    long long out_dim = 0;
+    for (int i = 0; i < n_parts; ++i) {
+        if (!parts[i].packed || !parts[i].scales || parts[i].rows <= 0)
+            return fail(c, XN_ERR_ARG, "null weight pointer or empty projection");
+        out_dim += parts[i].rows;
+    }
+    if (out_dim > (1 << 20)) return fail(c, XN_ERR_SHAPE, "out_dim %lld outside 1..2^20", out_dim);
+    XN_CUDA(c, cudaSetDevice(c->device));
+    XN_CUDA(c, cudaStreamSynchronize(c->stream));  // launches in flight may still read the old weights
+
+    OutProj op;
+    op.in_dim = in_dim;
+    op.out_dim = int(out_dim);
+    op.q_stride = int(align_up(size_t(in_dim), 128));
+    op.w_stride = op.q_stride / 4;
+    op.eps = norm_eps;
+    const size_t bpr = packed_row_bytes(size_t(in_dim), pack_type);
+    // device layout: [row / 32][K / 128][32 rows][32 bytes] (code_offset); rows past out_dim and
+    // columns past in_dim hold code 1 = weight 0
+    const int nkb = op.q_stride / 128;
+    std::vector<uint8_t> w2(size_t((out_dim + 31) / 32) * nkb * 1024, uint8_t(0x55));
+    std::vector<float> scales(size_t(out_dim), 0.f);
+    std::vector<uint8_t> row_codes(size_t(op.w_stride));
+    int o = 0;
+    for (int i = 0; i < n_parts; ++i)
+        for (int rr = 0; rr < parts[i].rows; ++rr, ++o) {
+            recode_row_2bit(parts[i].packed + size_t(rr) * bpr, size_t(in_dim), pack_type, row_codes.data(),
+                            row_codes.size());
+            for (int kb = 0; kb < nkb; ++kb)
+                memcpy(w2.data() + code_offset(o, kb * 128, nkb), row_codes.data() + size_t(kb) * 32, 32);
+            scales[size_t(o)] = parts[i].scales[rr];
+        }
+    auto upload = [&](void** dst, const void* src, size_t bytes) -> cudaError_t {
+        cudaError_t e = cudaMalloc(dst, bytes);
+        if (e != cudaSuccess) return e;
+        return cudaMemcpy(*dst, src, bytes, cudaMemcpyHostToDevice);
+    };
+    cudaError_t e = upload(reinterpret_cast<void**>(&op.w2), w2.data(), w2.size());
+    if (e == cudaSuccess) e = upload(reinterpret_cast<void**>(&op.w_scales), scales.data(), scales.size() * 4);
+    if (e == cudaSuccess && norm_weight)
+        e = upload(reinterpret_cast<void**>(&op.norm_w), norm_weight, size_t(in_dim) * 4);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(reinterpret_cast<const void*>(ternary_gemm_kernel),
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, kOutGemmSmem);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(reinterpret_cast<const void*>(ternary_gemm_tc_kernel),
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, tg::smem_bytes(tg::max_nkb()));
+    if (e == cudaSuccess && align_up(size_t(in_dim), 4) * 12 > 40 * 1024)  // static shared memory counts too
+        e = cudaFuncSetAttribute(reinterpret_cast<const void*>(subnorm_quant_kernel),
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 int(align_up(size_t(in_dim), 4) * 12));
+    if (e != cudaSuccess) {
+        if (op.w2) cudaFree(op.w2);
+        if (op.w_scales) cudaFree(op.w_scales);
+        if (op.norm_w) cudaFree(op.norm_w);
+        return fail(c, XN_ERR_CUDA, "uploading the weights failed: %s", cudaGetErrorString(e));
+    }
+    if (slot->w2) cudaFree(slot->w2);
+    if (slot->w_scales) cudaFree(slot->w_scales);
+    if (slot->norm_w) cudaFree(slot->norm_w);
+    op.set = true;
+    *slot = op;
+    return XN_OK;
+}
+}  // namespace
+
 int32_t xn_out_proj_set(xn_ctx* c, const xn_out_proj_desc* d) {
     if (!ctx_ok(c)) return XN_ERR_HANDLE;
     std::lock_guard<std::mutex> g(c->mu);
@@ -1423,65 +1569,22 @@ int32_t xn_out_proj_set(xn_ctx* c, const xn_out_proj_desc* d) {
     if (d->in_dim != c->num_heads * c->head_dim)
         return fail(c, XN_ERR_SHAPE, "Input dimension mismatch: expected %d, got %d",
                     c->num_heads * c->head_dim, d->in_dim);
-    if (d->out_dim <= 0 || d->out_dim > (1 << 20)) return fail(c, XN_ERR_SHAPE, "out_dim %d outside 1..2^20", d->out_dim);
-    if (d->pack_type != XN_PACK4 && d->pack_type != XN_PACK5)
-        return fail(c, XN_ERR_ARG, "pack_type must be XN_PACK4 or XN_PACK5");
-    if (size_t(d->in_dim) * 12 > 200 * 1024) return fail(c, XN_ERR_CAPACITY, "in_dim %d is beyond one block's shared memory", d->in_dim);
-    XN_CUDA(c, cudaSetDevice(c->device));
-    XN_CUDA(c, cudaStreamSynchronize(c->stream));  // launches in flight may still read the old block
+    if (d->out_dim <= 0) return fail(c, XN_ERR_SHAPE, "out_dim %d must be positive", d->out_dim);
+    const LinearPart part{d->packed, d->w_scales, d->out_dim};
+    return install_linear(c, &c->out_proj[size_t(d->layer)], d->in_dim, d->pack_type, &part, 1,
+                          d->norm_weight, d->norm_eps);
+}
 
-    OutProj op;
-    op.in_dim = d->in_dim;
-    op.out_dim = d->out_dim;
-    op.q_stride = int(align_up(size_t(d->in_dim), 128));
-    op.w_stride = op.q_stride / 4;
-    op.eps = d->norm_eps;
-    const size_t bpr = packed_row_bytes(size_t(d->in_dim), d->pack_type);
-    // device layout: [row / 32][K / 128][32 rows][32 bytes] (code_offset); rows past out_dim and
-    // columns past in_dim hold code 1 = weight 0
-    const int nkb = op.q_stride / 128;
-    std::vector<uint8_t> w2(size_t((d->out_dim + 31) / 32) * nkb * 1024, uint8_t(0x55));
-    std::vector<uint8_t> row_codes(size_t(op.w_stride));
-    for (int o = 0; o < d->out_dim; ++o) {
-        recode_row_2bit(d->packed + size_t(o) * bpr, size_t(d->in_dim), d->pack_type, row_codes.data(),
-                        row_codes.size());
-        for (int kb = 0; kb < nkb; ++kb)
-            memcpy(w2.data() + code_offset(o, kb * 128, nkb), row_codes.data() + size_t(kb) * 32, 32);
-    }
-    auto upload = [&](void** dst, const void* src, size_t bytes) -> cudaError_t {
-        cudaError_t e = cudaMalloc(dst, bytes);
-        if (e != cudaSuccess) return e;
-        return cudaMemcpy(*dst, src, bytes, cudaMemcpyHostToDevice);
-    };
-    cudaError_t e = upload(reinterpret_cast<void**>(&op.w2), w2.data(), w2.size());
-    if (e == cudaSuccess) e = upload(reinterpret_cast<void**>(&op.w_scales), d->w_scales, size_t(d->out_dim) * 4);
-    if (e == cudaSuccess && d->norm_weight)
-        e = upload(reinterpret_cast<void**>(&op.norm_w), d->norm_weight, size_t(d->in_dim) * 4);
-    if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(reinterpret_cast<const void*>(ternary_gemm_kernel),
-                                 cudaFuncAttributeMaxDynamicSharedMemorySize, kOutGemmSmem);
-    if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(reinterpret_cast<const void*>(ternary_gemm_tc_kernel),
-                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 std::max(tg::smem_bytes(24), tg::smem_bytes(tg::max_nkb())));
-
-    if (e == cudaSuccess && align_up(size_t(d->in_dim), 4) * 12 > 40 * 1024)  // static shared memory counts too
-        e = cudaFuncSetAttribute(reinterpret_cast<const void*>(subnorm_quant_kernel),
-                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 int(align_up(size_t(d->in_dim), 4) * 12));
-    if (e != cudaSuccess) {
-        if (op.w2) cudaFree(op.w2);
-        if (op.w_scales) cudaFree(op.w_scales);
-        if (op.norm_w) cudaFree(op.norm_w);
-        return fail(c, XN_ERR_CUDA, "uploading the output block failed: %s", cudaGetErrorString(e));
-    }
-    OutProj& old = c->out_proj[size_t(d->layer)];
-    if (old.w2) cudaFree(old.w2);
-    if (old.w_scales) cudaFree(old.w_scales);
-    if (old.norm_w) cudaFree(old.norm_w);
-    op.set = true;
-    old = op;
-    return XN_OK;
+int32_t xn_qkv_proj_set(xn_ctx* c, const xn_qkv_proj_desc* d) {
+    if (!ctx_ok(c)) return XN_ERR_HANDLE;
+    std::lock_guard<std::mutex> g(c->mu);
+    if (!d) return fail(c, XN_ERR_ARG, "null descriptor");
+    if (d->layer < 0 || d->layer >= c->num_layers)
+        return fail(c, XN_ERR_ARG, "layer %d outside 0..%d", d->layer, c->num_layers - 1);
+    const LinearPart parts[3] = {{d->q_packed, d->q_scales, c->num_heads * c->head_dim},
+                                 {d->k_packed, d->k_scales, c->num_kv_heads * c->head_dim},
+                                 {d->v_packed, d->v_scales, c->num_kv_heads * c->head_dim}};
+    return install_linear(c, &c->qkv_proj[size_t(d->layer)], d->in_dim, d->pack_type, parts, 3, nullptr, 0.f);
 }
 
 int32_t xn_out_proj(xn_ctx* c, int32_t layer, int32_t rows, const float* y, float* out, uint32_t flags) {
@@ -1498,7 +1601,7 @@ int32_t xn_out_proj(xn_ctx* c, int32_t layer, int32_t rows, const float* y, floa
     const size_t in_b = size_t(rows) * op.in_dim * 4, out_b = size_t(rows) * op.out_dim * 4;
     int32_t rc;
     const size_t q_rows_pad = align_up(size_t(rows), 256);
-    if ((rc = grow_device(c, &c->q8, &c->q8_cap, q8_floats(c, q_rows_pad))) != XN_OK) return rc;
+    if ((rc = grow_device(c, &c->q8, &c->q8_cap, q8_floats(size_t(op.q_stride), q_rows_pad))) != XN_OK) return rc;
     const float* src = y;
     float* dst = out;
     if (!dev) {
@@ -1515,7 +1618,7 @@ int32_t xn_out_proj(xn_ctx* c, int32_t layer, int32_t rows, const float* y, floa
     for (int t = 0; t < rows; ++t) tab[t] = {src + size_t(t) * op.in_dim, dst + size_t(t) * op.out_dim};
     XN_CUDA(c, cudaMemcpyAsync(slot->dev, slot->host, sizeof(OutRowDev) * size_t(rows),
                                cudaMemcpyHostToDevice, c->stream));
-    rc = launch_out_block(c, layer, reinterpret_cast<const OutRowDev*>(slot->dev), rows, 0, q_rows_pad);
+    rc = launch_out_block(c, op, reinterpret_cast<const OutRowDev*>(slot->dev), rows, 0, q_rows_pad);
     XN_CUDA(c, cudaEventRecord(slot->ev, c->stream));
     slot->used = true;
     if (rc != XN_OK) return rc;
