@@ -718,7 +718,7 @@ def run_gpu_arm(args):
                 "rows_per_pair": n_streams, "in_dim": Hq * D, "out_dim": (Hq + 2 * Hkv) * D}
         if out_block:
             line["out_block"] = {
-                "kernels": "subnorm_quant_kernel + ternary_gemm_kernel (dp4a), one pair per layer",
+                "kernels": "subnorm_quant_kernel + ternary_gemm_tc_kernel (tcgen05 kind::i8), one pair per layer",
                 "avg_pair_ms": ob_ms / max(ob_n, 1), "pairs_timed": int(ob_n),
                 "rows_per_pair": n_streams, "in_dim": Hq * D, "out_dim": Hq * D,
                 "weight_bytes_per_layer": Hq * D * (Hq * D // 4)}
