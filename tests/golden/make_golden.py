@@ -48,8 +48,51 @@ def build(name):
     return out
 
 
+# Whole attention block (ternary q/k/v projections, RoPE, attention, sub-norm, ternary o_proj):
+# name: (Hq, Hkv, D, hidden, out_dim, pack, theta, steps, capacity)
+BLOCK_CASES = {
+    "block_pack4": (4, 2, 16, 48, 40, xo.PACK4, 10000.0, [(0, 5), (5, 1), (6, 1)], 16),
+    "block_pack5": (3, 1, 32, 60, 20, xo.PACK5, 500000.0, [(0, 3), (3, 1)], 8),
+}
+
+
+def block_layers(z_or_rng, Hq, Hkv, D, hidden, out_dim, pack):
+    """The four TernaryLinears of a block case, from stored f32 weights or fresh from a generator."""
+    shapes = {"wq": (Hq * D, hidden), "wk": (Hkv * D, hidden), "wv": (Hkv * D, hidden), "wo": (out_dim, Hq * D)}
+    ws = {n: (z_or_rng[n] if not hasattr(z_or_rng, "standard_normal")
+              else z_or_rng.standard_normal(sh).astype(np.float32)) for n, sh in shapes.items()}
+    scale = {n: (float(hidden) ** -0.5 if n != "wo" else None) for n in ws}   # q, k, v rows stay O(1)
+    return ws, scale
+
+
+def build_block(name):
+    Hq, Hkv, D, hidden, out_dim, pack, theta, steps, cap = BLOCK_CASES[name]
+    rng = np.random.default_rng(sum(map(ord, name)))
+    xo.set_quant_body(1)   # the AVX-512 quantiser body, whatever CPU generates the fixture
+    ws, scale = block_layers(rng, Hq, Hkv, D, hidden, out_dim, pack)
+    lin = {n: xo.TernaryLinear(w.shape[1], w.shape[0], w, pack, scale[n]) for n, w in ws.items()}
+    norm_w = (1.0 + 0.2 * rng.standard_normal(Hq * D)).astype(np.float32)
+    cos, sin = xo.rope_tables(theta, D, max(p + s for p, s in steps))
+    cache = xo.RingCache(1, Hkv, cap, D)
+    out = {"meta": np.array([Hq, Hkv, D, hidden, out_dim, pack, cap, len(steps)], np.int64),
+           "theta": np.float64(theta), "steps": np.array(steps, np.int64), "norm_w": norm_w,
+           "eps": np.float32(1e-5), **ws}
+    for i, (pos, S) in enumerate(steps):
+        x = rng.standard_normal((1, S, hidden)).astype(np.float32)
+        y, attn = xo.causal_self_attention_forward(x, pos, 0, cache, cos, sin, lin["wq"], lin["wk"], lin["wv"],
+                                                   Hq, Hkv, D, norm_w, 1e-5, lin["wo"])
+        out[f"x{i}"], out[f"y{i}"], out[f"attn{i}"] = x, y, attn
+    out["k_cache"] = cache.k_buffer(0).copy()
+    out["v_cache"] = cache.v_buffer(0).copy()
+    xo.set_quant_body(-1)
+    return out
+
+
 if __name__ == "__main__":
     xo.set_isa(xo.ISA_AVX512) if xo.set_isa(xo.ISA_AVX512) == 0 else None
     for name in CASES:
         np.savez_compressed(os.path.join(HERE, name + ".npz"), **build(name))
+        print("wrote", name)
+    for name in BLOCK_CASES:
+        np.savez_compressed(os.path.join(HERE, name + ".npz"), **build_block(name))
         print("wrote", name)

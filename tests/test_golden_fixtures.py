@@ -13,7 +13,9 @@ import pytest
 import oracle as xo
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-FIXTURES = sorted(glob.glob(os.path.join(HERE, "golden", "*.npz")))
+FIXTURES = sorted(p for p in glob.glob(os.path.join(HERE, "golden", "*.npz"))
+                  if not os.path.basename(p).startswith("block_"))
+BLOCK_FIXTURES = sorted(glob.glob(os.path.join(HERE, "golden", "block_*.npz")))
 
 
 def load(path):
@@ -58,6 +60,64 @@ def test_gpu_matches_fixture(path):
     for i, (pos, S) in enumerate(steps):
         got = ctx.attention(st, 0, pos, z[f"q{i}"], z[f"k{i}"], z[f"v{i}"], rope=True)
         assert_parity(got, z[f"out{i}"], f"{os.path.basename(path)} step {i}")
+    k, v = st.read_range(0, 0, cap)
+    assert np.array_equal(k.ravel(), z["k_cache"]) and np.array_equal(v.ravel(), z["v_cache"])
+    ctx.close()
+
+
+# ---- whole attention block (ternary projections around the attention) ---------------------------
+
+def load_block(path):
+    z = np.load(path)
+    Hq, Hkv, D, hidden, out_dim, pack, cap, n = (int(x) for x in z["meta"])
+    steps = [tuple(int(x) for x in s) for s in z["steps"]]
+    scale = {n_: (float(hidden) ** -0.5 if n_ != "wo" else None) for n_ in ("wq", "wk", "wv", "wo")}
+    return z, Hq, Hkv, D, hidden, out_dim, pack, cap, float(z["theta"]), steps, scale
+
+
+@pytest.mark.parametrize("path", BLOCK_FIXTURES, ids=[os.path.basename(p) for p in BLOCK_FIXTURES])
+def test_oracle_reproduces_block_fixture(path):
+    z, Hq, Hkv, D, hidden, out_dim, pack, cap, theta, steps, scale = load_block(path)
+    exact = xo.set_isa(xo.ISA_AVX512) == 0
+    if not exact:
+        xo.set_isa(xo.ISA_AUTO)
+    xo.set_quant_body(1)
+    try:
+        lin = {n: xo.TernaryLinear(z[n].shape[1], z[n].shape[0], z[n], pack, scale[n]) for n in scale}
+        cos, sin = xo.rope_tables(theta, D, max(p + s for p, s in steps))
+        cache = xo.RingCache(1, Hkv, cap, D)
+        for i, (pos, S) in enumerate(steps):
+            y, attn = xo.causal_self_attention_forward(z[f"x{i}"], pos, 0, cache, cos, sin, lin["wq"], lin["wk"],
+                                                       lin["wv"], Hq, Hkv, D, z["norm_w"], float(z["eps"]), lin["wo"])
+            if exact:
+                assert np.array_equal(y, z[f"y{i}"]) and np.array_equal(attn, z[f"attn{i}"]), f"step {i}"
+            else:
+                assert np.linalg.norm(y - z[f"y{i}"]) <= 1e-3 * np.linalg.norm(z[f"y{i}"])
+        # the projections and the rotation do not depend on the attention's ISA body: always exact
+        assert np.array_equal(cache.k_buffer(0), z["k_cache"]) and np.array_equal(cache.v_buffer(0), z["v_cache"])
+    finally:
+        xo.set_quant_body(-1)
+        xo.set_isa(xo.ISA_AUTO)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("path", BLOCK_FIXTURES, ids=[os.path.basename(p) for p in BLOCK_FIXTURES])
+def test_gpu_matches_block_fixture(path):
+    import xor_net_b200 as xn
+    from gpu_util import assert_parity, errs
+
+    z, Hq, Hkv, D, hidden, out_dim, pack, cap, theta, steps, scale = load_block(path)
+    cos, sin = xn.rope_tables(theta, D, max(p + s for p, s in steps))
+    ctx = xn.Context(1, Hq, Hkv, D, pool_pages=4, rope=(cos, sin), prefill_mode=1)
+    lin = {n: xn.TernaryLinear(z[n].shape[1], z[n].shape[0], z[n], pack, scale[n]) for n in scale}
+    ctx.set_qkv_proj(0, lin["wq"], lin["wk"], lin["wv"])
+    ctx.set_out_proj(0, lin["wo"], z["norm_w"], float(z["eps"]))
+    st = ctx.new_stream(cap)
+    for i, (pos, S) in enumerate(steps):
+        attn = ctx.attention_batch([st], 0, [pos], [z[f"x{i}"]], qkv_proj=True)[0]
+        y = ctx.attention_batch([st], 0, [pos], [z[f"x{i}"]], qkv_proj=True, out_proj=True)[0]
+        assert_parity(attn, xo.transpose_heads_to_seq(z[f"attn{i}"]), f"{os.path.basename(path)} attention {i}")
+        assert errs(y, z[f"y{i}"])[1] <= 1e-3, f"{os.path.basename(path)} block {i}"
     k, v = st.read_range(0, 0, cap)
     assert np.array_equal(k.ravel(), z["k_cache"]) and np.array_equal(v.ravel(), z["v_cache"])
     ctx.close()
