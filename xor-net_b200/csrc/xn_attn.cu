@@ -101,6 +101,7 @@ struct xn_ctx {
     bool fuse_pinned = true; // ... also when q,k,v live in page-locked host memory
     bool out_tc = true;      // output projection on the tensor cores (else the dp4a kernel)
     bool out_pdl = true;     // ... launched as a programmatic dependent of the quantiser kernel
+    bool out_rows_kernel = true;  // ... and, for more than 128 rows, the many-row variant
     int* sync_d = nullptr;   // chunk counter, done counter, per-unit arrival counters
     size_t sync_cap = 0;     // ints
     cudaStream_t stream = nullptr;
@@ -402,20 +403,30 @@ int32_t launch_out_block(xn_ctx* c, const OutProj& op, const OutRowDev* rows_d, 
         ga.w_scales = op.w_scales; ga.inv_scale = inv; ga.rows = rows_d;
         ga.n_rows = n_rows; ga.out_dim = op.out_dim; ga.k_bytes = op.q_stride;
         ga.status = c->status_d;
+        // up to 128 rows: one 128 x 32 tile per block; more rows: blocks that keep 64 output rows'
+        // weights resident and walk over the token tiles
+        const int nkb = op.q_stride / tg::kBK;
+        const bool many = c->out_rows_kernel && n_rows > tg::kTM && nkb <= tgr::max_nkb();
         dim3 grid(unsigned((op.out_dim + tg::kTN - 1) / tg::kTN), unsigned((n_rows + tg::kTM - 1) / tg::kTM));
+        if (many) {
+            const int o_tiles = (op.out_dim + tgr::kTN - 1) / tgr::kTN;
+            const int n_tiles = (n_rows + tgr::kTM - 1) / tgr::kTM;
+            grid = dim3(unsigned(o_tiles), unsigned(std::max(1, std::min(n_tiles, c->sm_count / std::max(1, o_tiles)))));
+        }
         // programmatic dependent launch: the blocks may start while the quantiser kernel still
         // runs (it releases them at its start) and decode their weights in the meantime
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = grid;
-        cfg.blockDim = dim3(tg::kThreads);
-        cfg.dynamicSmemBytes = size_t(tg::smem_bytes(op.q_stride / tg::kBK));
+        cfg.blockDim = dim3(many ? tgr::kThreads : tg::kThreads);
+        cfg.dynamicSmemBytes = size_t(many ? tgr::smem_bytes(nkb) : tg::smem_bytes(nkb));
         cfg.stream = c->stream;
         cudaLaunchAttribute attr[1];
         attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[0].val.programmaticStreamSerializationAllowed = c->out_pdl ? 1 : 0;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        XN_CUDA(c, cudaLaunchKernelEx(&cfg, ternary_gemm_tc_kernel, ga));
+        if (many) XN_CUDA(c, cudaLaunchKernelEx(&cfg, ternary_gemm_rows_kernel, ga));
+        else XN_CUDA(c, cudaLaunchKernelEx(&cfg, ternary_gemm_tc_kernel, ga));
     } else {
         const int R = std::max(1, std::min(kOutMaxRowsPerCta, (op.out_dim + c->sm_count - 1) / c->sm_count));
         dim3 grid(unsigned((op.out_dim + R - 1) / R), unsigned((n_rows + kOutRowsTile - 1) / kOutRowsTile));
@@ -1014,6 +1025,7 @@ int32_t xn_ctx_create(const xn_ctx_desc* d, xn_ctx** out_ctx) {
     if (const char* env = getenv("XORNET_ATTN_FUSE_PINNED")) c->fuse_pinned = atoi(env) != 0;
     if (const char* env = getenv("XORNET_ATTN_OUTPROJ_TC")) c->out_tc = atoi(env) != 0;
     if (const char* env = getenv("XORNET_ATTN_OUTPROJ_PDL")) c->out_pdl = atoi(env) != 0;
+    if (const char* env = getenv("XORNET_ATTN_OUTPROJ_ROWS")) c->out_rows_kernel = atoi(env) != 0;
 
 
     const size_t page_bytes =
@@ -1541,6 +1553,9 @@ int32_t install_linear(xn_ctx* c, OutProj* slot, int in_dim, int pack_type, cons
     if (e == cudaSuccess)
         e = cudaFuncSetAttribute(reinterpret_cast<const void*>(ternary_gemm_tc_kernel),
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, tg::smem_bytes(tg::max_nkb()));
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(reinterpret_cast<const void*>(ternary_gemm_rows_kernel),
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, tgr::smem_bytes(tgr::max_nkb()));
     if (e == cudaSuccess && align_up(size_t(in_dim), 4) * 12 > 40 * 1024)  // static shared memory counts too
         e = cudaFuncSetAttribute(reinterpret_cast<const void*>(subnorm_quant_kernel),
                                  cudaFuncAttributeMaxDynamicSharedMemorySize,

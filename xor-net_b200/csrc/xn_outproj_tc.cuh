@@ -360,4 +360,259 @@ ternary_gemm_tc_kernel(const TernaryGemmArgs a) {
     }
 }
 
+// ================================================================================================
+// Many-row variant (prefill-size inputs): the same arithmetic, shaped for throughput.
+//
+// One thread block keeps the weights of 64 output rows resident (decoded once, 160 KB for
+// K = 2560) and walks over token tiles of 128 rows: blockIdx.y, blockIdx.y + gridDim.y, ...  The
+// activation ring, the MMA issuer and the epilogue never drain between tiles: two accumulators of
+// 64 columns alternate in tensor memory, so tile i is stored while tile i + 1 is multiplied.
+// Per 256-column stage: 8 MMAs with N = 64.  Roles as in ternary_gemm_tc_kernel (320 threads).
+// ================================================================================================
+namespace tgr {
+constexpr int kTM = 128;
+constexpr int kTN = 64;
+constexpr int kBK = 128;
+constexpr int kPieceKb = 2;
+constexpr int kActBlock = kTM * kBK;               // 16 KB
+constexpr int kActStage = kPieceKb * kActBlock;    // 32 KB
+constexpr int kActStages = 2;
+constexpr int kWBlock = kTN * kBK;                 // 8 KB of decoded weights per K-block
+constexpr int kMaxPieces = 10;                     // K <= 2560
+constexpr int kThreads = 320;
+constexpr int kDecoderWarps = 8;
+__host__ __device__ constexpr int smem_bytes(int nkb) {
+    return kActStages * kActStage + nkb * kWBlock + 1024 /* alignment slack */ + 512 /* barriers */;
+}
+__host__ __device__ constexpr int max_nkb() { return kMaxPieces * kPieceKb; }
+}  // namespace tgr
+
+__global__ void __launch_bounds__(tgr::kThreads, 1)
+ternary_gemm_rows_kernel(const TernaryGemmArgs a) {
+    using namespace tgr;
+    using tg::warp_wait;
+    extern __shared__ unsigned char smem_dyn[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
+    const int nkb = a.k_bytes / kBK;
+    const int n_pieces = (nkb + kPieceKb - 1) / kPieceKb;
+    const int n_tiles = (a.n_rows + kTM - 1) / kTM;
+    unsigned char* act_s = smem;                                  // [2][2][128 rows x 128 B]
+    unsigned char* w_s = act_s + kActStages * kActStage;          // [nkb][64 rows x 128 B], decoded
+    uint64_t* bars = reinterpret_cast<uint64_t*>(w_s + nkb * kWBlock);
+    uint64_t* w_full = bars;                         // [kMaxPieces] piece decoded (once)
+    uint64_t* act_full = w_full + kMaxPieces;        // [2] stage landed
+    uint64_t* act_empty = act_full + kActStages;     // [2] stage consumed
+    uint64_t* acc_full = act_empty + kActStages;     // [2] accumulator complete
+    uint64_t* acc_empty = acc_full + 2;              // [2] accumulator read out by the 8 epilogue warps
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);
+    static_assert((kMaxPieces + 2 * kActStages + 4) * 8 + 16 <= 512, "barrier area");
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int o0 = blockIdx.x * kTN;
+
+    // decoders: item = (K-block, row 0..63, half); 128 items per K-block, so one pass of the 256
+    // decoder threads covers one piece of 2 K-blocks.  All codes are requested up front.
+    const int dtid = tid - 64;
+    const int kb_in = (dtid >> 7) & 1;
+    const int r = (dtid >> 1) & 63, h = dtid & 1;
+    uint4 codes[kMaxPieces];
+    if (warp >= 2) {
+        const bool valid = o0 + r < a.out_dim;
+        // the code layout groups 32 rows: this block's 64 rows are two consecutive groups
+        const uint8_t* src = a.w2 + ((size_t(2 * blockIdx.x + (r >> 5)) * nkb + kb_in) * 32 + (r & 31)) * 32 + h * 16;
+#pragma unroll
+        for (int p = 0; p < kMaxPieces; ++p) {
+            codes[p] = make_uint4(0x55555555u, 0x55555555u, 0x55555555u, 0x55555555u);
+            if (valid && p * kPieceKb + kb_in < nkb)
+                codes[p] = __ldg(reinterpret_cast<const uint4*>(src + size_t(p) * kPieceKb * 1024));
+        }
+    }
+
+    if (tid == 0) {
+        for (int p = 0; p < n_pieces; ++p) mbar_init(&w_full[p], kDecoderWarps);
+        for (int s = 0; s < kActStages; ++s) {
+            mbar_init(&act_full[s], 1);
+            mbar_init(&act_empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], kDecoderWarps);
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         smem_u32(tmem_slot)),
+                     "r"(uint32_t(2 * kTN))
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    pf::fence_before_sync();
+    __syncthreads();
+    pf::fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ======================= copy producer: activation stages of every tile =======================
+        pdl_wait();
+        const size_t kb_step = size_t(a.q_rows_pad) * kBK;
+        int st = 0;
+        uint32_t wrap_par = 1;
+        int issued = 0;
+        bool ok = true;
+        for (int tile = blockIdx.y; tile < n_tiles && ok; tile += gridDim.y) {
+            const int8_t* src = a.q + size_t(a.q_row0 + size_t(tile) * kTM) * kBK;
+            for (int p = 0; p < n_pieces; ++p, ++issued) {
+                if (issued >= kActStages) {
+                    wrap_par ^= (st == 0) ? 1u : 0u;
+                    if (!warp_wait(&act_empty[st], wrap_par, lane)) {
+                        if (lane == 0) {
+                            report_status(a.status, kDevWaitEmpty);
+                            *abort_flag = 1;
+                        }
+                        ok = false;
+                        break;
+                    }
+                }
+                if (lane == 0) {
+                    const int kbs = min(kPieceKb, nkb - p * kPieceKb);
+                    mbar_arrive_expect_tx(&act_full[st], uint32_t(kbs * kActBlock));
+                    for (int j = 0; j < kbs; ++j)
+                        bulk_g2s(act_s + st * kActStage + j * kActBlock, src + size_t(j) * kb_step,
+                                 uint32_t(kActBlock), &act_full[st]);
+                }
+                src += size_t(kPieceKb) * kb_step;
+                st ^= 1;
+                __syncwarp();
+            }
+        }
+    } else if (warp == 1) {
+        // =============================== MMA issuer ===============================
+        const uint32_t idesc = tg::make_idesc_i8(kTM, kTN);
+        const uint64_t adesc0 = pf::smem_desc(smem_u32(act_s), 0, 1024, pf::kLayoutSw128);
+        const uint64_t bdesc0 = pf::smem_desc(smem_u32(w_s), 0, 1024, pf::kLayoutSw128);
+        bool ok = true;
+        int st = 0;
+        uint32_t par = 0;
+        int tile_idx = 0;
+        for (int tile = blockIdx.y; tile < n_tiles && ok; tile += gridDim.y, ++tile_idx) {
+            const int b = tile_idx & 1;
+            if (tile_idx >= 2)   // the epilogue must have read this accumulator's previous tile
+                ok = warp_wait(&acc_empty[b], uint32_t(((tile_idx >> 1) - 1) & 1), lane);
+            uint64_t bdesc = bdesc0;
+            for (int p = 0; p < n_pieces && ok; ++p) {
+                if (tile_idx == 0) ok = warp_wait(&w_full[p], 0, lane);
+                ok = ok && warp_wait(&act_full[st], par, lane);
+                if (!ok || *abort_flag) { ok = false; break; }
+                if (lane == 0) {
+                    pf::fence_after_sync();
+                    const int kbs = min(kPieceKb, nkb - p * kPieceKb);
+                    const uint64_t adesc = adesc0 + uint64_t(st * (kActStage >> 4));
+                    for (int j = 0; j < kbs; ++j)
+#pragma unroll
+                        for (int k4 = 0; k4 < kBK / 32; ++k4)
+                            tg::mma_ss_i8(tmem_base + uint32_t(b * kTN),
+                                          adesc + uint64_t(j * (kActBlock >> 4) + k4 * 2),
+                                          bdesc + uint64_t(j * (kWBlock >> 4) + k4 * 2), idesc,
+                                          uint32_t((p | j | k4) != 0));
+                    pf::mma_commit(&act_empty[st]);
+                }
+                bdesc += uint64_t(kPieceKb * (kWBlock >> 4));
+                par ^= uint32_t(st);
+                st ^= 1;
+                __syncwarp();
+            }
+            if (ok && lane == 0) pf::mma_commit(&acc_full[b]);
+            __syncwarp();
+        }
+        if (!ok && lane == 0) {
+            report_status(a.status, kDevWaitFull);
+            *abort_flag = 1;
+        }
+    } else {
+        // =============================== weight decoders ===============================
+        const int w_off = (r >> 3) * 1024 + (r & 7) * 128;
+#pragma unroll
+        for (int p = 0; p < kMaxPieces; ++p) {
+            if (p < n_pieces) {
+                const int kb = p * kPieceKb + kb_in;
+                if (kb < nkb) {
+                    const uint32_t w[4] = {codes[p].x, codes[p].y, codes[p].z, codes[p].w};
+                    unsigned char* dst = w_s + kb * kWBlock + w_off;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        uint4 v;
+                        v.x = tg::decode4_canon(w[j] & 0xffu);
+                        v.y = tg::decode4_canon((w[j] >> 8) & 0xffu);
+                        v.z = tg::decode4_canon((w[j] >> 16) & 0xffu);
+                        v.w = tg::decode4_canon(w[j] >> 24);
+                        *reinterpret_cast<uint4*>(dst + (((h * 4 + j) ^ (r & 7)) << 4)) = v;
+                    }
+                }
+                tg::fence_generic_to_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&w_full[p]);
+            }
+        }
+
+        // =============================== epilogue, tile after tile ===============================
+        // thread = token row; the two warps of a lane quarter take 32 of the 64 output columns each:
+        // 128 contiguous bytes per thread
+        pdl_wait();
+        const int quarter = warp & 3;
+        const int half = (warp - 2) >> 2;
+        const int oc = o0 + half * 32;
+        int tile_idx = 0;
+        for (int tile = blockIdx.y; tile < n_tiles; tile += gridDim.y, ++tile_idx) {
+            const int b = tile_idx & 1;
+            const int t = tile * kTM + quarter * 32 + lane;
+            const bool t_valid = t < a.n_rows;
+            float* dst = t_valid ? a.rows[t].dst + oc : nullptr;
+            const float is = t_valid ? a.inv_scale[a.q_row0 + t] : 0.f;
+            if (!warp_wait(&acc_full[b], uint32_t((tile_idx >> 1) & 1), lane) || *abort_flag) {
+                if (lane == 0 && !*abort_flag) report_status(a.status, kDevWaitMma);
+                break;
+            }
+            pf::fence_after_sync();
+            uint32_t acc[32];
+            pf::tmem_ld32(tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(b * kTN + half * 32), acc);
+            pf::tmem_wait_ld();
+            pf::fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[b]);   // the MMA issuer may overwrite this accumulator
+            if (t_valid) {
+                if (oc + 32 <= a.out_dim && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4) {
+                        const float4 ws = *reinterpret_cast<const float4*>(a.w_scales + oc + i);
+                        float4 v;
+                        v.x = __fmul_rn(__fmul_rn(float(int(acc[i + 0])), is), ws.x);
+                        v.y = __fmul_rn(__fmul_rn(float(int(acc[i + 1])), is), ws.y);
+                        v.z = __fmul_rn(__fmul_rn(float(int(acc[i + 2])), is), ws.z);
+                        v.w = __fmul_rn(__fmul_rn(float(int(acc[i + 3])), is), ws.w);
+                        *reinterpret_cast<float4*>(dst + i) = v;
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (oc + i < a.out_dim)
+                            dst[i] = __fmul_rn(__fmul_rn(float(int(acc[i])), is), a.w_scales[oc + i]);
+                }
+            }
+        }
+    }
+
+    pf::fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        pf::fence_after_sync();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                     "r"(uint32_t(2 * kTN))
+                     : "memory");
+    }
+}
+
 }  // namespace xn
