@@ -58,6 +58,15 @@ WORKLOADS = {
 }
 
 
+def host_threads():
+    """Threads the CPU legs use: every core this process may run on.  (The launcher of multi-rank
+    runs exports OMP_NUM_THREADS=1, which must not shrink the CPU baseline to one thread.)"""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def algorithmic_bytes_per_layer(lens, Hq, Hkv, D):
     return int(sum(2 * Hkv * int(L) * D * 4 + 4 * Hkv * D * 4 + 2 * Hq * D * 4 for L in lens))
 
@@ -149,7 +158,7 @@ def cpu_sample(lens, Hq, Hkv, D, kv_by_stream, q, k, v, layer, budget_s=12.0, ma
     import oracle as xo
 
     n = len(lens)
-    threads = xo.max_threads()
+    threads = host_threads()
     cap = int(max(lens))
     caches = []
     for i in range(n):
@@ -183,7 +192,7 @@ def run_reference_arm(args):
     sample = min(args.cpu_streams, n_streams)
     lens = lens_all[:sample]
     rng = np.random.default_rng(BASE_SEED + 3000 + 1)
-    threads = xo.max_threads()
+    threads = host_threads()
     cap = int(max(lens))
     caches, qs, ks, vs = [], [], [], []
     for L in lens:
