@@ -91,6 +91,16 @@ __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, int la
     return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
+// True in exactly one lane of the (converged) warp.  Unlike `lane == 0`, the election tells the
+// compiler that a single thread runs the guarded code.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
+}
+
 __device__ __forceinline__ void fence_generic_to_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
@@ -107,6 +117,12 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 }
 }  // namespace tg
 
+// The thread of the MMA warp that issues tcgen05.mma and tcgen05.commit (a commit tracks the MMAs
+// of the thread that executes it, so every site must pick the same thread; the election is
+// deterministic for a given member mask).
+#ifndef XN_TG_ISSUER
+#define XN_TG_ISSUER tg::elect_one()
+#endif
 #ifdef XN_TG_TIMING
 // tuning build: cycle stamps of block 0, stored as they happen, printed by the block at its end
 __device__ long long g_tg_dbg[256];
@@ -235,7 +251,7 @@ ternary_gemm_tc_kernel(const TernaryGemmArgs a) {
             if (lane == 0) TGD(96 + p);
             ok = warp_wait(&piece_full[p], 0, lane);
             if (!ok || *abort_flag) { ok = false; break; }
-            if (lane == 0) {
+            if (XN_TG_ISSUER) {
                 TGD(48 + p);
                 pf::fence_after_sync();
                 const int kbs = min(kPieceKb, nkb - p * kPieceKb);
@@ -264,7 +280,7 @@ ternary_gemm_tc_kernel(const TernaryGemmArgs a) {
             st ^= 1;
             __syncwarp();
         }
-        if (lane == 0) {
+        if (XN_TG_ISSUER) {
             if (ok) {
                 pf::mma_commit(acc_full);
             } else {
@@ -507,7 +523,7 @@ ternary_gemm_rows_kernel(const TernaryGemmArgs a) {
                 if (tile_idx == 0) ok = warp_wait(&w_full[p], 0, lane);
                 ok = ok && warp_wait(&act_full[st], par, lane);
                 if (!ok || *abort_flag) { ok = false; break; }
-                if (lane == 0) {
+                if (XN_TG_ISSUER) {
                     pf::fence_after_sync();
                     const int kbs = min(kPieceKb, nkb - p * kPieceKb);
                     const uint64_t adesc = adesc0 + uint64_t(st * (kActStage >> 4));
@@ -525,7 +541,7 @@ ternary_gemm_rows_kernel(const TernaryGemmArgs a) {
                 st ^= 1;
                 __syncwarp();
             }
-            if (ok && lane == 0) pf::mma_commit(&acc_full[b]);
+            if (ok && XN_TG_ISSUER) pf::mma_commit(&acc_full[b]);
             __syncwarp();
         }
         if (!ok && lane == 0) {
