@@ -29,6 +29,38 @@ extern "C" {
     fn xn_kv_read_range(c: *mut XnCtx, s: *mut XnStream, layer: i32, t0: i64, n: i64,
                         k: *mut f32, v: *mut f32) -> i32;
     fn xn_last_error(c: *mut XnCtx) -> *const c_char;
+    // the projections around the attention (models/llama/attention.rs:52-89 and :103-108)
+    fn xn_qkv_proj_set(c: *mut XnCtx, d: *const XnQkvProjDesc) -> i32;
+    fn xn_out_proj_set(c: *mut XnCtx, d: *const XnOutProjDesc) -> i32;
+    fn xn_attention_batch(c: *mut XnCtx, n: i32, reqs: *const XnReq) -> i32;
+}
+
+/// Request flags of `xn_req.flags` (include/xn_attn.h).
+pub const XN_REQ_OUT_PROJ: u32 = 1 << 4;
+pub const XN_REQ_QKV_PROJ: u32 = 1 << 5;
+
+#[repr(C)]
+pub struct XnReq {
+    pub stream: *mut XnStream, pub layer: i32, pub seq_len: i32, pub index_pos: i64,
+    pub q: *const f32, pub k: *const f32, pub v: *const f32, pub out: *mut f32,
+    pub flags: u32, pub reserved: u32,
+}
+
+/// `xn_qkv_proj_desc`: the dense `TernaryLinear`s q_proj / k_proj / v_proj of one layer.
+#[repr(C)]
+pub struct XnQkvProjDesc {
+    pub layer: i32, pub in_dim: i32, pub pack_type: i32, pub reserved: i32,
+    pub q_packed: *const u8, pub q_scales: *const f32,
+    pub k_packed: *const u8, pub k_scales: *const f32,
+    pub v_packed: *const u8, pub v_scales: *const f32,
+}
+
+/// `xn_out_proj_desc`: o_proj (dense `TernaryLinear`) and the optional sub-norm of one layer.
+#[repr(C)]
+pub struct XnOutProjDesc {
+    pub layer: i32, pub in_dim: i32, pub out_dim: i32, pub pack_type: i32,
+    pub packed: *const u8, pub w_scales: *const f32, pub norm_weight: *const f32,
+    pub norm_eps: f32, pub reserved: u32,
 }
 
 /// The tensor type of the reference (src/tensor.rs:6-10), re-declared so the crate stands alone;
