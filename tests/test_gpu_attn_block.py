@@ -164,3 +164,56 @@ def test_errors():
         ctx.set_qkv_proj(0, lin(32, 24), lin(16, 20), lin(16, 24))
     assert st.length(0) == 0
     ctx.close()
+
+
+def test_mixed_batch_of_projected_and_plain_requests():
+    # one submission: whole block on layer 0, plain attention on layer 1, projections only on layer 2,
+    # whole block on layer 0 again (a second run of rows for the same layer, not adjacent)
+    rng = np.random.default_rng(12)
+    Hq, Hkv, D, hidden, out_dim = 4, 2, 32, 96, 48
+    cos, sin = xn.rope_tables(10000.0, D, 256)
+    ctx = xn.Context(3, Hq, Hkv, D, pool_pages=16, rope=(cos, sin), prefill_mode=1)
+    mk = lambda o, i, s=None: (xn.TernaryLinear(i, o, w := rng.standard_normal((o, i)).astype(np.float32), xn.PACK4, s),
+                               xo.TernaryLinear(i, o, w, xo.PACK4, s))
+    lin = {}
+    for layer in (0, 2):
+        q, k, v = mk(Hq * D, hidden, hidden ** -0.5), mk(Hkv * D, hidden, hidden ** -0.5), mk(Hkv * D, hidden, hidden ** -0.5)
+        ctx.set_qkv_proj(layer, q[0], k[0], v[0])
+        lin[layer] = (q[1], k[1], v[1])
+    o_dev, o_ref = mk(out_dim, Hq * D)
+    nw = (1.0 + 0.1 * rng.standard_normal(Hq * D)).astype(np.float32)
+    ctx.set_out_proj(0, o_dev, nw, 1e-5)
+    sts = [ctx.new_stream(128) for _ in range(4)]
+    caches = [xo.RingCache(3, Hkv, 128, D) for _ in range(4)]
+    S = [5, 3, 1, 7]
+    x0 = rng.standard_normal((1, S[0], hidden)).astype(np.float32)
+    q1, k1, v1 = (rng.standard_normal((1, S[1], h * D)).astype(np.float32) for h in (Hq, Hkv, Hkv))
+    x2 = rng.standard_normal((1, S[2], hidden)).astype(np.float32)
+    x3 = rng.standard_normal((1, S[3], hidden)).astype(np.float32)
+    outs = [np.empty((1, S[0], out_dim), np.float32), np.empty((1, S[1], Hq * D), np.float32),
+            np.empty((1, S[2], Hq * D), np.float32), np.empty((1, S[3], out_dim), np.float32)]
+    p = lambda a: a.ctypes.data
+    reqs = ctx.make_batch([(sts[0], 0, 0, S[0], p(x0), None, None, p(outs[0])),
+                           (sts[1], 1, 0, S[1], p(q1), p(k1), p(v1), p(outs[1])),
+                           (sts[2], 2, 0, S[2], p(x2), None, None, p(outs[2])),
+                           (sts[3], 0, 0, S[3], p(x3), None, None, p(outs[3]))], 0)
+    reqs[0].flags = xn.REQ_QKV_PROJ | xn.REQ_OUT_PROJ
+    reqs[1].flags = xn.REQ_SEQ_MAJOR
+    reqs[2].flags = xn.REQ_QKV_PROJ
+    reqs[3].flags = xn.REQ_QKV_PROJ | xn.REQ_OUT_PROJ
+    ctx.submit(reqs)
+    for i, x in ((0, x0), (3, x3)):
+        y_ref, _ = xo.causal_self_attention_forward(x, 0, 0, caches[i], cos, sin, *lin[0], Hq, Hkv, D, nw, 1e-5, o_ref)
+        # rows of only 128 activations: one i8 step of one activation weighs ten times more than in
+        # the 2560-wide rows the 1e-3 bound is stated for
+        assert errs(outs[i], y_ref)[1] <= 1e-2, f"request {i}"
+    want1 = xo.fast_attention(xo.transpose_seq_to_heads(q1, Hq, D), xo.transpose_seq_to_heads(k1, Hkv, D),
+                              xo.transpose_seq_to_heads(v1, Hkv, D), 1, 0, caches[1], Hq, Hkv, D)
+    assert_parity(outs[1], xo.transpose_heads_to_seq(want1), "plain request")
+    none_lin = xo.TernaryLinear(Hq * D, 1, np.zeros((1, Hq * D), np.float32))
+    _, attn2 = xo.causal_self_attention_forward(x2, 0, 2, caches[2], cos, sin, *lin[2], Hq, Hkv, D, None, 0.0, none_lin)
+    assert np.array_equal(outs[2], xo.transpose_heads_to_seq(attn2))      # one token at position 0: exact
+    for i, layer in ((0, 0), (1, 1), (2, 2), (3, 0)):
+        k, v = sts[i].read_range(layer, 0, 128)
+        assert np.array_equal(k.ravel(), caches[i].k_buffer(layer)) and np.array_equal(v.ravel(), caches[i].v_buffer(layer))
+    ctx.close()
