@@ -61,8 +61,16 @@ subnorm_quant_kernel(const OutRowDev* __restrict__ rows, const float* __restrict
     __shared__ float bc_s;
     // the projection kernel behind this one may start now: its prologue (fetching and decoding its
     // weights) does not depend on anything written here, and it waits before it reads the rows
+#ifdef XN_SQ_TIMING
+    __shared__ long long sq_marks[8];
+    const long long sq_t0 = clock64();
+#define SQM(i) do { if (threadIdx.x == 0) sq_marks[i] = clock64() - sq_t0; } while (0)
+#else
+#define SQM(i)
+#endif
     pdl_launch_dependents();
     pdl_wait();   // this kernel itself may have been set up while the attention kernel still ran
+    SQM(0);
     const int r = blockIdx.x;
     const float* src = rows[r].src;
     const int tid = threadIdx.x;
@@ -89,6 +97,7 @@ subnorm_quant_kernel(const OutRowDev* __restrict__ rows, const float* __restrict
         }
     }
     __syncthreads();
+    SQM(1);
     if (norm_w != nullptr) {
         if (tid < 32) {
             // the whole first warp runs the chain (same value in every lane: no divergence);
@@ -117,52 +126,66 @@ subnorm_quant_kernel(const OutRowDev* __restrict__ rows, const float* __restrict
             if (tid == 0) bc_s = __fdiv_rn(1.0f, rms);
         }
         __syncthreads();
-        const float inv_rms = bc_s;
-        for (int i = tid; i < in_dim; i += blockDim.x)
-            row_s[i] = __fmul_rn(__fmul_rn(row_s[i], inv_rms), nw_s[i]);
-        __syncthreads();
+        SQM(2);
     }
-    // each thread owns whole 16-element chunks from here on: the unit of the quantiser's rounding
-    // rule and of the swizzled global layout
-    const int n_chunks = q_stride >> 4;
+    // normalise (two rounded multiplies) and take max |x| in one pass; consecutive threads take
+    // consecutive groups of four elements, which keeps shared memory and the global stores dense
+    const float inv_rms = norm_w != nullptr ? bc_s : 1.0f;
+    const int n4 = in_dim >> 2;
     float m = 0.f;
-    for (int c = tid; c < n_chunks; c += blockDim.x) {
-        const int i0 = c << 4;
-        if (i0 + 16 <= in_dim) {
-#pragma unroll
-            for (int j = 0; j < 16; j += 4) {
-                const float4 v = *reinterpret_cast<const float4*>(row_s + i0 + j);
-                m = fmaxf(m, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
-            }
-        } else {
-            for (int i = i0; i < in_dim; ++i) m = fmaxf(m, fabsf(row_s[i]));
+    for (int g = tid; g < n4; g += blockDim.x) {
+        float4 v = *reinterpret_cast<const float4*>(row_s + 4 * g);
+        if (norm_w != nullptr) {
+            const float4 w = *reinterpret_cast<const float4*>(nw_s + 4 * g);
+            v.x = __fmul_rn(__fmul_rn(v.x, inv_rms), w.x);
+            v.y = __fmul_rn(__fmul_rn(v.y, inv_rms), w.y);
+            v.z = __fmul_rn(__fmul_rn(v.z, inv_rms), w.z);
+            v.w = __fmul_rn(__fmul_rn(v.w, inv_rms), w.w);
+            *reinterpret_cast<float4*>(row_s + 4 * g) = v;
         }
+        m = fmaxf(m, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
     }
+    for (int i = (n4 << 2) + tid; i < in_dim; i += blockDim.x) {
+        float v = row_s[i];
+        if (norm_w != nullptr) {
+            v = __fmul_rn(__fmul_rn(v, inv_rms), nw_s[i]);
+            row_s[i] = v;
+        }
+        m = fmaxf(m, fabsf(v));
+    }
+    SQM(3);
     for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
     if ((tid & 31) == 0) red_s[tid >> 5] = m;
     __syncthreads();
     m = red_s[0];
     for (int w = 1; w < int(blockDim.x >> 5); ++w) m = fmaxf(m, red_s[w]);
+    SQM(4);
     const float scale = m > 0.f ? __fdiv_rn(127.0f, m) : 1.0f;
     if (tid == 0) inv_scale_out[q_row0 + r] = m > 0.f ? __fdiv_rn(m, 127.0f) : 1.0f;
+    // whole 16-element chunks round to nearest even after clamping, the tail half away from zero
     const int simd_end = (in_dim / 16) * 16;
-    for (int c = tid; c < n_chunks; c += blockDim.x) {
-        const int i0 = c << 4;
-        uint32_t packed[4] = {0u, 0u, 0u, 0u};
+    for (int g = tid; g < (q_stride >> 2); g += blockDim.x) {
+        const int i0 = g << 2;
+        uint32_t packed = 0u;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
+        for (int j = 0; j < 4; ++j) {
             const int i = i0 + j;
             int v = 0;
             if (i < in_dim) {
-                const float s = __fmul_rn(row_s[i], scale);
-                if (i < simd_end) v = __float2int_rn(fmaxf(-127.0f, fminf(127.0f, s)));
-                else v = int(fmaxf(-127.0f, fminf(127.0f, roundf(s))));
+                const float sc = __fmul_rn(row_s[i], scale);
+                if (i < simd_end) v = __float2int_rn(fmaxf(-127.0f, fminf(127.0f, sc)));
+                else v = int(fmaxf(-127.0f, fminf(127.0f, roundf(sc))));
             }
-            packed[j >> 2] |= uint32_t(v & 0xff) << ((j & 3) * 8);
+            packed |= uint32_t(v & 0xff) << (j * 8);
         }
-        *reinterpret_cast<uint4*>(q_out + act_offset(q_row0 + r, i0, q_rows_pad)) =
-            make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        *reinterpret_cast<uint32_t*>(q_out + act_offset(q_row0 + r, i0, q_rows_pad)) = packed;
     }
+#ifdef XN_SQ_TIMING
+    __syncthreads();
+    if (threadIdx.x == 0 && blockIdx.x == 0)
+        printf("sq: after wait %lld, row staged %lld, chain done %lld, normalised %lld, max known %lld, end %lld\n",
+               sq_marks[0], sq_marks[1], sq_marks[2], sq_marks[3], sq_marks[4], clock64() - sq_t0);
+#endif
 }
 
 // ---- ternary projection: i8 activations x 2-bit weights -> f32 rows ---------------------------
