@@ -99,6 +99,7 @@ struct xn_ctx {
     int decode_chunks = 0;   // chunks the tile list is cut into (several per block)
     bool fuse_append = true; // decode batches: the attention kernel appends the new token itself
     bool fuse_pinned = true; // ... also when q,k,v live in page-locked host memory
+    size_t stage_direct_bytes = size_t(2) << 20;  // small staged calls: kernels use the pinned staging itself
     bool out_tc = true;      // output projection on the tensor cores (else the dp4a kernel)
     bool out_pdl = true;     // ... launched as a programmatic dependent of the quantiser kernel
     bool out_rows_kernel = true;  // ... and, for more than 128 rows, the many-row variant
@@ -581,6 +582,11 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
     }
     if (qkv_rows && (rc = grow_device(c, &c->qkv_seq, &c->qkv_seq_cap, qkv_rows * qkv_width)) != XN_OK) return rc;
     if (host_mode && (rc = grow_io(c, io_in + io_out)) != XN_OK) return rc;
+    // Small staged calls skip the two DMA copies: the library's page-locked staging buffer is
+    // device-accessible, so the kernels read the inputs from it and write the outputs into it
+    // over PCIe themselves; what remains is one plan upload, the launches and the wait.
+    const bool stage_direct = host_mode && !pinned && io_in + io_out <= c->stage_direct_bytes;
+    unsigned char* const io_base = stage_direct ? c->io_host : c->io_dev;
 
     // -- request descriptors, page ids, units
     std::vector<ReqDev> rd(n);
@@ -614,20 +620,20 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
             if (qkv) {
                 const size_t xf = size_t(S) * c->qkv_proj[size_t(r.layer)].in_dim;
                 memcpy(c->io_host + in_off, r.q, xf * 4);
-                q_dev = reinterpret_cast<const float*>(c->io_dev + in_off);   // x, for now
+                q_dev = reinterpret_cast<const float*>(io_base + in_off);   // x, for now
                 in_off += align_up(xf * 4, 16);
             } else {
                 memcpy(c->io_host + in_off, r.q, qf * 4);
-                q_dev = reinterpret_cast<const float*>(c->io_dev + in_off);
+                q_dev = reinterpret_cast<const float*>(io_base + in_off);
                 in_off += align_up(qf * 4, 16);
                 memcpy(c->io_host + in_off, r.k, kvf * 4);
-                k_dev = reinterpret_cast<const float*>(c->io_dev + in_off);
+                k_dev = reinterpret_cast<const float*>(io_base + in_off);
                 in_off += align_up(kvf * 4, 16);
                 memcpy(c->io_host + in_off, r.v, kvf * 4);
-                v_dev = reinterpret_cast<const float*>(c->io_dev + in_off);
+                v_dev = reinterpret_cast<const float*>(io_base + in_off);
                 in_off += align_up(kvf * 4, 16);
             }
-            o_dev = reinterpret_cast<float*>(c->io_dev + out_off);
+            o_dev = reinterpret_cast<float*>(io_base + out_off);
             out_off += align_up(((r.flags & XN_REQ_OUT_PROJ)
                                      ? size_t(S) * c->out_proj[size_t(r.layer)].out_dim : qf) * 4, 16);
         }
@@ -758,7 +764,8 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
     const int* ring_d = reinterpret_cast<const int*>(slot->dev + o_ring);
 
     if (host_mode && !pinned && io_in) {
-        XN_CUDA(c, cudaMemcpyAsync(c->io_dev, c->io_host, io_in, cudaMemcpyHostToDevice, c->stream));
+        if (!stage_direct)
+            XN_CUDA(c, cudaMemcpyAsync(c->io_dev, c->io_host, io_in, cudaMemcpyHostToDevice, c->stream));
         c->stats.h2d_bytes += io_in;
     }
 
@@ -861,8 +868,9 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
 
     if (host_mode) {
         if (io_out) {
-            XN_CUDA(c, cudaMemcpyAsync(c->io_host + io_in, c->io_dev + io_in, io_out,
-                                       cudaMemcpyDeviceToHost, c->stream));
+            if (!stage_direct)
+                XN_CUDA(c, cudaMemcpyAsync(c->io_host + io_in, c->io_dev + io_in, io_out,
+                                           cudaMemcpyDeviceToHost, c->stream));
             c->stats.d2h_bytes += io_out;
         }
     }
@@ -1023,6 +1031,7 @@ int32_t xn_ctx_create(const xn_ctx_desc* d, xn_ctx** out_ctx) {
     c->decode_chunks = c->decode_ctas * chunks_per_cta;
     if (const char* env = getenv("XORNET_ATTN_FUSE_APPEND")) c->fuse_append = atoi(env) != 0;
     if (const char* env = getenv("XORNET_ATTN_FUSE_PINNED")) c->fuse_pinned = atoi(env) != 0;
+    if (const char* env = getenv("XORNET_ATTN_STAGE_DIRECT_BYTES")) c->stage_direct_bytes = size_t(atoll(env));
     if (const char* env = getenv("XORNET_ATTN_OUTPROJ_TC")) c->out_tc = atoi(env) != 0;
     if (const char* env = getenv("XORNET_ATTN_OUTPROJ_PDL")) c->out_pdl = atoi(env) != 0;
     if (const char* env = getenv("XORNET_ATTN_OUTPROJ_ROWS")) c->out_rows_kernel = atoi(env) != 0;
