@@ -261,20 +261,25 @@ XN_API int64_t xn_stream_pages(xn_ctx* ctx, xn_stream* stream, int32_t* out, int
 /* Packing of ternary weights, TernaryPackType (src/bit1_58/quantization.rs:1-5). */
 enum {
     XN_PACK4 = 4, /* four 2-bit codes per byte  (pack_1_58bit_4pack, quantization.rs:7-27)        */
-    XN_PACK5 = 5  /* five base-3 digits per byte (pack_1_58bit_5pack, quantization.rs:49-72)      */
+    XN_PACK5 = 5, /* five base-3 digits per byte (pack_1_58bit_5pack, quantization.rs:49-72)      */
+    XN_SPARSE = 64 /* the XorSparse blob of TernaryRep::Sparse (src/bit1_58/sparse.rs:9-17): rows   */
+                   /* back to back, each u32 num_blocks + per 64-element block {u64 mask of the    */
+                   /* non-zero positions, ceil(popcount/8) bytes of sign bits}.  Lossless, so the  */
+                   /* results equal the dense representation's                                    */
 };
 
 /* The tensors CausalSelfAttention holds for the tail of its forward pass
  * (src/models/llama/attention.rs:38-40, loaded at :147-163): the o_proj TernaryLinear in its
- * dense representation (src/bit1_58/layers.rs:34-41: packed rows + per-row scales) and the optional
- * inner_attn_ln / attn_sub_norm FastRmsNorm (src/nn/fast_rmsnorm.rs:5-17).  The sparse
- * representation (TernaryRep::Sparse) is not taken. */
+ * dense (src/bit1_58/layers.rs:34-41: packed rows + per-row scales) or sparse (XN_SPARSE: the blob of
+ * SparseTernary) representation and the optional inner_attn_ln / attn_sub_norm FastRmsNorm
+ * (src/nn/fast_rmsnorm.rs:5-17). */
 typedef struct xn_out_proj_desc {
     int32_t layer;
     int32_t in_dim;           /* must equal num_heads * head_dim                                  */
     int32_t out_dim;
     int32_t pack_type;        /* XN_PACK4 or XN_PACK5                                             */
-    const uint8_t* packed;    /* host: out_dim rows of ceil(in_dim/4) or ceil(in_dim/5) bytes     */
+    const uint8_t* packed;    /* host: out_dim rows of ceil(in_dim/4) or ceil(in_dim/5) bytes, or */
+                              /*       the XorSparse blob of out_dim rows                         */
     const float* w_scales;    /* host: [out_dim]                                                  */
     const float* norm_weight; /* host: [in_dim], or NULL when the model has no sub-norm           */
     float norm_eps;
@@ -287,7 +292,7 @@ typedef struct xn_out_proj_desc {
 typedef struct xn_qkv_proj_desc {
     int32_t layer;
     int32_t in_dim;
-    int32_t pack_type;        /* XN_PACK4 or XN_PACK5, the same for the three                     */
+    int32_t pack_type;        /* XN_PACK4, XN_PACK5 or XN_SPARSE, the same for the three          */
     int32_t reserved;
     const uint8_t* q_packed;
     const float* q_scales;
@@ -323,6 +328,14 @@ XN_API int32_t xn_out_proj(xn_ctx* ctx, int32_t layer, int32_t rows, const float
 XN_API int32_t xn_ternary_pack(int32_t in_dim, int32_t out_dim, const float* weights,
                                int32_t pack_type, float provided_scale, uint8_t* packed,
                                float* w_scales);
+
+/* TernaryLinear::new_sparse (src/bit1_58/layers.rs:151-181), on the host: ternarises `weights`
+ * [out_dim, in_dim] like xn_ternary_pack and encodes the rows as an XorSparse blob.  blob_cap is the
+ * capacity of `blob` (out_dim * (4 + ceil(in_dim/64) * 16) bytes always suffice); *blob_len
+ * receives the bytes written.  Returns XN_ERR_CAPACITY when the blob does not fit.  No GPU needed. */
+XN_API int32_t xn_ternary_pack_sparse(int32_t in_dim, int32_t out_dim, const float* weights,
+                                      float provided_scale, uint8_t* blob, int64_t blob_cap,
+                                      int64_t* blob_len, float* w_scales);
 
 /* ---- host-side planning, exposed for tests (no GPU needed) ----------------------------------- */
 

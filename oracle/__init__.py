@@ -27,7 +27,7 @@ _i8p = C.POINTER(C.c_int8)
 _u8p = C.POINTER(C.c_uint8)
 _sz = C.c_size_t
 
-PACK4, PACK5 = 4, 5
+PACK4, PACK5, SPARSE = 4, 5, 64
 
 
 def build(force: bool = False) -> str:
@@ -106,6 +106,14 @@ def lib() -> C.CDLL:
             getattr(L, name).restype = C.c_int32
         L.xo_ternary_linear_pack.argtypes = [_sz, _sz, _f32p, C.c_int, C.c_float, _u8p, _f32p]
         L.xo_ternary_linear_pack.restype = None
+        L.xo_sparse_encode_row.argtypes = [_i8p, _sz, _u8p]
+        L.xo_sparse_encode_row.restype = _sz
+        L.xo_sparse_decode_row.argtypes = [_u8p, _sz, _i8p]
+        L.xo_sparse_decode_row.restype = _sz
+        L.xo_ternary_dot_sparse.argtypes = [_i8p, _u8p, _sz]
+        L.xo_ternary_dot_sparse.restype = C.c_int32
+        L.xo_ternary_linear_pack_sparse.argtypes = [_sz, _sz, _f32p, C.c_float, _u8p, _f32p]
+        L.xo_ternary_linear_pack_sparse.restype = _sz
         L.xo_ternary_linear_forward.argtypes = [_f32p, _sz, _sz, _sz, C.c_int, _u8p, _f32p, _f32p,
                                                 C.c_int]
         L.xo_ternary_linear_forward.restype = None
@@ -336,13 +344,56 @@ def ternary_dot(acts_i8, packed, n, pack_type=PACK4) -> int:
     return int(fn(a.ctypes.data_as(_i8p), packed.ctypes.data_as(_u8p), n))
 
 
+def sparse_encode_row(vals_i8, in_dim) -> np.ndarray:
+    """encode_sparse_row_into (bit1_58/sparse.rs:62-89)."""
+    v = np.ascontiguousarray(vals_i8, dtype=np.int8)
+    out = np.zeros(4 + ((in_dim + 63) // 64) * 16, dtype=np.uint8)
+    n = lib().xo_sparse_encode_row(v.ctypes.data_as(_i8p), in_dim, out.ctypes.data_as(_u8p))
+    return out[:n].copy()
+
+
+def sparse_decode_row(row_bytes, in_dim):
+    """SparseTernary::decode_row (bit1_58/sparse.rs:206-249) -> (i8 values, bytes of the row)."""
+    row = np.ascontiguousarray(row_bytes, dtype=np.uint8)
+    out = np.zeros(in_dim, dtype=np.int8)
+    n = lib().xo_sparse_decode_row(row.ctypes.data_as(_u8p), in_dim, out.ctypes.data_as(_i8p))
+    return out, int(n)
+
+
+def ternary_dot_sparse(acts_i8, row_bytes, in_dim) -> int:
+    a = np.ascontiguousarray(acts_i8, dtype=np.int8)
+    row = np.ascontiguousarray(row_bytes, dtype=np.uint8)
+    return int(lib().xo_ternary_dot_sparse(a.ctypes.data_as(_i8p), row.ctypes.data_as(_u8p), in_dim))
+
+
 class TernaryLinear:
-    """TernaryLinear with the dense packed representation (bit1_58/layers.rs:34-149, 262-313)."""
+    """TernaryLinear (bit1_58/layers.rs:34-313) with the dense packed representation, or with
+    ``pack_type=SPARSE`` the XorSparse one of ``new_sparse`` (:151-181): ``packed`` is then the blob
+    and the forward pass runs over the rows decoded from it (the format is lossless)."""
 
     def __init__(self, in_dim, out_dim, weights_f32, pack_type=PACK4, provided_scale=None):
         w = _f32(weights_f32).ravel()
         if w.size != in_dim * out_dim:
             raise ValueError("Weight length must match in_dim * out_dim")
+        if pack_type == SPARSE:
+            self.in_dim, self.out_dim, self.pack_type = in_dim, out_dim, SPARSE
+            blob = np.zeros(out_dim * (4 + ((in_dim + 63) // 64) * 16) + 16, dtype=np.uint8)
+            self.w_scales = np.zeros(out_dim, dtype=np.float32)
+            n = lib().xo_ternary_linear_pack_sparse(in_dim, out_dim, _p(w),
+                                                    float("nan") if provided_scale is None else provided_scale,
+                                                    blob.ctypes.data_as(_u8p), _p(self.w_scales))
+            self.packed = blob[:n].copy()
+            rows, off = [], 0
+            for _ in range(out_dim):
+                vals, used = sparse_decode_row(self.packed[off:], in_dim)
+                rows.append(vals.astype(np.float32))
+                off += used
+            assert off == self.packed.size
+            # the dense twin the forward pass uses: exactly the decoded rows, original scales
+            self._dense = TernaryLinear(in_dim, out_dim, np.stack(rows) if rows else np.zeros((0, in_dim)), PACK4, 1.0)
+            self._dense.w_scales = self.w_scales
+            self.row_bytes = 0
+            return
         self.in_dim, self.out_dim, self.pack_type = in_dim, out_dim, pack_type
         self.row_bytes = int(lib().xo_packed_row_bytes(in_dim, pack_type))
         self.packed = np.zeros(out_dim * self.row_bytes, dtype=np.uint8)
@@ -352,6 +403,8 @@ class TernaryLinear:
                                      self.packed.ctypes.data_as(_u8p), _p(self.w_scales))
 
     def forward(self, x, threads: int = 0) -> np.ndarray:
+        if self.pack_type == SPARSE:
+            return self._dense.forward(x, threads)
         x = _f32(x)
         if x.ndim == 0:
             raise ValueError("Input must have at least 1 dimension")

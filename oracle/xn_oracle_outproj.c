@@ -286,3 +286,114 @@ XO_API void xo_attention_out_block(const float* y_heads, size_t num_heads, size_
     xo_ternary_linear_forward(seq, seq_len, hidden, out_dim, pack_type, packed, w_scales, out, threads);
     free(seq);
 }
+
+/* ------------------------------------------------------------------------- */
+/* XorSparse rows  (src/bit1_58/sparse.rs)                                     */
+/* ------------------------------------------------------------------------- */
+
+/* ternarize_row (src/bit1_58/layers.rs:45-88) for one weight.  (A non-positive scale maps to 0
+ * here as in the dense packers, quantization.rs:12.) */
+static int ternary_value(float w, float w_scale, int already_ternary) {
+    if (already_ternary) return (int)w;
+    return (int)ternary_code(w, w_scale) - 1;
+}
+
+/* encode_sparse_row_into (sparse.rs:62-89): u32 num_blocks, then per 64-element block the u64
+ * mask of non-zero positions and ceil(nnz/8) bytes of sign bits in scan order (bit set = -1).
+ * Returns the bytes written (the caller provides 4 + ceil(in_dim/64)*16 bytes). */
+XO_API size_t xo_sparse_encode_row(const int8_t* vals, size_t in_dim, uint8_t* out) {
+    const uint32_t num_blocks = (uint32_t)((in_dim + 63) / 64);
+    size_t p = 0;
+    for (int i = 0; i < 4; ++i) out[p++] = (uint8_t)(num_blocks >> (8 * i));
+    for (uint32_t b = 0; b < num_blocks; ++b) {
+        const size_t start = (size_t)b * 64, end = start + 64 < in_dim ? start + 64 : in_dim;
+        uint64_t mask = 0, signs = 0;
+        unsigned si = 0;
+        for (size_t i = start; i < end; ++i)
+            if (vals[i] != 0) {
+                mask |= (uint64_t)1 << (i - start);
+                if (vals[i] < 0) signs |= (uint64_t)1 << si;
+                ++si;
+            }
+        for (int i = 0; i < 8; ++i) out[p++] = (uint8_t)(mask >> (8 * i));
+        for (unsigned i = 0; i < (si + 7) / 8; ++i) out[p++] = (uint8_t)(signs >> (8 * i));
+    }
+    return p;
+}
+
+/* SparseTernary::decode_row (sparse.rs:206-249).  Returns the bytes of the row. */
+XO_API size_t xo_sparse_decode_row(const uint8_t* row, size_t in_dim, int8_t* out) {
+    const uint32_t num_blocks = (uint32_t)row[0] | (uint32_t)row[1] << 8 | (uint32_t)row[2] << 16 |
+                                (uint32_t)row[3] << 24;
+    size_t p = 4;
+    memset(out, 0, in_dim);
+    for (uint32_t b = 0; b < num_blocks; ++b) {
+        const size_t start = (size_t)b * 64, end = start + 64 < in_dim ? start + 64 : in_dim;
+        uint64_t mask = 0, sb = 0;
+        for (int i = 0; i < 8; ++i) mask |= (uint64_t)row[p + i] << (8 * i);
+        p += 8;
+        const unsigned nnz = (unsigned)__builtin_popcountll(mask);
+        for (unsigned k = 0; k < (nnz + 7) / 8; ++k) sb |= (uint64_t)row[p + k] << (8 * k);
+        p += (nnz + 7) / 8;
+        unsigned si = 0;
+        for (size_t i = start; i < end; ++i)
+            if ((mask >> (i - start)) & 1) {
+                out[i] = ((sb >> si) & 1) ? -1 : 1;
+                ++si;
+            }
+    }
+    return p;
+}
+
+/* ternary_dot_product_sparse_scalar over one row of the blob (src/bit1_58/simd.rs:425-461, with the
+ * lane-order sign expansion of SparseTernary::from_blob, sparse.rs:160-177, folded in). */
+XO_API int32_t xo_ternary_dot_sparse(const int8_t* a, const uint8_t* row, size_t in_dim) {
+    const uint32_t num_blocks = (uint32_t)row[0] | (uint32_t)row[1] << 8 | (uint32_t)row[2] << 16 |
+                                (uint32_t)row[3] << 24;
+    size_t p = 4;
+    int32_t total = 0;
+    for (uint32_t b = 0; b < num_blocks; ++b) {
+        uint64_t mask = 0, sb = 0;
+        for (int i = 0; i < 8; ++i) mask |= (uint64_t)row[p + i] << (8 * i);
+        p += 8;
+        const unsigned nnz = (unsigned)__builtin_popcountll(mask);
+        for (unsigned k = 0; k < (nnz + 7) / 8; ++k) sb |= (uint64_t)row[p + k] << (8 * k);
+        p += (nnz + 7) / 8;
+        unsigned si = 0;
+        for (unsigned lane = 0; lane < 64 && (size_t)b * 64 + lane < in_dim; ++lane)
+            if ((mask >> lane) & 1) {
+                total += (int32_t)a[(size_t)b * 64 + lane] * (((sb >> si) & 1) ? -1 : 1);
+                ++si;
+            }
+    }
+    return total;
+}
+
+/* TernaryLinear::new_sparse (src/bit1_58/layers.rs:151-181): ternarise each row like the dense
+ * constructor and encode it.  blob must hold out_dim * (4 + ceil(in_dim/64)*16) bytes; returns the
+ * bytes used. */
+XO_API size_t xo_ternary_linear_pack_sparse(size_t in_dim, size_t out_dim, const float* weights,
+                                            float provided_scale, uint8_t* blob, float* w_scales) {
+    int already = 1;
+    for (size_t i = 0; i < in_dim * out_dim; ++i)
+        if (!(weights[i] == -1.0f || weights[i] == 0.0f || weights[i] == 1.0f)) { already = 0; break; }
+    const int has_scale = !isnan(provided_scale);
+    int8_t* vals = (int8_t*)malloc(in_dim + 1);
+    size_t p = 0;
+    for (size_t o = 0; o < out_dim; ++o) {
+        const float* row = weights + o * in_dim;
+        float s;
+        if (already) s = has_scale ? provided_scale : 1.0f;
+        else if (has_scale) s = provided_scale;
+        else {
+            float sum_abs = 0.0f;
+            for (size_t i = 0; i < in_dim; ++i) sum_abs += fabsf(row[i]);
+            s = in_dim == 0 ? 1.0f : sum_abs / (float)in_dim;
+        }
+        w_scales[o] = s;
+        for (size_t i = 0; i < in_dim; ++i) vals[i] = (int8_t)ternary_value(row[i], s, already);
+        p += xo_sparse_encode_row(vals, in_dim, blob + p);
+    }
+    free(vals);
+    return p;
+}

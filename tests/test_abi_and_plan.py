@@ -137,3 +137,18 @@ def test_ternary_pack_matches_the_oracle_packer():
                 assert np.array_equal(a.w_scales, b.w_scales)
     with pytest.raises(ValueError):
         TernaryLinear(4, 2, np.zeros(7, np.float32))
+
+
+def test_sparse_pack_matches_the_oracle_encoder():
+    # xn_ternary_pack_sparse is host-only (TernaryLinear::new_sparse): no GPU needed
+    import oracle as xo
+    from xor_net_b200.api import TernaryLinear
+
+    rng = np.random.default_rng(4)
+    for in_dim, out_dim in ((1, 1), (7, 3), (64, 5), (65, 2), (2560, 3)):
+        w = rng.standard_normal((out_dim, in_dim)).astype(np.float32)
+        tern = rng.integers(-1, 2, (out_dim, in_dim)).astype(np.float32)
+        for weights, scale in ((w, None), (w, 0.7), (tern, None)):
+            a = xo.TernaryLinear(in_dim, out_dim, weights, xo.SPARSE, scale)
+            b = TernaryLinear(in_dim, out_dim, weights, xn.SPARSE, scale)
+            assert np.array_equal(a.packed, b.packed) and np.array_equal(a.w_scales, b.w_scales)

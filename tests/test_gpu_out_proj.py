@@ -81,6 +81,33 @@ def test_tensor_core_and_cuda_core_projections_agree(rows, monkeypatch):
     assert np.array_equal(outs[0], ref_block(ref, nw, 1e-5, y))
 
 
+def test_sparse_representation_gives_the_dense_results():
+    # XN_SPARSE: the XorSparse blob of TernaryRep::Sparse is decoded on upload; lossless, so the
+    # projected rows equal the pack4 layer's bit for bit (and the oracle's)
+    rng = np.random.default_rng(77)
+    Hq, D, out_dim, rows = 20, 128, 200, 70
+    w = rng.standard_normal((out_dim, Hq * D)).astype(np.float32)
+    nw = (1.0 + 0.2 * rng.standard_normal(Hq * D)).astype(np.float32)
+    y = rng.standard_normal((rows, Hq * D)).astype(np.float32)
+    outs = []
+    for pack in (xn.SPARSE, xn.PACK4):
+        ctx = xn.Context(1, Hq, 1, D, pool_pages=1)
+        ctx.set_out_proj(0, xn.TernaryLinear(Hq * D, out_dim, w, pack), nw, 1e-5)
+        outs.append(ctx.out_proj(0, y))
+        ctx.close()
+    assert np.array_equal(outs[0], outs[1])
+    ref = xo.TernaryLinear(Hq * D, out_dim, w, xo.SPARSE)
+    assert np.array_equal(outs[0], ref.forward(xo.tensor_rmsnorm(y, nw, 1e-5)))
+    # a blob whose rows describe another width is refused
+    ctx = xn.Context(1, Hq, 1, D, pool_pages=1)
+    bad = xn.TernaryLinear(Hq * D, out_dim, w, xn.SPARSE)
+    bad.packed = xn.TernaryLinear(64, out_dim, w[:, :64].copy(), xn.SPARSE).packed
+    with pytest.raises(xn.XnError) as e:
+        ctx.set_out_proj(0, bad, nw, 1e-5)
+    assert e.value.code == 2
+    ctx.close()
+
+
 def test_rounding_ties_follow_the_avx512_body():
     # rows whose scale is exactly 1 (max |x| = 127) with values on .5: whole chunks round to even,
     # the tail rounds half away from zero; an all-zero row has scale 1 and gives zeros

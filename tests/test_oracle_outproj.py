@@ -197,3 +197,46 @@ def test_out_block_equals_its_parts(pack):
     assert lin.w_scales.shape == (out_dim,) and np.all(lin.w_scales > 0)
     # no sub-norm: projection of the transposed tensor
     assert np.array_equal(xo.attention_out_block(y, None, 1e-5, lin), lin.forward(seq))
+
+
+# ---- XorSparse rows (src/bit1_58/sparse.rs) -----------------------------------------------------
+
+def test_sparse_row_layout_literal():
+    # sparse.rs:9-17: u32 num_blocks, then per 64-element block the u64 mask of the non-zero positions
+    # and ceil(nnz/8) bytes of sign bits in scan order (bit set = -1), all little-endian
+    vals = np.zeros(70, np.int8)
+    vals[[0, 3, 63]] = [1, -1, -1]       # block 0: mask bits 0,3,63; signs (scan order) 0,1,1 -> 0b110
+    vals[[64, 69]] = [-1, 1]             # block 1: mask bits 0,5; signs 1,0 -> 0b01
+    row = xo.sparse_encode_row(vals, 70)
+    want = [2, 0, 0, 0] + list((1 | 1 << 3 | 1 << 63).to_bytes(8, "little")) + [0b110] + \
+        list((1 | 1 << 5).to_bytes(8, "little")) + [0b01]
+    assert row.tolist() == want
+    back, used = xo.sparse_decode_row(row, 70)
+    assert used == row.size and np.array_equal(back, vals)
+
+
+def test_sparse_is_lossless_and_dots_match_dense():
+    rng = np.random.default_rng(17)
+    for n in (1, 5, 63, 64, 65, 128, 200, 2560):
+        vals = rng.integers(-1, 2, n).astype(np.int8)
+        row = xo.sparse_encode_row(vals, n)
+        back, used = xo.sparse_decode_row(row, n)
+        assert used == row.size and np.array_equal(back, vals)
+        acts = rng.integers(-127, 128, n).astype(np.int8)
+        want = int(np.dot(acts.astype(np.int64), vals.astype(np.int64)))
+        assert xo.ternary_dot_sparse(acts, row, n) == want
+        assert xo.ternary_dot(acts, xo.pack_ternary(vals.astype(np.float32), 1.0), n) == want
+    # all-zero and all-nonzero rows: 12 and 20 bytes per block
+    assert xo.sparse_encode_row(np.zeros(64, np.int8), 64).size == 4 + 8
+    assert xo.sparse_encode_row(np.ones(64, np.int8), 64).size == 4 + 8 + 8
+
+
+def test_sparse_linear_equals_dense_linear():
+    # TernaryLinear::new_sparse ternarises like ::new (layers.rs:151-181): same scales, same outputs
+    rng = np.random.default_rng(18)
+    for in_dim, out_dim, scale in ((48, 7, None), (130, 5, 0.4), (64, 3, None)):
+        w = rng.standard_normal((out_dim, in_dim)).astype(np.float32)
+        sp, de = xo.TernaryLinear(in_dim, out_dim, w, xo.SPARSE, scale), xo.TernaryLinear(in_dim, out_dim, w, xo.PACK4, scale)
+        assert np.array_equal(sp.w_scales, de.w_scales)
+        x = rng.standard_normal((4, in_dim)).astype(np.float32)
+        assert np.array_equal(sp.forward(x), de.forward(x))

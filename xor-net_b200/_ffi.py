@@ -50,7 +50,7 @@ class OutProjDesc(C.Structure):
 
 
 REQ_DEVICE_PTRS, REQ_ROPE, REQ_SEQ_MAJOR, REQ_HOST_PINNED, REQ_OUT_PROJ, REQ_QKV_PROJ = 1, 2, 4, 8, 16, 32
-PACK4, PACK5 = 4, 5
+PACK4, PACK5, SPARSE = 4, 5, 64
 
 STATUS_NAMES = {
     0: "XN_OK", 1: "XN_ERR_ARG", 2: "XN_ERR_SHAPE", 3: "XN_ERR_HANDLE", 4: "XN_ERR_OUT_OF_PAGES",
@@ -100,6 +100,8 @@ SIGNATURES = {
     "xn_out_proj": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_uint32]),
     "xn_ternary_pack": (C.c_int32, [C.c_int32, C.c_int32, C.c_void_p, C.c_int32, C.c_float,
                                     C.c_void_p, C.c_void_p]),
+    "xn_ternary_pack_sparse": (C.c_int32, [C.c_int32, C.c_int32, C.c_void_p, C.c_float, C.c_void_p,
+                                           C.c_int64, C.POINTER(C.c_int64), C.c_void_p]),
     "xn_version": (C.c_char_p, []),
 }
 

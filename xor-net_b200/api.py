@@ -21,7 +21,7 @@ from typing import Optional, Sequence
 import numpy as np
 
 from . import _ffi
-from ._ffi import (PACK4, PACK5, REQ_DEVICE_PTRS, REQ_HOST_PINNED, REQ_OUT_PROJ, REQ_QKV_PROJ, REQ_ROPE,
+from ._ffi import (PACK4, PACK5, SPARSE, REQ_DEVICE_PTRS, REQ_HOST_PINNED, REQ_OUT_PROJ, REQ_QKV_PROJ, REQ_ROPE,
                    REQ_SEQ_MAJOR, CtxDesc, OutProjDesc, QkvProjDesc, Req, Stats)
 
 
@@ -289,15 +289,24 @@ class TernaryLinear:
         w = _f32(weights_f32).ravel()
         if w.size != in_dim * out_dim:
             raise ValueError("Weight length must match in_dim * out_dim")
-        if pack_type not in (PACK4, PACK5):
-            raise ValueError("pack_type must be PACK4 or PACK5")
+        if pack_type not in (PACK4, PACK5, SPARSE):
+            raise ValueError("pack_type must be PACK4, PACK5 or SPARSE")
         self.in_dim, self.out_dim, self.pack_type = in_dim, out_dim, pack_type
-        self.row_bytes = (in_dim + 4) // 5 if pack_type == PACK5 else (in_dim + 3) // 4
-        self.packed = np.zeros(max(1, out_dim * self.row_bytes), dtype=np.uint8)
         self.w_scales = np.zeros(max(1, out_dim), dtype=np.float32)
-        rc = _ffi.load().xn_ternary_pack(in_dim, out_dim, _ptr(w), pack_type,
-                                         float("nan") if provided_scale is None else provided_scale,
-                                         self.packed.ctypes.data, _ptr(self.w_scales))
+        scale = float("nan") if provided_scale is None else provided_scale
+        if pack_type == SPARSE:   # TernaryLinear::new_sparse: the XorSparse blob, rows back to back
+            cap = out_dim * (4 + ((in_dim + 63) // 64) * 16) + 16
+            self.packed = np.zeros(cap, dtype=np.uint8)
+            n = C.c_int64(0)
+            rc = _ffi.load().xn_ternary_pack_sparse(in_dim, out_dim, _ptr(w), scale, self.packed.ctypes.data,
+                                                    cap, C.byref(n), _ptr(self.w_scales))
+            self.packed = self.packed[: n.value].copy()
+            self.row_bytes = 0
+        else:
+            self.row_bytes = (in_dim + 4) // 5 if pack_type == PACK5 else (in_dim + 3) // 4
+            self.packed = np.zeros(max(1, out_dim * self.row_bytes), dtype=np.uint8)
+            rc = _ffi.load().xn_ternary_pack(in_dim, out_dim, _ptr(w), pack_type, scale,
+                                             self.packed.ctypes.data, _ptr(self.w_scales))
         if rc != 0:
             raise XnError(rc, "xn_ternary_pack")
         self.w_scales = self.w_scales[:out_dim]

@@ -1511,8 +1511,8 @@ struct LinearPart {
 // (all with the same in_dim and packing) and stores it in *slot, replacing what was there.
 int32_t install_linear(xn_ctx* c, OutProj* slot, int in_dim, int pack_type, const LinearPart* parts,
                        int n_parts, const float* norm_weight, float norm_eps) {
-    if (pack_type != XN_PACK4 && pack_type != XN_PACK5)
-        return fail(c, XN_ERR_ARG, "pack_type must be XN_PACK4 or XN_PACK5");
+    if (pack_type != XN_PACK4 && pack_type != XN_PACK5 && pack_type != XN_SPARSE)
+        return fail(c, XN_ERR_ARG, "pack_type must be XN_PACK4, XN_PACK5 or XN_SPARSE");
     if (in_dim <= 0 || size_t(in_dim) * 12 > 200 * 1024)
         return fail(c, XN_ERR_CAPACITY, "in_dim %d outside what one block's shared memory holds", in_dim);
     long long out_dim = 0;
@@ -1531,7 +1531,7 @@ int32_t install_linear(xn_ctx* c, OutProj* slot, int in_dim, int pack_type, cons
     op.q_stride = int(align_up(size_t(in_dim), 128));
     op.w_stride = op.q_stride / 4;
     op.eps = norm_eps;
-    const size_t bpr = packed_row_bytes(size_t(in_dim), pack_type);
+    const size_t bpr = pack_type == XN_SPARSE ? 0 : packed_row_bytes(size_t(in_dim), pack_type);
     // device layout: [row / 32][K / 128][32 rows][32 bytes] (code_offset); rows past out_dim and
     // columns past in_dim hold code 1 = weight 0
     const int nkb = op.q_stride / 128;
@@ -1539,14 +1539,24 @@ int32_t install_linear(xn_ctx* c, OutProj* slot, int in_dim, int pack_type, cons
     std::vector<float> scales(size_t(out_dim), 0.f);
     std::vector<uint8_t> row_codes(size_t(op.w_stride));
     int o = 0;
-    for (int i = 0; i < n_parts; ++i)
+    for (int i = 0; i < n_parts; ++i) {
+        const uint8_t* sparse_row = parts[i].packed;   // XN_SPARSE: rows are found by walking the blob
         for (int rr = 0; rr < parts[i].rows; ++rr, ++o) {
-            recode_row_2bit(parts[i].packed + size_t(rr) * bpr, size_t(in_dim), pack_type, row_codes.data(),
-                            row_codes.size());
+            if (pack_type == XN_SPARSE) {
+                const size_t used = recode_sparse_row_2bit(sparse_row, size_t(in_dim), row_codes.data(),
+                                                           row_codes.size());
+                if (used == 0)
+                    return fail(c, XN_ERR_SHAPE, "sparse row %d does not describe %d columns", o, in_dim);
+                sparse_row += used;
+            } else {
+                recode_row_2bit(parts[i].packed + size_t(rr) * bpr, size_t(in_dim), pack_type, row_codes.data(),
+                                row_codes.size());
+            }
             for (int kb = 0; kb < nkb; ++kb)
                 memcpy(w2.data() + code_offset(o, kb * 128, nkb), row_codes.data() + size_t(kb) * 32, 32);
             scales[size_t(o)] = parts[i].scales[rr];
         }
+    }
     auto upload = [&](void** dst, const void* src, size_t bytes) -> cudaError_t {
         cudaError_t e = cudaMalloc(dst, bytes);
         if (e != cudaSuccess) return e;
@@ -1583,6 +1593,35 @@ int32_t install_linear(xn_ctx* c, OutProj* slot, int in_dim, int pack_type, cons
     return XN_OK;
 }
 }  // namespace
+
+int32_t xn_ternary_pack_sparse(int32_t in_dim, int32_t out_dim, const float* weights, float provided_scale,
+                               uint8_t* blob, int64_t blob_cap, int64_t* blob_len, float* w_scales) {
+    if (in_dim < 0 || out_dim < 0 || !weights || !blob || !blob_len || !w_scales || blob_cap < 0) return XN_ERR_ARG;
+    const bool has_scale = !std::isnan(provided_scale);
+    bool already = true;
+    for (size_t i = 0; i < size_t(in_dim) * size_t(out_dim) && already; ++i)
+        already = weights[i] == -1.0f || weights[i] == 0.0f || weights[i] == 1.0f;
+    std::vector<uint8_t> buf;
+    std::vector<int8_t> vals(size_t(in_dim) + 1);
+    for (int o = 0; o < out_dim; ++o) {   // ternarize_row, src/bit1_58/layers.rs:45-88
+        const float* row = weights + size_t(o) * in_dim;
+        float s;
+        if (already) s = has_scale ? provided_scale : 1.0f;
+        else if (has_scale) s = provided_scale;
+        else {
+            float sum_abs = 0.0f;
+            for (int i = 0; i < in_dim; ++i) sum_abs += std::fabs(row[i]);
+            s = in_dim == 0 ? 1.0f : sum_abs / float(in_dim);
+        }
+        w_scales[o] = s;
+        for (int i = 0; i < in_dim; ++i) vals[size_t(i)] = int8_t(ternary_value(row[i], s, already));
+        sparse_encode_row(vals.data(), size_t(in_dim), buf);
+    }
+    *blob_len = int64_t(buf.size());
+    if (int64_t(buf.size()) > blob_cap) return XN_ERR_CAPACITY;
+    if (!buf.empty()) memcpy(blob, buf.data(), buf.size());
+    return XN_OK;
+}
 
 int32_t xn_out_proj_set(xn_ctx* c, const xn_out_proj_desc* d) {
     if (!ctx_ok(c)) return XN_ERR_HANDLE;

@@ -2,6 +2,7 @@
 // src/bit1_58/layers.rs:91-149): ternarising + packing f32 weights the way TernaryLinear::new does,
 // and re-coding packed rows into the 2-bit device format of the projection kernel.
 #pragma once
+#include <algorithm>
 #include <cmath>
 #include <cstddef>
 #include <cstdint>
@@ -75,6 +76,65 @@ inline void recode_row_2bit(const uint8_t* src, size_t in_dim, int pack, uint8_t
         uint8_t& byte = dst[i / 4];
         byte = uint8_t((byte & ~(3u << ((i % 4) * 2))) | (code << ((i % 4) * 2)));
     }
+}
+
+// ---- XorSparse rows (src/bit1_58/sparse.rs) ------------------------------------------------------
+// per row: u32 num_blocks, then per 64-element block a u64 mask of the non-zero positions and
+// ceil(popcount / 8) bytes of sign bits in scan order (bit set = weight -1); little-endian.
+
+// ternarize_row (src/bit1_58/layers.rs:45-88): the weight of one position as -1 / 0 / +1
+inline int ternary_value(float w, float w_scale, bool already_ternary) {
+    if (already_ternary) return int(w);
+    return int(ternary_code(w, w_scale)) - 1;
+}
+
+// encode_sparse_row_into (sparse.rs:62-89); returns the bytes appended
+inline size_t sparse_encode_row(const int8_t* vals, size_t in_dim, std::vector<uint8_t>& buf) {
+    const size_t before = buf.size();
+    const uint32_t num_blocks = uint32_t((in_dim + 63) / 64);
+    for (int i = 0; i < 4; ++i) buf.push_back(uint8_t(num_blocks >> (8 * i)));
+    for (uint32_t b = 0; b < num_blocks; ++b) {
+        uint64_t mask = 0, signs = 0;
+        unsigned si = 0;
+        for (size_t i = size_t(b) * 64; i < std::min(in_dim, size_t(b) * 64 + 64); ++i)
+            if (vals[i] != 0) {
+                mask |= uint64_t(1) << (i - size_t(b) * 64);
+                if (vals[i] < 0) signs |= uint64_t(1) << si;
+                ++si;
+            }
+        for (int i = 0; i < 8; ++i) buf.push_back(uint8_t(mask >> (8 * i)));
+        for (unsigned i = 0; i < (si + 7) / 8; ++i) buf.push_back(uint8_t(signs >> (8 * i)));
+    }
+    return buf.size() - before;
+}
+
+// One sparse row -> the device's 2-bit codes (decode_row, sparse.rs:206-249).  Returns the bytes
+// of the row in the blob, or 0 when the row does not describe in_dim columns.
+inline size_t recode_sparse_row_2bit(const uint8_t* src, size_t in_dim, uint8_t* dst, size_t stride) {
+    for (size_t b = 0; b < stride; ++b) dst[b] = 0x55u;
+    const uint32_t num_blocks = uint32_t(src[0]) | uint32_t(src[1]) << 8 | uint32_t(src[2]) << 16 |
+                                uint32_t(src[3]) << 24;
+    if (size_t(num_blocks) != (in_dim + 63) / 64) return 0;
+    size_t p = 4;
+    for (uint32_t b = 0; b < num_blocks; ++b) {
+        uint64_t mask = 0;
+        for (int i = 0; i < 8; ++i) mask |= uint64_t(src[p + i]) << (8 * i);
+        p += 8;
+        unsigned nnz = 0;
+        for (uint64_t m = mask; m; m &= m - 1) ++nnz;
+        uint64_t sb = 0;
+        for (unsigned k = 0; k < (nnz + 7) / 8; ++k) sb |= uint64_t(src[p + k]) << (8 * k);
+        p += (nnz + 7) / 8;
+        unsigned si = 0;
+        for (size_t i = size_t(b) * 64; i < std::min(in_dim, size_t(b) * 64 + 64); ++i)
+            if ((mask >> (i - size_t(b) * 64)) & 1) {
+                const unsigned code = ((sb >> si) & 1) ? 0u : 2u;   // -1 : +1
+                uint8_t& byte = dst[i / 4];
+                byte = uint8_t((byte & ~(3u << ((i % 4) * 2))) | (code << ((i % 4) * 2)));
+                ++si;
+            }
+    }
+    return p;
 }
 
 }  // namespace xn
