@@ -65,6 +65,19 @@ enum {
     XN_PREFILL_TF32 = 2  /* TF32 kernel whenever it supports the shape                          */
 };
 
+/* KV cache format (xn_ctx_desc.kv_format). */
+enum {
+    XN_KV_F32 = 0, /* f32 rows: what fast_attention reads (k_buffers / v_buffers,                 */
+                   /* fast_attention.rs:20-21); results equal the reference's                      */
+    XN_KV_U8 = 1   /* opt-in: ONLY the reference's u8 shadow is kept (one byte per element, one    */
+                   /* f32 scale per KV head and token; U8CacheLayer fast_attention.rs:5-16, the    */
+                   /* quantiser :62-71, the append :117-128) and attention runs over the           */
+                   /* dequantised values (byte - 128) * scale.  A quarter of the cache bytes; the  */
+                   /* stored bytes and scales equal the reference's shadow bit for bit, the        */
+                   /* attention output differs from the f32 cache's by the quantisation error.     */
+                   /* The tensor-core prefill kernel is not available in this format.              */
+};
+
 typedef struct xn_ctx_desc {
     int32_t device;       /* CUDA ordinal                                                        */
     int32_t num_layers;   /* CpuRingCache::new(num_layers, ...)   fast_attention.rs:31-34        */
@@ -81,7 +94,7 @@ typedef struct xn_ctx_desc {
     const float* rope_sin;
     void* cuda_stream;    /* cudaStream_t to launch on; NULL: the context creates its own        */
     int32_t batch_window_us; /* how long a lone xn_attention caller waits for company            */
-    int32_t reserved;
+    int32_t kv_format;       /* XN_KV_*                                                           */
 } xn_ctx_desc;
 
 /* Request flags. */
@@ -245,6 +258,13 @@ XN_API int32_t xn_kv_read(xn_ctx* ctx, xn_stream* stream, int32_t layer, int32_t
 /* Slots [t0, t0+n) of every KV head: k_out, v_out are [num_kv_heads, n, head_dim]. */
 XN_API int32_t xn_kv_read_range(xn_ctx* ctx, xn_stream* stream, int32_t layer, int64_t t0,
                                 int64_t n, float* k_out, float* v_out);
+/* XN_KV_U8 contexts only: the stored representation of slots [t0, t0+n) of every KV head, i.e.
+ * the reference's u8_k / u8_v [num_kv_heads, n, head_dim] and k_scales / v_scales
+ * [num_kv_heads, n] (fast_attention.rs:8-15).  Any output may be NULL.  Never-written slots read
+ * as byte 128 with scale 0.0 (:45-48).  (xn_kv_read and xn_kv_read_range return the dequantised
+ * rows in this format.) */
+XN_API int32_t xn_kv_read_u8(xn_ctx* ctx, xn_stream* stream, int32_t layer, int64_t t0, int64_t n,
+                             uint8_t* k_u8, uint8_t* v_u8, float* k_scales, float* v_scales);
 /* Fills slots [t0, t0+n) of one layer with N(0,1) values from a counter-based generator on the
  * device (no host copy) so that benchmarks can build large caches. */
 XN_API int32_t xn_kv_fill_normal(xn_ctx* ctx, xn_stream* stream, int32_t layer, int64_t t0,

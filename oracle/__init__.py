@@ -77,6 +77,10 @@ def lib() -> C.CDLL:
         L.xo_cache_v.restype = _f32p
         L.xo_cache_append.argtypes = [C.c_void_p, _sz, _sz, _sz, _f32p, _f32p]
         L.xo_cache_append.restype = None
+        L.xo_quantize_to_u8.argtypes = [_f32p, _sz, _sz, C.c_void_p, _f32p]
+        L.xo_quantize_to_u8.restype = None
+        L.xo_dequantize_u8.argtypes = [C.c_void_p, _f32p, _sz, _sz, _f32p]
+        L.xo_dequantize_u8.restype = None
         L.xo_fast_attention.argtypes = [_f32p, _f32p, _f32p, _sz, _sz, C.c_void_p, _sz, _sz, _sz,
                                         _sz, C.c_int, _sz, _f32p, C.c_int]
         L.xo_fast_attention.restype = C.c_int
@@ -250,6 +254,34 @@ class RingCache:
             self.close()
         except Exception:
             pass
+
+
+def quantize_to_u8(rows):
+    """CpuRingCache::quantize_to_u8 (fast_attention.rs:62-71) on every row (last axis) of ``rows``:
+    returns (bytes uint8 of the same shape, scales float32 of the leading shape)."""
+    x = _f32(rows)
+    n = x.shape[-1]
+    r = x.size // n if n else 0
+    q = np.zeros(x.shape, dtype=np.uint8)
+    sc = np.zeros(x.shape[:-1], dtype=np.float32)
+    lib().xo_quantize_to_u8(_p(x), r, n, q.ctypes.data_as(C.c_void_p), _p(sc))
+    return q, sc
+
+
+def dequantize_u8(q, scales) -> np.ndarray:
+    """(byte - 128) * scale per row: what a reader of the u8 cache format sees."""
+    q = np.ascontiguousarray(q, dtype=np.uint8)
+    sc = _f32(scales)
+    n = q.shape[-1]
+    out = np.zeros(q.shape, dtype=np.float32)
+    lib().xo_dequantize_u8(q.ctypes.data_as(C.c_void_p), _p(sc), q.size // n if n else 0, n, _p(out))
+    return out
+
+
+def u8_round_trip(rows) -> np.ndarray:
+    """Rows as the u8 cache format returns them: quantise, then dequantise."""
+    q, sc = quantize_to_u8(rows)
+    return dequantize_u8(q, sc)
 
 
 def fast_attention(q, k, v, layer_idx, index_pos, cache: RingCache, num_heads, num_kv_heads,

@@ -506,7 +506,8 @@ XO_API void xo_transpose_heads_to_seq(const float* in, float* out, size_t seq_le
 
 /* CpuRingCache, fast_attention.rs:18-60.  The u8 shadow (:62-71, :117-128) is
  * write-only in the reference -- nothing reads it back -- so it does not take
- * part in any result and is not restated. */
+ * part in any result of the f32 cache; its quantiser is restated below
+ * (xo_quantize_to_u8) for the opt-in u8 cache format of the CUDA library. */
 typedef struct xo_ring_cache {
     size_t num_layers, num_kv_heads, max_seq_len, head_dim;
     float** k_buffers; /* [layer][h*cap*D + t*D + d], zero initialised (:40-41) */
@@ -562,6 +563,42 @@ static void cache_append(xo_ring_cache* cache, size_t layer_idx, size_t index_po
             memcpy(v_buf + dest, v_data + src, head_dim * sizeof(float));
         }
     }
+}
+
+/* CpuRingCache::quantize_to_u8, fast_attention.rs:62-71, applied to `rows` rows of n floats (the
+ * reference calls it once per (KV head, new token) slice, :120-121): max_abs folds f32::max over
+ * |x| from 0.0 (NaNs are ignored), scale = max_abs / 127 or 1.0, inv_scale = 1 / scale, and each
+ * byte is ((x * inv_scale) + 128).round().clamp(0, 255) as u8 -- round half away from zero, the
+ * multiply and the add separate roundings, NaN -> 0.
+ * PARITY UNPINNED: the reference holds no test or golden vector for the shadow. */
+XO_API void xo_quantize_to_u8(const float* data, size_t rows, size_t n, uint8_t* out, float* scales) {
+    for (size_t r = 0; r < rows; ++r) {
+        const float* x = data + r * n;
+        float max_abs = 0.0f;
+        for (size_t i = 0; i < n; ++i) {
+            float a = fabsf(x[i]);
+            if (a > max_abs) max_abs = a; /* f32::max: a NaN operand loses */
+        }
+        float scale = max_abs > 0.0f ? max_abs / 127.0f : 1.0f;
+        float inv_scale = 1.0f / scale;
+        for (size_t i = 0; i < n; ++i) {
+            float v = roundf((x[i] * inv_scale) + 128.0f);
+            uint8_t b;
+            if (v != v) b = 0;            /* NaN as u8 */
+            else if (v < 0.0f) b = 0;
+            else if (v > 255.0f) b = 255;
+            else b = (uint8_t)v;
+            out[r * n + i] = b;
+        }
+        scales[r] = scale;
+    }
+}
+
+/* The values a reader of the u8 cache sees: (byte - 128) * scale.  (The reference never wrote its
+ * "lazy dequantisation"; this is the inverse of the quantiser above.) */
+XO_API void xo_dequantize_u8(const uint8_t* q, const float* scales, size_t rows, size_t n, float* out) {
+    for (size_t r = 0; r < rows; ++r)
+        for (size_t i = 0; i < n; ++i) out[r * n + i] = ((float)q[r * n + i] - 128.0f) * scales[r];
 }
 
 XO_API void xo_cache_append(xo_ring_cache* cache, size_t layer_idx, size_t index_pos,

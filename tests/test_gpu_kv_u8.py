@@ -1,0 +1,298 @@
+"""The opt-in u8 cache format (XN_KV_U8) against the CPU oracle, through the C ABI.
+
+Two bars:
+  * storage -- the bytes and scales the library keeps equal the reference's u8 shadow
+    (CpuRingCache::quantize_to_u8, fast_attention.rs:62-71, applied per (KV head, token) row at
+    append, :117-128) BIT FOR BIT, and the dequantised rows read back equal (byte - 128) * scale
+    bit for bit;
+  * attention -- the output equals the oracle's fast_attention run over those dequantised rows
+    within the f32 path's tolerance (max abs <= 1e-4, relative L2 <= 1e-5): only the order of the
+    f32 sums and exp2f-vs-expf differ.
+The distance to the f32 cache's result is the quantisation error of the format itself and is only
+bounded loosely (relative L2 <= 2e-2 on N(0,1) data).
+"""
+import numpy as np
+import pytest
+
+import oracle as xo
+import xor_net_b200 as xn
+from gpu_util import assert_parity, errs, rand_qkv
+
+pytestmark = pytest.mark.gpu
+
+
+class PairU8:
+    """A device stream of a KV_U8 context and an oracle ring cache fed with the round-tripped rows,
+    plus the oracle's shadow arrays (bytes, scales) by slot."""
+
+    def __init__(self, ctx, cap, rope=None):
+        self.ctx, self.cap, self.rope = ctx, cap, rope
+        self.st = ctx.new_stream(cap)
+        self.ref = xo.RingCache(ctx.num_layers, ctx.num_kv_heads, cap, ctx.head_dim)
+        H, D = ctx.num_kv_heads, ctx.head_dim
+        self.k8 = {l: np.full((H, cap, D), 128, np.uint8) for l in range(ctx.num_layers)}
+        self.v8 = {l: np.full((H, cap, D), 128, np.uint8) for l in range(ctx.num_layers)}
+        self.ks = {l: np.zeros((H, cap), np.float32) for l in range(ctx.num_layers)}
+        self.vs = {l: np.zeros((H, cap), np.float32) for l in range(ctx.num_layers)}
+
+    def oracle_step(self, layer, pos, q, k, v, rope=False):
+        if rope:
+            cos, sin = self.rope
+            q = xo.tensor_rope(q, cos, sin, pos)
+            k = xo.tensor_rope(k, cos, sin, pos)
+        kq, ksc = xo.quantize_to_u8(k[0])
+        vq, vsc = xo.quantize_to_u8(v[0])
+        S = k.shape[2]
+        for t in range(S):                       # sequential, like the reference's append loop
+            slot = (pos + t) % self.cap
+            self.k8[layer][:, slot], self.v8[layer][:, slot] = kq[:, t], vq[:, t]
+            self.ks[layer][:, slot], self.vs[layer][:, slot] = ksc[:, t], vsc[:, t]
+        kd = xo.dequantize_u8(kq, ksc)[None]
+        vd = xo.dequantize_u8(vq, vsc)[None]
+        return xo.fast_attention(q, kd, vd, layer, pos, self.ref, self.ctx.num_heads,
+                                 self.ctx.num_kv_heads, self.ctx.head_dim)
+
+    def step(self, layer, pos, q, k, v, rope=False):
+        got = self.ctx.attention(self.st, layer, pos, q, k, v, rope=rope)
+        return got, self.oracle_step(layer, pos, q, k, v, rope)
+
+    def check_cache(self, layer):
+        k8, v8, ks, vs = self.st.read_u8(layer, 0, self.cap)
+        assert np.array_equal(k8, self.k8[layer]), "K bytes differ from the reference's shadow"
+        assert np.array_equal(v8, self.v8[layer]), "V bytes differ from the reference's shadow"
+        assert np.array_equal(ks.view(np.uint32), self.ks[layer].view(np.uint32)), "K scales differ"
+        assert np.array_equal(vs.view(np.uint32), self.vs[layer].view(np.uint32)), "V scales differ"
+        k, v = self.st.read_range(layer, 0, self.cap)
+        assert np.array_equal(k.ravel(), self.ref.k_buffer(layer))
+        assert np.array_equal(v.ravel(), self.ref.v_buffer(layer))
+
+
+def u8_ctx(L, Hq, Hkv, D, pages, **kw):
+    return xn.Context(L, Hq, Hkv, D, pool_pages=pages, kv_format=xn.KV_U8, **kw)
+
+
+@pytest.mark.parametrize("D", [2, 7, 16, 17, 32, 33, 64, 100, 128, 160, 256])
+def test_head_dims(D):
+    rng = np.random.default_rng(D)
+    for Hq, Hkv in [(4, 2), (3, 3), (8, 2)]:
+        ctx = u8_ctx(2, Hq, Hkv, D, 16)
+        p = PairU8(ctx, 300)
+        q, k, v = rand_qkv(rng, Hq, Hkv, 70, D)
+        got, want = p.step(1, 0, q, k, v)                 # prefill rows across a page boundary
+        assert_parity(got, want, f"prefill D={D} Hq={Hq} Hkv={Hkv}")
+        for pos in (70, 71):
+            q, k, v = rand_qkv(rng, Hq, Hkv, 1, D)
+            got, want = p.step(1, pos, q, k, v)
+            assert_parity(got, want, f"decode D={D} pos={pos}")
+        p.check_cache(1)
+        p.check_cache(0)                                  # untouched layer: bytes 128, scales 0
+        ctx.close()
+
+
+@pytest.mark.parametrize("Hq,Hkv", [(1, 1), (2, 1), (3, 1), (4, 1), (5, 1), (8, 1), (12, 4), (32, 8), (20, 5)])
+def test_group_sizes(Hq, Hkv):
+    rng = np.random.default_rng(Hq * 100 + Hkv)
+    ctx = u8_ctx(1, Hq, Hkv, 64, 16)
+    p = PairU8(ctx, 512)
+    q, k, v = rand_qkv(rng, Hq, Hkv, 130, 64)
+    got, want = p.step(0, 0, q, k, v)
+    assert_parity(got, want, f"G={Hq // Hkv} prefill")
+    q, k, v = rand_qkv(rng, Hq, Hkv, 1, 64)
+    got, want = p.step(0, 130, q, k, v)
+    assert_parity(got, want, f"G={Hq // Hkv} decode")
+    p.check_cache(0)
+    ctx.close()
+
+
+def test_decode_lengths_around_boundaries():
+    rng = np.random.default_rng(5)
+    ctx = u8_ctx(1, 20, 5, 128, 40)
+    for L in [1, 2, 31, 32, 33, 63, 64, 65, 127, 128, 129, 191, 192, 193, 1000]:
+        p = PairU8(ctx, 2048)
+        if L > 1:
+            qq, kk, vv = rand_qkv(rng, 20, 5, L - 1, 128)
+            p.step(0, 0, qq, kk, vv)
+        q, k, v = rand_qkv(rng, 20, 5, 1, 128)
+        got, want = p.step(0, L - 1, q, k, v)
+        assert_parity(got, want, f"L={L}")
+        p.st.destroy()
+    ctx.close()
+
+
+def test_rope_append_and_chunks():
+    # fused rotation before the quantiser, chunked prefill, overwrite of existing positions
+    rng = np.random.default_rng(17)
+    rope = xn.rope_tables(500000.0, 128, 2048)
+    ctx = u8_ctx(2, 20, 5, 128, 40, rope=rope)
+    p = PairU8(ctx, 1024, rope=rope)
+    pos = 0
+    for S in (100, 57, 1, 200, 1):
+        q, k, v = rand_qkv(rng, 20, 5, S, 128)
+        got, want = p.step(1, pos, q, k, v, rope=True)
+        assert_parity(got, want, f"rope chunk at {pos}+{S}")
+        pos += S
+    q, k, v = rand_qkv(rng, 20, 5, 30, 128)
+    got, want = p.step(1, 300, q, k, v, rope=True)
+    assert_parity(got, want, "overwrite")
+    p.check_cache(1)
+    ctx.close()
+
+
+def test_long_stream_cut_units():
+    # few streams, long caches: units are cut across thread blocks and merged from partial records
+    rng = np.random.default_rng(23)
+    ctx = u8_ctx(1, 15, 5, 64, 200)
+    pairs = [PairU8(ctx, 4096) for _ in range(2)]
+    lens = [3000, 1777]
+    for p, L in zip(pairs, lens):
+        q, k, v = rand_qkv(rng, 15, 5, L, 64)
+        want = p.oracle_step(0, 0, q, k, v)
+        got = ctx.attention(p.st, 0, 0, q, k, v)
+        assert_parity(got[:, :, -3:], want[:, :, -3:], f"prefill tail L={L}")
+    qs, ks, vs = zip(*[rand_qkv(rng, 15, 5, 1, 64) for _ in pairs])
+    got = ctx.attention_batch([p.st for p in pairs], 0, lens, qs, ks, vs)
+    for i, p in enumerate(pairs):
+        want = p.oracle_step(0, lens[i], qs[i], ks[i], vs[i])
+        assert_parity(got[i], want, f"decode stream {i}")
+        p.check_cache(0)
+    ctx.close()
+
+
+def test_ragged_batch_of_streams():
+    rng = np.random.default_rng(31)
+    ctx = u8_ctx(2, 20, 5, 64, 300)
+    lens = [1, 5, 64, 65, 200, 513, 700, 1023]
+    pairs = [PairU8(ctx, 2048) for _ in lens]
+    for p, L in zip(pairs, lens):
+        q, k, v = rand_qkv(rng, 20, 5, L, 64)
+        p.step(1, 0, q, k, v)
+    for step in range(3):
+        qs, ks, vs = zip(*[rand_qkv(rng, 20, 5, 1, 64) for _ in pairs])
+        got = ctx.attention_batch([p.st for p in pairs], 1, [L + step for L in lens], qs, ks, vs)
+        for i, p in enumerate(pairs):
+            want = p.oracle_step(1, lens[i] + step, qs[i], ks[i], vs[i])
+            assert_parity(got[i], want, f"step {step} stream {i}")
+    for p in pairs:
+        p.check_cache(1)
+    ctx.close()
+
+
+def test_gap_reads_as_never_written():
+    # positions skipped over keep byte 128 / scale 0.0 and contribute exact zeros
+    rng = np.random.default_rng(41)
+    ctx = u8_ctx(1, 4, 2, 64, 16)
+    p = PairU8(ctx, 512)
+    q, k, v = rand_qkv(rng, 4, 2, 10, 64)
+    p.step(0, 0, q, k, v)
+    q, k, v = rand_qkv(rng, 4, 2, 3, 64)
+    got, want = p.step(0, 100, q, k, v)          # slots 10..99 were never written
+    assert_parity(got, want, "gap")
+    p.check_cache(0)
+    p.st.reset()
+    k8, v8, ks, vs = p.st.read_u8(0, 0, 128)
+    assert (k8 == 128).all() and (v8 == 128).all() and (ks == 0).all() and (vs == 0).all()
+    ctx.close()
+
+
+def test_ring_wrap():
+    # index_pos + seq_len beyond the capacity: positions fold modulo the capacity (generic kernel)
+    rng = np.random.default_rng(43)
+    ctx = u8_ctx(1, 6, 2, 32, 16)
+    p = PairU8(ctx, 96)
+    q, k, v = rand_qkv(rng, 6, 2, 90, 32)
+    got, want = p.step(0, 0, q, k, v)
+    assert_parity(got, want, "fill")
+    q, k, v = rand_qkv(rng, 6, 2, 20, 32)
+    got, want = p.step(0, 90, q, k, v)           # wraps at 96
+    assert_parity(got, want, "wrap")
+    q, k, v = rand_qkv(rng, 6, 2, 1, 32)
+    got, want = p.step(0, 110, q, k, v)
+    assert_parity(got, want, "decode after wrap")
+    p.check_cache(0)
+    ctx.close()
+
+
+def test_quantiser_edge_rows():
+    # all-zero rows (scale 1.0), a single huge element, values that round to ties, denormals
+    ctx = u8_ctx(1, 2, 2, 16, 4)
+    p = PairU8(ctx, 64)
+    k = np.zeros((1, 2, 4, 16), np.float32)
+    v = np.zeros((1, 2, 4, 16), np.float32)
+    k[0, 0, 1, 3] = 1e30
+    k[0, 1, 1] = np.linspace(-1, 1, 16, dtype=np.float32)
+    k[0, 0, 2] = (np.arange(16) - 8).astype(np.float32) * 0.5      # exact halves after scaling
+    v[0, 1, 2] = 1e-41                                             # denormals
+    v[0, 0, 3] = -np.arange(16, dtype=np.float32)
+    q = np.ones((1, 2, 4, 16), np.float32)
+    got, want = p.step(0, 0, q, k, v)
+    assert_parity(got, want, "edge rows")
+    p.check_cache(0)
+    ctx.close()
+
+
+def test_distance_to_f32_cache_is_the_quantisation_error():
+    rng = np.random.default_rng(47)
+    c8 = u8_ctx(1, 20, 5, 128, 40)
+    c32 = xn.Context(1, 20, 5, 128, pool_pages=40, prefill_mode=1)
+    s8, s32 = c8.new_stream(1024), c32.new_stream(1024)
+    q, k, v = rand_qkv(rng, 20, 5, 600, 128)
+    a = c8.attention(s8, 0, 0, q, k, v)
+    b = c32.attention(s32, 0, 0, q, k, v)
+    ea, er = errs(a, b)
+    print(f"u8 cache vs f32 cache: max abs {ea:.3e}, rel L2 {er:.3e}")
+    assert 1e-4 < er <= 2e-2
+    c8.close()
+    c32.close()
+
+
+def test_device_pointer_batch_and_synthetic_fill():
+    torch = pytest.importorskip("torch")
+    rng = np.random.default_rng(53)
+    ctx = u8_ctx(2, 15, 5, 64, 600)
+    n, L = 6, 900
+    streams = [ctx.new_stream(2048) for _ in range(n)]
+    for i, s in enumerate(streams):
+        s.fill_normal(-1, 0, L, 1234 + i)
+    dev = torch.device("cuda:0")
+    q = torch.from_numpy(rng.standard_normal((n, 15, 1, 64)).astype(np.float32)).to(dev)
+    k = torch.from_numpy(rng.standard_normal((n, 5, 1, 64)).astype(np.float32)).to(dev)
+    v = torch.from_numpy(rng.standard_normal((n, 5, 1, 64)).astype(np.float32)).to(dev)
+    out = torch.empty_like(q)
+    reqs = ctx.make_batch([(s, 1, L, 1, q[i].data_ptr(), k[i].data_ptr(), v[i].data_ptr(), out[i].data_ptr())
+                           for i, s in enumerate(streams)], xn.REQ_DEVICE_PTRS)
+    torch.cuda.synchronize()
+    ctx.submit(reqs)
+    ctx.synchronize()
+    got = out.cpu().numpy()
+    for i, s in enumerate(streams):
+        kc, vc = s.read_range(1, 0, L + 1)               # dequantised rows, new token included
+        ref = xo.RingCache(1, 5, L + 1, 64)
+        ref.append(0, 0, kc[None], vc[None])
+        want = xo.fast_attention(q[i:i + 1].cpu().numpy(), kc[None, :, L:], vc[None, :, L:], 0, L, ref, 15, 5, 64)
+        assert_parity(got[i:i + 1], want, f"stream {i}")
+        # the synthetic fill is the quantised image of the f32 fill (same generator)
+        k8, v8, ks, vs = s.read_u8(1, 0, 4)
+        assert ks.min() > 0 and vs.min() > 0
+        assert ((k8 == 255) | (k8 == 1)).any(axis=-1).all()   # every row's largest element hits +-127
+    ctx.close()
+
+
+def test_rejects_tf32_mode_and_f32_reader():
+    with pytest.raises(xn.XnError):
+        xn.Context(1, 4, 2, 64, pool_pages=4, kv_format=xn.KV_U8, prefill_mode=2)
+    with pytest.raises(xn.XnError):
+        xn.Context(1, 4, 2, 64, pool_pages=4, kv_format=7)
+    c = xn.Context(1, 4, 2, 64, pool_pages=4)
+    s = c.new_stream(64)
+    with pytest.raises(xn.XnError):
+        s.read_u8(0, 0, 4)
+    c.close()
+
+
+def test_pool_bytes_buys_four_times_the_pages():
+    a = xn.Context(2, 20, 5, 128, pool_bytes=64 << 20)
+    b = u8_ctx(2, 20, 5, 128, 0, pool_bytes=64 << 20)
+    pa, pb = a.stats()["pages_total"], b.stats()["pages_total"]
+    assert 3.8 * pa < pb <= 4 * pa
+    a.close()
+    b.close()

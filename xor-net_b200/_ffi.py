@@ -17,7 +17,7 @@ class CtxDesc(C.Structure):
         ("pool_pages", C.c_int64), ("pool_bytes", C.c_int64), ("shuffle_seed", C.c_uint64),
         ("max_pos", C.c_int32), ("prefill_mode", C.c_int32),
         ("rope_cos", C.c_void_p), ("rope_sin", C.c_void_p), ("cuda_stream", C.c_void_p),
-        ("batch_window_us", C.c_int32), ("reserved", C.c_int32),
+        ("batch_window_us", C.c_int32), ("kv_format", C.c_int32),
     ]
 
 
@@ -51,6 +51,7 @@ class OutProjDesc(C.Structure):
 
 REQ_DEVICE_PTRS, REQ_ROPE, REQ_SEQ_MAJOR, REQ_HOST_PINNED, REQ_OUT_PROJ, REQ_QKV_PROJ = 1, 2, 4, 8, 16, 32
 PACK4, PACK5, SPARSE = 4, 5, 64
+KV_F32, KV_U8 = 0, 1   # xn_ctx_desc.kv_format
 
 STATUS_NAMES = {
     0: "XN_OK", 1: "XN_ERR_ARG", 2: "XN_ERR_SHAPE", 3: "XN_ERR_HANDLE", 4: "XN_ERR_OUT_OF_PAGES",
@@ -86,6 +87,8 @@ SIGNATURES = {
                                C.c_void_p, C.c_void_p]),
     "xn_kv_read_range": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int64,
                                      C.c_void_p, C.c_void_p]),
+    "xn_kv_read_u8": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int64,
+                                  C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "xn_kv_fill_normal": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int64,
                                       C.c_uint64]),
     "xn_fill_normal": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int64, C.c_uint64]),

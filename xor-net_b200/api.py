@@ -21,7 +21,7 @@ from typing import Optional, Sequence
 import numpy as np
 
 from . import _ffi
-from ._ffi import (PACK4, PACK5, SPARSE, REQ_DEVICE_PTRS, REQ_HOST_PINNED, REQ_OUT_PROJ, REQ_QKV_PROJ, REQ_ROPE,
+from ._ffi import (KV_F32, KV_U8, PACK4, PACK5, SPARSE, REQ_DEVICE_PTRS, REQ_HOST_PINNED, REQ_OUT_PROJ, REQ_QKV_PROJ, REQ_ROPE,
                    REQ_SEQ_MAJOR, CtxDesc, OutProjDesc, QkvProjDesc, Req, Stats)
 
 
@@ -94,6 +94,18 @@ class Stream:
         c._check(c.lib.xn_kv_read_range(c.handle, self.handle, layer, t0, n, _ptr(k), _ptr(v)))
         return k, v
 
+    def read_u8(self, layer: int, t0: int, n: int):
+        """``KV_U8`` contexts: the stored (k_u8, v_u8, k_scales, v_scales) of slots t0..t0+n, shaped
+        ``[Hkv, n, D]`` (uint8) and ``[Hkv, n]`` (float32) like the reference's ``U8CacheLayer``."""
+        c = self.ctx
+        k8 = np.zeros((c.num_kv_heads, n, c.head_dim), dtype=np.uint8)
+        v8 = np.zeros_like(k8)
+        ks = np.zeros((c.num_kv_heads, n), dtype=np.float32)
+        vs = np.zeros_like(ks)
+        c._check(c.lib.xn_kv_read_u8(c.handle, self.handle, layer, t0, n, k8.ctypes.data, v8.ctypes.data,
+                                     _ptr(ks), _ptr(vs)))
+        return k8, v8, ks, vs
+
     def read(self, layer: int, kv_head: int, t: int):
         c = self.ctx
         k = np.zeros(c.head_dim, dtype=np.float32)
@@ -108,7 +120,7 @@ class Context:
     def __init__(self, num_layers: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  pool_pages: int = 0, pool_bytes: int = 0, device: int = 0, shuffle_seed: int = 0,
                  rope: Optional[tuple] = None, cuda_stream: int = 0, prefill_mode: int = 0,
-                 batch_window_us: int = 0):
+                 batch_window_us: int = 0, kv_format: int = KV_F32):
         self.lib = _ffi.load()
         self.num_layers, self.num_heads = num_layers, num_heads
         self.num_kv_heads, self.head_dim = num_kv_heads, head_dim
@@ -118,6 +130,8 @@ class Context:
         d.num_kv_heads, d.head_dim, d.page_tokens = num_kv_heads, head_dim, 64
         d.pool_pages, d.pool_bytes, d.shuffle_seed = pool_pages, pool_bytes, shuffle_seed
         d.prefill_mode, d.batch_window_us = prefill_mode, batch_window_us
+        d.kv_format = kv_format
+        self.kv_format = kv_format
         d.cuda_stream = cuda_stream or None
         self._rope = None
         if rope is not None:

@@ -18,6 +18,7 @@
 #include "xn_append.cuh"
 #include "xn_common.cuh"
 #include "xn_decode.cuh"
+#include "xn_kv_u8.cuh"
 #include "xn_outproj.cuh"
 #include "xn_outproj_tc.cuh"
 #include "xn_plan.hpp"
@@ -110,6 +111,10 @@ struct xn_ctx {
     cudaStream_t copy_stream = nullptr;  // plan uploads run here, off the launch stream's critical path
     float* k_pool = nullptr;
     float* v_pool = nullptr;
+    // u8 cache format: one pool of K bytes | V bytes | scales blocks instead of the two f32 pools
+    bool kv_u8 = false;
+    int dq = 0;                  // bytes per stored row
+    uint8_t* pool8 = nullptr;
     float* cos_d = nullptr;
     float* sin_d = nullptr;
     std::vector<int32_t> free_pages;  // stack: back() is handed out next
@@ -217,6 +222,26 @@ SplitKernel pick_split(int nv_class, int gt, bool exact) {
         case 25: return pick_gt<25, true>(gt);
         case 32: return exact ? pick_gt<32, true>(gt) : pick_gt<32, false>(gt);
         default: return exact ? pick_gt<64, true>(gt) : pick_gt<64, false>(gt);
+    }
+}
+
+using Split8Fn = void (*)(const ReqDev*, const UnitDev*, const ItemDev*, const int*, int, const int*,
+                          const uint8_t*, float*, int*, long long, int, int, float);
+
+template <int LPK>
+Split8Fn pick8_gt(int gt) {
+    if (gt == 4) return kv8::attn_splitkv_u8_kernel<LPK, 4>;
+    if (gt == 2) return kv8::attn_splitkv_u8_kernel<LPK, 2>;
+    return kv8::attn_splitkv_u8_kernel<LPK, 1>;
+}
+
+Split8Fn pick_split8(int dq, int gt) {
+    switch (dq) {
+        case 16: return pick8_gt<1>(gt);
+        case 32: return pick8_gt<2>(gt);
+        case 64: return pick8_gt<4>(gt);
+        case 128: return pick8_gt<8>(gt);
+        default: return pick8_gt<16>(gt);
     }
 }
 
@@ -555,7 +580,7 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
     // the new token itself: no separate append launch.  Needs rows the bulk copies can take
     // (head_dim % 4 == 0, 16-byte aligned pointers) and, for RoPE, the pair layout of head_dim
     // 64 / 128.
-    bool fused = c->fuse_append && n_ring_rows == 0 && D % 4 == 0 && c->nv_class <= 32;
+    bool fused = c->fuse_append && !c->kv_u8 && n_ring_rows == 0 && D % 4 == 0 && c->nv_class <= 32;
     for (int i = 0; i < n && fused; ++i) {
         const xn_req& r = reqs[i];
         if (r.seq_len != 1) { fused = false; break; }
@@ -718,7 +743,8 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
     if (size_t(n_cut) + 2 > c->sync_cap)
         return fail(c, XN_ERR_CAPACITY, "internal: %d cut units exceed the arrival counters", n_cut);
     if ((rc = grow_device(c, &c->partials, &c->partials_cap,
-                          size_t(sp.n_parts) * c->gt * part_stride_floats(nv))) != XN_OK)
+                          size_t(sp.n_parts) * c->gt *
+                              (c->kv_u8 ? kv8::part_stride(c->dq) : part_stride_floats(nv)))) != XN_OK)
         return rc;
 
     // -- pack the plan: one pinned buffer, one copy
@@ -801,6 +827,11 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
     for (const GapFill& g : gaps) {
         const long long total = g.n * Hkv * D;
         const int blocks = int(std::min<long long>((total + 255) / 256, 4096));
+        if (c->kv_u8)
+            kv8::slots_fill_u8_kernel<<<int(std::min<long long>((g.n * Hkv + 7) / 8, 4096)), 256, 0, c->stream>>>(
+                pages_d + rd[g.req].page_off, c->pool8, c->pool_pages, rd[g.req].layer, Hkv, D, c->dq,
+                g.slot0, g.n, 0, 0ull);
+        else
         slots_fill_kernel<<<blocks, 256, 0, c->stream>>>(
             pages_d + rd[g.req].page_off, c->k_pool, c->v_pool, c->pool_pages, rd[g.req].layer, Hkv,
             D, nv, g.slot0, g.n, 0, 0ull);
@@ -808,12 +839,27 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
     }
     if (max_rows > 0) {
         dim3 grid(unsigned(std::min<long long>((max_rows + 15) / 16, 4096)), unsigned(n));
+        if (c->kv_u8) {
+            dim3 grid8(unsigned(std::min<long long>((max_rows + 7) / 8, 4096)), unsigned(n));
+            kv8::rope_append_u8_kernel<<<grid8, 256, 0, c->stream>>>(reqs_d, pages_d, c->pool8, c->cos_d,
+                                                                    c->sin_d, c->pool_pages, Hq, Hkv, D,
+                                                                    c->dq);
+        } else
         rope_append_kernel<<<grid, 256, 0, c->stream>>>(reqs_d, pages_d, c->k_pool, c->v_pool,
                                                         c->cos_d, c->sin_d, c->pool_pages, Hq, Hkv,
                                                         D, nv);
         c->stats.kernel_launches += 1;
     }
-    if (sp.ctas > 0) {
+    if (sp.ctas > 0 && c->kv_u8) {
+        if (c->profile && (rc = profile_begin(c, 0)) != XN_OK) return rc;
+        pick_split8(c->dq, c->gt)<<<std::min(sp.ctas, c->decode_ctas), kv8::kThreads,
+                                    kv8::red_floats(c->gt) * 4, c->stream>>>(
+            reqs_d, units_d, items_d, cta_d, sp.ctas, pages_d, c->pool8, c->partials, c->sync_d,
+            c->pool_pages, Hkv, D, c->scale * 1.4426950408889634f);
+        if (c->profile && (rc = profile_end(c)) != XN_OK) return rc;
+        c->stats.kernel_launches += 1;
+        c->stats.decode_launches += 1;
+    } else if (sp.ctas > 0) {
         SplitKernel k = pick_split(c->nv_class, c->gt, c->nv_exact);
         if (c->profile && (rc = profile_begin(c, 0)) != XN_OK) return rc;
         // sp.ctas chunks, taken dynamically by at most one block per SM
@@ -853,7 +899,7 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         const int rows = int(ring_rows.size() / 2);
         attn_ring_kernel<<<rows * Hq, 256, 0, c->stream>>>(reqs_d, ring_d, rows, pages_d, c->k_pool,
                                                            c->v_pool, c->pool_pages, Hq, Hkv, D, nv,
-                                                           c->scale);
+                                                           c->scale, c->pool8, c->dq);
         c->stats.kernel_launches += 1;
     }
     XN_CUDA(c, cudaGetLastError());
@@ -979,6 +1025,8 @@ int32_t xn_ctx_create(const xn_ctx_desc* d, xn_ctx** out_ctx) {
         return fail(nullptr, XN_ERR_SHAPE, "head_dim %d outside 1..256", d->head_dim);
     if (d->page_tokens != 0 && d->page_tokens != kPageTokens)
         return fail(nullptr, XN_ERR_ARG, "page_tokens must be 0 or %d", kPageTokens);
+    if (d->kv_format != XN_KV_F32 && d->kv_format != XN_KV_U8)
+        return fail(nullptr, XN_ERR_ARG, "kv_format %d is neither XN_KV_F32 nor XN_KV_U8", d->kv_format);
     if ((d->rope_cos == nullptr) != (d->rope_sin == nullptr) || (d->rope_cos && d->max_pos <= 0))
         return fail(nullptr, XN_ERR_ARG, "rope tables need cos, sin and max_pos together");
 
@@ -1011,6 +1059,11 @@ int32_t xn_ctx_create(const xn_ctx_desc* d, xn_ctx** out_ctx) {
     c->nv_class = nv_class_for(c->nv);
     c->nv_exact = c->nv_class == c->nv;
     c->tile_tokens = pick_split(c->nv_class, c->gt, c->nv_exact).tile_tokens;
+    c->kv_u8 = d->kv_format == XN_KV_U8;
+    if (c->kv_u8) {
+        c->dq = kv8::row_bytes_for(d->head_dim);
+        c->tile_tokens = kPageTokens;  // the u8 kernel's plan tile is one page
+    }
     c->scale = 1.0f / sqrtf(float(d->head_dim));  // fast_attention.rs:135
     c->max_pos = d->max_pos;
     c->prefill_mode = d->prefill_mode;
@@ -1038,7 +1091,8 @@ int32_t xn_ctx_create(const xn_ctx_desc* d, xn_ctx** out_ctx) {
 
 
     const size_t page_bytes =
-        size_t(d->num_layers) * d->num_kv_heads * kPageTokens * c->nv * 16 * 2;  // K and V
+        c->kv_u8 ? size_t(d->num_layers) * d->num_kv_heads * kv8::block_bytes(c->dq)
+                 : size_t(d->num_layers) * d->num_kv_heads * kPageTokens * c->nv * 16 * 2;  // K and V
     long long pages = d->pool_pages > 0 ? d->pool_pages : (d->pool_bytes > 0 ? d->pool_bytes / (long long)page_bytes : 0);
     if (pages <= 0 || pages > (1ll << 30)) {
         delete c;
@@ -1069,12 +1123,21 @@ int32_t xn_ctx_create(const xn_ctx_desc* d, xn_ctx** out_ctx) {
         c->own_stream = true;
     }
     XN_CREATE_CUDA(cudaStreamCreateWithFlags(&c->copy_stream, cudaStreamNonBlocking));
-    const size_t pool_floats = size_t(pages) * d->num_layers * d->num_kv_heads * kPageTokens * c->nv * 4;
-    XN_CREATE_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->k_pool), pool_floats * 4));
-    XN_CREATE_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->v_pool), pool_floats * 4));
-    // Row padding (head_dim rounded up to 4 floats) must hold zeros for the lifetime of the pool.
-    XN_CREATE_CUDA(cudaMemsetAsync(c->k_pool, 0, pool_floats * 4, c->stream));
-    XN_CREATE_CUDA(cudaMemsetAsync(c->v_pool, 0, pool_floats * 4, c->stream));
+    if (c->kv_u8) {
+        const long long n_blocks = pages * d->num_layers * d->num_kv_heads;
+        XN_CREATE_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->pool8), size_t(n_blocks) * kv8::block_bytes(c->dq)));
+        // every slot starts as the reference's shadow does: byte 128, scale 0.0
+        kv8::pool_init_u8_kernel<<<unsigned(std::min<long long>(n_blocks, 4096)), 256, 0, c->stream>>>(
+            c->pool8, n_blocks, c->dq);
+        XN_CREATE_CUDA(cudaGetLastError());
+    } else {
+        const size_t pool_floats = size_t(pages) * d->num_layers * d->num_kv_heads * kPageTokens * c->nv * 4;
+        XN_CREATE_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->k_pool), pool_floats * 4));
+        XN_CREATE_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->v_pool), pool_floats * 4));
+        // Row padding (head_dim rounded up to 4 floats) must hold zeros for the lifetime of the pool.
+        XN_CREATE_CUDA(cudaMemsetAsync(c->k_pool, 0, pool_floats * 4, c->stream));
+        XN_CREATE_CUDA(cudaMemsetAsync(c->v_pool, 0, pool_floats * 4, c->stream));
+    }
     if (d->rope_cos) {
         const size_t tb = size_t(d->max_pos) * (d->head_dim / 2) * 4;
         XN_CREATE_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->cos_d), std::max<size_t>(tb, 16)));
@@ -1089,7 +1152,11 @@ int32_t xn_ctx_create(const xn_ctx_desc* d, xn_ctx** out_ctx) {
     *c->status_h = kDevOk;
     XN_CREATE_CUDA(cudaHostGetDevicePointer(reinterpret_cast<void**>(&c->status_d), c->status_h, 0));
 
-    {
+    if (c->kv_u8) {
+        XN_CREATE_CUDA(cudaFuncSetAttribute(reinterpret_cast<const void*>(pick_split8(c->dq, c->gt)),
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            int(kv8::red_floats(c->gt) * 4)));
+    } else {
         SplitKernel k = pick_split(c->nv_class, c->gt, c->nv_exact);
         XN_CREATE_CUDA(cudaFuncSetAttribute(reinterpret_cast<const void*>(k.fn),
                                             cudaFuncAttributeMaxDynamicSharedMemorySize, int(k.smem)));
@@ -1098,7 +1165,7 @@ int32_t xn_ctx_create(const xn_ctx_desc* d, xn_ctx** out_ctx) {
     // tensor-core prefill: possible when rows are exactly head_dim floats and TMA can address them
     {
         const unsigned long long rows = (unsigned long long)pages * d->num_layers * d->num_kv_heads * kPageTokens;
-        if (d->head_dim % 4 == 0 && d->head_dim >= 16 && d->head_dim <= 128 && rows < (1ull << 31)) {
+        if (!c->kv_u8 && d->head_dim % 4 == 0 && d->head_dim >= 16 && d->head_dim <= 128 && rows < (1ull << 31)) {
             const cuuint64_t dims[2] = {cuuint64_t(d->head_dim), cuuint64_t(rows)};
             const cuuint64_t str[1] = {cuuint64_t(d->head_dim) * 4};
             const cuuint32_t box[2] = {32, cuuint32_t(pf::kPage)};
@@ -1116,7 +1183,8 @@ int32_t xn_ctx_create(const xn_ctx_desc* d, xn_ctx** out_ctx) {
             if (v > 0) c->tf32_min_rows = v;
         }
         if (d->prefill_mode == XN_PREFILL_TF32 && !c->tf32_ok) {
-            fail(nullptr, XN_ERR_SHAPE, "head_dim %d cannot use the TF32 prefill kernel", d->head_dim);
+            fail(nullptr, XN_ERR_SHAPE, c->kv_u8 ? "the TF32 prefill kernel does not read the u8 cache format (head_dim %d)"
+                                                  : "head_dim %d cannot use the TF32 prefill kernel", d->head_dim);
             return bail(XN_ERR_SHAPE);
         }
     }
@@ -1172,6 +1240,7 @@ int32_t xn_ctx_destroy(xn_ctx* c) {
     if (c->sin_d) cudaFree(c->sin_d);
     if (c->k_pool) cudaFree(c->k_pool);
     if (c->v_pool) cudaFree(c->v_pool);
+    if (c->pool8) cudaFree(c->pool8);
     if (c->copy_stream) cudaStreamDestroy(c->copy_stream);
     if (c->own_stream && c->stream) cudaStreamDestroy(c->stream);
     c->magic = 0;
@@ -1372,6 +1441,68 @@ static int32_t upload_pages(xn_ctx* c, xn_stream* s, const int** pages_d, PlanSl
     return XN_OK;
 }
 
+// u8 cache format: dequantised rows and / or the stored bytes and scales of slots [t0, t0+n).
+// Called with the context lock held and the arguments checked.
+static int32_t kv_read_u8_locked(xn_ctx* c, xn_stream* s, int32_t layer, int64_t t0, int64_t n,
+                                 float* k_out, float* v_out, uint8_t* k_u8, uint8_t* v_u8,
+                                 float* k_sc, float* v_sc) {
+    const size_t D = size_t(c->head_dim), H = size_t(c->num_kv_heads);
+    const size_t elems = size_t(n) * H * D, rows = size_t(n) * H;
+    if (k_out) memset(k_out, 0, elems * 4);
+    if (v_out) memset(v_out, 0, elems * 4);
+    if (k_u8) memset(k_u8, 128, elems);
+    if (v_u8) memset(v_u8, 128, elems);
+    if (k_sc) memset(k_sc, 0, rows * 4);
+    if (v_sc) memset(v_sc, 0, rows * 4);
+    const int64_t have = std::min<int64_t>(
+        {int64_t(s->pages.size()) * kPageTokens, t0 + n, std::min<int64_t>(s->hw[size_t(layer)], s->cap)});
+    if (have <= t0) return XN_OK;
+    const int64_t m = have - t0;
+    const size_t melems = size_t(m) * H * D, mrows = size_t(m) * H;
+    const size_t o_v = melems * 4, o_ks = 2 * melems * 4, o_vs = o_ks + mrows * 4, o_kr = o_vs + mrows * 4,
+                 o_vr = o_kr + melems, total_bytes = o_vr + melems;
+    int32_t rc = grow_io(c, total_bytes);
+    if (rc != XN_OK) return rc;
+    const int* pages_d = nullptr;
+    PlanSlot* slot = nullptr;
+    if ((rc = upload_pages(c, s, &pages_d, &slot)) != XN_OK) return rc;
+    unsigned char* b = c->io_dev;
+    const int blocks = int(std::min<size_t>((melems + 255) / 256, 8192));
+    kv8::slots_gather_u8_kernel<<<blocks, 256, 0, c->stream>>>(
+        pages_d, c->pool8, c->pool_pages, layer, c->num_kv_heads, c->head_dim, c->dq, t0, m,
+        reinterpret_cast<float*>(b), reinterpret_cast<float*>(b + o_v), b + o_kr, b + o_vr,
+        reinterpret_cast<float*>(b + o_ks), reinterpret_cast<float*>(b + o_vs));
+    c->stats.kernel_launches += 1;
+    XN_CUDA(c, cudaGetLastError());
+    XN_CUDA(c, cudaMemcpyAsync(c->io_host, c->io_dev, total_bytes, cudaMemcpyDeviceToHost, c->stream));
+    XN_CUDA(c, cudaEventRecord(slot->ev, c->stream));
+    slot->used = true;
+    XN_CUDA(c, cudaStreamSynchronize(c->stream));
+    const unsigned char* hb = c->io_host;
+    for (size_t h = 0; h < H; ++h) {  // [Hkv, m, ...] -> [Hkv, n, ...]
+        if (k_out) memcpy(k_out + h * n * D, hb + h * m * D * 4, size_t(m) * D * 4);
+        if (v_out) memcpy(v_out + h * n * D, hb + o_v + h * m * D * 4, size_t(m) * D * 4);
+        if (k_u8) memcpy(k_u8 + h * n * D, hb + o_kr + h * m * D, size_t(m) * D);
+        if (v_u8) memcpy(v_u8 + h * n * D, hb + o_vr + h * m * D, size_t(m) * D);
+        if (k_sc) memcpy(k_sc + h * n, hb + o_ks + h * m * 4, size_t(m) * 4);
+        if (v_sc) memcpy(v_sc + h * n, hb + o_vs + h * m * 4, size_t(m) * 4);
+    }
+    return XN_OK;
+}
+
+int32_t xn_kv_read_u8(xn_ctx* c, xn_stream* s, int32_t layer, int64_t t0, int64_t n, uint8_t* k_u8,
+                      uint8_t* v_u8, float* k_scales, float* v_scales) {
+    if (!ctx_ok(c)) return XN_ERR_HANDLE;
+    std::lock_guard<std::mutex> g(c->mu);
+    if (!stream_ok(c, s)) return fail(c, XN_ERR_HANDLE, "stream handle is not live");
+    if (!c->kv_u8) return fail(c, XN_ERR_ARG, "xn_kv_read_u8: the context keeps the f32 cache format");
+    if (layer < 0 || layer >= c->num_layers || t0 < 0 || n < 0 || t0 + n > s->cap)
+        return fail(c, XN_ERR_ARG, "slot range outside the stream's capacity");
+    if (n == 0) return XN_OK;
+    XN_CUDA(c, cudaSetDevice(c->device));
+    return kv_read_u8_locked(c, s, layer, t0, n, nullptr, nullptr, k_u8, v_u8, k_scales, v_scales);
+}
+
 int32_t xn_kv_read_range(xn_ctx* c, xn_stream* s, int32_t layer, int64_t t0, int64_t n,
                          float* k_out, float* v_out) {
     if (!ctx_ok(c)) return XN_ERR_HANDLE;
@@ -1381,6 +1512,7 @@ int32_t xn_kv_read_range(xn_ctx* c, xn_stream* s, int32_t layer, int64_t t0, int
         return fail(c, XN_ERR_ARG, "slot range outside the stream's capacity");
     if (n == 0) return XN_OK;
     XN_CUDA(c, cudaSetDevice(c->device));
+    if (c->kv_u8) return kv_read_u8_locked(c, s, layer, t0, n, k_out, v_out, nullptr, nullptr, nullptr, nullptr);
     const size_t elems = size_t(n) * c->num_kv_heads * c->head_dim;
     if (k_out) memset(k_out, 0, elems * 4);
     if (v_out) memset(v_out, 0, elems * 4);
@@ -1450,6 +1582,12 @@ int32_t xn_kv_fill_normal(xn_ctx* c, xn_stream* s, int32_t layer, int64_t t0, in
     const int blocks = int(std::min<long long>((total + 255) / 256, 8192));
     const int l0 = layer < 0 ? 0 : layer, l1 = layer < 0 ? c->num_layers : layer + 1;
     for (int l = l0; l < l1; ++l) {
+        if (c->kv_u8)
+            kv8::slots_fill_u8_kernel<<<int(std::min<long long>((n * c->num_kv_heads + 7) / 8, 8192)), 256, 0,
+                                        c->stream>>>(pages_d, c->pool8, c->pool_pages, l, c->num_kv_heads,
+                                                     c->head_dim, c->dq, t0, n, 1,
+                                                     seed + 0x632BE59BD9B4E019ull * uint64_t(l));
+        else
         slots_fill_kernel<<<blocks, 256, 0, c->stream>>>(pages_d, c->k_pool, c->v_pool, c->pool_pages,
                                                          l, c->num_kv_heads, c->head_dim, c->nv, t0,
                                                          n, 1, seed + 0x632BE59BD9B4E019ull * uint64_t(l));

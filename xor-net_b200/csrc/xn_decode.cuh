@@ -775,12 +775,15 @@ attn_splitkv_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restrict__
 // capacity): logical positions 0..=limit are visited in order and mapped with % cap exactly as
 // the reference does (fast_attention_simd.rs:608, :145), so a slot that was overwritten is
 // counted once per visit.  One block per (request row, query head); plain loads, chunked online
-// softmax.  Never on the fast path.
+// softmax.  Never on the fast path.  With pool8 != nullptr the cache is the u8 format (rows of dq
+// bytes with one scale each, blocks of K bytes | V bytes | K scales | V scales) and the values
+// are (byte - 128) * scale.
 __global__ void __launch_bounds__(256, 1)
 attn_ring_kernel(const ReqDev* __restrict__ reqs, const int* __restrict__ ring_rows, int n_rows,
                  const int* __restrict__ page_ids, const float* __restrict__ k_pool,
                  const float* __restrict__ v_pool, long long pool_pages, int num_heads,
-                 int num_kv_heads, int head_dim, int nv, float scale) {
+                 int num_kv_heads, int head_dim, int nv, float scale,
+                 const unsigned char* __restrict__ pool8, int dq) {
     constexpr int kChunk = 1024;
     __shared__ float s_q[256];
     __shared__ float s_p[kChunk];
@@ -806,11 +809,19 @@ attn_ring_kernel(const ReqDev* __restrict__ reqs, const int* __restrict__ ring_r
         float lmax = -INFINITY;
         for (int i = tid; i < cn; i += 256) {
             const int slot = (c0 + i) % r.cap;
-            const float* krow = k_pool +
-                                ((layer_base + size_t(pages[slot / kPageTokens])) * num_kv_heads + h_kv) * page_floats +
-                                size_t(slot % kPageTokens) * dp;
             float dot = 0.f;
-            for (int d = 0; d < head_dim; ++d) dot = fmaf(s_q[d], krow[d], dot);
+            if (pool8) {
+                const unsigned char* blk = pool8 + ((layer_base + size_t(pages[slot / kPageTokens])) * num_kv_heads + h_kv) *
+                                                       (size_t(kPageTokens) * (2 * size_t(dq) + 8));
+                const unsigned char* krow = blk + size_t(slot % kPageTokens) * dq;
+                const float ks = reinterpret_cast<const float*>(blk + 2 * size_t(kPageTokens) * dq)[slot % kPageTokens];
+                for (int d = 0; d < head_dim; ++d) dot = fmaf(s_q[d], (float(krow[d]) - 128.0f) * ks, dot);
+            } else {
+                const float* krow = k_pool +
+                                    ((layer_base + size_t(pages[slot / kPageTokens])) * num_kv_heads + h_kv) * page_floats +
+                                    size_t(slot % kPageTokens) * dp;
+                for (int d = 0; d < head_dim; ++d) dot = fmaf(s_q[d], krow[d], dot);
+            }
             dot *= scale;
             s_p[i] = dot;
             lmax = fmaxf(lmax, dot);
@@ -842,10 +853,18 @@ attn_ring_kernel(const ReqDev* __restrict__ reqs, const int* __restrict__ ring_r
             acc *= alpha;
             for (int i = 0; i < cn; ++i) {
                 const int slot = (c0 + i) % r.cap;
-                const float* vrow = v_pool +
-                                    ((layer_base + size_t(pages[slot / kPageTokens])) * num_kv_heads + h_kv) * page_floats +
-                                    size_t(slot % kPageTokens) * dp;
-                acc = fmaf(s_p[i], vrow[tid], acc);
+                if (pool8) {
+                    const unsigned char* blk = pool8 + ((layer_base + size_t(pages[slot / kPageTokens])) * num_kv_heads + h_kv) *
+                                                           (size_t(kPageTokens) * (2 * size_t(dq) + 8));
+                    const float vs = reinterpret_cast<const float*>(blk + 2 * size_t(kPageTokens) * dq)[kPageTokens + slot % kPageTokens];
+                    const float vv = (float(blk[size_t(kPageTokens + slot % kPageTokens) * dq + tid]) - 128.0f) * vs;
+                    acc = fmaf(s_p[i], vv, acc);
+                } else {
+                    const float* vrow = v_pool +
+                                        ((layer_base + size_t(pages[slot / kPageTokens])) * num_kv_heads + h_kv) * page_floats +
+                                        size_t(slot % kPageTokens) * dp;
+                    acc = fmaf(s_p[i], vrow[tid], acc);
+                }
             }
         }
         __syncthreads();
