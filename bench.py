@@ -67,8 +67,12 @@ def host_threads():
         return max(1, os.cpu_count() or 1)
 
 
-def algorithmic_bytes_per_layer(lens, Hq, Hkv, D):
-    return int(sum(2 * Hkv * int(L) * D * 4 + 4 * Hkv * D * 4 + 2 * Hq * D * 4 for L in lens))
+def algorithmic_bytes_per_layer(lens, Hq, Hkv, D, u8=False):
+    """Bytes one layer's decode step must move: every cached K and V row once, the new token's rows
+    in and into the cache, q in and the output out.  In the u8 cache format a cached row is D bytes
+    plus one f32 scale."""
+    row = (D + 4) if u8 else D * 4
+    return int(sum(2 * Hkv * int(L) * row + 2 * Hkv * D * 4 + 2 * Hkv * row + 2 * Hq * D * 4 for L in lens))
 
 
 def stream_lengths(n, lo, hi, seed):
@@ -533,9 +537,13 @@ def run_gpu_arm(args):
     torch.cuda.set_stream(tstream)
     whole_block = args.workload.endswith("b")   # x in, y out: projections on the device too
     rope = xn.rope_tables(500000.0, D, int(hi) + 1) if whole_block else None
+    u8 = args.kv == "u8"
+    if u8:
+        desc += " [opt-in u8 cache format: results differ from the f32 cache by the quantisation error]"
     ctx = xn.Context(num_layers=layers, num_heads=Hq, num_kv_heads=Hkv, head_dim=D,
                      pool_pages=pages_needed + 8, device=local_rank,
-                     shuffle_seed=BASE_SEED + rank, cuda_stream=tstream.cuda_stream, rope=rope)
+                     shuffle_seed=BASE_SEED + rank, cuda_stream=tstream.cuda_stream, rope=rope,
+                     kv_format=xn.KV_U8 if u8 else xn.KV_F32)
     streams = [ctx.new_stream(int(hi)) for _ in range(n_streams)]
     for i, st in enumerate(streams):
         if lens[i] > 1:
@@ -614,7 +622,7 @@ def run_gpu_arm(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    bytes_per_layer = algorithmic_bytes_per_layer(lens, Hq, Hkv, D)
+    bytes_per_layer = algorithmic_bytes_per_layer(lens, Hq, Hkv, D, u8)
     bytes_per_step = bytes_per_layer * layers
 
     # ---- device-resident timing (value) + live kernel timing (roofline) -------------------------
@@ -686,7 +694,7 @@ def run_gpu_arm(args):
         # (dram__bytes_read.sum + dram__bytes_write.sum; the summary is kept under profiles/);
         # only valid for the unmodified c3 workload, whose per-launch work is fixed by its seed
         traffic, traffic_src = None, None
-        if args.workload == "c3" and not args.streams and world == 1:
+        if args.workload == "c3" and not args.streams and world == 1 and not u8:
             traffic = 708.71e6 + 5.04e6
             traffic_src = "ncu capture of this workload (2 of 30 layers), summary under profiles/"
         line = {
@@ -697,6 +705,7 @@ def run_gpu_arm(args):
             "config": {"workload": f"{args.workload}: {desc}", "streams_per_gpu": n_streams,
                        "layers": layers, "num_heads": Hq, "num_kv_heads": Hkv, "head_dim": D,
                        "kv_tokens_per_gpu": int(lens.sum()), "page_tokens": 64,
+                       "kv_format": "u8 bytes + one f32 scale per row" if u8 else "f32",
                        "parallelism": f"streams sharded over {world} GPU(s), no collective",
                        "l2": "inputs larger than L2: %.1f GB of KV per GPU read per step" %
                              (bytes_per_step / 1e9)},
@@ -711,7 +720,8 @@ def run_gpu_arm(args):
                     "staged_ms_per_step": staged_ms / max(e2e_steps, 1),
                     "staged_value": (bytes_per_step * e2e_steps / (staged_ms * 1e-3) / 1e9) if staged_ms else None},
             "gpu_launches": int(launches),
-            "roofline": {"bound": "hbm", "kernel": "attn_splitkv_kernel<32,4>",
+            "roofline": {"bound": "hbm",
+                         "kernel": "attn_splitkv_u8_kernel" if u8 else "attn_splitkv_kernel<32,4>",
                          "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak if peak else None, "peak_source": peak_kind,
                          "traffic": traffic, "traffic_source": traffic_src, "avg_launch_ms": kern_avg_ms,
@@ -744,6 +754,9 @@ def run_gpu_arm(args):
         qs = [q_h[layer, i].numpy().reshape(1, Hq, 1, D) for i in range(sample)]
         ks = [k_h[layer, i].numpy().reshape(1, Hkv, 1, D) for i in range(sample)]
         vs = [v_h[layer, i].numpy().reshape(1, Hkv, 1, D) for i in range(sample)]
+        if u8:   # the checker attends over what the u8 cache holds: the new rows round-tripped too
+            import oracle as xo
+            ks, vs = [xo.u8_round_trip(a) for a in ks], [xo.u8_round_trip(a) for a in vs]
         gbs, per_pass, outs, threads, reps = cpu_sample(lens[:sample], Hq, Hkv, D, kv, qs, ks, vs,
                                                         layer, budget_s=args.cpu_seconds)
         got = o_h[layer, :sample].numpy()
@@ -826,6 +839,8 @@ def main():
     ap.add_argument("--seq", type=int, default=0, help="prefill length for --workload c2")
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (profiling)")
     ap.add_argument("--streams", type=int, default=0, help="override streams per GPU (profiling)")
+    ap.add_argument("--kv", default="f32", choices=["f32", "u8"],
+                    help="KV cache format of the decode workloads (u8: the opt-in compressed pages)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)

@@ -114,6 +114,7 @@ struct xn_ctx {
     // u8 cache format: one pool of K bytes | V bytes | scales blocks instead of the two f32 pools
     bool kv_u8 = false;
     int dq = 0;                  // bytes per stored row
+    int kv8_epl = 16;            // bytes of a row one lane of the attention kernel handles
     uint8_t* pool8 = nullptr;
     float* cos_d = nullptr;
     float* sin_d = nullptr;
@@ -228,21 +229,30 @@ SplitKernel pick_split(int nv_class, int gt, bool exact) {
 using Split8Fn = void (*)(const ReqDev*, const UnitDev*, const ItemDev*, const int*, int, const int*,
                           const uint8_t*, float*, int*, long long, int, int, float);
 
-template <int LPK>
+template <int DQ, int EPL>
 Split8Fn pick8_gt(int gt) {
-    if (gt == 4) return kv8::attn_splitkv_u8_kernel<LPK, 4>;
-    if (gt == 2) return kv8::attn_splitkv_u8_kernel<LPK, 2>;
-    return kv8::attn_splitkv_u8_kernel<LPK, 1>;
+    if (gt == 4) return kv8::attn_splitkv_u8_kernel<DQ / EPL, 4, EPL>;
+    if (gt == 2) return kv8::attn_splitkv_u8_kernel<DQ / EPL, 2, EPL>;
+    return kv8::attn_splitkv_u8_kernel<DQ / EPL, 1, EPL>;
 }
 
-Split8Fn pick_split8(int dq, int gt) {
+template <int EPL>
+Split8Fn pick8_dq(int dq, int gt) {
     switch (dq) {
-        case 16: return pick8_gt<1>(gt);
-        case 32: return pick8_gt<2>(gt);
-        case 64: return pick8_gt<4>(gt);
-        case 128: return pick8_gt<8>(gt);
-        default: return pick8_gt<16>(gt);
+        case 16: return pick8_gt<16, EPL>(gt);
+        case 32: return pick8_gt<32, EPL>(gt);
+        case 64: return pick8_gt<64, EPL>(gt);
+        case 128: return pick8_gt<128, EPL>(gt);
+        default: return pick8_gt<256, EPL>(gt);
     }
+}
+
+// epl: bytes of a row per lane.  Only 16 is built: with 8 a lane needs half the registers and
+// twice the warps fit, but every key then costs 1.5x the instructions (the per-key bookkeeping is
+// spread over half as many elements) and the config-3 batch ran at 134 us per launch against 104.
+Split8Fn pick_split8(int dq, int gt, int epl) {
+    (void)epl;
+    return pick8_dq<16>(dq, gt);
 }
 
 int nv_class_for(int nv) {
@@ -852,8 +862,8 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
     }
     if (sp.ctas > 0 && c->kv_u8) {
         if (c->profile && (rc = profile_begin(c, 0)) != XN_OK) return rc;
-        pick_split8(c->dq, c->gt)<<<std::min(sp.ctas, c->decode_ctas), kv8::kThreads,
-                                    kv8::red_floats(c->gt) * 4, c->stream>>>(
+        pick_split8(c->dq, c->gt, c->kv8_epl)<<<std::min(sp.ctas, c->decode_ctas), kv8::kThreads,
+                                                kv8::smem_bytes(c->gt, c->kv8_epl), c->stream>>>(
             reqs_d, units_d, items_d, cta_d, sp.ctas, pages_d, c->pool8, c->partials, c->sync_d,
             c->pool_pages, Hkv, D, c->scale * 1.4426950408889634f);
         if (c->profile && (rc = profile_end(c)) != XN_OK) return rc;
@@ -1071,7 +1081,7 @@ int32_t xn_ctx_create(const xn_ctx_desc* d, xn_ctx** out_ctx) {
     c->sm_count = prop.multiProcessorCount;
     c->out_proj.resize(size_t(d->num_layers));
     c->qkv_proj.resize(size_t(d->num_layers));
-    c->decode_ctas = c->sm_count;
+    c->decode_ctas = c->kv_u8 ? c->sm_count * kv8::blocks_per_sm(c->kv8_epl) : c->sm_count;
     if (const char* env = getenv("XORNET_ATTN_DECODE_CTAS")) {
         int v = atoi(env);
         if (v > 0) c->decode_ctas = v;
@@ -1153,9 +1163,9 @@ int32_t xn_ctx_create(const xn_ctx_desc* d, xn_ctx** out_ctx) {
     XN_CREATE_CUDA(cudaHostGetDevicePointer(reinterpret_cast<void**>(&c->status_d), c->status_h, 0));
 
     if (c->kv_u8) {
-        XN_CREATE_CUDA(cudaFuncSetAttribute(reinterpret_cast<const void*>(pick_split8(c->dq, c->gt)),
+        XN_CREATE_CUDA(cudaFuncSetAttribute(reinterpret_cast<const void*>(pick_split8(c->dq, c->gt, c->kv8_epl)),
                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                            int(kv8::red_floats(c->gt) * 4)));
+                                            int(kv8::smem_bytes(c->gt, c->kv8_epl))));
     } else {
         SplitKernel k = pick_split(c->nv_class, c->gt, c->nv_exact);
         XN_CREATE_CUDA(cudaFuncSetAttribute(reinterpret_cast<const void*>(k.fn),

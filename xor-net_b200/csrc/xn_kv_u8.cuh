@@ -14,6 +14,7 @@
 // Never-written slots hold byte 128 and scale 0.0 as in the reference (:45-48).
 #pragma once
 #include "xn_common.cuh"
+#include "xn_decode.cuh"
 
 namespace xn {
 namespace kv8 {
@@ -235,23 +236,67 @@ slots_gather_u8_kernel(const int* __restrict__ pages, const uint8_t* __restrict_
 
 // ---- split-KV attention over u8 pages --------------------------------------------------------
 
-constexpr int kThreads = 256;
-constexpr int kWarps = 8;
-#ifndef XN_KV8_PREFETCH
-#define XN_KV8_PREFETCH 2
+// One warp per thread block, many blocks per SM: every warp walks its own item, so the chain of
+// dependent loads that opens an item (descriptors, query rows, page ids, first copies) overlaps
+// with the other warps' arithmetic instead of idling a whole 8-warp block.
+#ifndef XN_KV8_WARPS
+#define XN_KV8_WARPS 1
 #endif
+constexpr int kWarps = XN_KV8_WARPS;
+constexpr int kThreads = 32 * kWarps;
+// Bytes of a row one lane handles (EPL): 16 keeps the per-key bookkeeping lowest, 8 halves the
+// registers a lane needs for its query slice and accumulators and so doubles the resident warps.
+// (The register file is split over the SM's four schedulers, 16384 registers each: a one-warp
+// block of up to 168 registers per thread fits three times per scheduler, up to 128 four times.)
+#ifndef XN_KV8_BLOCKS_EPL16
+#define XN_KV8_BLOCKS_EPL16 12
+#endif
+__host__ __device__ constexpr int blocks_per_sm(int epl) { return (epl == 8 ? 16 : XN_KV8_BLOCKS_EPL16) / kWarps; }
+#ifndef XN_KV8_PREFETCH
+#define XN_KV8_PREFETCH 8
+#endif
+#ifndef XN_KV8_KEYS_PER_TRIP
+#define XN_KV8_KEYS_PER_TRIP 2
+#endif
+constexpr int kKeysPerTrip = XN_KV8_KEYS_PER_TRIP;   // keys a lane handles between two waits on its copies
+constexpr int kPrefetch = XN_KV8_PREFETCH;   // warp iterations a thread's copies run ahead of their use
 
-__host__ __device__ constexpr size_t red_floats(int gt) { return size_t(4096) * gt; }
+// reduction buffer of an item's end: [groups of the block][gt][dq] floats = 32 * epl * gt per warp
+__host__ __device__ constexpr size_t red_floats(int gt, int epl) { return size_t(32) * epl * kWarps * gt; }
+// ring of per-thread copy slots: [kPrefetch][kThreads] x (epl K bytes, epl V bytes, K scale, V scale)
+__host__ __device__ constexpr size_t ring_bytes(int epl) { return size_t(kPrefetch) * kThreads * (2 * epl + 8); }
+// the two are never live at the same time and share the block's dynamic shared memory
+__host__ __device__ constexpr size_t smem_bytes(int gt, int epl) {
+    return ring_bytes(epl) > red_floats(gt, epl) * 4 ? ring_bytes(epl) : red_floats(gt, epl) * 4;
+}
+
+// Per-thread asynchronous copies global -> shared (LDGSTS): no register holds the data in flight,
+// completion is awaited per commit group by the issuing thread, which is also the only reader of
+// what it copied -- no barrier between threads is involved.
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async8(void* smem_dst, const void* gsrc) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async4(void* smem_dst, const void* gsrc) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
 // partial record of one (item, head): [m (base-2 log domain), l, 0, 0, acc[dq]]
 __host__ __device__ __forceinline__ size_t part_stride(int dq) { return size_t(dq) + 4; }
 
-// 16 stored bytes -> 16 exact f32 values (byte - 128): the byte is dropped into the mantissa of
+// 4 * W stored bytes -> exact f32 values (byte - 128): the byte is dropped into the mantissa of
 // 2^23 (one PRMT) and 2^23 + 128 is subtracted (exact).
-__device__ __forceinline__ void dequant16(const uint4& w, float2 (&f)[8]) {
-    const unsigned ws[4] = {w.x, w.y, w.z, w.w};
+template <int W>
+__device__ __forceinline__ void dequant(const uint32_t (&ws)[W], float2 (&f)[2 * W]) {
     const float2 c = make_float2(-8388736.0f, -8388736.0f);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < W; ++i) {
         const float a0 = __uint_as_float(__byte_perm(ws[i], 0x4B000000u, 0x7650));
         const float a1 = __uint_as_float(__byte_perm(ws[i], 0x4B000000u, 0x7651));
         const float a2 = __uint_as_float(__byte_perm(ws[i], 0x4B000000u, 0x7652));
@@ -261,21 +306,32 @@ __device__ __forceinline__ void dequant16(const uint4& w, float2 (&f)[8]) {
     }
 }
 
+constexpr float kLazy = 8.0f;   // log2 units the running softmax reference may lag the true maximum
+
+// the lane (within a group of LPK lanes) whose owned_head<GT>() is hh
+template <int GT>
+__device__ __forceinline__ constexpr int src_sub(int hh) {
+    return GT == 4 ? (hh == 1 ? 2 : (hh == 2 ? 1 : hh)) : (GT == 2 ? hh : 0);
+}
+
+template <int W>
 struct Fetch {
-    uint4 k, v;
+    uint32_t k[W], v[W];
     float ks, vs;
 };
 
 // Same work decomposition and plan as the f32 kernel (units, items, chunks taken dynamically by
-// one block per SM, partial records combined by the block that delivers a cut unit's last one),
-// but no staging: a row is dq bytes, so the LPK = dq / 16 lanes that share a key fetch it with one
-// 16-byte load each, straight into registers, XN_KV8_PREFETCH warp iterations ahead of its use.
+// the resident blocks, partial records combined by the block that delivers a cut unit's last one),
+// but no producer warp and no barriers on the data path: a row is dq bytes, so the LPK = dq / EPL
+// lanes that share a key fetch it with one EPL-byte asynchronous copy each into a slot of shared
+// memory that only the copying thread reads back, kPrefetch warp iterations ahead of its use
+// (80 to 100 KB in flight per SM: enough to cover the HBM latency at full bandwidth).
 // Every group of LPK lanes keeps its own online-softmax state for the keys it sees and its own
-// partial accumulator for its 16 output dims; the states meet once per item, through shared
+// partial accumulator for its EPL output dims; the states meet once per item, through shared
 // memory.  Scores carry log2(e) (exp2f softmax).  No waits on other blocks or on copies: the
 // kernel cannot hang.
-template <int LPK, int GT>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int LPK, int GT, int EPL>
+__global__ void __launch_bounds__(kThreads, blocks_per_sm(EPL))
 attn_splitkv_u8_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restrict__ units,
                        const ItemDev* __restrict__ items, const int* __restrict__ chunk_item_begin,
                        int n_chunks, const int* __restrict__ page_ids,
@@ -283,26 +339,43 @@ attn_splitkv_u8_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restric
                        int* __restrict__ sync, long long pool_pages, int num_kv_heads, int head_dim,
                        float scale_log2) {
     constexpr int KPI = 32 / LPK;       // keys per warp iteration
-    constexpr int DQ = LPK * 16;        // bytes per stored row
+    constexpr int DQ = LPK * EPL;       // bytes per stored row
+    constexpr int WE = EPL / 4;         // 32-bit words of a row per lane
+    constexpr int HE = EPL / 2;         // float2 of a row per lane
     constexpr int STEP = kWarps * KPI;  // keys per block iteration
-    constexpr int PF = XN_KV8_PREFETCH;
+    constexpr int PF = kPrefetch;
+    constexpr int U = kKeysPerTrip;
+    static_assert(PF % U == 0, "the ring must hold a whole number of trips");
     constexpr unsigned kFull = 0xffffffffu;
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    float* red = reinterpret_cast<float*>(smem_raw);  // [kWarps * KPI groups][GT][DQ]
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    uint32_t* ring_k = reinterpret_cast<uint32_t*>(smem_raw);           // [PF][kThreads][WE]
+    uint32_t* ring_v = ring_k + PF * kThreads * WE;                     // [PF][kThreads][WE]
+    float2* ring_s = reinterpret_cast<float2*>(ring_v + PF * kThreads * WE);  // [PF][kThreads] (K scale, V scale)
+    float* red = reinterpret_cast<float*>(smem_raw);  // [kWarps * KPI groups][GT][DQ], while the ring is idle
     __shared__ float sm_m[kWarps][4], sm_l[kWarps][4];
     __shared__ int sm_next, sm_last;
 
     pdl_launch_dependents();
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
-    const int sub = lane % LPK, grp = lane / LPK;
+    const int sub = lane % LPK, grp = lane / LPK, gbase = lane - sub;
     const size_t blk_bytes = block_bytes(DQ);
     const size_t page_stride = size_t(num_kv_heads) * blk_bytes;
     const size_t pstride = part_stride(DQ);
 
+#ifdef XN_KV8_TIMING
+    long long tm_start = clock64(), tm_pro = 0, tm_loop = 0, tm_merge = 0, tm_t = 0;
+    int tm_items = 0, tm_iters = 0, tm_merges = 0;
+#define KT_MARK tm_t = clock64();
+#define KT_ADD(v) { long long now__ = clock64(); v += now__ - tm_t; tm_t = now__; }
+#else
+#define KT_MARK
+#define KT_ADD(v)
+#endif
     int chunk = blockIdx.x;
     while (chunk < n_chunks) {
         const int it_lo = chunk_item_begin[chunk], it_hi = chunk_item_begin[chunk + 1];
         for (int it = it_lo; it < it_hi; ++it) {
+            KT_MARK
             const ItemDev item = items[it];
             const UnitDev u = units[item.unit];
             const ReqDev& r = reqs[u.req];
@@ -314,12 +387,12 @@ attn_splitkv_u8_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restric
             const int tok_begin = item.tile_begin * kPageTokens;
             const int tok_end = min(item.tile_end * kPageTokens, u.kv_len);
 
-            float2 q2[GT][8];
+            float2 q2[GT][HE];
 #pragma unroll
             for (int hh = 0; hh < GT; ++hh)
 #pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    const int d = sub * 16 + 2 * e;
+                for (int e = 0; e < HE; ++e) {
+                    const int d = sub * EPL + 2 * e;
                     float a = 0.f, b = 0.f;
                     if (hh < u.nheads) {
                         if (d < head_dim) a = qrow[size_t(hh) * q_hs + d];
@@ -328,94 +401,203 @@ attn_splitkv_u8_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restric
                     q2[hh][e] = make_float2(a, b);
                 }
             float m[GT], l[GT];
-            float2 acc[GT][8];
+            float2 acc[GT][HE];
 #pragma unroll
             for (int hh = 0; hh < GT; ++hh) {
                 m[hh] = -INFINITY;
                 l[hh] = 0.f;
 #pragma unroll
-                for (int e = 0; e < 8; ++e) acc[hh][e] = make_float2(0.f, 0.f);
+                for (int e = 0; e < HE; ++e) acc[hh][e] = make_float2(0.f, 0.f);
             }
 
-            auto fetch = [&](Fetch& f, int kk) {
+            // one commit group per warp iteration, empty past the item's end, so that "all but the
+            // newest PF - 1 groups" always names the iteration about to be used
+            // (an item starts on a page boundary and a warp iteration never straddles one, so the
+            // page's block address only changes when kk reaches a multiple of the page size)
+            const uint8_t* page_blk = nullptr;
+            auto issue = [&](int stage, int kk) {
                 const int key = kk + grp;
+                if (kk < tok_end && (kk % kPageTokens) == w * KPI)
+                    page_blk = base + size_t(pages[kk / kPageTokens]) * page_stride;
                 if (key < tok_end) {
-                    const uint8_t* b = base + size_t(pages[kk / kPageTokens]) * page_stride;
+                    const uint8_t* b = page_blk;
                     const int tk = key % kPageTokens;
-                    f.k = __ldg(reinterpret_cast<const uint4*>(b + size_t(tk) * DQ + sub * 16));
-                    f.v = __ldg(reinterpret_cast<const uint4*>(b + size_t(kPageTokens + tk) * DQ + sub * 16));
+                    const int slot = stage * kThreads + tid;
+                    if constexpr (EPL == 16) {
+                        cp_async16(ring_k + slot * WE, b + size_t(tk) * DQ + sub * EPL);
+                        cp_async16(ring_v + slot * WE, b + size_t(kPageTokens + tk) * DQ + sub * EPL);
+                    } else {
+                        cp_async8(ring_k + slot * WE, b + size_t(tk) * DQ + sub * EPL);
+                        cp_async8(ring_v + slot * WE, b + size_t(kPageTokens + tk) * DQ + sub * EPL);
+                    }
                     const float* sc = reinterpret_cast<const float*>(b + 2 * size_t(kPageTokens) * DQ);
-                    f.ks = __ldg(sc + tk);
-                    f.vs = __ldg(sc + kPageTokens + tk);
-                } else {
-                    f.k = f.v = make_uint4(0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u);
-                    f.ks = f.vs = 0.f;
+                    cp_async4(&ring_s[slot].x, sc + tk);
+                    cp_async4(&ring_s[slot].y, sc + kPageTokens + tk);
                 }
+                cp_async_commit();
             };
 
-            Fetch f[PF];
-            int key0 = tok_begin + w * KPI;
+            const int key_first = tok_begin + w * KPI;
 #pragma unroll
-            for (int p = 0; p < PF; ++p) fetch(f[p], key0 + p * STEP);
-            for (; key0 < tok_end; key0 += PF * STEP) {
+            for (int p = 0; p < PF; ++p) issue(p, key_first + p * STEP);
+#ifdef XN_KV8_TIMING
+            cp_async_wait<PF - 1>();
+            if (q2[0][0].x == 123456.789f) tm_items += 100;   // the query rows have arrived
+            ++tm_items;
+            tm_iters += (tok_end - key_first + STEP - 1) / STEP;
+#endif
+            KT_ADD(tm_pro)
+            for (int key0 = key_first; key0 < tok_end; key0 += PF * STEP) {
 #pragma unroll
-                for (int p = 0; p < PF; ++p) {
+                for (int p = 0; p < PF; p += U) {
                     const int kk = key0 + p * STEP;
                     if (kk >= tok_end) break;  // the same for every lane of the warp
-                    const Fetch cur = f[p];
-                    fetch(f[p], kk + PF * STEP);
-                    const bool valid = kk + grp < tok_end;
-
-                    // ---- scores of this group's key for the unit's heads ----
-                    float2 kf[8];
-                    dequant16(cur.k, kf);
-                    float dot[GT];
+                    // U keys per lane and trip: their instruction chains are independent up to the
+                    // softmax bookkeeping, which they share
+                    cp_async_wait<PF - U>();
+                    Fetch<WE> cur[U];
+                    bool valid[U];
 #pragma unroll
-                    for (int hh = 0; hh < GT; ++hh) {
-                        float2 a = make_float2(0.f, 0.f);
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) a = __ffma2_rn(q2[hh][e], kf[e], a);
-                        dot[hh] = a.x + a.y;
+                    for (int u = 0; u < U; ++u) {
+                        // a lane past the item's end reads whatever its slot holds: its score is
+                        // forced to -inf and its weight to 0 below; stored bytes are always finite
+                        const int slot = (p + u) * kThreads + tid;
+                        if constexpr (EPL == 16) {
+                            const uint4 a = *reinterpret_cast<const uint4*>(ring_k + slot * WE);
+                            const uint4 b = *reinterpret_cast<const uint4*>(ring_v + slot * WE);
+                            cur[u].k[0] = a.x; cur[u].k[1] = a.y; cur[u].k[2] = a.z; cur[u].k[3] = a.w;
+                            cur[u].v[0] = b.x; cur[u].v[1] = b.y; cur[u].v[2] = b.z; cur[u].v[3] = b.w;
+                        } else {
+                            const uint2 a = *reinterpret_cast<const uint2*>(ring_k + slot * WE);
+                            const uint2 b = *reinterpret_cast<const uint2*>(ring_v + slot * WE);
+                            cur[u].k[0] = a.x; cur[u].k[1] = a.y;
+                            cur[u].v[0] = b.x; cur[u].v[1] = b.y;
+                        }
+                        const float2 sc = ring_s[slot];
+                        cur[u].ks = sc.x;
+                        cur[u].vs = sc.y;
+                        valid[u] = kk + u * STEP + grp < tok_end;
                     }
 #pragma unroll
-                    for (int o = 1; o < LPK; o <<= 1)
-#pragma unroll
-                        for (int hh = 0; hh < GT; ++hh) dot[hh] += __shfl_xor_sync(kFull, dot[hh], o);
+                    for (int u = 0; u < U; ++u) issue(p + u, kk + (PF + u) * STEP);  // the slots' next use
 
-                    // ---- online softmax, per group ----
-                    const float ksc = cur.ks * scale_log2;
-                    float s[GT];
-                    bool moved = false;
+                    // ---- scores of this group's keys for the unit's heads ----
+                    float dot[U][GT];
 #pragma unroll
-                    for (int hh = 0; hh < GT; ++hh) {
-                        s[hh] = valid ? dot[hh] * ksc : -INFINITY;
-                        moved |= s[hh] > m[hh];
-                    }
-                    if (__any_sync(kFull, moved)) {
+                    for (int u = 0; u < U; ++u) {
+                        float2 kf[HE];
+                        dequant<WE>(cur[u].k, kf);
 #pragma unroll
                         for (int hh = 0; hh < GT; ++hh) {
-                            const float m_new = fmaxf(m[hh], s[hh]);
-                            const float alpha = (m_new == -INFINITY) ? 1.f : exp2f(m[hh] - m_new);
-                            m[hh] = m_new;
-                            l[hh] *= alpha;
-                            const float2 a2 = make_float2(alpha, alpha);
+                            float2 a = make_float2(0.f, 0.f);
 #pragma unroll
-                            for (int e = 0; e < 8; ++e) acc[hh][e] = __fmul2_rn(acc[hh][e], a2);
+                            for (int e = 0; e < HE; ++e) a = __ffma2_rn(q2[hh][e], kf[e], a);
+                            dot[u][hh] = a.x + a.y;
                         }
                     }
-                    float2 vf[8];
-                    dequant16(cur.v, vf);
+                    // ---- online softmax.  The running reference m only has to stay within
+                    // 2^kLazy of the true maximum (weights up to 2^8 are harmless in f32), so it
+                    // moves -- and the accumulators are rescaled -- only on a jump of more than kLazy.
+                    float pv[U][GT];
+                    if constexpr (LPK >= GT) {
+                        // every lane ends up with the score of ONE head (owned_head(sub)): GT - 1 +
+                        // log2(LPK / GT) shuffles instead of GT * log2(LPK), one exp2f instead of GT
+                        float s_own[U], smax = -INFINITY;
 #pragma unroll
-                    for (int hh = 0; hh < GT; ++hh) {
-                        const float p = valid ? exp2f(s[hh] - m[hh]) : 0.f;
-                        l[hh] += p;
-                        const float pv = p * cur.vs;
-                        const float2 p2 = make_float2(pv, pv);
+                        for (int u = 0; u < U; ++u) {
+                            const float d = group_reduce<GT, LPK>(dot[u], sub);
+                            s_own[u] = valid[u] ? d * (cur[u].ks * scale_log2) : -INFINITY;
+                            smax = fmaxf(smax, s_own[u]);
+                        }
+                        const bool moved = smax > m[0] + kLazy;
+                        if (__any_sync(kFull, moved)) {
+                            const float alpha = moved ? exp2f(m[0] - smax) : 1.f;
+                            if (moved) m[0] = smax;
+                            l[0] *= alpha;
 #pragma unroll
-                        for (int e = 0; e < 8; ++e) acc[hh][e] = __ffma2_rn(p2, vf[e], acc[hh][e]);
+                            for (int hh = 0; hh < GT; ++hh) {
+                                const float a = __shfl_sync(kFull, alpha, gbase + src_sub<GT>(hh));
+                                const float2 a2 = make_float2(a, a);
+#pragma unroll
+                                for (int e = 0; e < HE; ++e) acc[hh][e] = __fmul2_rn(acc[hh][e], a2);
+                            }
+                        }
+#pragma unroll
+                        for (int u = 0; u < U; ++u) {
+                            const float pw = valid[u] ? exp2f(s_own[u] - m[0]) : 0.f;
+                            l[0] += pw;
+                            const float pvs = valid[u] ? pw * cur[u].vs : 0.f;   // (a stale scale may be anything)
+#pragma unroll
+                            for (int hh = 0; hh < GT; ++hh)
+                                pv[u][hh] = __shfl_sync(kFull, pvs, gbase + src_sub<GT>(hh));
+                        }
+                    } else {
+                        float sc_all[U][GT], smax[GT];
+#pragma unroll
+                        for (int hh = 0; hh < GT; ++hh) smax[hh] = -INFINITY;
+#pragma unroll
+                        for (int u = 0; u < U; ++u) {
+#pragma unroll
+                            for (int o = 1; o < LPK; o <<= 1)
+#pragma unroll
+                                for (int hh = 0; hh < GT; ++hh)
+                                    dot[u][hh] += __shfl_xor_sync(kFull, dot[u][hh], o);
+#pragma unroll
+                            for (int hh = 0; hh < GT; ++hh) {
+                                sc_all[u][hh] = valid[u] ? dot[u][hh] * (cur[u].ks * scale_log2) : -INFINITY;
+                                smax[hh] = fmaxf(smax[hh], sc_all[u][hh]);
+                            }
+                        }
+                        bool moved = false;
+#pragma unroll
+                        for (int hh = 0; hh < GT; ++hh) moved |= smax[hh] > m[hh] + kLazy;
+                        if (__any_sync(kFull, moved)) {
+#pragma unroll
+                            for (int hh = 0; hh < GT; ++hh) {
+                                const bool mv = smax[hh] > m[hh] + kLazy;
+                                const float alpha = mv ? exp2f(m[hh] - smax[hh]) : 1.f;
+                                if (mv) m[hh] = smax[hh];
+                                l[hh] *= alpha;
+                                const float2 a2 = make_float2(alpha, alpha);
+#pragma unroll
+                                for (int e = 0; e < HE; ++e) acc[hh][e] = __fmul2_rn(acc[hh][e], a2);
+                            }
+                        }
+#pragma unroll
+                        for (int u = 0; u < U; ++u)
+#pragma unroll
+                            for (int hh = 0; hh < GT; ++hh) {
+                                const float pw = valid[u] ? exp2f(sc_all[u][hh] - m[hh]) : 0.f;
+                                l[hh] += pw;
+                                pv[u][hh] = valid[u] ? pw * cur[u].vs : 0.f;
+                            }
+                    }
+                    // ---- weighted V rows ----
+#pragma unroll
+                    for (int u = 0; u < U; ++u) {
+                        float2 vf[HE];
+                        dequant<WE>(cur[u].v, vf);
+#pragma unroll
+                        for (int hh = 0; hh < GT; ++hh) {
+                            const float2 p2 = make_float2(pv[u][hh], pv[u][hh]);
+#pragma unroll
+                            for (int e = 0; e < HE; ++e) acc[hh][e] = __ffma2_rn(p2, vf[e], acc[hh][e]);
+                        }
                     }
                 }
             }
+
+            if constexpr (LPK >= GT) {
+                // back to one (m, l) per head on every lane of the group, for the merge below
+                const float m_own = m[0], l_own = l[0];
+#pragma unroll
+                for (int hh = 0; hh < GT; ++hh) {
+                    m[hh] = __shfl_sync(kFull, m_own, gbase + src_sub<GT>(hh));
+                    l[hh] = __shfl_sync(kFull, l_own, gbase + src_sub<GT>(hh));
+                }
+            }
+            cp_async_wait<0>();   // nothing of this item is still on its way into the ring
+            KT_ADD(tm_loop)
 
             // ---- the block's group states meet ----
 #pragma unroll
@@ -426,7 +608,7 @@ attn_splitkv_u8_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restric
                 if (lane == 0) sm_m[w][hh] = wm;
             }
             __syncthreads();
-            float* mine = red + (size_t(w * KPI + grp) * GT) * DQ + sub * 16;
+            float* mine = red + (size_t(w * KPI + grp) * GT) * DQ + sub * EPL;
 #pragma unroll
             for (int hh = 0; hh < GT; ++hh) {
                 float M = -INFINITY;
@@ -438,7 +620,7 @@ attn_splitkv_u8_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restric
                 for (int o = 16; o > 0; o >>= 1) lv += __shfl_xor_sync(kFull, lv, o);
                 if (lane == 0) sm_l[w][hh] = lv;
 #pragma unroll
-                for (int e = 0; e < 8; e += 2)
+                for (int e = 0; e < HE; e += 2)
                     *reinterpret_cast<float4*>(mine + size_t(hh) * DQ + 2 * e) =
                         make_float4(acc[hh][e].x * fct, acc[hh][e].y * fct, acc[hh][e + 1].x * fct,
                                     acc[hh][e + 1].y * fct);
@@ -457,7 +639,7 @@ attn_splitkv_u8_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restric
                     L += sm_l[ww][hh];
                 }
                 if (item.part < 0) {
-                    if (d < head_dim) orow[size_t(hh) * o_hs + d] = sum / L;
+                    if (d < head_dim) orow[size_t(hh) * o_hs + d] = sum * (1.0f / L);
                 } else {
                     float* rec = partials + (size_t(item.part) * GT + hh) * pstride;
                     if (d == 0) {
@@ -482,32 +664,91 @@ attn_splitkv_u8_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restric
                     sm_last = last;
                 }
                 __syncthreads();
-                if (sm_last) {
-                    for (int e = tid; e < GT * DQ; e += kThreads) {
-                        const int hh = e / DQ, d = e % DQ;
-                        if (hh >= u.nheads || d >= head_dim) continue;
-                        float M = -INFINITY;
-                        for (int i = 0; i < u.part_count; ++i)
-                            M = fmaxf(M, __ldcg(partials + (size_t(u.part_begin + i) * GT + hh) * pstride));
-                        float L = 0.f, sum = 0.f;
-                        for (int i = 0; i < u.part_count; ++i) {
-                            const float* rec = partials + (size_t(u.part_begin + i) * GT + hh) * pstride;
-                            const float mi = __ldcg(rec);
-                            const float wgt = (mi == -INFINITY) ? 0.f : exp2f(mi - M);
-                            L += __ldcg(rec + 1) * wgt;
-                            sum = fmaf(wgt, __ldcg(rec + 4 + d), sum);
+                if (sm_last && w == 0) {
+                    // One warp combines the unit's partial records, all heads at once.  Lane i takes
+                    // the (m, l) pairs of record i (32 records at a time, merged online), the
+                    // weights travel by shuffle, and the accumulator loads of several records are
+                    // all independent of one another, so they overlap instead of paying the L2
+                    // latency one by one.
+                    constexpr int J = (DQ + 31) / 32;
+                    const size_t rstride = size_t(GT) * pstride;
+                    const float* rec0 = partials + size_t(u.part_begin) * rstride;
+                    float Mrun[GT], L[GT], sum[GT][J];
+#pragma unroll
+                    for (int hh = 0; hh < GT; ++hh) {
+                        Mrun[hh] = -INFINITY;
+                        L[hh] = 0.f;
+#pragma unroll
+                        for (int j = 0; j < J; ++j) sum[hh][j] = 0.f;
+                    }
+                    for (int i0 = 0; i0 < u.part_count; i0 += 32) {
+                        const int cnt = min(32, u.part_count - i0);
+                        float mi[GT], li[GT], wgt[GT];
+#pragma unroll
+                        for (int hh = 0; hh < GT; ++hh) {
+                            const float* rec = rec0 + size_t(i0 + lane) * rstride + size_t(hh) * pstride;
+                            mi[hh] = lane < cnt ? __ldcg(rec) : -INFINITY;
+                            li[hh] = lane < cnt ? __ldcg(rec + 1) : 0.f;
                         }
-                        orow[size_t(hh) * o_hs + d] = sum / L;
+#pragma unroll
+                        for (int hh = 0; hh < GT; ++hh) {
+                            float mb = mi[hh];
+#pragma unroll
+                            for (int o = 16; o > 0; o >>= 1) mb = fmaxf(mb, __shfl_xor_sync(kFull, mb, o));
+                            const float mn = fmaxf(Mrun[hh], mb);
+                            const float alpha = (Mrun[hh] == -INFINITY) ? 0.f : exp2f(Mrun[hh] - mn);
+                            wgt[hh] = (mi[hh] == -INFINITY) ? 0.f : exp2f(mi[hh] - mn);
+                            float lw = li[hh] * wgt[hh];
+#pragma unroll
+                            for (int o = 16; o > 0; o >>= 1) lw += __shfl_xor_sync(kFull, lw, o);
+                            L[hh] = L[hh] * alpha + lw;
+#pragma unroll
+                            for (int j = 0; j < J; ++j) sum[hh][j] *= alpha;
+                            Mrun[hh] = mn;
+                        }
+#pragma unroll 4
+                        for (int i = 0; i < cnt; ++i) {
+                            const float* rec = rec0 + size_t(i0 + i) * rstride + 4;
+#pragma unroll
+                            for (int hh = 0; hh < GT; ++hh) {
+                                const float wi = __shfl_sync(kFull, wgt[hh], i);
+#pragma unroll
+                                for (int j = 0; j < J; ++j) {
+                                    const int d = lane + 32 * j;
+                                    if (d < DQ) sum[hh][j] = fmaf(wi, __ldcg(rec + size_t(hh) * pstride + d), sum[hh][j]);
+                                }
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int hh = 0; hh < GT; ++hh) {
+                        if (hh >= u.nheads) break;
+                        const float inv = 1.0f / L[hh];
+#pragma unroll
+                        for (int j = 0; j < J; ++j) {
+                            const int d = lane + 32 * j;
+                            if (d < head_dim) orow[size_t(hh) * o_hs + d] = sum[hh][j] * inv;
+                        }
                     }
                 }
             }
             __syncthreads();  // red, sm_m, sm_l and sm_last are rewritten by the next item
+#ifdef XN_KV8_TIMING
+            if (item.part >= 0 && sm_last) ++tm_merges;
+#endif
+            KT_ADD(tm_merge)
         }
         if (tid == 0) sm_next = atomicAdd(&sync[kSyncChunk], 1) + int(gridDim.x);
         __syncthreads();
         chunk = sm_next;
         __syncthreads();
     }
+#ifdef XN_KV8_TIMING
+    if (tid == 0 && (blockIdx.x % 97) == 0)
+        printf("block %4d: total %lld clk, %d items %d iters %d final merges: prologue %lld loop %lld (%lld/iter) merge %lld\n",
+               blockIdx.x, clock64() - tm_start, tm_items, tm_iters, tm_merges, tm_pro, tm_loop,
+               tm_iters ? tm_loop / tm_iters : 0, tm_merge);
+#endif
     if (tid == 0) {
         // the last block to finish re-arms the chunk counter for the next launch
         __threadfence();
