@@ -16,8 +16,13 @@ pub struct XnCtxDesc {
     pub head_dim: i32, pub page_tokens: i32, pub pool_pages: i64, pub pool_bytes: i64,
     pub shuffle_seed: u64, pub max_pos: i32, pub prefill_mode: i32,
     pub rope_cos: *const f32, pub rope_sin: *const f32, pub cuda_stream: *mut c_void,
-    pub batch_window_us: i32, pub reserved: i32,
+    pub batch_window_us: i32, pub kv_format: i32,
 }
+
+/// `XnCtxDesc::kv_format`: the f32 cache `fast_attention` reads, or only the u8 shadow of
+/// `CpuRingCache::new(.., use_u8 = true)` (src/nn/fast_attention.rs:42-50) as the cache itself.
+pub const XN_KV_F32: i32 = 0;
+pub const XN_KV_U8: i32 = 1;
 
 extern "C" {
     fn xn_ctx_create(d: *const XnCtxDesc, out: *mut *mut XnCtx) -> i32;
@@ -91,7 +96,7 @@ fn shared_context(device: i32, layers: usize, heads: usize, kv_heads: usize, dim
     let desc = XnCtxDesc { device, num_layers: layers as i32, num_heads: heads as i32,
         num_kv_heads: kv_heads as i32, head_dim: dim as i32, page_tokens: 64, pool_pages: pages,
         pool_bytes: 0, shuffle_seed: 0, max_pos: 0, prefill_mode: 0, rope_cos: std::ptr::null(),
-        rope_sin: std::ptr::null(), cuda_stream: std::ptr::null_mut(), batch_window_us: 0, reserved: 0 };
+        rope_sin: std::ptr::null(), cuda_stream: std::ptr::null_mut(), batch_window_us: 0, kv_format: XN_KV_F32 };
     let mut raw: *mut XnCtx = std::ptr::null_mut();
     let rc = unsafe { xn_ctx_create(&desc, &mut raw) };
     if rc != 0 {
