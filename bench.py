@@ -797,7 +797,7 @@ def run_gpu_arm(args):
                 cache.append(0, 0, kk, vv)
             y_ref, _ = xo.causal_self_attention_forward(
                 x_h[layer, i].numpy().reshape(1, 1, hidden), L - 1, 0, cache, rope[0], rope[1], ref_q, ref_k, ref_v,
-                Hq, Hkv, D, norm_w, 1e-5, ref_o)
+                Hq, Hkv, D, norm_w, 1e-5, ref_o, kv_u8=u8)
             got = o_h[layer, i].numpy().reshape(1, 1, hidden)
             worst = max(worst, float(np.linalg.norm(got - y_ref) / np.linalg.norm(y_ref)))
         line["parity_vs_cpu_sample"] = {"rel_l2": worst, "streams": min(4, n_streams), "layer": layer,

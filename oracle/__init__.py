@@ -467,7 +467,7 @@ def attention_out_block(y, norm_weight, eps, o_proj: TernaryLinear, threads: int
 def causal_self_attention_forward(x, index_pos, layer_idx, cache: "RingCache", cos, sin,
                                   q_proj: TernaryLinear, k_proj: TernaryLinear, v_proj: TernaryLinear,
                                   num_heads, num_kv_heads, head_dim, sub_norm_weight, eps,
-                                  o_proj: TernaryLinear, threads: int = 0):
+                                  o_proj: TernaryLinear, threads: int = 0, kv_u8: bool = False):
     """CausalSelfAttention::forward (models/llama/attention.rs:40-108) for ternary projections:
     x [1,S,hidden] -> q/k/v projections (each quantises the rows of x the same way, as the fused
     single-token path of bit1_58/layers.rs:347-424 does once) -> heads layout -> RoPE ->
@@ -479,6 +479,8 @@ def causal_self_attention_forward(x, index_pos, layer_idx, cache: "RingCache", c
     v = transpose_seq_to_heads(v_proj.forward(x, threads), num_kv_heads, head_dim)
     q = tensor_rope(q, cos, sin, index_pos)
     k = tensor_rope(k, cos, sin, index_pos)
+    if kv_u8:   # checker of the u8 cache format: the cache holds (and returns) the round-tripped rows
+        k, v = u8_round_trip(k), u8_round_trip(v)
     attn = fast_attention(q, k, v, layer_idx, index_pos, cache, num_heads, num_kv_heads, head_dim, threads)
     return attention_out_block(attn, sub_norm_weight, eps, o_proj, threads), attn
 

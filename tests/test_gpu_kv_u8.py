@@ -296,3 +296,51 @@ def test_pool_bytes_buys_four_times_the_pages():
     assert 3.8 * pa < pb <= 4 * pa
     a.close()
     b.close()
+
+
+def test_whole_block_over_u8_cache():
+    # q/k/v projections -> RoPE -> quantised append -> attention -> sub-norm -> o_proj, all on the
+    # device: the stored bytes equal the oracle's shadow of the projected, rotated rows bit for
+    # bit; the attention rows keep the f32 bounds; the block output keeps the whole-block bound
+    # (rel L2 <= 1e-3: an activation may quantise one step apart)
+    xo.set_quant_body(1)
+    try:
+        rng = np.random.default_rng(61)
+        Hq, Hkv, D, hidden, layer = 20, 5, 128, 2560, 1
+        rope = xn.rope_tables(500000.0, D, 1024)
+        ctx = u8_ctx(2, Hq, Hkv, D, 40, rope=rope, shuffle_seed=3)
+        mk = lambda o, i: rng.standard_normal((o, i)).astype(np.float32)
+        ws = {"q": mk(Hq * D, hidden), "k": mk(Hkv * D, hidden), "v": mk(Hkv * D, hidden), "o": mk(hidden, Hq * D)}
+        scale = {n: (float(hidden) ** -0.5 if n != "o" else None) for n in ws}
+        dev = {n: xn.TernaryLinear(w.shape[1], w.shape[0], w, xn.PACK4, scale[n]) for n, w in ws.items()}
+        ref = {n: xo.TernaryLinear(w.shape[1], w.shape[0], w, xn.PACK4, scale[n]) for n, w in ws.items()}
+        nw = (1.0 + 0.2 * rng.standard_normal(Hq * D)).astype(np.float32)
+        ctx.set_qkv_proj(layer, dev["q"], dev["k"], dev["v"])
+        ctx.set_out_proj(layer, dev["o"], nw, 1e-5)
+        lens = [70, 300]
+        pairs = [(ctx.new_stream(1024), xo.RingCache(2, Hkv, 1024, D)) for _ in lens]
+        oracle = lambda x, pos, cache: xo.causal_self_attention_forward(
+            x, pos, layer, cache, rope[0], rope[1], ref["q"], ref["k"], ref["v"], Hq, Hkv, D, nw, 1e-5,
+            ref["o"], kv_u8=True)
+        for (st, cache), L in zip(pairs, lens):
+            x = rng.standard_normal((1, L, hidden)).astype(np.float32)
+            attn_dev = ctx.attention_batch([st], layer, [0], [x], qkv_proj=True)[0]
+            _, attn_ref = oracle(x, 0, cache)
+            assert_parity(attn_dev, xo.transpose_heads_to_seq(attn_ref), f"prefill rows L={L}")
+        xs = [rng.standard_normal((1, 1, hidden)).astype(np.float32) for _ in lens]
+        y_dev = ctx.attention_batch([p[0] for p in pairs], layer, lens, xs, qkv_proj=True, out_proj=True)
+        for i, (st, cache) in enumerate(pairs):
+            y_ref, _ = oracle(xs[i], lens[i], cache)
+            assert errs(y_dev[i], y_ref)[1] <= 1e-3, f"block output, stream {i}"
+            # cache: dequantised rows equal the oracle ring (which holds the round-tripped rows) ...
+            k, v = st.read_range(layer, 0, lens[i] + 1)
+            kb = cache.k_buffer(layer).reshape(Hkv, 1024, D)[:, :lens[i] + 1]
+            vb = cache.v_buffer(layer).reshape(Hkv, 1024, D)[:, :lens[i] + 1]
+            assert np.array_equal(k, kb) and np.array_equal(v, vb)
+            # ... and they are what the stored bytes and scales say
+            k8, v8, ks, vs = st.read_u8(layer, 0, lens[i] + 1)
+            assert np.array_equal((k8.astype(np.float32) - 128.0) * ks[..., None], k)
+            assert np.array_equal((v8.astype(np.float32) - 128.0) * vs[..., None], v)
+        ctx.close()
+    finally:
+        xo.set_quant_body(-1)

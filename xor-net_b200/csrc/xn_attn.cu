@@ -227,7 +227,8 @@ SplitKernel pick_split(int nv_class, int gt, bool exact) {
 }
 
 using Split8Fn = void (*)(const ReqDev*, const UnitDev*, const ItemDev*, const int*, int, const int*,
-                          const uint8_t*, float*, int*, long long, int, int, float);
+                          const uint8_t*, float*, int*, long long, int, int, float, const float*,
+                          const float*);
 
 template <int DQ, int EPL>
 Split8Fn pick8_gt(int gt) {
@@ -590,14 +591,21 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
     // the new token itself: no separate append launch.  Needs rows the bulk copies can take
     // (head_dim % 4 == 0, 16-byte aligned pointers) and, for RoPE, the pair layout of head_dim
     // 64 / 128.
-    bool fused = c->fuse_append && !c->kv_u8 && n_ring_rows == 0 && D % 4 == 0 && c->nv_class <= 32;
+    // (u8 cache format: rows without padding, i.e. head_dim a power of two >= 16; the rotation needs
+    // at least two lanes per row; plain loads, so no alignment condition.)
+    bool fused = c->fuse_append && n_ring_rows == 0 &&
+                 (c->kv_u8 ? D == c->dq : (D % 4 == 0 && c->nv_class <= 32));
     for (int i = 0; i < n && fused; ++i) {
         const xn_req& r = reqs[i];
         if (r.seq_len != 1) { fused = false; break; }
         const bool qkv = r.flags & XN_REQ_QKV_PROJ;   // q, k, v then live in the library's aligned rows
-        if (((r.flags & XN_REQ_ROPE) || qkv) && !(c->nv_exact && (c->nv == 16 || c->nv == 32))) fused = false;
-        if (pinned && !c->fuse_pinned) fused = false;
-        if ((!host_mode || pinned) && !qkv)
+        if (((r.flags & XN_REQ_ROPE) || qkv) &&
+            !(c->kv_u8 ? c->dq >= 32 : (c->nv_exact && (c->nv == 16 || c->nv == 32))))
+            fused = false;
+        // (u8 kernel: a lane reads its slice of q, k and v with plain 4-byte loads, which is slow
+        // over PCIe; page-locked host rows go through the append kernel's coalesced copy instead)
+        if (pinned && (c->kv_u8 || !c->fuse_pinned)) fused = false;
+        if ((!host_mode || pinned) && !qkv && !c->kv_u8)
             if ((reinterpret_cast<uintptr_t>(r.q) | reinterpret_cast<uintptr_t>(r.k) |
                  reinterpret_cast<uintptr_t>(r.v)) & 15)
                 fused = false;
@@ -865,7 +873,7 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         pick_split8(c->dq, c->gt, c->kv8_epl)<<<std::min(sp.ctas, c->decode_ctas), kv8::kThreads,
                                                 kv8::smem_bytes(c->gt, c->kv8_epl), c->stream>>>(
             reqs_d, units_d, items_d, cta_d, sp.ctas, pages_d, c->pool8, c->partials, c->sync_d,
-            c->pool_pages, Hkv, D, c->scale * 1.4426950408889634f);
+            c->pool_pages, Hkv, D, c->scale * 1.4426950408889634f, c->cos_d, c->sin_d);
         if (c->profile && (rc = profile_end(c)) != XN_OK) return rc;
         c->stats.kernel_launches += 1;
         c->stats.decode_launches += 1;

@@ -314,6 +314,44 @@ __device__ __forceinline__ constexpr int src_sub(int hh) {
     return GT == 4 ? (hh == 1 ? 2 : (hh == 2 ? 1 : hh)) : (GT == 2 ? hh : 0);
 }
 
+// quantize_to_u8 (src/nn/fast_attention.rs:62-71) for a row spread over the LPK lanes of a group,
+// EPL elements per lane: the same operations as quantize_row_store, so the same bytes and scale.
+template <int LPK, int EPL>
+__device__ __forceinline__ void quantize_group(const float (&x)[EPL], uint32_t (&w)[EPL / 4], float& scale) {
+    float mx = 0.f;
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) mx = fmaxf(mx, fabsf(x[j]));
+#pragma unroll
+    for (int o = 1; o < LPK; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    scale = mx > 0.f ? __fdiv_rn(mx, 127.0f) : 1.0f;
+    const float inv = __fdiv_rn(1.0f, scale);
+#pragma unroll
+    for (int i = 0; i < EPL / 4; ++i) w[i] = 0u;
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) {
+        float r = roundf(__fadd_rn(__fmul_rn(x[j], inv), 128.0f));
+        r = fminf(fmaxf(r, 0.0f), 255.0f);
+        w[j / 4] |= uint32_t(r) << (8 * (j % 4));
+    }
+}
+
+// Rotate-half RoPE (src/nn/fast_attention_simd.rs:380-387) of a row spread over the LPK >= 2 lanes of a
+// group with head_dim == LPK * EPL: the partner of element (sub, j) sits on lane sub ^ (LPK / 2)
+// at the same j.  cs / sn are the table rows of the position.  Unfused multiplies, as the reference.
+template <int LPK, int EPL>
+__device__ __forceinline__ void rope_group(float (&x)[EPL], const float* __restrict__ cs,
+                                           const float* __restrict__ sn, int sub) {
+    const bool lo = sub < LPK / 2;
+    const int d0 = (sub % (LPK / 2)) * EPL;
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) {
+        const float other = __shfl_xor_sync(0xffffffffu, x[j], LPK / 2);
+        const float c = cs[d0 + j], s = sn[d0 + j];
+        x[j] = lo ? __fsub_rn(__fmul_rn(x[j], c), __fmul_rn(other, s))
+                  : __fadd_rn(__fmul_rn(other, s), __fmul_rn(x[j], c));
+    }
+}
+
 template <int W>
 struct Fetch {
     uint32_t k[W], v[W];
@@ -337,7 +375,8 @@ attn_splitkv_u8_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restric
                        int n_chunks, const int* __restrict__ page_ids,
                        const uint8_t* __restrict__ pool, float* __restrict__ partials,
                        int* __restrict__ sync, long long pool_pages, int num_kv_heads, int head_dim,
-                       float scale_log2) {
+                       float scale_log2, const float* __restrict__ cos_t,
+                       const float* __restrict__ sin_t) {
     constexpr int KPI = 32 / LPK;       // keys per warp iteration
     constexpr int DQ = LPK * EPL;       // bytes per stored row
     constexpr int WE = EPL / 4;         // 32-bit words of a row per lane
@@ -400,6 +439,32 @@ attn_splitkv_u8_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restric
                     }
                     q2[hh][e] = make_float2(a, b);
                 }
+            // Fused append (ReqDev flag 8: one new token, not yet in the cache): the unit's last key is
+            // taken from the request, rotated when asked, quantised here and stored by the unit
+            // that owns the store; the query rows are rotated here as well.  Needs head_dim == DQ.
+            const bool fused = r.flags & 8u;
+            const bool fused_rope = fused && (r.flags & 1u);
+            const bool fused_new = fused && tok_end == u.kv_len;
+            const int loop_end = fused_new ? tok_end - 1 : tok_end;
+            if constexpr (LPK >= 2) {
+                if (fused_rope) {
+                    const int half = head_dim / 2;
+                    const float* cs = cos_t + size_t(r.index_pos) * half;
+                    const float* sn = sin_t + size_t(r.index_pos) * half;
+#pragma unroll
+                    for (int hh = 0; hh < GT; ++hh) {
+                        float x[EPL];
+#pragma unroll
+                        for (int e = 0; e < HE; ++e) {
+                            x[2 * e] = q2[hh][e].x;
+                            x[2 * e + 1] = q2[hh][e].y;
+                        }
+                        rope_group<LPK, EPL>(x, cs, sn, sub);
+#pragma unroll
+                        for (int e = 0; e < HE; ++e) q2[hh][e] = make_float2(x[2 * e], x[2 * e + 1]);
+                    }
+                }
+            }
             float m[GT], l[GT];
             float2 acc[GT][HE];
 #pragma unroll
@@ -417,9 +482,9 @@ attn_splitkv_u8_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restric
             const uint8_t* page_blk = nullptr;
             auto issue = [&](int stage, int kk) {
                 const int key = kk + grp;
-                if (kk < tok_end && (kk % kPageTokens) == w * KPI)
+                if (kk < loop_end && (kk % kPageTokens) == w * KPI)
                     page_blk = base + size_t(pages[kk / kPageTokens]) * page_stride;
-                if (key < tok_end) {
+                if (key < loop_end) {
                     const uint8_t* b = page_blk;
                     const int tk = key % kPageTokens;
                     const int slot = stage * kThreads + tid;
@@ -444,14 +509,122 @@ attn_splitkv_u8_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restric
             cp_async_wait<PF - 1>();
             if (q2[0][0].x == 123456.789f) tm_items += 100;   // the query rows have arrived
             ++tm_items;
-            tm_iters += (tok_end - key_first + STEP - 1) / STEP;
+            tm_iters += (loop_end - key_first + STEP - 1) / STEP;
 #endif
             KT_ADD(tm_pro)
-            for (int key0 = key_first; key0 < tok_end; key0 += PF * STEP) {
+            // One trip: U keys per lane (their instruction chains are independent up to the softmax
+            // bookkeeping, which they share).
+            auto trip = [&](const Fetch<WE> (&cur)[U], const bool (&valid)[U]) {
+                // ---- scores of this group's keys for the unit's heads ----
+                float dot[U][GT];
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    float2 kf[HE];
+                    dequant<WE>(cur[u].k, kf);
+#pragma unroll
+                    for (int hh = 0; hh < GT; ++hh) {
+                        float2 a = make_float2(0.f, 0.f);
+#pragma unroll
+                        for (int e = 0; e < HE; ++e) a = __ffma2_rn(q2[hh][e], kf[e], a);
+                        dot[u][hh] = a.x + a.y;
+                    }
+                }
+                // ---- online softmax.  The running reference m only has to stay within
+                // 2^kLazy of the true maximum (weights up to 2^8 are harmless in f32), so it
+                // moves -- and the accumulators are rescaled -- only on a jump of more than kLazy.
+                float pv[U][GT];
+                if constexpr (LPK >= GT) {
+                    // every lane ends up with the score of ONE head (owned_head(sub)): GT - 1 +
+                    // log2(LPK / GT) shuffles instead of GT * log2(LPK), one exp2f instead of GT
+                    float s_own[U], smax = -INFINITY;
+#pragma unroll
+                    for (int u = 0; u < U; ++u) {
+                        const float d = group_reduce<GT, LPK>(dot[u], sub);
+                        s_own[u] = valid[u] ? d * (cur[u].ks * scale_log2) : -INFINITY;
+                        smax = fmaxf(smax, s_own[u]);
+                    }
+                    const bool moved = smax > m[0] + kLazy;
+                    if (__any_sync(kFull, moved)) {
+                        const float alpha = moved ? exp2f(m[0] - smax) : 1.f;
+                        if (moved) m[0] = smax;
+                        l[0] *= alpha;
+#pragma unroll
+                        for (int hh = 0; hh < GT; ++hh) {
+                            const float a = __shfl_sync(kFull, alpha, gbase + src_sub<GT>(hh));
+                            const float2 a2 = make_float2(a, a);
+#pragma unroll
+                            for (int e = 0; e < HE; ++e) acc[hh][e] = __fmul2_rn(acc[hh][e], a2);
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < U; ++u) {
+                        const float pw = valid[u] ? exp2f(s_own[u] - m[0]) : 0.f;
+                        l[0] += pw;
+                        const float pvs = valid[u] ? pw * cur[u].vs : 0.f;   // (a stale scale may be anything)
+#pragma unroll
+                        for (int hh = 0; hh < GT; ++hh)
+                            pv[u][hh] = __shfl_sync(kFull, pvs, gbase + src_sub<GT>(hh));
+                    }
+                } else {
+                    float sc_all[U][GT], smax[GT];
+#pragma unroll
+                    for (int hh = 0; hh < GT; ++hh) smax[hh] = -INFINITY;
+#pragma unroll
+                    for (int u = 0; u < U; ++u) {
+#pragma unroll
+                        for (int o = 1; o < LPK; o <<= 1)
+#pragma unroll
+                            for (int hh = 0; hh < GT; ++hh)
+                                dot[u][hh] += __shfl_xor_sync(kFull, dot[u][hh], o);
+#pragma unroll
+                        for (int hh = 0; hh < GT; ++hh) {
+                            sc_all[u][hh] = valid[u] ? dot[u][hh] * (cur[u].ks * scale_log2) : -INFINITY;
+                            smax[hh] = fmaxf(smax[hh], sc_all[u][hh]);
+                        }
+                    }
+                    bool moved = false;
+#pragma unroll
+                    for (int hh = 0; hh < GT; ++hh) moved |= smax[hh] > m[hh] + kLazy;
+                    if (__any_sync(kFull, moved)) {
+#pragma unroll
+                        for (int hh = 0; hh < GT; ++hh) {
+                            const bool mv = smax[hh] > m[hh] + kLazy;
+                            const float alpha = mv ? exp2f(m[hh] - smax[hh]) : 1.f;
+                            if (mv) m[hh] = smax[hh];
+                            l[hh] *= alpha;
+                            const float2 a2 = make_float2(alpha, alpha);
+#pragma unroll
+                            for (int e = 0; e < HE; ++e) acc[hh][e] = __fmul2_rn(acc[hh][e], a2);
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < U; ++u)
+#pragma unroll
+                        for (int hh = 0; hh < GT; ++hh) {
+                            const float pw = valid[u] ? exp2f(sc_all[u][hh] - m[hh]) : 0.f;
+                            l[hh] += pw;
+                            pv[u][hh] = valid[u] ? pw * cur[u].vs : 0.f;
+                        }
+                }
+                // ---- weighted V rows ----
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    float2 vf[HE];
+                    dequant<WE>(cur[u].v, vf);
+#pragma unroll
+                    for (int hh = 0; hh < GT; ++hh) {
+                        const float2 p2 = make_float2(pv[u][hh], pv[u][hh]);
+#pragma unroll
+                        for (int e = 0; e < HE; ++e) acc[hh][e] = __ffma2_rn(p2, vf[e], acc[hh][e]);
+                    }
+                }
+            };
+
+            for (int key0 = key_first; key0 < loop_end; key0 += PF * STEP) {
 #pragma unroll
                 for (int p = 0; p < PF; p += U) {
                     const int kk = key0 + p * STEP;
-                    if (kk >= tok_end) break;  // the same for every lane of the warp
+                    if (kk >= loop_end) break;  // the same for every lane of the warp
                     // U keys per lane and trip: their instruction chains are independent up to the
                     // softmax bookkeeping, which they share
                     cp_async_wait<PF - U>();
@@ -476,115 +649,62 @@ attn_splitkv_u8_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restric
                         const float2 sc = ring_s[slot];
                         cur[u].ks = sc.x;
                         cur[u].vs = sc.y;
-                        valid[u] = kk + u * STEP + grp < tok_end;
+                        valid[u] = kk + u * STEP + grp < loop_end;
                     }
 #pragma unroll
                     for (int u = 0; u < U; ++u) issue(p + u, kk + (PF + u) * STEP);  // the slots' next use
 
-                    // ---- scores of this group's keys for the unit's heads ----
-                    float dot[U][GT];
+                    trip(cur, valid);
+                }
+            }
+            if (fused_new) {   // (the same for every lane of the block)
+                // the request's new token, on the lanes of group 0
+                Fetch<WE> cur[U];
+                bool valid[U];
 #pragma unroll
-                    for (int u = 0; u < U; ++u) {
-                        float2 kf[HE];
-                        dequant<WE>(cur[u].k, kf);
+                for (int uu = 0; uu < U; ++uu) {
+                    valid[uu] = false;
+                    cur[uu].ks = cur[uu].vs = 0.f;
 #pragma unroll
-                        for (int hh = 0; hh < GT; ++hh) {
-                            float2 a = make_float2(0.f, 0.f);
+                    for (int i = 0; i < WE; ++i) cur[uu].k[i] = cur[uu].v[i] = 0x80808080u;
+                }
+                const float* kn = r.k + size_t(u.kv_head) * r.kv_hs;
+                const float* vn = r.v + size_t(u.kv_head) * r.kv_hs;
+                float kx[EPL], vx[EPL];
 #pragma unroll
-                            for (int e = 0; e < HE; ++e) a = __ffma2_rn(q2[hh][e], kf[e], a);
-                            dot[u][hh] = a.x + a.y;
-                        }
-                    }
-                    // ---- online softmax.  The running reference m only has to stay within
-                    // 2^kLazy of the true maximum (weights up to 2^8 are harmless in f32), so it
-                    // moves -- and the accumulators are rescaled -- only on a jump of more than kLazy.
-                    float pv[U][GT];
-                    if constexpr (LPK >= GT) {
-                        // every lane ends up with the score of ONE head (owned_head(sub)): GT - 1 +
-                        // log2(LPK / GT) shuffles instead of GT * log2(LPK), one exp2f instead of GT
-                        float s_own[U], smax = -INFINITY;
-#pragma unroll
-                        for (int u = 0; u < U; ++u) {
-                            const float d = group_reduce<GT, LPK>(dot[u], sub);
-                            s_own[u] = valid[u] ? d * (cur[u].ks * scale_log2) : -INFINITY;
-                            smax = fmaxf(smax, s_own[u]);
-                        }
-                        const bool moved = smax > m[0] + kLazy;
-                        if (__any_sync(kFull, moved)) {
-                            const float alpha = moved ? exp2f(m[0] - smax) : 1.f;
-                            if (moved) m[0] = smax;
-                            l[0] *= alpha;
-#pragma unroll
-                            for (int hh = 0; hh < GT; ++hh) {
-                                const float a = __shfl_sync(kFull, alpha, gbase + src_sub<GT>(hh));
-                                const float2 a2 = make_float2(a, a);
-#pragma unroll
-                                for (int e = 0; e < HE; ++e) acc[hh][e] = __fmul2_rn(acc[hh][e], a2);
-                            }
-                        }
-#pragma unroll
-                        for (int u = 0; u < U; ++u) {
-                            const float pw = valid[u] ? exp2f(s_own[u] - m[0]) : 0.f;
-                            l[0] += pw;
-                            const float pvs = valid[u] ? pw * cur[u].vs : 0.f;   // (a stale scale may be anything)
-#pragma unroll
-                            for (int hh = 0; hh < GT; ++hh)
-                                pv[u][hh] = __shfl_sync(kFull, pvs, gbase + src_sub<GT>(hh));
-                        }
-                    } else {
-                        float sc_all[U][GT], smax[GT];
-#pragma unroll
-                        for (int hh = 0; hh < GT; ++hh) smax[hh] = -INFINITY;
-#pragma unroll
-                        for (int u = 0; u < U; ++u) {
-#pragma unroll
-                            for (int o = 1; o < LPK; o <<= 1)
-#pragma unroll
-                                for (int hh = 0; hh < GT; ++hh)
-                                    dot[u][hh] += __shfl_xor_sync(kFull, dot[u][hh], o);
-#pragma unroll
-                            for (int hh = 0; hh < GT; ++hh) {
-                                sc_all[u][hh] = valid[u] ? dot[u][hh] * (cur[u].ks * scale_log2) : -INFINITY;
-                                smax[hh] = fmaxf(smax[hh], sc_all[u][hh]);
-                            }
-                        }
-                        bool moved = false;
-#pragma unroll
-                        for (int hh = 0; hh < GT; ++hh) moved |= smax[hh] > m[hh] + kLazy;
-                        if (__any_sync(kFull, moved)) {
-#pragma unroll
-                            for (int hh = 0; hh < GT; ++hh) {
-                                const bool mv = smax[hh] > m[hh] + kLazy;
-                                const float alpha = mv ? exp2f(m[hh] - smax[hh]) : 1.f;
-                                if (mv) m[hh] = smax[hh];
-                                l[hh] *= alpha;
-                                const float2 a2 = make_float2(alpha, alpha);
-#pragma unroll
-                                for (int e = 0; e < HE; ++e) acc[hh][e] = __fmul2_rn(acc[hh][e], a2);
-                            }
-                        }
-#pragma unroll
-                        for (int u = 0; u < U; ++u)
-#pragma unroll
-                            for (int hh = 0; hh < GT; ++hh) {
-                                const float pw = valid[u] ? exp2f(sc_all[u][hh] - m[hh]) : 0.f;
-                                l[hh] += pw;
-                                pv[u][hh] = valid[u] ? pw * cur[u].vs : 0.f;
-                            }
-                    }
-                    // ---- weighted V rows ----
-#pragma unroll
-                    for (int u = 0; u < U; ++u) {
-                        float2 vf[HE];
-                        dequant<WE>(cur[u].v, vf);
-#pragma unroll
-                        for (int hh = 0; hh < GT; ++hh) {
-                            const float2 p2 = make_float2(pv[u][hh], pv[u][hh]);
-#pragma unroll
-                            for (int e = 0; e < HE; ++e) acc[hh][e] = __ffma2_rn(p2, vf[e], acc[hh][e]);
-                        }
+                for (int j = 0; j < EPL; ++j) {
+                    const int d = sub * EPL + j;
+                    kx[j] = (grp == 0 && d < head_dim) ? kn[d] : 0.f;
+                    vx[j] = (grp == 0 && d < head_dim) ? vn[d] : 0.f;
+                }
+                if constexpr (LPK >= 2) {
+                    if (fused_rope) {
+                        const int half = head_dim / 2;
+                        rope_group<LPK, EPL>(kx, cos_t + size_t(r.index_pos) * half,
+                                             sin_t + size_t(r.index_pos) * half, sub);
                     }
                 }
+                quantize_group<LPK, EPL>(kx, cur[0].k, cur[0].ks);
+                quantize_group<LPK, EPL>(vx, cur[0].v, cur[0].vs);
+                valid[0] = grp == 0;
+                if (u.store_new && grp == 0) {
+                    const int slot_new = u.kv_len - 1;
+                    uint8_t* blk = const_cast<uint8_t*>(base) + size_t(pages[slot_new / kPageTokens]) * page_stride;
+                    const int tk = slot_new % kPageTokens;
+                    uint32_t* kd = reinterpret_cast<uint32_t*>(blk + size_t(tk) * DQ + sub * EPL);
+                    uint32_t* vd = reinterpret_cast<uint32_t*>(blk + size_t(kPageTokens + tk) * DQ + sub * EPL);
+#pragma unroll
+                    for (int i = 0; i < WE; ++i) {
+                        kd[i] = cur[0].k[i];
+                        vd[i] = cur[0].v[i];
+                    }
+                    if (sub == 0) {
+                        float* sc = reinterpret_cast<float*>(blk + 2 * size_t(kPageTokens) * DQ);
+                        sc[tk] = cur[0].ks;
+                        sc[kPageTokens + tk] = cur[0].vs;
+                    }
+                }
+                trip(cur, valid);
             }
 
             if constexpr (LPK >= GT) {
