@@ -344,3 +344,27 @@ def test_whole_block_over_u8_cache():
         ctx.close()
     finally:
         xo.set_quant_body(-1)
+
+
+@pytest.mark.parametrize("D", [16, 32, 64, 100, 128, 256])
+def test_rotated_decode_steps_all_row_widths(D):
+    # decode with pre-RoPE q and k: for power-of-two head dims >= 32 the attention kernel rotates,
+    # quantises and stores the new token itself (one launch per call); other dims go through the
+    # append kernel.  Either way the stored bytes equal the oracle's shadow of the rotated rows.
+    rng = np.random.default_rng(700 + D)
+    rope = xn.rope_tables(10000.0, D, 512)
+    Hq, Hkv = 8, 2
+    ctx = u8_ctx(1, Hq, Hkv, D, 16, rope=rope)
+    p = PairU8(ctx, 256, rope=rope)
+    q, k, v = rand_qkv(rng, Hq, Hkv, 37, D)
+    got, want = p.step(0, 0, q, k, v, rope=True)
+    assert_parity(got, want, f"prefill D={D}")
+    for pos in range(37, 70):                      # crosses a page boundary at 64
+        q, k, v = rand_qkv(rng, Hq, Hkv, 1, D)
+        before = ctx.stats()["kernel_launches"]
+        got, want = p.step(0, pos, q, k, v, rope=True)
+        launches = ctx.stats()["kernel_launches"] - before
+        assert_parity(got, want, f"decode D={D} pos={pos}")
+        assert launches == (1 if D in (32, 64, 128, 256) else 2), launches
+    p.check_cache(0)
+    ctx.close()
