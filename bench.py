@@ -253,12 +253,13 @@ def load_tf32_peak():
     return 1590.0 / 2.0, "fallback bf16 / 2"
 
 
-def measure_prefill(xn, torch, tstream, device, S, Hq, Hkv, D, theta, steps, warmup, e2e=True):
+def measure_prefill(xn, torch, tstream, device, S, Hq, Hkv, D, theta, steps, warmup, e2e=True, u8=False):
     """One causal prefill of S tokens (fused RoPE + append + attention) per step, one layer."""
     cos, sin = xn.rope_tables(theta, D, S)
     ctx = xn.Context(num_layers=1, num_heads=Hq, num_kv_heads=Hkv, head_dim=D,
                      pool_pages=(S + 63) // 64 + 2, device=device, shuffle_seed=BASE_SEED + 2000,
-                     rope=(cos, sin), cuda_stream=tstream.cuda_stream)
+                     rope=(cos, sin), cuda_stream=tstream.cuda_stream,
+                     kv_format=xn.KV_U8 if u8 else xn.KV_F32)
     st = ctx.new_stream(S)
     gen = torch.Generator(device="cpu").manual_seed(BASE_SEED + 2000)
     q_h = torch.randn(Hq, S, D, generator=gen).pin_memory()
@@ -293,7 +294,7 @@ def measure_prefill(xn, torch, tstream, device, S, Hq, Hkv, D, theta, steps, war
            "tflops": flops / (total_ms / steps * 1e-3) / 1e12,
            "kernel_ms": kern_ms / max(kern_n, 1),
            "kernel_tflops": flops / (kern_ms / max(kern_n, 1) * 1e-3) / 1e12 if kern_n else None,
-           "launches_per_step": 2}
+           "launches_per_step": 3 if u8 else 2}
     if e2e:
         ctx.submit(host)
         t0 = time.perf_counter()
@@ -324,7 +325,8 @@ def run_prefill_arm(args):
     S = args.seq or 2048
     sampler = ClockSampler(local_rank) if rank == 0 else None
     wall0 = time.time()
-    r = measure_prefill(xn, torch, tstream, local_rank, S, 20, 5, 128, 500000.0, args.steps, args.warmup)
+    u8 = args.kv == "u8"
+    r = measure_prefill(xn, torch, tstream, local_rank, S, 20, 5, 128, 500000.0, args.steps, args.warmup, u8=u8)
     wall1 = time.time()
     clocks = sampler.stop(wall0, wall1) if sampler else None
     if rank != 0:
@@ -336,13 +338,15 @@ def run_prefill_arm(args):
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "tf32",
         "data": "synthetic",
         "config": {"workload": f"c2: causal GQA prefill, BitNet-2B shape, {S} tokens, 20/5 heads, "
-                               "head_dim 128, fused RoPE theta 5e5 + append into 64-token pages",
+                               "head_dim 128, fused RoPE theta 5e5 + append into 64-token pages" +
+                               (" [opt-in u8 cache format: quantised append, pages dequantised into an f32 "
+                                "staging area for the tensor-core kernel]" if u8 else ""),
                    "l2": "256 MB buffer written between timed iterations (L2 flush)",
                    "parallelism": f"{world} independent replica(s)"},
         "e2e": {"value": r.get("e2e_tflops"), "unit": "TFLOP/s",
                 "h2d_bytes_per_step": r.get("e2e_h2d_bytes"), "d2h_bytes_per_step": r.get("e2e_d2h_bytes"),
                 "ms_per_step": r.get("e2e_ms")},
-        "gpu_launches": 2 * args.steps,
+        "gpu_launches": r["launches_per_step"] * args.steps,
         "roofline": {"bound": "tensor", "kernel": "prefill_tf32_kernel", "achieved": r["kernel_tflops"],
                      "peak": peak, "unit": "TFLOP/s", "frac": r["kernel_tflops"] / peak,
                      "peak_source": peak_kind, "traffic": None, "avg_launch_ms": r["kernel_ms"],

@@ -75,7 +75,8 @@ enum {
                    /* dequantised values (byte - 128) * scale.  A quarter of the cache bytes; the  */
                    /* stored bytes and scales equal the reference's shadow bit for bit, the        */
                    /* attention output differs from the f32 cache's by the quantisation error.     */
-                   /* The tensor-core prefill kernel is not available in this format.              */
+                   /* Prefills served by the tensor-core kernel first dequantise the stream's      */
+                   /* pages of the layer into an f32 staging area (grown on demand).               */
 };
 
 typedef struct xn_ctx_desc {

@@ -68,6 +68,8 @@ class PairU8:
 
 
 def u8_ctx(L, Hq, Hkv, D, pages, **kw):
+    # exact-f32 prefill rows unless a test asks otherwise: this module checks the f32 tolerances
+    kw.setdefault("prefill_mode", 1)
     return xn.Context(L, Hq, Hkv, D, pool_pages=pages, kv_format=xn.KV_U8, **kw)
 
 
@@ -277,9 +279,37 @@ def test_device_pointer_batch_and_synthetic_fill():
     ctx.close()
 
 
-def test_rejects_tf32_mode_and_f32_reader():
-    with pytest.raises(xn.XnError):
-        xn.Context(1, 4, 2, 64, pool_pages=4, kv_format=xn.KV_U8, prefill_mode=2)
+@pytest.mark.parametrize("D,Hq,Hkv", [(128, 20, 5), (64, 8, 2), (32, 4, 4)])
+def test_tensor_core_prefill_over_u8_cache(D, Hq, Hkv):
+    # prefills of >= 128 rows: append (rotate, quantise), dequantise the stream's pages of the layer
+    # into the f32 staging area, run the tcgen05 TF32 kernel over it.  Storage stays bit-exact; the
+    # output keeps the TF32 kernel's bound (rel L2 <= 5e-3) against the oracle over the dequantised rows.
+    rng = np.random.default_rng(800 + D)
+    rope = xn.rope_tables(500000.0, D, 4096)
+    ctx = u8_ctx(2, Hq, Hkv, D, 80, rope=rope, shuffle_seed=5, prefill_mode=0)
+    p = PairU8(ctx, 2048, rope=rope)
+    pos = 0
+    for S in (300, 1, 130, 700):                  # 1: a decode step between chunks; 700 grows the staging area
+        q, k, v = rand_qkv(rng, Hq, Hkv, S, D)
+        before = ctx.stats()["prefill_launches"]
+        got, want = p.step(1, pos, q, k, v, rope=True)
+        assert ctx.stats()["prefill_launches"] - before == (1 if S >= 128 else 0)
+        if S >= 128:
+            assert errs(got, want)[1] <= 5e-3, f"TF32 chunk at {pos}+{S}: rel {errs(got, want)[1]:.2e}"
+        else:
+            assert_parity(got, want, f"decode at {pos}")
+        pos += S
+    p.check_cache(1)
+    # a second stream reuses the staging area
+    p2 = PairU8(ctx, 2048, rope=rope)
+    q, k, v = rand_qkv(rng, Hq, Hkv, 200, D)
+    got, want = p2.step(0, 0, q, k, v, rope=True)
+    assert errs(got, want)[1] <= 5e-3
+    p2.check_cache(0)
+    ctx.close()
+
+
+def test_rejects_bad_format_and_f32_reader():
     with pytest.raises(xn.XnError):
         xn.Context(1, 4, 2, 64, pool_pages=4, kv_format=7)
     c = xn.Context(1, 4, 2, 64, pool_pages=4)

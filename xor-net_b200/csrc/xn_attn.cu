@@ -116,6 +116,13 @@ struct xn_ctx {
     int dq = 0;                  // bytes per stored row
     int kv8_epl = 16;            // bytes of a row one lane of the attention kernel handles
     uint8_t* pool8 = nullptr;
+    // ... and the f32 staging area the tensor-core prefill kernel reads in that format: the pages of
+    // one stream and layer, dequantised, addressed through an identity page table
+    float* k_stage = nullptr;
+    float* v_stage = nullptr;
+    long long stage_pages = 0;
+    int* stage_ident_d = nullptr;
+    CUtensorMap k_stage_map, v_stage_map;
     float* cos_d = nullptr;
     float* sin_d = nullptr;
     std::vector<int32_t> free_pages;  // stack: back() is handed out next
@@ -477,6 +484,37 @@ int32_t launch_out_block(xn_ctx* c, const OutProj& op, const OutRowDev* rows_d, 
     return XN_OK;
 }
 
+// u8 cache format: room for `pages` dequantised pages of one layer, with tensor maps over it.
+int32_t ensure_stage(xn_ctx* c, long long pages) {
+    if (pages <= c->stage_pages) return XN_OK;
+    XN_CUDA(c, cudaStreamSynchronize(c->stream));  // nothing in flight may still use the old area
+    if (c->k_stage) cudaFree(c->k_stage);
+    if (c->v_stage) cudaFree(c->v_stage);
+    if (c->stage_ident_d) cudaFree(c->stage_ident_d);
+    const long long np = std::max<long long>({pages, 2 * c->stage_pages, 32});
+    c->k_stage = c->v_stage = nullptr;
+    c->stage_ident_d = nullptr;
+    c->stage_pages = 0;
+    const size_t rows = size_t(np) * c->num_kv_heads * kPageTokens;
+    const size_t bytes = rows * size_t(c->head_dim) * 4;
+    XN_CUDA(c, cudaMalloc(reinterpret_cast<void**>(&c->k_stage), bytes));
+    XN_CUDA(c, cudaMalloc(reinterpret_cast<void**>(&c->v_stage), bytes));
+    XN_CUDA(c, cudaMemset(c->k_stage, 0, bytes));
+    XN_CUDA(c, cudaMemset(c->v_stage, 0, bytes));
+    std::vector<int32_t> ident(size_t(np), 0);
+    for (long long i = 0; i < np; ++i) ident[size_t(i)] = int32_t(i);
+    XN_CUDA(c, cudaMalloc(reinterpret_cast<void**>(&c->stage_ident_d), size_t(np) * 4));
+    XN_CUDA(c, cudaMemcpy(c->stage_ident_d, ident.data(), size_t(np) * 4, cudaMemcpyHostToDevice));
+    const cuuint64_t dims[2] = {cuuint64_t(c->head_dim), cuuint64_t(rows)};
+    const cuuint64_t str[1] = {cuuint64_t(c->head_dim) * 4};
+    const cuuint32_t box[2] = {32, cuuint32_t(pf::kPage)};
+    if (rows >= (1ull << 31) || !make_map_f32(&c->k_stage_map, c->k_stage, 2, dims, str, box) ||
+        !make_map_f32(&c->v_stage_map, c->v_stage, 2, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B))
+        return fail(c, XN_ERR_CUDA, "tensor maps over the prefill staging area could not be encoded");
+    c->stage_pages = np;
+    return XN_OK;
+}
+
 // ---- one batched submission ----------------------------------------------------------------
 
 struct GapFill {
@@ -552,7 +590,7 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
     std::vector<GapFill> gaps;
     size_t io_in = 0, io_out = 0, qrot_floats = 0, n_page_ids = 0, out_rows = 0, qkv_rows = 0;
     const size_t qkv_width = size_t(Hq + 2 * Hkv) * D;   // floats of one projected row [q | k | v]
-    long long n_units = 0, n_ring_rows = 0;
+    long long n_units = 0, n_ring_rows = 0, stage_need = 0;
     int max_rows = 0;
     for (int i = 0; i < n; ++i) {
         const xn_req& r = reqs[i];
@@ -579,7 +617,9 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         }
         if ((r.flags & XN_REQ_ROPE) || pinned || qkv) qrot_floats += align_up(qf, 4);
         if (end > s->cap) n_ring_rows += r.seq_len;
-        else if (use_tf32(c, r, direct)) { /* served by the tensor-core prefill kernel */ }
+        else if (use_tf32(c, r, direct)) {   // served by the tensor-core prefill kernel
+            stage_need = std::max<long long>(stage_need, (end + kPageTokens - 1) / kPageTokens);
+        }
         else n_units += (long long)r.seq_len * Hkv * c->subs;
         max_rows = std::max<long long>(max_rows, (long long)r.seq_len * (Hq + 2 * Hkv));
         if (pinned) {  // bytes the kernels move over PCIe themselves
@@ -619,6 +659,7 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
                     n_units, kMaxUnits);
 
     int32_t rc;
+    if (c->kv_u8 && stage_need && (rc = ensure_stage(c, stage_need)) != XN_OK) return rc;
     if ((rc = grow_device(c, &c->q_rot, &c->q_rot_cap, qrot_floats)) != XN_OK) return rc;
     if (out_rows) {
         if ((rc = grow_device(c, &c->attn_seq, &c->attn_seq_cap, out_rows * size_t(Hq) * D)) != XN_OK) return rc;
@@ -894,11 +935,11 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         pa.q = d.q;
         pa.q_hs = d.q_hs;
         pa.q_ts = d.q_ts;
-        pa.pages = pages_d + d.page_off;
+        pa.pages = c->kv_u8 ? c->stage_ident_d : pages_d + d.page_off;
         pa.out = d.out;
         pa.o_hs = d.o_hs;
         pa.o_ts = d.o_ts;
-        pa.layer_page_base = (long long)d.layer * c->pool_pages;
+        pa.layer_page_base = c->kv_u8 ? 0 : (long long)d.layer * c->pool_pages;
         pa.num_kv_heads = Hkv;
         pa.group = c->group;
         pa.seq_len = d.seq_len;
@@ -908,6 +949,16 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         pa.status = c->status_d;
         dim3 grid(unsigned((d.seq_len + pf::kBM - 1) / pf::kBM) * unsigned(Hq));
         if (c->profile && (rc = profile_begin(c, 1)) != XN_OK) return rc;
+        if (c->kv_u8) {
+            // the stream's pages of this layer (the new rows included: the append ran above),
+            // dequantised into the staging area the kernel's tensor maps cover
+            const int n_pages = (d.index_pos + d.seq_len + kPageTokens - 1) / kPageTokens;
+            kv8::dequant_pages_u8_kernel<<<n_pages * Hkv, 256, 0, c->stream>>>(
+                c->pool8, pages_d + d.page_off, n_pages, d.layer, c->pool_pages, Hkv, D, c->dq, c->k_stage,
+                c->v_stage);
+            c->stats.kernel_launches += 1;
+            prefill_tf32_kernel<<<grid, pf::kThreads, pf::kSmemBytes, c->stream>>>(c->k_stage_map, c->v_stage_map, pa);
+        } else
         prefill_tf32_kernel<<<grid, pf::kThreads, pf::kSmemBytes, c->stream>>>(c->k_map, c->v_map, pa);
         if (c->profile && (rc = profile_end(c)) != XN_OK) return rc;
         c->stats.kernel_launches += 1;
@@ -1183,7 +1234,14 @@ int32_t xn_ctx_create(const xn_ctx_desc* d, xn_ctx** out_ctx) {
     // tensor-core prefill: possible when rows are exactly head_dim floats and TMA can address them
     {
         const unsigned long long rows = (unsigned long long)pages * d->num_layers * d->num_kv_heads * kPageTokens;
-        if (!c->kv_u8 && d->head_dim % 4 == 0 && d->head_dim >= 16 && d->head_dim <= 128 && rows < (1ull << 31)) {
+        if (c->kv_u8) {
+            // the kernel reads a dequantised staging area, mapped when the first prefill needs it
+            c->tf32_ok = d->head_dim % 4 == 0 && d->head_dim >= 16 && d->head_dim <= 128 && encode_tiled_fn() != nullptr;
+            if (c->tf32_ok)
+                XN_CREATE_CUDA(cudaFuncSetAttribute(reinterpret_cast<const void*>(prefill_tf32_kernel),
+                                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                    pf::kSmemBytes));
+        } else if (d->head_dim % 4 == 0 && d->head_dim >= 16 && d->head_dim <= 128 && rows < (1ull << 31)) {
             const cuuint64_t dims[2] = {cuuint64_t(d->head_dim), cuuint64_t(rows)};
             const cuuint64_t str[1] = {cuuint64_t(d->head_dim) * 4};
             const cuuint32_t box[2] = {32, cuuint32_t(pf::kPage)};
@@ -1201,8 +1259,7 @@ int32_t xn_ctx_create(const xn_ctx_desc* d, xn_ctx** out_ctx) {
             if (v > 0) c->tf32_min_rows = v;
         }
         if (d->prefill_mode == XN_PREFILL_TF32 && !c->tf32_ok) {
-            fail(nullptr, XN_ERR_SHAPE, c->kv_u8 ? "the TF32 prefill kernel does not read the u8 cache format (head_dim %d)"
-                                                  : "head_dim %d cannot use the TF32 prefill kernel", d->head_dim);
+            fail(nullptr, XN_ERR_SHAPE, "head_dim %d cannot use the TF32 prefill kernel", d->head_dim);
             return bail(XN_ERR_SHAPE);
         }
     }
@@ -1259,6 +1316,9 @@ int32_t xn_ctx_destroy(xn_ctx* c) {
     if (c->k_pool) cudaFree(c->k_pool);
     if (c->v_pool) cudaFree(c->v_pool);
     if (c->pool8) cudaFree(c->pool8);
+    if (c->k_stage) cudaFree(c->k_stage);
+    if (c->v_stage) cudaFree(c->v_stage);
+    if (c->stage_ident_d) cudaFree(c->stage_ident_d);
     if (c->copy_stream) cudaStreamDestroy(c->copy_stream);
     if (c->own_stream && c->stream) cudaStreamDestroy(c->stream);
     c->magic = 0;

@@ -234,6 +234,35 @@ slots_gather_u8_kernel(const int* __restrict__ pages, const uint8_t* __restrict_
     }
 }
 
+// Pages [0, n_pages) of one stream and layer, dequantised into an f32 staging area laid out as the
+// tensor-core prefill kernel expects its pool: [staging page = position / 64][KV head][64][head_dim]
+// (head_dim a multiple of 4).  One block per (page, KV head); whole pages are written, so the
+// staging area only ever holds finite values.
+__global__ void __launch_bounds__(256)
+dequant_pages_u8_kernel(const uint8_t* __restrict__ pool, const int* __restrict__ pages, int n_pages,
+                        int layer, long long pool_pages, int num_kv_heads, int head_dim, int dq,
+                        float* __restrict__ k_stage, float* __restrict__ v_stage) {
+    const int p = blockIdx.x / num_kv_heads, h = blockIdx.x % num_kv_heads;
+    if (p >= n_pages) return;
+    const uint8_t* blk = pool + ((size_t(layer) * size_t(pool_pages) + size_t(pages[p])) * num_kv_heads + h) *
+                                    block_bytes(dq);
+    const float* sc = reinterpret_cast<const float*>(blk + 2 * size_t(kPageTokens) * dq);
+    const size_t out0 = (size_t(p) * num_kv_heads + h) * kPageTokens * head_dim;
+    const int quads = head_dim / 4;
+    for (int e = threadIdx.x; e < kPageTokens * quads; e += blockDim.x) {
+        const int t = e / quads, d = (e % quads) * 4;
+        const uchar4 kb = *reinterpret_cast<const uchar4*>(blk + size_t(t) * dq + d);
+        const uchar4 vb = *reinterpret_cast<const uchar4*>(blk + size_t(kPageTokens + t) * dq + d);
+        const float ks = sc[t], vs = sc[kPageTokens + t];
+        *reinterpret_cast<float4*>(k_stage + out0 + size_t(t) * head_dim + d) =
+            make_float4((float(kb.x) - 128.0f) * ks, (float(kb.y) - 128.0f) * ks, (float(kb.z) - 128.0f) * ks,
+                        (float(kb.w) - 128.0f) * ks);
+        *reinterpret_cast<float4*>(v_stage + out0 + size_t(t) * head_dim + d) =
+            make_float4((float(vb.x) - 128.0f) * vs, (float(vb.y) - 128.0f) * vs, (float(vb.z) - 128.0f) * vs,
+                        (float(vb.w) - 128.0f) * vs);
+    }
+}
+
 // ---- split-KV attention over u8 pages --------------------------------------------------------
 
 // One warp per thread block, many blocks per SM: every warp walks its own item, so the chain of
