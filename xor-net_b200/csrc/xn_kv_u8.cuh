@@ -268,10 +268,9 @@ dequant_pages_u8_kernel(const uint8_t* __restrict__ pool, const int* __restrict_
 // One warp per thread block, many blocks per SM: every warp walks its own item, so the chain of
 // dependent loads that opens an item (descriptors, query rows, page ids, first copies) overlaps
 // with the other warps' arithmetic instead of idling a whole 8-warp block.
-#ifndef XN_KV8_WARPS
-#define XN_KV8_WARPS 1
-#endif
-constexpr int kWarps = XN_KV8_WARPS;
+// (Measured on the config-3 batch: eight-warp blocks, one per SM, 127 us per launch; one-warp
+// blocks, eight per SM, 104 us.)
+constexpr int kWarps = 1;
 constexpr int kThreads = 32 * kWarps;
 // Bytes of a row one lane handles (EPL): 16 keeps the per-key bookkeeping lowest, 8 halves the
 // registers a lane needs for its query slice and accumulators and so doubles the resident warps.
@@ -333,6 +332,15 @@ __device__ __forceinline__ void dequant(const uint32_t (&ws)[W], float2 (&f)[2 *
         f[2 * i] = __fadd2_rn(make_float2(a0, a1), c);
         f[2 * i + 1] = __fadd2_rn(make_float2(a2, a3), c);
     }
+}
+
+// 2^x for the softmax weights in the key loop: one MUFU instruction (about 2 ulp), without exp2f's
+// extra handling of results below 2^-126, which may flush to 0 here (85.6 against 88.1 us per
+// launch on the config-3 batch).  Arguments are <= kLazy.
+__device__ __forceinline__ float exp2_weight(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
 }
 
 constexpr float kLazy = 8.0f;   // log2 units the running softmax reference may lag the true maximum
@@ -574,7 +582,7 @@ attn_splitkv_u8_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restric
                     }
                     const bool moved = smax > m[0] + kLazy;
                     if (__any_sync(kFull, moved)) {
-                        const float alpha = moved ? exp2f(m[0] - smax) : 1.f;
+                        const float alpha = moved ? exp2_weight(m[0] - smax) : 1.f;
                         if (moved) m[0] = smax;
                         l[0] *= alpha;
 #pragma unroll
@@ -587,7 +595,7 @@ attn_splitkv_u8_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restric
                     }
 #pragma unroll
                     for (int u = 0; u < U; ++u) {
-                        const float pw = valid[u] ? exp2f(s_own[u] - m[0]) : 0.f;
+                        const float pw = valid[u] ? exp2_weight(s_own[u] - m[0]) : 0.f;
                         l[0] += pw;
                         const float pvs = valid[u] ? pw * cur[u].vs : 0.f;   // (a stale scale may be anything)
 #pragma unroll
@@ -618,7 +626,7 @@ attn_splitkv_u8_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restric
 #pragma unroll
                         for (int hh = 0; hh < GT; ++hh) {
                             const bool mv = smax[hh] > m[hh] + kLazy;
-                            const float alpha = mv ? exp2f(m[hh] - smax[hh]) : 1.f;
+                            const float alpha = mv ? exp2_weight(m[hh] - smax[hh]) : 1.f;
                             if (mv) m[hh] = smax[hh];
                             l[hh] *= alpha;
                             const float2 a2 = make_float2(alpha, alpha);
@@ -630,7 +638,7 @@ attn_splitkv_u8_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restric
                     for (int u = 0; u < U; ++u)
 #pragma unroll
                         for (int hh = 0; hh < GT; ++hh) {
-                            const float pw = valid[u] ? exp2f(sc_all[u][hh] - m[hh]) : 0.f;
+                            const float pw = valid[u] ? exp2_weight(sc_all[u][hh] - m[hh]) : 0.f;
                             l[hh] += pw;
                             pv[u][hh] = valid[u] ? pw * cur[u].vs : 0.f;
                         }
