@@ -398,3 +398,41 @@ def test_rotated_decode_steps_all_row_widths(D):
         assert launches == (1 if D in (32, 64, 128, 256) else 2), launches
     p.check_cache(0)
     ctx.close()
+
+
+def test_pinned_host_rows_equal_staged_rows():
+    # XN_REQ_HOST_PINNED over the u8 cache: page-locked rows go through the append kernel (not the
+    # fused path); the staged path at the same positions (fused append) must leave the same bytes in
+    # the cache and return the same result up to the order of the sums (the fused path handles the
+    # new token after the cached ones)
+    torch = pytest.importorskip("torch")
+    rng = np.random.default_rng(59)
+    ctx = u8_ctx(1, 20, 5, 128, 80)
+    lens = [300, 64, 1500, 1]
+    pairs = [PairU8(ctx, 2048) for _ in lens]
+    for p, L in zip(pairs, lens):
+        if L > 1:
+            p.step(0, 0, *rand_qkv(rng, 20, 5, L - 1, 128))
+    n = len(lens)
+    q = torch.from_numpy(rng.standard_normal((n, 20, 128)).astype(np.float32)).pin_memory()
+    k = torch.from_numpy(rng.standard_normal((n, 5, 128)).astype(np.float32)).pin_memory()
+    v = torch.from_numpy(rng.standard_normal((n, 5, 128)).astype(np.float32)).pin_memory()
+    out = torch.zeros(n, 20, 128).pin_memory()
+    reqs = ctx.make_batch([(pairs[i].st, 0, lens[i] - 1, 1, q[i].data_ptr(), k[i].data_ptr(),
+                            v[i].data_ptr(), out[i].data_ptr()) for i in range(n)], xn.REQ_HOST_PINNED)
+    ctx.submit(reqs)
+    for i, p in enumerate(pairs):
+        want = p.oracle_step(0, lens[i] - 1, q[i].numpy().reshape(1, 20, 1, 128),
+                             k[i].numpy().reshape(1, 5, 1, 128), v[i].numpy().reshape(1, 5, 1, 128))
+        assert_parity(out[i].numpy().reshape(1, 20, 1, 128), want, f"pinned stream {i}")
+        p.check_cache(0)
+    before = ctx.stats()["kernel_launches"]
+    staged = ctx.attention_batch([p.st for p in pairs], 0, [L - 1 for L in lens],
+                                 [q[i].numpy().reshape(1, 20, 1, 128) for i in range(n)],
+                                 [k[i].numpy().reshape(1, 5, 1, 128) for i in range(n)],
+                                 [v[i].numpy().reshape(1, 5, 1, 128) for i in range(n)])
+    assert ctx.stats()["kernel_launches"] - before == 1          # fused: the attention kernel alone
+    for i, p in enumerate(pairs):
+        assert_parity(staged[i].reshape(20, 128), out[i].numpy(), f"staged vs pinned, stream {i}")
+        p.check_cache(0)
+    ctx.close()
