@@ -701,6 +701,10 @@ def run_gpu_arm(args):
         if args.workload == "c3" and not args.streams and world == 1 and not u8:
             traffic = 708.71e6 + 5.04e6
             traffic_src = "ncu capture of this workload (2 of 30 layers), summary under profiles/"
+        if args.workload == "c3" and not args.streams and world == 1 and u8:
+            traffic = 184.37e6 + 4.51e6
+            traffic_src = ("ncu capture of this workload over the u8 cache format (2 of 30 layers), "
+                           "profiles/attn_splitkv_u8_c3_2layers.md")
         line = {
             "metric": "decode_attn_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
