@@ -436,3 +436,56 @@ def test_pinned_host_rows_equal_staged_rows():
         assert_parity(staged[i].reshape(20, 128), out[i].numpy(), f"staged vs pinned, stream {i}")
         p.check_cache(0)
     ctx.close()
+
+
+# ---- the variant with q.k on the integer tensor-core path ---------------------------------------
+# Large submissions (>= 65536 attended rows) over 64- and 128-byte rows run
+# attn_splitkv_u8_mma_kernel: the K bytes are an MMA operand, the query rows three int8 terms.
+# XORNET_ATTN_KV8_MMA_MIN_ROWS=0 forces it for every submission of a context created afterwards.
+
+@pytest.mark.parametrize("case", [
+    lambda: test_head_dims(64), lambda: test_head_dims(128),
+    lambda: test_group_sizes(1, 1), lambda: test_group_sizes(2, 1), lambda: test_group_sizes(3, 1),
+    lambda: test_group_sizes(5, 1), lambda: test_group_sizes(8, 1), lambda: test_group_sizes(32, 8),
+    lambda: test_group_sizes(20, 5),
+    test_decode_lengths_around_boundaries, test_rope_append_and_chunks, test_long_stream_cut_units,
+    test_ragged_batch_of_streams, test_gap_reads_as_never_written, test_whole_block_over_u8_cache,
+    test_device_pointer_batch_and_synthetic_fill,
+])
+def test_tensor_core_variant(monkeypatch, case):
+    monkeypatch.setenv("XORNET_ATTN_KV8_MMA_MIN_ROWS", "0")
+    case()
+
+
+def test_large_batch_takes_the_tensor_core_variant_and_agrees():
+    # 24 streams x ~700 tokens x 5 KV heads > 65536 attended rows: the default choice; the same
+    # batch with the variant disabled must agree within the f32 bounds, and both with the oracle
+    import os
+    rng = np.random.default_rng(91)
+    lens = [int(x) for x in rng.integers(500, 900, 24)]
+    outs = {}
+    for mode in ("1", "0"):
+        os.environ["XORNET_ATTN_KV8_MMA"] = mode
+        try:
+            ctx = u8_ctx(1, 20, 5, 128, 400)
+        finally:
+            del os.environ["XORNET_ATTN_KV8_MMA"]
+        streams = [ctx.new_stream(1024) for _ in lens]
+        for i, (st, L) in enumerate(zip(streams, lens)):
+            st.fill_normal(0, 0, L, 77 + i)
+        r2 = np.random.default_rng(92)
+        qs, ks, vs = zip(*[rand_qkv(r2, 20, 5, 1, 128) for _ in lens])
+        before = ctx.stats()["kernel_launches"]
+        outs[mode] = ctx.attention_batch(streams, 0, lens, qs, ks, vs)
+        launches = ctx.stats()["kernel_launches"] - before
+        assert launches == (2 if mode == "1" else 1)      # append + attention / attention alone
+        if mode == "1":
+            for i in (0, 7, 23):
+                kc, vc = streams[i].read_range(0, 0, lens[i] + 1)
+                ref = xo.RingCache(1, 5, lens[i] + 1, 128)
+                ref.append(0, 0, kc[None], vc[None])
+                want = xo.fast_attention(qs[i], kc[None, :, lens[i]:], vc[None, :, lens[i]:], 0, lens[i], ref, 20, 5, 128)
+                assert_parity(outs[mode][i], want, f"stream {i} vs oracle")
+        ctx.close()
+    for i in range(len(lens)):
+        assert_parity(outs["1"][i], outs["0"][i], f"stream {i}: tensor-core variant vs CUDA-core kernel")

@@ -19,6 +19,7 @@
 #include "xn_common.cuh"
 #include "xn_decode.cuh"
 #include "xn_kv_u8.cuh"
+#include "xn_kv_u8_mma.cuh"
 #include "xn_outproj.cuh"
 #include "xn_outproj_tc.cuh"
 #include "xn_plan.hpp"
@@ -115,6 +116,9 @@ struct xn_ctx {
     bool kv_u8 = false;
     int dq = 0;                  // bytes per stored row
     int kv8_epl = 16;            // bytes of a row one lane of the attention kernel handles
+    bool kv8_mma = true;         // q.k of the u8 attention kernel on the integer tensor-core path ...
+    long long kv8_mma_min_rows = 65536;  // ... for submissions that attend at least this many cached rows
+                                 // (smaller ones are latency bound: the kernel that also appends wins)
     uint8_t* pool8 = nullptr;
     // ... and the f32 staging area the tensor-core prefill kernel reads in that format: the pages of
     // one stream and layer, dequantised, addressed through an identity page table
@@ -235,7 +239,7 @@ SplitKernel pick_split(int nv_class, int gt, bool exact) {
 
 using Split8Fn = void (*)(const ReqDev*, const UnitDev*, const ItemDev*, const int*, int, const int*,
                           const uint8_t*, float*, int*, long long, int, int, float, const float*,
-                          const float*);
+                          const float*, int*);
 
 template <int DQ, int EPL>
 Split8Fn pick8_gt(int gt) {
@@ -261,6 +265,15 @@ Split8Fn pick8_dq(int dq, int gt) {
 Split8Fn pick_split8(int dq, int gt, int epl) {
     (void)epl;
     return pick8_dq<16>(dq, gt);
+}
+
+// the variant with q.k on the integer tensor-core path: row widths 64 and 128 only
+Split8Fn pick_split8_mma(int dq, int gt) {
+    if (dq == 128)
+        return gt == 4 ? kv8m::attn_splitkv_u8_mma_kernel<8, 4>
+                       : (gt == 2 ? kv8m::attn_splitkv_u8_mma_kernel<8, 2> : kv8m::attn_splitkv_u8_mma_kernel<8, 1>);
+    return gt == 4 ? kv8m::attn_splitkv_u8_mma_kernel<4, 4>
+                   : (gt == 2 ? kv8m::attn_splitkv_u8_mma_kernel<4, 2> : kv8m::attn_splitkv_u8_mma_kernel<4, 1>);
 }
 
 int nv_class_for(int nv) {
@@ -590,7 +603,7 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
     std::vector<GapFill> gaps;
     size_t io_in = 0, io_out = 0, qrot_floats = 0, n_page_ids = 0, out_rows = 0, qkv_rows = 0;
     const size_t qkv_width = size_t(Hq + 2 * Hkv) * D;   // floats of one projected row [q | k | v]
-    long long n_units = 0, n_ring_rows = 0, stage_need = 0;
+    long long n_units = 0, n_ring_rows = 0, stage_need = 0, key_rows = 0;
     int max_rows = 0;
     for (int i = 0; i < n; ++i) {
         const xn_req& r = reqs[i];
@@ -620,7 +633,11 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         else if (use_tf32(c, r, direct)) {   // served by the tensor-core prefill kernel
             stage_need = std::max<long long>(stage_need, (end + kPageTokens - 1) / kPageTokens);
         }
-        else n_units += (long long)r.seq_len * Hkv * c->subs;
+        else {
+            n_units += (long long)r.seq_len * Hkv * c->subs;
+            key_rows += (long long)Hkv * c->subs *
+                        ((long long)r.seq_len * r.index_pos + (long long)r.seq_len * (r.seq_len + 1) / 2);
+        }
         max_rows = std::max<long long>(max_rows, (long long)r.seq_len * (Hq + 2 * Hkv));
         if (pinned) {  // bytes the kernels move over PCIe themselves
             c->stats.h2d_bytes += (qkv ? xf : qf + 2 * kvf) * 4;
@@ -633,7 +650,8 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
     // 64 / 128.
     // (u8 cache format: rows without padding, i.e. head_dim a power of two >= 16; the rotation needs
     // at least two lanes per row; plain loads, so no alignment condition.)
-    bool fused = c->fuse_append && n_ring_rows == 0 &&
+    const bool mma_now = c->kv_u8 && c->kv8_mma && key_rows >= c->kv8_mma_min_rows;
+    bool fused = c->fuse_append && n_ring_rows == 0 && !mma_now &&
                  (c->kv_u8 ? D == c->dq : (D % 4 == 0 && c->nv_class <= 32));
     for (int i = 0; i < n && fused; ++i) {
         const xn_req& r = reqs[i];
@@ -911,10 +929,11 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
     }
     if (sp.ctas > 0 && c->kv_u8) {
         if (c->profile && (rc = profile_begin(c, 0)) != XN_OK) return rc;
-        pick_split8(c->dq, c->gt, c->kv8_epl)<<<std::min(sp.ctas, c->decode_ctas), kv8::kThreads,
-                                                kv8::smem_bytes(c->gt, c->kv8_epl), c->stream>>>(
+        const Split8Fn fn8 = mma_now ? pick_split8_mma(c->dq, c->gt) : pick_split8(c->dq, c->gt, c->kv8_epl);
+        const size_t smem8 = mma_now ? kv8m::smem_bytes(c->gt, c->dq) : kv8::smem_bytes(c->gt, c->kv8_epl);
+        fn8<<<std::min(sp.ctas, c->decode_ctas), kv8::kThreads, smem8, c->stream>>>(
             reqs_d, units_d, items_d, cta_d, sp.ctas, pages_d, c->pool8, c->partials, c->sync_d,
-            c->pool_pages, Hkv, D, c->scale * 1.4426950408889634f, c->cos_d, c->sin_d);
+            c->pool_pages, Hkv, D, c->scale * 1.4426950408889634f, c->cos_d, c->sin_d, c->status_d);
         if (c->profile && (rc = profile_end(c)) != XN_OK) return rc;
         c->stats.kernel_launches += 1;
         c->stats.decode_launches += 1;
@@ -1132,6 +1151,9 @@ int32_t xn_ctx_create(const xn_ctx_desc* d, xn_ctx** out_ctx) {
     if (c->kv_u8) {
         c->dq = kv8::row_bytes_for(d->head_dim);
         c->tile_tokens = kPageTokens;  // the u8 kernel's plan tile is one page
+        if (const char* env = getenv("XORNET_ATTN_KV8_MMA")) c->kv8_mma = atoi(env) != 0;
+        if (const char* env = getenv("XORNET_ATTN_KV8_MMA_MIN_ROWS")) c->kv8_mma_min_rows = atoll(env);
+        c->kv8_mma = c->kv8_mma && d->head_dim == c->dq && (c->dq == 64 || c->dq == 128);
     }
     c->scale = 1.0f / sqrtf(float(d->head_dim));  // fast_attention.rs:135
     c->max_pos = d->max_pos;
@@ -1140,7 +1162,8 @@ int32_t xn_ctx_create(const xn_ctx_desc* d, xn_ctx** out_ctx) {
     c->sm_count = prop.multiProcessorCount;
     c->out_proj.resize(size_t(d->num_layers));
     c->qkv_proj.resize(size_t(d->num_layers));
-    c->decode_ctas = c->kv_u8 ? c->sm_count * kv8::blocks_per_sm(c->kv8_epl) : c->sm_count;
+    c->decode_ctas = c->kv_u8 ? c->sm_count * (c->kv8_mma ? kv8m::kBlocksPerSm : kv8::blocks_per_sm(c->kv8_epl))
+                              : c->sm_count;
     if (const char* env = getenv("XORNET_ATTN_DECODE_CTAS")) {
         int v = atoi(env);
         if (v > 0) c->decode_ctas = v;

@@ -413,7 +413,8 @@ attn_splitkv_u8_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restric
                        const uint8_t* __restrict__ pool, float* __restrict__ partials,
                        int* __restrict__ sync, long long pool_pages, int num_kv_heads, int head_dim,
                        float scale_log2, const float* __restrict__ cos_t,
-                       const float* __restrict__ sin_t) {
+                       const float* __restrict__ sin_t, int* __restrict__ status) {
+    (void)status;                       // this kernel waits on nothing that could fail
     constexpr int KPI = 32 / LPK;       // keys per warp iteration
     constexpr int DQ = LPK * EPL;       // bytes per stored row
     constexpr int WE = EPL / 4;         // 32-bit words of a row per lane
@@ -516,11 +517,16 @@ attn_splitkv_u8_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restric
             // newest PF - 1 groups" always names the iteration about to be used
             // (an item starts on a page boundary and a warp iteration never straddles one, so the
             // page's block address only changes when kk reaches a multiple of the page size)
+            // (the id of the page after the current one is fetched a page ahead, so that its latency is
+            // not paid when the boundary is reached)
             const uint8_t* page_blk = nullptr;
+            int next_page = pages[tok_begin / kPageTokens];
             auto issue = [&](int stage, int kk) {
                 const int key = kk + grp;
-                if (kk < loop_end && (kk % kPageTokens) == w * KPI)
-                    page_blk = base + size_t(pages[kk / kPageTokens]) * page_stride;
+                if (kk < loop_end && (kk % kPageTokens) == w * KPI) {
+                    page_blk = base + size_t(next_page) * page_stride;
+                    if (kk - w * KPI + kPageTokens < loop_end) next_page = pages[kk / kPageTokens + 1];
+                }
                 if (key < loop_end) {
                     const uint8_t* b = page_blk;
                     const int tk = key % kPageTokens;
