@@ -702,7 +702,7 @@ def run_gpu_arm(args):
             traffic = 708.71e6 + 5.04e6
             traffic_src = "ncu capture of this workload (2 of 30 layers), summary under profiles/"
         if args.workload == "c3" and not args.streams and world == 1 and u8:
-            traffic = 184.37e6 + 4.51e6
+            traffic = 185.15e6 + 4.54e6
             traffic_src = ("ncu capture of this workload over the u8 cache format (2 of 30 layers), "
                            "profiles/attn_splitkv_u8_c3_2layers.md")
         line = {
@@ -729,7 +729,8 @@ def run_gpu_arm(args):
                     "staged_value": (bytes_per_step * e2e_steps / (staged_ms * 1e-3) / 1e9) if staged_ms else None},
             "gpu_launches": int(launches),
             "roofline": {"bound": "hbm",
-                         "kernel": "attn_splitkv_u8_kernel" if u8 else "attn_splitkv_kernel<32,4>",
+                         "kernel": ("attn_splitkv_u8_mma_kernel (large batches) / attn_splitkv_u8_kernel" if u8
+                                    else "attn_splitkv_kernel<32,4>"),
                          "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak if peak else None, "peak_source": peak_kind,
                          "traffic": traffic, "traffic_source": traffic_src, "avg_launch_ms": kern_avg_ms,
