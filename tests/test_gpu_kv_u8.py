@@ -439,7 +439,7 @@ def test_pinned_host_rows_equal_staged_rows():
 
 
 # ---- the variant with q.k on the integer tensor-core path ---------------------------------------
-# Large submissions (>= 65536 attended rows) over 64- and 128-byte rows run
+# Large submissions (>= 524288 attended rows) over 64- and 128-byte rows run
 # attn_splitkv_u8_mma_kernel: the K bytes are an MMA operand, the query rows three int8 terms.
 # XORNET_ATTN_KV8_MMA_MIN_ROWS=0 forces it for every submission of a context created afterwards.
 
@@ -458,18 +458,21 @@ def test_tensor_core_variant(monkeypatch, case):
 
 
 def test_large_batch_takes_the_tensor_core_variant_and_agrees():
-    # 24 streams x ~700 tokens x 5 KV heads > 65536 attended rows: the default choice; the same
-    # batch with the variant disabled must agree within the f32 bounds, and both with the oracle
+    # 24 streams x ~700 tokens x 5 KV heads = 84 k attended rows, with the threshold lowered to 65536:
+    # the variant is chosen by size; the same batch with the variant disabled must agree within the
+    # f32 bounds, and both with the oracle
     import os
     rng = np.random.default_rng(91)
     lens = [int(x) for x in rng.integers(500, 900, 24)]
     outs = {}
     for mode in ("1", "0"):
         os.environ["XORNET_ATTN_KV8_MMA"] = mode
+        os.environ["XORNET_ATTN_KV8_MMA_MIN_ROWS"] = "65536"
         try:
             ctx = u8_ctx(1, 20, 5, 128, 400)
         finally:
             del os.environ["XORNET_ATTN_KV8_MMA"]
+            del os.environ["XORNET_ATTN_KV8_MMA_MIN_ROWS"]
         streams = [ctx.new_stream(1024) for _ in lens]
         for i, (st, L) in enumerate(zip(streams, lens)):
             st.fill_normal(0, 0, L, 77 + i)

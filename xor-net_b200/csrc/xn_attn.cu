@@ -117,8 +117,10 @@ struct xn_ctx {
     int dq = 0;                  // bytes per stored row
     int kv8_epl = 16;            // bytes of a row one lane of the attention kernel handles
     bool kv8_mma = true;         // q.k of the u8 attention kernel on the integer tensor-core path ...
-    long long kv8_mma_min_rows = 65536;  // ... for submissions that attend at least this many cached rows
-                                 // (smaller ones are latency bound: the kernel that also appends wins)
+    long long kv8_mma_min_rows = 1 << 19;  // ... for submissions that attend at least this many cached rows.
+                                 // (Smaller ones are latency bound and the kernel that also appends wins:
+                                 // measured on the config-3 shape, 1.75 against 1.80 ms per 30-layer step at
+                                 // 32 streams = 315 k rows, 2.64 against 2.42 at 64 streams = 676 k rows.)
     uint8_t* pool8 = nullptr;
     // ... and the f32 staging area the tensor-core prefill kernel reads in that format: the pages of
     // one stream and layer, dequantised, addressed through an identity page table
