@@ -23,9 +23,6 @@ namespace xn {
 namespace kv8m {
 
 using kv8::block_bytes;
-using kv8::cp_async16;
-using kv8::cp_async_commit;
-using kv8::cp_async_wait;
 using kv8::exp2_weight;
 using kv8::kLazy;
 using kv8::part_stride;
@@ -251,13 +248,7 @@ attn_splitkv_u8_mma_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __res
                     for (int s = 0; s < KS; ++s) {
                         const uint32_t a[4] = {kw[0][2 * s], kw[1][2 * s], kw[0][2 * s + 1], kw[1][2 * s + 1]};
 #pragma unroll
-                        for (int term = 0; term < 3; ++term) {
-#ifndef XN_KV8M_NO_MMA
-                            imma_u8s8(ci[term], a, bq[term][2 * s], bq[term][2 * s + 1]);
-#else
-                            ci[term][0] += int(a[0] ^ bq[term][2 * s]); ci[term][3] += int(a[3] ^ bq[term][2 * s + 1]);
-#endif
-                        }
+                        for (int term = 0; term < 3; ++term) imma_u8s8(ci[term], a, bq[term][2 * s], bq[term][2 * s + 1]);
                     }
                     // ---- scores of keys g and g + 8 for heads 2t, 2t + 1 (log2 domain) ----
                     const float* scp = stage_sc(p);
@@ -328,9 +319,6 @@ attn_splitkv_u8_mma_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __res
                     // ---- weighted V rows on the CUDA cores ----
 #pragma unroll
                     for (int i = 0; i < SUBS; ++i) {
-#ifdef XN_KV8M_NO_PV
-                        if (i > 0) break;
-#endif
                         const int kk = KPI * i + grp;
                         const float4 p4 = *reinterpret_cast<const float4*>(sm_p[kk]);
                         const float pv[4] = {p4.x, p4.y, p4.z, p4.w};
