@@ -87,7 +87,8 @@ typedef struct xn_ctx_desc {
     int32_t head_dim;     /* 1..256                                                              */
     int32_t page_tokens;  /* 0 or 64                                                             */
     int64_t pool_pages;   /* pages in the pool (each holds 64 tokens of every layer); if 0,      */
-    int64_t pool_bytes;   /*   derived from pool_bytes                                           */
+    int64_t pool_bytes;   /*   derived from pool_bytes; if that is 0 too, from XORNET_ATTN_POOL_MB */
+                          /*   or, when unset, half of the device memory that is free             */
     uint64_t shuffle_seed;/* 0: pages handed out in ascending order; else a seeded permutation   */
     int32_t max_pos;      /* rows of the RoPE tables, 0 if none                                  */
     int32_t prefill_mode; /* XN_PREFILL_*                                                        */
@@ -178,6 +179,42 @@ XN_API int32_t xn_profile_enable(xn_ctx* ctx, int32_t on);
 XN_API int32_t xn_profile_read_all(xn_ctx* ctx, double* ms, uint64_t* launches);
 XN_API int32_t xn_profile_read(xn_ctx* ctx, double* splitkv_ms, uint64_t* splitkv_launches,
                                double* prefill_ms, uint64_t* prefill_launches);
+
+/* ---- device groups ---------------------------------------------------------------------------- */
+
+/* The reference's server and batch_bench are ONE process whose slot threads share one model
+ * (server/main.rs:635-645, examples/batch_bench.rs:138-151) and each own a `Cache`
+ * (server/main.rs:92, batch_bench.rs:188).  A group puts every GPU of the box behind that one
+ * process: one context per device, and each new stream (one per `Cache::new`, i.e. per
+ * CpuRingCache::new, fast_attention.rs:31-34) is placed on one of them for its whole life.  The
+ * blocking calls of streams on different devices then run in parallel: every context has its own
+ * queue that merges its own concurrent callers. */
+typedef struct xn_group xn_group;
+
+enum {
+    XN_PLACE_LEAST_LOADED = 0, /* the device holding the fewest cached (or announced) tokens; ties: */
+                               /* the fewest live streams, then round-robin                          */
+    XN_PLACE_ROUND_ROBIN = 1   /* device = stream number mod number of devices                      */
+};
+
+/* One context per listed CUDA ordinal, all created from `desc` (its `device` and `cuda_stream` are
+ * ignored; pool_pages / pool_bytes apply per device).  n_devices = 0: the ordinals named by the
+ * environment variable XORNET_ATTN_DEVICES ("0,1,5"), or every visible device when it is unset. */
+XN_API int32_t xn_group_create(const xn_ctx_desc* desc, const int32_t* devices, int32_t n_devices,
+                               xn_group** out_group);
+/* Destroys the contexts of the group (and with them their streams). */
+XN_API int32_t xn_group_destroy(xn_group* group);
+XN_API int32_t xn_group_size(xn_group* group);          /* number of devices, or a negative xn_status */
+XN_API xn_ctx* xn_group_ctx(xn_group* group, int32_t i); /* the i-th device's context, or NULL        */
+/* xn_stream_create on the device the policy picks.  expected_tokens (0 = unknown) announces how many
+ * tokens the stream is going to hold, so that streams created before they are filled still spread by
+ * load.  *ctx_out receives the context that owns the stream: pass it with the stream to every call. */
+XN_API int32_t xn_group_stream_create(xn_group* group, int64_t max_seq_len, int64_t expected_tokens,
+                                      int32_t policy, xn_ctx** ctx_out, xn_stream** out_stream);
+/* The placement rule on its own (no GPU needed): tokens[i] and live_streams[i] describe device i,
+ * ticket is the number of streams placed so far.  Returns the chosen index or a negative xn_status. */
+XN_API int32_t xn_place_stream(int32_t n_devices, const int64_t* tokens, const int64_t* live_streams,
+                               uint64_t ticket, int32_t policy);
 
 /* ---- streams (one per reference `Cache`, models/llama/mod.rs:202-279) ------------------------ */
 

@@ -152,3 +152,18 @@ def test_sparse_pack_matches_the_oracle_encoder():
             a = xo.TernaryLinear(in_dim, out_dim, weights, xo.SPARSE, scale)
             b = TernaryLinear(in_dim, out_dim, weights, xn.SPARSE, scale)
             assert np.array_equal(a.packed, b.packed) and np.array_equal(a.w_scales, b.w_scales)
+
+
+def test_static_decode_entry_names_no_allocating_call(repo_root):
+    """The allocation-free entry point and its two kernels must not name any allocating or freeing
+    CUDA routine: read its definition and the kernels' header as text."""
+    src = open(os.path.join(repo_root, "xor-net_b200", "csrc", "xn_attn.cu")).read()
+    start = src.index('extern "C" int32_t xn_decode_attention_static')
+    body = src[start:]
+    body = body[:body.index("\n}\n") + 3]
+    kernels = open(os.path.join(repo_root, "xor-net_b200", "csrc", "xn_static_decode.cuh")).read()
+    for text in (body, kernels):
+        for word in ("cudaMalloc", "cudaFree", "cudaHostAlloc", "cudaMallocHost", "cudaMallocAsync", "operator new",
+                     "std::vector", "malloc("):
+            assert word not in text, f"{word!r} appears in the allocation-free entry point"
+    assert "cudaGetSymbolAddress" in body and "g_static_scratch" in body

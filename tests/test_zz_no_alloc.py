@@ -14,6 +14,7 @@ import ctypes as C
 import numpy as np
 import pytest
 
+import oracle as xo
 import xor_net_b200 as xn
 from gpu_util import ABS_TOL, REL_TOL, assert_parity, rand_qkv
 
@@ -56,9 +57,41 @@ def test_static_entry_matches_regular_entry_twice(Hq, Hkv, D, L0):
         k_all, v_all = st.read_range(0, 0, pos + 1)           # cache including the new token
         got, used = static_decode(lib, torch, q, k_all, v_all, Hq, Hkv, D, pos + 1, pad=37 * call)
         assert_parity(got, want, f"static call {call}", ABS_TOL, REL_TOL)
+        # ... and against the CPU oracle run over the same cached bytes
+        ref = xo.RingCache(1, Hkv, pos + 1, D)
+        ref.append(0, 0, k_all[:, :pos], v_all[:, :pos])
+        cpu = xo.fast_attention(q, k, v, 0, pos, ref, Hq, Hkv, D)
+        assert_parity(got, cpu, f"static call {call} vs oracle", ABS_TOL, REL_TOL)
+        ref.close()
         grown.append(used)
     assert grown[1] == 0, "the second call changed the amount of free device memory"
     ctx.close()
+
+
+@pytest.mark.parametrize("Hq,Hkv,D,L", [
+    (1, 1, 8, 177601),     # 592 splits of 301 tokens: the last split starts past kv_len (empty record)
+    (8, 2, 256, 3000),     # the widest row the scratch takes
+    (600, 300, 16, 700),   # so many heads that the record budget leaves one split per head
+])
+def test_static_entry_split_limits_against_the_oracle(Hq, Hkv, D, L):
+    """The split-count caps (records per call, blocks per launch), an empty trailing split and
+    head_dim 256, on dense caller-owned caches, two calls in a row; the checker is the CPU oracle."""
+    import torch
+
+    lib = xn.load()
+    rng = np.random.default_rng(7 * D + Hq)
+    k_all = rng.standard_normal((Hkv, L, D)).astype(np.float32)
+    v_all = rng.standard_normal((Hkv, L, D)).astype(np.float32)
+    ref = xo.RingCache(1, Hkv, L, D)
+    ref.append(0, 0, k_all[:, :L - 1], v_all[:, :L - 1])
+    for call in range(2):
+        q = rng.standard_normal((1, Hq, 1, D)).astype(np.float32)
+        want = xo.fast_attention(q, k_all[None, :, L - 1:L], v_all[None, :, L - 1:L], 0, L - 1, ref, Hq, Hkv, D)
+        got, used = static_decode(lib, torch, q, k_all, v_all, Hq, Hkv, D, L, pad=5 * call)
+        assert_parity(got, want, f"static call {call}", ABS_TOL, REL_TOL)
+        if call:
+            assert used == 0, "the second call changed the amount of free device memory"
+    ref.close()
 
 
 def test_static_entry_rejects_sizes_beyond_its_scratch():

@@ -5,14 +5,16 @@ this package is the Python host side.  Importing it never falls back to a CPU pa
 if the library is not built or no sm_100 device is present.
 """
 from ._build import LIB_PATH, build_library
-from .api import (Context, DeviceKvCache, FastTensor, Stream, TernaryLinear, XnError,
-                  close_default_contexts, default_context, fast_attention, rope_tables)
+from .api import (Context, DeviceKvCache, FastTensor, Group, Stream, TernaryLinear, XnError,
+                  close_default_contexts, default_context, default_group, fast_attention, place_stream,
+                  rope_tables)
 from . import sharding
-from ._ffi import (KV_F32, KV_U8, PACK4, PACK5, SPARSE, REQ_DEVICE_PTRS, REQ_HOST_PINNED, REQ_OUT_PROJ, REQ_QKV_PROJ, REQ_ROPE,
+from ._ffi import (PLACE_LEAST_LOADED, PLACE_ROUND_ROBIN, KV_F32, KV_U8, PACK4, PACK5, SPARSE, REQ_DEVICE_PTRS, REQ_HOST_PINNED, REQ_OUT_PROJ, REQ_QKV_PROJ, REQ_ROPE,
                    REQ_SEQ_MAJOR, SIGNATURES, load)
 
 __all__ = [
-    "Context", "Stream", "DeviceKvCache", "FastTensor", "XnError", "fast_attention", "rope_tables",
+    "Context", "Stream", "Group", "default_group", "place_stream", "PLACE_LEAST_LOADED", "PLACE_ROUND_ROBIN",
+    "DeviceKvCache", "FastTensor", "XnError", "fast_attention", "rope_tables",
     "default_context", "close_default_contexts", "build_library", "load", "LIB_PATH", "SIGNATURES",
     "REQ_DEVICE_PTRS", "REQ_ROPE", "REQ_SEQ_MAJOR", "REQ_HOST_PINNED", "REQ_OUT_PROJ", "REQ_QKV_PROJ", "KV_F32", "KV_U8", "SPARSE", "PACK4",
     "PACK5", "TernaryLinear", "sharding",

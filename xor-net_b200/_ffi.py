@@ -52,6 +52,7 @@ class OutProjDesc(C.Structure):
 REQ_DEVICE_PTRS, REQ_ROPE, REQ_SEQ_MAJOR, REQ_HOST_PINNED, REQ_OUT_PROJ, REQ_QKV_PROJ = 1, 2, 4, 8, 16, 32
 PACK4, PACK5, SPARSE = 4, 5, 64
 KV_F32, KV_U8 = 0, 1   # xn_ctx_desc.kv_format
+PLACE_LEAST_LOADED, PLACE_ROUND_ROBIN = 0, 1
 
 STATUS_NAMES = {
     0: "XN_OK", 1: "XN_ERR_ARG", 2: "XN_ERR_SHAPE", 3: "XN_ERR_HANDLE", 4: "XN_ERR_OUT_OF_PAGES",
@@ -105,6 +106,14 @@ SIGNATURES = {
                                     C.c_void_p, C.c_void_p]),
     "xn_ternary_pack_sparse": (C.c_int32, [C.c_int32, C.c_int32, C.c_void_p, C.c_float, C.c_void_p,
                                            C.c_int64, C.POINTER(C.c_int64), C.c_void_p]),
+    "xn_group_create": (C.c_int32, [C.POINTER(CtxDesc), c_i32p, C.c_int32, C.POINTER(C.c_void_p)]),
+    "xn_group_destroy": (C.c_int32, [C.c_void_p]),
+    "xn_group_size": (C.c_int32, [C.c_void_p]),
+    "xn_group_ctx": (C.c_void_p, [C.c_void_p, C.c_int32]),
+    "xn_group_stream_create": (C.c_int32, [C.c_void_p, C.c_int64, C.c_int64, C.c_int32,
+                                           C.POINTER(C.c_void_p), C.POINTER(C.c_void_p)]),
+    "xn_place_stream": (C.c_int32, [C.c_int32, C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.c_uint64,
+                                    C.c_int32]),
     "xn_version": (C.c_char_p, []),
 }
 

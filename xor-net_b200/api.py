@@ -59,6 +59,36 @@ def rope_tables(theta: float, head_dim: int, max_pos: int, scaling=None):
     return cos, sin
 
 
+def _ctx_desc(num_layers, num_heads, num_kv_heads, head_dim, pool_pages, pool_bytes, device, shuffle_seed,
+              rope, cuda_stream, prefill_mode, batch_window_us, kv_format):
+    """(xn_ctx_desc, arrays it points at)."""
+    d = CtxDesc()
+    d.device, d.num_layers, d.num_heads = device, num_layers, num_heads
+    d.num_kv_heads, d.head_dim, d.page_tokens = num_kv_heads, head_dim, 64
+    d.pool_pages, d.pool_bytes, d.shuffle_seed = pool_pages, pool_bytes, shuffle_seed
+    d.prefill_mode, d.batch_window_us = prefill_mode, batch_window_us
+    d.kv_format = kv_format
+    d.cuda_stream = cuda_stream or None
+    keep = None
+    if rope is not None:
+        cos, sin = _f32(rope[0]), _f32(rope[1])
+        keep = (cos, sin)
+        d.max_pos, d.rope_cos, d.rope_sin = cos.shape[0], _ptr(cos), _ptr(sin)
+    return d, keep
+
+
+def place_stream(tokens, live_streams, ticket: int, policy: int = _ffi.PLACE_LEAST_LOADED) -> int:
+    """xn_place_stream: the device a new stream goes to, given every device's cached (or announced)
+    tokens and live streams and the number of streams placed so far.  Needs no GPU."""
+    n = len(tokens)
+    t = (C.c_int64 * n)(*[int(x) for x in tokens])
+    l = (C.c_int64 * n)(*[int(x) for x in live_streams])
+    where = _ffi.load().xn_place_stream(n, t, l, ticket, policy)
+    if where < 0:
+        raise XnError(-where, "xn_place_stream: bad argument")
+    return where
+
+
 class Stream:
     """One sequence's KV cache (one reference ``Cache``)."""
 
@@ -125,33 +155,35 @@ class Context:
         self.num_layers, self.num_heads = num_layers, num_heads
         self.num_kv_heads, self.head_dim = num_kv_heads, head_dim
         self.device = device
-        d = CtxDesc()
-        d.device, d.num_layers, d.num_heads = device, num_layers, num_heads
-        d.num_kv_heads, d.head_dim, d.page_tokens = num_kv_heads, head_dim, 64
-        d.pool_pages, d.pool_bytes, d.shuffle_seed = pool_pages, pool_bytes, shuffle_seed
-        d.prefill_mode, d.batch_window_us = prefill_mode, batch_window_us
-        d.kv_format = kv_format
         self.kv_format = kv_format
-        d.cuda_stream = cuda_stream or None
-        self._rope = None
-        if rope is not None:
-            cos, sin = _f32(rope[0]), _f32(rope[1])
-            self._rope = (cos, sin)
-            d.max_pos, d.rope_cos, d.rope_sin = cos.shape[0], _ptr(cos), _ptr(sin)
+        self._owner = None
+        d, self._rope = _ctx_desc(num_layers, num_heads, num_kv_heads, head_dim, pool_pages, pool_bytes, device,
+                                  shuffle_seed, rope, cuda_stream, prefill_mode, batch_window_us, kv_format)
         h = C.c_void_p()
         rc = self.lib.xn_ctx_create(C.byref(d), C.byref(h))
         if rc != 0:
             raise XnError(rc, (self.lib.xn_last_error(None) or b"").decode())
         self.handle = h.value
 
+    @classmethod
+    def _adopt(cls, owner, handle, device, num_layers, num_heads, num_kv_heads, head_dim, kv_format):
+        """A context that a ``Group`` created and destroys."""
+        self = cls.__new__(cls)
+        self.lib = _ffi.load()
+        self.num_layers, self.num_heads = num_layers, num_heads
+        self.num_kv_heads, self.head_dim = num_kv_heads, head_dim
+        self.device, self.kv_format = device, kv_format
+        self._owner, self._rope, self.handle = owner, None, handle
+        return self
+
     def _check(self, rc: int):
         if rc != 0:
             raise XnError(rc, (self.lib.xn_last_error(self.handle) or b"").decode())
 
     def close(self):
-        if getattr(self, "handle", None):
+        if getattr(self, "handle", None) and self._owner is None:
             self.lib.xn_ctx_destroy(self.handle)
-            self.handle = None
+        self.handle = None
 
     def __del__(self):
         try:
@@ -350,8 +382,77 @@ class FastTensor:
         return self.data.reshape(self.shape)
 
 
+class Group:
+    """One context per GPU behind one handle (``xn_group``): what a single server process uses to
+    reach every GPU of the box.  ``new_stream`` places the stream on the least-loaded device (or
+    round-robin) and returns a ``Stream`` bound to that device's ``Context``."""
+
+    def __init__(self, num_layers: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                 devices: Optional[Sequence[int]] = None, pool_pages: int = 0, pool_bytes: int = 0,
+                 shuffle_seed: int = 0, rope: Optional[tuple] = None, prefill_mode: int = 0,
+                 batch_window_us: int = 0, kv_format: int = KV_F32):
+        self.lib = _ffi.load()
+        d, self._rope = _ctx_desc(num_layers, num_heads, num_kv_heads, head_dim, pool_pages, pool_bytes, 0,
+                                  shuffle_seed, rope, 0, prefill_mode, batch_window_us, kv_format)
+        devs = list(devices) if devices else []
+        arr = (C.c_int32 * max(1, len(devs)))(*devs)
+        h = C.c_void_p()
+        rc = self.lib.xn_group_create(C.byref(d), arr if devs else None, len(devs), C.byref(h))
+        if rc != 0:
+            raise XnError(rc, (self.lib.xn_last_error(None) or b"").decode())
+        self.handle = h.value
+        n = self.lib.xn_group_size(self.handle)
+        self.contexts = [Context._adopt(self, self.lib.xn_group_ctx(self.handle, i), devs[i] if devs else i,
+                                        num_layers, num_heads, num_kv_heads, head_dim, kv_format)
+                         for i in range(n)]
+        self._by_handle = {c.handle: c for c in self.contexts}
+
+    def __len__(self):
+        return len(self.contexts)
+
+    def new_stream(self, max_seq_len: int, expected_tokens: int = 0,
+                   policy: int = _ffi.PLACE_LEAST_LOADED) -> Stream:
+        ch, sh = C.c_void_p(), C.c_void_p()
+        rc = self.lib.xn_group_stream_create(self.handle, max_seq_len, expected_tokens, policy,
+                                             C.byref(ch), C.byref(sh))
+        if rc != 0:
+            raise XnError(rc, (self.lib.xn_last_error(None) or b"").decode())
+        return Stream(self._by_handle[ch.value], sh.value, max_seq_len)
+
+    def close(self):
+        if getattr(self, "handle", None):
+            self.lib.xn_group_destroy(self.handle)
+            for c in self.contexts:
+                c.handle = None
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 _contexts: dict = {}
 _contexts_lock = threading.Lock()
+_groups: dict = {}
+
+
+def default_group(num_layers, num_heads, num_kv_heads, head_dim) -> Group:
+    """Process-wide group per model shape over the devices of ``XORNET_ATTN_DEVICES`` (default: all
+    visible), created on first use.  Pool per device: ``XORNET_ATTN_POOL_PAGES`` pages if set, else
+    ``XORNET_ATTN_POOL_MB`` (default 1024) megabytes."""
+    key = (num_layers, num_heads, num_kv_heads, head_dim)
+    with _contexts_lock:
+        g = _groups.get(key)
+        if g is None or g.handle is None:
+            pages = int(os.environ.get("XORNET_ATTN_POOL_PAGES", "0"))
+            mb = int(os.environ.get("XORNET_ATTN_POOL_MB", "1024"))
+            g = Group(num_layers, num_heads, num_kv_heads, head_dim, pool_pages=pages,
+                      pool_bytes=0 if pages else mb << 20)
+            _groups[key] = g
+        return g
+
 
 
 def default_context(num_layers, num_heads, num_kv_heads, head_dim, device: int = 0) -> Context:
@@ -377,6 +478,9 @@ def close_default_contexts():
         for ctx in _contexts.values():
             ctx.close()
         _contexts.clear()
+        for g in _groups.values():
+            g.close()
+        _groups.clear()
 
 
 class DeviceKvCache:
@@ -388,10 +492,10 @@ class DeviceKvCache:
     (:62-71, :117-128) is written but never read, so it cannot influence any result.
     """
 
-    def __init__(self, num_layers, num_kv_heads, max_seq_len, head_dim, use_u8=False, device=0):
+    def __init__(self, num_layers, num_kv_heads, max_seq_len, head_dim, use_u8=False, device=None):
         self.num_layers, self.num_kv_heads = num_layers, num_kv_heads
         self.max_seq_len, self.head_dim = max_seq_len, head_dim
-        self.device = device
+        self.device = device   # None: whichever GPU of the process-wide group is least loaded
         self._ctx: Optional[Context] = None
         self._stream: Optional[Stream] = None
 
@@ -401,9 +505,19 @@ class DeviceKvCache:
 
     def _bind(self, num_heads: int):
         if self._stream is None:
-            self._ctx = default_context(self.num_layers, num_heads, self.num_kv_heads,
-                                        self.head_dim, self.device)
-            self._stream = self._ctx.new_stream(self.max_seq_len)
+            if self.device is None:
+                # one process, every GPU: the cache lands on the device with the fewest cached tokens
+                # (XORNET_ATTN_PLACEMENT=rr: stream number mod number of devices)
+                rr = os.environ.get("XORNET_ATTN_PLACEMENT", "least").lower() in ("rr", "round_robin")
+                group = default_group(self.num_layers, num_heads, self.num_kv_heads, self.head_dim)
+                self._stream = group.new_stream(self.max_seq_len, 0,
+                                                _ffi.PLACE_ROUND_ROBIN if rr else _ffi.PLACE_LEAST_LOADED)
+                self._ctx = self._stream.ctx
+                self.device = self._ctx.device
+            else:
+                self._ctx = default_context(self.num_layers, num_heads, self.num_kv_heads,
+                                            self.head_dim, self.device)
+                self._stream = self._ctx.new_stream(self.max_seq_len)
         return self._ctx, self._stream
 
     def _buffers(self, which: int):

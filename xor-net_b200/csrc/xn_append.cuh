@@ -77,6 +77,7 @@ rope_append_kernel(const ReqDev* __restrict__ reqs, const int* __restrict__ page
                    float* __restrict__ k_pool, float* __restrict__ v_pool,
                    const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                    long long pool_pages, int num_heads, int num_kv_heads, int head_dim, int nv) {
+    pdl_launch_dependents();   // a prefill kernel launched as a programmatic dependent may set up now
     const ReqDev& r = reqs[blockIdx.y];
     const bool rope = r.flags & 1u;
     const bool q_rows = r.flags & 3u;  // q is rotated, or just moved next to the kernels
@@ -88,39 +89,85 @@ rope_append_kernel(const ReqDev* __restrict__ reqs, const int* __restrict__ page
     const int dp = nv * 4;
     const int* pages = page_ids + r.page_off;
     const bool dim_vec = (head_dim % 8) == 0;
-    for (long long row = (long long)blockIdx.x * 16 + hw; row < n_rows;
-         row += (long long)gridDim.x * 16) {
-        const int t = int(row / rows_per_tok);
-        int rr = int(row % rows_per_tok);
-        const int pos = r.index_pos + t;
-        const float* c = cos_t + size_t(pos) * half;
-        const float* s = sin_t + size_t(pos) * half;
-        const float* src;
-        float* dst;
-        bool rotate = false;
-        if (q_rows && rr < num_heads) {
-            // query row -> scratch (ReqDev::q points at it), rotated when the request asks for it
-            src = r.q_in + size_t(rr) * r.qi_hs + size_t(t) * r.qi_ts;
-            dst = const_cast<float*>(r.q) + size_t(rr) * r.q_hs + size_t(t) * r.q_ts;
-            rotate = rope;
-        } else {
-            if (q_rows) rr -= num_heads;
-            if ((long long)t + r.cap < (long long)r.seq_len) continue;  // overwritten later in this call
-            const int slot = pos % r.cap;
-            if (rr < num_kv_heads) {
-                src = r.k + size_t(rr) * r.kv_hs + size_t(t) * r.kv_ts;
-                dst = k_pool + slot_offset(pages, pool_pages, r.layer, num_kv_heads, rr, slot, dp);
-                rotate = rope;
+    // Four rows per half-warp and pass: their page-table reads, then their row loads, are in
+    // flight together (one row at a time is a chain of three dependent memory round trips).
+    constexpr int U = 4;
+    const long long stride = (long long)gridDim.x * 16;
+    for (long long row0 = (long long)blockIdx.x * 16 + hw; row0 < n_rows; row0 += stride * U) {
+        const float* src[U];
+        float* dst[U];
+        const float* c[U];
+        const float* s[U];
+        int kind[U];   // 0 skip, 1 copy, 2 rotate
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const long long row = row0 + u * stride;
+            kind[u] = 0;
+            src[u] = nullptr;
+            dst[u] = nullptr;
+            c[u] = s[u] = nullptr;
+            if (row >= n_rows) continue;
+            const int t = int(row / rows_per_tok);
+            int rr = int(row % rows_per_tok);
+            const int pos = r.index_pos + t;
+            c[u] = cos_t + size_t(pos) * half;
+            s[u] = sin_t + size_t(pos) * half;
+            if (q_rows && rr < num_heads) {
+                // query row -> scratch (ReqDev::q points at it), rotated when the request asks for it
+                src[u] = r.q_in + size_t(rr) * r.qi_hs + size_t(t) * r.qi_ts;
+                dst[u] = const_cast<float*>(r.q) + size_t(rr) * r.q_hs + size_t(t) * r.q_ts;
+                kind[u] = rope ? 2 : 1;
             } else {
-                rr -= num_kv_heads;
-                src = r.v + size_t(rr) * r.kv_hs + size_t(t) * r.kv_ts;
-                dst = v_pool + slot_offset(pages, pool_pages, r.layer, num_kv_heads, rr, slot, dp);
+                if (q_rows) rr -= num_heads;
+                if ((long long)t + r.cap < (long long)r.seq_len) continue;  // overwritten later in this call
+                const int slot = pos % r.cap;
+                if (rr < num_kv_heads) {
+                    src[u] = r.k + size_t(rr) * r.kv_hs + size_t(t) * r.kv_ts;
+                    dst[u] = k_pool + slot_offset(pages, pool_pages, r.layer, num_kv_heads, rr, slot, dp);
+                    kind[u] = rope ? 2 : 1;
+                } else {
+                    rr -= num_kv_heads;
+                    src[u] = r.v + size_t(rr) * r.kv_hs + size_t(t) * r.kv_ts;
+                    dst[u] = v_pool + slot_offset(pages, pool_pages, r.layer, num_kv_heads, rr, slot, dp);
+                    kind[u] = 1;
+                }
             }
         }
-        const bool vec = dim_vec &&
-                         (((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0);
-        if (rotate) row_rotate(src, dst, c, s, head_dim, hl, vec);
-        else row_copy(src, dst, head_dim, hl, vec);
+        bool fast = dim_vec && head_dim <= 128;   // whole rows as one float4 per lane and half
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+            if (kind[u] && ((reinterpret_cast<uintptr_t>(src[u]) | reinterpret_cast<uintptr_t>(dst[u])) & 15)) fast = false;
+        if (fast) {
+            const int i = hl * 4;
+            const bool in = i < half;
+            float4 lo[U], hi[U], cv[U], sv[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                if (!kind[u] || !in) continue;
+                lo[u] = *reinterpret_cast<const float4*>(src[u] + i);
+                hi[u] = *reinterpret_cast<const float4*>(src[u] + i + half);
+                if (kind[u] == 2) {
+                    cv[u] = *reinterpret_cast<const float4*>(c[u] + i);
+                    sv[u] = *reinterpret_cast<const float4*>(s[u] + i);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                if (!kind[u] || !in) continue;
+                if (kind[u] == 2) rotate4(lo[u], hi[u], cv[u], sv[u]);
+                *reinterpret_cast<float4*>(dst[u] + i) = lo[u];
+                *reinterpret_cast<float4*>(dst[u] + i + half) = hi[u];
+            }
+        } else {
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                if (!kind[u]) continue;
+                const bool vec = dim_vec && (((reinterpret_cast<uintptr_t>(src[u]) |
+                                               reinterpret_cast<uintptr_t>(dst[u])) & 15) == 0);
+                if (kind[u] == 2) row_rotate(src[u], dst[u], c[u], s[u], head_dim, hl, vec);
+                else row_copy(src[u], dst[u], head_dim, hl, vec);
+            }
+        }
     }
 }
 

@@ -81,6 +81,15 @@ struct xn_stream {
     int64_t cap = 0;
     std::vector<int32_t> pages;   // page id of slots [64*i, 64*i+64)
     std::vector<int64_t> hw;      // per layer: highest written position + 1
+    int64_t expected = 0;         // tokens the creator said the stream will hold (placement only)
+};
+
+// One context per GPU of a box behind one handle; streams are placed on the least-loaded one.
+struct xn_group {
+    uint32_t magic = 0x786e4752u;  // "xnGR"
+    std::vector<xn_ctx*> ctxs;
+    std::mutex mu;
+    uint64_t ticket = 0;           // streams created so far
 };
 
 struct xn_ctx {
@@ -105,6 +114,7 @@ struct xn_ctx {
     bool out_tc = true;      // output projection on the tensor cores (else the dp4a kernel)
     bool out_pdl = true;     // ... launched as a programmatic dependent of the quantiser kernel
     bool out_rows_kernel = true;  // ... and, for more than 128 rows, the many-row variant
+    bool pf_pdl = true;      // tensor-core prefill launched as a programmatic dependent of the append
     int* sync_d = nullptr;   // chunk counter, done counter, per-unit arrival counters
     size_t sync_cap = 0;     // ints
     cudaStream_t stream = nullptr;
@@ -151,6 +161,7 @@ struct xn_ctx {
     int* status_d = nullptr;  // device-side address of the same word
     int* status_h = nullptr;
     xn_stats stats{};
+    std::mutex err_mu;       // guards last_error only: readers never wait for a submission
     std::string last_error;
 
     // tensor-core prefill (tcgen05 TF32): tensor maps over the K and V pools
@@ -180,6 +191,7 @@ int32_t fail(xn_ctx* ctx, int32_t code, const char* fmt, ...) {
     vsnprintf(buf, sizeof buf, fmt, ap);
     va_end(ap);
     if (ctx) {
+        std::lock_guard<std::mutex> g(ctx->err_mu);
         ctx->last_error = buf;
     } else {
         std::lock_guard<std::mutex> g(g_err_mu);
@@ -578,6 +590,36 @@ bool use_tf32(const xn_ctx* c, const xn_req& r, bool direct) {
     return r.seq_len >= (c->prefill_mode == XN_PREFILL_TF32 ? 2 : c->tf32_min_rows);
 }
 
+// What a submission changes in its streams before its first launch (pages taken from the pool,
+// the per-layer high-water marks).  Unless commit() is called, the destructor puts every stream
+// back as it was, so a submission that fails on the way to its launches leaves no position
+// claimed that was never written.
+struct StreamRollback {
+    struct Entry {
+        xn_stream* s;
+        size_t n_pages;
+        int layer;
+        int64_t hw;
+    };
+    xn_ctx* c;
+    std::vector<Entry> entries;
+    bool committed = false;
+    explicit StreamRollback(xn_ctx* ctx) : c(ctx) {}
+    void note(xn_stream* s, int layer) { entries.push_back({s, s->pages.size(), layer, s->hw[size_t(layer)]}); }
+    void commit() { committed = true; }
+    ~StreamRollback() {
+        if (committed) return;
+        for (auto it = entries.rbegin(); it != entries.rend(); ++it) {
+            xn_stream* s = it->s;
+            while (s->pages.size() > it->n_pages) {
+                c->free_pages.push_back(s->pages.back());
+                s->pages.pop_back();
+            }
+            s->hw[size_t(it->layer)] = it->hw;
+        }
+    }
+};
+
 // reqs[i] are valid, on distinct streams, all host-mode or all device-mode.
 int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
     const int Hq = c->num_heads, Hkv = c->num_kv_heads, D = c->head_dim, nv = c->nv;
@@ -602,6 +644,7 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
                         new_pages, c->free_pages.size(), c->pool_pages);
     }
     // -- pages, gaps, staging sizes
+    StreamRollback undo(c);   // until the launches are certain, every early return restores the streams
     std::vector<GapFill> gaps;
     size_t io_in = 0, io_out = 0, qrot_floats = 0, n_page_ids = 0, out_rows = 0, qkv_rows = 0;
     const size_t qkv_width = size_t(Hq + 2 * Hkv) * D;   // floats of one projected row [q | k | v]
@@ -612,6 +655,7 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         if (r.seq_len == 0) continue;
         xn_stream* s = r.stream;
         const int64_t end = r.index_pos + r.seq_len;
+        undo.note(s, r.layer);
         int32_t rc = ensure_pages(c, s, std::min<int64_t>(end, s->cap));
         if (rc != XN_OK) return rc;
         int64_t& hw = s->hw[r.layer];
@@ -678,6 +722,10 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         return fail(c, XN_ERR_CAPACITY, "%lld attention rows in one submission exceed the limit %lld",
                     n_units, kMaxUnits);
 
+    // Small staged calls skip the two DMA copies: the library's page-locked staging buffer is
+    // device-accessible, so the kernels read the inputs from it and write the outputs into it
+    // over PCIe themselves; what remains is one plan upload, the launches and the wait.
+    const bool stage_direct = host_mode && !pinned && io_in + io_out <= c->stage_direct_bytes;
     int32_t rc;
     if (c->kv_u8 && stage_need && (rc = ensure_stage(c, stage_need)) != XN_OK) return rc;
     if ((rc = grow_device(c, &c->q_rot, &c->q_rot_cap, qrot_floats)) != XN_OK) return rc;
@@ -686,10 +734,6 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
     }
     if (qkv_rows && (rc = grow_device(c, &c->qkv_seq, &c->qkv_seq_cap, qkv_rows * qkv_width)) != XN_OK) return rc;
     if (host_mode && (rc = grow_io(c, io_in + io_out)) != XN_OK) return rc;
-    // Small staged calls skip the two DMA copies: the library's page-locked staging buffer is
-    // device-accessible, so the kernels read the inputs from it and write the outputs into it
-    // over PCIe themselves; what remains is one plan upload, the launches and the wait.
-    const bool stage_direct = host_mode && !pinned && io_in + io_out <= c->stage_direct_bytes;
     unsigned char* const io_base = stage_direct ? c->io_host : c->io_dev;
 
     // -- request descriptors, page ids, units
@@ -762,6 +806,7 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
             q_ts = kv_ts = (long long)qkv_width;
         }
         d.q_in = q_dev; d.qi_hs = q_hs; d.qi_ts = q_ts;
+        const bool to_tf32 = r.index_pos + S <= s->cap && use_tf32(c, r, direct);
         if (fused) {
             d.q = q_dev; d.q_hs = q_hs; d.q_ts = q_ts;
             d.flags = 8u | (rope ? 1u : 0u);
@@ -793,7 +838,7 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         d.cap = int(std::min<int64_t>(s->cap, int64_t(1) << 30));
         if (r.index_pos + S > s->cap) {
             for (int t = 0; t < S; ++t) { ring_rows.push_back(i); ring_rows.push_back(t); }
-        } else if (use_tf32(c, r, direct)) {
+        } else if (to_tf32) {
             tf32_reqs.push_back(i);
         } else {
             for (int h = 0; h < Hkv; ++h)
@@ -894,7 +939,8 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         if (need && (rc = grow_device(c, &c->q8, &c->q8_cap, need)) != XN_OK) return rc;
     }
 
-    // -- launches
+    // -- launches: every sizing step above has succeeded, the cache positions are going to be written
+    undo.commit();
     for (const OutRun& run : qkv_runs) {   // x -> [q | k | v] rows, before anything reads them
         const OutRowDev* rows_d = reinterpret_cast<const OutRowDev*>(slot->dev + o_qkv) + run.row_begin;
         if (c->profile && (rc = profile_begin(c, 3)) != XN_OK) return rc;
@@ -917,7 +963,7 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         c->stats.kernel_launches += 1;
     }
     if (max_rows > 0) {
-        dim3 grid(unsigned(std::min<long long>((max_rows + 15) / 16, 4096)), unsigned(n));
+        dim3 grid(unsigned(std::min<long long>((max_rows + 63) / 64, 4096)), unsigned(n));
         if (c->kv_u8) {
             dim3 grid8(unsigned(std::min<long long>((max_rows + 7) / 8, 4096)), unsigned(n));
             kv8::rope_append_u8_kernel<<<grid8, 256, 0, c->stream>>>(reqs_d, pages_d, c->pool8, c->cos_d,
@@ -951,7 +997,7 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         c->stats.decode_launches += 1;
     }
     for (int i : tf32_reqs) {
-        const ReqDev& d = rd[i];
+        const ReqDev& d = rd[size_t(i)];
         PrefillArgs pa;
         pa.q = d.q;
         pa.q_hs = d.q_hs;
@@ -968,7 +1014,6 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         pa.head_dim = D;
         pa.scale_log2 = c->scale * 1.4426950408889634f;
         pa.status = c->status_d;
-        dim3 grid(unsigned((d.seq_len + pf::kBM - 1) / pf::kBM) * unsigned(Hq));
         if (c->profile && (rc = profile_begin(c, 1)) != XN_OK) return rc;
         if (c->kv_u8) {
             // the stream's pages of this layer (the new rows included: the append ran above),
@@ -978,9 +1023,22 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
                 c->pool8, pages_d + d.page_off, n_pages, d.layer, c->pool_pages, Hkv, D, c->dq, c->k_stage,
                 c->v_stage);
             c->stats.kernel_launches += 1;
-            prefill_tf32_kernel<<<grid, pf::kThreads, pf::kSmemBytes, c->stream>>>(c->k_stage_map, c->v_stage_map, pa);
-        } else
-        prefill_tf32_kernel<<<grid, pf::kThreads, pf::kSmemBytes, c->stream>>>(c->k_map, c->v_map, pa);
+        }
+        // A programmatic dependent of the kernel before it (the append): its blocks set up while
+        // that kernel drains; their reads of what it wrote wait inside the kernel.  Not behind
+        // another prefill launch: two of them must not share the SMs' tensor memory.
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(unsigned((d.seq_len + pf::kBM - 1) / pf::kBM) * unsigned(Hq));
+        cfg.blockDim = dim3(pf::kThreads);
+        cfg.dynamicSmemBytes = pf::kSmemBytes;
+        cfg.stream = c->stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = (c->pf_pdl && i == tf32_reqs.front() && !c->profile) ? 1 : 0;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        XN_CUDA(c, cudaLaunchKernelEx(&cfg, prefill_tf32_kernel, c->kv_u8 ? c->k_stage_map : c->k_map,
+                                      c->kv_u8 ? c->v_stage_map : c->v_map, pa));
         if (c->profile && (rc = profile_end(c)) != XN_OK) return rc;
         c->stats.kernel_launches += 1;
         c->stats.prefill_launches += 1;
@@ -1053,6 +1111,11 @@ void run_group(xn_ctx* c, std::vector<Pending*>& group) {
         int32_t rc = submit_locked(c, int(ok.size()), ok.data(), true);
         for (Pending* p : ok_p) p->status = rc;
         c->stats.coalesced_max = std::max<uint64_t>(c->stats.coalesced_max, ok.size());
+        // The callers are independent, as in the reference: when the merged submission was
+        // refused before anything ran (it left the streams untouched), one request that does not
+        // fit must not fail the others.  Run them one by one; each gets its own status.
+        if (ok.size() > 1 && (rc == XN_ERR_OUT_OF_PAGES || rc == XN_ERR_CAPACITY || rc == XN_ERR_NOMEM))
+            for (size_t i = 0; i < ok.size(); ++i) ok_p[i]->status = submit_locked(c, 1, &ok[i], true);
     }
 }
 
@@ -1096,10 +1159,16 @@ extern "C" {
 const char* xn_version(void) { return "xn_attn 0.1 sm_100a"; }
 
 const char* xn_last_error(xn_ctx* ctx) {
-    if (ctx_ok(ctx)) return ctx->last_error.c_str();
-    std::lock_guard<std::mutex> g(g_err_mu);
+    // The text is copied into a buffer of the calling thread: other threads may fail, and rewrite
+    // the context's message, while the caller still reads this one.
     static thread_local std::string copy;
-    copy = g_create_error;
+    if (ctx_ok(ctx)) {
+        std::lock_guard<std::mutex> g(ctx->err_mu);
+        copy = ctx->last_error;
+    } else {
+        std::lock_guard<std::mutex> g(g_err_mu);
+        copy = g_create_error;
+    }
     return copy.c_str();
 }
 
@@ -1182,12 +1251,22 @@ int32_t xn_ctx_create(const xn_ctx_desc* d, xn_ctx** out_ctx) {
     if (const char* env = getenv("XORNET_ATTN_OUTPROJ_TC")) c->out_tc = atoi(env) != 0;
     if (const char* env = getenv("XORNET_ATTN_OUTPROJ_PDL")) c->out_pdl = atoi(env) != 0;
     if (const char* env = getenv("XORNET_ATTN_OUTPROJ_ROWS")) c->out_rows_kernel = atoi(env) != 0;
+    if (const char* env = getenv("XORNET_ATTN_PREFILL_PDL")) c->pf_pdl = atoi(env) != 0;
 
 
     const size_t page_bytes =
         c->kv_u8 ? size_t(d->num_layers) * d->num_kv_heads * kv8::block_bytes(c->dq)
                  : size_t(d->num_layers) * d->num_kv_heads * kPageTokens * c->nv * 16 * 2;  // K and V
-    long long pages = d->pool_pages > 0 ? d->pool_pages : (d->pool_bytes > 0 ? d->pool_bytes / (long long)page_bytes : 0);
+    long long pool_bytes = d->pool_bytes;
+    if (d->pool_pages <= 0 && pool_bytes <= 0) {
+        // neither given: a bounded byte budget -- XORNET_ATTN_POOL_MB, else half of what the device has free
+        if (const char* env = getenv("XORNET_ATTN_POOL_MB")) pool_bytes = atoll(env) << 20;
+        if (pool_bytes <= 0) {
+            size_t free_b = 0, total_b = 0;
+            if (cudaMemGetInfo(&free_b, &total_b) == cudaSuccess) pool_bytes = (long long)(free_b / 2);
+        }
+    }
+    long long pages = d->pool_pages > 0 ? d->pool_pages : (pool_bytes > 0 ? pool_bytes / (long long)page_bytes : 0);
     if (pages <= 0 || pages > (1ll << 30)) {
         delete c;
         return fail(nullptr, XN_ERR_ARG, "pool_pages (or pool_bytes) must give at least one page");
@@ -1493,6 +1572,114 @@ int32_t xn_attention_batch(xn_ctx* c, int32_t n, const xn_req* reqs) {
             return fail(c, XN_ERR_ARG, "request %d repeats a stream of this batch", i);
     }
     return submit_locked(c, n, reqs, !dev);
+}
+
+// ---- device groups: one context per GPU, streams placed on the least-loaded one ----------------
+
+int32_t xn_place_stream(int32_t n_devices, const int64_t* tokens, const int64_t* live_streams,
+                        uint64_t ticket, int32_t policy) {
+    if (n_devices <= 0) return -XN_ERR_ARG;
+    const int start = int(ticket % uint64_t(n_devices));
+    if (policy == XN_PLACE_ROUND_ROBIN || !tokens) return start;
+    if (policy != XN_PLACE_LEAST_LOADED) return -XN_ERR_ARG;
+    int best = start;
+    for (int k = 1; k < n_devices; ++k) {   // ties go to the round-robin candidate, then onwards from it
+        const int i = (start + k) % n_devices;
+        const int64_t li = live_streams ? live_streams[i] : 0, lb = live_streams ? live_streams[best] : 0;
+        if (tokens[i] < tokens[best] || (tokens[i] == tokens[best] && li < lb)) best = i;
+    }
+    return best;
+}
+
+static bool group_ok(const xn_group* g) { return g && g->magic == 0x786e4752u; }
+
+int32_t xn_group_create(const xn_ctx_desc* desc, const int32_t* devices, int32_t n_devices, xn_group** out) {
+    if (!desc || !out || n_devices < 0 || (n_devices > 0 && !devices))
+        return fail(nullptr, XN_ERR_ARG, "null descriptor, output or device list");
+    *out = nullptr;
+    std::vector<int32_t> devs(devices, devices + n_devices);
+    if (devs.empty()) {
+        if (const char* env = getenv("XORNET_ATTN_DEVICES")) {   // "0,2,3"
+            for (const char* p = env; *p;) {
+                char* end = nullptr;
+                const long v = strtol(p, &end, 10);
+                if (end == p) break;
+                devs.push_back(int32_t(v));
+                p = *end ? end + 1 : end;
+            }
+        }
+        if (devs.empty()) {
+            int n = 0;
+            if (cudaGetDeviceCount(&n) != cudaSuccess || n <= 0)
+                return fail(nullptr, XN_ERR_NO_DEVICE, "no CUDA device; this library has no CPU fallback");
+            for (int i = 0; i < n; ++i) devs.push_back(i);
+        }
+    }
+    xn_group* g = new (std::nothrow) xn_group();
+    if (!g) return fail(nullptr, XN_ERR_NOMEM, "out of host memory");
+    for (int32_t dev : devs) {
+        xn_ctx_desc d = *desc;
+        d.device = dev;
+        d.cuda_stream = nullptr;   // a caller's stream belongs to one device: each context makes its own
+        xn_ctx* c = nullptr;
+        const int32_t rc = xn_ctx_create(&d, &c);
+        if (rc != XN_OK) {
+            for (xn_ctx* made : g->ctxs) xn_ctx_destroy(made);
+            g->magic = 0;
+            delete g;
+            return rc;   // the text of xn_ctx_create stays in xn_last_error(NULL)
+        }
+        g->ctxs.push_back(c);
+    }
+    *out = g;
+    return XN_OK;
+}
+
+int32_t xn_group_destroy(xn_group* g) {
+    if (!group_ok(g)) return XN_ERR_HANDLE;
+    for (xn_ctx* c : g->ctxs) xn_ctx_destroy(c);
+    g->magic = 0;
+    delete g;
+    return XN_OK;
+}
+
+int32_t xn_group_size(xn_group* g) { return group_ok(g) ? int32_t(g->ctxs.size()) : -XN_ERR_HANDLE; }
+
+xn_ctx* xn_group_ctx(xn_group* g, int32_t i) {
+    return group_ok(g) && i >= 0 && size_t(i) < g->ctxs.size() ? g->ctxs[size_t(i)] : nullptr;
+}
+
+int32_t xn_group_stream_create(xn_group* g, int64_t max_seq_len, int64_t expected_tokens, int32_t policy,
+                               xn_ctx** ctx_out, xn_stream** stream_out) {
+    if (!group_ok(g)) return XN_ERR_HANDLE;
+    if (!ctx_out || !stream_out || expected_tokens < 0) return fail(nullptr, XN_ERR_ARG, "bad argument");
+    *ctx_out = nullptr;
+    *stream_out = nullptr;
+    std::lock_guard<std::mutex> lk(g->mu);   // placements are decided one at a time
+    const int n = int(g->ctxs.size());
+    std::vector<int64_t> tokens(size_t(n), 0), live(size_t(n), 0);
+    for (int i = 0; i < n; ++i) {
+        xn_ctx* c = g->ctxs[size_t(i)];
+        std::lock_guard<std::mutex> cl(c->mu);
+        for (const xn_stream* s : c->streams) {   // what the stream holds, or what it was announced to hold
+            int64_t len = 0;
+            for (int64_t h : s->hw) len = std::max(len, std::min(h, s->cap));
+            tokens[size_t(i)] += std::max(len, s->expected);
+        }
+        live[size_t(i)] = int64_t(c->streams.size());
+    }
+    const int where = xn_place_stream(n, tokens.data(), live.data(), g->ticket, policy);
+    if (where < 0) return fail(nullptr, XN_ERR_ARG, "unknown placement policy %d", policy);
+    xn_ctx* c = g->ctxs[size_t(where)];
+    const int32_t rc = xn_stream_create(c, max_seq_len, stream_out);
+    if (rc != XN_OK) return rc;
+    {
+        std::lock_guard<std::mutex> cl(c->mu);
+        (*stream_out)->expected = std::min(expected_tokens, max_seq_len);
+    }
+    g->ticket += 1;
+    *ctx_out = c;
+    return XN_OK;
 }
 
 int32_t xn_rope_tables(float theta, int32_t head_dim, int32_t max_pos, float factor,

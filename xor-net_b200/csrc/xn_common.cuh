@@ -167,6 +167,43 @@ __device__ __forceinline__ bool mbar_spin_bounded(uint64_t* bar, uint32_t parity
     }
 }
 
+// The same poll with a short sleep between two tests, for waits that usually last long (a whole
+// work item): the thread stays off the shared-memory pipe most of the time and still notices the
+// completion within about `sleep_ns` (a parked try_wait was seen to wake tens of microseconds late).
+__device__ __forceinline__ bool mbar_poll_sleep_bounded(uint64_t* bar, uint32_t parity, unsigned sleep_ns,
+                                                        unsigned long long limit_ns = 2000000000ull) {
+    unsigned long long t0 = 0;
+    for (uint32_t spins = 1;; ++spins) {
+        if (mbar_test_wait(bar, parity)) return true;
+        __nanosleep(sleep_ns);
+        if ((spins & 0xffu) == 0) {
+            unsigned long long now = global_timer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > limit_ns) return false;
+        }
+    }
+}
+
+// One lane polls for the warp and the result is broadcast.  The __syncwarp() behind the broadcast
+// is needed: it reconverges the warp (without it, warp shuffles that followed such a wait were
+// seen to exchange wrong lanes' values) and orders the other lanes' later reads behind the
+// poller's acquire.
+__device__ __forceinline__ bool warp_spin_bounded(uint64_t* bar, uint32_t parity, int lane) {
+    int ok = 1;
+    if (lane == 0) ok = mbar_spin_bounded(bar, parity) ? 1 : 0;
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    __syncwarp();
+    return ok != 0;
+}
+__device__ __forceinline__ bool warp_poll_sleep_bounded(uint64_t* bar, uint32_t parity, int lane,
+                                                        unsigned sleep_ns) {
+    int ok = 1;
+    if (lane == 0) ok = mbar_poll_sleep_bounded(bar, parity, sleep_ns) ? 1 : 0;
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    __syncwarp();
+    return ok != 0;
+}
+
 // 1-D bulk copy global -> shared, completion counted in bytes on an mbarrier.  Both addresses
 // must be 16-byte aligned and bytes a multiple of 16.
 __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gmem_src, uint32_t bytes,

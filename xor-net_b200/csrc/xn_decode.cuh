@@ -401,21 +401,10 @@ attn_splitkv_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restrict__
     float4 qreg[GT][SQ];
     float4 acc[GT][SV];
     float m_run = -INFINITY, l_run = 0.f;
-#ifdef XN_DECODE_TIMING
-    long long tm_wait = 0, tm_qk = 0, tm_sm = 0, tm_pv = 0, tm_merge = 0, tm_start = clock64(), tm_t = 0;
-    int tm_tiles = 0, tm_items = 0;
-#define DT_BEGIN tm_t = clock64();
-#define DT_END(v) v += clock64() - tm_t;
-#else
-#define DT_BEGIN
-#define DT_END(v)
-#endif
 
     for (int fill = 0;; ++fill) {
         const int s = fill % ST;
-        DT_BEGIN
         const bool got = __all_sync(kFull, XN_DECODE_WAIT(&full_bar[s], (fill / ST) & 1));
-        DT_END(tm_wait)
         if (!got) {
             report_status(status, kDevWaitFull);
             *abort_flag = 1;
@@ -425,9 +414,6 @@ attn_splitkv_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restrict__
         // same tile, or the block-wide barriers of the merge below would lose a participant)
         const StageHdr h = hdr[s];
         if (h.flags & kHdrEnd) break;
-#ifdef XN_DECODE_TIMING
-        ++tm_tiles;
-#endif
         const float4* Ks = reinterpret_cast<const float4*>(stage_ptr(s));
         const float4* Vs = Ks + TPS * NV;
 
@@ -527,7 +513,6 @@ attn_splitkv_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restrict__
 
         {
             const int ntok = h.ntok;
-            DT_BEGIN
             // ---- scores for this warp's keys ----
             float sc[ITERS];
             float bm = -INFINITY;
@@ -557,8 +542,6 @@ attn_splitkv_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restrict__
             }
 #pragma unroll
             for (int o = LPK; o < 32; o <<= 1) bm = fmaxf(bm, __shfl_xor_sync(kFull, bm, o));
-            DT_END(tm_qk)
-            DT_BEGIN
 
             const float m_new = fmaxf(m_run, bm);
             const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
@@ -591,8 +574,6 @@ attn_splitkv_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restrict__
                     }
             }
 
-            DT_END(tm_sm)
-            DT_BEGIN
             // ---- weighted V rows of the same keys ----
             // No branch per key: a key beyond the tile's end has p = 0 and is pointed at the
             // tile's first row (always valid data of this unit), never at stale shared memory.
@@ -616,13 +597,8 @@ attn_splitkv_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restrict__
             }
         }
         __syncwarp();
-        DT_END(tm_pv)
         if (lane == 0) mbar_arrive(&empty_bar[s]);
         if (!(h.flags & kHdrLast)) continue;
-        DT_BEGIN
-#ifdef XN_DECODE_TIMING
-        ++tm_items;
-#endif
 
         // ---- last tile of the item: merge the W warp states ----
         float l_tot = l_run;
@@ -712,7 +688,7 @@ attn_splitkv_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restrict__
                 }
             }
         }
-        if (h.part < 0) { DT_END(tm_merge) continue; }
+        if (h.part < 0) continue;
 
         // ---- the unit was cut: whoever delivers its last partial combines them all ----
         // (block barrier, then one thread fences and counts: the fence is cumulative over the
@@ -761,14 +737,7 @@ attn_splitkv_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restrict__
         }
         // (no barrier here: `red` and `last_flag` are next written behind the next item's barriers,
         // which no thread passes before every thread has left this point)
-        DT_END(tm_merge)
     }
-#ifdef XN_DECODE_TIMING
-    if ((blockIdx.x == 0 || blockIdx.x == 77) && tid == 32 && tm_tiles > 8)
-        printf("block %d: %d tiles %d items, total %lld clk (%lld/tile): wait %lld qk %lld softmax %lld pv %lld per tile; merge %lld per item\n",
-               blockIdx.x, tm_tiles, tm_items, clock64() - tm_start, (clock64() - tm_start) / tm_tiles, tm_wait / tm_tiles,
-               tm_qk / tm_tiles, tm_sm / tm_tiles, tm_pv / tm_tiles, tm_items ? tm_merge / tm_items : 0);
-#endif
 }
 
 // Generic attention for requests whose positions fold around the ring (index_pos + seq_len >

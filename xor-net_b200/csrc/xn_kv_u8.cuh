@@ -439,20 +439,10 @@ attn_splitkv_u8_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restric
     const size_t page_stride = size_t(num_kv_heads) * blk_bytes;
     const size_t pstride = part_stride(DQ);
 
-#ifdef XN_KV8_TIMING
-    long long tm_start = clock64(), tm_pro = 0, tm_loop = 0, tm_merge = 0, tm_t = 0;
-    int tm_items = 0, tm_iters = 0, tm_merges = 0;
-#define KT_MARK tm_t = clock64();
-#define KT_ADD(v) { long long now__ = clock64(); v += now__ - tm_t; tm_t = now__; }
-#else
-#define KT_MARK
-#define KT_ADD(v)
-#endif
     int chunk = blockIdx.x;
     while (chunk < n_chunks) {
         const int it_lo = chunk_item_begin[chunk], it_hi = chunk_item_begin[chunk + 1];
         for (int it = it_lo; it < it_hi; ++it) {
-            KT_MARK
             const ItemDev item = items[it];
             const UnitDev u = units[item.unit];
             const ReqDev& r = reqs[u.req];
@@ -548,13 +538,6 @@ attn_splitkv_u8_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restric
             const int key_first = tok_begin + w * KPI;
 #pragma unroll
             for (int p = 0; p < PF; ++p) issue(p, key_first + p * STEP);
-#ifdef XN_KV8_TIMING
-            cp_async_wait<PF - 1>();
-            if (q2[0][0].x == 123456.789f) tm_items += 100;   // the query rows have arrived
-            ++tm_items;
-            tm_iters += (loop_end - key_first + STEP - 1) / STEP;
-#endif
-            KT_ADD(tm_pro)
             // One trip: U keys per lane (their instruction chains are independent up to the softmax
             // bookkeeping, which they share).
             auto trip = [&](const Fetch<WE> (&cur)[U], const bool (&valid)[U]) {
@@ -760,7 +743,6 @@ attn_splitkv_u8_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restric
                 }
             }
             cp_async_wait<0>();   // nothing of this item is still on its way into the ring
-            KT_ADD(tm_loop)
 
             // ---- the block's group states meet ----
 #pragma unroll
@@ -896,22 +878,12 @@ attn_splitkv_u8_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restric
                 }
             }
             __syncthreads();  // red, sm_m, sm_l and sm_last are rewritten by the next item
-#ifdef XN_KV8_TIMING
-            if (item.part >= 0 && sm_last) ++tm_merges;
-#endif
-            KT_ADD(tm_merge)
         }
         if (tid == 0) sm_next = atomicAdd(&sync[kSyncChunk], 1) + int(gridDim.x);
         __syncthreads();
         chunk = sm_next;
         __syncthreads();
     }
-#ifdef XN_KV8_TIMING
-    if (tid == 0 && (blockIdx.x % 97) == 0)
-        printf("block %4d: total %lld clk, %d items %d iters %d final merges: prologue %lld loop %lld (%lld/iter) merge %lld\n",
-               blockIdx.x, clock64() - tm_start, tm_items, tm_iters, tm_merges, tm_pro, tm_loop,
-               tm_iters ? tm_loop / tm_iters : 0, tm_merge);
-#endif
     if (tid == 0) {
         // the last block to finish re-arms the chunk counter for the next launch
         __threadfence();

@@ -97,20 +97,10 @@ attn_splitkv_u8_mma_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __res
     auto stage_v = [&](int s) { return stage_k(s) + kTileKeys * DQ; };
     auto stage_sc = [&](int s) { return reinterpret_cast<float*>(stage_v(s) + kTileKeys * DQ); };
 
-#ifdef XN_KV8M_TIMING
-    long long tm_start = clock64(), tm_pro = 0, tm_wait = 0, tm_qk = 0, tm_pv = 0, tm_issue = 0, tm_merge = 0, tm_t = 0;
-    int tm_tiles = 0, tm_items = 0;
-#define MT_MARK tm_t = clock64();
-#define MT_ADD(v) { long long now__ = clock64(); v += now__ - tm_t; tm_t = now__; }
-#else
-#define MT_MARK
-#define MT_ADD(v)
-#endif
     int chunk = blockIdx.x;
     while (ok && chunk < n_chunks) {
         const int it_lo = chunk_item_begin[chunk], it_hi = chunk_item_begin[chunk + 1];
         for (int it = it_lo; ok && it < it_hi; ++it) {
-            MT_MARK
             const ItemDev item = items[it];
             const UnitDev u = units[item.unit];
             const ReqDev& r = reqs[u.req];
@@ -208,10 +198,6 @@ attn_splitkv_u8_mma_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __res
 
 #pragma unroll
             for (int p = 0; p < PF; ++p) issue(tok_begin + p * kTileKeys);
-#ifdef XN_KV8M_TIMING
-            ++tm_items;
-#endif
-            MT_ADD(tm_pro)
             for (int kt = tok_begin; ok && kt < tok_end; kt += kTileKeys) {
                 {
                     const int p = use % PF;
@@ -224,10 +210,6 @@ attn_splitkv_u8_mma_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __res
                         break;
                     }
                     ++use;
-#ifdef XN_KV8M_TIMING
-                    ++tm_tiles;
-#endif
-                    MT_ADD(tm_wait)
                     // ---- q.k on the tensor cores ----
                     uint32_t kw[2][KW];
 #pragma unroll
@@ -315,7 +297,6 @@ attn_splitkv_u8_mma_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __res
                         }
                     }
                     __syncwarp();
-                    MT_ADD(tm_qk)
                     // ---- weighted V rows on the CUDA cores ----
 #pragma unroll
                     for (int i = 0; i < SUBS; ++i) {
@@ -334,9 +315,7 @@ attn_splitkv_u8_mma_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __res
                         }
                     }
                     __syncwarp();   // sm_p is rewritten by the next tile
-                    MT_ADD(tm_pv)
                     issue(kt + PF * kTileKeys);
-                    MT_ADD(tm_issue)
                 }
             }
             if (!ok) break;
@@ -462,19 +441,12 @@ attn_splitkv_u8_mma_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __res
                 }
             }
             __syncwarp();   // red / the ring, sm_p and sm_last are rewritten by the next item
-            MT_ADD(tm_merge)
         }
         if (lane == 0) sm_next = atomicAdd(&sync[kSyncChunk], 1) + int(gridDim.x);
         __syncwarp();
         chunk = sm_next;
         __syncwarp();
     }
-#ifdef XN_KV8M_TIMING
-    if (lane == 0 && (blockIdx.x % 177) == 0)
-        printf("block %4d: total %lld clk, %d items %d tiles: prologue %lld, per tile wait %lld qk %lld pv %lld issue %lld, merge %lld\n",
-               blockIdx.x, clock64() - tm_start, tm_items, tm_tiles, tm_pro, tm_wait / max(tm_tiles, 1),
-               tm_qk / max(tm_tiles, 1), tm_pv / max(tm_tiles, 1), tm_issue / max(tm_tiles, 1), tm_merge);
-#endif
     if (lane == 0) {
         __threadfence();
         if (atomicAdd(&sync[kSyncDone], 1) == int(gridDim.x) - 1) {

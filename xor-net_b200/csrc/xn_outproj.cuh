@@ -61,16 +61,8 @@ subnorm_quant_kernel(const OutRowDev* __restrict__ rows, const float* __restrict
     __shared__ float bc_s;
     // the projection kernel behind this one may start now: its prologue (fetching and decoding its
     // weights) does not depend on anything written here, and it waits before it reads the rows
-#ifdef XN_SQ_TIMING
-    __shared__ long long sq_marks[8];
-    const long long sq_t0 = clock64();
-#define SQM(i) do { if (threadIdx.x == 0) sq_marks[i] = clock64() - sq_t0; } while (0)
-#else
-#define SQM(i)
-#endif
     pdl_launch_dependents();
     pdl_wait();   // this kernel itself may have been set up while the attention kernel still ran
-    SQM(0);
     const int r = blockIdx.x;
     const float* src = rows[r].src;
     const int tid = threadIdx.x;
@@ -97,7 +89,6 @@ subnorm_quant_kernel(const OutRowDev* __restrict__ rows, const float* __restrict
         }
     }
     __syncthreads();
-    SQM(1);
     if (norm_w != nullptr) {
         if (tid < 32) {
             // the whole first warp runs the chain (same value in every lane: no divergence);
@@ -126,7 +117,6 @@ subnorm_quant_kernel(const OutRowDev* __restrict__ rows, const float* __restrict
             if (tid == 0) bc_s = __fdiv_rn(1.0f, rms);
         }
         __syncthreads();
-        SQM(2);
     }
     // normalise (two rounded multiplies) and take max |x| in one pass; consecutive threads take
     // consecutive groups of four elements, which keeps shared memory and the global stores dense
@@ -153,13 +143,11 @@ subnorm_quant_kernel(const OutRowDev* __restrict__ rows, const float* __restrict
         }
         m = fmaxf(m, fabsf(v));
     }
-    SQM(3);
     for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
     if ((tid & 31) == 0) red_s[tid >> 5] = m;
     __syncthreads();
     m = red_s[0];
     for (int w = 1; w < int(blockDim.x >> 5); ++w) m = fmaxf(m, red_s[w]);
-    SQM(4);
     const float scale = m > 0.f ? __fdiv_rn(127.0f, m) : 1.0f;
     if (tid == 0) inv_scale_out[q_row0 + r] = m > 0.f ? __fdiv_rn(m, 127.0f) : 1.0f;
     // whole 16-element chunks round to nearest even after clamping, the tail half away from zero
@@ -180,12 +168,6 @@ subnorm_quant_kernel(const OutRowDev* __restrict__ rows, const float* __restrict
         }
         *reinterpret_cast<uint32_t*>(q_out + act_offset(q_row0 + r, i0, q_rows_pad)) = packed;
     }
-#ifdef XN_SQ_TIMING
-    __syncthreads();
-    if (threadIdx.x == 0 && blockIdx.x == 0)
-        printf("sq: after wait %lld, row staged %lld, chain done %lld, normalised %lld, max known %lld, end %lld\n",
-               sq_marks[0], sq_marks[1], sq_marks[2], sq_marks[3], sq_marks[4], clock64() - sq_t0);
-#endif
 }
 
 // ---- ternary projection: i8 activations x 2-bit weights -> f32 rows ---------------------------

@@ -117,20 +117,6 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 }
 }  // namespace tg
 
-// The thread of the MMA warp that issues tcgen05.mma and tcgen05.commit (a commit tracks the MMAs
-// of the thread that executes it, so every site must pick the same thread; the election is
-// deterministic for a given member mask).
-#ifndef XN_TG_ISSUER
-#define XN_TG_ISSUER tg::elect_one()
-#endif
-#ifdef XN_TG_TIMING
-// tuning build: cycle stamps of block 0, stored as they happen, printed by the block at its end
-__device__ long long g_tg_dbg[256];
-#define TGD(idx) do { if (blockIdx.x == 0 && blockIdx.y == 0) g_tg_dbg[idx] = clock64() - tg_t0; } while (0)
-#else
-#define TGD(idx)
-#endif
-
 struct TernaryGemmArgs {
     const int8_t* q;         // activations, tiled: act_offset()
     const uint8_t* w2;       // weight codes, tiled: code_offset()
@@ -166,9 +152,6 @@ ternary_gemm_tc_kernel(const TernaryGemmArgs a) {
     static_assert((kActStages + kMaxPieces + 1) * 8 + 16 <= 512, "barrier area");
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-#ifdef XN_TG_TIMING
-    const long long tg_t0 = clock64();
-#endif
     const int o0 = blockIdx.x * kTN;
     const int t0 = blockIdx.y * kTM;
 
@@ -208,7 +191,6 @@ ternary_gemm_tc_kernel(const TernaryGemmArgs a) {
     __syncthreads();
     pf::fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
-    if (tid == 0) TGD(0);
 
     if (warp == 0) {
         // ======================= copy producer: activation stages =======================
@@ -241,6 +223,10 @@ ternary_gemm_tc_kernel(const TernaryGemmArgs a) {
         }
     } else if (warp == 1) {
         // =============================== MMA issuer ===============================
+        // Its first wait needs the activation copies, which cannot start before the preceding
+        // kernels have finished: wait for them here, so that the 2 s limit of the bounded waits
+        // below is measured from that moment and never counts a long predecessor's run time.
+        pdl_wait();
         const uint32_t idesc = make_idesc_i8(kTM, kTN);
         // descriptor address fields advance by bytes >> 4
         const uint64_t adesc0 = pf::smem_desc(smem_u32(act_s), 0, 1024, pf::kLayoutSw128);
@@ -248,11 +234,9 @@ ternary_gemm_tc_kernel(const TernaryGemmArgs a) {
         bool ok = true;
         int st = 0;
         for (int p = 0; p < n_pieces; ++p) {
-            if (lane == 0) TGD(96 + p);
             ok = warp_wait(&piece_full[p], 0, lane);
             if (!ok || *abort_flag) { ok = false; break; }
-            if (XN_TG_ISSUER) {
-                TGD(48 + p);
+            if (tg::elect_one()) {
                 pf::fence_after_sync();
                 const int kbs = min(kPieceKb, nkb - p * kPieceKb);
                 const uint64_t adesc = adesc0 + uint64_t(st * (kActStage >> 4));
@@ -275,12 +259,11 @@ ternary_gemm_tc_kernel(const TernaryGemmArgs a) {
                 }
                 bdesc += uint64_t(kPieceKb * (kWBlock >> 4));
                 pf::mma_commit(&act_empty[st]);
-                TGD(64 + p);
             }
             st ^= 1;
             __syncwarp();
         }
-        if (XN_TG_ISSUER) {
+        if (tg::elect_one()) {
             if (ok) {
                 pf::mma_commit(acc_full);
             } else {
@@ -311,7 +294,6 @@ ternary_gemm_tc_kernel(const TernaryGemmArgs a) {
                 fence_generic_to_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&piece_full[p]);
-                if (lane == 0 && warp == 2) TGD(32 + p);
             }
         }
 
@@ -329,7 +311,6 @@ ternary_gemm_tc_kernel(const TernaryGemmArgs a) {
         const float is_mine = t_mine < a.n_rows ? a.inv_scale[a.q_row0 + t_mine] : 0.f;
         const bool acc_ok = warp_wait(acc_full, 0, lane) && !*abort_flag;
         pf::fence_after_sync();
-        if (lane == 0 && warp == 2) TGD(1);
         float* out_s = reinterpret_cast<float*>(act_s);   // every stage has been consumed by now
         if (acc_ok) {
             const int quarter = warp & 3;
@@ -356,18 +337,8 @@ ternary_gemm_tc_kernel(const TernaryGemmArgs a) {
         }
     }
 
-    if (lane == 0 && warp == 2) TGD(2);
     pf::fence_before_sync();
     __syncthreads();
-#ifdef XN_TG_TIMING
-    if (tid == 0 && blockIdx.x == 0 && blockIdx.y == 0) {
-        __threadfence();
-        printf("tg setup %lld, acc ready %lld, epilogue done %lld\n", g_tg_dbg[0], g_tg_dbg[1], g_tg_dbg[2]);
-        for (int p = 0; p < n_pieces; ++p)
-            printf("tg piece %d: decoded %6lld  mma: waiting %6lld  operands seen %6lld  committed %6lld\n", p,
-                   g_tg_dbg[32 + p], g_tg_dbg[96 + p], g_tg_dbg[48 + p], g_tg_dbg[64 + p]);
-    }
-#endif
     if (warp == 1) {
         pf::fence_after_sync();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
@@ -507,6 +478,7 @@ ternary_gemm_rows_kernel(const TernaryGemmArgs a) {
         }
     } else if (warp == 1) {
         // =============================== MMA issuer ===============================
+        pdl_wait();   // as in ternary_gemm_tc_kernel: the bounded waits start counting here
         const uint32_t idesc = tg::make_idesc_i8(kTM, kTN);
         const uint64_t adesc0 = pf::smem_desc(smem_u32(act_s), 0, 1024, pf::kLayoutSw128);
         const uint64_t bdesc0 = pf::smem_desc(smem_u32(w_s), 0, 1024, pf::kLayoutSw128);
@@ -523,7 +495,7 @@ ternary_gemm_rows_kernel(const TernaryGemmArgs a) {
                 if (tile_idx == 0) ok = warp_wait(&w_full[p], 0, lane);
                 ok = ok && warp_wait(&act_full[st], par, lane);
                 if (!ok || *abort_flag) { ok = false; break; }
-                if (XN_TG_ISSUER) {
+                if (tg::elect_one()) {
                     pf::fence_after_sync();
                     const int kbs = min(kPieceKb, nkb - p * kPieceKb);
                     const uint64_t adesc = adesc0 + uint64_t(st * (kActStage >> 4));
@@ -541,7 +513,7 @@ ternary_gemm_rows_kernel(const TernaryGemmArgs a) {
                 st ^= 1;
                 __syncwarp();
             }
-            if (ok && XN_TG_ISSUER) pf::mma_commit(&acc_full[b]);
+            if (ok && tg::elect_one()) pf::mma_commit(&acc_full[b]);
             __syncwarp();
         }
         if (!ok && lane == 0) {

@@ -23,6 +23,8 @@
 //               shared memory, exp2 with the softmax scale folded into one FMA, P written back
 //               with tcgen05.st.  The accumulator is rescaled lazily: only when a row's maximum
 //               grows by more than 2^8.  Epilogue: O / l to global.
+// The kernel may be launched as a programmatic dependent of the append kernel: its blocks set up
+// (barriers, tensor memory) while that kernel drains and wait for it before their first read.
 // Every wait is bounded; on expiry the kernel records a status code, drains and returns.
 #pragma once
 #include <cuda.h>
@@ -45,9 +47,6 @@ struct PrefillArgs {
     int head_dim;         // D (multiple of 4, 16..128)
     float scale_log2;     // (1/sqrt(D)) * log2(e)
     int* status;
-#ifdef XN_PF_TIMING
-    long long* timing;    // instrumentation build only: cycle counters of one softmax thread
-#endif
 };
 
 namespace pf {
@@ -255,6 +254,7 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap k_map,
         // Order of issue = order of consumption by the MMA warp: K tile j+1 is wanted before the
         // V pages of tile j.
         if (lane == 0) {
+            pdl_wait();   // the pages (and the page table) are written before this kernel: wait for the append
             auto page_row = [&](int pg) -> int {
                 return int(((a.layer_page_base + a.pages[pg]) * a.num_kv_heads + h_kv) * kPage);
             };
@@ -377,6 +377,7 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap k_map,
         auto wg_barrier = [&]() { named_bar_sync(1, 256); };
 
         // ---- prologue: Q -> tensor memory (rounded to TF32); each warpgroup half of the columns
+        pdl_wait();   // the query rows may come out of the append kernel's rotation scratch
         {
             const float* qrow = a.q + size_t(h) * a.q_hs + size_t(t) * a.q_ts;
             const bool valid = t < a.seq_len;
