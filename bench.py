@@ -80,6 +80,31 @@ def stream_lengths(n, lo, hi, seed):
     return rng.integers(lo, hi + 1, n).astype(np.int64)
 
 
+def place_streams(xn, lens_global, world, policy):
+    """Owner GPU of every stream of one global list, decided in creation order like the library's
+    device group does (xn_place_stream): "least" = the GPU with the fewest announced tokens (ties:
+    fewest streams, then round-robin), "rr" = stream number mod number of GPUs."""
+    tokens, live, owner = [0] * world, [0] * world, []
+    for i, L in enumerate(lens_global):
+        w = i % world if policy == "rr" else xn.place_stream(tokens, live, i, xn.PLACE_LEAST_LOADED)
+        owner.append(w)
+        tokens[w] += int(L)
+        live[w] += 1
+    return owner
+
+
+def load_traffic(name):
+    """DRAM bytes per launch of a kernel from the tracked summary of its ncu capture
+    (profiles/<name>.json: dram__bytes_read.sum + dram__bytes_write.sum, the commit it was taken at)."""
+    path = os.path.join(ROOT, "profiles", name + ".json")
+    if not os.path.exists(path):
+        return None, None
+    with open(path) as f:
+        d = json.load(f)
+    return float(d["dram_bytes_read"]) + float(d["dram_bytes_written"]), \
+        f"ncu capture at commit {d.get('commit', '?')}: {d.get('workload', '')}"
+
+
 def load_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -279,7 +304,7 @@ L2_BYTES = 126 << 20
 
 
 def measure_prefill(xn, torch, tstream, device, S, Hq, Hkv, D, theta, steps, warmup, e2e=True, u8=False,
-                    min_seconds=0.25, index_pos=0, chunk=0):
+                    min_seconds=0.25, index_pos=0, chunk=0, n_seqs=1, prefill_mode=0):
     """One causal prefill of S tokens (fused RoPE + append + attention) per step, one layer.
 
     ``ms`` is the device time of one call (append + attention) behind an L2 flush, median over the
@@ -291,15 +316,16 @@ def measure_prefill(xn, torch, tstream, device, S, Hq, Hkv, D, theta, steps, war
 
     With ``chunk`` > 0 the S tokens arrive as chunks of that many rows at growing positions (the
     chunked prefill of examples/chat.rs:297-306); ``index_pos`` > 0 puts a filled prefix before them.
+    ``n_seqs`` > 1 submits that many independent sequences of S tokens in one call.
     """
     P = int(index_pos)
     cos, sin = xn.rope_tables(theta, D, P + S)
-    set_bytes = ((Hq + 2 * Hkv) + Hq + 2 * Hkv) * S * D * 4
+    set_bytes = ((Hq + 2 * Hkv) + Hq + 2 * Hkv) * S * D * 4 * n_seqs
     n_sets = int(min(8, max(2, -(-2 * L2_BYTES // set_bytes) + 1)))
     ctx = xn.Context(num_layers=1, num_heads=Hq, num_kv_heads=Hkv, head_dim=D,
-                     pool_pages=(n_sets + 1) * ((P + S + 63) // 64 + 2), device=device,
+                     pool_pages=(n_sets + 1) * n_seqs * ((P + S + 63) // 64 + 2), device=device,
                      shuffle_seed=BASE_SEED + 2000, rope=(cos, sin), cuda_stream=tstream.cuda_stream,
-                     kv_format=xn.KV_U8 if u8 else xn.KV_F32)
+                     kv_format=xn.KV_U8 if u8 else xn.KV_F32, prefill_mode=prefill_mode)
     gen = torch.Generator(device="cpu").manual_seed(BASE_SEED + 2000)
     q_h = torch.randn(Hq, S, D, generator=gen).pin_memory()
     k_h = torch.randn(Hkv, S, D, generator=gen).pin_memory()
@@ -314,6 +340,15 @@ def measure_prefill(xn, torch, tstream, device, S, Hq, Hkv, D, theta, steps, war
         q_d, k_d, v_d = q_h.cuda(), k_h.cuda(), v_h.cuda()
         o_d = torch.empty(Hq, S, D, device="cuda")
         keep.append((q_d, k_d, v_d, o_d))
+        if n_seqs > 1:   # further sequences of the same call: own streams, own tensors
+            entries = [(st, 0, P, S, q_d.data_ptr(), k_d.data_ptr(), v_d.data_ptr(), o_d.data_ptr())]
+            for _ in range(n_seqs - 1):
+                st2 = ctx.new_stream(P + S)
+                t4 = (q_h.cuda(), k_h.cuda(), v_h.cuda(), torch.empty(Hq, S, D, device="cuda"))
+                keep.append(t4)
+                entries.append((st2, 0, P, S, t4[0].data_ptr(), t4[1].data_ptr(), t4[2].data_ptr(), t4[3].data_ptr()))
+            sets.append([ctx.make_batch(entries, xn.REQ_DEVICE_PTRS | xn.REQ_ROPE)])
+            continue
         if chunk:   # chunks are row ranges of the sequence-major tensors
             qs, ks, vs = (x.transpose(0, 1).contiguous() for x in (q_d, k_d, v_d))
             os_ = torch.empty(S, Hq, D, device="cuda")
@@ -371,8 +406,9 @@ def measure_prefill(xn, torch, tstream, device, S, Hq, Hkv, D, theta, steps, war
         runs.append(e0.elapsed_time(e1) / run)
         total += runs[-1] * run
     pipe_ms = float(np.median(runs))
-    flops = prefill_flops(Hq, D, S, P)
-    res = {"seq_len": S, "index_pos": P, "chunk": chunk or S, "flops": flops, "ms": ms,
+    flops = prefill_flops(Hq, D, S, P) * n_seqs
+    kern_per_call *= n_seqs
+    res = {"seq_len": S, "index_pos": P, "chunk": chunk or S, "sequences": n_seqs, "flops": flops, "ms": ms,
            "tflops": flops / (ms * 1e-3) / 1e12,
            "timing": f"median of {len(iso)} calls, each behind a 256 MB write that flushes L2",
            "pipelined_ms": pipe_ms, "pipelined_tflops": flops / (pipe_ms * 1e-3) / 1e12,
@@ -381,7 +417,7 @@ def measure_prefill(xn, torch, tstream, device, S, Hq, Hkv, D, theta, steps, war
            "kernel_ms": kern_per_call,
            "kernel_tflops": flops / (kern_per_call * 1e-3) / 1e12 if kern_n else None,
            "launches_per_step": (3 if u8 else 2) * len(pieces)}
-    if e2e and not chunk:
+    if e2e and not chunk and n_seqs == 1:
         host = ctx.make_batch([(host_st, 0, P, S, q_h.data_ptr(), k_h.data_ptr(), v_h.data_ptr(), o_h.data_ptr())],
                               xn.REQ_ROPE | xn.REQ_HOST_PINNED)  # page-locked host buffers
         if P:
@@ -601,6 +637,92 @@ def run_split_prefill_arm(args):
 
 
 # =================================================================================================
+# Short summaries of the other workload shapes (extras of the default line)
+# =================================================================================================
+
+def measure_decode(xn, torch, tstream, device, lens, Hq, Hkv, D, layers, steps, grow=False, theta=None,
+                   min_seconds=0.15):
+    """Batched decode over device-resident inputs: one submission per layer and step.  With ``grow``
+    every step appends at the next position (one layer), else the positions stay put.  Returns the
+    per-step device time, the split-KV kernel's own time per launch and algorithmic GB/s."""
+    n = len(lens)
+    rope = xn.rope_tables(theta, D, int(max(lens)) + steps + 2) if theta else None
+    pages = int(sum((int(L) + steps + 64) // 64 + 1 for L in lens))
+    ctx = xn.Context(num_layers=layers, num_heads=Hq, num_kv_heads=Hkv, head_dim=D, pool_pages=pages + 8,
+                     device=device, shuffle_seed=BASE_SEED + 77, cuda_stream=tstream.cuda_stream, rope=rope)
+    sts = [ctx.new_stream(int(max(lens)) + steps + 2) for _ in range(n)]
+    for i, st in enumerate(sts):
+        if lens[i] > 1:
+            st.fill_normal(-1, 0, int(lens[i]) - 1, BASE_SEED + 7000 + i)
+    gen = torch.Generator(device="cpu").manual_seed(BASE_SEED + 7000)
+    q = torch.randn(layers, n, Hq, D, generator=gen).cuda()
+    k = torch.randn(layers, n, Hkv, D, generator=gen).cuda()
+    v = torch.randn(layers, n, Hkv, D, generator=gen).cuda()
+    o = torch.zeros(layers, n, Hq, D, device="cuda")
+    flags = xn.REQ_DEVICE_PTRS | (xn.REQ_ROPE if theta else 0)
+
+    def batch(l, s):
+        return ctx.make_batch([(sts[i], l, int(lens[i]) - 1 + s, 1, q[l, i].data_ptr(), k[l, i].data_ptr(),
+                                v[l, i].data_ptr(), o[l, i].data_ptr()) for i in range(n)], flags)
+
+    if grow:
+        plan = [[batch(0, s)] for s in range(steps)]           # every step at the next position
+        per_step_bytes = [algorithmic_bytes_per_layer([int(L) + s for L in lens], Hq, Hkv, D) for s in range(steps)]
+    else:
+        plan = [[batch(l, 0) for l in range(layers)]] * steps
+        per_step_bytes = [algorithmic_bytes_per_layer(lens, Hq, Hkv, D) * layers] * steps
+    for b in plan[0] * 3:
+        ctx.submit(b)
+    torch.cuda.synchronize()
+    brackets = []
+    while len(brackets) < 1 or (sum(brackets) < min_seconds * 1e3 and len(brackets) < 100 and not grow):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(tstream)
+        for step in plan:
+            for b in step:
+                ctx.submit(b)
+        e1.record(tstream)
+        torch.cuda.synchronize()
+        brackets.append(e0.elapsed_time(e1))
+    ms = float(np.median(brackets))
+    ctx.profile_enable(True)
+    ctx.profile_read()
+    for b in plan[-1]:
+        ctx.submit(b)
+    kern_ms, kern_n = ctx.profile_read("splitkv")
+    ctx.profile_enable(False)
+    ctx.close()
+    peak, peak_kind = load_peaks()
+    kern = kern_ms / max(kern_n, 1)
+    launch_bytes = per_step_bytes[-1] / (1 if grow else layers)
+    return {"streams": n, "layers": layers, "steps": steps, "kv_tokens": int(sum(int(L) for L in lens)),
+            "ms_per_step": ms / steps, "gbs": sum(per_step_bytes) / (ms * 1e-3) / 1e9,
+            "tokens_per_s": n * steps / (ms * 1e-3),
+            "kernel_us": kern * 1e3, "kernel_gbs": launch_bytes / (kern * 1e-3) / 1e9 if kern else None,
+            "roofline": {"bound": "hbm", "achieved": launch_bytes / (kern * 1e-3) / 1e9 if kern else None, "peak": peak,
+                         "unit": "GB/s", "frac": launch_bytes / (kern * 1e-3) / 1e9 / peak if kern else None,
+                         "peak_source": peak_kind, "algorithmic_bytes_per_launch": launch_bytes}}
+
+
+def run_dropin_leg(xn, n_streams, layers, Hq, Hkv, D, lo, hi, steps, warmup, device, pool_mb):
+    """The call xor-net's front-ends make: one OS thread per stream blocking in fast_attention with
+    pageable buffers, one call per layer (server/main.rs:126, examples/batch_bench.rs:194-199),
+    driven by the compiled C++ harness over the C++ host mirror.  Returns its JSON."""
+    exe = xn.build_host_tool("dropin_bench")
+    env = dict(os.environ)
+    env.setdefault("XORNET_ATTN_DEVICES", str(device))
+    env.setdefault("XORNET_ATTN_POOL_MB", str(pool_mb))
+    res = subprocess.run([exe, str(n_streams), str(layers), str(Hq), str(Hkv), str(D), str(lo), str(hi), str(steps),
+                          str(warmup), str(BASE_SEED)], env=env, capture_output=True, text=True, timeout=600)
+    if res.returncode != 0:
+        return {"error": (res.stderr or res.stdout)[-400:]}
+    out = json.loads(res.stdout.strip().splitlines()[-1])
+    out["api"] = ("fast_attention of the C++ host mirror -> xn_attention: one OS thread per stream, pageable "
+                  "std::vector<float> tensors, one blocking call per layer; the library merges concurrent callers")
+    return out
+
+
+# =================================================================================================
 # GPU arm
 # =================================================================================================
 
@@ -627,8 +749,16 @@ def run_gpu_arm(args):
     if args.streams:
         n_streams = args.streams
         desc += f" [reduced to {n_streams} streams]"
-    # every rank owns its own streams (weak scaling: per-GPU work is fixed); no data-path collective
-    lens = stream_lengths(n_streams, lo, hi, BASE_SEED + 3000 + 7919 * rank)
+    # ONE global list of world x n_streams lengths (weak scaling: the work per GPU is fixed on
+    # average); every stream lives on one GPU for good, no data-path collective
+    lens_global = stream_lengths(world * n_streams, lo, hi, BASE_SEED + 3000)
+    owner = place_streams(xn, lens_global, world, args.placement)
+    mine = [i for i in range(len(lens_global)) if owner[i] == rank]
+    lens = lens_global[mine]
+    n_total_streams = len(lens_global)
+    n_streams = len(mine)
+    tokens_by_rank = [int(sum(int(lens_global[i]) for i in range(n_total_streams) if owner[i] == r))
+                      for r in range(world)]
     pages_needed = int(sum((int(L) + 63) // 64 for L in lens))
     # a real (non-default) stream shared by torch and the library, so that CUDA events recorded
     # here bracket the library's launches
@@ -646,7 +776,7 @@ def run_gpu_arm(args):
     streams = [ctx.new_stream(int(hi)) for _ in range(n_streams)]
     for i, st in enumerate(streams):
         if lens[i] > 1:
-            st.fill_normal(-1, 0, int(lens[i]) - 1, BASE_SEED + 3000 + 1000003 * rank + i)
+            st.fill_normal(-1, 0, int(lens[i]) - 1, BASE_SEED + 3000 + 1000003 + mine[i])
     ctx.synchronize()
 
     # per-layer inputs, resident on the device and mirrored in pinned host memory
@@ -728,24 +858,36 @@ def run_gpu_arm(args):
     for _ in range(max(args.warmup, 3)):
         step_device()
     barrier()
-    s0 = ctx.stats()
+    # K steps between two events, a barrier and a synchronize on both sides; the bracket is repeated
+    # until the timed regions add up to --min-seconds, and the median bracket is reported
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    wall0 = time.time()
+    brackets, launches_per_bracket = [], 0
+    while len(brackets) < 1 or (sum(brackets) < args.min_seconds * 1e3 and len(brackets) < 200):
+        s0 = ctx.stats()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        ev0.record(tstream)
+        for _ in range(args.steps):
+            step_device()
+        ev1.record(tstream)
+        barrier()
+        t_bracket = ev0.elapsed_time(ev1)
+        if world > 1:   # every rank must take the same number of brackets: agree on the slowest time
+            (t_bracket,), _ = xn.sharding.aggregate([t_bracket], [0.0], device="cuda")
+        brackets.append(t_bracket)
+        launches_per_bracket = ctx.stats()["kernel_launches"] - s0["kernel_launches"]
+    wall1 = time.time()
+    ms = float(np.median(brackets))
+    clocks = sampler.stop(wall0, wall1) if sampler else None
+    # the attention kernel alone: CUDA events around each of its launches, in a pass of its own
+    # (the events would sit between kernels that otherwise overlap head to tail)
     ctx.profile_enable(True)
     ctx.profile_read()
-    sampler = ClockSampler(local_rank) if rank == 0 else None
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    wall0 = time.time()
-    ev0.record(tstream)
-    for _ in range(args.steps):
+    for _ in range(max(1, min(args.steps, 5))):
         step_device()
-    ev1.record(tstream)
-    barrier()
-    wall1 = time.time()
-    ms = ev0.elapsed_time(ev1)
     (kern_ms, kern_n), _, (ob_ms, ob_n), (qb_ms, qb_n) = ctx.profile_read_all()
     ctx.profile_enable(False)
-    s1 = ctx.stats()
-    clocks = sampler.stop(wall0, wall1) if sampler else None
     ctx.synchronize()
 
     # ---- end to end through the blocking C-ABI call with host buffers ----------------------------
@@ -775,9 +917,19 @@ def run_gpu_arm(args):
         barrier()
         staged_ms = (time.perf_counter() - t0) * 1e3
 
-    # job-wide figures: slowest rank's time, all ranks' bytes (no-op in a single process)
-    (ms, e2e_ms, kern_avg_ms), (total_bytes_per_step,) = xn.sharding.aggregate(
-        [ms, e2e_ms, kern_ms / max(kern_n, 1)], [float(bytes_per_step)], device="cuda")
+    # job-wide figures: slowest rank's time, all ranks' bytes (no-op in a single process); the
+    # kernel's roofline figure is per rank: its own bytes over its own launch time
+    my_kern_ms = kern_ms / max(kern_n, 1)
+    my_achieved = bytes_per_layer / (my_kern_ms * 1e-3) / 1e9 if my_kern_ms > 0 else 0.0
+    (ms, e2e_ms), (total_bytes_per_step,) = xn.sharding.aggregate(
+        [ms, e2e_ms], [float(bytes_per_step)], device="cuda")
+    per_rank = [{"rank": rank, "streams": n_streams, "kv_tokens": int(lens.sum()), "kernel_ms": my_kern_ms,
+                 "kernel_gbs": my_achieved}]
+    if world > 1:
+        gathered = [None] * world
+        dist.all_gather_object(gathered, per_rank[0])
+        per_rank = gathered
+    kern_avg_ms = max(p["kernel_ms"] for p in per_rank)
 
     # outputs of both paths agree (same kernels, same inputs)
     same = bool(torch.equal(o_d.cpu(), o_h)) if e2e_steps > 0 else None
@@ -785,39 +937,39 @@ def run_gpu_arm(args):
     line = None
     if rank == 0:
         peak, peak_kind = load_peaks()
-        achieved = bytes_per_layer / (kern_avg_ms * 1e-3) / 1e9 if kern_avg_ms > 0 else 0.0
+        achieved = min(p["kernel_gbs"] for p in per_rank)   # the slowest rank's own bytes / own time
         value = total_bytes_per_step * args.steps / (ms * 1e-3) / 1e9
         e2e_value = total_bytes_per_step * e2e_steps / (e2e_ms * 1e-3) / 1e9
-        launches = s1["kernel_launches"] - s0["kernel_launches"]
+        launches = launches_per_bracket
         # DRAM bytes per launch of the split-KV kernel from an ncu capture of this same workload
         # (dram__bytes_read.sum + dram__bytes_write.sum; the summary is kept under profiles/);
         # only valid for the unmodified c3 workload, whose per-launch work is fixed by its seed
         traffic, traffic_src = None, None
-        if args.workload == "c3" and not args.streams and world == 1 and not u8:
-            traffic = 708.71e6 + 5.04e6
-            traffic_src = "ncu capture of this workload (2 of 30 layers), summary under profiles/"
-        if args.workload == "c3" and not args.streams and world == 1 and u8:
-            traffic = 185.15e6 + 4.54e6
-            traffic_src = ("ncu capture of this workload over the u8 cache format (2 of 30 layers), "
-                           "profiles/attn_splitkv_u8_c3_2layers.md")
+        if args.workload == "c3" and not args.streams and not args.layers and world == 1:
+            traffic, traffic_src = load_traffic("attn_splitkv_u8_c3_traffic" if u8 else "attn_splitkv_c3_traffic")
         line = {
             "metric": "decode_attn_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic",
-            "config": {"workload": f"{args.workload}: {desc}", "streams_per_gpu": n_streams,
+            "config": {"workload": f"{args.workload}: {desc}", "streams": n_total_streams,
+                       "streams_per_gpu": [p["streams"] for p in per_rank],
                        "layers": layers, "num_heads": Hq, "num_kv_heads": Hkv, "head_dim": D,
-                       "kv_tokens_per_gpu": int(lens.sum()), "page_tokens": 64,
+                       "kv_tokens_per_gpu": tokens_by_rank, "page_tokens": 64,
                        "kv_format": "u8 bytes + one f32 scale per row" if u8 else "f32",
+                       "placement": ("least-loaded GPU by announced tokens (xn_place_stream)" if args.placement == "least"
+                                     else "round-robin: stream id mod GPUs"),
                        "parallelism": f"streams sharded over {world} GPU(s), no collective",
+                       "timing": f"median of {len(brackets)} brackets of {args.steps} steps "
+                                 f"({sum(brackets) / 1e3:.2f} s timed)",
                        "l2": "inputs larger than L2: %.1f GB of KV per GPU read per step" %
                              (bytes_per_step / 1e9)},
-            "tokens_per_s": n_streams * world * args.steps / (ms * 1e-3),
+            "tokens_per_s": n_total_streams * args.steps / (ms * 1e-3),
             "e2e": {"value": e2e_value, "unit": "GB/s",
                     "h2d_bytes_per_step": layers * (n_streams * Hq * D if whole_block else q_elems + 2 * kv_elems) * 4,
                     "d2h_bytes_per_step": layers * q_elems * 4,
                     "ms_per_step": e2e_ms / max(e2e_steps, 1),
-                    "tokens_per_s": n_streams * world * e2e_steps / (e2e_ms * 1e-3),
+                    "tokens_per_s": n_total_streams * e2e_steps / (e2e_ms * 1e-3),
                     "api": "xn_attention_batch, page-locked host pointers (XN_REQ_HOST_PINNED), one "
                            "blocking call per layer",
                     "staged_ms_per_step": staged_ms / max(e2e_steps, 1),
@@ -830,7 +982,9 @@ def run_gpu_arm(args):
                          "frac": achieved / peak if peak else None, "peak_source": peak_kind,
                          "traffic": traffic, "traffic_source": traffic_src, "avg_launch_ms": kern_avg_ms,
                          "launches_timed": int(kern_n),
-                         "algorithmic_bytes_per_launch": bytes_per_layer},
+                         "algorithmic_bytes_per_launch": bytes_per_layer,
+                         "per_rank": per_rank,
+                         "note": "achieved = the slowest rank's own algorithmic bytes over its own launch time"},
             "clocks": clocks,
             "host_and_device_paths_agree": same,
         }
@@ -915,12 +1069,55 @@ def run_gpu_arm(args):
         pre = {}
         for S in (2048, 8192):
             r = measure_prefill(xn, torch, tstream, local_rank, S, 20, 5, 128, 500000.0,
-                                steps=5, warmup=3, e2e=(S == 2048))
-            r["frac_of_tf32_peak"] = r["kernel_tflops"] / peak
+                                steps=10, warmup=3, e2e=(S == 2048), min_seconds=0.1)
+            r["frac_of_tf32_peak"] = r["tflops"] / peak                 # the whole call: append + attention
+            r["kernel_frac_of_tf32_peak"] = r["kernel_tflops"] / peak   # the tensor-core kernel alone
             pre[f"S{S}"] = r
+        # chunked prefill (examples/chat.rs:297-306): 512-row chunks behind a long prefix
+        r = measure_prefill(xn, torch, tstream, local_rank, 2048, 20, 5, 128, 500000.0, steps=10, warmup=3,
+                            e2e=False, min_seconds=0.1, index_pos=6144, chunk=512)
+        r["frac_of_tf32_peak"] = r["tflops"] / peak
+        pre["S2048_chunks512_at6144"] = r
+        # the exact-f32 path (XN_PREFILL_F32): the tiled CUDA-core kernel, and beside it the row-wise
+        # stand-in it replaced (every query row served as a decode unit by the split-KV kernel)
+        f32 = {}
+        for name, env in (("tiled_kernel", "1"), ("row_wise", "0")):
+            os.environ["XORNET_ATTN_F32_TILED"] = env
+            r = measure_prefill(xn, torch, tstream, local_rank, 2048, 20, 5, 128, 500000.0, steps=5, warmup=3,
+                                e2e=False, min_seconds=0.05, prefill_mode=1)
+            f32[name] = {"ms": r["ms"], "tflops": r["tflops"], "kernel_ms": r["kernel_ms"]}
+        os.environ.pop("XORNET_ATTN_F32_TILED", None)
+        f32["note"] = "f32 CUDA-core math: against the 2 x 74 TFLOP/s an SM's FMA pipes allow, not the tensor peak"
+        pre["S2048_exact_f32"] = f32
         line["prefill"] = {"kernel": "prefill_tf32_kernel (tcgen05 TF32, TMEM accumulators)",
                            "shape": "1 sequence, 20/5 heads, head_dim 128, fused RoPE + append",
-                           "tf32_peak_tflops": peak, "peak_source": peak_kind, **pre}
+                           "tf32_peak_tflops": peak, "peak_source": peak_kind,
+                           "library_tf32_matmul_tflops": tf32_matmul_tflops(torch), **pre}
+    if rank == 0 and world == 1 and not args.no_extras and args.workload == "c3":
+        # the other workload shapes, one short summary each
+        c1 = measure_decode(xn, torch, tstream, local_rank, [1024], 20, 5, 128, 1, steps=200)
+        c1["workload"] = WORKLOADS["c1"][-1]
+        c1["note"] = "5.3 MB per launch: bound by launch and hand-over latency, not by HBM"
+        lens5 = stream_lengths(8 * 32, 2048, 8192, BASE_SEED + 5000)
+        own5 = place_streams(xn, lens5, 8, args.placement)
+        c5 = measure_decode(xn, torch, tstream, local_rank, [int(L) for i, L in enumerate(lens5) if own5[i] == 0],
+                            32, 8, 128, 32, steps=3)
+        c5["workload"] = WORKLOADS["c5"][-1] + " (one GPU's share of 256 streams placed over 8 GPUs)"
+        c4p = measure_prefill(xn, torch, tstream, local_rank, 1024, 32, 32, 100, 10000.0, steps=10, warmup=3,
+                              e2e=False, min_seconds=0.1, n_seqs=8)
+        c4p["frac_of_tf32_peak"] = c4p["tflops"] / peak
+        c4p["kernel_frac_of_tf32_peak"] = c4p["kernel_tflops"] / peak
+        c4p["roofline"] = {"bound": "tensor", "achieved": c4p["kernel_tflops"], "peak": peak, "unit": "TFLOP/s",
+                           "frac": c4p["kernel_tflops"] / peak, "peak_source": peak_kind,
+                           "note": "flops counted with head_dim 100; the kernel pads rows to 104 / 112 columns"}
+        c4d = measure_decode(xn, torch, tstream, local_rank, [1025] * 8, 32, 32, 100, 1, steps=256, grow=True,
+                             theta=10000.0)
+        line["configs"] = {"c1": c1, "c5": c5,
+                           "c4": {"workload": "BitNet-3B shape: 32/32 heads, head_dim 100, RoPE theta 1e4, 8 sequences: "
+                                              "1024-token prefill, then 256 decode steps that append",
+                                  "prefill": c4p, "decode": c4d}}
+        line["e2e"]["dropin"] = run_dropin_leg(xn, 64, 30, 20, 5, 128, 128, 4096, steps=10, warmup=2,
+                                               device=local_rank, pool_mb=28000)
     if rank == 0:
         print(json.dumps(line))
     if world > 1:
@@ -940,13 +1137,17 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill summary")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the summaries of the other workload shapes and the drop-in leg")
     ap.add_argument("--seq", type=int, default=0, help="prefill length for --workload c2")
-    ap.add_argument("--min-seconds", type=float, default=0.25,
-                    help="keep repeating the timed loop until it has covered this much device time")
+    ap.add_argument("--min-seconds", type=float, default=0.5,
+                    help="keep repeating the timed bracket until it has covered this much device time")
     ap.add_argument("--pos", type=int, default=0, help="c2: cached tokens in front of the prefill (index_pos)")
     ap.add_argument("--chunk", type=int, default=0, help="c2: feed the prefill in chunks of this many rows")
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (profiling)")
     ap.add_argument("--streams", type=int, default=0, help="override streams per GPU (profiling)")
+    ap.add_argument("--placement", default="least", choices=["least", "rr"],
+                    help="which GPU a stream lives on: least-loaded by announced tokens, or stream id mod GPUs")
     ap.add_argument("--kv", default="f32", choices=["f32", "u8"],
                     help="KV cache format of the decode workloads (u8: the opt-in compressed pages)")
     args = ap.parse_args()

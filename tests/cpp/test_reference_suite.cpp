@@ -3,6 +3,7 @@
 // passed.  Needs a B200; built and run by tests/test_gpu_cpp_host.py.
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <stdexcept>
 #include <string>
 
@@ -104,7 +105,8 @@ static void shape_errors() {  // fast_attention.rs:86-92
 // and the literals of that test, which belong to the global weight scale 5/8 it was written with.
 static void ternary_linear_layer() {
     using namespace xor_net;
-    AttnContext ctx(0, 1, 1, 1, 4, 1);
+    AttnGroup grp(1, 1, 1, 4);
+    xn_ctx* ctx = grp.ctx(0);
     const std::vector<float> w = {1, 0, -1, 1, 0, -1, 1, 0};
     const FastTensor x({0.5f, 1.0f, -0.5f, 2.0f}, {1, 4});
     set_out_proj(ctx, 0, TernaryLinear::create(4, 2, w, TernaryPackType::Pack4, 0.625f), nullptr);
@@ -115,7 +117,8 @@ static void ternary_linear_layer() {
     CHECK(std::fabs(o4.data[0] - 1.879921f) < 1e-4f, "o_proj[0]");
     CHECK(std::fabs(o4.data[1] + 0.944882f) < 1e-4f, "o_proj[1]");
     // tests/tensor_rmsnorm_tests.rs:20-31 through the block: identity weights, unit norm weight
-    AttnContext ctx2(0, 1, 1, 1, 2, 1);
+    AttnGroup grp2(1, 1, 1, 2);
+    xn_ctx* ctx2 = grp2.ctx(0);
     FastRmsNorm norm;
     norm.eps = 1e-6f;
     norm.weight = {1.0f, 1.0f};
@@ -128,6 +131,8 @@ static void ternary_linear_layer() {
 }
 
 int main() {
+    setenv("XORNET_ATTN_POOL_MB", "64", 0);   // small pools: these tests hold a handful of tokens
+
     try {
         ternary_linear_layer();
         attention_single_token_is_identity();

@@ -167,3 +167,26 @@ def test_static_decode_entry_names_no_allocating_call(repo_root):
                      "std::vector", "malloc("):
             assert word not in text, f"{word!r} appears in the allocation-free entry point"
     assert "cudaGetSymbolAddress" in body and "g_static_scratch" in body
+
+
+def test_stream_placement_policy():
+    """xn_place_stream: least-loaded by tokens, ties by live streams, then round-robin; and the
+    plain round-robin rule (stream number mod devices)."""
+    least, rr = xn.PLACE_LEAST_LOADED, xn.PLACE_ROUND_ROBIN
+    assert xn.place_stream([5, 3, 9], [1, 1, 1], 0, least) == 1
+    assert xn.place_stream([4, 4, 4], [2, 1, 2], 0, least) == 1          # tie on tokens: fewest streams
+    assert [xn.place_stream([0, 0, 0, 0], [0, 0, 0, 0], t, least) for t in range(6)] == [0, 1, 2, 3, 0, 1]
+    assert [xn.place_stream([7, 1, 1], [0, 0, 0], t, rr) for t in range(5)] == [0, 1, 2, 0, 1]
+    with pytest.raises(xn.XnError):
+        xn.place_stream([1, 2], [0, 0], 0, 7)
+    # placing a seeded draw of lengths one by one keeps the GPUs within one stream of each other
+    rng = np.random.default_rng(299792458 + 3000)
+    lens = rng.integers(128, 4097, 512)
+    tokens, live = [0] * 8, [0] * 8
+    for i, L in enumerate(lens):
+        w = xn.place_stream(tokens, live, i, least)
+        tokens[w] += int(L)
+        live[w] += 1
+    assert max(tokens) - min(tokens) <= 4096
+    rr_tokens = [int(lens[r::8].sum()) for r in range(8)]
+    assert (max(tokens) / (sum(tokens) / 8)) < (max(rr_tokens) / (sum(rr_tokens) / 8))

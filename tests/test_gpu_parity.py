@@ -3,6 +3,8 @@
 Tolerance of the f32 path (gpu_util.ABS_TOL / REL_TOL): max abs <= 1e-4 and relative L2 <= 1e-5.
 Cache contents (append, fused RoPE) must be bit-identical.
 """
+import os
+
 import numpy as np
 import pytest
 
@@ -331,7 +333,11 @@ def test_submission_refused_after_page_assignment_restores_the_streams():
     # claimed that was never written: lengths, page tables and the free list as before, and a
     # later read of those positions returns the reference's zeros.
     Hq, Hkv, D = 8, 8, 4
-    ctx = xn.Context(1, Hq, Hkv, D, pool_pages=9500, prefill_mode=F32)
+    os.environ["XORNET_ATTN_F32_TILED"] = "0"     # row-wise exact prefill: one unit per row and KV head
+    try:
+        ctx = xn.Context(1, Hq, Hkv, D, pool_pages=9500, prefill_mode=F32)
+    finally:
+        del os.environ["XORNET_ATTN_F32_TILED"]
     rng = np.random.default_rng(55)
     st = ctx.new_stream(1 << 20)
     ctx.attention(st, 0, 0, *rand_qkv(rng, Hq, Hkv, 70, D))
@@ -456,3 +462,32 @@ def test_expired_device_wait_is_reported_and_the_context_survives():
     assert_parity(got, want, "after an expired wait")
     ctx.synchronize()                                              # status word was cleared
     ctx.close()
+
+
+@pytest.mark.parametrize("Hq,Hkv,D,S,pos", [(20, 5, 128, 333, 0), (8, 8, 100, 200, 70), (4, 2, 7, 150, 5),
+                                            (6, 2, 160, 130, 0), (3, 1, 256, 90, 33)])
+def test_tiled_exact_prefill_equals_the_row_wise_path(Hq, Hkv, D, S, pos):
+    # the tiled exact-f32 prefill kernel and the row-wise path (every query row a decode unit) on
+    # the same inputs: both within the f32 bounds of the oracle, caches identical
+    rng = np.random.default_rng(900 + D)
+    outs = {}
+    for tiled in ("1", "0"):
+        os.environ["XORNET_ATTN_F32_TILED"] = tiled
+        try:
+            ctx = xn.Context(1, Hq, Hkv, D, pool_pages=16, shuffle_seed=3, prefill_mode=F32)
+        finally:
+            del os.environ["XORNET_ATTN_F32_TILED"]
+        p = Pair(ctx, 512)
+        r2 = np.random.default_rng(901 + D)
+        if pos:
+            p.step(0, 0, *rand_qkv(r2, Hq, Hkv, pos, D))
+        before = ctx.stats()
+        got, want = p.step(0, pos, *rand_qkv(r2, Hq, Hkv, S, D))
+        after = ctx.stats()
+        assert_parity(got, want, f"tiled={tiled} D={D}")
+        assert (after["prefill_launches"] - before["prefill_launches"]) == (1 if tiled == "1" else 0)
+        p.check_cache(0)
+        outs[tiled] = got
+        ctx.close()
+    a, r = errs(outs["1"], outs["0"])
+    assert a <= 1e-4 and r <= 1e-5

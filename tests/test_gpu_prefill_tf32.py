@@ -134,7 +134,7 @@ def test_unaligned_device_tensors_fall_back_to_the_exact_path():
                             od.data_ptr() + 4)], xn.REQ_DEVICE_PTRS)
     ctx.submit(reqs)
     ctx.synchronize()
-    assert ctx.stats()["prefill_launches"] == 0
+    assert ctx.stats()["prefill_launches"] == 1      # the tiled exact-f32 kernel: the f32 bounds below hold
     want = xo.fast_attention(q, k, v, 0, 0, p.ref, 4, 2, 64)
     assert_parity(od[1:].cpu().numpy().reshape(q.shape), want, "unaligned device tensors")
     ctx.close()

@@ -54,6 +54,22 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
     return LIB_PATH
 
 
+def build_host_tool(name: str, force: bool = False) -> str:
+    """Compiles host/<name>.cpp (a C++ program over the host mirror and the C ABI) beside the
+    library and returns the path of the executable."""
+    src = os.path.join(HERE, "host", name + ".cpp")
+    exe = os.path.join(HERE, name)
+    build_library()
+    deps = [src, os.path.join(HERE, "host", "xor_net_attn.hpp"), os.path.join(INCLUDE, "xn_attn.h")]
+    if force or not os.path.exists(exe) or any(os.path.getmtime(p) > os.path.getmtime(exe) for p in deps):
+        cmd = ["g++", "-std=c++17", "-O2", "-pthread", "-I", INCLUDE, "-I", os.path.join(HERE, "host"), src,
+               "-o", exe, "-L", HERE, "-lxn_attn", f"-Wl,-rpath,{HERE}"]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError("g++ failed:\n" + res.stdout + res.stderr)
+    return exe
+
+
 if __name__ == "__main__":
     import sys
     print(build_library(force="--force" in sys.argv, verbose="-v" in sys.argv))

@@ -23,6 +23,7 @@
 #include "xn_outproj.cuh"
 #include "xn_outproj_tc.cuh"
 #include "xn_plan.hpp"
+#include "xn_prefill_f32.cuh"
 #include "xn_prefill_tf32.cuh"
 #include "xn_static_decode.cuh"
 #include "xn_ternary.hpp"
@@ -67,10 +68,17 @@ struct OutRun {
     size_t q_row0;             // first row in the quantised-activation buffer (multiple of 256)
 };
 
+// One blocking caller of xn_attention waiting in the context's queue.  Every caller sleeps on its
+// own condition variable: waking sixty-four slot threads one by one costs less than letting them
+// all fight for one lock.
 struct Pending {
     xn_req req;
     int32_t status = XN_OK;
-    bool done = false;
+    bool done = false;      // served: status is final          (guarded by the context's q_mu)
+    bool promoted = false;  // not served yet, but now the leader (guarded by the context's q_mu)
+    std::condition_variable cv;
+    float* user_out = nullptr;   // where the caller wants the output when the request was re-pointed
+    size_t out_bytes = 0;        // at the stream's page-locked call buffer
 };
 
 }  // namespace
@@ -82,6 +90,11 @@ struct xn_stream {
     std::vector<int32_t> pages;   // page id of slots [64*i, 64*i+64)
     std::vector<int64_t> hw;      // per layer: highest written position + 1
     int64_t expected = 0;         // tokens the creator said the stream will hold (placement only)
+    // Page-locked, device-mapped buffer for the tensors of one blocking single-token call
+    // [q | k | v | out]: the caller copies its pageable tensors in and out itself, in parallel
+    // with the other callers, and the kernels read and write the buffer over PCIe directly.
+    unsigned char* call_buf = nullptr;
+    size_t call_cap = 0;
 };
 
 // One context per GPU of a box behind one handle; streams are placed on the least-loaded one.
@@ -105,6 +118,7 @@ struct xn_ctx {
     int max_pos = 0;
     int prefill_mode = 0;
     int batch_window_us = 0;
+    int auto_window_us = 0;     // >0: a leader waits this long for the previous group's callers to return
     int sm_count = 0;
     int decode_ctas = 0;     // thread blocks of the split-KV launch (one per SM)
     int decode_chunks = 0;   // chunks the tile list is cut into (several per block)
@@ -115,6 +129,8 @@ struct xn_ctx {
     bool out_pdl = true;     // ... launched as a programmatic dependent of the quantiser kernel
     bool out_rows_kernel = true;  // ... and, for more than 128 rows, the many-row variant
     bool pf_pdl = true;      // tensor-core prefill launched as a programmatic dependent of the append
+    bool f32_tiled = true;   // exact-f32 prefills of f32_tiled_min_rows rows or more: the tiled kernel
+    int f32_tiled_min_rows = 32;   // (shorter ones are served row by row by the split-KV kernel)
     int* sync_d = nullptr;   // chunk counter, done counter, per-unit arrival counters
     size_t sync_cap = 0;     // ints
     cudaStream_t stream = nullptr;
@@ -180,6 +196,8 @@ struct xn_ctx {
     std::condition_variable q_cv;
     std::vector<Pending*> queue;
     bool leader_active = false;
+    size_t last_group = 1;          // callers merged into the previous submission
+    bool leader_in_window = false;  // the leader is waiting for company: arrivals tell it
 };
 
 namespace {
@@ -298,6 +316,23 @@ int nv_class_for(int nv) {
     return 64;
 }
 
+// ---- tiled exact-f32 prefill: instantiation by row length ------------------------------------
+
+using PrefillF32Fn = void (*)(const ReqDev*, const F32Item*, const int*, const float*, const float*, long long,
+                              int, int, int, int, float, int*);
+struct PrefillF32Kernel {
+    PrefillF32Fn fn;
+    size_t smem;      // dynamic shared memory of a launch for this row length
+    size_t smem_max;  // ... for the longest rows the instantiation serves: the per-function limit is
+                      // shared by all contexts of the process, whatever their head_dim
+};
+PrefillF32Kernel pick_prefill_f32(int nv) {
+    const int dp = nv * 4;
+    if (dp <= 64) return {prefill_f32_kernel<64, 1>, pf32::smem_bytes(dp, 64), pf32::smem_bytes(64, 64)};
+    if (dp <= 128) return {prefill_f32_kernel<64, 2>, pf32::smem_bytes(dp, 64), pf32::smem_bytes(128, 64)};
+    return {prefill_f32_kernel<32, 4>, pf32::smem_bytes(dp, 32), pf32::smem_bytes(256, 32)};
+}
+
 // ---- TMA tensor maps (driver entry point resolved at run time; libcuda is not linked) -------
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -396,6 +431,12 @@ int32_t ensure_pages(xn_ctx* c, xn_stream* s, int64_t slots_needed) {
         c->free_pages.pop_back();
     }
     return XN_OK;
+}
+
+void free_call_buffer(xn_stream* s) {
+    if (s->call_buf) cudaFreeHost(s->call_buf);
+    s->call_buf = nullptr;
+    s->call_cap = 0;
 }
 
 void release_pages(xn_ctx* c, xn_stream* s) {
@@ -620,6 +661,13 @@ struct StreamRollback {
     }
 };
 
+// Whether a request that the tensor-core kernel does not take goes to the tiled exact-f32 kernel
+// (f32 cache format, no ring fold, enough rows to fill a tile usefully).
+bool use_f32_tiled(const xn_ctx* c, const xn_req& r) {
+    return c->f32_tiled && !c->kv_u8 && r.seq_len >= c->f32_tiled_min_rows &&
+           r.index_pos + r.seq_len <= r.stream->cap;
+}
+
 // reqs[i] are valid, on distinct streams, all host-mode or all device-mode.
 int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
     const int Hq = c->num_heads, Hkv = c->num_kv_heads, D = c->head_dim, nv = c->nv;
@@ -679,7 +727,7 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         else if (use_tf32(c, r, direct)) {   // served by the tensor-core prefill kernel
             stage_need = std::max<long long>(stage_need, (end + kPageTokens - 1) / kPageTokens);
         }
-        else {
+        else if (!use_f32_tiled(c, r)) {
             n_units += (long long)r.seq_len * Hkv * c->subs;
             key_rows += (long long)Hkv * c->subs *
                         ((long long)r.seq_len * r.index_pos + (long long)r.seq_len * (r.seq_len + 1) / 2);
@@ -746,6 +794,7 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
     kv_lens.reserve(size_t(n_units));
     std::vector<int32_t> ring_rows;
     std::vector<int> tf32_reqs;
+    std::vector<F32Item> f32_items;
     std::vector<OutRowDev> out_row_tab;
     out_row_tab.reserve(out_rows);
     std::vector<OutRun> out_runs;
@@ -840,6 +889,10 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
             for (int t = 0; t < S; ++t) { ring_rows.push_back(i); ring_rows.push_back(t); }
         } else if (to_tf32) {
             tf32_reqs.push_back(i);
+        } else if (use_f32_tiled(c, r)) {
+            // heaviest query tiles first (blocks are handed to SMs in index order)
+            for (int qt = (S + pf32::kTQ - 1) / pf32::kTQ - 1; qt >= 0; --qt)
+                for (int h = 0; h < Hq; ++h) f32_items.push_back({i, h, qt, 0});
         } else {
             for (int h = 0; h < Hkv; ++h)
                 for (int sb = 0; sb < c->subs; ++sb)
@@ -882,6 +935,7 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
     const size_t o_ring = place(sizeof(int32_t) * ring_rows.size());
     const size_t o_rows = place(sizeof(OutRowDev) * out_row_tab.size());
     const size_t o_qkv = place(sizeof(OutRowDev) * qkv_row_tab.size());
+    const size_t o_f32 = place(sizeof(F32Item) * f32_items.size());
     PlanSlot* slot = nullptr;
     if ((rc = acquire_slot(c, off, &slot)) != XN_OK) return rc;
     memcpy(slot->host + o_req, rd.data(), sizeof(ReqDev) * n);
@@ -895,6 +949,7 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         memcpy(slot->host + o_rows, out_row_tab.data(), sizeof(OutRowDev) * out_row_tab.size());
     if (!qkv_row_tab.empty())
         memcpy(slot->host + o_qkv, qkv_row_tab.data(), sizeof(OutRowDev) * qkv_row_tab.size());
+    if (!f32_items.empty()) memcpy(slot->host + o_f32, f32_items.data(), sizeof(F32Item) * f32_items.size());
     // The plan does not depend on anything in flight: upload it on the copy stream so that it
     // overlaps the previous submission's kernels, and make the launch stream wait for it.
     // (A blocking host-pointer call has nothing in flight to overlap with: plain in-stream copy.)
@@ -996,6 +1051,16 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         c->stats.kernel_launches += 1;
         c->stats.decode_launches += 1;
     }
+    if (!f32_items.empty()) {
+        const PrefillF32Kernel pk = pick_prefill_f32(nv);
+        if (c->profile && (rc = profile_begin(c, 1)) != XN_OK) return rc;
+        pk.fn<<<unsigned(f32_items.size()), pf32::kThreads, pk.smem, c->stream>>>(
+            reqs_d, reinterpret_cast<const F32Item*>(slot->dev + o_f32), pages_d, c->k_pool, c->v_pool,
+            c->pool_pages, Hkv, c->group, D, nv, c->scale, c->status_d);
+        if (c->profile && (rc = profile_end(c)) != XN_OK) return rc;
+        c->stats.kernel_launches += 1;
+        c->stats.prefill_launches += 1;
+    }
     for (int i : tf32_reqs) {
         const ReqDev& d = rd[size_t(i)];
         PrefillArgs pa;
@@ -1090,12 +1155,14 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
     return XN_OK;
 }
 
-// Runs a group of blocking host-pointer requests as one submission.  Requests that fail
-// validation, or that name a stream already in the group, get their own status and are left out.
+// Runs a group of blocking host-pointer requests.  Requests that fail validation, or that name a
+// stream already in the group, get their own status and are left out.  The others go out as one
+// submission per kind of memory they point at (the streams' page-locked call buffers, or pageable
+// memory that the library stages).
 void run_group(xn_ctx* c, std::vector<Pending*>& group) {
     std::lock_guard<std::mutex> g(c->mu);
-    std::vector<xn_req> ok;
-    std::vector<Pending*> ok_p;
+    std::vector<xn_req> ok[2];   // [0] pageable, [1] page-locked
+    std::vector<Pending*> ok_p[2];
     std::unordered_set<xn_stream*> seen;
     for (Pending* p : group) {
         int32_t rc = validate_req(c, p->req);
@@ -1103,48 +1170,108 @@ void run_group(xn_ctx* c, std::vector<Pending*>& group) {
             rc = fail(c, XN_ERR_ARG, "two concurrent calls on one stream");
         p->status = rc;
         if (rc == XN_OK) {
-            ok.push_back(p->req);
-            ok_p.push_back(p);
+            const int kind = (p->req.flags & XN_REQ_HOST_PINNED) ? 1 : 0;
+            ok[kind].push_back(p->req);
+            ok_p[kind].push_back(p);
         }
     }
-    if (!ok.empty()) {
-        int32_t rc = submit_locked(c, int(ok.size()), ok.data(), true);
-        for (Pending* p : ok_p) p->status = rc;
-        c->stats.coalesced_max = std::max<uint64_t>(c->stats.coalesced_max, ok.size());
+    c->stats.coalesced_max = std::max<uint64_t>(c->stats.coalesced_max, ok[0].size() + ok[1].size());
+    for (int kind = 1; kind >= 0; --kind) {
+        if (ok[kind].empty()) continue;
+        int32_t rc = submit_locked(c, int(ok[kind].size()), ok[kind].data(), true);
+        for (Pending* p : ok_p[kind]) p->status = rc;
         // The callers are independent, as in the reference: when the merged submission was
         // refused before anything ran (it left the streams untouched), one request that does not
         // fit must not fail the others.  Run them one by one; each gets its own status.
-        if (ok.size() > 1 && (rc == XN_ERR_OUT_OF_PAGES || rc == XN_ERR_CAPACITY || rc == XN_ERR_NOMEM))
-            for (size_t i = 0; i < ok.size(); ++i) ok_p[i]->status = submit_locked(c, 1, &ok[i], true);
+        if (ok[kind].size() > 1 && (rc == XN_ERR_OUT_OF_PAGES || rc == XN_ERR_CAPACITY || rc == XN_ERR_NOMEM))
+            for (size_t i = 0; i < ok[kind].size(); ++i)
+                ok_p[kind][i]->status = submit_locked(c, 1, &ok[kind][i], true);
     }
 }
 
+// A single-token call brings its tensors to the stream's page-locked call buffer itself (every
+// caller in parallel, outside all locks) and is queued pointing there; the kernels then need no
+// staging copy.  Larger calls stay as they are and go through the library's staging.
+void stage_in_call_buffer(xn_ctx* c, Pending& me) {
+    xn_req& r = me.req;
+    xn_stream* s = r.stream;
+    // (u8 cache format: its attention kernel reads the new rows with plain 4-byte loads, which is
+    // slow over PCIe; those calls keep the staged path and its fused append)
+    if (c->kv_u8 || r.seq_len != 1 || !stream_ok(c, s) || !r.q || !r.k || !r.v || !r.out ||
+        (r.flags & ~uint32_t(XN_REQ_ROPE)))
+        return;
+    const size_t qb = align_up(size_t(c->num_heads) * c->head_dim * 4, 16);
+    const size_t kb = align_up(size_t(c->num_kv_heads) * c->head_dim * 4, 16);
+    if (s->call_cap < 2 * qb + 2 * kb) {
+        if (s->call_buf) return;   // sized at first use; a stream's shape does not change
+        void* p = nullptr;
+        if (cudaSetDevice(c->device) != cudaSuccess ||
+            cudaHostAlloc(&p, 2 * qb + 2 * kb, cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess) {
+            cudaGetLastError();
+            return;                // no page-locked memory to be had: the staged path serves the call
+        }
+        s->call_buf = static_cast<unsigned char*>(p);
+        s->call_cap = 2 * qb + 2 * kb;
+    }
+    unsigned char* b = s->call_buf;
+    memcpy(b, r.q, size_t(c->num_heads) * c->head_dim * 4);
+    memcpy(b + qb, r.k, size_t(c->num_kv_heads) * c->head_dim * 4);
+    memcpy(b + qb + kb, r.v, size_t(c->num_kv_heads) * c->head_dim * 4);
+    me.user_out = r.out;
+    me.out_bytes = size_t(c->num_heads) * c->head_dim * 4;
+    r.q = reinterpret_cast<const float*>(b);
+    r.k = reinterpret_cast<const float*>(b + qb);
+    r.v = reinterpret_cast<const float*>(b + qb + kb);
+    r.out = reinterpret_cast<float*>(b + qb + 2 * kb);
+    r.flags |= XN_REQ_HOST_PINNED;
+}
+
+// The queue of blocking callers.  Whoever finds no leader becomes one: it takes everything queued
+// (its own request included), runs it as one group, wakes the callers it served, and hands the
+// lead to the first caller that arrived meanwhile.  When the previous group held several callers
+// a new leader first waits briefly for as many to show up again: slot threads that were woken
+// together come back together, one layer later.
 int32_t attention_blocking(xn_ctx* c, const xn_req& req) {
     Pending me;
     me.req = req;
+    stage_in_call_buffer(c, me);
     std::unique_lock<std::mutex> lk(c->q_mu);
     c->queue.push_back(&me);
-    while (!me.done) {
-        if (!c->leader_active) {
-            c->leader_active = true;
-            if (c->batch_window_us > 0) {
-                const size_t target = std::max<size_t>(1, c->streams.size());
-                c->q_cv.wait_for(lk, std::chrono::microseconds(c->batch_window_us),
-                                 [&] { return c->queue.size() >= target; });
-            }
-            std::vector<Pending*> group;
-            group.swap(c->queue);
-            lk.unlock();
-            run_group(c, group);
-            lk.lock();
-            for (Pending* p : group) p->done = true;
+    if (c->leader_active) {
+        if (c->leader_in_window) c->q_cv.notify_one();
+        me.cv.wait(lk, [&] { return me.done || me.promoted; });
+    } else {
+        c->leader_active = true;
+        me.promoted = true;
+    }
+    if (!me.done) {
+        // ---- leader
+        const size_t target = c->batch_window_us > 0 ? std::max<size_t>(1, c->streams.size()) : c->last_group;
+        const int window_us = c->batch_window_us > 0 ? c->batch_window_us : (c->last_group > 1 ? c->auto_window_us : 0);
+        if (window_us > 0 && c->queue.size() < target) {
+            c->leader_in_window = true;
+            c->q_cv.wait_for(lk, std::chrono::microseconds(window_us), [&] { return c->queue.size() >= target; });
+            c->leader_in_window = false;
+        }
+        std::vector<Pending*> group;
+        group.swap(c->queue);
+        lk.unlock();
+        run_group(c, group);
+        lk.lock();
+        c->last_group = group.size();
+        for (Pending* p : group) {
+            p->done = true;
+            if (p != &me) p->cv.notify_one();
+        }
+        if (c->queue.empty()) {
             c->leader_active = false;
-            c->q_cv.notify_all();
-        } else {
-            c->q_cv.notify_all();  // lets a leader that is waiting for company re-check
-            c->q_cv.wait(lk);
+        } else {   // someone arrived while the group ran: that caller leads the next one
+            c->queue.front()->promoted = true;
+            c->queue.front()->cv.notify_one();
         }
     }
+    lk.unlock();
+    if (me.user_out && me.status == XN_OK) memcpy(me.user_out, me.req.out, me.out_bytes);
     return me.status;
 }
 
@@ -1230,6 +1357,9 @@ int32_t xn_ctx_create(const xn_ctx_desc* d, xn_ctx** out_ctx) {
     c->max_pos = d->max_pos;
     c->prefill_mode = d->prefill_mode;
     c->batch_window_us = d->batch_window_us;
+    if (c->batch_window_us == 0)
+        if (const char* env = getenv("XORNET_ATTN_BATCH_WINDOW_US")) c->batch_window_us = std::max(0, atoi(env));
+    if (const char* env = getenv("XORNET_ATTN_AUTO_WINDOW_US")) c->auto_window_us = std::max(0, atoi(env));
     c->sm_count = prop.multiProcessorCount;
     c->out_proj.resize(size_t(d->num_layers));
     c->qkv_proj.resize(size_t(d->num_layers));
@@ -1252,6 +1382,8 @@ int32_t xn_ctx_create(const xn_ctx_desc* d, xn_ctx** out_ctx) {
     if (const char* env = getenv("XORNET_ATTN_OUTPROJ_PDL")) c->out_pdl = atoi(env) != 0;
     if (const char* env = getenv("XORNET_ATTN_OUTPROJ_ROWS")) c->out_rows_kernel = atoi(env) != 0;
     if (const char* env = getenv("XORNET_ATTN_PREFILL_PDL")) c->pf_pdl = atoi(env) != 0;
+    if (const char* env = getenv("XORNET_ATTN_F32_TILED")) c->f32_tiled = atoi(env) != 0;
+    if (const char* env = getenv("XORNET_ATTN_F32_TILED_MIN_ROWS")) c->f32_tiled_min_rows = std::max(1, atoi(env));
 
 
     const size_t page_bytes =
@@ -1333,6 +1465,9 @@ int32_t xn_ctx_create(const xn_ctx_desc* d, xn_ctx** out_ctx) {
         SplitKernel k = pick_split(c->nv_class, c->gt, c->nv_exact);
         XN_CREATE_CUDA(cudaFuncSetAttribute(reinterpret_cast<const void*>(k.fn),
                                             cudaFuncAttributeMaxDynamicSharedMemorySize, int(k.smem)));
+        const PrefillF32Kernel pk = pick_prefill_f32(c->nv);
+        XN_CREATE_CUDA(cudaFuncSetAttribute(reinterpret_cast<const void*>(pk.fn),
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize, int(pk.smem_max)));
     }
 
     // tensor-core prefill: possible when rows are exactly head_dim floats and TMA can address them
@@ -1389,6 +1524,7 @@ int32_t xn_ctx_destroy(xn_ctx* c) {
     cudaSetDevice(c->device);
     if (c->stream) cudaStreamSynchronize(c->stream);
     for (xn_stream* s : c->streams) {
+        free_call_buffer(s);
         s->magic = 0;
         delete s;
     }
@@ -1533,6 +1669,7 @@ int32_t xn_stream_destroy(xn_ctx* c, xn_stream* s) {
         std::lock_guard<std::mutex> q(c->q_mu);
         c->streams.erase(s);
     }
+    free_call_buffer(s);
     s->magic = 0;
     delete s;
     return XN_OK;

@@ -37,46 +37,45 @@ struct FastTensor {
     const std::vector<size_t>& dims() const { return shape; }
 };
 
-// One page pool and launch state per (device, model shape), shared by every cache of that shape:
-// the counterpart of the `Arc<Llama>` the reference's slots share (server/main.rs:613-645).
-class AttnContext {
+// Every GPU of the box behind one process, per model shape: one context (page pool, launch state,
+// queue of concurrent callers) per device, shared by every cache of that shape -- the counterpart
+// of the `Arc<Llama>` the reference's slot threads share (server/main.rs:613-645).  Devices:
+// XORNET_ATTN_DEVICES ("0,1,5"; default every visible device).  Pool per device:
+// XORNET_ATTN_POOL_PAGES pages, else XORNET_ATTN_POOL_MB megabytes, else half of the free memory.
+class AttnGroup {
 public:
-    AttnContext(int device, int num_layers, int num_heads, int num_kv_heads, int head_dim,
-                long long pool_pages) {
+    AttnGroup(int num_layers, int num_heads, int num_kv_heads, int head_dim) {
         xn_ctx_desc d{};
-        d.device = device;
         d.num_layers = num_layers;
         d.num_heads = num_heads;
         d.num_kv_heads = num_kv_heads;
         d.head_dim = head_dim;
         d.page_tokens = 64;
-        d.pool_pages = pool_pages;
-        if (xn_ctx_create(&d, &ctx_) != XN_OK)
-            throw std::runtime_error(std::string("xn_ctx_create: ") + xn_last_error(nullptr));
+        if (const char* env = std::getenv("XORNET_ATTN_POOL_PAGES")) d.pool_pages = std::atoll(env);
+        if (const char* env = std::getenv("XORNET_ATTN_BATCH_WINDOW_US")) d.batch_window_us = std::atoi(env);
+        if (xn_group_create(&d, nullptr, 0, &group_) != XN_OK)
+            throw std::runtime_error(std::string("xn_group_create: ") + xn_last_error(nullptr));
     }
-    ~AttnContext() { xn_ctx_destroy(ctx_); }
-    AttnContext(const AttnContext&) = delete;
-    AttnContext& operator=(const AttnContext&) = delete;
-    xn_ctx* get() const { return ctx_; }
+    ~AttnGroup() { xn_group_destroy(group_); }
+    AttnGroup(const AttnGroup&) = delete;
+    AttnGroup& operator=(const AttnGroup&) = delete;
+    xn_group* get() const { return group_; }
+    int size() const { return xn_group_size(group_); }
+    xn_ctx* ctx(int i) const { return xn_group_ctx(group_, i); }
 
-    // Pool size: XORNET_ATTN_POOL_PAGES pages if set, else enough for `max_seq_len` x 64 streams.
-    static std::shared_ptr<AttnContext> shared(int device, int num_layers, int num_heads,
-                                               int num_kv_heads, int head_dim, size_t max_seq_len) {
+    static std::shared_ptr<AttnGroup> shared(int num_layers, int num_heads, int num_kv_heads, int head_dim) {
         static std::mutex mu;
-        static std::map<std::tuple<int, int, int, int, int>, std::weak_ptr<AttnContext>> all;
+        static std::map<std::tuple<int, int, int, int>, std::weak_ptr<AttnGroup>> all;
         std::lock_guard<std::mutex> g(mu);
-        auto key = std::make_tuple(device, num_layers, num_heads, num_kv_heads, head_dim);
+        auto key = std::make_tuple(num_layers, num_heads, num_kv_heads, head_dim);
         if (auto sp = all[key].lock()) return sp;
-        long long pages = 0;
-        if (const char* env = std::getenv("XORNET_ATTN_POOL_PAGES")) pages = std::atoll(env);
-        if (pages <= 0) pages = (long long)((max_seq_len + 63) / 64) * 64;
-        auto sp = std::make_shared<AttnContext>(device, num_layers, num_heads, num_kv_heads, head_dim, pages);
+        auto sp = std::make_shared<AttnGroup>(num_layers, num_heads, num_kv_heads, head_dim);
         all[key] = sp;
         return sp;
     }
 
 private:
-    xn_ctx* ctx_ = nullptr;
+    xn_group* group_ = nullptr;
 };
 
 class DeviceKvCache {
@@ -85,12 +84,16 @@ public:
 
     // CpuRingCache::new(num_layers, num_kv_heads, max_seq_len, head_dim, use_u8).  The u8 shadow of
     // the reference is write-only (nothing reads it), so `use_u8` has no effect on any result.
+    // The cache lands on the GPU that holds the fewest cached tokens (XORNET_ATTN_PLACEMENT=rr:
+    // cache number mod number of GPUs) and stays there.  `expected_tokens` (0 = unknown) lets a
+    // caller that creates its caches before filling them spread them by the load they will carry.
+    // Unlike the reference's Cache it is not copyable: it names pages of a device pool.
     DeviceKvCache(size_t num_layers_, size_t num_kv_heads_, size_t max_seq_len_, size_t head_dim_,
-                  bool /*use_u8*/ = false, int device = 0)
+                  bool /*use_u8*/ = false, size_t expected_tokens = 0)
         : max_seq_len(max_seq_len_), num_kv_heads(num_kv_heads_), head_dim(head_dim_),
-          num_layers(num_layers_), device_(device) {}
+          num_layers(num_layers_), expected_(expected_tokens) {}
     ~DeviceKvCache() {
-        if (stream_) xn_stream_destroy(ctx_->get(), stream_);
+        if (stream_) xn_stream_destroy(ctx_, stream_);
     }
     DeviceKvCache(const DeviceKvCache&) = delete;
     DeviceKvCache& operator=(const DeviceKvCache&) = delete;
@@ -99,29 +102,33 @@ public:
     std::vector<float> k_buffer(size_t layer) const { return buffer(layer, true); }
     std::vector<float> v_buffer(size_t layer) const { return buffer(layer, false); }
 
-    // binds to the shared context on first use (the query head count arrives with the first call)
+    // binds to the shared group on first use (the query head count arrives with the first call)
     std::pair<xn_ctx*, xn_stream*> bind(size_t num_heads) {
         if (!stream_) {
-            ctx_ = AttnContext::shared(device_, int(num_layers), int(num_heads), int(num_kv_heads),
-                                       int(head_dim), max_seq_len);
-            if (xn_stream_create(ctx_->get(), (int64_t)max_seq_len, &stream_) != XN_OK)
-                throw std::runtime_error(std::string("xn_stream_create: ") + xn_last_error(ctx_->get()));
+            group_ = AttnGroup::shared(int(num_layers), int(num_heads), int(num_kv_heads), int(head_dim));
+            int policy = XN_PLACE_LEAST_LOADED;
+            if (const char* env = std::getenv("XORNET_ATTN_PLACEMENT"))
+                if (std::string(env) == "rr" || std::string(env) == "round_robin") policy = XN_PLACE_ROUND_ROBIN;
+            if (xn_group_stream_create(group_->get(), (int64_t)max_seq_len, (int64_t)expected_, policy, &ctx_,
+                                       &stream_) != XN_OK)
+                throw std::runtime_error(std::string("xn_group_stream_create: ") + xn_last_error(nullptr));
         }
-        return {ctx_->get(), stream_};
+        return {ctx_, stream_};
     }
 
 private:
     std::vector<float> buffer(size_t layer, bool keys) const {
         std::vector<float> out(num_kv_heads * max_seq_len * head_dim, 0.0f);
         if (stream_) {
-            int rc = xn_kv_read_range(ctx_->get(), stream_, int(layer), 0, (int64_t)max_seq_len,
+            int rc = xn_kv_read_range(ctx_, stream_, int(layer), 0, (int64_t)max_seq_len,
                                       keys ? out.data() : nullptr, keys ? nullptr : out.data());
-            if (rc != XN_OK) throw std::runtime_error(std::string("xn_kv_read_range: ") + xn_last_error(ctx_->get()));
+            if (rc != XN_OK) throw std::runtime_error(std::string("xn_kv_read_range: ") + xn_last_error(ctx_));
         }
         return out;
     }
-    int device_;
-    std::shared_ptr<AttnContext> ctx_;
+    size_t expected_;
+    std::shared_ptr<AttnGroup> group_;
+    xn_ctx* ctx_ = nullptr;
     xn_stream* stream_ = nullptr;
 };
 
@@ -181,8 +188,9 @@ struct FastRmsNorm {  // src/nn/fast_rmsnorm.rs:5-17
     std::vector<float> weight;
 };
 
-// Uploads a layer's o_proj (and optional sub-norm) to the context.
-inline void set_out_proj(AttnContext& ctx, size_t layer, const TernaryLinear& o_proj,
+// Uploads a layer's o_proj (and optional sub-norm) to one device's context (every context of a
+// group that serves the layer needs it).
+inline void set_out_proj(xn_ctx* ctx, size_t layer, const TernaryLinear& o_proj,
                          const FastRmsNorm* sub_norm) {
     xn_out_proj_desc d{};
     d.layer = int(layer);
@@ -193,20 +201,20 @@ inline void set_out_proj(AttnContext& ctx, size_t layer, const TernaryLinear& o_
     d.w_scales = o_proj.w_scales.data();
     d.norm_weight = sub_norm ? sub_norm->weight.data() : nullptr;
     d.norm_eps = sub_norm ? sub_norm->eps : 0.0f;
-    if (xn_out_proj_set(ctx.get(), &d) != XN_OK)
-        throw std::runtime_error(std::string("xn_out_proj_set: ") + xn_last_error(ctx.get()));
+    if (xn_out_proj_set(ctx, &d) != XN_OK)
+        throw std::runtime_error(std::string("xn_out_proj_set: ") + xn_last_error(ctx));
 }
 
 // y [.., in_dim] -> o_proj(sub_norm(y)) [.., out_dim]: FastRmsNorm::forward + TernaryLinear::forward.
-inline FastTensor out_proj_forward(AttnContext& ctx, size_t layer, const FastTensor& y, size_t out_dim) {
+inline FastTensor out_proj_forward(xn_ctx* ctx, size_t layer, const FastTensor& y, size_t out_dim) {
     if (y.shape.empty()) throw std::runtime_error("Input must have at least 1 dimension");
     const size_t in_dim = y.shape.back();
     const size_t rows = in_dim ? y.data.size() / in_dim : 0;
     std::vector<size_t> shape = y.shape;
     shape.back() = out_dim;
     FastTensor out = FastTensor::zeros(shape);
-    if (xn_out_proj(ctx.get(), int(layer), int(rows), y.data.data(), out.data.data(), 0) != XN_OK)
-        throw std::runtime_error(std::string("xn_out_proj: ") + xn_last_error(ctx.get()));
+    if (xn_out_proj(ctx, int(layer), int(rows), y.data.data(), out.data.data(), 0) != XN_OK)
+        throw std::runtime_error(std::string("xn_out_proj: ") + xn_last_error(ctx));
     return out;
 }
 
