@@ -55,7 +55,8 @@ typedef enum xn_status {
     XN_ERR_DEVICE_WAIT = 7,  /* a kernel gave up on a bounded wait and reported it               */
     XN_ERR_NO_TABLES = 8,    /* fused-RoPE entry used on a context created without cos/sin       */
     XN_ERR_NOMEM = 9,        /* host allocation failed                                           */
-    XN_ERR_NO_DEVICE = 10    /* no usable CUDA device: there is no CPU fallback                  */
+    XN_ERR_NO_DEVICE = 10,   /* no usable CUDA device: there is no CPU fallback                  */
+    XN_ERR_GUARD = 11        /* xn_debug_check_guards found bytes written outside a device buffer */
 } xn_status;
 
 /* Prefill kernel choice (xn_ctx_desc.prefill_mode). */
@@ -411,6 +412,13 @@ XN_API int32_t xn_plan_split(int32_t n_units, const int32_t* kv_len, int32_t til
  * that waits, for at most timeout_ms (1..1000), on a barrier nothing will complete, then
  * synchronises.  Returns XN_ERR_DEVICE_WAIT (the expected outcome); the context stays usable. */
 XN_API int32_t xn_debug_expire_wait(xn_ctx* ctx, int32_t timeout_ms);
+
+/* Memory-safety check that needs no external tool: every device buffer of a context (page pools,
+ * split-KV partials, rotation scratch, projection rows, staging, plan slots ...) is allocated between
+ * two 256-byte guard areas filled with a known pattern.  This call waits for the context's stream,
+ * reads the guard areas back and returns XN_ERR_GUARD (the text names the buffer and the side) when
+ * any byte changed, XN_OK otherwise.  The test-suite calls it before it destroys a context. */
+XN_API int32_t xn_debug_check_guards(xn_ctx* ctx);
 
 /* Library build identification: "xn_attn <version> sm_100a". */
 XN_API const char* xn_version(void);

@@ -190,3 +190,19 @@ def test_stream_placement_policy():
     assert max(tokens) - min(tokens) <= 4096
     rr_tokens = [int(lens[r::8].sum()) for r in range(8)]
     assert (max(tokens) / (sum(tokens) / 8)) < (max(rr_tokens) / (sum(rr_tokens) / 8))
+
+
+def test_bounds_checking_build_compiles(repo_root, tmp_path):
+    """The opt-in -DXN_BOUNDS build (copy producers range-check page ids and report kDevBadIndex
+    instead of issuing the copy) compiles for sm_100a and exports the same symbols."""
+    import subprocess
+
+    from xor_net_b200 import _build
+
+    out = str(tmp_path / "libxn_attn_bounds.so")
+    cmd = [_build._nvcc(), *_build.NVCC_FLAGS, "-DXN_BOUNDS", "-I", _build.INCLUDE, "-o", out, *_build.sources()]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    assert res.returncode == 0, res.stdout + res.stderr
+    lib = C.CDLL(out)
+    for name in header_symbols(repo_root):
+        assert hasattr(lib, name)

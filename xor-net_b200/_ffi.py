@@ -57,7 +57,7 @@ PLACE_LEAST_LOADED, PLACE_ROUND_ROBIN = 0, 1
 STATUS_NAMES = {
     0: "XN_OK", 1: "XN_ERR_ARG", 2: "XN_ERR_SHAPE", 3: "XN_ERR_HANDLE", 4: "XN_ERR_OUT_OF_PAGES",
     5: "XN_ERR_CAPACITY", 6: "XN_ERR_CUDA", 7: "XN_ERR_DEVICE_WAIT", 8: "XN_ERR_NO_TABLES",
-    9: "XN_ERR_NOMEM", 10: "XN_ERR_NO_DEVICE",
+    9: "XN_ERR_NOMEM", 10: "XN_ERR_NO_DEVICE", 11: "XN_ERR_GUARD",
 }
 
 # symbol -> (restype, argtypes); must list every XN_API function of include/xn_attn.h
@@ -98,6 +98,7 @@ SIGNATURES = {
     "xn_plan_split": (C.c_int32, [C.c_int32, c_i32p, C.c_int32, C.c_int32, C.c_int32, c_i32p,
                                   c_i32p, c_i32p, c_i32p, c_i32p, c_i32p, c_i32p]),
     "xn_debug_expire_wait": (C.c_int32, [C.c_void_p, C.c_int32]),
+    "xn_debug_check_guards": (C.c_int32, [C.c_void_p]),
     "xn_profile_read_all": (C.c_int32, [C.c_void_p, C.POINTER(C.c_double), C.POINTER(C.c_uint64)]),
     "xn_qkv_proj_set": (C.c_int32, [C.c_void_p, C.POINTER(QkvProjDesc)]),
     "xn_out_proj_set": (C.c_int32, [C.c_void_p, C.POINTER(OutProjDesc)]),

@@ -180,9 +180,20 @@ class Context:
         if rc != 0:
             raise XnError(rc, (self.lib.xn_last_error(self.handle) or b"").decode())
 
-    def close(self):
+    def check_guards(self):
+        """xn_debug_check_guards: raises if a kernel wrote outside one of the context's device buffers."""
+        self._check(self.lib.xn_debug_check_guards(self.handle))
+
+    def close(self, check_guards: bool = True):
+        """Destroys the context.  The guard areas around its device buffers are verified first (a
+        few small copies), so that every test that closes its context also checks memory safety."""
         if getattr(self, "handle", None) and self._owner is None:
+            rc = self.lib.xn_debug_check_guards(self.handle) if check_guards else 0
+            text = (self.lib.xn_last_error(self.handle) or b"").decode() if rc else ""
             self.lib.xn_ctx_destroy(self.handle)
+            self.handle = None
+            if rc == 11:
+                raise XnError(rc, text)
         self.handle = None
 
     def __del__(self):
@@ -421,6 +432,9 @@ class Group:
 
     def close(self):
         if getattr(self, "handle", None):
+            for c in self.contexts:
+                if c.handle:
+                    c.check_guards()
             self.lib.xn_group_destroy(self.handle)
             for c in self.contexts:
                 c.handle = None

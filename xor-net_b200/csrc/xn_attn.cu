@@ -176,6 +176,13 @@ struct xn_ctx {
     // directly (they only ever write it when a wait ran out), so reading it needs no copy.
     int* status_d = nullptr;  // device-side address of the same word
     int* status_h = nullptr;
+    // every device buffer of the context sits between two 256-byte guard areas (see guarded_malloc)
+    struct GuardRec {
+        unsigned char* user;
+        size_t bytes;       // rounded up to 256
+        const char* name;
+    };
+    std::vector<GuardRec> guards;
     xn_stats stats{};
     std::mutex err_mu;       // guards last_error only: readers never wait for a submission
     std::string last_error;
@@ -231,6 +238,41 @@ bool stream_ok(const xn_ctx* c, const xn_stream* s) {
 }
 
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// ---- guarded device allocations -----------------------------------------------------------
+// compute-sanitizer is not always available where this library runs, and the kernels do raw
+// pointer arithmetic from host-built descriptors.  Every device buffer of a context is therefore
+// allocated with 256 bytes of a known pattern before and behind it; xn_debug_check_guards reads
+// the patterns back and names the buffer whose neighbourhood was written.
+constexpr size_t kGuardBytes = 256;
+constexpr int kGuardByte = 0xA5;
+
+cudaError_t guarded_malloc(xn_ctx* c, void** out, size_t bytes, const char* name) {
+    *out = nullptr;
+    const size_t body = align_up(std::max<size_t>(bytes, 1), kGuardBytes);
+    unsigned char* base = nullptr;
+    cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&base), body + 2 * kGuardBytes);
+    if (e != cudaSuccess) return e;
+    e = cudaMemset(base, kGuardByte, kGuardBytes);
+    if (e == cudaSuccess) e = cudaMemset(base + kGuardBytes + body, kGuardByte, kGuardBytes);
+    if (e != cudaSuccess) {
+        cudaFree(base);
+        return e;
+    }
+    c->guards.push_back({base + kGuardBytes, body, name});
+    *out = base + kGuardBytes;
+    return cudaSuccess;
+}
+
+cudaError_t guarded_free(xn_ctx* c, void* user) {
+    if (!user) return cudaSuccess;
+    for (size_t i = 0; i < c->guards.size(); ++i)
+        if (c->guards[i].user == user) {
+            c->guards.erase(c->guards.begin() + long(i));
+            return cudaFree(static_cast<unsigned char*>(user) - kGuardBytes);
+        }
+    return cudaFree(user);   // not one of ours (never happens): free it as it is
+}
 
 // ---- kernel dispatch table ---------------------------------------------------------------
 
@@ -376,12 +418,12 @@ bool make_map_f32(CUtensorMap* map, const void* base, int rank, const cuuint64_t
 int32_t grow_device(xn_ctx* c, float** buf, size_t* cap, size_t need_floats) {
     if (need_floats <= *cap) return XN_OK;
     XN_CUDA(c, cudaStreamSynchronize(c->stream));  // nothing in flight may still use the old one
-    if (*buf) XN_CUDA(c, cudaFree(*buf));
+    if (*buf) XN_CUDA(c, guarded_free(c, *buf));
     *buf = nullptr;
     *cap = 0;
     size_t want = std::max(need_floats, size_t(1) << 18);
     want = align_up(want + want / 4, 1024);
-    XN_CUDA(c, cudaMalloc(reinterpret_cast<void**>(buf), want * sizeof(float)));
+    XN_CUDA(c, guarded_malloc(c, reinterpret_cast<void**>(buf), want * sizeof(float), "workspace"));
     *cap = want;
     return XN_OK;
 }
@@ -390,12 +432,12 @@ int32_t grow_io(xn_ctx* c, size_t need_bytes) {
     if (need_bytes <= c->io_cap) return XN_OK;
     XN_CUDA(c, cudaStreamSynchronize(c->stream));
     if (c->io_host) XN_CUDA(c, cudaFreeHost(c->io_host));
-    if (c->io_dev) XN_CUDA(c, cudaFree(c->io_dev));
+    if (c->io_dev) XN_CUDA(c, guarded_free(c, c->io_dev));
     c->io_host = c->io_dev = nullptr;
     c->io_cap = 0;
     size_t want = align_up(std::max(need_bytes + need_bytes / 4, size_t(1) << 20), 4096);
     XN_CUDA(c, cudaMallocHost(reinterpret_cast<void**>(&c->io_host), want));
-    XN_CUDA(c, cudaMalloc(reinterpret_cast<void**>(&c->io_dev), want));
+    XN_CUDA(c, guarded_malloc(c, reinterpret_cast<void**>(&c->io_dev), want, "staging"));
     c->io_cap = want;
     return XN_OK;
 }
@@ -407,12 +449,12 @@ int32_t acquire_slot(xn_ctx* c, size_t need_bytes, PlanSlot** out) {
     s.used = false;
     if (need_bytes > s.cap) {
         if (s.host) XN_CUDA(c, cudaFreeHost(s.host));
-        if (s.dev) XN_CUDA(c, cudaFree(s.dev));
+        if (s.dev) XN_CUDA(c, guarded_free(c, s.dev));
         s.host = s.dev = nullptr;
         s.cap = 0;
         size_t want = align_up(std::max(need_bytes * 2, size_t(1) << 16), 4096);
         XN_CUDA(c, cudaMallocHost(reinterpret_cast<void**>(&s.host), want));
-        XN_CUDA(c, cudaMalloc(reinterpret_cast<void**>(&s.dev), want));
+        XN_CUDA(c, guarded_malloc(c, reinterpret_cast<void**>(&s.dev), want, "plan"));
         s.cap = want;
     }
     if (!s.ev) XN_CUDA(c, cudaEventCreateWithFlags(&s.ev, cudaEventDisableTiming));
@@ -556,22 +598,22 @@ int32_t launch_out_block(xn_ctx* c, const OutProj& op, const OutRowDev* rows_d, 
 int32_t ensure_stage(xn_ctx* c, long long pages) {
     if (pages <= c->stage_pages) return XN_OK;
     XN_CUDA(c, cudaStreamSynchronize(c->stream));  // nothing in flight may still use the old area
-    if (c->k_stage) cudaFree(c->k_stage);
-    if (c->v_stage) cudaFree(c->v_stage);
-    if (c->stage_ident_d) cudaFree(c->stage_ident_d);
+    guarded_free(c, c->k_stage);
+    guarded_free(c, c->v_stage);
+    guarded_free(c, c->stage_ident_d);
     const long long np = std::max<long long>({pages, 2 * c->stage_pages, 32});
     c->k_stage = c->v_stage = nullptr;
     c->stage_ident_d = nullptr;
     c->stage_pages = 0;
     const size_t rows = size_t(np) * c->num_kv_heads * kPageTokens;
     const size_t bytes = rows * size_t(c->head_dim) * 4;
-    XN_CUDA(c, cudaMalloc(reinterpret_cast<void**>(&c->k_stage), bytes));
-    XN_CUDA(c, cudaMalloc(reinterpret_cast<void**>(&c->v_stage), bytes));
+    XN_CUDA(c, guarded_malloc(c, reinterpret_cast<void**>(&c->k_stage), bytes, "k_stage"));
+    XN_CUDA(c, guarded_malloc(c, reinterpret_cast<void**>(&c->v_stage), bytes, "v_stage"));
     XN_CUDA(c, cudaMemset(c->k_stage, 0, bytes));
     XN_CUDA(c, cudaMemset(c->v_stage, 0, bytes));
     std::vector<int32_t> ident(size_t(np), 0);
     for (long long i = 0; i < np; ++i) ident[size_t(i)] = int32_t(i);
-    XN_CUDA(c, cudaMalloc(reinterpret_cast<void**>(&c->stage_ident_d), size_t(np) * 4));
+    XN_CUDA(c, guarded_malloc(c, reinterpret_cast<void**>(&c->stage_ident_d), size_t(np) * 4, "stage page table"));
     XN_CUDA(c, cudaMemcpy(c->stage_ident_d, ident.data(), size_t(np) * 4, cudaMemcpyHostToDevice));
     const cuuint64_t dims[2] = {cuuint64_t(c->head_dim), cuuint64_t(rows)};
     const cuuint64_t str[1] = {cuuint64_t(c->head_dim) * 4};
@@ -1072,6 +1114,7 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         pa.o_hs = d.o_hs;
         pa.o_ts = d.o_ts;
         pa.layer_page_base = c->kv_u8 ? 0 : (long long)d.layer * c->pool_pages;
+        pa.pool_pages = c->kv_u8 ? c->stage_pages : c->pool_pages;
         pa.num_kv_heads = Hkv;
         pa.group = c->group;
         pa.seq_len = d.seq_len;
@@ -1430,28 +1473,28 @@ int32_t xn_ctx_create(const xn_ctx_desc* d, xn_ctx** out_ctx) {
     XN_CREATE_CUDA(cudaStreamCreateWithFlags(&c->copy_stream, cudaStreamNonBlocking));
     if (c->kv_u8) {
         const long long n_blocks = pages * d->num_layers * d->num_kv_heads;
-        XN_CREATE_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->pool8), size_t(n_blocks) * kv8::block_bytes(c->dq)));
+        XN_CREATE_CUDA(guarded_malloc(c, reinterpret_cast<void**>(&c->pool8), size_t(n_blocks) * kv8::block_bytes(c->dq), "pool8"));
         // every slot starts as the reference's shadow does: byte 128, scale 0.0
         kv8::pool_init_u8_kernel<<<unsigned(std::min<long long>(n_blocks, 4096)), 256, 0, c->stream>>>(
             c->pool8, n_blocks, c->dq);
         XN_CREATE_CUDA(cudaGetLastError());
     } else {
         const size_t pool_floats = size_t(pages) * d->num_layers * d->num_kv_heads * kPageTokens * c->nv * 4;
-        XN_CREATE_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->k_pool), pool_floats * 4));
-        XN_CREATE_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->v_pool), pool_floats * 4));
+        XN_CREATE_CUDA(guarded_malloc(c, reinterpret_cast<void**>(&c->k_pool), pool_floats * 4, "k_pool"));
+        XN_CREATE_CUDA(guarded_malloc(c, reinterpret_cast<void**>(&c->v_pool), pool_floats * 4, "v_pool"));
         // Row padding (head_dim rounded up to 4 floats) must hold zeros for the lifetime of the pool.
         XN_CREATE_CUDA(cudaMemsetAsync(c->k_pool, 0, pool_floats * 4, c->stream));
         XN_CREATE_CUDA(cudaMemsetAsync(c->v_pool, 0, pool_floats * 4, c->stream));
     }
     if (d->rope_cos) {
         const size_t tb = size_t(d->max_pos) * (d->head_dim / 2) * 4;
-        XN_CREATE_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->cos_d), std::max<size_t>(tb, 16)));
-        XN_CREATE_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->sin_d), std::max<size_t>(tb, 16)));
+        XN_CREATE_CUDA(guarded_malloc(c, reinterpret_cast<void**>(&c->cos_d), std::max<size_t>(tb, 16), "cos table"));
+        XN_CREATE_CUDA(guarded_malloc(c, reinterpret_cast<void**>(&c->sin_d), std::max<size_t>(tb, 16), "sin table"));
         XN_CREATE_CUDA(cudaMemcpyAsync(c->cos_d, d->rope_cos, tb, cudaMemcpyHostToDevice, c->stream));
         XN_CREATE_CUDA(cudaMemcpyAsync(c->sin_d, d->rope_sin, tb, cudaMemcpyHostToDevice, c->stream));
     }
     c->sync_cap = size_t(c->decode_chunks) + 8;  // a unit is cut at most once per chunk boundary
-    XN_CREATE_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->sync_d), c->sync_cap * sizeof(int)));
+    XN_CREATE_CUDA(guarded_malloc(c, reinterpret_cast<void**>(&c->sync_d), c->sync_cap * sizeof(int), "arrival counters"));
     XN_CREATE_CUDA(cudaMemsetAsync(c->sync_d, 0, c->sync_cap * sizeof(int), c->stream));
     XN_CREATE_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&c->status_h), sizeof(int), cudaHostAllocMapped));
     *c->status_h = kDevOk;
@@ -1531,34 +1574,34 @@ int32_t xn_ctx_destroy(xn_ctx* c) {
     c->streams.clear();
     for (PlanSlot& s : c->slots) {
         if (s.host) cudaFreeHost(s.host);
-        if (s.dev) cudaFree(s.dev);
+        guarded_free(c, s.dev);
         if (s.ev) cudaEventDestroy(s.ev);
         if (s.up_ev) cudaEventDestroy(s.up_ev);
     }
     for (cudaEvent_t e : c->prof_events) cudaEventDestroy(e);
     for (std::vector<OutProj>* v : {&c->out_proj, &c->qkv_proj})
         for (OutProj& op : *v) {
-            if (op.w2) cudaFree(op.w2);
-            if (op.w_scales) cudaFree(op.w_scales);
-            if (op.norm_w) cudaFree(op.norm_w);
+            guarded_free(c, op.w2);
+            guarded_free(c, op.w_scales);
+            guarded_free(c, op.norm_w);
         }
-    if (c->qkv_seq) cudaFree(c->qkv_seq);
-    if (c->attn_seq) cudaFree(c->attn_seq);
-    if (c->q8) cudaFree(c->q8);
-    if (c->q_rot) cudaFree(c->q_rot);
-    if (c->partials) cudaFree(c->partials);
+    guarded_free(c, c->qkv_seq);
+    guarded_free(c, c->attn_seq);
+    guarded_free(c, c->q8);
+    guarded_free(c, c->q_rot);
+    guarded_free(c, c->partials);
     if (c->io_host) cudaFreeHost(c->io_host);
-    if (c->io_dev) cudaFree(c->io_dev);
-    if (c->sync_d) cudaFree(c->sync_d);
+    guarded_free(c, c->io_dev);
+    guarded_free(c, c->sync_d);
     if (c->status_h) cudaFreeHost(c->status_h);
-    if (c->cos_d) cudaFree(c->cos_d);
-    if (c->sin_d) cudaFree(c->sin_d);
-    if (c->k_pool) cudaFree(c->k_pool);
-    if (c->v_pool) cudaFree(c->v_pool);
-    if (c->pool8) cudaFree(c->pool8);
-    if (c->k_stage) cudaFree(c->k_stage);
-    if (c->v_stage) cudaFree(c->v_stage);
-    if (c->stage_ident_d) cudaFree(c->stage_ident_d);
+    guarded_free(c, c->cos_d);
+    guarded_free(c, c->sin_d);
+    guarded_free(c, c->k_pool);
+    guarded_free(c, c->v_pool);
+    guarded_free(c, c->pool8);
+    guarded_free(c, c->k_stage);
+    guarded_free(c, c->v_stage);
+    guarded_free(c, c->stage_ident_d);
     if (c->copy_stream) cudaStreamDestroy(c->copy_stream);
     if (c->own_stream && c->stream) cudaStreamDestroy(c->stream);
     c->magic = 0;
@@ -2123,7 +2166,7 @@ int32_t install_linear(xn_ctx* c, OutProj* slot, int in_dim, int pack_type, cons
         }
     }
     auto upload = [&](void** dst, const void* src, size_t bytes) -> cudaError_t {
-        cudaError_t e = cudaMalloc(dst, bytes);
+        cudaError_t e = guarded_malloc(c, dst, bytes, "projection weights");
         if (e != cudaSuccess) return e;
         return cudaMemcpy(*dst, src, bytes, cudaMemcpyHostToDevice);
     };
@@ -2145,14 +2188,14 @@ int32_t install_linear(xn_ctx* c, OutProj* slot, int in_dim, int pack_type, cons
                                  cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  int(align_up(size_t(in_dim), 4) * 12));
     if (e != cudaSuccess) {
-        if (op.w2) cudaFree(op.w2);
-        if (op.w_scales) cudaFree(op.w_scales);
-        if (op.norm_w) cudaFree(op.norm_w);
+        guarded_free(c, op.w2);
+        guarded_free(c, op.w_scales);
+        guarded_free(c, op.norm_w);
         return fail(c, XN_ERR_CUDA, "uploading the weights failed: %s", cudaGetErrorString(e));
     }
-    if (slot->w2) cudaFree(slot->w2);
-    if (slot->w_scales) cudaFree(slot->w_scales);
-    if (slot->norm_w) cudaFree(slot->norm_w);
+    guarded_free(c, slot->w2);
+    guarded_free(c, slot->w_scales);
+    guarded_free(c, slot->norm_w);
     op.set = true;
     *slot = op;
     return XN_OK;
@@ -2269,6 +2312,23 @@ int32_t xn_debug_expire_wait(xn_ctx* c, int32_t timeout_ms) {
     XN_CUDA(c, cudaGetLastError());
     XN_CUDA(c, cudaStreamSynchronize(c->stream));
     return check_device_status(c);
+}
+
+int32_t xn_debug_check_guards(xn_ctx* c) {
+    if (!ctx_ok(c)) return XN_ERR_HANDLE;
+    std::lock_guard<std::mutex> g(c->mu);
+    XN_CUDA(c, cudaSetDevice(c->device));
+    XN_CUDA(c, cudaStreamSynchronize(c->stream));
+    unsigned char host[2 * kGuardBytes];
+    for (const xn_ctx::GuardRec& r : c->guards) {
+        XN_CUDA(c, cudaMemcpy(host, r.user - kGuardBytes, kGuardBytes, cudaMemcpyDeviceToHost));
+        XN_CUDA(c, cudaMemcpy(host + kGuardBytes, r.user + r.bytes, kGuardBytes, cudaMemcpyDeviceToHost));
+        for (size_t i = 0; i < 2 * kGuardBytes; ++i)
+            if (host[i] != kGuardByte)
+                return fail(c, XN_ERR_GUARD, "a kernel wrote %s the device buffer '%s' (%zu bytes): guard byte %zu is 0x%02x",
+                            i < kGuardBytes ? "in front of" : "behind", r.name, r.bytes, i % kGuardBytes, host[i]);
+    }
+    return XN_OK;
 }
 
 int32_t xn_plan_split(int32_t n_units, const int32_t* kv_len, int32_t tile_tokens, int32_t max_ctas,

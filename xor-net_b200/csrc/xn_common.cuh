@@ -17,6 +17,16 @@ __device__ __forceinline__ void report_status(int* status, int code) {
     __threadfence_system();
 }
 
+// Opt-in build (-DXN_BOUNDS) in which the copy producers range-check every page id they take
+// from a host-built table: a bad one is reported through the status word (kDevBadIndex) and its
+// copy is not issued -- the kernel gives up and returns, it never traps.  The default build trusts
+// the planner.
+#ifdef XN_BOUNDS
+#define XN_PAGE_OK(page, pool_pages) ((page) >= 0 && (long long)(page) < (long long)(pool_pages))
+#else
+#define XN_PAGE_OK(page, pool_pages) true
+#endif
+
 // ---- plan structures (built on the host per batch, copied once to the device) ---------------
 
 // One attention request as the kernels see it.  Strides are in floats.

@@ -306,6 +306,10 @@ attn_splitkv_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restrict__
                                     report_status(status, kDevWaitEmpty);
                                     *abort_flag = 1;
                                     ok = false;
+                                } else if (!XN_PAGE_OK(page, pool_pages)) {
+                                    report_status(status, kDevBadIndex);
+                                    *abort_flag = 1;
+                                    ok = false;
                                 } else {
                                     const int tok0 = tile * TPS;
                                     const int ntok = min(TPS, kv_len - tok0);

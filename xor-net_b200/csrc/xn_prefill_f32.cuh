@@ -84,6 +84,12 @@ prefill_f32_kernel(const ReqDev* __restrict__ reqs, const F32Item* __restrict__ 
     __syncthreads();
     auto issue = [&](int j) {   // K and V tile j -> stage j & 1 (thread 0)
         const int page = pages[j / kTilesPerPage];
+        if (!XN_PAGE_OK(page, pool_pages)) {   // bounds-checking build: report, skip the copy, give up
+            report_status(status, kDevBadIndex);
+            abort_s = 1;
+            mbar_arrive(&full[j & 1]);         // nothing will fill the stage: let the waiters through
+            return;
+        }
         const size_t off = ((size_t(r.layer) * size_t(pool_pages) + size_t(page)) * num_kv_heads + h_kv) * page_floats +
                            size_t(j % kTilesPerPage) * TK * dp;
         float* dst = kv_s + size_t(j & 1) * 2 * TK * dp;
@@ -118,7 +124,10 @@ prefill_f32_kernel(const ReqDev* __restrict__ reqs, const F32Item* __restrict__ 
     const int pos0 = r.index_pos + t0 + row0; // position of its first row
 
     for (int j = 0; j < n_tiles; ++j) {
-        if (!mbar_wait_bounded(&full[j & 1], uint32_t((j >> 1) & 1))) abort_s = 1;
+        if (!mbar_wait_bounded(&full[j & 1], uint32_t((j >> 1) & 1))) {
+            abort_s = 1;
+            report_status(status, kDevWaitFull);
+        }
         __syncthreads();
         if (abort_s) break;
         const float* k_t = kv_s + size_t(j & 1) * 2 * TK * dp;
@@ -212,10 +221,7 @@ prefill_f32_kernel(const ReqDev* __restrict__ reqs, const F32Item* __restrict__ 
         __syncthreads();   // every thread is done with this stage and with the P tile
         if (tid == 0 && j + 2 < n_tiles) issue(j + 2);
     }
-    if (abort_s) {
-        if (tid == 0) report_status(status, kDevWaitFull);
-        return;
-    }
+    if (abort_s) return;   // the cause is in the status word already
     // ---- O / l -> out
 #pragma unroll
     for (int i = 0; i < 4; ++i) {

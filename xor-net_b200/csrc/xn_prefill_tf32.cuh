@@ -40,6 +40,7 @@ struct PrefillArgs {
     float* out;           // output base
     long long o_hs, o_ts; // output head / token strides in floats
     long long layer_page_base;  // layer * pool_pages
+    long long pool_pages;       // pages per layer (the bounds-checking build checks page ids against it)
     int num_kv_heads;
     int group;            // query heads per KV head
     int seq_len;          // S
@@ -255,16 +256,21 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap k_map,
         // V pages of tile j.
         if (lane == 0) {
             pdl_wait();   // the pages (and the page table) are written before this kernel: wait for the append
+            bool bad_page = false;   // bounds-checking build only
             auto page_row = [&](int pg) -> int {
+                if (!XN_PAGE_OK(a.pages[pg], a.pool_pages)) { bad_page = true; return -1; }
                 return int(((a.layer_page_base + a.pages[pg]) * a.num_kv_heads + h_kv) * kPage);
             };
             auto load_k_tile = [&](int j) -> bool {
                 const int st = j % kKStages;
                 if (j >= kKStages && !mbar_wait_bounded(&k_empty[st], uint32_t((j / kKStages - 1) & 1))) return false;
                 const int np = min(2, n_pages - 2 * j);
+                int rows[2] = {0, 0};
+                for (int p = 0; p < np; ++p) rows[p] = page_row(2 * j + p);
+                if (bad_page) return false;   // before any byte count is armed: nothing is in flight
                 mbar_arrive_expect_tx(&k_full[st], uint32_t(np * n_kb) * kVSub);
                 for (int p = 0; p < np; ++p) {
-                    const int row = page_row(2 * j + p);
+                    const int row = rows[p];
                     for (int kb = 0; kb < n_kb; ++kb)
                         tma_load_2d(k_s + st * kKBytes + kb * kKSub + p * kVSub, &k_map, kb * 32, row, &k_full[st]);
                 }
@@ -274,6 +280,7 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap k_map,
                 const int st = pg % kVStages;
                 if (pg >= kVStages && !mbar_wait_bounded(&v_empty[st], uint32_t((pg / kVStages - 1) & 1))) return false;
                 const int row = page_row(pg);
+                if (bad_page) return false;
                 mbar_arrive_expect_tx(&v_full[st], uint32_t(n_kb) * kVSub);
                 for (int kb = 0; kb < n_kb; ++kb)
                     tma_load_2d(v_s + st * kVBytes + kb * kVSub, &v_map, kb * 32, row, &v_full[st]);
@@ -285,7 +292,7 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap k_map,
                 for (int p = 2 * j; p < min(2 * j + 2, n_pages) && ok; ++p) ok = load_v_page(p);
                 if (*abort_flag) break;
             }
-            if (!ok) { report_status(a.status, kDevWaitEmpty); *abort_flag = 1; }
+            if (!ok) { report_status(a.status, bad_page ? kDevBadIndex : kDevWaitEmpty); *abort_flag = 1; }
         }
     } else if (warp == 1) {
         // =============================== MMA issuer ===============================
