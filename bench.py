@@ -453,7 +453,8 @@ def run_prefill_arm(args):
     wall0 = time.time()
     u8 = args.kv == "u8"
     r = measure_prefill(xn, torch, tstream, local_rank, S, 20, 5, 128, 500000.0, args.steps, args.warmup, u8=u8,
-                        index_pos=args.pos, chunk=args.chunk, min_seconds=args.min_seconds)
+                        index_pos=args.pos, chunk=args.chunk, min_seconds=args.min_seconds,
+                        prefill_mode=1 if args.f32 else 0)
     wall1 = time.time()
     clocks = sampler.stop(wall0, wall1) if sampler else None
     if rank != 0:
@@ -466,6 +467,7 @@ def run_prefill_arm(args):
         "data": "synthetic",
         "config": {"workload": f"c2: causal GQA prefill, BitNet-2B shape, {S} tokens, 20/5 heads, "
                                "head_dim 128, fused RoPE theta 5e5 + append into 64-token pages" +
+                               (" [exact-f32 path: tiled CUDA-core kernel]" if args.f32 else "") +
                                (f", behind {args.pos} cached tokens" if args.pos else "") +
                                (f", in chunks of {args.chunk} rows" if args.chunk else "") +
                                (" [opt-in u8 cache format: quantised append, pages dequantised into an f32 "
@@ -476,7 +478,8 @@ def run_prefill_arm(args):
                 "h2d_bytes_per_step": r.get("e2e_h2d_bytes"), "d2h_bytes_per_step": r.get("e2e_d2h_bytes"),
                 "ms_per_step": r.get("e2e_ms")},
         "gpu_launches": r["launches_per_step"] * args.steps,
-        "roofline": {"bound": "tensor", "kernel": "prefill_tf32_kernel", "achieved": r["kernel_tflops"],
+        "roofline": {"bound": "tensor", "kernel": "prefill_f32_kernel (CUDA cores)" if args.f32 else "prefill_tf32_kernel",
+                     "achieved": r["kernel_tflops"],
                      "peak": peak, "unit": "TFLOP/s", "frac": r["kernel_tflops"] / peak,
                      "peak_source": peak_kind, "traffic": None, "avg_launch_ms": r["kernel_ms"],
                      "algorithmic_flops_per_launch": r["flops"],
@@ -1142,6 +1145,7 @@ def main():
     ap.add_argument("--seq", type=int, default=0, help="prefill length for --workload c2")
     ap.add_argument("--min-seconds", type=float, default=0.5,
                     help="keep repeating the timed bracket until it has covered this much device time")
+    ap.add_argument("--f32", action="store_true", help="c2: the exact-f32 prefill path (XN_PREFILL_F32)")
     ap.add_argument("--pos", type=int, default=0, help="c2: cached tokens in front of the prefill (index_pos)")
     ap.add_argument("--chunk", type=int, default=0, help="c2: feed the prefill in chunks of this many rows")
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (profiling)")
