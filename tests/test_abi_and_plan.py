@@ -206,3 +206,23 @@ def test_bounds_checking_build_compiles(repo_root, tmp_path):
     lib = C.CDLL(out)
     for name in header_symbols(repo_root):
         assert hasattr(lib, name)
+
+
+def test_rust_binding_source_agrees_with_the_header(repo_root):
+    """The Rust crate cannot be compiled where no Rust toolchain exists, so its declarations are
+    checked as text: every extern it names is declared in the header, the counters struct lists
+    the header's fields in the header's order, and the binding goes through the device group (no
+    fixed device ordinal, no pool sized from a sequence length)."""
+    src = open(os.path.join(repo_root, "xor-net_b200", "rust", "xor-net-attn", "src", "lib.rs")).read()
+    hdr = open(os.path.join(repo_root, "include", "xn_attn.h")).read()
+    declared = set(re.findall(r"XN_API\s+[\w\s\*]+?\b(xn_\w+)\s*\(", hdr))
+    named = set(re.findall(r"\bfn (xn_\w+)\s*\(", src))
+    assert named and named <= declared, sorted(named - declared)
+    for must in ("xn_attention_rope", "xn_stream_reset", "xn_stats_get", "xn_ctx_synchronize",
+                 "xn_group_create", "xn_group_stream_create", "xn_debug_check_guards"):
+        assert must in named, must
+    h_fields = re.findall(r"uint64_t (\w+);", hdr[hdr.index("typedef struct xn_stats {"):hdr.index("} xn_stats;")])
+    r_fields = re.findall(r"pub (\w+): u64", src[src.index("pub struct XnStats {"):])[:len(h_fields)]
+    assert r_fields == h_fields
+    assert "impl Clone for DeviceKvCache" not in src and "NOT `Clone`" in src
+    assert "shared_context(0" not in src and "max_seq_len + 63" not in src
