@@ -138,3 +138,52 @@ def test_unaligned_device_tensors_fall_back_to_the_exact_path():
     want = xo.fast_attention(q, k, v, 0, 0, p.ref, 4, 2, 64)
     assert_parity(od[1:].cpu().numpy().reshape(q.shape), want, "unaligned device tensors")
     ctx.close()
+
+
+@pytest.mark.parametrize("Hq,Hkv,D,S,pos", [(20, 5, 128, 700, 0), (8, 2, 64, 333, 130), (4, 4, 128, 129, 64)])
+def test_query_rotation_inside_the_kernel_equals_the_rotation_scratch(Hq, Hkv, D, S, pos):
+    """For head_dim 64 / 128 the prefill kernel rotates the query rows itself (the append kernel
+    then moves K and V only).  Same arithmetic as the append kernel's rotation, so the result must
+    equal, bit for bit, the one computed from the rotated scratch copy (rotation in the kernel
+    switched off), for head-major and sequence-major rows, and stay within the TF32 bound of the
+    oracle (src/tensor.rs:295-316 applied before src/nn/fast_attention.rs:75)."""
+    import os
+    rng = np.random.default_rng(D + S)
+    cos, sin = xn.rope_tables(10000.0, D, 1024)
+    q, k, v = rand_qkv(rng, Hq, Hkv, S, D)
+    k0, v0 = rand_qkv(rng, Hq, Hkv, pos, D)[1:] if pos else (None, None)
+    outs, caches, launches = [], [], []
+    for flag in ("1", "0"):
+        os.environ["XORNET_ATTN_PREFILL_ROPE_Q"] = flag
+        try:
+            ctx = xn.Context(1, Hq, Hkv, D, pool_pages=24, shuffle_seed=9, rope=(cos, sin), prefill_mode=TF32)
+        finally:
+            del os.environ["XORNET_ATTN_PREFILL_ROPE_Q"]
+        for seq_major in (False, True):
+            st = ctx.new_stream(1024)
+            if pos:   # an earlier chunk, so that the rotation uses positions pos..pos+S-1
+                ctx.attention(st, 0, 0, rng.standard_normal((1, Hq, pos, D)).astype(np.float32), k0, v0, rope=True)
+            before = ctx.stats()["kernel_launches"]
+            if seq_major:
+                o = ctx.attention_batch([st], 0, [pos], [xo.transpose_heads_to_seq(q)],
+                                        [xo.transpose_heads_to_seq(k)], [xo.transpose_heads_to_seq(v)],
+                                        seq_major=True, rope=True)[0]
+                o = xo.transpose_seq_to_heads(o, Hq, D)
+            else:
+                o = ctx.attention(st, 0, pos, q, k, v, rope=True)
+            launches.append(ctx.stats()["kernel_launches"] - before)
+            outs.append(np.asarray(o).reshape(Hq, S, D))
+            caches.append(st.read_range(0, 0, pos + S))
+        ctx.close()
+    assert launches == [2, 2, 2, 2]           # append + prefill either way
+    assert np.array_equal(outs[0], outs[2]) and np.array_equal(outs[1], outs[3])
+    assert np.array_equal(outs[0], outs[1])
+    for kd, vd in caches[1:]:
+        assert np.array_equal(kd, caches[0][0]) and np.array_equal(vd, caches[0][1])
+    ref = xo.RingCache(1, Hkv, 1024, D)
+    if pos:
+        ref.append(0, 0, xo.tensor_rope(k0, cos, sin, 0)[0], v0[0])
+    want = xo.fast_attention(xo.tensor_rope(q, cos, sin, pos), xo.tensor_rope(k, cos, sin, pos), v, 0, pos,
+                             ref, Hq, Hkv, D)
+    check_tf32(outs[0], want[0], f"D={D} S={S} pos={pos}")
+    ref.close()

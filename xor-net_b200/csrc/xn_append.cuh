@@ -80,7 +80,9 @@ rope_append_kernel(const ReqDev* __restrict__ reqs, const int* __restrict__ page
     pdl_launch_dependents();   // a prefill kernel launched as a programmatic dependent may set up now
     const ReqDev& r = reqs[blockIdx.y];
     const bool rope = r.flags & 1u;
-    const bool q_rows = r.flags & 3u;  // q is rotated, or just moved next to the kernels
+    // q is rotated, or just moved next to the kernels -- unless the prefill kernel rotates the
+    // query rows itself (bit 4)
+    const bool q_rows = (r.flags & 3u) && !(r.flags & 16u);
     const int rows_per_tok = (q_rows ? num_heads : 0) + 2 * num_kv_heads;
     const long long n_rows = (long long)r.seq_len * rows_per_tok;
     const int hl = threadIdx.x & 15;         // lane inside the half-warp

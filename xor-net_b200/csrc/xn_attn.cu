@@ -49,6 +49,27 @@ struct PlanSlot {
     bool used = false;
 };
 
+// The plan of the last pure-decode submission, kept on the device.  The layers of one decode step
+// submit the same streams at the same positions one after another; only the tensors' addresses
+// and the layer differ, and those travel as a kernel parameter (ReqPatchTable).  A submission
+// that matches therefore skips planning and the plan upload altogether.
+struct PlanCache {
+    struct Entry {
+        xn_stream* stream;
+        int64_t index_pos;
+        uint32_t flags;
+        int n_pages;
+    };
+    bool valid = false;
+    bool host_mode = false, pinned = false;
+    PlanSlot* slot = nullptr;
+    std::vector<Entry> ent;
+    size_t o_req = 0, o_unit = 0, o_item = 0, o_cta = 0, o_page = 0;
+    int ctas = 0;
+    uint64_t h2d_bytes = 0, d2h_bytes = 0;   // what the kernel moves over PCIe itself (page-locked callers)
+    ReqPatchTable table;
+};
+
 // Output block of one layer on the device (xn_out_proj_set).
 struct OutProj {
     bool set = false;
@@ -124,6 +145,9 @@ struct xn_ctx {
     int decode_chunks = 0;   // chunks the tile list is cut into (several per block)
     bool fuse_append = true; // decode batches: the attention kernel appends the new token itself
     bool fuse_pinned = true; // ... also when q,k,v live in page-locked host memory
+    bool plan_reuse = true;  // a decode submission of the previous one's geometry reuses its plan
+    bool pf_rope_q = true;   // the tensor-core prefill kernel rotates the query rows itself
+    PlanCache pcache;
     size_t stage_direct_bytes = size_t(2) << 20;  // small staged calls: kernels use the pinned staging itself
     bool out_tc = true;      // output projection on the tensor cores (else the dp4a kernel)
     bool out_pdl = true;     // ... launched as a programmatic dependent of the quantiser kernel
@@ -278,7 +302,7 @@ cudaError_t guarded_free(xn_ctx* c, void* user) {
 
 using SplitFn = void (*)(const ReqDev*, const UnitDev*, const ItemDev*, const int*, int, const int*,
                          const float*, const float*, float*, int*, long long, int, int, int, float,
-                         const float*, const float*, int*);
+                         const float*, const float*, int*, const ReqPatchTable);
 
 struct SplitKernel {
     SplitFn fn;
@@ -443,6 +467,8 @@ int32_t grow_io(xn_ctx* c, size_t need_bytes) {
 }
 
 int32_t acquire_slot(xn_ctx* c, size_t need_bytes, PlanSlot** out) {
+    // the slot whose plan is kept for reuse stays out of the rotation while that plan is valid
+    if (c->pcache.valid && c->pcache.slot == &c->slots[c->next_slot]) c->next_slot = (c->next_slot + 1) % kPlanSlots;
     PlanSlot& s = c->slots[c->next_slot];
     c->next_slot = (c->next_slot + 1) % kPlanSlots;
     if (s.used) XN_CUDA(c, cudaEventSynchronize(s.ev));
@@ -482,6 +508,7 @@ void free_call_buffer(xn_stream* s) {
 }
 
 void release_pages(xn_ctx* c, xn_stream* s) {
+    c->pcache.valid = false;   // the kept plan may name this stream's pages
     for (auto it = s->pages.rbegin(); it != s->pages.rend(); ++it) c->free_pages.push_back(*it);
     s->pages.clear();
     std::fill(s->hw.begin(), s->hw.end(), 0);
@@ -673,6 +700,18 @@ bool use_tf32(const xn_ctx* c, const xn_req& r, bool direct) {
     return r.seq_len >= (c->prefill_mode == XN_PREFILL_TF32 ? 2 : c->tf32_min_rows);
 }
 
+// The tensor-core prefill kernel rotates the query rows itself (head_dim 64 / 128, rows it can read
+// as float4 from device memory): the append kernel then handles K and V only and no rotated copy
+// of q is written and read back.
+bool rope_in_prefill(const xn_ctx* c, const xn_req& r, bool direct, bool pinned) {
+    if (!c->pf_rope_q || c->kv_u8 || pinned) return false;
+    const bool qkv = r.flags & XN_REQ_QKV_PROJ;
+    if (!((r.flags & XN_REQ_ROPE) || qkv)) return false;
+    if (c->head_dim != 64 && c->head_dim != 128) return false;
+    if (direct && !qkv && (reinterpret_cast<uintptr_t>(r.q) & 15)) return false;
+    return use_tf32(c, r, direct);
+}
+
 // What a submission changes in its streams before its first launch (pages taken from the pool,
 // the per-layer high-water marks).  Unless commit() is called, the destructor puts every stream
 // back as it was, so a submission that fails on the way to its launches leaves no position
@@ -711,9 +750,75 @@ bool use_f32_tiled(const xn_ctx* c, const xn_req& r) {
 }
 
 // reqs[i] are valid, on distinct streams, all host-mode or all device-mode.
+// A decode submission with the geometry of the plan kept on the device: the same streams, in the
+// same order, at the same positions, one token each, all on one layer (any layer), nothing to
+// zero-fill.  Launches the attention kernel over the kept plan with this call's addresses and layer
+// as a kernel parameter.  Returns false when the submission does not match (nothing was touched).
+bool submit_reusing_plan(xn_ctx* c, int n, const xn_req* reqs, bool host_mode, int32_t* rc_out) {
+    PlanCache& pc = c->pcache;
+    if (!pc.valid || !c->plan_reuse || n != int(pc.ent.size()) || host_mode != pc.host_mode) return false;
+    const bool pinned = host_mode && (reqs[0].flags & XN_REQ_HOST_PINNED);
+    if (pinned != pc.pinned) return false;
+    const int layer = reqs[0].layer;
+    for (int i = 0; i < n; ++i) {
+        const xn_req& r = reqs[i];
+        const PlanCache::Entry& e = pc.ent[size_t(i)];
+        if (r.stream != e.stream || r.seq_len != 1 || r.index_pos != e.index_pos || r.flags != e.flags ||
+            r.layer != layer || int(r.stream->pages.size()) != e.n_pages ||
+            r.index_pos > r.stream->hw[size_t(layer)])
+            return false;
+        if ((reinterpret_cast<uintptr_t>(r.q) | reinterpret_cast<uintptr_t>(r.k) |
+             reinterpret_cast<uintptr_t>(r.v)) & 15)
+            return false;
+    }
+    auto run = [&]() -> int32_t {
+        ReqPatchTable& t = pc.table;
+        t.n = n;
+        t.layer = layer;
+        for (int i = 0; i < n; ++i) t.e[i] = {reqs[i].q, reqs[i].k, reqs[i].v, reqs[i].out};
+        const unsigned char* dev = pc.slot->dev;
+        int32_t rc;
+        SplitKernel k = pick_split(c->nv_class, c->gt, c->nv_exact);
+        if (c->profile && (rc = profile_begin(c, 0)) != XN_OK) return rc;
+        k.fn<<<std::min(pc.ctas, c->decode_ctas), k.threads, k.smem, c->stream>>>(
+            reinterpret_cast<const ReqDev*>(dev + pc.o_req), reinterpret_cast<const UnitDev*>(dev + pc.o_unit),
+            reinterpret_cast<const ItemDev*>(dev + pc.o_item), reinterpret_cast<const int*>(dev + pc.o_cta),
+            pc.ctas, reinterpret_cast<const int*>(dev + pc.o_page), c->k_pool, c->v_pool, c->partials,
+            c->sync_d, c->pool_pages, c->num_kv_heads, c->head_dim, c->nv, c->scale, c->cos_d, c->sin_d,
+            c->status_d, t);
+        t.n = 0;
+        XN_CUDA(c, cudaGetLastError());
+        if (c->profile && (rc = profile_end(c)) != XN_OK) return rc;
+        for (int i = 0; i < n; ++i) {
+            int64_t& hw = reqs[i].stream->hw[size_t(layer)];
+            hw = std::max(hw, reqs[i].index_pos + 1);
+        }
+        XN_CUDA(c, cudaEventRecord(pc.slot->ev, c->stream));
+        pc.slot->used = true;
+        c->stats.kernel_launches += 1;
+        c->stats.decode_launches += 1;
+        c->stats.batches += 1;
+        c->stats.calls += uint64_t(n);
+        c->stats.plan_reuses += 1;
+        c->stats.h2d_bytes += pc.h2d_bytes;
+        c->stats.d2h_bytes += pc.d2h_bytes;
+        if (host_mode) {
+            XN_CUDA(c, cudaStreamSynchronize(c->stream));
+            if ((rc = check_device_status(c)) != XN_OK) return rc;
+        }
+        return XN_OK;
+    };
+    *rc_out = run();
+    return true;
+}
+
 int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
     const int Hq = c->num_heads, Hkv = c->num_kv_heads, D = c->head_dim, nv = c->nv;
     XN_CUDA(c, cudaSetDevice(c->device));
+    {
+        int32_t rc;
+        if (n > 0 && submit_reusing_plan(c, n, reqs, host_mode, &rc)) return rc;
+    }
 
     // host memory that is page-locked and device-mapped is read and written by the kernels directly
     const bool pinned = host_mode && (reqs[0].flags & XN_REQ_HOST_PINNED);
@@ -764,7 +869,8 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
             io_in += qkv ? align_up(xf * 4, 16) : align_up(qf * 4, 16) + 2 * align_up(kvf * 4, 16);
             io_out += align_up(of * 4, 16);
         }
-        if ((r.flags & XN_REQ_ROPE) || pinned || qkv) qrot_floats += align_up(qf, 4);
+        if (((r.flags & XN_REQ_ROPE) || pinned || qkv) && !rope_in_prefill(c, r, direct, pinned))
+            qrot_floats += align_up(qf, 4);
         if (end > s->cap) n_ring_rows += r.seq_len;
         else if (use_tf32(c, r, direct)) {   // served by the tensor-core prefill kernel
             stage_need = std::max<long long>(stage_need, (end + kPageTokens - 1) / kPageTokens);
@@ -901,6 +1007,9 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         if (fused) {
             d.q = q_dev; d.q_hs = q_hs; d.q_ts = q_ts;
             d.flags = 8u | (rope ? 1u : 0u);
+        } else if (rope_in_prefill(c, r, direct, pinned)) {
+            d.q = q_dev; d.q_hs = q_hs; d.q_ts = q_ts;
+            d.flags = 1u | 16u;   // rotate k here, q in the prefill kernel
         } else if (rope || pinned) {
             d.q = c->q_rot + qrot_off;
             d.q_hs = (long long)S * D; d.q_ts = D;
@@ -1086,12 +1195,36 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         SplitKernel k = pick_split(c->nv_class, c->gt, c->nv_exact);
         if (c->profile && (rc = profile_begin(c, 0)) != XN_OK) return rc;
         // sp.ctas chunks, taken dynamically by at most one block per SM
+        c->pcache.table.n = 0;
         k.fn<<<std::min(sp.ctas, c->decode_ctas), k.threads, k.smem, c->stream>>>(
             reqs_d, units_d, items_d, cta_d, sp.ctas, pages_d, c->k_pool, c->v_pool, c->partials,
-            c->sync_d, c->pool_pages, Hkv, D, nv, c->scale, c->cos_d, c->sin_d, c->status_d);
+            c->sync_d, c->pool_pages, Hkv, D, nv, c->scale, c->cos_d, c->sin_d, c->status_d,
+            c->pcache.table);
         if (c->profile && (rc = profile_end(c)) != XN_OK) return rc;
         c->stats.kernel_launches += 1;
         c->stats.decode_launches += 1;
+        // Keep the plan when the whole submission was this one launch: one new token per request,
+        // appended by the kernel, tensors addressed directly (device or page-locked host memory).
+        PlanCache& pc = c->pcache;
+        pc.valid = false;
+        if (c->plan_reuse && fused && direct && n <= kPatchReqs && gaps.empty() && out_runs.empty() &&
+            qkv_runs.empty() && tf32_reqs.empty() && f32_items.empty() && ring_rows.empty()) {
+            pc.ent.resize(size_t(n));
+            bool all = true;
+            for (int i = 0; i < n && all; ++i) {
+                if (reqs[i].seq_len != 1) { all = false; break; }
+                pc.ent[size_t(i)] = {reqs[i].stream, reqs[i].index_pos, reqs[i].flags,
+                                     int(reqs[i].stream->pages.size())};
+            }
+            if (all) {
+                pc.valid = true;
+                pc.host_mode = host_mode; pc.pinned = pinned; pc.slot = slot;
+                pc.o_req = o_req; pc.o_unit = o_unit; pc.o_item = o_item; pc.o_cta = o_cta; pc.o_page = o_page;
+                pc.ctas = sp.ctas;
+                pc.h2d_bytes = pinned ? uint64_t(n) * size_t(Hq + 2 * Hkv) * D * 4 : 0;
+                pc.d2h_bytes = pinned ? uint64_t(n) * size_t(Hq) * D * 4 : 0;
+            }
+        }
     }
     if (!f32_items.empty()) {
         const PrefillF32Kernel pk = pick_prefill_f32(nv);
@@ -1109,6 +1242,9 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         pa.q = d.q;
         pa.q_hs = d.q_hs;
         pa.q_ts = d.q_ts;
+        pa.cos_t = c->cos_d;
+        pa.sin_t = c->sin_d;
+        pa.rope_q = (d.flags & 16u) ? 1 : 0;
         pa.pages = c->kv_u8 ? c->stage_ident_d : pages_d + d.page_off;
         pa.out = d.out;
         pa.o_hs = d.o_hs;
@@ -1420,6 +1556,8 @@ int32_t xn_ctx_create(const xn_ctx_desc* d, xn_ctx** out_ctx) {
     c->decode_chunks = c->decode_ctas * chunks_per_cta;
     if (const char* env = getenv("XORNET_ATTN_FUSE_APPEND")) c->fuse_append = atoi(env) != 0;
     if (const char* env = getenv("XORNET_ATTN_FUSE_PINNED")) c->fuse_pinned = atoi(env) != 0;
+    if (const char* env = getenv("XORNET_ATTN_PLAN_REUSE")) c->plan_reuse = atoi(env) != 0;
+    if (const char* env = getenv("XORNET_ATTN_PREFILL_ROPE_Q")) c->pf_rope_q = atoi(env) != 0;
     if (const char* env = getenv("XORNET_ATTN_STAGE_DIRECT_BYTES")) c->stage_direct_bytes = size_t(atoll(env));
     if (const char* env = getenv("XORNET_ATTN_OUTPROJ_TC")) c->out_tc = atoi(env) != 0;
     if (const char* env = getenv("XORNET_ATTN_OUTPROJ_PDL")) c->out_pdl = atoi(env) != 0;

@@ -48,8 +48,27 @@ struct ReqDev {
     int n_pages;
     unsigned flags;           // bit 0: rotate q and k with the context tables; bit 1: copy q
                               // (unrotated) into the scratch `q` points at; bit 3: one new
-                              // token, appended (and rotated) by the attention kernel itself
+                              // token, appended (and rotated) by the attention kernel itself;
+                              // bit 4: the prefill kernel rotates the query rows (the append
+                              // kernel leaves them alone)
     int pad;
+};
+
+// What differs between two decode submissions of the same geometry (the same streams at the same
+// positions, e.g. the layers of one decode step): the tensors' addresses and the layer.  Passed as
+// a kernel parameter, it lets a launch reuse the plan the previous submission left on the device.
+constexpr int kPatchReqs = 64;
+struct ReqPatch {
+    const float* q;
+    const float* k;
+    const float* v;
+    float* out;
+};
+struct ReqPatchTable {
+    int n;        // 0: the request descriptors are used as they are
+    int layer;
+    long long pad;
+    ReqPatch e[kPatchReqs];
 };
 
 // A (request, KV head, query-head subgroup, query row) to attend over kv_len cached tokens.

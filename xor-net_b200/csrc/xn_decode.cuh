@@ -181,7 +181,7 @@ attn_splitkv_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restrict__
                     float* __restrict__ partials, int* __restrict__ sync, long long pool_pages,
                     int num_kv_heads, int head_dim, int nv_arg, float scale,
                     const float* __restrict__ cos_t, const float* __restrict__ sin_t,
-                    int* __restrict__ status) {
+                    int* __restrict__ status, const __grid_constant__ ReqPatchTable patch) {
     const int nv = EXACT ? NV : nv_arg;
     using Cfg = DecodeCfg<NV>;
     using Sm = DecodeSmem<NV, GT>;
@@ -245,15 +245,22 @@ attn_splitkv_kernel(const ReqDev* __restrict__ reqs, const UnitDev* __restrict__
                     item = items[my_it];
                     u = units[item.unit];
                     const ReqDev& r = reqs[u.req];
-                    q_ptr = r.q + size_t(u.head0) * r.q_hs + size_t(u.t_q) * r.q_ts;
-                    o_ptr = r.out + size_t(u.head0) * r.o_hs + size_t(u.t_q) * r.o_ts;
+                    // a reused plan: addresses and layer come with the launch
+                    const bool patched = patch.n != 0;
+                    const float* rq = patched ? patch.e[u.req].q : r.q;
+                    const float* rk = patched ? patch.e[u.req].k : r.k;
+                    const float* rv = patched ? patch.e[u.req].v : r.v;
+                    float* ro = patched ? patch.e[u.req].out : r.out;
+                    const int rlayer = patched ? patch.layer : r.layer;
+                    q_ptr = rq + size_t(u.head0) * r.q_hs + size_t(u.t_q) * r.q_ts;
+                    o_ptr = ro + size_t(u.head0) * r.o_hs + size_t(u.t_q) * r.o_ts;
                     q_hs = r.q_hs;
                     o_hs = r.o_hs;
                     pages = page_ids + r.page_off;
-                    layer_base = size_t(r.layer) * size_t(pool_pages);
+                    layer_base = size_t(rlayer) * size_t(pool_pages);
                     if (r.flags & 8u) {
-                        k_new = r.k + size_t(u.kv_head) * r.kv_hs;
-                        v_new = r.v + size_t(u.kv_head) * r.kv_hs;
+                        k_new = rk + size_t(u.kv_head) * r.kv_hs;
+                        v_new = rv + size_t(u.kv_head) * r.kv_hs;
                         fused = 1 | ((r.flags & 1u) ? 2 : 0) | (u.store_new ? 4 : 0);
                         pos = r.index_pos;
                     }

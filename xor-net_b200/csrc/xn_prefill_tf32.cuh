@@ -18,7 +18,12 @@
 //               signals the mbarriers;
 //   warps 2..9  two softmax warpgroups; thread r of each owns query row r, warpgroup 0 the first
 //               page of every score tile, warpgroup 1 the second.  Prologue: Q goes global ->
-//               registers -> tensor memory (rounded to TF32).  Per tile: tcgen05.ld of the S
+//               shared memory (whole rows per warp instruction) -> registers -> tensor memory
+//               (rounded to TF32); for head_dim 64 / 128 the rotary
+//               embedding of the query rows (src/tensor.rs:295-316, call site
+//               src/models/llama/attention.rs:88) is applied on the way, with the append
+//               kernel's unfused arithmetic, so the append kernel handles K and V only and the
+//               prologue does not wait for it.  Per tile: tcgen05.ld of the S
 //               row, causal mask, row maximum exchanged between the two warpgroups through
 //               shared memory, exp2 with the softmax scale folded into one FMA, P written back
 //               with tcgen05.st.  The accumulator is rescaled lazily: only when a row's maximum
@@ -34,8 +39,11 @@
 namespace xn {
 
 struct PrefillArgs {
-    const float* q;       // rotated queries (device)
+    const float* q;       // queries: rotated already (rope_q == 0) or as supplied (rope_q == 1)
     long long q_hs, q_ts; // query head / token strides in floats
+    const float* cos_t;   // rotary tables [position][head_dim / 2], read when rope_q
+    const float* sin_t;
+    int rope_q;           // rotate the query rows in the prologue (head_dim 64 or 128 only)
     const int* pages;     // page ids of the stream (device)
     float* out;           // output base
     long long o_hs, o_ts; // output head / token strides in floats
@@ -263,7 +271,7 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap k_map,
             };
             auto load_k_tile = [&](int j) -> bool {
                 const int st = j % kKStages;
-                if (j >= kKStages && !mbar_wait_bounded(&k_empty[st], uint32_t((j / kKStages - 1) & 1))) return false;
+                if (j >= kKStages && !mbar_poll_sleep_bounded(&k_empty[st], uint32_t((j / kKStages - 1) & 1), 64u)) return false;
                 const int np = min(2, n_pages - 2 * j);
                 int rows[2] = {0, 0};
                 for (int p = 0; p < np; ++p) rows[p] = page_row(2 * j + p);
@@ -278,7 +286,9 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap k_map,
             };
             auto load_v_page = [&](int pg) -> bool {
                 const int st = pg % kVStages;
-                if (pg >= kVStages && !mbar_wait_bounded(&v_empty[st], uint32_t((pg / kVStages - 1) & 1))) return false;
+                // stages 1 and 2 stage the query tile first: page 1 is the first to go there
+                if (pg == 1 && !mbar_poll_sleep_bounded(q_ready, 0, 64u)) return false;
+                if (pg >= kVStages && !mbar_poll_sleep_bounded(&v_empty[st], uint32_t((pg / kVStages - 1) & 1), 64u)) return false;
                 const int row = page_row(pg);
                 if (bad_page) return false;
                 mbar_arrive_expect_tx(&v_full[st], uint32_t(n_kb) * kVSub);
@@ -310,7 +320,7 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap k_map,
             constexpr uint64_t kKStageStep = uint64_t(kKBytes) >> 4;
             constexpr uint64_t kVStageStep = uint64_t(kVBytes) >> 4;
             constexpr uint64_t kKBlockStep = uint64_t(kKSub) >> 4;  // next 32-float column block
-            bool ok = mbar_wait_bounded(q_ready, 0);
+            bool ok = mbar_spin_bounded(q_ready, 0);
             if (!ok) { report_status(a.status, kDevWaitFull); *abort_flag = 1; }
             fence_after_sync();
 
@@ -319,7 +329,7 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap k_map,
             int pv_issued = 0;          // tiles whose O += P V has been issued
 
             auto issue_qk = [&](int j) -> bool {
-                if (!mbar_wait_bounded(&k_full[k_st], uint32_t(k_ph))) return false;
+                if (!mbar_spin_bounded(&k_full[k_st], uint32_t(k_ph))) return false;
                 fence_after_sync();
                 const uint64_t kd = kdesc0 + uint64_t(k_st) * kKStageStep;
                 const uint32_t d_addr = tmem_s + (j & 1) * kBN;
@@ -342,10 +352,10 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap k_map,
             // 8 tokens = 1024 B inside each column block, column blocks kVSub apart (leading
             // offset), 4-token swizzle groups 512 B apart (stride offset).
             auto issue_pv = [&](int j) -> bool {
-                if (!mbar_wait_bounded(&p_full[j & 1], uint32_t((j >> 1) & 1))) return false;
+                if (!mbar_spin_bounded(&p_full[j & 1], uint32_t((j >> 1) & 1))) return false;
                 const int np = min(2, n_pages - 2 * j);
                 for (int p = 0; p < np; ++p) {
-                    if (!mbar_wait_bounded(&v_full[v_st], uint32_t(v_ph))) return false;
+                    if (!mbar_spin_bounded(&v_full[v_st], uint32_t(v_ph))) return false;
                     fence_after_sync();
                     const uint64_t vd = vdesc0 + uint64_t(v_st) * kVStageStep;
                     const uint32_t p_addr = tmem_s + (j & 1) * kBN + p * kPage;
@@ -383,21 +393,85 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap k_map,
         const int col0 = wg * kPage;             // this warpgroup's columns of a score tile
         auto wg_barrier = [&]() { named_bar_sync(1, 256); };
 
-        // ---- prologue: Q -> tensor memory (rounded to TF32); each warpgroup half of the columns
-        pdl_wait();   // the query rows may come out of the append kernel's rotation scratch
+        // ---- prologue: Q -> tensor memory (rounded to TF32)
+        // Global -> shared memory with whole rows per warp instruction (a thread reading its own
+        // row would touch 32 cache lines per instruction), optionally rotating on the way, then
+        // shared -> registers -> tensor memory with thread r owning row r.  The staging tile sits
+        // in V stages 1 and 2, which the TMA warp leaves alone until q_ready completes.
+        // 16-byte chunk c of row r sits at chunk position c ^ (r & 31): conflict-free both ways.
         {
-            const float* qrow = a.q + size_t(h) * a.q_hs + size_t(t) * a.q_ts;
-            const bool valid = t < a.seq_len;
+            float4* qs = reinterpret_cast<float4*>(v_s + kVBytes);   // [128 rows][32 chunks]
+            const int w8 = warp - 2;        // 0..7: rows [16 w8, 16 w8 + 16) of the tile
+            const int n_ch = D >> 2;        // 16-byte chunks per row
+            const bool rope = a.rope_q != 0;
+            const int half_ch = n_ch >> 1;  // rope: 8 or 16; pair i of a row is (x[i], x[i + D/2])
+            // rotated rows come out of the append kernel's scratch: wait for it; rows rotated here
+            // are the caller's own and need no wait
+            if (!rope) pdl_wait();
+            const float* qbase = a.q + size_t(h) * a.q_hs;
+            // eight rows at a time: all their loads are issued before the first is used
+#pragma unroll
+            for (int b = 0; b < 2; ++b) {
+                float4 x[8], cv[8], sv[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int tt = t0 + w8 * 16 + b * 8 + i;
+                    const bool act = tt < a.seq_len && lane < n_ch;
+                    x[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    cv[i] = x[i];
+                    sv[i] = x[i];
+                    if (act) {
+                        x[i] = *reinterpret_cast<const float4*>(qbase + size_t(tt) * a.q_ts + lane * 4);
+                        if (rope) {
+                            const size_t trow = size_t(a.index_pos + tt) * size_t(D >> 1) + size_t(lane & (half_ch - 1)) * 4;
+                            cv[i] = *reinterpret_cast<const float4*>(a.cos_t + trow);
+                            sv[i] = *reinterpret_cast<const float4*>(a.sin_t + trow);
+                        }
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int rr = w8 * 16 + b * 8 + i;
+                    float4 v = x[i];
+                    if (rope) {
+                        float4 y;
+                        y.x = __shfl_xor_sync(kFull, v.x, half_ch);
+                        y.y = __shfl_xor_sync(kFull, v.y, half_ch);
+                        y.z = __shfl_xor_sync(kFull, v.z, half_ch);
+                        y.w = __shfl_xor_sync(kFull, v.w, half_ch);
+                        const float4 c4 = cv[i], s4 = sv[i];
+                        // the append kernel's arithmetic (unfused): lo' = lo c - hi s, hi' = lo s + hi c
+                        if ((lane & half_ch) == 0) {
+                            v.x = __fsub_rn(__fmul_rn(v.x, c4.x), __fmul_rn(y.x, s4.x));
+                            v.y = __fsub_rn(__fmul_rn(v.y, c4.y), __fmul_rn(y.y, s4.y));
+                            v.z = __fsub_rn(__fmul_rn(v.z, c4.z), __fmul_rn(y.z, s4.z));
+                            v.w = __fsub_rn(__fmul_rn(v.w, c4.w), __fmul_rn(y.w, s4.w));
+                        } else {
+                            v.x = __fadd_rn(__fmul_rn(y.x, s4.x), __fmul_rn(v.x, c4.x));
+                            v.y = __fadd_rn(__fmul_rn(y.y, s4.y), __fmul_rn(v.y, c4.y));
+                            v.z = __fadd_rn(__fmul_rn(y.z, s4.z), __fmul_rn(v.z, c4.z));
+                            v.w = __fadd_rn(__fmul_rn(y.w, s4.w), __fmul_rn(v.w, c4.w));
+                        }
+                    }
+                    // rows past the end and chunks past head_dim were loaded as zeros
+                    uint4 xr;
+                    xr.x = round_tf32(__float_as_uint(v.x));
+                    xr.y = round_tf32(__float_as_uint(v.y));
+                    xr.z = round_tf32(__float_as_uint(v.z));
+                    xr.w = round_tf32(__float_as_uint(v.w));
+                    reinterpret_cast<uint4*>(qs)[rr * 32 + (lane ^ (rr & 31))] = xr;
+                }
+            }
+            wg_barrier();
             for (int c0 = col0; c0 < min(col0 + kPage, k_steps * 8); c0 += 32) {
                 uint32_t qv[32];
 #pragma unroll
-                for (int c = 0; c < 32; c += 4) {
-                    float4 v4 = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (valid && c0 + c < D) v4 = *reinterpret_cast<const float4*>(qrow + c0 + c);
-                    qv[c] = round_tf32(__float_as_uint(v4.x));
-                    qv[c + 1] = round_tf32(__float_as_uint(v4.y));
-                    qv[c + 2] = round_tf32(__float_as_uint(v4.z));
-                    qv[c + 3] = round_tf32(__float_as_uint(v4.w));
+                for (int c = 0; c < 8; ++c) {
+                    const uint4 v4 = reinterpret_cast<const uint4*>(qs)[r * 32 + (((c0 >> 2) + c) ^ (r & 31))];
+                    qv[4 * c] = v4.x;
+                    qv[4 * c + 1] = v4.y;
+                    qv[4 * c + 2] = v4.z;
+                    qv[4 * c + 3] = v4.w;
                 }
                 tmem_st32(tmem_q + lane_base + c0, qv);
             }
@@ -410,7 +484,7 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap k_map,
         bool dead = false;
         for (int j = 0; j < n_tiles; ++j) {
             const int sb = j & 1;
-            if (!__all_sync(kFull, mbar_wait_bounded(&s_full[sb], uint32_t((j >> 1) & 1)))) dead = true;
+            if (!warp_spin_bounded(&s_full[sb], uint32_t((j >> 1) & 1), lane)) dead = true;
             // all eight warps must take the same exit: agree through a flag only they write
             if (lane == 0 && dead) { *sm_dead = 1; *abort_flag = 1; }
             fence_after_sync();
@@ -454,7 +528,7 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap k_map,
             if (__any_sync(kFull, need)) {
                 // the accumulator must be quiet: wait for O += P_{j-1} V_{j-1}; each warpgroup
                 // rescales its half of the columns
-                if (!__all_sync(kFull, mbar_wait_bounded(&pv_done[(j - 1) & 1], uint32_t(((j - 1) >> 1) & 1)))) {
+                if (!warp_spin_bounded(&pv_done[(j - 1) & 1], uint32_t(((j - 1) >> 1) & 1), lane)) {
                     // cannot bail out alone (the other warpgroup may not rescale): record and go on
                     report_status(a.status, kDevWaitMma);
                 }
@@ -499,7 +573,7 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap k_map,
             wg_barrier();
             const float l_tot = l_sum + xchg[(wg ^ 1) * 128 + r];
             const int jl = n_tiles - 1;
-            if (__all_sync(kFull, mbar_wait_bounded(&pv_done[jl & 1], uint32_t((jl >> 1) & 1)))) {
+            if (warp_spin_bounded(&pv_done[jl & 1], uint32_t((jl >> 1) & 1), lane)) {
                 fence_after_sync();
                 const float inv = 1.0f / l_tot;
                 // Stage the tile in shared memory (the K stages are idle by now) so that the
