@@ -83,6 +83,19 @@ rope_append_kernel(const ReqDev* __restrict__ reqs, const int* __restrict__ page
     // q is rotated, or just moved next to the kernels -- unless the prefill kernel rotates the
     // query rows itself (bit 4)
     const bool q_rows = (r.flags & 3u) && !(r.flags & 16u);
+    if (r.flags & 16u) {
+        // The prefill kernel behind this one reads the query rows itself.  Ask for them now, so
+        // that they travel from DRAM to L2 while this kernel moves K and V (nothing waits here).
+        const long long lines_per_row = ((long long)head_dim * 4 + 127) / 128;
+        const long long n_lines = (long long)r.seq_len * num_heads * lines_per_row;
+        for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n_lines;
+             i += (long long)gridDim.x * blockDim.x) {
+            const long long row = i / lines_per_row, line = i % lines_per_row;
+            const long long t = row / num_heads, hh = row % num_heads;
+            const float* p = r.q_in + size_t(hh) * r.qi_hs + size_t(t) * r.qi_ts + line * 32;
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+        }
+    }
     const int rows_per_tok = (q_rows ? num_heads : 0) + 2 * num_kv_heads;
     const long long n_rows = (long long)r.seq_len * rows_per_tok;
     const int hl = threadIdx.x & 15;         // lane inside the half-warp

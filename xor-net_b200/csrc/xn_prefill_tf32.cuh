@@ -165,6 +165,16 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
         : "memory");
 }
 
+// A 16-byte read-only load the compiler keeps where it is written: the prologue issues the loads of
+// eight rows back to back and only then starts to consume them.
+__device__ __forceinline__ float4 ldg_keep(const float* p) {
+    float4 v;
+    asm volatile("ld.global.nc.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "l"(p));
+    return v;
+}
+
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
@@ -412,20 +422,22 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap k_map,
             // eight rows at a time: all their loads are issued before the first is used
 #pragma unroll
             for (int b = 0; b < 2; ++b) {
-                float4 x[8], cv[8], sv[8];
+                float4 x[8], y[8], cv[8], sv[8];   // y: the row's other half, read again (an L1 hit)
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     const int tt = t0 + w8 * 16 + b * 8 + i;
                     const bool act = tt < a.seq_len && lane < n_ch;
                     x[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    y[i] = x[i];
                     cv[i] = x[i];
                     sv[i] = x[i];
                     if (act) {
-                        x[i] = *reinterpret_cast<const float4*>(qbase + size_t(tt) * a.q_ts + lane * 4);
+                        x[i] = ldg_keep(qbase + size_t(tt) * a.q_ts + lane * 4);
                         if (rope) {
                             const size_t trow = size_t(a.index_pos + tt) * size_t(D >> 1) + size_t(lane & (half_ch - 1)) * 4;
-                            cv[i] = *reinterpret_cast<const float4*>(a.cos_t + trow);
-                            sv[i] = *reinterpret_cast<const float4*>(a.sin_t + trow);
+                            y[i] = ldg_keep(qbase + size_t(tt) * a.q_ts + (lane ^ half_ch) * 4);
+                            cv[i] = ldg_keep(a.cos_t + trow);
+                            sv[i] = ldg_keep(a.sin_t + trow);
                         }
                     }
                 }
@@ -434,23 +446,18 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap k_map,
                     const int rr = w8 * 16 + b * 8 + i;
                     float4 v = x[i];
                     if (rope) {
-                        float4 y;
-                        y.x = __shfl_xor_sync(kFull, v.x, half_ch);
-                        y.y = __shfl_xor_sync(kFull, v.y, half_ch);
-                        y.z = __shfl_xor_sync(kFull, v.z, half_ch);
-                        y.w = __shfl_xor_sync(kFull, v.w, half_ch);
                         const float4 c4 = cv[i], s4 = sv[i];
                         // the append kernel's arithmetic (unfused): lo' = lo c - hi s, hi' = lo s + hi c
                         if ((lane & half_ch) == 0) {
-                            v.x = __fsub_rn(__fmul_rn(v.x, c4.x), __fmul_rn(y.x, s4.x));
-                            v.y = __fsub_rn(__fmul_rn(v.y, c4.y), __fmul_rn(y.y, s4.y));
-                            v.z = __fsub_rn(__fmul_rn(v.z, c4.z), __fmul_rn(y.z, s4.z));
-                            v.w = __fsub_rn(__fmul_rn(v.w, c4.w), __fmul_rn(y.w, s4.w));
+                            v.x = __fsub_rn(__fmul_rn(v.x, c4.x), __fmul_rn(y[i].x, s4.x));
+                            v.y = __fsub_rn(__fmul_rn(v.y, c4.y), __fmul_rn(y[i].y, s4.y));
+                            v.z = __fsub_rn(__fmul_rn(v.z, c4.z), __fmul_rn(y[i].z, s4.z));
+                            v.w = __fsub_rn(__fmul_rn(v.w, c4.w), __fmul_rn(y[i].w, s4.w));
                         } else {
-                            v.x = __fadd_rn(__fmul_rn(y.x, s4.x), __fmul_rn(v.x, c4.x));
-                            v.y = __fadd_rn(__fmul_rn(y.y, s4.y), __fmul_rn(v.y, c4.y));
-                            v.z = __fadd_rn(__fmul_rn(y.z, s4.z), __fmul_rn(v.z, c4.z));
-                            v.w = __fadd_rn(__fmul_rn(y.w, s4.w), __fmul_rn(v.w, c4.w));
+                            v.x = __fadd_rn(__fmul_rn(y[i].x, s4.x), __fmul_rn(v.x, c4.x));
+                            v.y = __fadd_rn(__fmul_rn(y[i].y, s4.y), __fmul_rn(v.y, c4.y));
+                            v.z = __fadd_rn(__fmul_rn(y[i].z, s4.z), __fmul_rn(v.z, c4.z));
+                            v.w = __fadd_rn(__fmul_rn(y[i].w, s4.w), __fmul_rn(v.w, c4.w));
                         }
                     }
                     // rows past the end and chunks past head_dim were loaded as zeros
