@@ -385,13 +385,16 @@ def measure_prefill(xn, torch, tstream, device, S, Hq, Hkv, D, theta, steps, war
     #    the prefill kernel, so this loop runs without their overlap)
     ctx.profile_enable(True)
     ctx.profile_read()
-    for j in range(max(3, min(steps, 10))):
+    n_prof = max(3, min(steps, 10))
+    launched0 = ctx.stats()["kernel_launches"]
+    for j in range(n_prof):
         flush.zero_()
         call(j)
     torch.cuda.synchronize()
     kern_ms, kern_n = ctx.profile_read("prefill")
     ctx.profile_enable(False)
-    kern_per_call = kern_ms / max(kern_n, 1) * len(pieces)
+    launches_per_call = (ctx.stats()["kernel_launches"] - launched0) / n_prof
+    kern_per_call = kern_ms / n_prof   # all prefill launches of one call (chunks, sequences)
     # -- back-to-back calls, timed in runs: sustained (power-capped) clocks
     run = max(4, min(64, steps))
     runs, total, i = [], 0.0, 0
@@ -407,7 +410,6 @@ def measure_prefill(xn, torch, tstream, device, S, Hq, Hkv, D, theta, steps, war
         total += runs[-1] * run
     pipe_ms = float(np.median(runs))
     flops = prefill_flops(Hq, D, S, P) * n_seqs
-    kern_per_call *= n_seqs
     res = {"seq_len": S, "index_pos": P, "chunk": chunk or S, "sequences": n_seqs, "flops": flops, "ms": ms,
            "tflops": flops / (ms * 1e-3) / 1e12,
            "timing": f"median of {len(iso)} calls, each behind a 256 MB write that flushes L2",
@@ -416,7 +418,7 @@ def measure_prefill(xn, torch, tstream, device, S, Hq, Hkv, D, theta, steps, war
                                f"input sets ({n_sets * set_bytes / 1e6:.0f} MB, larger than L2); sustained clocks",
            "kernel_ms": kern_per_call,
            "kernel_tflops": flops / (kern_per_call * 1e-3) / 1e12 if kern_n else None,
-           "launches_per_step": (3 if u8 else 2) * len(pieces)}
+           "launches_per_step": launches_per_call}
     if e2e and not chunk and n_seqs == 1:
         host = ctx.make_batch([(host_st, 0, P, S, q_h.data_ptr(), k_h.data_ptr(), v_h.data_ptr(), o_h.data_ptr())],
                               xn.REQ_ROPE | xn.REQ_HOST_PINNED)  # page-locked host buffers
@@ -899,6 +901,7 @@ def run_gpu_arm(args):
         step_host()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reuses0 = ctx.stats()["plan_reuses"]
     t0 = time.perf_counter()
     e0.record(tstream)
     for _ in range(e2e_steps):
@@ -906,6 +909,7 @@ def run_gpu_arm(args):
     e1.record(tstream)
     barrier()
     e2e_wall_ms = (time.perf_counter() - t0) * 1e3
+    e2e_reuses = ctx.stats()["plan_reuses"] - reuses0
     e2e_ms = max(e0.elapsed_time(e1), 0.0)
     # the host side of the call is part of it: the wall clock is the honest end-to-end time
     e2e_ms = max(e2e_ms, e2e_wall_ms)
@@ -975,6 +979,7 @@ def run_gpu_arm(args):
                     "tokens_per_s": n_total_streams * e2e_steps / (e2e_ms * 1e-3),
                     "api": "xn_attention_batch, page-locked host pointers (XN_REQ_HOST_PINNED), one "
                            "blocking call per layer",
+                    "plans_reused_per_step": e2e_reuses / max(e2e_steps, 1),
                     "staged_ms_per_step": staged_ms / max(e2e_steps, 1),
                     "staged_value": (bytes_per_step * e2e_steps / (staged_ms * 1e-3) / 1e9) if staged_ms else None},
             "gpu_launches": int(launches),

@@ -232,7 +232,7 @@ def test_fused_behind_tf32_prefill_rope_seq_major_and_mixed_batch():
     reqs[0].flags |= xn.REQ_OUT_PROJ
     reqs[2].flags |= xn.REQ_OUT_PROJ
     ctx.submit(reqs)
-    assert ctx.stats()["prefill_launches"] == 2 and ctx.stats()["out_proj_rows"] == 2 * S
+    assert ctx.stats()["prefill_launches"] == 1 and ctx.stats()["out_proj_rows"] == 2 * S   # both prompts in one launch
     for i, layer, st in ((0, 0, a), (2, 2, c3)):
         ref, nw = blocks[layer]
         plain = ctx.attention_batch([st], layer, [0], [ins[i][0]], [ins[i][1]], [ins[i][2]], rope=True,

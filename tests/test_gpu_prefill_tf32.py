@@ -187,3 +187,45 @@ def test_query_rotation_inside_the_kernel_equals_the_rotation_scratch(Hq, Hkv, D
                              ref, Hq, Hkv, D)
     check_tf32(outs[0], want[0], f"D={D} S={S} pos={pos}")
     ref.close()
+
+
+def test_several_prompts_share_one_launch():
+    """A submission with several tensor-core prefills (a batch of prompts of different lengths, one
+    of them a later chunk, on different layers) runs as ONE launch whose blocks are ordered by
+    weight across all requests.  Results equal, bit for bit, the ones of one launch per request,
+    and match the oracle (src/nn/fast_attention.rs:138-201 per request)."""
+    import os
+    Hq, Hkv, D = 8, 2, 128
+    shapes = [(700, 0, 0), (129, 0, 1), (300, 256, 1), (128, 0, 0)]   # (rows, index_pos, layer)
+    rng = np.random.default_rng(4242)
+    cos, sin = xn.rope_tables(10000.0, D, 1024)
+    qkv = [rand_qkv(rng, Hq, Hkv, S, D) for S, _, _ in shapes]
+    first = rand_qkv(rng, Hq, Hkv, 256, D)        # the earlier chunk of the third stream
+    outs = {}
+    for flag in ("1", "0"):
+        os.environ["XORNET_ATTN_PREFILL_MULTI"] = flag
+        try:
+            ctx = xn.Context(2, Hq, Hkv, D, pool_pages=64, shuffle_seed=11, rope=(cos, sin), prefill_mode=TF32)
+        finally:
+            del os.environ["XORNET_ATTN_PREFILL_MULTI"]
+        sts = [ctx.new_stream(1024) for _ in shapes]
+        ctx.attention(sts[2], 1, 0, *first, rope=True)
+        before = ctx.stats()["prefill_launches"]
+        res = ctx.attention_batch(sts, [l for _, _, l in shapes], [p for _, p, _ in shapes],
+                                  [a[0] for a in qkv], [a[1] for a in qkv], [a[2] for a in qkv], rope=True)
+        assert ctx.stats()["prefill_launches"] - before == (1 if flag == "1" else len(shapes))
+        outs[flag] = res
+        if flag == "1":
+            for i, (S, pos, layer) in enumerate(shapes):
+                ref = xo.RingCache(1, Hkv, 1024, D)
+                if pos:
+                    ref.append(0, 0, xo.tensor_rope(first[1], cos, sin, 0)[0], first[2][0])
+                want = xo.fast_attention(xo.tensor_rope(qkv[i][0], cos, sin, pos), xo.tensor_rope(qkv[i][1], cos, sin, pos),
+                                         qkv[i][2], 0, pos, ref, Hq, Hkv, D)
+                check_tf32(res[i], want, f"request {i}")
+                kd, vd = sts[i].read_range(layer, 0, pos + S)
+                assert np.array_equal(kd.ravel(), ref.k_buffer(0).reshape(Hkv, 1024, D)[:, :pos + S].ravel())
+                ref.close()
+        ctx.close()
+    for a, b in zip(outs["1"], outs["0"]):
+        assert np.array_equal(a, b)

@@ -72,6 +72,11 @@ __device__ __forceinline__ void row_copy(const float* __restrict__ src, float* _
     }
 }
 
+// F2: instantiation for head dims that are a multiple of 4 but not of 8 (100: the second half of a
+// row starts 8 bytes off a 16-byte boundary): rows move as float2, two per lane and half, with the
+// four rows of a pass in flight together.  A separate instantiation so that the float4 variant
+// keeps its register budget (two blocks per SM).
+template <bool F2>
 __global__ void __launch_bounds__(256)
 rope_append_kernel(const ReqDev* __restrict__ reqs, const int* __restrict__ page_ids,
                    float* __restrict__ k_pool, float* __restrict__ v_pool,
@@ -152,6 +157,12 @@ rope_append_kernel(const ReqDev* __restrict__ reqs, const int* __restrict__ page
 #pragma unroll
         for (int u = 0; u < U; ++u)
             if (kind[u] && ((reinterpret_cast<uintptr_t>(src[u]) | reinterpret_cast<uintptr_t>(dst[u])) & 15)) fast = false;
+        bool fast2 = F2 && !dim_vec && (head_dim % 4) == 0 && head_dim <= 128;
+        if (F2) {
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+                if (kind[u] && ((reinterpret_cast<uintptr_t>(src[u]) | reinterpret_cast<uintptr_t>(dst[u])) & 7)) fast2 = false;
+        }
         if (fast) {
             const int i = hl * 4;
             const bool in = i < half;
@@ -172,6 +183,36 @@ rope_append_kernel(const ReqDev* __restrict__ reqs, const int* __restrict__ page
                 if (kind[u] == 2) rotate4(lo[u], hi[u], cv[u], sv[u]);
                 *reinterpret_cast<float4*>(dst[u] + i) = lo[u];
                 *reinterpret_cast<float4*>(dst[u] + i + half) = hi[u];
+            }
+        } else if (F2 && fast2) {
+#pragma unroll 1
+            for (int k = 0; k < 2; ++k) {
+                const int i = (hl + 16 * k) * 2;
+                if (i >= half) break;
+                float2 lo[U], hi[U], cv[U], sv[U];
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    if (!kind[u]) continue;
+                    lo[u] = *reinterpret_cast<const float2*>(src[u] + i);
+                    hi[u] = *reinterpret_cast<const float2*>(src[u] + i + half);
+                    if (kind[u] == 2) {
+                        cv[u] = *reinterpret_cast<const float2*>(c[u] + i);
+                        sv[u] = *reinterpret_cast<const float2*>(s[u] + i);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    if (!kind[u]) continue;
+                    float2 a = lo[u], b = hi[u];
+                    if (kind[u] == 2) {   // unfused, as everywhere: x1 c - x2 s, x1 s + x2 c
+                        a.x = __fsub_rn(__fmul_rn(lo[u].x, cv[u].x), __fmul_rn(hi[u].x, sv[u].x));
+                        a.y = __fsub_rn(__fmul_rn(lo[u].y, cv[u].y), __fmul_rn(hi[u].y, sv[u].y));
+                        b.x = __fadd_rn(__fmul_rn(lo[u].x, sv[u].x), __fmul_rn(hi[u].x, cv[u].x));
+                        b.y = __fadd_rn(__fmul_rn(lo[u].y, sv[u].y), __fmul_rn(hi[u].y, cv[u].y));
+                    }
+                    *reinterpret_cast<float2*>(dst[u] + i) = a;
+                    *reinterpret_cast<float2*>(dst[u] + i + half) = b;
+                }
             }
         } else {
 #pragma unroll

@@ -147,6 +147,7 @@ struct xn_ctx {
     bool fuse_pinned = true; // ... also when q,k,v live in page-locked host memory
     bool plan_reuse = true;  // a decode submission of the previous one's geometry reuses its plan
     bool pf_rope_q = true;   // the tensor-core prefill kernel rotates the query rows itself
+    bool pf_multi = true;    // several tensor-core prefills of one submission share one launch
     PlanCache pcache;
     size_t stage_direct_bytes = size_t(2) << 20;  // small staged calls: kernels use the pinned staging itself
     bool out_tc = true;      // output projection on the tensor cores (else the dp4a kernel)
@@ -750,6 +751,31 @@ bool use_f32_tiled(const xn_ctx* c, const xn_req& r) {
 }
 
 // reqs[i] are valid, on distinct streams, all host-mode or all device-mode.
+// Arguments of the tensor-core prefill kernel for one request of a submission.
+PrefillArgs make_prefill_args(const xn_ctx* c, const ReqDev& d, const int* pages_d) {
+    PrefillArgs pa;
+    pa.q = d.q;
+    pa.q_hs = d.q_hs;
+    pa.q_ts = d.q_ts;
+    pa.cos_t = c->cos_d;
+    pa.sin_t = c->sin_d;
+    pa.rope_q = (d.flags & 16u) ? 1 : 0;
+    pa.pages = c->kv_u8 ? c->stage_ident_d : pages_d + d.page_off;
+    pa.out = d.out;
+    pa.o_hs = d.o_hs;
+    pa.o_ts = d.o_ts;
+    pa.layer_page_base = c->kv_u8 ? 0 : (long long)d.layer * c->pool_pages;
+    pa.pool_pages = c->kv_u8 ? c->stage_pages : c->pool_pages;
+    pa.num_kv_heads = c->num_kv_heads;
+    pa.group = c->group;
+    pa.seq_len = d.seq_len;
+    pa.index_pos = d.index_pos;
+    pa.head_dim = c->head_dim;
+    pa.scale_log2 = c->scale * 1.4426950408889634f;
+    pa.status = c->status_d;
+    return pa;
+}
+
 // A decode submission with the geometry of the plan kept on the device: the same streams, in the
 // same order, at the same positions, one token each, all on one layer (any layer), nothing to
 // zero-fill.  Launches the attention kernel over the kept plan with this call's addresses and layer
@@ -1087,6 +1113,29 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
     const size_t o_rows = place(sizeof(OutRowDev) * out_row_tab.size());
     const size_t o_qkv = place(sizeof(OutRowDev) * qkv_row_tab.size());
     const size_t o_f32 = place(sizeof(F32Item) * f32_items.size());
+    // Several tensor-core prefills in one submission share one launch: a table of their arguments
+    // and a list of (request, query tile, head) blocks, heaviest first over all of them.  (Not in
+    // the u8 format, whose requests take turns in one staging area.)
+    const bool multi_prefill = c->pf_multi && !c->kv_u8 && tf32_reqs.size() > 1;
+    std::vector<PrefillBlock> pf_blocks;
+    if (multi_prefill) {
+        std::vector<std::pair<int, PrefillBlock>> weighted;
+        for (size_t k = 0; k < tf32_reqs.size(); ++k) {
+            const ReqDev& d = rd[size_t(tf32_reqs[k])];
+            const int n_qt = (d.seq_len + pf::kBM - 1) / pf::kBM;
+            for (int qt = 0; qt < n_qt; ++qt) {
+                const int last_row = std::min((qt + 1) * pf::kBM, d.seq_len) - 1;
+                const int tiles = ((d.index_pos + last_row) / kPageTokens + 2) / 2;
+                for (int h = 0; h < Hq; ++h) weighted.push_back({tiles, {int(k), qt, h, 0}});
+            }
+        }
+        std::stable_sort(weighted.begin(), weighted.end(),
+                         [](const auto& x, const auto& y) { return x.first > y.first; });
+        pf_blocks.reserve(weighted.size());
+        for (const auto& w : weighted) pf_blocks.push_back(w.second);
+    }
+    const size_t o_pft = place(multi_prefill ? sizeof(PrefillArgs) * tf32_reqs.size() : 0);
+    const size_t o_pfb = place(sizeof(PrefillBlock) * pf_blocks.size());
     PlanSlot* slot = nullptr;
     if ((rc = acquire_slot(c, off, &slot)) != XN_OK) return rc;
     memcpy(slot->host + o_req, rd.data(), sizeof(ReqDev) * n);
@@ -1101,6 +1150,12 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
     if (!qkv_row_tab.empty())
         memcpy(slot->host + o_qkv, qkv_row_tab.data(), sizeof(OutRowDev) * qkv_row_tab.size());
     if (!f32_items.empty()) memcpy(slot->host + o_f32, f32_items.data(), sizeof(F32Item) * f32_items.size());
+    if (multi_prefill) {
+        PrefillArgs* tab = reinterpret_cast<PrefillArgs*>(slot->host + o_pft);
+        for (size_t k = 0; k < tf32_reqs.size(); ++k)
+            tab[k] = make_prefill_args(c, rd[size_t(tf32_reqs[k])], reinterpret_cast<const int*>(slot->dev + o_page));
+        memcpy(slot->host + o_pfb, pf_blocks.data(), sizeof(PrefillBlock) * pf_blocks.size());
+    }
     // The plan does not depend on anything in flight: upload it on the copy stream so that it
     // overlaps the previous submission's kernels, and make the launch stream wait for it.
     // (A blocking host-pointer call has nothing in flight to overlap with: plain in-stream copy.)
@@ -1176,9 +1231,11 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
                                                                     c->sin_d, c->pool_pages, Hq, Hkv, D,
                                                                     c->dq);
         } else
-        rope_append_kernel<<<grid, 256, 0, c->stream>>>(reqs_d, pages_d, c->k_pool, c->v_pool,
-                                                        c->cos_d, c->sin_d, c->pool_pages, Hq, Hkv,
-                                                        D, nv);
+        {
+            auto append = (D % 8 != 0 && D % 4 == 0 && D <= 128) ? rope_append_kernel<true> : rope_append_kernel<false>;
+            append<<<grid, 256, 0, c->stream>>>(reqs_d, pages_d, c->k_pool, c->v_pool, c->cos_d, c->sin_d,
+                                                c->pool_pages, Hq, Hkv, D, nv);
+        }
         c->stats.kernel_launches += 1;
     }
     if (sp.ctas > 0 && c->kv_u8) {
@@ -1236,28 +1293,40 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         c->stats.kernel_launches += 1;
         c->stats.prefill_launches += 1;
     }
+    auto prefill_args = [&](int i) { return make_prefill_args(c, rd[size_t(i)], pages_d); };
+    // A programmatic dependent of the kernel before it (the append): its blocks set up while that
+    // kernel drains; their reads of what it wrote wait inside the kernel.  Not behind another
+    // prefill launch: two of them must not share the SMs' tensor memory.
+    auto launch_prefill = [&](unsigned blocks, bool pdl, bool multi, const PrefillArgs& pa,
+                              const PrefillArgs* table_d, const PrefillBlock* blocks_d) -> cudaError_t {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(blocks);
+        cfg.blockDim = dim3(pf::kThreads);
+        cfg.dynamicSmemBytes = pf::kSmemBytes;
+        cfg.stream = c->stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = (c->pf_pdl && pdl && !c->profile) ? 1 : 0;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        const CUtensorMap& km = c->kv_u8 ? c->k_stage_map : c->k_map;
+        const CUtensorMap& vm = c->kv_u8 ? c->v_stage_map : c->v_map;
+        return multi ? cudaLaunchKernelEx(&cfg, prefill_tf32_kernel<true>, km, vm, pa, table_d, blocks_d)
+                     : cudaLaunchKernelEx(&cfg, prefill_tf32_kernel<false>, km, vm, pa, table_d, blocks_d);
+    };
+    if (multi_prefill) {
+        // several prompts in one submission: one launch, blocks of all requests heaviest first
+        if (c->profile && (rc = profile_begin(c, 1)) != XN_OK) return rc;
+        XN_CUDA(c, launch_prefill(unsigned(pf_blocks.size()), true, true, prefill_args(tf32_reqs.front()),
+                                  reinterpret_cast<const PrefillArgs*>(slot->dev + o_pft),
+                                  reinterpret_cast<const PrefillBlock*>(slot->dev + o_pfb)));
+        if (c->profile && (rc = profile_end(c)) != XN_OK) return rc;
+        c->stats.kernel_launches += 1;
+        c->stats.prefill_launches += 1;
+    } else
     for (int i : tf32_reqs) {
         const ReqDev& d = rd[size_t(i)];
-        PrefillArgs pa;
-        pa.q = d.q;
-        pa.q_hs = d.q_hs;
-        pa.q_ts = d.q_ts;
-        pa.cos_t = c->cos_d;
-        pa.sin_t = c->sin_d;
-        pa.rope_q = (d.flags & 16u) ? 1 : 0;
-        pa.pages = c->kv_u8 ? c->stage_ident_d : pages_d + d.page_off;
-        pa.out = d.out;
-        pa.o_hs = d.o_hs;
-        pa.o_ts = d.o_ts;
-        pa.layer_page_base = c->kv_u8 ? 0 : (long long)d.layer * c->pool_pages;
-        pa.pool_pages = c->kv_u8 ? c->stage_pages : c->pool_pages;
-        pa.num_kv_heads = Hkv;
-        pa.group = c->group;
-        pa.seq_len = d.seq_len;
-        pa.index_pos = d.index_pos;
-        pa.head_dim = D;
-        pa.scale_log2 = c->scale * 1.4426950408889634f;
-        pa.status = c->status_d;
+        const PrefillArgs pa = prefill_args(i);
         if (c->profile && (rc = profile_begin(c, 1)) != XN_OK) return rc;
         if (c->kv_u8) {
             // the stream's pages of this layer (the new rows included: the append ran above),
@@ -1268,21 +1337,8 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
                 c->v_stage);
             c->stats.kernel_launches += 1;
         }
-        // A programmatic dependent of the kernel before it (the append): its blocks set up while
-        // that kernel drains; their reads of what it wrote wait inside the kernel.  Not behind
-        // another prefill launch: two of them must not share the SMs' tensor memory.
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(unsigned((d.seq_len + pf::kBM - 1) / pf::kBM) * unsigned(Hq));
-        cfg.blockDim = dim3(pf::kThreads);
-        cfg.dynamicSmemBytes = pf::kSmemBytes;
-        cfg.stream = c->stream;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = (c->pf_pdl && i == tf32_reqs.front() && !c->profile) ? 1 : 0;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
-        XN_CUDA(c, cudaLaunchKernelEx(&cfg, prefill_tf32_kernel, c->kv_u8 ? c->k_stage_map : c->k_map,
-                                      c->kv_u8 ? c->v_stage_map : c->v_map, pa));
+        XN_CUDA(c, launch_prefill(unsigned((d.seq_len + pf::kBM - 1) / pf::kBM) * unsigned(Hq),
+                                  i == tf32_reqs.front(), false, pa, nullptr, nullptr));
         if (c->profile && (rc = profile_end(c)) != XN_OK) return rc;
         c->stats.kernel_launches += 1;
         c->stats.prefill_launches += 1;
@@ -1558,6 +1614,7 @@ int32_t xn_ctx_create(const xn_ctx_desc* d, xn_ctx** out_ctx) {
     if (const char* env = getenv("XORNET_ATTN_FUSE_PINNED")) c->fuse_pinned = atoi(env) != 0;
     if (const char* env = getenv("XORNET_ATTN_PLAN_REUSE")) c->plan_reuse = atoi(env) != 0;
     if (const char* env = getenv("XORNET_ATTN_PREFILL_ROPE_Q")) c->pf_rope_q = atoi(env) != 0;
+    if (const char* env = getenv("XORNET_ATTN_PREFILL_MULTI")) c->pf_multi = atoi(env) != 0;
     if (const char* env = getenv("XORNET_ATTN_STAGE_DIRECT_BYTES")) c->stage_direct_bytes = size_t(atoll(env));
     if (const char* env = getenv("XORNET_ATTN_OUTPROJ_TC")) c->out_tc = atoi(env) != 0;
     if (const char* env = getenv("XORNET_ATTN_OUTPROJ_PDL")) c->out_pdl = atoi(env) != 0;
@@ -1658,7 +1715,7 @@ int32_t xn_ctx_create(const xn_ctx_desc* d, xn_ctx** out_ctx) {
             // the kernel reads a dequantised staging area, mapped when the first prefill needs it
             c->tf32_ok = d->head_dim % 4 == 0 && d->head_dim >= 16 && d->head_dim <= 128 && encode_tiled_fn() != nullptr;
             if (c->tf32_ok)
-                XN_CREATE_CUDA(cudaFuncSetAttribute(reinterpret_cast<const void*>(prefill_tf32_kernel),
+                XN_CREATE_CUDA(cudaFuncSetAttribute(reinterpret_cast<const void*>(prefill_tf32_kernel<false>),
                                                     cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                     pf::kSmemBytes));
         } else if (d->head_dim % 4 == 0 && d->head_dim >= 16 && d->head_dim <= 128 && rows < (1ull << 31)) {
@@ -1669,10 +1726,14 @@ int32_t xn_ctx_create(const xn_ctx_desc* d, xn_ctx** out_ctx) {
                          // V is consumed MN-major: 32-byte-chunk swizzle
                          make_map_f32(&c->v_map, c->v_pool, 2, dims, str, box,
                                       CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
-            if (c->tf32_ok)
-                XN_CREATE_CUDA(cudaFuncSetAttribute(reinterpret_cast<const void*>(prefill_tf32_kernel),
+            if (c->tf32_ok) {
+                XN_CREATE_CUDA(cudaFuncSetAttribute(reinterpret_cast<const void*>(prefill_tf32_kernel<false>),
                                                     cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                     pf::kSmemBytes));
+                XN_CREATE_CUDA(cudaFuncSetAttribute(reinterpret_cast<const void*>(prefill_tf32_kernel<true>),
+                                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                    pf::kSmemBytes));
+            }
         }
         if (const char* env = getenv("XORNET_ATTN_TF32_MIN_ROWS")) {
             int v = atoi(env);

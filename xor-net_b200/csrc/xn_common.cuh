@@ -57,7 +57,7 @@ struct ReqDev {
 // What differs between two decode submissions of the same geometry (the same streams at the same
 // positions, e.g. the layers of one decode step): the tensors' addresses and the layer.  Passed as
 // a kernel parameter, it lets a launch reuse the plan the previous submission left on the device.
-constexpr int kPatchReqs = 64;
+constexpr int kPatchReqs = 128;
 struct ReqPatch {
     const float* q;
     const float* k;

@@ -58,6 +58,15 @@ struct PrefillArgs {
     int* status;
 };
 
+// One thread block of a launch that serves several requests: which request, which query tile,
+// which head.  The host orders the blocks by score tiles, heaviest first, across all requests.
+struct PrefillBlock {
+    int req;
+    int qt;
+    int head;
+    int pad;
+};
+
 namespace pf {
 
 constexpr int kBM = 128;          // query rows per block
@@ -190,10 +199,17 @@ __device__ __forceinline__ uint32_t round_tf32(uint32_t bits) { return bits + 0x
 
 }  // namespace pf
 
+// MULTI: one launch for several requests (a batch of prompts): the block reads its request's
+// arguments and its (query tile, head) from tables the host placed in the plan.
+template <bool MULTI>
 __global__ void __launch_bounds__(pf::kThreads, 1)
 prefill_tf32_kernel(const __grid_constant__ CUtensorMap k_map,
-                    const __grid_constant__ CUtensorMap v_map, const PrefillArgs a) {
+                    const __grid_constant__ CUtensorMap v_map, const PrefillArgs a_one,
+                    const PrefillArgs* __restrict__ table, const PrefillBlock* __restrict__ blocks) {
     using namespace pf;
+    PrefillBlock pb = {0, 0, 0, 0};
+    if (MULTI) pb = blocks[blockIdx.x];
+    const PrefillArgs a = MULTI ? table[pb.req] : a_one;
     extern __shared__ unsigned char smem_dyn[];
     // 128-byte swizzled tiles want 1024-byte alignment
     unsigned char* smem = reinterpret_cast<unsigned char*>(
@@ -222,8 +238,8 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap k_map,
     // of one KV group on the same rows, which keeps their shared K/V pages hot in L2.
     const int n_qtiles = (a.seq_len + kBM - 1) / kBM;
     const int n_heads = a.num_kv_heads * a.group;
-    const int qt = n_qtiles - 1 - int(blockIdx.x) / n_heads;
-    const int h = int(blockIdx.x) % n_heads;
+    const int qt = MULTI ? pb.qt : n_qtiles - 1 - int(blockIdx.x) / n_heads;
+    const int h = MULTI ? pb.head : int(blockIdx.x) % n_heads;
     const int h_kv = h / a.group;
     const int t0 = qt * kBM;
     const int last_row = min(t0 + kBM, a.seq_len) - 1;
