@@ -421,6 +421,12 @@ XN_API int32_t xn_debug_expire_wait(xn_ctx* ctx, int32_t timeout_ms);
  * any byte changed, XN_OK otherwise.  The test-suite calls it before it destroys a context. */
 XN_API int32_t xn_debug_check_guards(xn_ctx* ctx);
 
+/* Forgets the plan the context keeps on the device for reuse by the next decode submission of the
+ * same geometry (xn_stats.plan_reuses).  In real decoding the first layer of every step plans afresh
+ * because the position moved on; a benchmark that re-submits the SAME positions step after step
+ * calls this once per step so that it measures that, and not thirty reuses out of thirty. */
+XN_API int32_t xn_debug_drop_plan(xn_ctx* ctx);
+
 /* Library build identification: "xn_attn <version> sm_100a". */
 XN_API const char* xn_version(void);
 

@@ -95,6 +95,9 @@ def test_what_changes_the_geometry_plans_afresh():
     check(2, sts, pos, True)             # the same layer again (an overwrite at the same position)
     check(1, sts[:2], pos[:2], False)    # fewer streams
     check(2, sts[:2], pos[:2], True)
+    ctx.drop_plan()
+    check(1, sts[:2], pos[:2], False)    # dropped by hand (xn_debug_drop_plan)
+    check(2, sts[:2], pos[:2], True)
     check(0, [sts[1], sts[0]], [pos[1], pos[0]], False)   # another order
     sts[0].reset()
     sts[0].fill_normal(-1, 0, 5, 5)

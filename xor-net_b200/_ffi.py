@@ -99,6 +99,7 @@ SIGNATURES = {
                                   c_i32p, c_i32p, c_i32p, c_i32p, c_i32p, c_i32p]),
     "xn_debug_expire_wait": (C.c_int32, [C.c_void_p, C.c_int32]),
     "xn_debug_check_guards": (C.c_int32, [C.c_void_p]),
+    "xn_debug_drop_plan": (C.c_int32, [C.c_void_p]),
     "xn_profile_read_all": (C.c_int32, [C.c_void_p, C.POINTER(C.c_double), C.POINTER(C.c_uint64)]),
     "xn_qkv_proj_set": (C.c_int32, [C.c_void_p, C.POINTER(QkvProjDesc)]),
     "xn_out_proj_set": (C.c_int32, [C.c_void_p, C.POINTER(OutProjDesc)]),

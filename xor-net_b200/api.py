@@ -180,6 +180,10 @@ class Context:
         if rc != 0:
             raise XnError(rc, (self.lib.xn_last_error(self.handle) or b"").decode())
 
+    def drop_plan(self):
+        """xn_debug_drop_plan: the next decode submission plans afresh (what a new position does)."""
+        self._check(self.lib.xn_debug_drop_plan(self.handle))
+
     def check_guards(self):
         """xn_debug_check_guards: raises if a kernel wrote outside one of the context's device buffers."""
         self._check(self.lib.xn_debug_check_guards(self.handle))

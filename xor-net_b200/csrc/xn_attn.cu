@@ -2513,6 +2513,13 @@ int32_t xn_debug_expire_wait(xn_ctx* c, int32_t timeout_ms) {
     return check_device_status(c);
 }
 
+int32_t xn_debug_drop_plan(xn_ctx* c) {
+    if (!ctx_ok(c)) return XN_ERR_HANDLE;
+    std::lock_guard<std::mutex> g(c->mu);
+    c->pcache.valid = false;
+    return XN_OK;
+}
+
 int32_t xn_debug_check_guards(xn_ctx* c) {
     if (!ctx_ok(c)) return XN_ERR_HANDLE;
     std::lock_guard<std::mutex> g(c->mu);
