@@ -435,54 +435,76 @@ prefill_tf32_kernel(const __grid_constant__ CUtensorMap k_map,
             // are the caller's own and need no wait
             if (!rope) pdl_wait();
             const float* qbase = a.q + size_t(h) * a.q_hs;
-            // eight rows at a time: all their loads are issued before the first is used
+            if (!rope) {
+                // sixteen rows, one 16-byte chunk per lane and row, all loads issued before the first use
+                float4 x[16];
 #pragma unroll
-            for (int b = 0; b < 2; ++b) {
-                float4 x[8], y[8], cv[8], sv[8];   // y: the row's other half, read again (an L1 hit)
+                for (int i = 0; i < 16; ++i) {
+                    const int tt = t0 + w8 * 16 + i;
+                    x[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (tt < a.seq_len && lane < n_ch) x[i] = ldg_keep(qbase + size_t(tt) * a.q_ts + lane * 4);
+                }
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const int rr = w8 * 16 + i;
+                    uint4 xr;   // rows past the end and chunks past head_dim were loaded as zeros
+                    xr.x = round_tf32(__float_as_uint(x[i].x));
+                    xr.y = round_tf32(__float_as_uint(x[i].y));
+                    xr.z = round_tf32(__float_as_uint(x[i].z));
+                    xr.w = round_tf32(__float_as_uint(x[i].w));
+                    reinterpret_cast<uint4*>(qs)[rr * 32 + (lane ^ (rr & 31))] = xr;
+                }
+            } else {
+                // Rotating: a lane owns pair-chunk p of a row: it loads x[4p..4p+3], x[D/2 + 4p..], and
+                // the cos and sin chunks of the row's position, and produces both rotated chunks.
+                // half_ch lanes cover a row, so one instruction serves 32 / half_ch rows (2 for
+                // head_dim 128, 4 for 64); the 16 rows of the warp take 8 (4) such steps, whose loads
+                // are all issued before the first is used.
+                const int pch = lane & (half_ch - 1);
+                const int rsub = lane / half_ch;
+                const int rows_per_step = 32 / half_ch;
+                const int n_steps = 16 / rows_per_step;
+                const int half = D >> 1;
+                float4 lo[8], hi[8], cv[8], sv[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
-                    const int tt = t0 + w8 * 16 + b * 8 + i;
-                    const bool act = tt < a.seq_len && lane < n_ch;
-                    x[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    y[i] = x[i];
-                    cv[i] = x[i];
-                    sv[i] = x[i];
-                    if (act) {
-                        x[i] = ldg_keep(qbase + size_t(tt) * a.q_ts + lane * 4);
-                        if (rope) {
-                            const size_t trow = size_t(a.index_pos + tt) * size_t(D >> 1) + size_t(lane & (half_ch - 1)) * 4;
-                            y[i] = ldg_keep(qbase + size_t(tt) * a.q_ts + (lane ^ half_ch) * 4);
-                            cv[i] = ldg_keep(a.cos_t + trow);
-                            sv[i] = ldg_keep(a.sin_t + trow);
-                        }
+                    const int tt = t0 + w8 * 16 + i * rows_per_step + rsub;
+                    lo[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    hi[i] = lo[i];
+                    cv[i] = lo[i];
+                    sv[i] = lo[i];
+                    if (i < n_steps && tt < a.seq_len) {
+                        const float* qrow = qbase + size_t(tt) * a.q_ts + pch * 4;
+                        const size_t trow = size_t(a.index_pos + tt) * size_t(half) + size_t(pch) * 4;
+                        lo[i] = ldg_keep(qrow);
+                        hi[i] = ldg_keep(qrow + half);
+                        cv[i] = ldg_keep(a.cos_t + trow);
+                        sv[i] = ldg_keep(a.sin_t + trow);
                     }
                 }
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
-                    const int rr = w8 * 16 + b * 8 + i;
-                    float4 v = x[i];
-                    if (rope) {
-                        const float4 c4 = cv[i], s4 = sv[i];
-                        // the append kernel's arithmetic (unfused): lo' = lo c - hi s, hi' = lo s + hi c
-                        if ((lane & half_ch) == 0) {
-                            v.x = __fsub_rn(__fmul_rn(v.x, c4.x), __fmul_rn(y[i].x, s4.x));
-                            v.y = __fsub_rn(__fmul_rn(v.y, c4.y), __fmul_rn(y[i].y, s4.y));
-                            v.z = __fsub_rn(__fmul_rn(v.z, c4.z), __fmul_rn(y[i].z, s4.z));
-                            v.w = __fsub_rn(__fmul_rn(v.w, c4.w), __fmul_rn(y[i].w, s4.w));
-                        } else {
-                            v.x = __fadd_rn(__fmul_rn(y[i].x, s4.x), __fmul_rn(v.x, c4.x));
-                            v.y = __fadd_rn(__fmul_rn(y[i].y, s4.y), __fmul_rn(v.y, c4.y));
-                            v.z = __fadd_rn(__fmul_rn(y[i].z, s4.z), __fmul_rn(v.z, c4.z));
-                            v.w = __fadd_rn(__fmul_rn(y[i].w, s4.w), __fmul_rn(v.w, c4.w));
-                        }
+                    if (i >= n_steps) break;
+                    const int rr = w8 * 16 + i * rows_per_step + rsub;
+                    // the append kernel's arithmetic (unfused): lo' = lo c - hi s, hi' = lo s + hi c
+                    uint4 l4, h4;
+                    l4.x = round_tf32(__float_as_uint(__fsub_rn(__fmul_rn(lo[i].x, cv[i].x), __fmul_rn(hi[i].x, sv[i].x))));
+                    l4.y = round_tf32(__float_as_uint(__fsub_rn(__fmul_rn(lo[i].y, cv[i].y), __fmul_rn(hi[i].y, sv[i].y))));
+                    l4.z = round_tf32(__float_as_uint(__fsub_rn(__fmul_rn(lo[i].z, cv[i].z), __fmul_rn(hi[i].z, sv[i].z))));
+                    l4.w = round_tf32(__float_as_uint(__fsub_rn(__fmul_rn(lo[i].w, cv[i].w), __fmul_rn(hi[i].w, sv[i].w))));
+                    h4.x = round_tf32(__float_as_uint(__fadd_rn(__fmul_rn(lo[i].x, sv[i].x), __fmul_rn(hi[i].x, cv[i].x))));
+                    h4.y = round_tf32(__float_as_uint(__fadd_rn(__fmul_rn(lo[i].y, sv[i].y), __fmul_rn(hi[i].y, cv[i].y))));
+                    h4.z = round_tf32(__float_as_uint(__fadd_rn(__fmul_rn(lo[i].z, sv[i].z), __fmul_rn(hi[i].z, cv[i].z))));
+                    h4.w = round_tf32(__float_as_uint(__fadd_rn(__fmul_rn(lo[i].w, sv[i].w), __fmul_rn(hi[i].w, cv[i].w))));
+                    uint4* row = reinterpret_cast<uint4*>(qs) + rr * 32;
+                    row[pch ^ (rr & 31)] = l4;
+                    row[(pch + half_ch) ^ (rr & 31)] = h4;
+                    // chunks past head_dim (head_dim 64: chunks 16..31) must read as zeros
+                    if (n_ch < 32) {
+                        const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+                        row[(pch + 2 * half_ch) ^ (rr & 31)] = z;
+                        row[(pch + 3 * half_ch) ^ (rr & 31)] = z;
                     }
-                    // rows past the end and chunks past head_dim were loaded as zeros
-                    uint4 xr;
-                    xr.x = round_tf32(__float_as_uint(v.x));
-                    xr.y = round_tf32(__float_as_uint(v.y));
-                    xr.z = round_tf32(__float_as_uint(v.z));
-                    xr.w = round_tf32(__float_as_uint(v.w));
-                    reinterpret_cast<uint4*>(qs)[rr * 32 + (lane ^ (rr & 31))] = xr;
                 }
             }
             wg_barrier();
