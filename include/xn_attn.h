@@ -152,6 +152,7 @@ typedef struct xn_stats {
     uint64_t coalesced_max;    /* largest number of blocking callers merged into one batch      */
     uint64_t out_proj_rows;    /* token rows run through a projection block (q/k/v or output)   */
     uint64_t plan_reuses;      /* decode submissions that reused the previous one's plan        */
+    uint64_t out_transfers;    /* submissions whose page-locked outputs left in one transfer    */
 } xn_stats;
 
 /* ---- context --------------------------------------------------------------------------------- */

@@ -230,16 +230,25 @@ def test_seq_major_layout(ctx2b):
     p.st.destroy()
 
 
-def test_concurrent_blocking_callers_are_coalesced():
+@pytest.mark.parametrize("out_slab", [False, True])
+def test_concurrent_blocking_callers_are_coalesced(out_slab):
     # one thread per stream, each blocking in xn_attention per layer, as the reference's server
     # slots and batch_bench do; results must equal the one-by-one oracle.  The context waits up to
     # 50 ms for all of its live streams to show up, which makes the merge deterministic here.
+    # out_slab: the group's outputs are collected in one page-locked slab and leave the device in
+    # one transfer (the library does that for groups above 128 KB; forced here for eight callers).
+    import os
     import threading
 
     rng = np.random.default_rng(47)
     n, steps = 8, 6
-    ctx = xn.Context(num_layers=3, num_heads=20, num_kv_heads=5, head_dim=128, pool_pages=32,
-                     prefill_mode=F32, batch_window_us=50000)
+    if out_slab:
+        os.environ["XORNET_ATTN_OUT_DMA_MIN_BYTES"] = "0"
+    try:
+        ctx = xn.Context(num_layers=3, num_heads=20, num_kv_heads=5, head_dim=128, pool_pages=32,
+                         prefill_mode=F32, batch_window_us=50000)
+    finally:
+        os.environ.pop("XORNET_ATTN_OUT_DMA_MIN_BYTES", None)
     pairs = [Pair(ctx, 512) for _ in range(n)]
     data = [[rand_qkv(rng, 20, 5, 1, 128) for _ in range(steps)] for _ in range(n)]
     got = [[None] * steps for _ in range(n)]
@@ -266,6 +275,7 @@ def test_concurrent_blocking_callers_are_coalesced():
     stats = ctx.stats()
     assert stats["coalesced_max"] == n, stats
     assert stats["batches"] == steps, stats   # one merged submission per step
+    assert stats["out_transfers"] == (steps if out_slab else 0), stats
     ctx.close()
 
 

@@ -124,3 +124,43 @@ def test_reuse_can_be_switched_off_and_changes_no_bit():
         outs.append(np.stack(res))
         ctx.close()
     assert np.array_equal(outs[0], outs[1])
+
+
+def test_page_locked_outputs_back_to_back_or_scattered_give_the_same_bits():
+    """Outputs of page-locked callers that form one run of host memory are produced in a device
+    buffer and copied home in one transfer; scattered outputs are stored by the kernel directly.
+    Same bits either way, with and without plan reuse, and the oracle's result."""
+    lens = [100, 65, 400, 31, 257]
+    n = len(lens)
+    pos = [L - 1 for L in lens]
+    results = []
+    for scattered in (False, True):
+        os.environ["XORNET_ATTN_OUT_DMA_MIN_BYTES"] = "0"     # small rows here: take the transfer at any size
+        try:
+            ctx = xn.Context(LAYERS, Hq, Hkv, D, pool_pages=64)
+        finally:
+            del os.environ["XORNET_ATTN_OUT_DMA_MIN_BYTES"]
+        sts = [ctx.new_stream(512) for _ in lens]
+        for i, st in enumerate(sts):
+            st.fill_normal(-1, 0, lens[i] - 1, 600 + i)
+        gen = torch.Generator().manual_seed(21)
+        outs = []
+        for layer in range(LAYERS):
+            q = torch.randn(n, Hq, 1, D, generator=gen).pin_memory()
+            k = torch.randn(n, Hkv, 1, D, generator=gen).pin_memory()
+            v = torch.randn(n, Hkv, 1, D, generator=gen).pin_memory()
+            width = Hq * D + (48 if scattered else 0)          # a gap between two requests' outputs
+            o = torch.full((n, width), 7.0).pin_memory()
+            b = ctx.make_batch([(sts[i], layer, pos[i], 1, q[i].data_ptr(), k[i].data_ptr(), v[i].data_ptr(),
+                                 o[i].data_ptr()) for i in range(n)], xn.REQ_HOST_PINNED)
+            ctx.submit(b)
+            got = o[:, :Hq * D].numpy().reshape(n, Hq, 1, D).copy()
+            assert scattered is False or bool((o[:, Hq * D:] == 7.0).all())    # the gaps stay untouched
+            for i, w in enumerate(_oracle_step(sts, layer, pos, q.numpy(), k.numpy(), v.numpy())):
+                assert_parity(got[i], w, f"scattered={scattered} layer {layer} stream {i}")
+            outs.append(got)
+        assert ctx.stats()["plan_reuses"] == LAYERS - 1
+        assert ctx.stats()["out_transfers"] == (0 if scattered else LAYERS)
+        results.append(np.stack(outs))
+        ctx.close()
+    assert np.array_equal(results[0], results[1])

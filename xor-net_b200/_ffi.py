@@ -33,7 +33,7 @@ class Stats(C.Structure):
     _fields_ = [(n, C.c_uint64) for n in (
         "calls", "batches", "kernel_launches", "decode_launches", "prefill_launches", "h2d_bytes",
         "d2h_bytes", "pages_total", "pages_in_use", "streams_live", "device_wait_errors",
-        "coalesced_max", "out_proj_rows", "plan_reuses")]
+        "coalesced_max", "out_proj_rows", "plan_reuses", "out_transfers")]
 
 
 class QkvProjDesc(C.Structure):

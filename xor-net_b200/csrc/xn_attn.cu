@@ -10,6 +10,8 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <atomic>
+#include <thread>
 #include <mutex>
 #include <string>
 #include <unordered_set>
@@ -67,6 +69,8 @@ struct PlanCache {
     size_t o_req = 0, o_unit = 0, o_item = 0, o_cta = 0, o_page = 0;
     int ctas = 0;
     uint64_t h2d_bytes = 0, d2h_bytes = 0;   // what the kernel moves over PCIe itself (page-locked callers)
+    bool out_dma = false;                    // outputs staged on the device, one copy to the host behind the kernel
+    size_t out_bytes = 0;                    // of all requests together
     ReqPatchTable table;
 };
 
@@ -92,7 +96,18 @@ struct OutRun {
 // One blocking caller of xn_attention waiting in the context's queue.  Every caller sleeps on its
 // own condition variable: waking sixty-four slot threads one by one costs less than letting them
 // all fight for one lock.
+// Page-locked rows that collect the outputs of one merged group of blocking callers back to back,
+// so that they leave the device in one transfer; every caller then copies its own row out.  Two of
+// them alternate: a slab is handed to a new group only after the last caller of the group that
+// used it before has taken its row.
+struct OutSlab {
+    unsigned char* host = nullptr;
+    size_t cap = 0;
+    std::atomic<int> readers{0};
+};
+
 struct Pending {
+    OutSlab* slab = nullptr;     // set when `req.out` points into a slab: decrement `readers` when done
     xn_req req;
     int32_t status = XN_OK;
     bool done = false;      // served: status is final          (guarded by the context's q_mu)
@@ -189,6 +204,14 @@ struct xn_ctx {
     PlanSlot slots[kPlanSlots];
     int next_slot = 0;
     float* q_rot = nullptr;    size_t q_rot_cap = 0;      // floats
+    // Outputs of page-locked callers whose `out` tensors lie back to back in host memory are
+    // produced here and leave with ONE copy-engine transfer: stores of the SMs into host memory
+    // cross PCIe at about a third of that rate.
+    float* out_stage = nullptr; size_t out_stage_cap = 0; // floats
+    bool pinned_out_dma = true;
+    size_t out_dma_min_bytes = 128 << 10;   // below this the kernels' own stores are quicker than a transfer
+    OutSlab slabs[2];
+    int slab_next = 0;
     float* partials = nullptr; size_t partials_cap = 0;   // floats
     // attention output block (sub-norm + ternary o_proj)
     std::vector<OutProj> out_proj;                         // per layer
@@ -797,11 +820,20 @@ bool submit_reusing_plan(xn_ctx* c, int n, const xn_req* reqs, bool host_mode, i
              reinterpret_cast<uintptr_t>(r.v)) & 15)
             return false;
     }
+    // outputs staged on the device (one copy home) only while they are still one run of host memory
+    const size_t row_bytes = size_t(c->num_heads) * c->head_dim * 4;
+    bool out_dma = pc.out_dma;
+    for (int i = 1; i < n && out_dma; ++i)
+        if (reinterpret_cast<unsigned char*>(reqs[i].out) != reinterpret_cast<unsigned char*>(reqs[0].out) + size_t(i) * row_bytes)
+            out_dma = false;
+    if (out_dma != pc.out_dma) return false;
     auto run = [&]() -> int32_t {
         ReqPatchTable& t = pc.table;
         t.n = n;
         t.layer = layer;
-        for (int i = 0; i < n; ++i) t.e[i] = {reqs[i].q, reqs[i].k, reqs[i].v, reqs[i].out};
+        for (int i = 0; i < n; ++i)
+            t.e[i] = {reqs[i].q, reqs[i].k, reqs[i].v,
+                      out_dma ? c->out_stage + size_t(i) * (row_bytes / 4) : reqs[i].out};
         const unsigned char* dev = pc.slot->dev;
         int32_t rc;
         SplitKernel k = pick_split(c->nv_class, c->gt, c->nv_exact);
@@ -815,6 +847,10 @@ bool submit_reusing_plan(xn_ctx* c, int n, const xn_req* reqs, bool host_mode, i
         t.n = 0;
         XN_CUDA(c, cudaGetLastError());
         if (c->profile && (rc = profile_end(c)) != XN_OK) return rc;
+        if (out_dma) {
+            XN_CUDA(c, cudaMemcpyAsync(reqs[0].out, c->out_stage, size_t(n) * row_bytes, cudaMemcpyDeviceToHost, c->stream));
+            c->stats.out_transfers += 1;
+        }
         for (int i = 0; i < n; ++i) {
             int64_t& hw = reqs[i].stream->hw[size_t(layer)];
             hw = std::max(hw, reqs[i].index_pos + 1);
@@ -944,6 +980,26 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         return fail(c, XN_ERR_CAPACITY, "%lld attention rows in one submission exceed the limit %lld",
                     n_units, kMaxUnits);
 
+    // Page-locked callers whose outputs are one contiguous run of host memory (a batch tensor, a
+    // prompt's output): the kernels write into a device buffer and one transfer carries it home.
+    bool out_dma = pinned && c->pinned_out_dma;
+    size_t out_dma_bytes = 0;
+    float* out_dma_host = nullptr;
+    if (out_dma) {
+        for (int i = 0; i < n; ++i) {
+            const xn_req& r = reqs[i];
+            if (r.seq_len == 0) continue;
+            const size_t of = (r.flags & XN_REQ_OUT_PROJ)
+                                  ? size_t(r.seq_len) * c->out_proj[size_t(r.layer)].out_dim
+                                  : size_t(Hq) * r.seq_len * D;
+            if (!out_dma_host) out_dma_host = r.out;
+            if (reinterpret_cast<unsigned char*>(r.out) != reinterpret_cast<unsigned char*>(out_dma_host) + out_dma_bytes ||
+                (of & 3)) { out_dma = false; break; }
+            out_dma_bytes += of * 4;
+        }
+        if (!out_dma_host || out_dma_bytes < c->out_dma_min_bytes) out_dma = false;
+    }
+
     // Small staged calls skip the two DMA copies: the library's page-locked staging buffer is
     // device-accessible, so the kernels read the inputs from it and write the outputs into it
     // over PCIe themselves; what remains is one plan upload, the launches and the wait.
@@ -955,6 +1011,7 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         if ((rc = grow_device(c, &c->attn_seq, &c->attn_seq_cap, out_rows * size_t(Hq) * D)) != XN_OK) return rc;
     }
     if (qkv_rows && (rc = grow_device(c, &c->qkv_seq, &c->qkv_seq_cap, qkv_rows * qkv_width)) != XN_OK) return rc;
+    if (out_dma && (rc = grow_device(c, &c->out_stage, &c->out_stage_cap, out_dma_bytes / 4)) != XN_OK) return rc;
     if (host_mode && (rc = grow_io(c, io_in + io_out)) != XN_OK) return rc;
     unsigned char* const io_base = stage_direct ? c->io_host : c->io_dev;
 
@@ -986,6 +1043,8 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         const size_t qf = size_t(Hq) * S * D, kvf = size_t(Hkv) * S * D;
         const float *q_dev = r.q, *k_dev = r.k, *v_dev = r.v;
         float* o_dev = r.out;
+        if (out_dma) o_dev = c->out_stage + (reinterpret_cast<unsigned char*>(r.out) -
+                                             reinterpret_cast<unsigned char*>(out_dma_host)) / 4;
         const bool qkv = r.flags & XN_REQ_QKV_PROJ;
         if (host_mode && !pinned) {
             if (qkv) {
@@ -1278,6 +1337,8 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
                 pc.host_mode = host_mode; pc.pinned = pinned; pc.slot = slot;
                 pc.o_req = o_req; pc.o_unit = o_unit; pc.o_item = o_item; pc.o_cta = o_cta; pc.o_page = o_page;
                 pc.ctas = sp.ctas;
+                pc.out_dma = out_dma;
+                pc.out_bytes = out_dma_bytes;
                 pc.h2d_bytes = pinned ? uint64_t(n) * size_t(Hq + 2 * Hkv) * D * 4 : 0;
                 pc.d2h_bytes = pinned ? uint64_t(n) * size_t(Hq) * D * 4 : 0;
             }
@@ -1360,6 +1421,10 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
         if (c->profile && (rc = profile_end(c)) != XN_OK) return rc;
     }
 
+    if (out_dma) {
+        XN_CUDA(c, cudaMemcpyAsync(out_dma_host, c->out_stage, out_dma_bytes, cudaMemcpyDeviceToHost, c->stream));
+        c->stats.out_transfers += 1;
+    }
     if (host_mode) {
         if (io_out) {
             if (!stage_direct)
@@ -1411,6 +1476,48 @@ void run_group(xn_ctx* c, std::vector<Pending*>& group) {
         }
     }
     c->stats.coalesced_max = std::max<uint64_t>(c->stats.coalesced_max, ok[0].size() + ok[1].size());
+    // Callers that went through their streams' call buffers: re-point their outputs at one slab,
+    // back to back, when the group is large enough for one transfer to beat the kernels' own
+    // stores into host memory.
+    {
+        const size_t row = size_t(c->num_heads) * c->head_dim * 4;
+        bool all_staged = c->pinned_out_dma && !ok[1].empty() && ok[1].size() * row >= c->out_dma_min_bytes;
+        for (Pending* p : ok_p[1]) all_staged = all_staged && p->user_out != nullptr && p->out_bytes == row;
+        if (all_staged) {
+            OutSlab& sl = c->slabs[c->slab_next];
+            const auto t0 = std::chrono::steady_clock::now();
+            while (sl.readers.load(std::memory_order_acquire) > 0 &&
+                   std::chrono::steady_clock::now() - t0 < std::chrono::milliseconds(2))
+                std::this_thread::yield();
+            bool usable = sl.readers.load(std::memory_order_acquire) == 0;
+            const size_t need = ok[1].size() * row;
+            if (usable && sl.cap < need) {
+                if (sl.host) cudaFreeHost(sl.host);
+                sl.host = nullptr;
+                sl.cap = 0;
+                void* p = nullptr;
+                const size_t want = std::max(need * 2, size_t(1) << 20);
+                if (cudaSetDevice(c->device) == cudaSuccess &&
+                    cudaHostAlloc(&p, want, cudaHostAllocMapped | cudaHostAllocPortable) == cudaSuccess) {
+                    sl.host = static_cast<unsigned char*>(p);
+                    sl.cap = want;
+                } else {
+                    cudaGetLastError();
+                    usable = false;
+                }
+            }
+            if (usable) {
+                c->slab_next ^= 1;
+                sl.readers.store(int(ok[1].size()), std::memory_order_release);
+                for (size_t i = 0; i < ok[1].size(); ++i) {
+                    float* dst = reinterpret_cast<float*>(sl.host + i * row);
+                    ok[1][i].out = dst;
+                    ok_p[1][i]->req.out = dst;
+                    ok_p[1][i]->slab = &sl;
+                }
+            }
+        }
+    }
     for (int kind = 1; kind >= 0; --kind) {
         if (ok[kind].empty()) continue;
         int32_t rc = submit_locked(c, int(ok[kind].size()), ok[kind].data(), true);
@@ -1507,6 +1614,7 @@ int32_t attention_blocking(xn_ctx* c, const xn_req& req) {
     }
     lk.unlock();
     if (me.user_out && me.status == XN_OK) memcpy(me.user_out, me.req.out, me.out_bytes);
+    if (me.slab) me.slab->readers.fetch_sub(1, std::memory_order_release);
     return me.status;
 }
 
@@ -1613,6 +1721,8 @@ int32_t xn_ctx_create(const xn_ctx_desc* d, xn_ctx** out_ctx) {
     if (const char* env = getenv("XORNET_ATTN_FUSE_APPEND")) c->fuse_append = atoi(env) != 0;
     if (const char* env = getenv("XORNET_ATTN_FUSE_PINNED")) c->fuse_pinned = atoi(env) != 0;
     if (const char* env = getenv("XORNET_ATTN_PLAN_REUSE")) c->plan_reuse = atoi(env) != 0;
+    if (const char* env = getenv("XORNET_ATTN_PINNED_OUT_DMA")) c->pinned_out_dma = atoi(env) != 0;
+    if (const char* env = getenv("XORNET_ATTN_OUT_DMA_MIN_BYTES")) c->out_dma_min_bytes = size_t(std::max(0ll, atoll(env)));
     if (const char* env = getenv("XORNET_ATTN_PREFILL_ROPE_Q")) c->pf_rope_q = atoi(env) != 0;
     if (const char* env = getenv("XORNET_ATTN_PREFILL_MULTI")) c->pf_multi = atoi(env) != 0;
     if (const char* env = getenv("XORNET_ATTN_STAGE_DIRECT_BYTES")) c->stage_direct_bytes = size_t(atoll(env));
@@ -1788,6 +1898,9 @@ int32_t xn_ctx_destroy(xn_ctx* c) {
     guarded_free(c, c->attn_seq);
     guarded_free(c, c->q8);
     guarded_free(c, c->q_rot);
+    if (c->out_stage) guarded_free(c, c->out_stage);
+    for (OutSlab& sl : c->slabs)
+        if (sl.host) cudaFreeHost(sl.host);
     guarded_free(c, c->partials);
     if (c->io_host) cudaFreeHost(c->io_host);
     guarded_free(c, c->io_dev);

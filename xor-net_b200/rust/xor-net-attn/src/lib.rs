@@ -68,7 +68,7 @@ pub struct XnStats {
     pub calls: u64, pub batches: u64, pub kernel_launches: u64, pub decode_launches: u64,
     pub prefill_launches: u64, pub h2d_bytes: u64, pub d2h_bytes: u64, pub pages_total: u64,
     pub pages_in_use: u64, pub streams_live: u64, pub device_wait_errors: u64, pub coalesced_max: u64,
-    pub out_proj_rows: u64, pub plan_reuses: u64,
+    pub out_proj_rows: u64, pub plan_reuses: u64, pub out_transfers: u64,
 }
 
 /// Request flags of `xn_req.flags` (include/xn_attn.h).
