@@ -212,6 +212,10 @@ struct xn_ctx {
     size_t out_dma_min_bytes = 128 << 10;   // below this the kernels' own stores are quicker than a transfer
     OutSlab slabs[2];
     int slab_next = 0;
+    // Merged groups of blocking callers are enqueued under the context's lock and waited for
+    // outside it (one event each), so that the next group's kernels queue up behind them.
+    bool defer_groups = true;
+    std::vector<cudaEvent_t> done_events;   // idle events
     float* partials = nullptr; size_t partials_cap = 0;   // floats
     // attention output block (sub-norm + ternary o_proj)
     std::vector<OutProj> out_proj;                         // per layer
@@ -253,6 +257,13 @@ struct xn_ctx {
     bool leader_active = false;
     size_t last_group = 1;          // callers merged into the previous submission
     bool leader_in_window = false;  // the leader is waiting for company: arrivals tell it
+    // Groups whose kernels are enqueued but not finished (guarded by q_mu).  A leader that is
+    // promoted while one is in flight enqueues behind it only once its own group is as large as
+    // the one its callers formed last time (groups alternate: the size two groups back);
+    // otherwise it keeps collecting until the GPU is idle.  At most two groups are in flight.
+    int in_flight = 0;
+    size_t group_before_last = 1;
+    std::condition_variable flight_cv;
 };
 
 namespace {
@@ -803,7 +814,8 @@ PrefillArgs make_prefill_args(const xn_ctx* c, const ReqDev& d, const int* pages
 // same order, at the same positions, one token each, all on one layer (any layer), nothing to
 // zero-fill.  Launches the attention kernel over the kept plan with this call's addresses and layer
 // as a kernel parameter.  Returns false when the submission does not match (nothing was touched).
-bool submit_reusing_plan(xn_ctx* c, int n, const xn_req* reqs, bool host_mode, int32_t* rc_out) {
+bool submit_reusing_plan(xn_ctx* c, int n, const xn_req* reqs, bool host_mode, int32_t* rc_out,
+                         cudaEvent_t defer) {
     PlanCache& pc = c->pcache;
     if (!pc.valid || !c->plan_reuse || n != int(pc.ent.size()) || host_mode != pc.host_mode) return false;
     const bool pinned = host_mode && (reqs[0].flags & XN_REQ_HOST_PINNED);
@@ -864,7 +876,9 @@ bool submit_reusing_plan(xn_ctx* c, int n, const xn_req* reqs, bool host_mode, i
         c->stats.plan_reuses += 1;
         c->stats.h2d_bytes += pc.h2d_bytes;
         c->stats.d2h_bytes += pc.d2h_bytes;
-        if (host_mode) {
+        if (host_mode && defer) {   // the caller waits for this event outside the context's lock
+            XN_CUDA(c, cudaEventRecord(defer, c->stream));
+        } else if (host_mode) {
             XN_CUDA(c, cudaStreamSynchronize(c->stream));
             if ((rc = check_device_status(c)) != XN_OK) return rc;
         }
@@ -874,12 +888,16 @@ bool submit_reusing_plan(xn_ctx* c, int n, const xn_req* reqs, bool host_mode, i
     return true;
 }
 
-int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
+// defer: (page-locked host pointers only) do not wait for the GPU: record this event behind the
+// submission's last operation and return; the caller synchronises on it without holding the
+// context's lock, so that the next group of blocking callers can be enqueued meanwhile, and then
+// reads the device status itself.
+int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode, cudaEvent_t defer = nullptr) {
     const int Hq = c->num_heads, Hkv = c->num_kv_heads, D = c->head_dim, nv = c->nv;
     XN_CUDA(c, cudaSetDevice(c->device));
     {
         int32_t rc;
-        if (n > 0 && submit_reusing_plan(c, n, reqs, host_mode, &rc)) return rc;
+        if (n > 0 && submit_reusing_plan(c, n, reqs, host_mode, &rc, defer)) return rc;
     }
 
     // host memory that is page-locked and device-mapped is read and written by the kernels directly
@@ -1438,6 +1456,10 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
     c->stats.batches += 1;
     c->stats.calls += uint64_t(n);
 
+    if (host_mode && pinned && defer) {
+        XN_CUDA(c, cudaEventRecord(defer, c->stream));
+        return XN_OK;
+    }
     if (host_mode) {
         XN_CUDA(c, cudaStreamSynchronize(c->stream));
         if ((rc = check_device_status(c)) != XN_OK) return rc;
@@ -1459,7 +1481,14 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode) {
 // stream already in the group, get their own status and are left out.  The others go out as one
 // submission per kind of memory they point at (the streams' page-locked call buffers, or pageable
 // memory that the library stages).
-void run_group(xn_ctx* c, std::vector<Pending*>& group) {
+// What the leader of a group still has to wait for after run_group returned: the page-locked part
+// of the group is only enqueued; `ev` fires behind its last operation.
+struct GroupWait {
+    cudaEvent_t ev = nullptr;
+    std::vector<Pending*> members;
+};
+
+void run_group(xn_ctx* c, std::vector<Pending*>& group, GroupWait* wait) {
     std::lock_guard<std::mutex> g(c->mu);
     std::vector<xn_req> ok[2];   // [0] pageable, [1] page-locked
     std::vector<Pending*> ok_p[2];
@@ -1484,11 +1513,11 @@ void run_group(xn_ctx* c, std::vector<Pending*>& group) {
         bool all_staged = c->pinned_out_dma && !ok[1].empty() && ok[1].size() * row >= c->out_dma_min_bytes;
         for (Pending* p : ok_p[1]) all_staged = all_staged && p->user_out != nullptr && p->out_bytes == row;
         if (all_staged) {
+            // a slab whose previous group has not finished reading is passed over (never waited
+            // for: this runs under the context's lock, which that group's leader needs to finish);
+            // with both busy the group's outputs go to the call buffers as before
+            if (c->slabs[c->slab_next].readers.load(std::memory_order_acquire) > 0) c->slab_next ^= 1;
             OutSlab& sl = c->slabs[c->slab_next];
-            const auto t0 = std::chrono::steady_clock::now();
-            while (sl.readers.load(std::memory_order_acquire) > 0 &&
-                   std::chrono::steady_clock::now() - t0 < std::chrono::milliseconds(2))
-                std::this_thread::yield();
             bool usable = sl.readers.load(std::memory_order_acquire) == 0;
             const size_t need = ok[1].size() * row;
             if (usable && sl.cap < need) {
@@ -1520,8 +1549,27 @@ void run_group(xn_ctx* c, std::vector<Pending*>& group) {
     }
     for (int kind = 1; kind >= 0; --kind) {
         if (ok[kind].empty()) continue;
-        int32_t rc = submit_locked(c, int(ok[kind].size()), ok[kind].data(), true);
+        // the page-locked part (callers that came through their call buffers) is enqueued and
+        // waited for outside this lock; the pageable part shares one staging area and stays inside
+        cudaEvent_t ev = nullptr;
+        if (kind == 1 && wait && c->defer_groups) {
+            if (!c->done_events.empty()) {
+                ev = c->done_events.back();
+                c->done_events.pop_back();
+            } else if (cudaSetDevice(c->device) != cudaSuccess ||
+                       cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess) {
+                cudaGetLastError();
+                ev = nullptr;
+            }
+        }
+        int32_t rc = submit_locked(c, int(ok[kind].size()), ok[kind].data(), true, ev);
         for (Pending* p : ok_p[kind]) p->status = rc;
+        if (ev && rc == XN_OK) {
+            wait->ev = ev;
+            wait->members = ok_p[kind];
+        } else if (ev) {
+            c->done_events.push_back(ev);
+        }
         // The callers are independent, as in the reference: when the merged submission was
         // refused before anything ran (it left the streams untouched), one request that does not
         // fit must not fail the others.  Run them one by one; each gets its own status.
@@ -1581,6 +1629,7 @@ int32_t attention_blocking(xn_ctx* c, const xn_req& req) {
     c->queue.push_back(&me);
     if (c->leader_active) {
         if (c->leader_in_window) c->q_cv.notify_one();
+        c->flight_cv.notify_one();   // a leader may be waiting for its group to fill up
         me.cv.wait(lk, [&] { return me.done || me.promoted; });
     } else {
         c->leader_active = true;
@@ -1595,21 +1644,46 @@ int32_t attention_blocking(xn_ctx* c, const xn_req& req) {
             c->q_cv.wait_for(lk, std::chrono::microseconds(window_us), [&] { return c->queue.size() >= target; });
             c->leader_in_window = false;
         }
+        if (c->in_flight > 0)
+            c->flight_cv.wait(lk, [&] {
+                return c->in_flight == 0 ||
+                       (c->in_flight < 2 && c->queue.size() >= std::max<size_t>(2, c->group_before_last));
+            });
         std::vector<Pending*> group;
         group.swap(c->queue);
+        c->in_flight += 1;
         lk.unlock();
-        run_group(c, group);
+        GroupWait wait;
+        run_group(c, group, &wait);
         lk.lock();
+        c->group_before_last = c->last_group;
         c->last_group = group.size();
+        // The lead passes on BEFORE this group's kernels have finished: whoever arrived meanwhile
+        // (or arrives next) enqueues the next group right behind them.
+        if (c->queue.empty()) {
+            c->leader_active = false;
+        } else {
+            c->queue.front()->promoted = true;
+            c->queue.front()->cv.notify_one();
+        }
+        if (wait.ev) {
+            lk.unlock();
+            const cudaError_t e = cudaEventSynchronize(wait.ev);
+            {
+                std::lock_guard<std::mutex> g(c->mu);
+                int32_t rc = e == cudaSuccess ? check_device_status(c)
+                                              : fail(c, XN_ERR_CUDA, "cudaEventSynchronize: %s", cudaGetErrorString(e));
+                if (rc != XN_OK)
+                    for (Pending* p : wait.members) p->status = rc;
+                c->done_events.push_back(wait.ev);
+            }
+            lk.lock();
+        }
+        c->in_flight -= 1;
+        c->flight_cv.notify_all();
         for (Pending* p : group) {
             p->done = true;
             if (p != &me) p->cv.notify_one();
-        }
-        if (c->queue.empty()) {
-            c->leader_active = false;
-        } else {   // someone arrived while the group ran: that caller leads the next one
-            c->queue.front()->promoted = true;
-            c->queue.front()->cv.notify_one();
         }
     }
     lk.unlock();
@@ -1722,6 +1796,7 @@ int32_t xn_ctx_create(const xn_ctx_desc* d, xn_ctx** out_ctx) {
     if (const char* env = getenv("XORNET_ATTN_FUSE_PINNED")) c->fuse_pinned = atoi(env) != 0;
     if (const char* env = getenv("XORNET_ATTN_PLAN_REUSE")) c->plan_reuse = atoi(env) != 0;
     if (const char* env = getenv("XORNET_ATTN_PINNED_OUT_DMA")) c->pinned_out_dma = atoi(env) != 0;
+    if (const char* env = getenv("XORNET_ATTN_DEFER_GROUPS")) c->defer_groups = atoi(env) != 0;
     if (const char* env = getenv("XORNET_ATTN_OUT_DMA_MIN_BYTES")) c->out_dma_min_bytes = size_t(std::max(0ll, atoll(env)));
     if (const char* env = getenv("XORNET_ATTN_PREFILL_ROPE_Q")) c->pf_rope_q = atoi(env) != 0;
     if (const char* env = getenv("XORNET_ATTN_PREFILL_MULTI")) c->pf_multi = atoi(env) != 0;
@@ -1899,6 +1974,7 @@ int32_t xn_ctx_destroy(xn_ctx* c) {
     guarded_free(c, c->q8);
     guarded_free(c, c->q_rot);
     if (c->out_stage) guarded_free(c, c->out_stage);
+    for (cudaEvent_t ev : c->done_events) cudaEventDestroy(ev);
     for (OutSlab& sl : c->slabs)
         if (sl.host) cudaFreeHost(sl.host);
     guarded_free(c, c->partials);
