@@ -1031,7 +1031,11 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode, cuda
     if (qkv_rows && (rc = grow_device(c, &c->qkv_seq, &c->qkv_seq_cap, qkv_rows * qkv_width)) != XN_OK) return rc;
     if (out_dma && (rc = grow_device(c, &c->out_stage, &c->out_stage_cap, out_dma_bytes / 4)) != XN_OK) return rc;
     if (host_mode && (rc = grow_io(c, io_in + io_out)) != XN_OK) return rc;
-    unsigned char* const io_base = stage_direct ? c->io_host : c->io_dev;
+    // (inputs are read in place either way; outputs above the transfer threshold are produced on the
+    // device and copied into the staging buffer: stores of the SMs into host memory are the slow part)
+    unsigned char* const in_base = stage_direct ? c->io_host : c->io_dev;
+    const bool out_direct = stage_direct && io_out < c->out_dma_min_bytes;
+    unsigned char* const out_base = out_direct ? c->io_host : c->io_dev;
 
     // -- request descriptors, page ids, units
     std::vector<ReqDev> rd(n);
@@ -1068,20 +1072,20 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode, cuda
             if (qkv) {
                 const size_t xf = size_t(S) * c->qkv_proj[size_t(r.layer)].in_dim;
                 memcpy(c->io_host + in_off, r.q, xf * 4);
-                q_dev = reinterpret_cast<const float*>(io_base + in_off);   // x, for now
+                q_dev = reinterpret_cast<const float*>(in_base + in_off);   // x, for now
                 in_off += align_up(xf * 4, 16);
             } else {
                 memcpy(c->io_host + in_off, r.q, qf * 4);
-                q_dev = reinterpret_cast<const float*>(io_base + in_off);
+                q_dev = reinterpret_cast<const float*>(in_base + in_off);
                 in_off += align_up(qf * 4, 16);
                 memcpy(c->io_host + in_off, r.k, kvf * 4);
-                k_dev = reinterpret_cast<const float*>(io_base + in_off);
+                k_dev = reinterpret_cast<const float*>(in_base + in_off);
                 in_off += align_up(kvf * 4, 16);
                 memcpy(c->io_host + in_off, r.v, kvf * 4);
-                v_dev = reinterpret_cast<const float*>(io_base + in_off);
+                v_dev = reinterpret_cast<const float*>(in_base + in_off);
                 in_off += align_up(kvf * 4, 16);
             }
-            o_dev = reinterpret_cast<float*>(io_base + out_off);
+            o_dev = reinterpret_cast<float*>(out_base + out_off);
             out_off += align_up(((r.flags & XN_REQ_OUT_PROJ)
                                      ? size_t(S) * c->out_proj[size_t(r.layer)].out_dim : qf) * 4, 16);
         }
@@ -1445,7 +1449,7 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode, cuda
     }
     if (host_mode) {
         if (io_out) {
-            if (!stage_direct)
+            if (!out_direct)
                 XN_CUDA(c, cudaMemcpyAsync(c->io_host + io_in, c->io_dev + io_in, io_out,
                                            cudaMemcpyDeviceToHost, c->stream));
             c->stats.d2h_bytes += io_out;
