@@ -73,3 +73,49 @@ def test_sharding_helpers_single_process():
     assert sharding.aggregate([1.0], [2.0]) == ([1.0], [2.0])
     with pytest.raises(ValueError):
         sharding.streams_of_rank(4, 2, 2)
+
+
+def _placement_worker(rank, world, port, out):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import bench
+    import xor_net_b200 as xn
+
+    # what every rank of `bench.py --gpus N` does before it builds its streams: ONE global list of
+    # N x 64 lengths (the same seed on every rank), placed by the library's own rule
+    lens = bench.stream_lengths(world * 64, 128, 4096, bench.BASE_SEED + 3000)
+    owners = {p: bench.place_streams(xn, lens, world, p) for p in ("least", "rr")}
+    mine = [i for i, w in enumerate(owners["least"]) if w == rank]
+    gathered = [None] * world
+    dist.all_gather_object(gathered, (owners, mine, int(sum(int(lens[i]) for i in mine))))
+    if rank == 0:
+        out.put((gathered, [int(x) for x in lens]))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_one_global_stream_list_is_placed_identically_on_every_rank(world):
+    """The decode benchmark shards ONE list of streams over the ranks with the device group's
+    placement rule.  Every rank must derive the same owners on its own (no collective on the data
+    path), the ranks' shares must partition the list, and the least-loaded rule must balance the
+    cached tokens better than stream-number-modulo-N does."""
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_placement_worker, args=(r, world, port, out)) for r in range(world)]
+    [p.start() for p in procs]
+    gathered, lens = out.get(timeout=180)
+    [p.join(timeout=60) for p in procs]
+    assert all(p.exitcode == 0 for p in procs)
+    owners0 = gathered[0][0]
+    assert all(g[0] == owners0 for g in gathered)                       # the same plan on every rank
+    assert sorted(i for g in gathered for i in g[1]) == list(range(world * 64))
+    tokens = [g[2] for g in gathered]
+    assert sum(tokens) == sum(lens)
+    assert max(tokens) - min(tokens) <= 4096                             # within one stream of each other
+    rr = [sum(lens[i] for i in range(len(lens)) if owners0["rr"][i] == r) for r in range(world)]
+    assert max(tokens) <= max(rr)
+    assert owners0["rr"] == [i % world for i in range(world * 64)]
