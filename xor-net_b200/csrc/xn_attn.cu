@@ -960,7 +960,10 @@ int32_t submit_locked(xn_ctx* c, int n, const xn_req* reqs, bool host_mode, cuda
             key_rows += (long long)Hkv * c->subs *
                         ((long long)r.seq_len * r.index_pos + (long long)r.seq_len * (r.seq_len + 1) / 2);
         }
-        max_rows = std::max<long long>(max_rows, (long long)r.seq_len * (Hq + 2 * Hkv));
+        // rows the append kernel moves for this request (the query rows stay where they are when
+        // the prefill kernel rotates them itself)
+        max_rows = std::max<long long>(max_rows, (long long)r.seq_len *
+                                                     ((rope_in_prefill(c, r, direct, pinned) ? 0 : Hq) + 2 * Hkv));
         if (pinned) {  // bytes the kernels move over PCIe themselves
             c->stats.h2d_bytes += (qkv ? xf : qf + 2 * kvf) * 4;
             c->stats.d2h_bytes += of * 4;
