@@ -501,3 +501,54 @@ def test_tiled_exact_prefill_equals_the_row_wise_path(Hq, Hkv, D, S, pos):
         ctx.close()
     a, r = errs(outs["1"], outs["0"])
     assert a <= 1e-4 and r <= 1e-5
+
+
+def test_free_running_callers_through_pipelined_groups_and_output_slabs():
+    """Twelve threads, each decoding its own stream layer by layer with no synchronisation between
+    them (the reference's slot threads, server/main.rs:176-199): groups form as callers happen to
+    arrive, a group is enqueued behind the one still running, and (forced here for small rows) the
+    outputs of a group travel through the alternating page-locked slabs.  Every call must still
+    return what the oracle computes for that stream alone."""
+    import os
+    import threading
+
+    rng = np.random.default_rng(4711)
+    n, layers, steps, Hq, Hkv, D = 12, 3, 20, 8, 2, 64
+    os.environ["XORNET_ATTN_OUT_DMA_MIN_BYTES"] = "0"
+    try:
+        ctx = xn.Context(num_layers=layers, num_heads=Hq, num_kv_heads=Hkv, head_dim=D, pool_pages=64)
+    finally:
+        del os.environ["XORNET_ATTN_OUT_DMA_MIN_BYTES"]
+    pairs = [Pair(ctx, 256) for _ in range(n)]
+    start = [int(x) for x in rng.integers(0, 100, n)]
+    for i, p in enumerate(pairs):   # different histories: a prefill of its own length each
+        if start[i]:
+            for layer in range(layers):
+                q, k, v = rand_qkv(rng, Hq, Hkv, start[i], D)
+                p.step(layer, 0, q, k, v)
+    data = [[[rand_qkv(rng, Hq, Hkv, 1, D) for _ in range(layers)] for _ in range(steps)] for _ in range(n)]
+    got = [[[None] * layers for _ in range(steps)] for _ in range(n)]
+    errors = []
+
+    def worker(i):
+        try:
+            for s in range(steps):
+                for layer in range(layers):
+                    got[i][s][layer] = ctx.attention(pairs[i].st, layer, start[i] + s, *data[i][s][layer])
+        except Exception as e:  # pragma: no cover
+            errors.append(e)
+
+    ts = [threading.Thread(target=worker, args=(i,)) for i in range(n)]
+    [t.start() for t in ts]
+    [t.join() for t in ts]
+    assert not errors, errors
+    for i in range(n):
+        for s in range(steps):
+            for layer in range(layers):
+                want = xo.fast_attention(*data[i][s][layer], layer, start[i] + s, pairs[i].ref, Hq, Hkv, D)
+                assert_parity(got[i][s][layer], want, f"thread {i} step {s} layer {layer}")
+    stats = ctx.stats()
+    assert stats["calls"] >= n * steps * layers and stats["device_wait_errors"] == 0
+    print(f"free-running callers: {stats['batches']} batches for {n * steps * layers} calls, "
+          f"largest group {stats['coalesced_max']}, {stats['out_transfers']} output transfers")
+    ctx.close()
