@@ -109,8 +109,12 @@ enum {
                                   /* transpose_heads_to_seq, tensor.rs:356-376)                  */
     XN_REQ_HOST_PINNED = 1u << 3, /* host pointers are page-locked, device-mapped memory         */
                                   /* (cudaHostAlloc / cudaHostRegister): the kernels read the    */
-                                  /* inputs and write the output over PCIe themselves and the    */
-                                  /* library's staging copies are skipped.  The call still       */
+                                  /* inputs over PCIe themselves and the library's staging       */
+                                  /* copies are skipped.  Outputs that lie back to back in host  */
+                                  /* memory (>= 128 KB in all, e.g. one tensor for the batch)    */
+                                  /* are produced on the device and leave in ONE transfer;       */
+                                  /* scattered outputs are stored by the kernels directly, which */
+                                  /* is about three times slower per byte.  The call still       */
                                   /* blocks until the output is complete.  All requests of a     */
                                   /* batch must agree on this flag.                              */
     XN_REQ_OUT_PROJ = 1u << 4,    /* `out` receives [seq_len, out_dim]: the attention output run */
